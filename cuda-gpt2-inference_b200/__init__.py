@@ -1,0 +1,323 @@
+"""B200-native GPT-2 forward engine: Python host side over the C ABI of libb200gpt2.so.
+
+The directory name carries a hyphen, so load it with
+``importlib.util.spec_from_file_location("cuda_gpt2_inference_b200", ".../__init__.py")``
+(see ``__graft_entry__.load_package``).
+
+The functions mirror the reference project's host wrappers one for one - same names, same
+argument order, device buffers owned by the caller, nothing allocated by the callee
+(GJ0407790/CUDA-GPT2-Inference: kernels/matmul/1_matmul_tiling.cuh:57,
+kernels/attention/3_flash_attention_permute.cuh:346, kernels/layernorm/1_layernorm_block.cuh:63,
+kernels/fused_residual_layernorm/fused_residual_layernorm.cuh:88, kernels/residual/1_residual_naive.cuh:15).
+Buffers are torch CUDA tensors (fp32 / int32, contiguous); torch is used only for device
+memory and streams.  There is no CPU fallback: every call goes through the CUDA library and
+raises if it is missing or if the call returns a non-zero status.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+from dataclasses import dataclass
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "lib", "libb200gpt2.so")
+
+B200_OK = 0
+B200_TF32, B200_TF32X3 = 0, 1
+ACT_NONE, ACT_GELU = 0, 1
+
+EXPORTS = (
+    "b200_ctx_create", "b200_ctx_destroy", "b200_ctx_set_stream", "b200_ctx_sync_check",
+    "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
+    "b200_ctx_last_error",
+    "b200_matmul_forward", "b200_attention_forward", "b200_layernorm_forward",
+    "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
+    "b200_encoder_forward",
+    "matmul_forward", "matmul_forward_gelu", "attention_forward", "layernorm_forward",
+    "fused_residual_layernorm_forward", "fused_residual_layernorm", "residual_forward",
+    "gelu_forward", "encoder_forward",
+    "b200_gpt2_param_offsets", "b200_gpt2_create", "b200_gpt2_destroy", "b200_gpt2_params",
+    "b200_gpt2_load_params_host", "b200_gpt2_set_options", "b200_gpt2_forward",
+    "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_activation",
+)
+
+_lib = None
+
+
+class B200Error(RuntimeError):
+    pass
+
+
+def lib() -> C.CDLL:
+    """Loads libb200gpt2.so; raises if it has not been built (no fallback exists)."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise B200Error(f"{LIB_PATH} is missing: build it with `python {os.path.join(_HERE, 'build.py')}`")
+        l = C.CDLL(LIB_PATH)
+        vp, i, sz = C.c_void_p, C.c_int, C.c_size_t
+        l.b200_ctx_create.argtypes = [C.POINTER(vp), i, vp]
+        l.b200_ctx_destroy.argtypes = [vp]
+        l.b200_ctx_set_stream.argtypes = [vp, vp]
+        l.b200_ctx_sync_check.argtypes = [vp]
+        l.b200_ctx_launch_count.argtypes = [vp]
+        l.b200_ctx_launch_count.restype = C.c_uint64
+        l.b200_ctx_reset_launch_count.argtypes = [vp]
+        l.b200_ctx_reset_launch_count.restype = None
+        l.b200_status_string.argtypes = [i]
+        l.b200_status_string.restype = C.c_char_p
+        l.b200_ctx_last_error.argtypes = [vp]
+        l.b200_ctx_last_error.restype = C.c_char_p
+        l.b200_matmul_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, i]
+        l.b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
+        l.b200_layernorm_forward.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i]
+        l.b200_fused_residual_layernorm_forward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i]
+        l.b200_residual_forward.argtypes = [vp, vp, vp, vp, sz]
+        l.b200_gelu_forward.argtypes = [vp, vp, vp, sz]
+        l.b200_encoder_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i]
+        for name, at in (("matmul_forward", [vp, vp, vp, vp, i, i, i, i]),
+                         ("matmul_forward_gelu", [vp, vp, vp, vp, i, i, i, i, i]),
+                         ("attention_forward", [vp, vp, vp, vp, i, i, i, i]),
+                         ("layernorm_forward", [vp, vp, vp, vp, vp, vp, i, i, i]),
+                         ("fused_residual_layernorm_forward", [vp] * 8 + [i, i, i]),
+                         ("fused_residual_layernorm", [vp] * 8 + [i, i, i]),
+                         ("residual_forward", [vp, vp, vp, i]),
+                         ("gelu_forward", [vp, vp, i]),
+                         ("encoder_forward", [vp, vp, vp, vp, i, i, i])):
+            f = getattr(l, name)
+            f.argtypes = at
+            f.restype = None
+        l.b200_gpt2_param_offsets.argtypes = [vp, C.POINTER(sz)]
+        l.b200_gpt2_param_offsets.restype = sz
+        l.b200_gpt2_create.argtypes = [C.POINTER(vp), vp, vp, i, i]
+        l.b200_gpt2_destroy.argtypes = [vp]
+        l.b200_gpt2_params.argtypes = [vp]
+        l.b200_gpt2_params.restype = vp
+        l.b200_gpt2_load_params_host.argtypes = [vp, vp, sz]
+        l.b200_gpt2_set_options.argtypes = [vp, i, i, i, i]
+        l.b200_gpt2_forward.argtypes = [vp, vp, i, i]
+        l.b200_gpt2_logits.argtypes = [vp]
+        l.b200_gpt2_logits.restype = vp
+        l.b200_gpt2_forward_host.argtypes = [vp, vp, i, i, vp, vp, vp]
+        l.b200_gpt2_activation.argtypes = [vp, C.c_char_p]
+        l.b200_gpt2_activation.restype = vp
+        _lib = l
+    return _lib
+
+
+def _ptr(t):
+    """Device (or host) address of a tensor / numpy array / None."""
+    if t is None:
+        return None
+    if hasattr(t, "data_ptr"):
+        if not t.is_contiguous():
+            raise B200Error("tensor must be contiguous")
+        return C.c_void_p(t.data_ptr())
+    return C.c_void_p(t.ctypes.data)
+
+
+class Context:
+    """One context per GPU / host thread: owns the stream binding and the device status word."""
+
+    def __init__(self, device: int = 0, stream=None):
+        self._h = C.c_void_p()
+        self.device = device
+        handle = None
+        if stream is not None:
+            handle = C.c_void_p(stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream))
+        st = lib().b200_ctx_create(C.byref(self._h), device, handle)
+        if st != B200_OK:
+            raise B200Error(f"b200_ctx_create: {lib().b200_status_string(st).decode()}")
+
+    def check(self, st: int, what: str):
+        if st != B200_OK:
+            msg = lib().b200_status_string(st).decode()
+            extra = lib().b200_ctx_last_error(self._h).decode()
+            raise B200Error(f"{what}: {msg}" + (f" ({extra})" if extra else ""))
+
+    def status(self, st: int) -> int:
+        return st
+
+    def set_stream(self, stream):
+        handle = None if stream is None else C.c_void_p(stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream))
+        self.check(lib().b200_ctx_set_stream(self._h, handle), "set_stream")
+
+    def sync_check(self):
+        self.check(lib().b200_ctx_sync_check(self._h), "sync_check")
+
+    def sync_status(self) -> int:
+        return lib().b200_ctx_sync_check(self._h)
+
+    @property
+    def launches(self) -> int:
+        return int(lib().b200_ctx_launch_count(self._h))
+
+    def reset_launches(self):
+        lib().b200_ctx_reset_launch_count(self._h)
+
+    def close(self):
+        if self._h:
+            lib().b200_ctx_destroy(self._h)
+            self._h = C.c_void_p()
+
+    # ---- operators: reference argument order, status-checked ---------------------------
+    def matmul_forward(self, out, inp, weight, bias, B, T, Cc, OC, act=ACT_NONE, residual=None, mode=B200_TF32):
+        self.check(lib().b200_matmul_forward(self._h, _ptr(out), _ptr(inp), _ptr(weight), _ptr(bias), B, T, Cc, OC,
+                                             act, _ptr(residual), mode), "matmul_forward")
+
+    def attention_forward(self, out, qkvr, att, inp, B, T, Cc, NH):
+        self.check(lib().b200_attention_forward(self._h, _ptr(out), _ptr(qkvr), _ptr(att), _ptr(inp), B, T, Cc, NH),
+                   "attention_forward")
+
+    def layernorm_forward(self, out, mean, rstd, inp, weight, bias, B, T, Cc):
+        self.check(lib().b200_layernorm_forward(self._h, _ptr(out), _ptr(mean), _ptr(rstd), _ptr(inp), _ptr(weight),
+                                                _ptr(bias), B, T, Cc), "layernorm_forward")
+
+    def fused_residual_layernorm_forward(self, res_out, layernorm_out, mean, rstd, inp1, inp2, weight, bias, B, T, Cc):
+        self.check(lib().b200_fused_residual_layernorm_forward(self._h, _ptr(res_out), _ptr(layernorm_out), _ptr(mean),
+                                                               _ptr(rstd), _ptr(inp1), _ptr(inp2), _ptr(weight),
+                                                               _ptr(bias), B, T, Cc), "fused_residual_layernorm_forward")
+
+    def residual_forward(self, out, inp1, inp2, N):
+        self.check(lib().b200_residual_forward(self._h, _ptr(out), _ptr(inp1), _ptr(inp2), N), "residual_forward")
+
+    def gelu_forward(self, out, inp, N):
+        self.check(lib().b200_gelu_forward(self._h, _ptr(out), _ptr(inp), N), "gelu_forward")
+
+    def encoder_forward(self, out, inp, wte, wpe, B, T, Cc):
+        self.check(lib().b200_encoder_forward(self._h, _ptr(out), _ptr(inp), _ptr(wte), _ptr(wpe), B, T, Cc),
+                   "encoder_forward")
+
+    def raw(self, name: str, *args) -> int:
+        """Calls b200_<name>(ctx, ...) and returns the status without raising (for error-path tests)."""
+        return getattr(lib(), "b200_" + name)(self._h, *[_ptr(a) if (a is None or hasattr(a, "data_ptr")) else a for a in args])
+
+
+class GPT2ConfigC(C.Structure):
+    _fields_ = [(n, C.c_int) for n in ("max_seq_len", "vocab_size", "padded_vocab_size",
+                                       "num_layers", "num_heads", "channels")]
+
+
+@dataclass(frozen=True)
+class GPT2Config:
+    max_seq_len: int = 1024
+    vocab_size: int = 50257
+    padded_vocab_size: int = 50304
+    num_layers: int = 12
+    num_heads: int = 12
+    channels: int = 768
+
+    def c(self) -> GPT2ConfigC:
+        return GPT2ConfigC(self.max_seq_len, self.vocab_size, self.padded_vocab_size,
+                           self.num_layers, self.num_heads, self.channels)
+
+    def num_params(self) -> int:
+        return param_offsets(self)[16]
+
+    def flops_per_token(self, T: int) -> float:
+        """Forward FLOP per token at sequence length T: GEMMs 2*K*N each, causal-exact attention."""
+        Cc, L, Vp = self.channels, self.num_layers, self.padded_vocab_size
+        gemm = 2.0 * (Cc * 3 * Cc + Cc * Cc + Cc * 4 * Cc + 4 * Cc * Cc) * L + 2.0 * Cc * Vp
+        att = 4.0 * 64 * (T + 1) / 2 * self.num_heads * L
+        return gemm + att
+
+
+GPT2_124M = GPT2Config()
+GPT2_XL = GPT2Config(num_layers=48, num_heads=25, channels=1600)
+
+PARAM_NAMES = ("wte", "wpe", "ln1w", "ln1b", "qkvw", "qkvb", "attprojw", "attprojb",
+               "ln2w", "ln2b", "fcw", "fcb", "fcprojw", "fcprojb", "lnfw", "lnfb")
+
+
+def param_offsets(cfg: GPT2Config) -> list[int]:
+    """Offsets (in floats) of the 16 parameter tensors; pure host arithmetic, same as the C side."""
+    Cc, L, Vp, mT = cfg.channels, cfg.num_layers, cfg.padded_vocab_size, cfg.max_seq_len
+    sizes = [Vp * Cc, mT * Cc, L * Cc, L * Cc, L * 3 * Cc * Cc, L * 3 * Cc, L * Cc * Cc, L * Cc,
+             L * Cc, L * Cc, L * 4 * Cc * Cc, L * 4 * Cc, L * Cc * 4 * Cc, L * Cc, Cc, Cc]
+    offs = [0]
+    for s in sizes:
+        offs.append(offs[-1] + s)
+    return offs
+
+
+def shard_batch(B: int, world_size: int, rank: int) -> tuple[int, int]:
+    """Contiguous batch shard [start, stop) of rank `rank`: sequences are independent, so the
+    forward needs no collective.  Earlier ranks take the remainder."""
+    if world_size <= 0 or not (0 <= rank < world_size) or B < 0:
+        raise ValueError("bad shard arguments")
+    base, rem = divmod(B, world_size)
+    start = rank * base + min(rank, rem)
+    return start, start + base + (1 if rank < rem else 0)
+
+
+class GPT2:
+    """gpt2_forward driver (C++ inside the library).  Allocates parameters and one reusable set
+    of activations for up to max_B x max_T tokens."""
+
+    def __init__(self, ctx: Context, cfg: GPT2Config, max_B: int, max_T: int):
+        self.ctx, self.cfg, self.max_B, self.max_T = ctx, cfg, max_B, max_T
+        self._h = C.c_void_p()
+        cc = cfg.c()
+        ctx.check(lib().b200_gpt2_create(C.byref(self._h), ctx._h, C.byref(cc), max_B, max_T), "gpt2_create")
+
+    def params_ptr(self) -> int:
+        return int(lib().b200_gpt2_params(self._h))
+
+    def params_tensor(self):
+        """The flat fp32 parameter array as a torch view over the library's device memory."""
+        import torch
+        n = self.cfg.num_params()
+        return _view_device(self.params_ptr(), (n,), torch.float32, self.ctx.device)
+
+    def load_params(self, host_params):
+        self.ctx.check(lib().b200_gpt2_load_params_host(self._h, _ptr(host_params), host_params.size), "load_params")
+
+    def set_options(self, round_operands=0, gemm_mode=B200_TF32, lmhead_mode=B200_TF32, use_graph=0):
+        self.ctx.check(lib().b200_gpt2_set_options(self._h, int(round_operands), gemm_mode, lmhead_mode, int(use_graph)),
+                       "set_options")
+
+    def forward(self, tokens, B: int, T: int):
+        """tokens: CUDA int32 [B,T].  Asynchronous; returns a view of the logits [B,T,Vp]."""
+        import torch
+        self.ctx.check(lib().b200_gpt2_forward(self._h, _ptr(tokens), B, T), "gpt2_forward")
+        return _view_device(int(lib().b200_gpt2_logits(self._h)), (B, T, self.cfg.padded_vocab_size),
+                            torch.float32, self.ctx.device)
+
+    def forward_host(self, tokens_host, B: int, T: int, logits_host=None, last_logits_host=None, argmax_host=None):
+        """Host-buffer call: H2D of tokens, forward, D2H of what is asked for; synchronous."""
+        self.ctx.check(lib().b200_gpt2_forward_host(self._h, _ptr(tokens_host), B, T, _ptr(logits_host),
+                                                    _ptr(last_logits_host), _ptr(argmax_host)), "gpt2_forward_host")
+
+    def activation(self, name: str, shape, dtype=None):
+        import torch
+        p = lib().b200_gpt2_activation(self._h, name.encode())
+        if not p:
+            raise KeyError(name)
+        return _view_device(int(p), shape, dtype or torch.float32, self.ctx.device)
+
+    def close(self):
+        if self._h:
+            lib().b200_gpt2_destroy(self._h)
+            self._h = C.c_void_p()
+
+
+def _view_device(ptr: int, shape, dtype, device: int):
+    """Zero-copy torch view over device memory owned by the library."""
+    import numpy as np
+    import torch
+
+    n = 1
+    for s in shape:
+        n *= int(s)
+    itemsize = torch.empty((), dtype=dtype).element_size()
+
+    class _Holder:
+        pass
+
+    h = _Holder()
+    typestr = {torch.float32: "<f4", torch.int32: "<i4"}[dtype]
+    h.__cuda_array_interface__ = {"shape": (n,), "typestr": typestr, "data": (ptr, False), "version": 3,
+                                  "strides": None}
+    t = torch.as_tensor(h, device=f"cuda:{device}")
+    assert t.element_size() == itemsize
+    return t.view(*shape)

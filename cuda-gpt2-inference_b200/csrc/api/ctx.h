@@ -1,0 +1,59 @@
+// Internal definition of the context behind the C ABI (include/b200gpt2.h).
+#pragma once
+#include <cstdint>
+#include <string>
+#include <unordered_map>
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include "../../../include/b200gpt2.h"
+
+typedef CUresult (*b200_encode_tiled_fn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                         const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                         const cuuint32_t*, CUtensorMapInterleave,
+                                         CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                         CUtensorMapFloatOOBfill);
+
+struct TensorMapKey {
+    const void* ptr;
+    uint64_t rows, cols, ld;
+    uint32_t box_rows, box_cols;
+    bool operator==(const TensorMapKey& o) const {
+        return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
+               box_rows == o.box_rows && box_cols == o.box_cols;
+    }
+};
+struct TensorMapKeyHash {
+    size_t operator()(const TensorMapKey& k) const {
+        uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+        h ^= (k.rows + 0x7F4A7C15ull) * 0xBF58476D1CE4E5B9ull;
+        h ^= (k.cols << 20) ^ (k.ld << 40) ^ (uint64_t(k.box_rows) << 8) ^ k.box_cols;
+        return static_cast<size_t>(h ^ (h >> 29));
+    }
+};
+
+struct b200_ctx {
+    int device = 0;
+    int num_sms = 148;
+    cudaStream_t stream = nullptr;
+    int* d_status = nullptr;  // device word: first device-side error code of any kernel
+    uint64_t launches = 0;
+    std::string last_error;
+    b200_encode_tiled_fn encode_tiled = nullptr;
+    std::unordered_map<TensorMapKey, CUtensorMap, TensorMapKeyHash> tmap_cache;
+};
+
+// Records a failing CUDA call on the context and returns B200_ERR_CUDA.
+int b200_fail_cuda(b200_ctx* ctx, cudaError_t e, const char* what);
+#define B200_CUDA(ctx, call)                                              \
+    do {                                                                  \
+        cudaError_t e__ = (call);                                         \
+        if (e__ != cudaSuccess) return b200_fail_cuda((ctx), e__, #call); \
+    } while (0)
+
+// Tiled fp32 2-D tensor map over a row-major [rows, cols] matrix with leading dimension ld
+// (elements), box = box_rows x box_cols, 128-byte swizzle, zero fill outside the matrix.
+// Cached per context.  Returns B200_OK or an error status.
+int b200_get_tensor_map(b200_ctx* ctx, CUtensorMap* out, const float* ptr, uint64_t rows,
+                        uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+
+inline bool b200_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

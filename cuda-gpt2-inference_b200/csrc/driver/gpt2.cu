@@ -1,0 +1,261 @@
+// gpt2_forward: the driver the reference's kernels plug into.  The reference ships only the
+// kernels (README.md:19 names llm.c's train_gpt2_fp32.cu as the program they were dropped into);
+// the operator order is the one drawn in images/gpt2/gpt2_flow.png and listed in README.md:9-15,
+// with every layernorm except the first fused with the residual add before it
+// (README.md:255-256).  Forward only, so one set of per-layer activations is reused by all
+// layers; parameters keep the flat fp32 layout documented in include/b200gpt2.h.
+#include <cstring>
+#include <map>
+#include <new>
+#include <utility>
+#include "../api/ctx.h"
+#include "../kernels/kernels.h"
+
+struct b200_gpt2 {
+    b200_ctx* ctx = nullptr;
+    b200_gpt2_config cfg{};
+    int max_B = 0, max_T = 0;
+    size_t n_params = 0;
+    size_t off[17] = {};
+    float* params = nullptr;
+    float* wte_rounded = nullptr;  // TF32-rounded copy of wte for the lm-head (round_operands)
+    bool weights_rounded = false;
+    // activations, sized for max_B * max_T rows
+    float *residual = nullptr, *ln_out = nullptr, *qkv = nullptr, *atty = nullptr,
+          *branch = nullptr, *fch = nullptr, *logits = nullptr;
+    int* tokens = nullptr;
+    int* argmax = nullptr;
+    int round_operands = 0, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
+    std::map<std::pair<int, int>, cudaGraphExec_t> graphs;
+};
+
+namespace {
+
+int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
+    using namespace b200;
+    b200_ctx* ctx = m->ctx;
+    const b200_gpt2_config& c = m->cfg;
+    const int C = c.channels, L = c.num_layers, NH = c.num_heads, Vp = c.padded_vocab_size;
+    const int M = B * T;
+    const float* P = m->params;
+    const size_t* off = m->off;
+    const int rnd = m->round_operands ? ROUND_OUT_TF32 : 0;
+    const int grnd = m->round_operands ? GEMM_ROUND_OUT_TF32 : 0;
+    int st;
+#define STEP(call) do { st = (call); if (st != B200_OK) return st; } while (0)
+    STEP(launch_encoder(ctx, m->residual, tokens, P + off[0], P + off[1], B, T, C, Vp));
+    STEP(launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], M, C, rnd));
+    for (int l = 0; l < L; ++l) {
+        const float* qkvw = P + off[4] + (size_t)l * 3 * C * C;
+        const float* qkvb = P + off[5] + (size_t)l * 3 * C;
+        const float* apw = P + off[6] + (size_t)l * C * C;
+        const float* apb = P + off[7] + (size_t)l * C;
+        const float* ln2w = P + off[8] + (size_t)l * C;
+        const float* ln2b = P + off[9] + (size_t)l * C;
+        const float* fcw = P + off[10] + (size_t)l * 4 * C * C;
+        const float* fcb = P + off[11] + (size_t)l * 4 * C;
+        const float* fpw = P + off[12] + (size_t)l * C * 4 * C;
+        const float* fpb = P + off[13] + (size_t)l * C;
+        STEP(launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * C, grnd, m->gemm_mode));
+        STEP(launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, C, NH, rnd));
+        STEP(launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, C, C, 0, m->gemm_mode));
+        STEP(launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
+                                             m->branch, ln2w, ln2b, M, C, rnd));
+        STEP(launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, 4 * C, GEMM_GELU | grnd, m->gemm_mode));
+        STEP(launch_gemm_tf32(ctx, m->branch, m->fch, fpw, fpb, nullptr, M, 4 * C, C, 0, m->gemm_mode));
+        const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
+        const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
+        STEP(launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
+                                             m->branch, nw, nb, M, C, rnd));
+    }
+    const float* head_w = (m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0];
+    STEP(launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, Vp, 0, m->lmhead_mode));
+#undef STEP
+    return B200_OK;
+}
+
+int round_weights_once(b200_gpt2* m) {
+    using namespace b200;
+    if (m->weights_rounded) return B200_OK;
+    b200_ctx* ctx = m->ctx;
+    const size_t* off = m->off;
+    const int idx[4] = {4, 6, 10, 12};  // qkvw, attprojw, fcw, fcprojw
+    for (int i = 0; i < 4; ++i) {
+        int st = launch_round_tf32_inplace(ctx, m->params + off[idx[i]], off[idx[i] + 1] - off[idx[i]]);
+        if (st != B200_OK) return st;
+    }
+    // wte also feeds the encoder, which must stay bit-exact: round a copy for the lm-head
+    const size_t n_wte = off[1] - off[0];
+    if (!m->wte_rounded) B200_CUDA(ctx, cudaMalloc(&m->wte_rounded, n_wte * sizeof(float)));
+    B200_CUDA(ctx, cudaMemcpyAsync(m->wte_rounded, m->params, n_wte * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+    int st = launch_round_tf32_inplace(ctx, m->wte_rounded, n_wte);
+    if (st != B200_OK) return st;
+    m->weights_rounded = true;
+    return B200_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t b200_gpt2_param_offsets(const b200_gpt2_config* cfg, size_t* offsets) {
+    const size_t C = cfg->channels, L = cfg->num_layers, Vp = cfg->padded_vocab_size, mT = cfg->max_seq_len;
+    const size_t sizes[16] = {Vp * C, mT * C, L * C, L * C, L * 3 * C * C, L * 3 * C, L * C * C, L * C,
+                              L * C, L * C, L * 4 * C * C, L * 4 * C, L * C * 4 * C, L * C, C, C};
+    size_t o = 0;
+    for (int i = 0; i < 16; ++i) { if (offsets) offsets[i] = o; o += sizes[i]; }
+    if (offsets) offsets[16] = o;
+    return o;
+}
+
+int b200_gpt2_create(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* cfg, int max_B, int max_T) {
+    if (!out || !ctx || !cfg) return B200_ERR_NULL;
+    *out = nullptr;
+    if (cfg->channels <= 0 || cfg->num_heads <= 0 || cfg->channels % cfg->num_heads ||
+        cfg->channels / cfg->num_heads != 64 || cfg->channels % 4 || cfg->channels > 4096 ||
+        cfg->num_layers <= 0 || cfg->padded_vocab_size % 4 || cfg->vocab_size > cfg->padded_vocab_size ||
+        cfg->vocab_size <= 0 || max_B <= 0 || max_T <= 0 || max_T > cfg->max_seq_len || max_T % 64)
+        return B200_ERR_SHAPE;
+    b200_gpt2* m = new (std::nothrow) b200_gpt2();
+    if (!m) return B200_ERR_CUDA;
+    m->ctx = ctx; m->cfg = *cfg; m->max_B = max_B; m->max_T = max_T;
+    m->n_params = b200_gpt2_param_offsets(cfg, m->off);
+    const size_t M = (size_t)max_B * max_T, C = cfg->channels, Vp = cfg->padded_vocab_size;
+    cudaError_t e = cudaSetDevice(ctx->device);
+    auto alloc = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, bytes); };
+    alloc((void**)&m->params, m->n_params * 4);
+    alloc((void**)&m->residual, M * C * 4);
+    alloc((void**)&m->ln_out, M * C * 4);
+    alloc((void**)&m->qkv, M * 3 * C * 4);
+    alloc((void**)&m->atty, M * C * 4);
+    alloc((void**)&m->branch, M * C * 4);
+    alloc((void**)&m->fch, M * 4 * C * 4);
+    alloc((void**)&m->logits, M * Vp * 4);
+    alloc((void**)&m->tokens, M * 4);
+    alloc((void**)&m->argmax, M * 4);
+    if (e != cudaSuccess) {
+        b200_fail_cuda(ctx, e, "cudaMalloc (b200_gpt2_create)");
+        b200_gpt2_destroy(m);
+        return B200_ERR_CUDA;
+    }
+    *out = m;
+    return B200_OK;
+}
+
+int b200_gpt2_destroy(b200_gpt2* m) {
+    if (!m) return B200_ERR_NULL;
+    cudaSetDevice(m->ctx->device);
+    for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+    void* ptrs[] = {m->params, m->wte_rounded, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
+                    m->fch, m->logits, m->tokens, m->argmax};
+    for (void* p : ptrs) if (p) cudaFree(p);
+    delete m;
+    return B200_OK;
+}
+
+float* b200_gpt2_params(b200_gpt2* m) { return m ? m->params : nullptr; }
+float* b200_gpt2_logits(b200_gpt2* m) { return m ? m->logits : nullptr; }
+
+int b200_gpt2_load_params_host(b200_gpt2* m, const float* host_params, size_t count) {
+    if (!m || !host_params) return B200_ERR_NULL;
+    if (count != m->n_params) return B200_ERR_SHAPE;
+    B200_CUDA(m->ctx, cudaMemcpyAsync(m->params, host_params, count * 4, cudaMemcpyHostToDevice, m->ctx->stream));
+    B200_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
+    m->weights_rounded = false;
+    return B200_OK;
+}
+
+int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int lmhead_mode, int use_graph) {
+    if (!m) return B200_ERR_NULL;
+    if ((gemm_mode != B200_TF32 && gemm_mode != B200_TF32X3) || (lmhead_mode != B200_TF32 && lmhead_mode != B200_TF32X3))
+        return B200_ERR_SHAPE;
+    if (m->round_operands != round_operands || m->gemm_mode != gemm_mode || m->lmhead_mode != lmhead_mode) {
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        m->graphs.clear();
+    }
+    m->round_operands = round_operands;
+    m->gemm_mode = gemm_mode;
+    m->lmhead_mode = lmhead_mode;
+    m->use_graph = use_graph;
+    return B200_OK;
+}
+
+int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) {
+    if (!m || !tokens) return B200_ERR_NULL;
+    if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
+    if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
+    b200_ctx* ctx = m->ctx;
+    if (m->round_operands) {
+        int st = round_weights_once(m);
+        if (st != B200_OK) return st;
+    }
+    if (!m->use_graph || ctx->stream == nullptr) return enqueue_forward(m, tokens, B, T);
+
+    // CUDA-graph replay: the graph reads token ids from the model's own token buffer
+    if (tokens != m->tokens)
+        B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens, (size_t)B * T * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    auto key = std::make_pair(B, T);
+    auto it = m->graphs.find(key);
+    if (it == m->graphs.end()) {
+        // warm the tensor-map cache and function attributes outside of capture
+        int st = enqueue_forward(m, m->tokens, B, T);
+        if (st != B200_OK) return st;
+        B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaGraph_t graph = nullptr;
+        const uint64_t launches_before = ctx->launches;
+        B200_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        st = enqueue_forward(m, m->tokens, B, T);
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+        ctx->launches = launches_before;
+        if (st != B200_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        if (e != cudaSuccess) return b200_fail_cuda(ctx, e, "cudaStreamEndCapture");
+        cudaGraphExec_t exec = nullptr;
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return b200_fail_cuda(ctx, e, "cudaGraphInstantiate");
+        it = m->graphs.emplace(key, exec).first;
+    }
+    B200_CUDA(ctx, cudaGraphLaunch(it->second, ctx->stream));
+    // kernels inside the replayed graph: encoder, first layernorm, 7 per layer, lm-head
+    ctx->launches += 2 + 7ull * m->cfg.num_layers + 1;
+    return B200_OK;
+}
+
+int b200_gpt2_forward_host(b200_gpt2* m, const int* tokens_host, int B, int T, float* logits_host,
+                           float* last_logits_host, int* argmax_host) {
+    if (!m || !tokens_host) return B200_ERR_NULL;
+    if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
+    if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
+    b200_ctx* ctx = m->ctx;
+    const size_t M = (size_t)B * T, Vp = m->cfg.padded_vocab_size;
+    B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens_host, M * 4, cudaMemcpyHostToDevice, ctx->stream));
+    int st = b200_gpt2_forward(m, m->tokens, B, T);
+    if (st != B200_OK) return st;
+    if (argmax_host) {
+        st = b200::launch_argmax_rows(ctx, m->argmax, m->logits, (int)M, m->cfg.vocab_size, (int)Vp);
+        if (st != B200_OK) return st;
+        B200_CUDA(ctx, cudaMemcpyAsync(argmax_host, m->argmax, M * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    if (last_logits_host) {
+        // rows (b, T-1): one strided 2-D copy
+        B200_CUDA(ctx, cudaMemcpy2DAsync(last_logits_host, Vp * 4, m->logits + (size_t)(T - 1) * Vp, (size_t)T * Vp * 4,
+                                         Vp * 4, B, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    if (logits_host)
+        B200_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, M * Vp * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return b200_ctx_sync_check(ctx);
+}
+
+void* b200_gpt2_activation(b200_gpt2* m, const char* name) {
+    if (!m || !name) return nullptr;
+    if (!strcmp(name, "residual") || !strcmp(name, "encoded")) return m->residual;
+    if (!strcmp(name, "ln_out")) return m->ln_out;
+    if (!strcmp(name, "qkv")) return m->qkv;
+    if (!strcmp(name, "atty")) return m->atty;
+    if (!strcmp(name, "branch")) return m->branch;
+    if (!strcmp(name, "fch")) return m->fch;
+    if (!strcmp(name, "argmax")) return m->argmax;
+    return nullptr;
+}
+
+}  // extern "C"

@@ -1,0 +1,288 @@
+// out[M,N] = act(inp[M,K] . weight[N,K]^T + bias[N]) (+ residual[M,N]) on the 5th-generation
+// tensor cores: tcgen05.mma kind::tf32, fp32 operand bits staged by TMA into 128-byte-swizzled
+// shared memory, fp32 accumulators in tensor memory, bias / tanh-GELU / residual applied in the
+// epilogue straight out of tensor memory.  One kernel replaces the reference's whole matmul
+// family (kernels/matmul/1_matmul_tiling.cuh:5-73 is the math; 9_matmul_async_cg_tf32_gelu.cuh
+// :13-275 the best variant, whose bias pre-load :57-84 and GELU epilogue :196-212 are the fused
+// steps kept here) and its separate add_bias pass (2_matmul_cublas.cuh:7-32).
+//
+// Both operands are K-major as stored (inp rows and weight rows are K-contiguous), so no
+// transposes are needed.
+//
+// CTA = 6 warps, persistent over output tiles of 128 x BN:
+//   warp 0      TMA producer: per 32-wide K block one {32 x 128} box of inp and one {32 x BN}
+//               box of weight into a ring of STAGES shared-memory stages (full/empty mbarriers)
+//   warp 1      allocates tensor memory; one elected lane issues 4 UMMAs (K = 8 each) per stage
+//               and commits the stage's empty barrier; commits tmem_full after the last K block
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bias/GELU/residual,
+//               float4 stores.  Two accumulators (2 x BN columns) let the epilogue of tile i
+//               overlap the main loop of tile i+1.
+// Every wait is time-bounded; a wait that runs out makes all roles leave, the CTA frees its
+// tensor memory and records a code in the context's status word.
+#include "kernels.h"
+#include "../prim/sm100.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 32;  // fp32 elements per K block = 128 bytes = one swizzle row
+constexpr int kGemmThreads = 192;
+constexpr int kMaxSmem = 232448;  // 227 KB
+
+template <int BN>
+struct GemmCfg {
+    static constexpr int A_BYTES = BM * BK * 4;
+    static constexpr int B_BYTES = BN * BK * 4;
+    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int BAR_BYTES = 512;
+    static constexpr int STAGES_RAW = (kMaxSmem - 1024 - BAR_BYTES) / STAGE_BYTES;
+    static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
+    static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
+    // one CTA per SM is guaranteed by shared memory (> half of the SM's), so a 512-column
+    // allocation can never wait on a co-resident CTA
+    static_assert(SMEM > 117 * 1024, "a second resident CTA could block in tcgen05.alloc");
+    static_assert(SMEM <= kMaxSmem, "shared memory over the 227 KB limit");
+    static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN: multiple of 32 up to 256");
+};
+
+struct GemmArgs {
+    float* out;
+    const float* bias;
+    const float* residual;
+    int M, N, K;
+    int num_m_blocks, num_n_blocks;
+    int n_fastest;
+    int flags;
+    int* status;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const GemmArgs args) {
+    using Cfg = GemmCfg<BN>;
+    constexpr int STAGES = Cfg::STAGES;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* smem_a = smem;
+    uint8_t* smem_b = smem + STAGES * Cfg::A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint64_t* full_bar = bars;                   // [STAGES]
+    uint64_t* empty_bar = bars + STAGES;         // [STAGES]
+    uint64_t* tmem_full_bar = bars + 2 * STAGES; // [2]
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;  // [2]
+    uint64_t* drain_bar = tmem_empty_bar + 2;    // [1]
+    uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(drain_bar + 1);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int num_tiles = args.num_m_blocks * args.num_n_blocks;
+    const int num_kb = (args.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 128); }
+        mbar_init(drain_bar, 1);
+        *abort_flag = 0;
+        fence_barrier_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_holder;
+
+    auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
+        if (args.n_fastest) { n_blk = tile % args.num_n_blocks; m_blk = tile / args.num_n_blocks; }
+        else { m_blk = tile % args.num_m_blocks; n_blk = tile / args.num_m_blocks; }
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                int m_blk, n_blk;
+                tile_coords(tile, m_blk, n_blk);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+                    tma_load_2d(smem_a + s * Cfg::A_BYTES, &tmap_a, kb * BK, m_blk * BM, &full_bar[s]);
+                    tma_load_2d(smem_b + s * Cfg::B_BYTES, &tmap_b, kb * BK, n_blk * BN, &full_bar[s]);
+                }
+            }
+            if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_PRODUCER);
+        }
+    } else if (warp == 1) {
+        // -------------------------------------------------------------- MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc_tf32(BM, BN, 0);
+            uint32_t it = 0;
+            bool ok = true;
+            int tile_iter = 0;
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+                const int acc = tile_iter & 1;
+                const uint32_t acc_ph = (tile_iter >> 1) & 1;
+                if (!mbar_wait(&tmem_empty_bar[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
+                tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    const uint32_t ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+                    tc_fence_after_sync();
+                    const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * Cfg::A_BYTES), 16, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * Cfg::B_BYTES), 16, 1024);
+#pragma unroll
+                    for (int k = 0; k < BK / 8; ++k) {
+                        // advance 8 fp32 = 32 bytes along K inside the swizzled row: +2 in the
+                        // (address >> 4) field
+                        umma_tf32_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(&empty_bar[s]);
+                }
+                if (ok) umma_commit(&tmem_full_bar[acc]);
+            }
+            // wait (bounded) until everything issued has retired before tensor memory is freed
+            umma_commit(drain_bar);
+            if (!mbar_wait(drain_bar, 0, abort_flag)) ok = false;
+            if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue
+        const int q = warp & 3;  // the lane quarter this warp may read
+        const bool do_gelu = (args.flags & GEMM_GELU) != 0;
+        const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
+        bool ok = true;
+        int tile_iter = 0;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
+            int m_blk, n_blk;
+            tile_coords(tile, m_blk, n_blk);
+            const int acc = tile_iter & 1;
+            const uint32_t acc_ph = (tile_iter >> 1) & 1;
+            if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
+            tc_fence_after_sync();
+            const int row = m_blk * BM + q * 32 + lane;
+            const bool row_ok = row < args.M;
+            float* out_row = args.out + (size_t)row * args.N;
+            const float* res_row = args.residual ? args.residual + (size_t)row * args.N : nullptr;
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, r);
+                tmem_ld_wait();
+                const int col0 = n_blk * BN + c * 32;
+                if (row_ok && col0 < args.N) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        const int col = col0 + 4 * j;
+                        if (col < args.N) {
+                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                            if (args.bias) {
+                                const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col));
+                                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                            }
+                            if (do_gelu) { v.x = gelu_tanh(v.x); v.y = gelu_tanh(v.y); v.z = gelu_tanh(v.z); v.w = gelu_tanh(v.w); }
+                            if (res_row) {
+                                const float4 rr = *reinterpret_cast<const float4*>(res_row + col);
+                                v.x += rr.x; v.y += rr.y; v.z += rr.z; v.w += rr.w;
+                            }
+                            if (do_round) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
+                            *reinterpret_cast<float4*>(out_row + col) = v;
+                        }
+                    }
+                }
+            }
+            tc_fence_before_sync();
+            mbar_arrive(&tmem_empty_bar[acc]);
+        }
+        if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_EPILOGUE);
+    }
+
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after_sync();
+        tmem_dealloc(tmem_base, Cfg::TMEM_COLS);
+    }
+}
+
+// estimated cycles of one 8-deep K step of a 128 x BN tile: tensor pipe vs shared-memory feed
+inline int tile_step_cost(int bn) {
+    const int tensor = bn / 2, feed = 32 + bn / 4;
+    return tensor > feed ? tensor : feed;
+}
+
+template <int BN>
+int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& a) {
+    using Cfg = GemmCfg<BN>;
+    static bool attr_set[64] = {};
+    if (!attr_set[ctx->device & 63]) {
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+        attr_set[ctx->device & 63] = true;
+    }
+    const int tiles = a.num_m_blocks * a.num_n_blocks;
+    const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
+    gemm_tf32_kernel<BN><<<grid, kGemmThreads, Cfg::SMEM, ctx->stream>>>(ta, tb, a);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+}  // namespace
+
+int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
+                     const float* bias, const float* residual, int M, int K, int N, int flags,
+                     int mode) {
+    (void)mode;
+    const int num_m = (M + BM - 1) / BM;
+    // pick the N tile that minimises waves x per-tile cost on this GPU's SM count
+    const int cands[5] = {256, 192, 128, 96, 64};
+    int best_bn = 256;
+    long best_cost = -1;
+    for (int i = 0; i < 5; ++i) {
+        const int bn = cands[i];
+        const long tiles = (long)num_m * ((N + bn - 1) / bn);
+        const long waves = (tiles + ctx->num_sms - 1) / ctx->num_sms;
+        const long cost = waves * tile_step_cost(bn);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
+    }
+    GemmArgs a;
+    a.out = out; a.bias = bias; a.residual = residual;
+    a.M = M; a.N = N; a.K = K;
+    a.num_m_blocks = num_m;
+    a.num_n_blocks = (N + best_bn - 1) / best_bn;
+    // weight small enough to stay in L2: sweep N fastest so each inp tile is fetched once;
+    // otherwise sweep M fastest so the (smaller) inp stays resident while weight streams
+    a.n_fastest = ((size_t)N * K * 4 <= (size_t)32 << 20) ? 1 : 0;
+    a.flags = flags;
+    a.status = ctx->d_status;
+
+    CUtensorMap ta, tb;
+    int st = b200_get_tensor_map(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);
+    if (st != B200_OK) return st;
+    st = b200_get_tensor_map(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)best_bn, BK);
+    if (st != B200_OK) return st;
+    switch (best_bn) {
+        case 256: return launch_one<256>(ctx, ta, tb, a);
+        case 192: return launch_one<192>(ctx, ta, tb, a);
+        case 128: return launch_one<128>(ctx, ta, tb, a);
+        case 96:  return launch_one<96>(ctx, ta, tb, a);
+        default:  return launch_one<64>(ctx, ta, tb, a);
+    }
+}
+
+}  // namespace b200

@@ -1,0 +1,39 @@
+// Internal launchers: each validates nothing (the C-ABI layer does) and enqueues kernels on
+// ctx->stream, bumping ctx->launches once per kernel launch.
+#pragma once
+#include "../api/ctx.h"
+
+namespace b200 {
+
+// flags for the row-wise producers
+enum : int { ROUND_OUT_TF32 = 1 };
+
+int launch_layernorm(b200_ctx* ctx, float* out, float* mean, float* rstd, const float* inp,
+                     const float* weight, const float* bias, int M, int C, int flags);
+int launch_fused_residual_layernorm(b200_ctx* ctx, float* res_out, float* ln_out, float* mean,
+                                    float* rstd, const float* inp1, const float* inp2,
+                                    const float* weight, const float* bias, int M, int C, int flags);
+int launch_residual(b200_ctx* ctx, float* out, const float* a, const float* b, size_t N);
+int launch_gelu(b200_ctx* ctx, float* out, const float* inp, size_t N);
+int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,
+                   int B, int T, int C, int vocab_rows /* <=0: unchecked */);
+int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N);
+int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
+
+// epilogue flags of the GEMM
+enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2 };
+int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
+                     const float* bias, const float* residual, int M, int K, int N, int flags,
+                     int mode);
+
+int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, int B, int T, int C,
+                     int NH, int flags);
+
+// fast, accurate tanh-GELU: x * sigmoid(2u), u = sqrt(2/pi) * (x + 0.044715 x^3)
+__device__ __forceinline__ float gelu_tanh(float x) {
+    const float k2 = 1.5957691216057308f;  // 2*sqrt(2/pi)
+    float u = k2 * (x + 0.044715f * x * x * x);
+    return __fdividef(x, 1.0f + __expf(-u));
+}
+
+}  // namespace b200

@@ -1,0 +1,287 @@
+// HBM-bound row-wise kernels of the GPT-2 forward: layernorm, fused residual+layernorm,
+// residual add, GELU, the token+position encoder gather, and two small helpers of the driver
+// (TF32 rounding of weights, per-row arg-max).  float4-coalesced access, one warp per row for
+// the normalisations with the row held in registers and warp-shuffle reductions; no tensor
+// cores.  Grids are sized from the SM count.
+//
+// Math follows kernels/layernorm/1_layernorm_block.cuh:32-60 (biased variance, eps 1e-5,
+// mean/rstd outputs), kernels/fused_residual_layernorm/fused_residual_layernorm.cuh:28-36,59-81
+// (intent; that kernel's float4 pointer stride at :19,48-50 is not followed),
+// kernels/residual/1_residual_naive.cuh:9-12 and kernels/matmul/9_matmul_async_cg_tf32_gelu.cuh:5-11.
+#include "kernels.h"
+#include "../prim/sm100.cuh"
+
+namespace b200 {
+
+namespace {
+
+constexpr int kRowWarps = 8;  // rows per CTA in the normalisation kernels
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) v += __shfl_xor_sync(0xffffffffu, v, s);
+    return v;
+}
+
+// One warp per row.  NV = float4 per lane held in registers (covers C <= 128*NV).
+// FUSED: x = inp1 + inp2 is stored to res_out first (which may alias an input: every
+// element is read before it is written, by the same lane).
+template <int NV, bool FUSED>
+__global__ void __launch_bounds__(kRowWarps * 32)
+layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict__ mean,
+                      float* __restrict__ rstd, const float* inp1, const float* inp2,
+                      const float* __restrict__ weight, const float* __restrict__ bias, int M, int C,
+                      int flags) {
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const int C4 = C >> 2;
+    const float4* x1 = reinterpret_cast<const float4*>(inp1 + (size_t)row * C);
+    const float4* x2 = FUSED ? reinterpret_cast<const float4*>(inp2 + (size_t)row * C) : nullptr;
+
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        if (c < C4) {
+            v[i] = x1[c];
+            if (FUSED) {
+                const float4 b = x2[c];
+                v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+            }
+        } else {
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if (FUSED) {
+        float4* ro = reinterpret_cast<float4*>(res_out + (size_t)row * C);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane + i * 32;
+            if (c < C4) ro[c] = v[i];
+        }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    const float m = warp_sum(s) / (float)C;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        if (c < C4) {
+            const float dx = v[i].x - m, dy = v[i].y - m, dz = v[i].z - m, dw = v[i].w - m;
+            q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+    }
+    const float r = rsqrtf(warp_sum(q) / (float)C + 1e-5f);
+    if (lane == 0) {
+        if (mean) mean[row] = m;
+        if (rstd) rstd[row] = r;
+    }
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+    const float4* b4 = reinterpret_cast<const float4*>(bias);
+    float4* o = reinterpret_cast<float4*>(out + (size_t)row * C);
+    const bool rnd = (flags & ROUND_OUT_TF32) != 0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        if (c < C4) {
+            const float4 w = __ldg(w4 + c), b = __ldg(b4 + c);
+            float4 y;
+            y.x = (v[i].x - m) * r * w.x + b.x;
+            y.y = (v[i].y - m) * r * w.y + b.y;
+            y.z = (v[i].z - m) * r * w.z + b.z;
+            y.w = (v[i].w - m) * r * w.w + b.w;
+            if (rnd) { y.x = round_tf32(y.x); y.y = round_tf32(y.y); y.z = round_tf32(y.z); y.w = round_tf32(y.w); }
+            o[c] = y;
+        }
+    }
+}
+
+template <bool FUSED>
+int launch_ln_any(b200_ctx* ctx, float* out, float* res_out, float* mean, float* rstd,
+                  const float* inp1, const float* inp2, const float* weight, const float* bias,
+                  int M, int C, int flags) {
+    const int nv = (C / 4 + 31) / 32;
+    const dim3 grid((M + kRowWarps - 1) / kRowWarps), block(kRowWarps * 32);
+#define B200_LN_CASE(NV)                                                                        \
+    layernorm_rows_kernel<NV, FUSED><<<grid, block, 0, ctx->stream>>>(out, res_out, mean, rstd, \
+                                                                      inp1, inp2, weight, bias, \
+                                                                      M, C, flags)
+    if (nv <= 2) B200_LN_CASE(2);
+    else if (nv <= 4) B200_LN_CASE(4);
+    else if (nv <= 6) B200_LN_CASE(6);       // C = 768
+    else if (nv <= 8) B200_LN_CASE(8);       // C = 1024
+    else if (nv <= 10) B200_LN_CASE(10);     // C = 1280
+    else if (nv <= 13) B200_LN_CASE(13);     // C = 1600
+    else if (nv <= 16) B200_LN_CASE(16);
+    else B200_LN_CASE(32);                   // C <= 4096
+#undef B200_LN_CASE
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+__global__ void residual_kernel(float4* __restrict__ out, const float4* __restrict__ a,
+                                const float4* __restrict__ b, size_t n4, float* out_s,
+                                const float* a_s, const float* b_s, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i < n4; i += stride) {
+        const float4 x = a[i], y = b[i];
+        out[i] = make_float4(x.x + y.x, x.y + y.y, x.z + y.z, x.w + y.w);
+    }
+    // scalar tail (N % 4)
+    i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out_s[i] = a_s[i] + b_s[i];
+}
+
+__global__ void gelu_kernel(float4* __restrict__ out, const float4* __restrict__ inp, size_t n4,
+                            float* out_s, const float* inp_s, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i < n4; i += stride) {
+        const float4 x = inp[i];
+        out[i] = make_float4(gelu_tanh(x.x), gelu_tanh(x.y), gelu_tanh(x.z), gelu_tanh(x.w));
+    }
+    i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) out_s[i] = gelu_tanh(inp_s[i]);
+}
+
+__global__ void round_tf32_kernel(float4* data, size_t n4, float* data_s, size_t n) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    for (; i < n4; i += stride) {
+        float4 x = data[i];
+        data[i] = make_float4(round_tf32(x.x), round_tf32(x.y), round_tf32(x.z), round_tf32(x.w));
+    }
+    i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) data_s[i] = round_tf32(data_s[i]);
+}
+
+// out[bt, :] = wte[tok[bt], :] + wpe[bt % T, :]; one fp32 add per element (bit-exact).
+// An id outside [0, vocab_rows) (when checked) is recorded in *status and treated as 0.
+__global__ void encoder_kernel(float4* __restrict__ out, const int* __restrict__ tok,
+                               const float4* __restrict__ wte, const float4* __restrict__ wpe,
+                               int M, int T, int C4, int vocab_rows, int* status) {
+    const size_t total = (size_t)M * C4;
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
+        const int bt = (int)(i / C4), c = (int)(i % C4);
+        int id = __ldg(tok + bt);
+        if (vocab_rows > 0 && (id < 0 || id >= vocab_rows)) {
+            if (c == 0) atomicCAS(status, 0, 201);
+            id = 0;
+        }
+        const float4 e = __ldg(wte + (size_t)id * C4 + c);
+        const float4 p = __ldg(wpe + (size_t)(bt % T) * C4 + c);
+        out[i] = make_float4(e.x + p.x, e.y + p.y, e.z + p.z, e.w + p.w);
+    }
+}
+
+// arg-max over columns [0,V) of each row (ties -> lowest index); one CTA per row.
+__global__ void __launch_bounds__(256)
+argmax_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, int ld) {
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    const int V4 = V >> 2;
+    const float4* r4 = reinterpret_cast<const float4*>(row);
+    for (int i = threadIdx.x; i < V4; i += blockDim.x) {
+        const float4 x = r4[i];
+        const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (xs[k] > best) { best = xs[k]; bi = i * 4 + k; }
+    }
+    for (int i = V4 * 4 + threadIdx.x; i < V; i += blockDim.x)
+        if (row[i] > best) { best = row[i]; bi = i; }
+    __shared__ float sb[8];
+    __shared__ int si[8];
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, s);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, s);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sb[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sb[w] > best || (sb[w] == best && si[w] < bi)) { best = sb[w]; bi = si[w]; }
+        out[blockIdx.x] = bi;
+    }
+}
+
+inline int stream_grid(const b200_ctx* ctx, size_t n4, int block, int ctas_per_sm) {
+    size_t want = (n4 + block - 1) / block;
+    size_t cap = (size_t)ctx->num_sms * ctas_per_sm;
+    if (want < 1) want = 1;
+    return (int)(want < cap ? want : cap);
+}
+
+}  // namespace
+
+int launch_layernorm(b200_ctx* ctx, float* out, float* mean, float* rstd, const float* inp,
+                     const float* weight, const float* bias, int M, int C, int flags) {
+    return launch_ln_any<false>(ctx, out, nullptr, mean, rstd, inp, nullptr, weight, bias, M, C, flags);
+}
+
+int launch_fused_residual_layernorm(b200_ctx* ctx, float* res_out, float* ln_out, float* mean,
+                                    float* rstd, const float* inp1, const float* inp2,
+                                    const float* weight, const float* bias, int M, int C, int flags) {
+    return launch_ln_any<true>(ctx, ln_out, res_out, mean, rstd, inp1, inp2, weight, bias, M, C, flags);
+}
+
+int launch_residual(b200_ctx* ctx, float* out, const float* a, const float* b, size_t N) {
+    const size_t n4 = N / 4;
+    const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
+    residual_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<float4*>(out),
+                                                   reinterpret_cast<const float4*>(a),
+                                                   reinterpret_cast<const float4*>(b), n4, out, a, b, N);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_gelu(b200_ctx* ctx, float* out, const float* inp, size_t N) {
+    const size_t n4 = N / 4;
+    const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
+    gelu_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<float4*>(out),
+                                               reinterpret_cast<const float4*>(inp), n4, out, inp, N);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N) {
+    const size_t n4 = N / 4;
+    const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
+    round_tf32_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<float4*>(data), n4, data, N);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,
+                   int B, int T, int C, int vocab_rows) {
+    const size_t n4 = (size_t)B * T * (C / 4);
+    const int grid = stream_grid(ctx, n4, 256, 16);
+    encoder_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<float4*>(out), tok,
+                                                  reinterpret_cast<const float4*>(wte),
+                                                  reinterpret_cast<const float4*>(wpe), B * T, T,
+                                                  C / 4, vocab_rows, ctx->d_status);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld) {
+    argmax_rows_kernel<<<M, 256, 0, ctx->stream>>>(out, logits, V, ld);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+}  // namespace b200

@@ -1,0 +1,194 @@
+/*
+ * b200gpt2.h - C ABI of the B200-native GPT-2 forward engine (libb200gpt2.so).
+ *
+ * The entry points keep the shape of the reference project's host wrappers
+ * (GJ0407790/CUDA-GPT2-Inference, kernels/.../*.cuh): free functions that take DEVICE
+ * float pointers and int dimensions, allocate nothing, and launch asynchronously.  Every
+ * activation and parameter is fp32, row-major, laid out exactly as in the reference:
+ *   activations [B,T,C]; linear weights [OC,C] (K contiguous); packed QKV [B,T,3,NH,HS].
+ *
+ * Two forms of every operator are exported:
+ *   - b200_<op>(ctx, ...) returns an int status (B200_OK == 0) and launches on the
+ *     context's stream;
+ *   - <op>(...) is the reference-shaped void shim: it runs on a process-wide default
+ *     context (current device, legacy default stream) and, like the reference's asserts,
+ *     aborts the process with a message on a precondition failure.
+ *
+ * Threading: a context is owned by one host thread at a time.  Nothing here synchronises
+ * the stream unless stated.  All pointers must be 16-byte aligned.
+ */
+#ifndef B200GPT2_H
+#define B200GPT2_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------- status codes */
+enum {
+    B200_OK = 0,
+    B200_ERR_NULL = 1,       /* a required pointer is NULL                          */
+    B200_ERR_SHAPE = 2,      /* a dimension violates a stated precondition          */
+    B200_ERR_ALIGN = 3,      /* a pointer is not 16-byte aligned                    */
+    B200_ERR_CUDA = 4,       /* a CUDA runtime/driver call failed (see last_error)  */
+    B200_ERR_DEVICE = 5,     /* not an sm_100 device                                */
+    B200_ERR_TIMEOUT = 6,    /* a device-side wait ran out; the kernel returned     */
+    B200_ERR_STATE = 7,      /* object used before it was set up                    */
+    B200_ERR_LIMIT = 8       /* size beyond a stated maximum                        */
+};
+
+/* GEMM arithmetic modes */
+enum {
+    B200_TF32 = 0,           /* one tcgen05 kind::tf32 pass (default)               */
+    B200_TF32X3 = 1          /* three-term split (big*big + small*big + big*small)  */
+};
+
+/* GEMM epilogue activation */
+enum { B200_ACT_NONE = 0, B200_ACT_GELU = 1 };
+
+typedef struct b200_ctx b200_ctx;
+
+/* Creates a context on `device` (made current).  `stream` is a cudaStream_t passed as
+ * void* (NULL = legacy default stream, the reference's behaviour). */
+int b200_ctx_create(b200_ctx** out, int device, void* stream);
+int b200_ctx_destroy(b200_ctx* ctx);
+int b200_ctx_set_stream(b200_ctx* ctx, void* stream);
+/* Synchronises the stream, then returns B200_ERR_TIMEOUT / B200_ERR_CUDA if a kernel
+ * recorded a device-side wait that ran out or CUDA reports an error; clears the word. */
+int b200_ctx_sync_check(b200_ctx* ctx);
+/* Number of kernels this context has launched since creation (or the last reset). */
+uint64_t b200_ctx_launch_count(const b200_ctx* ctx);
+void b200_ctx_reset_launch_count(b200_ctx* ctx);
+const char* b200_status_string(int status);
+/* Text of the last failing CUDA call on this context ("" if none). */
+const char* b200_ctx_last_error(const b200_ctx* ctx);
+
+/* ------------------------------------------------------------------ operators */
+
+/* out[B,T,OC] = act(inp[B,T,C] . weight[OC,C]^T + bias[OC]) (+ residual[B,T,OC]).
+ * Replaces matmul_forward_tiling (kernels/matmul/1_matmul_tiling.cuh:57-65),
+ * matmul_forward_cublas + add_bias (2_matmul_cublas.cuh:7-61), matmul_forward_ptx_2d
+ * (5_matmul_ptx_2d.cuh:165-173) and matmul_forward_async_cg_tf32_gelu
+ * (9_matmul_async_cg_tf32_gelu.cuh:237-246, whose `bool is_gelu` is `act`).
+ * bias and residual may be NULL.  Preconditions: C % 4 == 0, OC % 4 == 0. */
+int b200_matmul_forward(b200_ctx* ctx, float* out, const float* inp, const float* weight,
+                        const float* bias, int B, int T, int C, int OC, int act,
+                        const float* residual, int mode);
+
+/* Causal multi-head attention on the packed buffer inp[B,T,3C] -> out[B,T,C].
+ * Replaces attention_forward_cublas (kernels/attention/1_attention_cublas.cuh:31-36),
+ * flash_attention_forward (2_flash_attention.cuh:336-341) and
+ * flash_attention_permute_forward (3_flash_attention_permute.cuh:346-351).
+ * qkvr is unused and may be NULL.  If att is non-NULL it receives the softmax statistics
+ * lse[B,NH,T] = log(sum_j exp(q.k_j/sqrt(HS))).  inp is not modified.
+ * Preconditions: C/NH == 64, T % 64 == 0 (the reference's, 3_...cuh:336-337). */
+int b200_attention_forward(b200_ctx* ctx, float* out, float* qkvr, float* att, const float* inp,
+                           int B, int T, int C, int NH);
+
+/* Replaces layernorm_forward_block / _block_vectorized / _warp
+ * (kernels/layernorm/1_layernorm_block.cuh:63-65, 2_...:74-76, 3_layernorm_warp.cuh:78-80).
+ * mean and rstd ([B,T]) may be NULL.  Precondition: C % 4 == 0, C <= 4096. */
+int b200_layernorm_forward(b200_ctx* ctx, float* out, float* mean, float* rstd, const float* inp,
+                           const float* weight, const float* bias, int B, int T, int C);
+
+/* res_out = inp1 + inp2; layernorm_out = LN(res_out).  Replaces
+ * fused_residual_layernorm_forward
+ * (kernels/fused_residual_layernorm/fused_residual_layernorm.cuh:88-90).
+ * res_out may alias inp1 or inp2. */
+int b200_fused_residual_layernorm_forward(b200_ctx* ctx, float* res_out, float* layernorm_out,
+                                          float* mean, float* rstd, const float* inp1,
+                                          const float* inp2, const float* weight,
+                                          const float* bias, int B, int T, int C);
+
+/* out = inp1 + inp2.  Replaces residual_forward_naive / _cache_hint
+ * (kernels/residual/1_residual_naive.cuh:15, 2_residual_cache_hint.cuh:15). */
+int b200_residual_forward(b200_ctx* ctx, float* out, const float* inp1, const float* inp2,
+                          size_t N);
+
+/* tanh-GELU, the device function of kernels/matmul/9_matmul_async_cg_tf32_gelu.cuh:5-11 as a
+ * stand-alone operator (the reference names the step in README.md:15 but ships no kernel). */
+int b200_gelu_forward(b200_ctx* ctx, float* out, const float* inp, size_t N);
+
+/* out[b,t,:] = wte[inp[b,t],:] + wpe[t,:].  The reference names the step (README.md:10) but
+ * ships no kernel.  Token ids must lie in [0, vocabulary rows of wte). */
+int b200_encoder_forward(b200_ctx* ctx, float* out, const int* inp, const float* wte,
+                         const float* wpe, int B, int T, int C);
+
+/* --------------------------------------------- reference-shaped void shims */
+void matmul_forward(float* out, const float* inp, const float* weight, const float* bias, int B,
+                    int T, int C, int OC);
+void matmul_forward_gelu(float* out, const float* inp, const float* weight, const float* bias,
+                         int B, int T, int C, int OC, int is_gelu);
+void attention_forward(float* out, float* qkvr, float* att, const float* inp, int B, int T, int C,
+                       int NH);
+void layernorm_forward(float* out, float* mean, float* rstd, const float* inp, const float* weight,
+                       const float* bias, int B, int T, int C);
+void fused_residual_layernorm_forward(float* res_out, float* layernorm_out, float* mean,
+                                      float* rstd, const float* inp1, const float* inp2,
+                                      const float* weight, const float* bias, int B, int T, int C);
+void fused_residual_layernorm(float* res_out, float* layernorm_out, float* mean, float* rstd,
+                              const float* inp1, const float* inp2, const float* weight,
+                              const float* bias, int B, int T, int C);
+void residual_forward(float* out, const float* inp1, const float* inp2, int N);
+void gelu_forward(float* out, const float* inp, int N);
+void encoder_forward(float* out, const int* inp, const float* wte, const float* wpe, int B, int T,
+                     int C);
+
+/* ------------------------------------------------------------ gpt2_forward driver */
+/* The driver the reference's kernels plug into (llm.c's gpt2_forward; README.md:19 and
+ * images/gpt2/gpt2_flow.png give the operator order).  Forward only. */
+typedef struct {
+    int max_seq_len;        /* maxT, rows of wpe                       */
+    int vocab_size;         /* V                                       */
+    int padded_vocab_size;  /* Vp, rows of wte and width of the logits */
+    int num_layers;         /* L                                       */
+    int num_heads;          /* NH                                      */
+    int channels;           /* C                                       */
+} b200_gpt2_config;
+
+typedef struct b200_gpt2 b200_gpt2;
+
+/* Number of fp32 parameters, and the offsets (in floats) of the 16 parameter tensors in the
+ * flat parameter array, in this order, each stacked over layers:
+ *   wte[Vp,C] wpe[maxT,C] ln1w[L,C] ln1b[L,C] qkvw[L,3C,C] qkvb[L,3C] attprojw[L,C,C]
+ *   attprojb[L,C] ln2w[L,C] ln2b[L,C] fcw[L,4C,C] fcb[L,4C] fcprojw[L,C,4C] fcprojb[L,C]
+ *   lnfw[C] lnfb[C].   offsets has 17 entries; offsets[16] is the total. */
+size_t b200_gpt2_param_offsets(const b200_gpt2_config* cfg, size_t* offsets);
+
+/* Allocates device memory for the parameters and for the activations of a forward pass of up
+ * to max_B x max_T tokens.  Forward-only, so one layer's activations are reused by every
+ * layer.  This is the only allocating call. */
+int b200_gpt2_create(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* cfg, int max_B,
+                     int max_T);
+int b200_gpt2_destroy(b200_gpt2* model);
+/* Device pointer of the flat parameter array (fill it in place), or copy from the host. */
+float* b200_gpt2_params(b200_gpt2* model);
+int b200_gpt2_load_params_host(b200_gpt2* model, const float* host_params, size_t count);
+/* Options: round_operands != 0 makes every producer whose output feeds only a GEMM store
+ * TF32-round-to-nearest values and rounds the weight matrices once (in place), removing the
+ * truncation bias of raw fp32 operands.  gemm_mode applies to all GEMMs; lmhead_mode to the
+ * lm-head alone.  use_graph != 0 replays the forward from a CUDA graph after the first call
+ * of a given (B,T). */
+int b200_gpt2_set_options(b200_gpt2* model, int round_operands, int gemm_mode, int lmhead_mode,
+                          int use_graph);
+/* tokens: device int32 [B,T].  Asynchronous.  Logits: device [B,T,Vp], owned by the model. */
+int b200_gpt2_forward(b200_gpt2* model, const int* tokens, int B, int T);
+float* b200_gpt2_logits(b200_gpt2* model);
+/* Host-buffer form: copies tokens (host, ideally pinned) to the device, runs the forward,
+ * and copies back what is asked for, synchronising before it returns:
+ *   logits_host      [B,T,Vp]  all logits                     (nullable)
+ *   last_logits_host [B,Vp]    logits of the last position    (nullable)
+ *   argmax_host      [B,T]     arg-max token over [0,V) per position (nullable) */
+int b200_gpt2_forward_host(b200_gpt2* model, const int* tokens_host, int B, int T,
+                           float* logits_host, float* last_logits_host, int* argmax_host);
+/* Device pointer of an intermediate activation of the last forward, for tests:
+ * name in {"encoded","ln_out","qkv","atty","branch","fch","residual","argmax"}; NULL if unknown. */
+void* b200_gpt2_activation(b200_gpt2* model, const char* name);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200GPT2_H */

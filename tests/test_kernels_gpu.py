@@ -1,0 +1,223 @@
+"""Parity of every C-ABI operator against the CPU oracle on the same seeded inputs (GPU).
+
+Tolerances (frozen from the measured gap between a correct TF32 kernel and the fp64-accumulate
+oracle, see the per-test comments):
+  encoder, residual          bit-exact
+  layernorm / fused          1e-5 absolute on N(0,1) rows
+  gelu                       2e-6 absolute
+  GEMM, TF32                 relative RMS error <= 1e-3, max-abs <= 6e-3 * sqrt(K/768) on N(0,1) x N(0,0.02)
+  attention, TF32            3e-3 absolute on N(0,1) Q/K/V; lse 3e-3
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel_rms(a, b):
+    return float(np.sqrt(np.mean((a.astype(np.float64) - b) ** 2)) / (np.sqrt(np.mean(b.astype(np.float64) ** 2)) + 1e-30))
+
+
+# ------------------------------------------------------------------ memory-bound kernels
+@pytest.mark.parametrize("B,T,C", [(4, 64, 768), (2, 64, 1600), (1, 64, 128), (3, 64, 1024), (1, 192, 4096)])
+def test_layernorm_matches_oracle(ctx, dev, orc, B, T, C):
+    x = orc.fill_normal((B, T, C), 11)
+    w = orc.fill_normal((C,), 12, mean=1.0, std=0.1)
+    b = orc.fill_normal((C,), 13, std=0.1)
+    want, wmean, wrstd = orc.layernorm_forward(x, w, b, precise=True)
+    out, mean, rstd = dev.empty((B, T, C)), dev.empty((B, T)), dev.empty((B, T))
+    ctx.layernorm_forward(out, mean, rstd, dev.to(x), dev.to(w), dev.to(b), B, T, C)
+    assert np.abs(dev.back(out) - want).max() < 1e-5
+    assert np.abs(dev.back(mean) - wmean).max() < 1e-6
+    assert np.abs(dev.back(rstd) / wrstd - 1).max() < 1e-5
+
+
+def test_layernorm_null_stats_and_shifted_rows(ctx, dev, orc):
+    # mean/rstd may be NULL; rows with a large common offset stress the variance formula
+    B, T, C = 2, 64, 768
+    x = orc.fill_normal((B, T, C), 21) + 100.0
+    w = np.ones(C, np.float32)
+    b = np.zeros(C, np.float32)
+    want, _, _ = orc.layernorm_forward(x, w, b, precise=True)
+    out = dev.empty((B, T, C))
+    ctx.layernorm_forward(out, None, None, dev.to(x), dev.to(w), dev.to(b), B, T, C)
+    assert np.abs(dev.back(out) - want).max() < 2e-4  # fp32 input resolution at |x|~100 is 7.6e-6 * rstd~1
+
+
+@pytest.mark.parametrize("B,T,C", [(4, 64, 768), (2, 64, 1600)])
+def test_fused_residual_layernorm_matches_oracle(ctx, dev, orc, B, T, C):
+    x1 = orc.fill_normal((B, T, C), 31)
+    x2 = orc.fill_normal((B, T, C), 32)
+    w = orc.fill_normal((C,), 33, mean=1.0, std=0.1)
+    b = orc.fill_normal((C,), 34, std=0.1)
+    wres, wout, wmean, wrstd = orc.fused_residual_layernorm_forward(x1, x2, w, b, precise=True)
+    res, out, mean, rstd = dev.empty((B, T, C)), dev.empty((B, T, C)), dev.empty((B, T)), dev.empty((B, T))
+    ctx.fused_residual_layernorm_forward(res, out, mean, rstd, dev.to(x1), dev.to(x2), dev.to(w), dev.to(b), B, T, C)
+    assert np.array_equal(dev.back(res), wres)  # one fp32 add
+    assert np.abs(dev.back(out) - wout).max() < 1e-5
+    assert np.abs(dev.back(mean) - wmean).max() < 1e-6
+
+
+def test_fused_residual_layernorm_in_place(ctx, dev, orc):
+    # res_out aliasing inp1 is how the driver keeps the residual stream
+    B, T, C = 2, 64, 768
+    x1 = orc.fill_normal((B, T, C), 41)
+    x2 = orc.fill_normal((B, T, C), 42)
+    w = np.ones(C, np.float32)
+    b = np.zeros(C, np.float32)
+    wres, wout, _, _ = orc.fused_residual_layernorm_forward(x1, x2, w, b, precise=True)
+    d1, out = dev.to(x1), dev.empty((B, T, C))
+    ctx.fused_residual_layernorm_forward(d1, out, None, None, d1, dev.to(x2), dev.to(w), dev.to(b), B, T, C)
+    assert np.array_equal(dev.back(d1), wres)
+    assert np.abs(dev.back(out) - wout).max() < 1e-5
+
+
+@pytest.mark.parametrize("N", [1, 3, 4, 1000, 768 * 256 + 3])
+def test_residual_bit_exact(ctx, dev, orc, N):
+    a = orc.fill_normal((N,), 51)
+    b = orc.fill_normal((N,), 52)
+    npad = (N + 3) // 4 * 4
+    da, db, out = dev.to(np.resize(a, npad)), dev.to(np.resize(b, npad)), dev.empty((npad,))
+    ctx.residual_forward(out, da, db, N)
+    assert np.array_equal(dev.back(out)[:N], orc.residual_forward(a, b))
+
+
+@pytest.mark.parametrize("N", [5, 4096, 3072 * 256])
+def test_gelu_matches_oracle(ctx, dev, orc, N):
+    x = orc.fill_normal((N,), 61, std=3.0)
+    x[:5] = [0.0, -20.0, 20.0, -1e-8, 100.0][: min(5, N)]
+    npad = (N + 3) // 4 * 4
+    out = dev.empty((npad,))
+    ctx.gelu_forward(out, dev.to(np.resize(x, npad)), N)
+    want = orc.gelu_forward(x, precise=True)
+    assert np.abs(dev.back(out)[:N] - want).max() < 2e-6 * max(1.0, float(np.abs(want).max()) / 10)
+
+
+@pytest.mark.parametrize("B,T,C,V", [(4, 64, 768, 50304), (2, 128, 1600, 1024), (1, 64, 128, 7)])
+def test_encoder_bit_exact(ctx, dev, orc, B, T, C, V):
+    import torch
+    wte = orc.fill_normal((V, C), 71, std=0.02)
+    wpe = orc.fill_normal((T, C), 72, std=0.02)
+    tok = orc.fill_tokens((B, T), 73, vocab=V)
+    tok[0, 0], tok[-1, -1] = 0, V - 1  # both ends of the table
+    out = dev.empty((B, T, C))
+    ctx.encoder_forward(out, dev.to(tok), dev.to(wte), dev.to(wpe), B, T, C)
+    assert np.array_equal(dev.back(out), orc.encoder_forward(tok, wte, wpe))
+    assert out.dtype == torch.float32
+
+
+# ------------------------------------------------------------------------------- GEMM
+GEMM_SHAPES = [
+    # B, T, C(K), OC(N), bias, act, residual
+    (1, 128, 64, 64, True, 0, False),        # one tile, two K blocks
+    (2, 64, 768, 2304, True, 0, False),      # QKV, c0-sized M
+    (4, 64, 768, 768, True, 0, False),       # attn-proj
+    (4, 64, 768, 3072, True, 1, False),      # fc + GELU
+    (4, 64, 3072, 768, True, 0, True),       # fc-proj + residual
+    (2, 64, 768, 50304, False, 0, False),    # lm-head, no bias, ragged last N tile
+    (1, 192, 1600, 4800, True, 0, False),    # XL QKV, M not a multiple of 128
+    (1, 64, 1600, 6400, True, 1, False),     # XL fc, M < 128
+    (1, 64, 100, 36, True, 0, False),        # K not a multiple of 32, tiny N
+    (8, 128, 768, 768, True, 0, False),      # several M tiles
+]
+
+
+@pytest.mark.parametrize("B,T,C,OC,has_bias,act,has_res", GEMM_SHAPES)
+def test_matmul_tf32_matches_oracle(ctx, dev, orc, B, T, C, OC, has_bias, act, has_res):
+    x = orc.fill_normal((B, T, C), 81)
+    w = orc.fill_normal((OC, C), 82, std=0.02)
+    bias = orc.fill_normal((OC,), 83, std=0.01) if has_bias else None
+    res = orc.fill_normal((B, T, OC), 84) if has_res else None
+    want = orc.matmul_forward(x, w, bias, act=act, residual=res, precise=True)
+    out = dev.full((B, T, OC), float("nan"))
+    ctx.matmul_forward(out, dev.to(x), dev.to(w), None if bias is None else dev.to(bias), B, T, C, OC,
+                       act=act, residual=None if res is None else dev.to(res))
+    got = dev.back(out)
+    assert np.isfinite(got).all(), "unwritten or non-finite outputs"
+    ref_scale = want - (res if has_res else 0)  # error is relative to the GEMM part
+    rr = float(np.sqrt(np.mean((got.astype(np.float64) - want) ** 2)) / np.sqrt(np.mean(ref_scale.astype(np.float64) ** 2)))
+    assert rr < 1e-3, f"relative RMS error {rr}"
+    assert np.abs(got - want).max() < 6e-3 * max(1.0, (C / 768) ** 0.5)
+
+
+def test_matmul_linearity_full_size(ctx, dev, orc):
+    # size-independent property at the benchmark's row count (M = 8192): f(x1 + x2) = f(x1) + f(x2)
+    # up to TF32 rounding, and an oracle spot check on the last rows
+    import torch
+    B, T, C, OC = 8, 1024, 768, 2304
+    x1, x2 = orc.fill_normal((B, T, C), 91), orc.fill_normal((B, T, C), 92)
+    w = orc.fill_normal((OC, C), 93, std=0.02)
+    dw = dev.to(w)
+    outs = []
+    for x in (x1, x2, x1 + x2):
+        o = dev.empty((B, T, OC))
+        ctx.matmul_forward(o, dev.to(x), dw, None, B, T, C, OC)
+        ctx.sync_check()
+        outs.append(o)
+    lin = (outs[0] + outs[1] - outs[2]).abs().max().item()
+    assert lin < 8e-3
+    want = orc.matmul_forward(x1[-1:, -256:], w, None, precise=True)
+    assert np.abs(outs[0][-1:, -256:].cpu().numpy() - want).max() < 6e-3
+    assert torch.isfinite(outs[2]).all()
+
+
+# -------------------------------------------------------------------------- attention
+@pytest.mark.parametrize("B,T,NH", [(1, 64, 1), (2, 128, 2), (1, 256, 12), (2, 192, 3), (1, 1024, 2), (1, 384, 25)])
+def test_attention_matches_oracle(ctx, dev, orc, B, T, NH):
+    C = NH * 64
+    qkv = orc.fill_normal((B, T, 3 * C), 101)
+    want, wlse = orc.attention_forward(qkv, NH, precise=True)
+    out, lse = dev.full((B, T, C), float("nan")), dev.full((B, NH, T), float("nan"))
+    d_in = dev.to(qkv)
+    ctx.attention_forward(out, None, lse, d_in, B, T, C, NH)
+    got = dev.back(out)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() < 3e-3
+    assert np.abs(dev.back(lse) - wlse).max() < 3e-3
+    assert np.array_equal(d_in.cpu().numpy(), qkv), "inp must not be modified"
+
+
+def test_attention_without_stats_and_large_scores(ctx, dev, orc):
+    # att == NULL; scores far below zero except the diagonal exercise the running-max path
+    B, T, NH = 1, 256, 2
+    C = NH * 64
+    qkv = orc.fill_normal((B, T, 3 * C), 111, std=4.0)
+    want, _ = orc.attention_forward(qkv, NH, precise=True)
+    out = dev.empty((B, T, C))
+    ctx.attention_forward(out, None, None, dev.to(qkv), B, T, C, NH)
+    # |s| reaches ~100 here, so TF32 operand rounding moves the softmax weights by a few percent
+    assert np.abs(dev.back(out) - want).max() < 0.5
+    assert _rel_rms(dev.back(out), want) < 3e-2
+
+
+# ------------------------------------------------------------------------ error paths
+def test_precondition_failures_return_status(ctx, dev, pkg):
+    x = dev.empty((1, 64, 768))
+    w = dev.empty((768, 768))
+    assert ctx.raw("matmul_forward", x, x, w, None, 1, 64, 768, 766, 0, None, 0) == 2      # OC % 4
+    assert ctx.raw("matmul_forward", None, x, w, None, 1, 64, 768, 768, 0, None, 0) == 1   # NULL out
+    assert ctx.raw("attention_forward", x, None, None, x, 1, 64, 768, 8) == 2              # head size 96
+    assert ctx.raw("attention_forward", x, None, None, x, 1, 63, 768, 12) == 2             # T % 64
+    assert ctx.raw("layernorm_forward", x, None, None, x, w, w, 1, 64, 770) == 2           # C % 4
+    import torch
+    mis = torch.empty(64 * 768 + 1, device="cuda")[1:]
+    assert ctx.raw("layernorm_forward", x, None, None, mis, w, w, 1, 64, 768) == 3         # misaligned
+    ctx.sync_check()
+
+
+def test_void_shims_run_on_default_stream(ctx, dev, orc, pkg):
+    import torch
+    B, T, C = 2, 64, 768
+    a, b = orc.fill_normal((B * T * C,), 121), orc.fill_normal((B * T * C,), 122)
+    da, db, out = dev.to(a), dev.to(b), dev.empty((B * T * C,))
+    lib = pkg.lib()
+    lib.residual_forward(out.data_ptr(), da.data_ptr(), db.data_ptr(), B * T * C)
+    torch.cuda.synchronize()
+    assert np.array_equal(out.cpu().numpy(), a + b)
+    x = orc.fill_normal((B, T, C), 123)
+    w = orc.fill_normal((C, C), 124, std=0.02)
+    bias = orc.fill_normal((C,), 125, std=0.01)
+    o2 = dev.empty((B, T, C))
+    lib.matmul_forward(o2.data_ptr(), dev.to(x).data_ptr(), dev.to(w).data_ptr(), dev.to(bias).data_ptr(), B, T, C, C)
+    torch.cuda.synchronize()
+    assert np.abs(o2.cpu().numpy() - orc.matmul_forward(x, w, bias, precise=True)).max() < 6e-3
