@@ -39,7 +39,11 @@ EXPORTS = (
     "b200_gpt2_param_offsets", "b200_gpt2_create", "b200_gpt2_destroy", "b200_gpt2_params",
     "b200_gpt2_load_params_host", "b200_gpt2_set_options", "b200_gpt2_forward",
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_activation",
+    "b200_gpt2_set_profile", "b200_gpt2_read_profile",
 )
+
+PROF_NAMES = ("encoder", "layernorm", "gemm_qkv", "attention", "gemm_attproj", "fused_residual_layernorm",
+              "gemm_fc", "gemm_fcproj", "gemm_lmhead")
 
 _lib = None
 
@@ -101,6 +105,8 @@ def lib() -> C.CDLL:
         l.b200_gpt2_forward_host.argtypes = [vp, vp, i, i, vp, vp, vp]
         l.b200_gpt2_activation.argtypes = [vp, C.c_char_p]
         l.b200_gpt2_activation.restype = vp
+        l.b200_gpt2_set_profile.argtypes = [vp, i]
+        l.b200_gpt2_read_profile.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_long)]
         _lib = l
     return _lib
 
@@ -288,6 +294,16 @@ class GPT2:
         self.ctx.check(lib().b200_gpt2_forward_host(self._h, _ptr(tokens_host), B, T, _ptr(logits_host),
                                                     _ptr(last_logits_host), _ptr(argmax_host)), "gpt2_forward_host")
 
+    def set_profile(self, enabled: bool):
+        self.ctx.check(lib().b200_gpt2_set_profile(self._h, int(enabled)), "set_profile")
+
+    def read_profile(self) -> dict[str, tuple[float, int]]:
+        """{operator: (milliseconds, launches)} since the previous read-out; synchronises."""
+        ms = (C.c_double * len(PROF_NAMES))()
+        n = (C.c_long * len(PROF_NAMES))()
+        self.ctx.check(lib().b200_gpt2_read_profile(self._h, ms, n), "read_profile")
+        return {name: (float(ms[k]), int(n[k])) for k, name in enumerate(PROF_NAMES)}
+
     def activation(self, name: str, shape, dtype=None):
         import torch
         p = lib().b200_gpt2_activation(self._h, name.encode())
@@ -303,7 +319,6 @@ class GPT2:
 
 def _view_device(ptr: int, shape, dtype, device: int):
     """Zero-copy torch view over device memory owned by the library."""
-    import numpy as np
     import torch
 
     n = 1

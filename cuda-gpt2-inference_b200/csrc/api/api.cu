@@ -15,8 +15,9 @@ int b200_fail_cuda(b200_ctx* ctx, cudaError_t e, const char* what) {
 }
 
 int b200_get_tensor_map(b200_ctx* ctx, CUtensorMap* out, const float* ptr, uint64_t rows,
-                        uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
-    TensorMapKey key{ptr, rows, cols, ld, box_rows, box_cols};
+                        uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols,
+                        int swizzle_atom32) {
+    TensorMapKey key{ptr, rows, cols, ld, box_rows, box_cols, swizzle_atom32};
     auto it = ctx->tmap_cache.find(key);
     if (it != ctx->tmap_cache.end()) { *out = it->second; return B200_OK; }
     if (!ctx->encode_tiled) return B200_ERR_STATE;
@@ -28,7 +29,8 @@ int b200_get_tensor_map(b200_ctx* ctx, CUtensorMap* out, const float* ptr, uint6
     CUtensorMap m;
     CUresult r = ctx->encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), dims,
                                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                   swizzle_atom32 ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
         ctx->last_error = "cuTensorMapEncodeTiled failed with CUresult " + std::to_string((int)r);

@@ -17,16 +17,17 @@ struct TensorMapKey {
     const void* ptr;
     uint64_t rows, cols, ld;
     uint32_t box_rows, box_cols;
+    int swizzle;
     bool operator==(const TensorMapKey& o) const {
         return ptr == o.ptr && rows == o.rows && cols == o.cols && ld == o.ld &&
-               box_rows == o.box_rows && box_cols == o.box_cols;
+               box_rows == o.box_rows && box_cols == o.box_cols && swizzle == o.swizzle;
     }
 };
 struct TensorMapKeyHash {
     size_t operator()(const TensorMapKey& k) const {
         uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
         h ^= (k.rows + 0x7F4A7C15ull) * 0xBF58476D1CE4E5B9ull;
-        h ^= (k.cols << 20) ^ (k.ld << 40) ^ (uint64_t(k.box_rows) << 8) ^ k.box_cols;
+        h ^= (k.cols << 20) ^ (k.ld << 40) ^ (uint64_t(k.box_rows) << 8) ^ k.box_cols ^ (uint64_t(k.swizzle) << 60);
         return static_cast<size_t>(h ^ (h >> 29));
     }
 };
@@ -51,9 +52,12 @@ int b200_fail_cuda(b200_ctx* ctx, cudaError_t e, const char* what);
     } while (0)
 
 // Tiled fp32 2-D tensor map over a row-major [rows, cols] matrix with leading dimension ld
-// (elements), box = box_rows x box_cols, 128-byte swizzle, zero fill outside the matrix.
+// (elements), box = box_rows x box_cols, zero fill outside the matrix.  swizzle_atom32 == 0:
+// 128-byte swizzle of 16-byte chunks (K-major UMMA operands); != 0: 128-byte swizzle of 32-byte
+// chunks (the only layout the tensor core accepts for an MN-major TF32 operand).
 // Cached per context.  Returns B200_OK or an error status.
 int b200_get_tensor_map(b200_ctx* ctx, CUtensorMap* out, const float* ptr, uint64_t rows,
-                        uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+                        uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols,
+                        int swizzle_atom32 = 0);
 
 inline bool b200_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

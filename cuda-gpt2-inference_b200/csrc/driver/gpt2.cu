@@ -8,6 +8,7 @@
 #include <map>
 #include <new>
 #include <utility>
+#include <vector>
 #include "../api/ctx.h"
 #include "../kernels/kernels.h"
 
@@ -27,9 +28,35 @@ struct b200_gpt2 {
     int* argmax = nullptr;
     int round_operands = 0, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
     std::map<std::pair<int, int>, cudaGraphExec_t> graphs;
+    // per-operator timing (b200_gpt2_set_profile): one event pair per kernel launch
+    bool profile = false;
+    std::vector<cudaEvent_t> ev_pool;
+    std::vector<int> ev_cat;     // category of each recorded pair
+    size_t ev_used = 0;          // events handed out since the last read-out
+    double prof_ms[B200_PROF_NUM] = {};
+    long prof_launches[B200_PROF_NUM] = {};
 };
 
 namespace {
+
+// hands out a start/stop event pair for category `cat` and records the start
+int prof_begin(b200_gpt2* m, int cat) {
+    if (m->ev_used + 2 > m->ev_pool.size()) {
+        for (int i = 0; i < 256; ++i) {
+            cudaEvent_t e;
+            B200_CUDA(m->ctx, cudaEventCreate(&e));
+            m->ev_pool.push_back(e);
+        }
+    }
+    m->ev_cat.push_back(cat);
+    B200_CUDA(m->ctx, cudaEventRecord(m->ev_pool[m->ev_used], m->ctx->stream));
+    m->ev_used += 2;
+    return B200_OK;
+}
+int prof_end(b200_gpt2* m) {
+    B200_CUDA(m->ctx, cudaEventRecord(m->ev_pool[m->ev_used - 1], m->ctx->stream));
+    return B200_OK;
+}
 
 int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
     using namespace b200;
@@ -42,9 +69,16 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
     const int rnd = m->round_operands ? ROUND_OUT_TF32 : 0;
     const int grnd = m->round_operands ? GEMM_ROUND_OUT_TF32 : 0;
     int st;
-#define STEP(call) do { st = (call); if (st != B200_OK) return st; } while (0)
-    STEP(launch_encoder(ctx, m->residual, tokens, P + off[0], P + off[1], B, T, C, Vp));
-    STEP(launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], M, C, rnd));
+    const bool prof = m->profile;
+#define STEP(cat, call)                                             \
+    do {                                                            \
+        if (prof) { st = prof_begin(m, (cat)); if (st != B200_OK) return st; } \
+        st = (call);                                                \
+        if (st != B200_OK) return st;                               \
+        if (prof) { st = prof_end(m); if (st != B200_OK) return st; } \
+    } while (0)
+    STEP(B200_PROF_ENCODER, launch_encoder(ctx, m->residual, tokens, P + off[0], P + off[1], B, T, C, Vp));
+    STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], M, C, rnd));
     for (int l = 0; l < L; ++l) {
         const float* qkvw = P + off[4] + (size_t)l * 3 * C * C;
         const float* qkvb = P + off[5] + (size_t)l * 3 * C;
@@ -56,20 +90,25 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
         const float* fcb = P + off[11] + (size_t)l * 4 * C;
         const float* fpw = P + off[12] + (size_t)l * C * 4 * C;
         const float* fpb = P + off[13] + (size_t)l * C;
-        STEP(launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * C, grnd, m->gemm_mode));
-        STEP(launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, C, NH, rnd));
-        STEP(launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, C, C, 0, m->gemm_mode));
-        STEP(launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
+        // The attention kernel multiplies on the TF32 pipe in every mode.  Storing q, k and v
+        // rounded-to-nearest makes them exact TF32 values, so the tensor core's truncation no
+        // longer shrinks every product (a systematic bias); what is left is unbiased rounding
+        // noise that the softmax-weighted sums average down.
+        const int qkv_flags = (m->round_operands || m->gemm_mode == B200_TF32X3) ? GEMM_ROUND_OUT_TF32 : 0;
+        STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * C, qkv_flags, m->gemm_mode));
+        STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, C, NH, rnd));
+        STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, C, C, 0, m->gemm_mode));
+        STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
                                              m->branch, ln2w, ln2b, M, C, rnd));
-        STEP(launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, 4 * C, GEMM_GELU | grnd, m->gemm_mode));
-        STEP(launch_gemm_tf32(ctx, m->branch, m->fch, fpw, fpb, nullptr, M, 4 * C, C, 0, m->gemm_mode));
+        STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, 4 * C, GEMM_GELU | grnd, m->gemm_mode));
+        STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, m->branch, m->fch, fpw, fpb, nullptr, M, 4 * C, C, 0, m->gemm_mode));
         const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
         const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
-        STEP(launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
+        STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
                                              m->branch, nw, nb, M, C, rnd));
     }
     const float* head_w = (m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0];
-    STEP(launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, Vp, 0, m->lmhead_mode));
+    STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, Vp, 0, m->lmhead_mode));
 #undef STEP
     return B200_OK;
 }
@@ -146,6 +185,7 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     if (!m) return B200_ERR_NULL;
     cudaSetDevice(m->ctx->device);
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+    for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
     void* ptrs[] = {m->params, m->wte_rounded, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
                     m->fch, m->logits, m->tokens, m->argmax};
     for (void* p : ptrs) if (p) cudaFree(p);
@@ -189,7 +229,7 @@ int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) {
         int st = round_weights_once(m);
         if (st != B200_OK) return st;
     }
-    if (!m->use_graph || ctx->stream == nullptr) return enqueue_forward(m, tokens, B, T);
+    if (!m->use_graph || ctx->stream == nullptr || m->profile) return enqueue_forward(m, tokens, B, T);
 
     // CUDA-graph replay: the graph reads token ids from the model's own token buffer
     if (tokens != m->tokens)
@@ -244,6 +284,33 @@ int b200_gpt2_forward_host(b200_gpt2* m, const int* tokens_host, int B, int T, f
     if (logits_host)
         B200_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, M * Vp * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return b200_ctx_sync_check(ctx);
+}
+
+int b200_gpt2_set_profile(b200_gpt2* m, int enabled) {
+    if (!m) return B200_ERR_NULL;
+    m->profile = enabled != 0;
+    return B200_OK;
+}
+
+int b200_gpt2_read_profile(b200_gpt2* m, double* ms, long* launches) {
+    if (!m) return B200_ERR_NULL;
+    b200_ctx* ctx = m->ctx;
+    B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    for (size_t i = 0; i < m->ev_cat.size(); ++i) {
+        float t = 0.f;
+        B200_CUDA(ctx, cudaEventElapsedTime(&t, m->ev_pool[2 * i], m->ev_pool[2 * i + 1]));
+        m->prof_ms[m->ev_cat[i]] += t;
+        m->prof_launches[m->ev_cat[i]]++;
+    }
+    m->ev_cat.clear();
+    m->ev_used = 0;
+    for (int c = 0; c < B200_PROF_NUM; ++c) {
+        if (ms) ms[c] = m->prof_ms[c];
+        if (launches) launches[c] = m->prof_launches[c];
+        m->prof_ms[c] = 0.0;
+        m->prof_launches[c] = 0;
+    }
+    return B200_OK;
 }
 
 void* b200_gpt2_activation(b200_gpt2* m, const char* name) {

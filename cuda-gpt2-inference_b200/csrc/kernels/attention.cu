@@ -12,7 +12,8 @@
 //   warp 0     TMA producer: Q once, then K/V blocks of 128 keys into a 2-stage ring
 //   warp 1     tensor-memory owner and UMMA issuer:  S_j = Q K_j^T  (kind::tf32, both operands
 //              K-major from shared memory, accumulator in tensor memory, double buffered) and
-//              O_j = P_j V_j (P from shared memory, V as an MN-major operand)
+//              O_j = P_j V_j (P from shared memory, V as an MN-major operand, loaded with the
+//              32-byte-chunk swizzle that MN-major TF32 operands require)
 //   warps 2-5  softmax: one query row per thread (no shuffles in the 32x32b tensor-memory
 //              layout); two passes over S in tensor memory (row max, then exp2), P written to
 //              shared memory in the swizzled K-major operand layout, O_j accumulated in fp32
@@ -55,7 +56,8 @@ struct AttArgs {
 };
 
 __global__ void __launch_bounds__(kAttThreads, 1)
-attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttArgs args) {
+attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_v,
+                 const AttArgs args) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_s = smem + AttSmem::Q_OFF;
@@ -92,6 +94,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttArgs arg
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmap_qkv);
+        tma_prefetch_desc(&tmap_v);
     }
     if (warp == 1) {
         tmem_alloc(tmem_holder, kTmemCols);
@@ -118,8 +121,8 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttArgs arg
                 const int y = row_base + j * BKV;
                 tma_load_2d(k_s + (2 * s) * kBlk, &tmap_qkv, xk, y, &kv_full[s]);
                 tma_load_2d(k_s + (2 * s + 1) * kBlk, &tmap_qkv, xk + 32, y, &kv_full[s]);
-                tma_load_2d(v_s + (2 * s) * kBlk, &tmap_qkv, xv, y, &kv_full[s]);
-                tma_load_2d(v_s + (2 * s + 1) * kBlk, &tmap_qkv, xv + 32, y, &kv_full[s]);
+                tma_load_2d(v_s + (2 * s) * kBlk, &tmap_v, xv, y, &kv_full[s]);
+                tma_load_2d(v_s + (2 * s + 1) * kBlk, &tmap_v, xv + 32, y, &kv_full[s]);
             }
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_PRODUCER);
         }
@@ -161,9 +164,10 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const AttArgs arg
                 for (int ks = 0; ks < BKV / 8; ++ks) {
                     // A: P, K-major, 8 keys = 32 bytes inside the 32-key block
                     const uint64_t a = make_smem_desc_sw128(smem_u32(p_s) + (ks >> 2) * kBlk + (ks & 3) * 32, 16, 1024);
-                    // B: V, MN-major: 8 keys = 8 rows of 128 bytes; the two 32-wide halves of the
-                    // head dimension lie kBlk apart
-                    const uint64_t bd = make_smem_desc_sw128(smem_u32(v_s + 2 * s * kBlk) + ks * 1024, kBlk, 1024);
+                    // B: V, MN-major (32-byte-chunk swizzle): 8 keys = 8 rows of 128 bytes = two
+                    // 4-row swizzle groups 512 bytes apart; the two 32-wide halves of the head
+                    // dimension lie kBlk apart
+                    const uint64_t bd = make_smem_desc_sw128<1>(smem_u32(v_s + 2 * s * kBlk) + ks * 1024, kBlk, 512);
                     umma_tf32_ss(d, a, bd, idesc_o, ks != 0);
                 }
                 umma_commit(o_full);
@@ -296,6 +300,9 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
     CUtensorMap tm;
     int st = b200_get_tensor_map(ctx, &tm, qkv, (uint64_t)B * T, (uint64_t)3 * C, (uint64_t)3 * C, BKV, 32);
     if (st != B200_OK) return st;
+    CUtensorMap tmv;  // V is consumed as an MN-major operand: 32-byte-chunk swizzle
+    st = b200_get_tensor_map(ctx, &tmv, qkv, (uint64_t)B * T, (uint64_t)3 * C, (uint64_t)3 * C, BKV, 32, 1);
+    if (st != B200_OK) return st;
     AttArgs a;
     a.out = out; a.lse = lse; a.B = B; a.T = T; a.C = C; a.NH = NH;
     a.num_qt = (T + BQ - 1) / BQ;
@@ -303,7 +310,7 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
     a.round_out = (flags & ROUND_OUT_TF32) ? 1 : 0;
     a.status = ctx->d_status;
     dim3 grid(a.num_qt, NH, B);
-    attention_kernel<<<grid, kAttThreads, AttSmem::TOTAL, ctx->stream>>>(tm, a);
+    attention_kernel<<<grid, kAttThreads, AttSmem::TOTAL, ctx->stream>>>(tm, tmv, a);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

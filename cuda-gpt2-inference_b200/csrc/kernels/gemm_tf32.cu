@@ -9,14 +9,19 @@
 // Both operands are K-major as stored (inp rows and weight rows are K-contiguous), so no
 // transposes are needed.
 //
-// CTA = 6 warps, persistent over output tiles of 128 x BN:
+// CTA = 6 warps (10 in the 3xTF32 mode), persistent over output tiles of 128 x BN:
 //   warp 0      TMA producer: per 32-wide K block one {32 x 128} box of inp and one {32 x BN}
 //               box of weight into a ring of STAGES shared-memory stages (full/empty mbarriers)
-//   warp 1      allocates tensor memory; one elected lane issues 4 UMMAs (K = 8 each) per stage
-//               and commits the stage's empty barrier; commits tmem_full after the last K block
+//   warp 1      allocates tensor memory; one elected lane issues the UMMAs (K = 8 each) of a
+//               stage and commits the stage's empty barrier; commits tmem_full after the last
+//               K block
 //   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bias/GELU/residual,
 //               float4 stores.  Two accumulators (2 x BN columns) let the epilogue of tile i
 //               overlap the main loop of tile i+1.
+//   warps 6-9   (3xTF32 only) split warps: the tensor core reads only the upper 19 bits of an
+//               fp32 operand (it truncates), so for every staged tile they write the dropped
+//               part  x_small = x - trunc_tf32(x)  into a second buffer, and the issuer
+//               accumulates  A.B + A_small.B + A.B_small : fp32-level products on the TF32 pipe.
 // Every wait is time-bounded; a wait that runs out makes all roles leave, the CTA frees its
 // tensor memory and records a code in the context's status word.
 #include "kernels.h"
@@ -28,14 +33,15 @@ namespace {
 
 constexpr int BM = 128;
 constexpr int BK = 32;  // fp32 elements per K block = 128 bytes = one swizzle row
-constexpr int kGemmThreads = 192;
 constexpr int kMaxSmem = 232448;  // 227 KB
 
-template <int BN>
+template <int BN, bool X3>
 struct GemmCfg {
+    static constexpr int THREADS = X3 ? 320 : 192;
     static constexpr int A_BYTES = BM * BK * 4;
     static constexpr int B_BYTES = BN * BK * 4;
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (X3 ? 2 : 1);
+    static constexpr int TX_BYTES = A_BYTES + B_BYTES;  // what TMA delivers per stage
     static constexpr int BAR_BYTES = 512;
     static constexpr int STAGES_RAW = (kMaxSmem - 1024 - BAR_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
@@ -46,6 +52,7 @@ struct GemmCfg {
     static_assert(SMEM > 117 * 1024, "a second resident CTA could block in tcgen05.alloc");
     static_assert(SMEM <= kMaxSmem, "shared memory over the 227 KB limit");
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN: multiple of 32 up to 256");
+    static_assert(STAGES >= 2, "need at least a double buffer");
 };
 
 struct GemmArgs {
@@ -59,22 +66,29 @@ struct GemmArgs {
     int* status;
 };
 
-template <int BN>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__device__ __forceinline__ float tf32_dropped_part(float x) {
+    return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
+}
+
+template <int BN, bool X3>
+__global__ void __launch_bounds__(GemmCfg<BN, X3>::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const GemmArgs args) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, X3>;
     constexpr int STAGES = Cfg::STAGES;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem + STAGES * Cfg::A_BYTES;
+    uint8_t* smem_a = smem;                                        // [STAGES][A_BYTES]
+    uint8_t* smem_b = smem_a + STAGES * Cfg::A_BYTES;              // [STAGES][B_BYTES]
+    uint8_t* smem_as = smem_b + STAGES * Cfg::B_BYTES;             // X3: dropped parts of A
+    uint8_t* smem_bs = smem_as + (X3 ? STAGES * Cfg::A_BYTES : 0); // X3: dropped parts of B
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
-    uint64_t* full_bar = bars;                   // [STAGES]
-    uint64_t* empty_bar = bars + STAGES;         // [STAGES]
-    uint64_t* tmem_full_bar = bars + 2 * STAGES; // [2]
+    uint64_t* full_bar = bars;                     // [STAGES] TMA landed
+    uint64_t* empty_bar = bars + STAGES;           // [STAGES] UMMAs of the stage retired
+    uint64_t* split_bar = bars + 2 * STAGES;       // [STAGES] X3: dropped parts written
+    uint64_t* tmem_full_bar = bars + 3 * STAGES;   // [2]
     uint64_t* tmem_empty_bar = tmem_full_bar + 2;  // [2]
-    uint64_t* drain_bar = tmem_empty_bar + 2;    // [1]
+    uint64_t* drain_bar = tmem_empty_bar + 2;      // [1]
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(drain_bar + 1);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -84,7 +98,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int num_kb = (args.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+            mbar_init(&split_bar[s], 128);
+        }
         for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 128); }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
@@ -118,7 +136,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&full_bar[s], Cfg::STAGE_BYTES);
+                    mbar_arrive_expect_tx(&full_bar[s], Cfg::TX_BYTES);
                     tma_load_2d(smem_a + s * Cfg::A_BYTES, &tmap_a, kb * BK, m_blk * BM, &full_bar[s]);
                     tma_load_2d(smem_b + s * Cfg::B_BYTES, &tmap_b, kb * BK, n_blk * BN, &full_bar[s]);
                 }
@@ -141,7 +159,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
-                    if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+                    // in the 3xTF32 mode the split warps signal after the TMA data has landed
+                    if (!mbar_wait(X3 ? &split_bar[s] : &full_bar[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
                     const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * Cfg::A_BYTES), 16, 1024);
                     const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * Cfg::B_BYTES), 16, 1024);
@@ -150,6 +169,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         // advance 8 fp32 = 32 bytes along K inside the swizzled row: +2 in the
                         // (address >> 4) field
                         umma_tf32_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    }
+                    if (X3) {
+                        const uint64_t as_desc = make_smem_desc_sw128(smem_u32(smem_as + s * Cfg::A_BYTES), 16, 1024);
+                        const uint64_t bs_desc = make_smem_desc_sw128(smem_u32(smem_bs + s * Cfg::B_BYTES), 16, 1024);
+#pragma unroll
+                        for (int k = 0; k < BK / 8; ++k) {
+                            umma_tf32_ss(d_tmem, as_desc + 2 * k, b_desc + 2 * k, idesc, 1);
+                            umma_tf32_ss(d_tmem, a_desc + 2 * k, bs_desc + 2 * k, idesc, 1);
+                        }
                     }
                     umma_commit(&empty_bar[s]);
                 }
@@ -160,7 +188,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             if (!mbar_wait(drain_bar, 0, abort_flag)) ok = false;
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
         }
-    } else {
+    } else if (warp < 6) {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;  // the lane quarter this warp may read
         const bool do_gelu = (args.flags & GEMM_GELU) != 0;
@@ -210,6 +238,38 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             mbar_arrive(&tmem_empty_bar[acc]);
         }
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_EPILOGUE);
+    } else if (X3) {
+        // ------------------------------------------------------- split warps (3xTF32)
+        const int t = threadIdx.x - 192;  // 0..127
+        uint32_t it = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int s = it % STAGES;
+                const uint32_t ph = (it / STAGES) & 1;
+                if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
+                // element-wise, so the swizzled placement carries over unchanged
+                const float4* a_src = reinterpret_cast<const float4*>(smem_a + s * Cfg::A_BYTES);
+                float4* a_dst = reinterpret_cast<float4*>(smem_as + s * Cfg::A_BYTES);
+#pragma unroll
+                for (int i = 0; i < Cfg::A_BYTES / 16 / 128; ++i) {
+                    const float4 v = a_src[i * 128 + t];
+                    a_dst[i * 128 + t] = make_float4(tf32_dropped_part(v.x), tf32_dropped_part(v.y),
+                                                     tf32_dropped_part(v.z), tf32_dropped_part(v.w));
+                }
+                const float4* b_src = reinterpret_cast<const float4*>(smem_b + s * Cfg::B_BYTES);
+                float4* b_dst = reinterpret_cast<float4*>(smem_bs + s * Cfg::B_BYTES);
+#pragma unroll
+                for (int i = 0; i < Cfg::B_BYTES / 16 / 128; ++i) {
+                    const float4 v = b_src[i * 128 + t];
+                    b_dst[i * 128 + t] = make_float4(tf32_dropped_part(v.x), tf32_dropped_part(v.y),
+                                                     tf32_dropped_part(v.z), tf32_dropped_part(v.w));
+                }
+                fence_proxy_async_smem();
+                mbar_arrive(&split_bar[s]);
+            }
+        }
+        if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
     }
 
     tc_fence_before_sync();
@@ -226,17 +286,17 @@ inline int tile_step_cost(int bn) {
     return tensor > feed ? tensor : feed;
 }
 
-template <int BN>
+template <int BN, bool X3>
 int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& a) {
-    using Cfg = GemmCfg<BN>;
+    using Cfg = GemmCfg<BN, X3>;
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63]) {
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_kernel<BN, X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
         attr_set[ctx->device & 63] = true;
     }
     const int tiles = a.num_m_blocks * a.num_n_blocks;
     const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
-    gemm_tf32_kernel<BN><<<grid, kGemmThreads, Cfg::SMEM, ctx->stream>>>(ta, tb, a);
+    gemm_tf32_kernel<BN, X3><<<grid, Cfg::THREADS, Cfg::SMEM, ctx->stream>>>(ta, tb, a);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;
@@ -247,18 +307,20 @@ int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Gemm
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      int mode) {
-    (void)mode;
+    const bool x3 = (mode == B200_TF32X3);
     const int num_m = (M + BM - 1) / BM;
     // pick the N tile that minimises waves x per-tile cost on this GPU's SM count
-    const int cands[5] = {256, 192, 128, 96, 64};
-    int best_bn = 256;
-    long best_cost = -1;
-    for (int i = 0; i < 5; ++i) {
-        const int bn = cands[i];
-        const long tiles = (long)num_m * ((N + bn - 1) / bn);
-        const long waves = (tiles + ctx->num_sms - 1) / ctx->num_sms;
-        const long cost = waves * tile_step_cost(bn);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
+    int best_bn = 128;
+    if (!x3) {
+        const int cands[5] = {256, 192, 128, 96, 64};
+        long best_cost = -1;
+        for (int i = 0; i < 5; ++i) {
+            const int bn = cands[i];
+            const long tiles = (long)num_m * ((N + bn - 1) / bn);
+            const long waves = (tiles + ctx->num_sms - 1) / ctx->num_sms;
+            const long cost = waves * tile_step_cost(bn);
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
+        }
     }
     GemmArgs a;
     a.out = out; a.bias = bias; a.residual = residual;
@@ -276,12 +338,13 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
     if (st != B200_OK) return st;
     st = b200_get_tensor_map(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)best_bn, BK);
     if (st != B200_OK) return st;
+    if (x3) return launch_one<128, true>(ctx, ta, tb, a);
     switch (best_bn) {
-        case 256: return launch_one<256>(ctx, ta, tb, a);
-        case 192: return launch_one<192>(ctx, ta, tb, a);
-        case 128: return launch_one<128>(ctx, ta, tb, a);
-        case 96:  return launch_one<96>(ctx, ta, tb, a);
-        default:  return launch_one<64>(ctx, ta, tb, a);
+        case 256: return launch_one<256, false>(ctx, ta, tb, a);
+        case 192: return launch_one<192, false>(ctx, ta, tb, a);
+        case 128: return launch_one<128, false>(ctx, ta, tb, a);
+        case 96:  return launch_one<96, false>(ctx, ta, tb, a);
+        default:  return launch_one<64, false>(ctx, ta, tb, a);
     }
 }
 

@@ -172,10 +172,14 @@ __device__ __forceinline__ void tmem_ld_wait() {
 // Shared-memory matrix descriptor, 128-byte swizzle.  Field layout (64 bit):
 //   [0,14)  start address >> 4          [16,30) leading byte offset >> 4
 //   [32,46) stride byte offset >> 4     [46,48) version = 1 on sm_100
-//   [61,64) layout: 2 = SWIZZLE_128B
-// K-major operand (rows of 128 B = 32 fp32 along K, 8-row groups of 1024 B): SBO = 1024,
-// LBO unused.  MN-major operand (rows of 128 B = 32 fp32 along N, one row per k): LBO is the
-// byte distance between successive 32-wide N blocks, SBO between successive groups of 8 k.
+//   [61,64) layout: 2 = SWIZZLE_128B (16-byte chunks), 1 = SWIZZLE_128B with 32-byte chunks
+// K-major operand (rows of 128 B = 32 fp32 along K, 8-row groups of 1024 B): layout 2,
+// SBO = 1024, LBO unused.
+// MN-major TF32 operand (rows of 128 B = 32 fp32 along N, one row per k; the tensor core only
+// accepts the 32-byte-chunk swizzle here, whose pattern repeats every 4 rows): layout 1, LBO =
+// byte distance between successive 32-wide N blocks, SBO = between successive groups of 4 k
+// (512 for densely packed rows).
+template <int LAYOUT = 2>
 __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uint32_t lbo_bytes,
                                                          uint32_t sbo_bytes) {
     uint64_t d = 0;
@@ -183,7 +187,7 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
     d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
     d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
     d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
+    d |= static_cast<uint64_t>(LAYOUT) << 61;
     return d;
 }
 

@@ -184,6 +184,18 @@ float* b200_gpt2_logits(b200_gpt2* model);
  *   argmax_host      [B,T]     arg-max token over [0,V) per position (nullable) */
 int b200_gpt2_forward_host(b200_gpt2* model, const int* tokens_host, int B, int T,
                            float* logits_host, float* last_logits_host, int* argmax_host);
+/* Per-operator device timing of the forward.  While enabled, every kernel launch of
+ * b200_gpt2_forward is bracketed by a CUDA event pair on the context's stream (graph replay is
+ * bypassed).  b200_gpt2_read_profile synchronises the stream, adds up the elapsed milliseconds
+ * and launch counts per category since the previous read-out into ms[B200_PROF_NUM] and
+ * launches[B200_PROF_NUM], and clears them. */
+enum {
+    B200_PROF_ENCODER = 0, B200_PROF_LAYERNORM, B200_PROF_GEMM_QKV, B200_PROF_ATTENTION,
+    B200_PROF_GEMM_ATTPROJ, B200_PROF_FUSED_RES_LN, B200_PROF_GEMM_FC, B200_PROF_GEMM_FCPROJ,
+    B200_PROF_GEMM_LMHEAD, B200_PROF_NUM
+};
+int b200_gpt2_set_profile(b200_gpt2* model, int enabled);
+int b200_gpt2_read_profile(b200_gpt2* model, double* ms, long* launches);
 /* Device pointer of an intermediate activation of the last forward, for tests:
  * name in {"encoded","ln_out","qkv","atty","branch","fch","residual","argmax"}; NULL if unknown. */
 void* b200_gpt2_activation(b200_gpt2* model, const char* name);
