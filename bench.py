@@ -325,15 +325,130 @@ def run_ours(args):
     return 0
 
 
+def run_kernel_sweep(args):
+    """Per-kernel timings at the sweep sizes (8192 rows): one JSON line per case on stdout.
+    --op picks one family; --case N picks one case of it (for a profiler capture of one kernel).
+    Inputs are larger than L2 only for the big cases; --flush-l2 writes a 256 MB buffer between
+    launches so that every launch starts with a cold L2."""
+    import torch
+    import __graft_entry__ as ge
+
+    pkg = ge.load_package()
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    ctx = pkg.Context(0, stream)
+    peaks = _peaks()
+    M, Bb, Tt = 8192, 8, 1024
+    g = torch.Generator(device="cuda").manual_seed(1)
+
+    def randn(*shape, std=1.0):
+        return torch.empty(shape, device="cuda").normal_(0.0, std, generator=g)
+
+    cases = []
+    if args.op in ("matmul", "all"):
+        for (K, N, act, res, bias) in ((768, 2304, 0, False, True), (768, 768, 0, False, True), (768, 3072, 1, False, True),
+                                       (3072, 768, 0, True, True), (768, 50304, 0, False, False),
+                                       (1600, 4800, 0, False, True), (1600, 6400, 1, False, True), (6400, 1600, 0, True, True)):
+            for mode in ((0, 1) if args.modes == "both" else (0,)):
+                cases.append(("matmul", dict(K=K, N=N, act=act, res=res, bias=bias, mode=mode)))
+    if args.op in ("attention", "all"):
+        cases += [("attention", dict(NH=12)), ("attention", dict(NH=25))]
+    if args.op in ("layernorm", "all"):
+        cases += [("layernorm", dict(C=768)), ("layernorm", dict(C=1600))]
+    if args.op in ("fused_residual_layernorm", "all"):
+        cases += [("fused_residual_layernorm", dict(C=768)), ("fused_residual_layernorm", dict(C=1600))]
+    if args.op in ("rowwise", "all"):
+        cases += [("residual", dict(C=768)), ("gelu", dict(C=3072)), ("encoder", dict(C=768))]
+    if args.case is not None:
+        cases = [cases[args.case]]
+    flush = torch.empty(64 * 1024 * 1024, device="cuda") if args.flush_l2 else None
+    for op, c in cases:
+        if op == "matmul":
+            K, N = c["K"], c["N"]
+            x, w = randn(Bb, Tt, K), randn(N, K, std=0.02)
+            bias = randn(N, std=0.01) if c["bias"] else None
+            res = randn(Bb, Tt, N) if c["res"] else None
+            out = torch.empty(Bb, Tt, N, device="cuda")
+            fn = lambda: ctx.matmul_forward(out, x, w, bias, Bb, Tt, K, N, act=c["act"], residual=res, mode=c["mode"])
+            work, unit, peak = 2.0 * M * K * N / 1e12, "TFLOP/s", peaks["bf16_burst"] / 2
+            name = f"matmul {K}->{N}" + ("+gelu" if c["act"] else "") + ("+residual" if c["res"] else "") + (" 3xTF32" if c["mode"] else "")
+        elif op == "attention":
+            NH = c["NH"]
+            Cc = NH * 64
+            qkv, out = randn(Bb, Tt, 3 * Cc), torch.empty(Bb, Tt, Cc, device="cuda")
+            lse = torch.empty(Bb, NH, Tt, device="cuda")
+            fn = lambda: ctx.attention_forward(out, None, lse, qkv, Bb, Tt, Cc, NH)
+            work, unit, peak = 4.0 * 64 * Tt * (Tt + 1) / 2 * NH * Bb / 1e12, "TFLOP/s", peaks["bf16_burst"] / 2
+            name = f"attention B=8 T=1024 NH={NH} (causal-exact flop)"
+        elif op in ("layernorm", "fused_residual_layernorm"):
+            Cc = c["C"]
+            x, x2, w, b = randn(Bb, Tt, Cc), randn(Bb, Tt, Cc), randn(Cc), randn(Cc)
+            out, res_out = torch.empty_like(x), torch.empty_like(x)
+            mean, rstd = torch.empty(Bb, Tt, device="cuda"), torch.empty(Bb, Tt, device="cuda")
+            if op == "layernorm":
+                fn = lambda: ctx.layernorm_forward(out, mean, rstd, x, w, b, Bb, Tt, Cc)
+                work = (2.0 * M * Cc + 2 * M + 2 * Cc) * 4 / 1e9
+            else:
+                fn = lambda: ctx.fused_residual_layernorm_forward(res_out, out, mean, rstd, x, x2, w, b, Bb, Tt, Cc)
+                work = (4.0 * M * Cc + 2 * M + 2 * Cc) * 4 / 1e9
+            unit, peak, name = "GB/s", peaks["hbm_gbs"], f"{op} [8192,{Cc}]"
+        else:
+            Cc = c["C"]
+            x, x2, out = randn(Bb, Tt, Cc), randn(Bb, Tt, Cc), torch.empty(Bb, Tt, Cc, device="cuda")
+            if op == "residual":
+                fn = lambda: ctx.residual_forward(out, x, x2, M * Cc)
+                work = 3.0 * M * Cc * 4 / 1e9
+            elif op == "gelu":
+                fn = lambda: ctx.gelu_forward(out, x, M * Cc)
+                work = 2.0 * M * Cc * 4 / 1e9
+            else:
+                tok = torch.randint(0, 50257, (Bb, Tt), dtype=torch.int32, device="cuda", generator=g)
+                wte, wpe = randn(50304, Cc, std=0.02), randn(Tt, Cc, std=0.02)
+                fn = lambda: ctx.encoder_forward(out, tok, wte, wpe, Bb, Tt, Cc)
+                work = ((2.0 * M * Cc + Tt * Cc) * 4 + M * 4) / 1e9
+            unit, peak, name = "GB/s", peaks["hbm_gbs"], f"{op} [8192,{Cc}]"
+        torch.cuda.synchronize()
+        for _ in range(args.warmup):
+            fn()
+        ctx.sync_check()
+        times = []
+        for _ in range(args.steps):
+            if flush is not None:
+                with torch.cuda.stream(stream):
+                    flush.zero_()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            fn()
+            e1.record(stream)
+            e1.synchronize()
+            times.append(e0.elapsed_time(e1))
+        ctx.sync_check()
+        med, best = statistics.median(times), min(times)
+        scale = 1e3  # work is in T(FLOP) or G(B); time in ms
+        print(json.dumps({"kernel": name, "median_ms": round(med, 5), "min_ms": round(best, 5), "cold_l2": bool(args.flush_l2),
+                          "achieved": round(work / (med / scale), 1), "unit": unit, "peak": peak,
+                          "frac": round(work / (med / scale) / peak, 4), "peak_source": peaks["source"]}), flush=True)
+    ctx.close()
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--op", default=None,
+                    choices=["all", "matmul", "attention", "layernorm", "fused_residual_layernorm", "rowwise"],
+                    help="per-kernel sweep at 8192 rows instead of the forward benchmark")
+    ap.add_argument("--case", type=int, default=None, help="with --op: run only this case of the family")
+    ap.add_argument("--modes", default="tf32", choices=["tf32", "both"], help="with --op matmul: also time 3xTF32")
+    ap.add_argument("--flush-l2", action="store_true", help="with --op: cold L2 before every launch")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.op:
+        return run_kernel_sweep(args)
     return run_ours(args)
 
 

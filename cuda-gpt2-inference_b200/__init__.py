@@ -278,7 +278,7 @@ class GPT2:
     def load_params(self, host_params):
         self.ctx.check(lib().b200_gpt2_load_params_host(self._h, _ptr(host_params), host_params.size), "load_params")
 
-    def set_options(self, round_operands=0, gemm_mode=B200_TF32, lmhead_mode=B200_TF32, use_graph=0):
+    def set_options(self, round_operands=1, gemm_mode=B200_TF32, lmhead_mode=B200_TF32, use_graph=0):
         self.ctx.check(lib().b200_gpt2_set_options(self._h, int(round_operands), gemm_mode, lmhead_mode, int(use_graph)),
                        "set_options")
 

@@ -26,7 +26,7 @@ struct b200_gpt2 {
           *branch = nullptr, *fch = nullptr, *logits = nullptr;
     int* tokens = nullptr;
     int* argmax = nullptr;
-    int round_operands = 0, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
+    int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
     std::map<std::pair<int, int>, cudaGraphExec_t> graphs;
     // per-operator timing (b200_gpt2_set_profile): one event pair per kernel launch
     bool profile = false;

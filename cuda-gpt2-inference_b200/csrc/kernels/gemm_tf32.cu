@@ -15,15 +15,17 @@
 //   warp 1      allocates tensor memory; one elected lane issues the UMMAs (K = 8 each) of a
 //               stage and commits the stage's empty barrier; commits tmem_full after the last
 //               K block
-//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, bias/GELU/residual,
-//               float4 stores.  Two accumulators (2 x BN columns) let the epilogue of tile i
-//               overlap the main loop of tile i+1.
+//   warps 2-5   epilogue: tcgen05.ld 32 lanes x 32 columns at a time, transposed through a
+//               swizzled shared-memory buffer, bias/GELU/residual, row-contiguous float4
+//               stores.  Two accumulators (2 x BN columns) let the epilogue of tile i overlap
+//               the main loop of tile i+1.
 //   warps 6-9   (3xTF32 only) split warps: the tensor core reads only the upper 19 bits of an
 //               fp32 operand (it truncates), so for every staged tile they write the dropped
 //               part  x_small = x - trunc_tf32(x)  into a second buffer, and the issuer
 //               accumulates  A.B + A_small.B + A.B_small : fp32-level products on the TF32 pipe.
 // Every wait is time-bounded; a wait that runs out makes all roles leave, the CTA frees its
 // tensor memory and records a code in the context's status word.
+#include <cstdlib>
 #include "kernels.h"
 #include "../prim/sm100.cuh"
 
@@ -43,9 +45,12 @@ struct GemmCfg {
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (X3 ? 2 : 1);
     static constexpr int TX_BYTES = A_BYTES + B_BYTES;  // what TMA delivers per stage
     static constexpr int BAR_BYTES = 512;
-    static constexpr int STAGES_RAW = (kMaxSmem - 1024 - BAR_BYTES) / STAGE_BYTES;
+    // epilogue staging: per epilogue warp two {32 rows x 32 fp32} buffers (transposes the
+    // row-per-thread tensor-memory layout into row-contiguous, coalesced global stores)
+    static constexpr int EPI_BYTES = 4 * 2 * 4096;
+    static constexpr int STAGES_RAW = (kMaxSmem - 1024 - BAR_BYTES - EPI_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
-    static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + BAR_BYTES;
+    static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
     static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
     // one CTA per SM is guaranteed by shared memory (> half of the SM's), so a 512-column
     // allocation can never wait on a co-resident CTA
@@ -82,7 +87,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     uint8_t* smem_b = smem_a + STAGES * Cfg::A_BYTES;              // [STAGES][B_BYTES]
     uint8_t* smem_as = smem_b + STAGES * Cfg::B_BYTES;             // X3: dropped parts of A
     uint8_t* smem_bs = smem_as + (X3 ? STAGES * Cfg::A_BYTES : 0); // X3: dropped parts of B
-    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + STAGES * Cfg::STAGE_BYTES);
+    uint8_t* smem_epi = smem + STAGES * Cfg::STAGE_BYTES;          // [4 warps][2][32 x 128 B]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + Cfg::EPI_BYTES);
     uint64_t* full_bar = bars;                     // [STAGES] TMA landed
     uint64_t* empty_bar = bars + STAGES;           // [STAGES] UMMAs of the stage retired
     uint64_t* split_bar = bars + 2 * STAGES;       // [STAGES] X3: dropped parts written
@@ -202,37 +208,48 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t acc_ph = (tile_iter >> 1) & 1;
             if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            const int row = m_blk * BM + q * 32 + lane;
-            const bool row_ok = row < args.M;
-            float* out_row = args.out + (size_t)row * args.N;
-            const float* res_row = args.residual ? args.residual + (size_t)row * args.N : nullptr;
+            // Thread `lane` holds row (q*32 + lane) of the tile, 32 columns at a time.  Writing
+            // that straight to global memory would scatter 16-byte pieces over 32 rows per
+            // instruction, so the chunk goes through a swizzled shared-memory buffer and comes
+            // back with 8 lanes covering 128 contiguous bytes of one row.
+            const int row0 = m_blk * BM + q * 32;
+            const int sub_row = lane >> 3;  // 0..3: row within a group of four
+            const int sub_chk = lane & 7;   // 16-byte chunk within the 128-byte row piece
 #pragma unroll 1
             for (int c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, r);
                 tmem_ld_wait();
-                const int col0 = n_blk * BN + c * 32;
-                if (row_ok && col0 < args.N) {
+                uint8_t* stage = smem_epi + (q * 2 + (c & 1)) * 4096;
 #pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int col = col0 + 4 * j;
-                        if (col < args.N) {
-                            float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
-                                                   __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                            if (args.bias) {
-                                const float4 b = __ldg(reinterpret_cast<const float4*>(args.bias + col));
-                                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
-                            }
+                for (int j = 0; j < 8; ++j) {
+                    *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                        make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+                }
+                __syncwarp();
+                const int col = n_blk * BN + c * 32 + sub_chk * 4;
+                if (col < args.N) {
+                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (args.bias) b4 = __ldg(reinterpret_cast<const float4*>(args.bias + col));
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int rl = i * 4 + sub_row;
+                        const int row = row0 + rl;
+                        float4 v = *reinterpret_cast<const float4*>(stage + rl * 128 + ((sub_chk ^ (rl & 7)) << 4));
+                        if (row < args.M) {
+                            v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
                             if (do_gelu) { v.x = gelu_tanh(v.x); v.y = gelu_tanh(v.y); v.z = gelu_tanh(v.z); v.w = gelu_tanh(v.w); }
-                            if (res_row) {
-                                const float4 rr = *reinterpret_cast<const float4*>(res_row + col);
+                            if (args.residual) {
+                                const float4 rr = *reinterpret_cast<const float4*>(args.residual + (size_t)row * args.N + col);
                                 v.x += rr.x; v.y += rr.y; v.z += rr.z; v.w += rr.w;
                             }
                             if (do_round) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
-                            *reinterpret_cast<float4*>(out_row + col) = v;
+                            *reinterpret_cast<float4*>(args.out + (size_t)row * args.N + col) = v;
                         }
                     }
                 }
+                // the buffer used two chunks ago is free again once every lane is past this point
+                __syncwarp();
             }
             tc_fence_before_sync();
             mbar_arrive(&tmem_empty_bar[acc]);
@@ -280,10 +297,13 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     }
 }
 
-// estimated cycles of one 8-deep K step of a 128 x BN tile: tensor pipe vs shared-memory feed
-inline int tile_step_cost(int bn) {
-    const int tensor = bn / 2, feed = 32 + bn / 4;
-    return tensor > feed ? tensor : feed;
+// Estimated cycles of one 128 x BN output tile.  Per 32-deep K block the tensor pipe needs
+// 2*BN cycles, but the SM can only pull about 52 bytes per cycle from L2 (measured: the five
+// tile widths all saturate near 15 TB/s of L2->SM traffic), so a block costs
+// max(2*BN, (128+BN)*128/52); plus the part of the epilogue that is not hidden.
+inline long tile_cost(int bn, int num_kb) {
+    const long tensor = 2L * bn, feed = (128L + bn) * 128 / 52;
+    return num_kb * (tensor > feed ? tensor : feed) + 1500;
 }
 
 template <int BN, bool X3>
@@ -318,9 +338,12 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
             const int bn = cands[i];
             const long tiles = (long)num_m * ((N + bn - 1) / bn);
             const long waves = (tiles + ctx->num_sms - 1) / ctx->num_sms;
-            const long cost = waves * tile_step_cost(bn);
+            const long cost = waves * tile_cost(bn, (K + BK - 1) / BK);
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
         }
+        // tuning hook: B200_GEMM_BN=<64|96|128|192|256> forces the N tile
+        static const int forced_bn = [] { const char* e = getenv("B200_GEMM_BN"); return e ? atoi(e) : 0; }();
+        if (forced_bn == 64 || forced_bn == 96 || forced_bn == 128 || forced_bn == 192 || forced_bn == 256) best_bn = forced_bn;
     }
     GemmArgs a;
     a.out = out; a.bias = bias; a.residual = residual;

@@ -167,11 +167,16 @@ int b200_gpt2_destroy(b200_gpt2* model);
 /* Device pointer of the flat parameter array (fill it in place), or copy from the host. */
 float* b200_gpt2_params(b200_gpt2* model);
 int b200_gpt2_load_params_host(b200_gpt2* model, const float* host_params, size_t count);
-/* Options: round_operands != 0 makes every producer whose output feeds only a GEMM store
- * TF32-round-to-nearest values and rounds the weight matrices once (in place), removing the
- * truncation bias of raw fp32 operands.  gemm_mode applies to all GEMMs; lmhead_mode to the
- * lm-head alone.  use_graph != 0 replays the forward from a CUDA graph after the first call
- * of a given (B,T). */
+/* Options (defaults: round_operands 1, both modes B200_TF32, use_graph 0).
+ * round_operands != 0 makes every producer whose output feeds only a GEMM store
+ * TF32-round-to-nearest values and, on the next forward, rounds the four linear weight
+ * matrices once IN PLACE (the lm-head uses a rounded copy of wte; wte itself is untouched so
+ * the encoder stays bit-exact).  The tensor core truncates raw fp32 operands, which shrinks
+ * every product; rounding to nearest first removes that bias (logit error 4.6e-4 rms instead
+ * of 7.9e-4 on GPT-2 124M).  gemm_mode applies to all GEMMs; lmhead_mode to the lm-head alone;
+ * B200_TF32X3 ignores operand rounding except for q, k and v, which the attention kernel
+ * multiplies in one TF32 pass.  use_graph != 0 replays the forward from a CUDA graph after the
+ * first call of a given (B,T). */
 int b200_gpt2_set_options(b200_gpt2* model, int round_operands, int gemm_mode, int lmhead_mode,
                           int use_graph);
 /* tokens: device int32 [B,T].  Asynchronous.  Logits: device [B,T,Vp], owned by the model. */

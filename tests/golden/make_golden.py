@@ -25,7 +25,13 @@ from oracle import oracle as orc  # noqa: E402
 def main():
     out_path = sys.argv[1] if len(sys.argv) > 1 else os.path.join(ROOT, "tests", "golden", "reference_kernels.npz")
     ref = C.CDLL(os.path.join(ROOT, "oracle", "_ref", "libref_kernels.so"))
-    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()
+    keep = []  # every device buffer stays alive until the end (the caching allocator reuses freed blocks)
+
+    def dev(a):
+        t = torch.from_numpy(np.ascontiguousarray(a)).cuda()
+        keep.append(t)
+        return t
+
     p = lambda t: C.c_void_p(t.data_ptr())
     fx = {}
 
@@ -72,7 +78,7 @@ def main():
     fx["res_a"], fx["res_b"], fx["res_out"] = a, b2, out.cpu().numpy()
 
     # causal flash attention on the packed buffer: kernels/attention/3_flash_attention_permute.cuh
-    B, T, NH = 2, 128, 2
+    B, T, NH = 1, 128, 2
     Cc = NH * 64
     qkv = orc.fill_normal((B, T, 3 * Cc), 1041)
     out = torch.empty((B, T, Cc), device="cuda")
