@@ -20,6 +20,7 @@ SOURCES = [
     "api/api.cu",
     "kernels/rowwise.cu",
     "kernels/gemm_tf32.cu",
+    "kernels/gemm_tf32_pair.cu",
     "kernels/attention.cu",
     "driver/gpt2.cu",
 ]
@@ -52,7 +53,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         obj = os.path.join(obj_dir, src.replace("/", "_") + ".o")
         objs.append(obj)
-        cmd = ["nvcc", *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
+        # B200_NVCC_EXTRA: extra nvcc flags for experiments (e.g. -DB200_GEMM_TIMING)
+        cmd = ["nvcc", *NVCC_FLAGS, *os.environ.get("B200_NVCC_EXTRA", "").split(), "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

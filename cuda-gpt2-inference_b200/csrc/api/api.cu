@@ -115,6 +115,9 @@ int b200_ctx_sync_check(b200_ctx* ctx) {
     return B200_OK;
 }
 
+// debugging aid for kernel experiments: device address of the status words
+void* b200_ctx_debug_status(b200_ctx* ctx) { return ctx ? ctx->d_status : nullptr; }
+
 uint64_t b200_ctx_launch_count(const b200_ctx* ctx) { return ctx ? ctx->launches : 0; }
 void b200_ctx_reset_launch_count(b200_ctx* ctx) { if (ctx) ctx->launches = 0; }
 const char* b200_ctx_last_error(const b200_ctx* ctx) { return ctx ? ctx->last_error.c_str() : ""; }

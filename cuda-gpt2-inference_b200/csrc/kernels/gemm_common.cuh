@@ -1,0 +1,83 @@
+// Pieces shared by the single-CTA and the CTA-pair TF32 GEMM kernels: the argument block and
+// the epilogue that drains one 128 x BN accumulator out of tensor memory.
+#pragma once
+#include "kernels.h"
+#include "../prim/sm100.cuh"
+
+namespace b200 {
+
+constexpr int kGemmBM = 128;       // accumulator rows per CTA (tensor-memory lanes)
+constexpr int kGemmBK = 32;        // fp32 elements per K block = 128 bytes = one swizzle row
+constexpr int kGemmMaxSmem = 232448;  // 227 KB
+constexpr int kGemmEpiBytes = 4 * 2 * 4096;  // per epilogue warp two {32 rows x 128 B} buffers
+
+struct GemmArgs {
+    float* out;
+    const float* bias;
+    const float* residual;
+    int M, N, K;
+    int num_m_blocks, num_n_blocks;  // tiles along M (of 128, or 256 for CTA pairs) and N
+    int n_fastest;
+    int flags;
+    int* status;
+};
+
+// One epilogue warp drains its 32 lanes x BN columns.  Thread `lane` holds row (q*32 + lane) of
+// the accumulator, 32 columns at a time.  Writing that straight to global memory would scatter
+// 16-byte pieces over 32 rows per instruction, so each chunk goes through a swizzled
+// shared-memory buffer and comes back with 8 lanes covering 128 contiguous bytes of one row;
+// bias, tanh-GELU, residual add and TF32 rounding are applied on the way out.
+//   tmem_acc : tensor-memory address of the accumulator (column offset included, lane 0)
+//   row0     : global row of accumulator lane q*32
+//   col0     : global column of accumulator column 0
+//   stage2   : this warp's two 4 KB staging buffers
+template <int BN>
+__device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, uint32_t tmem_acc, int q, int lane,
+                                                       int row0, int col0, uint8_t* stage2) {
+    const bool do_gelu = (args.flags & GEMM_GELU) != 0;
+    const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
+    const int sub_row = lane >> 3;  // 0..3: row within a group of four
+    const int sub_chk = lane & 7;   // 16-byte chunk within the 128-byte row piece
+#pragma unroll 1
+    for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r);
+        tmem_ld_wait();
+        uint8_t* stage = stage2 + (c & 1) * 4096;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
+                make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
+        }
+        __syncwarp();
+        const int col = col0 + c * 32 + sub_chk * 4;
+        if (col < args.N) {
+            float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (args.bias) b4 = __ldg(reinterpret_cast<const float4*>(args.bias + col));
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                const int rl = i * 4 + sub_row;
+                const int row = row0 + rl;
+                float4 v = *reinterpret_cast<const float4*>(stage + rl * 128 + ((sub_chk ^ (rl & 7)) << 4));
+                if (row < args.M) {
+                    v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                    if (do_gelu) { v.x = gelu_tanh(v.x); v.y = gelu_tanh(v.y); v.z = gelu_tanh(v.z); v.w = gelu_tanh(v.w); }
+                    if (args.residual) {
+                        const float4 rr = *reinterpret_cast<const float4*>(args.residual + (size_t)row * args.N + col);
+                        v.x += rr.x; v.y += rr.y; v.z += rr.z; v.w += rr.w;
+                    }
+                    if (do_round) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
+                    *reinterpret_cast<float4*>(args.out + (size_t)row * args.N + col) = v;
+                }
+            }
+        }
+        // the buffer used two chunks ago is free again once every lane is past this point
+        __syncwarp();
+    }
+}
+
+// CTA-pair GEMM (gemm_tf32_pair.cu): 256 x BN tiles computed by two CTAs sharing one UMMA.
+int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
+                          const float* bias, const float* residual, int M, int K, int N, int flags);
+
+}  // namespace b200

@@ -26,16 +26,15 @@
 // Every wait is time-bounded; a wait that runs out makes all roles leave, the CTA frees its
 // tensor memory and records a code in the context's status word.
 #include <cstdlib>
-#include "kernels.h"
-#include "../prim/sm100.cuh"
+#include "gemm_common.cuh"
 
 namespace b200 {
 
 namespace {
 
-constexpr int BM = 128;
-constexpr int BK = 32;  // fp32 elements per K block = 128 bytes = one swizzle row
-constexpr int kMaxSmem = 232448;  // 227 KB
+constexpr int BM = kGemmBM;
+constexpr int BK = kGemmBK;
+constexpr int kMaxSmem = kGemmMaxSmem;
 
 template <int BN, bool X3>
 struct GemmCfg {
@@ -45,9 +44,9 @@ struct GemmCfg {
     static constexpr int STAGE_BYTES = (A_BYTES + B_BYTES) * (X3 ? 2 : 1);
     static constexpr int TX_BYTES = A_BYTES + B_BYTES;  // what TMA delivers per stage
     static constexpr int BAR_BYTES = 512;
-    // epilogue staging: per epilogue warp two {32 rows x 32 fp32} buffers (transposes the
-    // row-per-thread tensor-memory layout into row-contiguous, coalesced global stores)
-    static constexpr int EPI_BYTES = 4 * 2 * 4096;
+    // epilogue staging (transposes the row-per-thread tensor-memory layout into row-contiguous,
+    // coalesced global stores)
+    static constexpr int EPI_BYTES = kGemmEpiBytes;
     static constexpr int STAGES_RAW = (kMaxSmem - 1024 - BAR_BYTES - EPI_BYTES) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + EPI_BYTES + BAR_BYTES;
@@ -58,17 +57,6 @@ struct GemmCfg {
     static_assert(SMEM <= kMaxSmem, "shared memory over the 227 KB limit");
     static_assert(BN % 32 == 0 && BN >= 32 && BN <= 256, "BN: multiple of 32 up to 256");
     static_assert(STAGES >= 2, "need at least a double buffer");
-};
-
-struct GemmArgs {
-    float* out;
-    const float* bias;
-    const float* residual;
-    int M, N, K;
-    int num_m_blocks, num_n_blocks;
-    int n_fastest;
-    int flags;
-    int* status;
 };
 
 __device__ __forceinline__ float tf32_dropped_part(float x) {
@@ -197,8 +185,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp < 6) {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;  // the lane quarter this warp may read
-        const bool do_gelu = (args.flags & GEMM_GELU) != 0;
-        const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
         bool ok = true;
         int tile_iter = 0;
         for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tile_iter) {
@@ -208,49 +194,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t acc_ph = (tile_iter >> 1) & 1;
             if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            // Thread `lane` holds row (q*32 + lane) of the tile, 32 columns at a time.  Writing
-            // that straight to global memory would scatter 16-byte pieces over 32 rows per
-            // instruction, so the chunk goes through a swizzled shared-memory buffer and comes
-            // back with 8 lanes covering 128 contiguous bytes of one row.
-            const int row0 = m_blk * BM + q * 32;
-            const int sub_row = lane >> 3;  // 0..3: row within a group of four
-            const int sub_chk = lane & 7;   // 16-byte chunk within the 128-byte row piece
-#pragma unroll 1
-            for (int c = 0; c < BN / 32; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32b_x32(tmem_base + (uint32_t(q * 32) << 16) + acc * BN + c * 32, r);
-                tmem_ld_wait();
-                uint8_t* stage = smem_epi + (q * 2 + (c & 1)) * 4096;
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =
-                        make_uint4(r[4 * j], r[4 * j + 1], r[4 * j + 2], r[4 * j + 3]);
-                }
-                __syncwarp();
-                const int col = n_blk * BN + c * 32 + sub_chk * 4;
-                if (col < args.N) {
-                    float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-                    if (args.bias) b4 = __ldg(reinterpret_cast<const float4*>(args.bias + col));
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        const int rl = i * 4 + sub_row;
-                        const int row = row0 + rl;
-                        float4 v = *reinterpret_cast<const float4*>(stage + rl * 128 + ((sub_chk ^ (rl & 7)) << 4));
-                        if (row < args.M) {
-                            v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
-                            if (do_gelu) { v.x = gelu_tanh(v.x); v.y = gelu_tanh(v.y); v.z = gelu_tanh(v.z); v.w = gelu_tanh(v.w); }
-                            if (args.residual) {
-                                const float4 rr = *reinterpret_cast<const float4*>(args.residual + (size_t)row * args.N + col);
-                                v.x += rr.x; v.y += rr.y; v.z += rr.z; v.w += rr.w;
-                            }
-                            if (do_round) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
-                            *reinterpret_cast<float4*>(args.out + (size_t)row * args.N + col) = v;
-                        }
-                    }
-                }
-                // the buffer used two chunks ago is free again once every lane is past this point
-                __syncwarp();
-            }
+            gemm_drain_accumulator<BN>(args, tmem_base + acc * BN, q, lane, m_blk * BM + q * 32, n_blk * BN,
+                                       smem_epi + q * 2 * 4096);
             tc_fence_before_sync();
             mbar_arrive(&tmem_empty_bar[acc]);
         }
@@ -328,6 +273,12 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      int mode) {
     const bool x3 = (mode == B200_TF32X3);
+    // CTA pairs pull a third less operand traffic out of L2 per flop and win where there are many
+    // tiles per SM (wide outputs: lm-head, GPT-2 XL shapes); with a few tiles per SM the
+    // single-CTA kernel's finer N tiles quantise better.  B200_GEMM_PAIR=0/1 forces the choice.
+    static const int pair_env = [] { const char* e = getenv("B200_GEMM_PAIR"); return e ? (e[0] == '0' ? 0 : 1) : -1; }();
+    const bool use_pair = pair_env >= 0 ? pair_env == 1 : (N >= 4096 && M >= 2048);
+    if (!x3 && use_pair) return launch_gemm_tf32_pair(ctx, out, inp, weight, bias, residual, M, K, N, flags);
     const int num_m = (M + BM - 1) / BM;
     // pick the N tile that minimises waves x per-tile cost on this GPU's SM count
     int best_bn = 128;
