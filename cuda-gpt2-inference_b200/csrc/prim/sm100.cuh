@@ -69,24 +69,38 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "memory");
     return ok != 0;
 }
+// The same with a suspend-time hint: the thread may sleep in hardware until the phase completes
+// or about `hint_ns` have passed, instead of coming back at once and spinning.  A spinning
+// warp takes issue slots from the warps that share its scheduler.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t"
+        "}\n"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+        : "memory");
+    return ok != 0;
+}
 
 // Wait limit for every device-side wait.  A wait that runs out sets *abort_flag (shared
 // memory, visible to all roles of the CTA) and returns false; all roles then leave their
 // loops, the CTA frees its tensor memory and returns, and the host reads the status word.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr uint32_t kWaitSliceNs = 10000;          // one hardware-suspended poll
 
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
     while (true) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((++spins & 0xff) == 0) {
-            if (*abort_flag != 0) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                return false;
-            }
+        if (mbar_try_wait_hint(bar, parity, kWaitSliceNs)) return true;
+        if (*abort_flag != 0) return false;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            return false;
         }
     }
 }
@@ -149,6 +163,36 @@ __device__ __forceinline__ void umma_tf32_ss(uint32_t d_tmem, uint64_t a_desc, u
         : "memory");
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand (128 lanes x K columns of fp32, K-major by
+// construction) is read from tensor memory instead of shared memory
+__device__ __forceinline__ void umma_tf32_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t"
+        ".reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::tf32 [%0], [%1], %2, %3, p;\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// store 32 lanes x 32 columns of 32-bit: thread i writes lane (base_lane+i), columns [col, col+32)
+__device__ __forceinline__ void tmem_st_32x32b_x32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+          "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+          "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+          "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+        : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // 32 lanes x 32 columns of 32-bit: thread i of the warp receives lane (base_lane+i),
 // columns [col, col+32).  The warp may only touch lanes 32*(warp_id%4) .. +31.
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -200,10 +244,11 @@ __host__ __device__ constexpr uint32_t make_idesc_tf32(int M, int N, int b_mn_ma
            (static_cast<uint32_t>(N >> 3) << 17) | (static_cast<uint32_t>(M >> 4) << 24);
 }
 
+// Round an fp32 value to TF32 (10 explicit mantissa bits), nearest with ties away from zero -
+// the result of cvt.rna.tf32.f32 for finite inputs - with two integer instructions (the
+// conversion instruction issues at a quarter of their rate).
 __device__ __forceinline__ float round_tf32(float x) {
-    uint32_t r;
-    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
-    return __uint_as_float(r);
+    return __uint_as_float((__float_as_uint(x) + 0x1000u) & 0xFFFFE000u);
 }
 
 // ------------------------------------------------- CTA pairs (cta_group::2)
@@ -293,16 +338,14 @@ __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t pa
 __device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
     if (mbar_try_wait_cluster(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
-    uint32_t spins = 0;
     while (true) {
         if (mbar_try_wait_cluster(bar, parity)) return true;
-        if ((++spins & 0xff) == 0) {
-            if (*abort_flag != 0) return false;
-            if (globaltimer_ns() - t0 > kWaitLimitNs) {
-                *abort_flag = 1;
-                return false;
-            }
+        if (*abort_flag != 0) return false;
+        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+            *abort_flag = 1;
+            return false;
         }
+        __nanosleep(64);
     }
 }
 

@@ -103,10 +103,14 @@ def test_batch_rows_are_independent_and_deterministic(pkg, orc, ctx):
     tokens = orc.fill_tokens((B, T), seed=99, vocab=cfg.vocab_size)
     d_tok = torch.from_numpy(tokens).cuda()
     torch.cuda.synchronize()
-    full = model.forward(d_tok, B, T).clone()
+    # the forward runs on the context's stream: synchronise before torch touches the logits
+    out = model.forward(d_tok, B, T)
     ctx.sync_check()
-    again = model.forward(d_tok, B, T).clone()
+    full = out.clone()
+    out = model.forward(d_tok, B, T)
     ctx.sync_check()
+    again = out.clone()
+    torch.cuda.synchronize()
     assert torch.equal(full, again)
     for start, stop in (pkg.shard_batch(B, 2, r) for r in range(2)):
         part = model.forward(d_tok[start:stop].contiguous(), stop - start, T)
@@ -122,8 +126,10 @@ def test_graph_replay_matches_eager(pkg, orc, ctx):
     tokens = orc.fill_tokens((B, T), seed=7, vocab=cfg.vocab_size)
     d_tok = torch.from_numpy(tokens).cuda()
     torch.cuda.synchronize()
-    eager = model.forward(d_tok, B, T).clone()
+    out = model.forward(d_tok, B, T)
     ctx.sync_check()
+    eager = out.clone()
+    torch.cuda.synchronize()
     model.set_options(use_graph=1)
     n0 = ctx.launches
     for _ in range(3):

@@ -120,6 +120,8 @@ GEMM_SHAPES = [
     (1, 64, 1600, 6400, True, 1, False),     # XL fc, M < 128
     (1, 64, 100, 36, True, 0, False),        # K not a multiple of 32, tiny N
     (8, 128, 768, 768, True, 0, False),      # several M tiles
+    (2, 1024, 128, 4608, True, 1, False),    # wide output: CTA-pair kernel (M = 2048, 18 N tiles of 256)
+    (17, 128, 96, 4672, True, 0, True),      # CTA-pair kernel, odd number of 128-row tiles, ragged N tile
 ]
 
 
