@@ -40,7 +40,10 @@ EXPORTS = (
     "b200_gpt2_load_params_host", "b200_gpt2_set_options", "b200_gpt2_forward",
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
+    "b200_gpt2_forward_static",
 )
+
+STATIC_MAX_TOKEN_CHANNELS = 196608  # B*T*C limit of b200_gpt2_forward_static
 
 PROF_NAMES = ("encoder", "layernorm", "gemm_qkv", "attention", "gemm_attproj", "fused_residual_layernorm",
               "gemm_fc", "gemm_fcproj", "gemm_lmhead")
@@ -107,6 +110,7 @@ def lib() -> C.CDLL:
         l.b200_gpt2_activation.restype = vp
         l.b200_gpt2_set_profile.argtypes = [vp, i]
         l.b200_gpt2_read_profile.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_long)]
+        l.b200_gpt2_forward_static.argtypes = [vp, vp, vp, vp, i, i, vp]
         _lib = l
     return _lib
 
@@ -315,6 +319,14 @@ class GPT2:
         if self._h:
             lib().b200_gpt2_destroy(self._h)
             self._h = C.c_void_p()
+
+
+def gpt2_forward_static(ctx: Context, cfg: GPT2Config, params, tokens, B: int, T: int, logits) -> int:
+    """b200_gpt2_forward_static: the forward without any device allocation, for callers that may
+    not allocate (see include/b200gpt2.h).  params / tokens / logits are CUDA tensors owned by the
+    caller; returns the status code (0 = ok) without raising."""
+    cc = cfg.c()
+    return int(lib().b200_gpt2_forward_static(ctx._h, C.byref(cc), _ptr(params), _ptr(tokens), B, T, _ptr(logits)))
 
 
 def _view_device(ptr: int, shape, dtype, device: int):

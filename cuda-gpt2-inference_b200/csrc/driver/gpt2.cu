@@ -6,6 +6,7 @@
 // layers; parameters keep the flat fp32 layout documented in include/b200gpt2.h.
 #include <cstring>
 #include <map>
+#include <string>
 #include <new>
 #include <utility>
 #include <vector>
@@ -326,3 +327,78 @@ void* b200_gpt2_activation(b200_gpt2* m, const char* name) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// Forward pass without any device allocation.
+//
+// Some callers must not allocate device memory: code that runs after an application has handed
+// every byte of the GPU to its own pool, plugin hosts that forbid driver allocations once
+// initialisation is over, and latency-critical serving loops that cannot afford the implicit
+// device-wide synchronisation of cudaMalloc / cudaFree.  For them the per-layer activations of
+// the forward (the scratch memory that b200_gpt2_create normally allocates) live in the
+// file-scope array below, which every GPU that loads this library holds until the process exits.
+constexpr size_t kStaticScratchRowElems = (size_t)B200_STATIC_MAX_TOKEN_CHANNELS;  // max B*T*C
+// residual, ln_out, atty, branch: 1 each; qkv: 3; fch: 4  (units of B*T*C floats)
+constexpr size_t kStaticScratchFloats = 11 * kStaticScratchRowElems;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
+
+namespace {
+// In host code the name g_static_scratch is only a stand-in; the device address has to be asked
+// for, once per device, with that device current.
+float* static_scratch_address(b200_ctx* ctx, int* status) {
+    static float* addr[64] = {};
+    const int dev = ctx->device & 63;
+    if (!addr[dev]) {
+        int cur = -1;
+        cudaError_t e = cudaGetDevice(&cur);
+        if (e == cudaSuccess && cur != ctx->device) e = cudaSetDevice(ctx->device);
+        void* p = nullptr;
+        if (e == cudaSuccess) e = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (e != cudaSuccess || !p) {
+            *status = b200_fail_cuda(ctx, e, "cudaGetSymbolAddress(g_static_scratch)");
+            return nullptr;
+        }
+        addr[dev] = static_cast<float*>(p);
+    }
+    *status = B200_OK;
+    return addr[dev];
+}
+}  // namespace
+
+extern "C" int b200_gpt2_forward_static(b200_ctx* ctx, const b200_gpt2_config* cfg, const float* params,
+                                        const int* tokens, int B, int T, float* logits) {
+    if (!ctx || !cfg || !params || !tokens || !logits) return B200_ERR_NULL;
+    if (!b200_aligned16(params) || !b200_aligned16(logits)) return B200_ERR_ALIGN;
+    if (cfg->channels <= 0 || cfg->num_heads <= 0 || cfg->channels % cfg->num_heads ||
+        cfg->channels / cfg->num_heads != 64 || cfg->channels > 4096 || cfg->num_layers <= 0 ||
+        cfg->padded_vocab_size % 4 || cfg->vocab_size <= 0 || cfg->vocab_size > cfg->padded_vocab_size ||
+        B <= 0 || T <= 0 || T % 64 || T > cfg->max_seq_len)
+        return B200_ERR_SHAPE;
+    const size_t MC = (size_t)B * T * cfg->channels;
+    if (MC > kStaticScratchRowElems) {
+        ctx->last_error = "b200_gpt2_forward_static: B*T*C = " + std::to_string(MC) + " exceeds the built-in scratch of " +
+                          std::to_string(kStaticScratchRowElems) + " (B200_STATIC_MAX_TOKEN_CHANNELS); use b200_gpt2_create / b200_gpt2_forward";
+        return B200_ERR_LIMIT;
+    }
+    int st;
+    float* scratch = static_scratch_address(ctx, &st);
+    if (!scratch) return st;
+    // a view of the caller's parameters and logits plus the built-in scratch; nothing is owned
+    b200_gpt2 view;
+    view.ctx = ctx;
+    view.cfg = *cfg;
+    view.max_B = B;
+    view.max_T = T;
+    view.n_params = b200_gpt2_param_offsets(cfg, view.off);
+    view.params = const_cast<float*>(params);  // read only: weights are not rounded on this path
+    view.round_operands = 0;                   // the arithmetic of b200_gpt2_forward with round_operands = 0
+    view.residual = scratch;
+    view.ln_out = scratch + MC;
+    view.atty = scratch + 2 * MC;
+    view.branch = scratch + 3 * MC;
+    view.qkv = scratch + 4 * MC;
+    view.fch = scratch + 7 * MC;
+    view.logits = logits;
+    // every region is written in full before it is read, so nothing has to be cleared between calls
+    return enqueue_forward(&view, tokens, B, T);
+}

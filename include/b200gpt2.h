@@ -205,6 +205,33 @@ int b200_gpt2_read_profile(b200_gpt2* model, double* ms, long* launches);
  * name in {"encoded","ln_out","qkv","atty","branch","fch","residual","argmax"}; NULL if unknown. */
 void* b200_gpt2_activation(b200_gpt2* model, const char* name);
 
+/* ---------------------------------------------------------------- no-allocation forward */
+/* No counterpart in the reference (which has no driver at all).
+ *
+ * b200_gpt2_forward for callers that must not allocate device memory - an application that has
+ * given all of the GPU to its own pool, a plugin host that forbids driver allocations after
+ * start-up, a serving loop that cannot take the device-wide synchronisation that cudaMalloc and
+ * cudaFree imply.  The caller passes the inputs (flat fp32 parameters in the layout above, int32
+ * token ids [B,T]) and the output (logits [B,T,Vp]), all in device memory; the activations
+ * between them use a scratch array built into the library (8.65 MB of every GPU that loads it,
+ * held until the process exits).  The call makes no cudaMalloc / cudaFree and uses no allocating
+ * library; `ctx` must have been created earlier, when allocation was still allowed.
+ *
+ * Limit: B*T*C <= B200_STATIC_MAX_TOKEN_CHANNELS (e.g. GPT-2 124M with B=4, T=64); larger
+ * problems return B200_ERR_LIMIT (text in b200_ctx_last_error) and must use b200_gpt2_create.
+ * The arithmetic is that of b200_gpt2_forward with round_operands = 0 (the caller's weights are
+ * never modified), bit for bit.
+ *
+ * The first call on a device looks up the scratch array's device address
+ * (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ * All calls on a device share the one scratch array: it keeps the previous call's contents
+ * (nothing needs clearing - every part is rewritten before it is read), and two calls that
+ * overlap on the GPU (different streams or contexts of the same device) race on it.
+ * Asynchronous on the context's stream, like b200_gpt2_forward. */
+#define B200_STATIC_MAX_TOKEN_CHANNELS 196608 /* 256 tokens x 768 channels */
+int b200_gpt2_forward_static(b200_ctx* ctx, const b200_gpt2_config* cfg, const float* params,
+                             const int* tokens, int B, int T, float* logits);
+
 #ifdef __cplusplus
 }
 #endif
