@@ -30,7 +30,7 @@ EXPORTS = (
     "b200_ctx_create", "b200_ctx_destroy", "b200_ctx_set_stream", "b200_ctx_sync_check",
     "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
     "b200_ctx_last_error",
-    "b200_matmul_forward", "b200_attention_forward", "b200_layernorm_forward",
+    "b200_matmul_forward", "b200_attention_forward", "b200_attention_forward_x3", "b200_layernorm_forward",
     "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
     "b200_encoder_forward",
     "matmul_forward", "matmul_forward_gelu", "attention_forward", "layernorm_forward",
@@ -77,6 +77,7 @@ def lib() -> C.CDLL:
         l.b200_ctx_last_error.restype = C.c_char_p
         l.b200_matmul_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, i]
         l.b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
+        l.b200_attention_forward_x3.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_layernorm_forward.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i]
         l.b200_fused_residual_layernorm_forward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i]
         l.b200_residual_forward.argtypes = [vp, vp, vp, vp, sz]
@@ -178,6 +179,11 @@ class Context:
     def attention_forward(self, out, qkvr, att, inp, B, T, Cc, NH):
         self.check(lib().b200_attention_forward(self._h, _ptr(out), _ptr(qkvr), _ptr(att), _ptr(inp), B, T, Cc, NH),
                    "attention_forward")
+
+    def attention_forward_x3(self, out, qkvr, att, inp, B, T, Cc, NH):
+        """3xTF32 attention; qkvr ([B,T,3C] scratch) is required."""
+        self.check(lib().b200_attention_forward_x3(self._h, _ptr(out), _ptr(qkvr), _ptr(att), _ptr(inp), B, T, Cc, NH),
+                   "attention_forward_x3")
 
     def layernorm_forward(self, out, mean, rstd, inp, weight, bias, B, T, Cc):
         self.check(lib().b200_layernorm_forward(self._h, _ptr(out), _ptr(mean), _ptr(rstd), _ptr(inp), _ptr(weight),

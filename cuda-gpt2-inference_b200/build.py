@@ -22,6 +22,7 @@ SOURCES = [
     "kernels/gemm_tf32.cu",
     "kernels/gemm_tf32_pair.cu",
     "kernels/attention.cu",
+    "kernels/attention_x3.cu",
     "driver/gpt2.cu",
 ]
 

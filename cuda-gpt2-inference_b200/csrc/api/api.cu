@@ -148,6 +148,14 @@ int b200_attention_forward(b200_ctx* ctx, float* out, float* qkvr, float* att, c
     return b200::launch_attention(ctx, out, att, inp, B, T, C, NH, 0);
 }
 
+int b200_attention_forward_x3(b200_ctx* ctx, float* out, float* qkvr, float* att, const float* inp,
+                              int B, int T, int C, int NH) {
+    if (!ctx) return B200_ERR_NULL;
+    REQUIRE_PTR(out); REQUIRE_PTR(inp); REQUIRE_PTR(qkvr); OPTIONAL_PTR(att);
+    if (B <= 0 || T <= 0 || C <= 0 || NH <= 0 || C % NH || C / NH != 64 || T % 64) return B200_ERR_SHAPE;
+    return b200::launch_attention_x3(ctx, out, qkvr, att, inp, B, T, C, NH);
+}
+
 int b200_layernorm_forward(b200_ctx* ctx, float* out, float* mean, float* rstd, const float* inp,
                            const float* weight, const float* bias, int B, int T, int C) {
     if (!ctx) return B200_ERR_NULL;

@@ -21,6 +21,7 @@ struct b200_gpt2 {
     size_t off[17] = {};
     float* params = nullptr;
     float* wte_rounded = nullptr;  // TF32-rounded copy of wte for the lm-head (round_operands)
+    float* qkv_small = nullptr;    // scratch of the 3xTF32 attention (allocated by set_options)
     bool weights_rounded = false;
     // activations, sized for max_B * max_T rows
     float *residual = nullptr, *ln_out = nullptr, *qkv = nullptr, *atty = nullptr,
@@ -91,13 +92,16 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
         const float* fcb = P + off[11] + (size_t)l * 4 * C;
         const float* fpw = P + off[12] + (size_t)l * C * 4 * C;
         const float* fpb = P + off[13] + (size_t)l * C;
-        // The attention kernel multiplies on the TF32 pipe in every mode.  Storing q, k and v
-        // rounded-to-nearest makes them exact TF32 values, so the tensor core's truncation no
-        // longer shrinks every product (a systematic bias); what is left is unbiased rounding
-        // noise that the softmax-weighted sums average down.
-        const int qkv_flags = (m->round_operands || m->gemm_mode == B200_TF32X3) ? GEMM_ROUND_OUT_TF32 : 0;
+        // The single-pass attention kernel multiplies q, k and v on the TF32 pipe as they are.
+        // Storing them rounded-to-nearest makes them exact TF32 values, so the tensor core's
+        // truncation no longer shrinks every product (a systematic bias); what is left is
+        // unbiased rounding noise that the softmax-weighted sums average down.  The 3xTF32
+        // attention needs the unrounded values.
+        const bool att_x3 = (m->gemm_mode == B200_TF32X3) && m->qkv_small;
+        const int qkv_flags = (!att_x3 && (m->round_operands || m->gemm_mode == B200_TF32X3)) ? GEMM_ROUND_OUT_TF32 : 0;
         STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * C, qkv_flags, m->gemm_mode));
-        STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, C, NH, rnd));
+        if (att_x3) STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->atty, m->qkv_small, nullptr, m->qkv, B, T, C, NH));
+        else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, C, NH, rnd));
         STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, C, C, 0, m->gemm_mode));
         STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
                                              m->branch, ln2w, ln2b, M, C, rnd));
@@ -187,7 +191,7 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     cudaSetDevice(m->ctx->device);
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
-    void* ptrs[] = {m->params, m->wte_rounded, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
+    void* ptrs[] = {m->params, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
                     m->fch, m->logits, m->tokens, m->argmax};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete m;
@@ -213,6 +217,10 @@ int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int l
     if (m->round_operands != round_operands || m->gemm_mode != gemm_mode || m->lmhead_mode != lmhead_mode) {
         for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
         m->graphs.clear();
+    }
+    if (gemm_mode == B200_TF32X3 && !m->qkv_small) {
+        cudaSetDevice(m->ctx->device);
+        B200_CUDA(m->ctx, cudaMalloc(&m->qkv_small, (size_t)m->max_B * m->max_T * 3 * m->cfg.channels * sizeof(float)));
     }
     m->round_operands = round_operands;
     m->gemm_mode = gemm_mode;
@@ -257,8 +265,9 @@ int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) {
         it = m->graphs.emplace(key, exec).first;
     }
     B200_CUDA(ctx, cudaGraphLaunch(it->second, ctx->stream));
-    // kernels inside the replayed graph: encoder, first layernorm, 7 per layer, lm-head
-    ctx->launches += 2 + 7ull * m->cfg.num_layers + 1;
+    // kernels inside the replayed graph: encoder, first layernorm, 7 per layer (8 with the
+    // 3xTF32 attention's split pass), lm-head
+    ctx->launches += 2 + (m->gemm_mode == B200_TF32X3 ? 8ull : 7ull) * m->cfg.num_layers + 1;
     return B200_OK;
 }
 

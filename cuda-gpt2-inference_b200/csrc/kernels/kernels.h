@@ -29,6 +29,11 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
 int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, int B, int T, int C,
                      int NH, int flags);
 
+// 3xTF32 attention: qkv_small is a scratch buffer shaped like qkv ([B,T,3C]) that receives the
+// dropped low parts of qkv; two kernel launches (split + attention)
+int launch_attention_x3(b200_ctx* ctx, float* out, float* qkv_small, float* lse, const float* qkv, int B,
+                        int T, int C, int NH);
+
 // fast, accurate tanh-GELU: x * sigmoid(2u), u = sqrt(2/pi) * (x + 0.044715 x^3)
 __device__ __forceinline__ float gelu_tanh(float x) {
     const float k2 = 1.5957691216057308f;  // 2*sqrt(2/pi)

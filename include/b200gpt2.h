@@ -88,6 +88,13 @@ int b200_matmul_forward(b200_ctx* ctx, float* out, const float* inp, const float
 int b200_attention_forward(b200_ctx* ctx, float* out, float* qkvr, float* att, const float* inp,
                            int B, int T, int C, int NH);
 
+/* The same operator with split-operand (3xTF32) products, for the B200_TF32X3 mode: q.k and p.v
+ * keep the low mantissa bits that a single TF32 pass drops.  qkvr is REQUIRED here: a scratch
+ * buffer of the shape of inp ([B,T,3C], the buffer the reference's signature already carries,
+ * kernels/attention/2_flash_attention.cuh:336-341) that receives the dropped parts of inp. */
+int b200_attention_forward_x3(b200_ctx* ctx, float* out, float* qkvr, float* att, const float* inp,
+                              int B, int T, int C, int NH);
+
 /* Replaces layernorm_forward_block / _block_vectorized / _warp
  * (kernels/layernorm/1_layernorm_block.cuh:63-65, 2_...:74-76, 3_layernorm_warp.cuh:78-80).
  * mean and rstd ([B,T]) may be NULL.  Precondition: C % 4 == 0, C <= 4096. */
@@ -174,8 +181,8 @@ int b200_gpt2_load_params_host(b200_gpt2* model, const float* host_params, size_
  * the encoder stays bit-exact).  The tensor core truncates raw fp32 operands, which shrinks
  * every product; rounding to nearest first removes that bias (logit error 4.6e-4 rms instead
  * of 7.9e-4 on GPT-2 124M).  gemm_mode applies to all GEMMs; lmhead_mode to the lm-head alone;
- * B200_TF32X3 ignores operand rounding except for q, k and v, which the attention kernel
- * multiplies in one TF32 pass.  use_graph != 0 replays the forward from a CUDA graph after the
+ * B200_TF32X3 ignores operand rounding; with gemm_mode == B200_TF32X3 attention also runs with
+ * split operands (b200_attention_forward_x3; its scratch buffer is allocated by this call).  use_graph != 0 replays the forward from a CUDA graph after the
  * first call of a given (B,T). */
 int b200_gpt2_set_options(b200_gpt2* model, int round_operands, int gemm_mode, int lmhead_mode,
                           int use_graph);

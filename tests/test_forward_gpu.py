@@ -63,7 +63,8 @@ def test_gpt2_124m_full_length_sequences(pkg, orc, ctx, mode):
     single TF32 pass, whose logit error is 4.6e-4 rms, physically cannot hold 99.9 %: it measures
     99.4-100 % per sequence.  The single-pass mode is therefore held to the max-abs bar, to
     >= 99 % agreement and to the property that it only ever differs from the oracle on such
-    near-ties; the 3xTF32 mode (1e-4 rms) is held to the full 99.9 % bar."""
+    near-ties; the 3xTF32 mode (split-operand GEMMs and attention: 1.3e-5 rms, 8e-5 max) is held to
+    the full 99.9 % bar and to 1e-4 of the largest logit."""
     import torch
     B, T = 8, 1024
     cfg, ocfg, params, model = _make(pkg, orc, ctx, dict(), B, T)
@@ -89,8 +90,8 @@ def test_gpt2_124m_full_length_sequences(pkg, orc, ctx, mode):
             assert len(gaps) == 0 or gaps.max() < 4e-3, "a top-1 miss that is not a near-tie"
         else:
             assert agree >= 0.999, agree
-            assert rms < 2e-4
-            assert mx < 5e-4 * np.abs(want).max()  # attention still runs one TF32 pass per product
+            assert rms < 5e-5
+            assert mx < 1e-4 * np.abs(want).max()  # "within 1e-4 relative error"
     model.close()
 
 

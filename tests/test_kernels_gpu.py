@@ -252,3 +252,21 @@ def test_matmul_tf32x3_within_1e4_relative(ctx, dev, orc, pkg, B, T, C, OC, has_
     assert np.isfinite(got).all()
     scale = float(np.abs(want - (res if has_res else 0)).max())
     assert np.abs(got - want).max() <= 1e-4 * scale, (np.abs(got - want).max(), scale)
+
+
+@pytest.mark.parametrize("B,T,NH", [(1, 64, 1), (2, 128, 2), (1, 256, 12), (2, 192, 3), (1, 1024, 2)])
+def test_attention_x3_matches_oracle(ctx, dev, orc, B, T, NH):
+    """Split-operand attention of the 3xTF32 mode: fp32-level agreement with the oracle."""
+    C = NH * 64
+    qkv = orc.fill_normal((B, T, 3 * C), 141)
+    want, wlse = orc.attention_forward(qkv, NH, precise=True)
+    out, lse = dev.full((B, T, C), float("nan")), dev.full((B, NH, T), float("nan"))
+    scratch = dev.empty((B, T, 3 * C))
+    d_in = dev.to(qkv)
+    ctx.attention_forward_x3(out, scratch, lse, d_in, B, T, C, NH)
+    got = dev.back(out)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() < 2e-5, np.abs(got - want).max()
+    assert np.abs(dev.back(lse) - wlse).max() < 2e-5
+    assert np.array_equal(d_in.cpu().numpy(), qkv), "inp must not be modified"
+    assert ctx.raw("attention_forward_x3", out, None, None, d_in, B, T, C, NH) == 1  # scratch is required
