@@ -41,12 +41,15 @@ EXPORTS = (
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
     "b200_gpt2_forward_static",
+    "b200_gpt2_create_tp", "b200_gpt2_set_allreduce", "b200_gpt2_param_offsets_tp", "b200_gpt2_shard_params_host",
 )
 
 STATIC_MAX_TOKEN_CHANNELS = 196608  # B*T*C limit of b200_gpt2_forward_static
 
 PROF_NAMES = ("encoder", "layernorm", "gemm_qkv", "attention", "gemm_attproj", "fused_residual_layernorm",
-              "gemm_fc", "gemm_fcproj", "gemm_lmhead")
+              "gemm_fc", "gemm_fcproj", "gemm_lmhead", "allreduce")
+
+ALLREDUCE_FN = C.CFUNCTYPE(C.c_int, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p)
 
 _lib = None
 
@@ -112,6 +115,11 @@ def lib() -> C.CDLL:
         l.b200_gpt2_set_profile.argtypes = [vp, i]
         l.b200_gpt2_read_profile.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_long)]
         l.b200_gpt2_forward_static.argtypes = [vp, vp, vp, vp, i, i, vp]
+        l.b200_gpt2_create_tp.argtypes = [C.POINTER(vp), vp, vp, i, i, i, i]
+        l.b200_gpt2_set_allreduce.argtypes = [vp, ALLREDUCE_FN, vp]
+        l.b200_gpt2_param_offsets_tp.argtypes = [vp, i, i, C.POINTER(sz)]
+        l.b200_gpt2_param_offsets_tp.restype = sz
+        l.b200_gpt2_shard_params_host.argtypes = [vp, i, i, vp, vp]
         _lib = l
     return _lib
 
@@ -266,15 +274,72 @@ def shard_batch(B: int, world_size: int, rank: int) -> tuple[int, int]:
     return start, start + base + (1 if rank < rem else 0)
 
 
+def tp_heads(num_heads: int, tp_size: int, tp_rank: int) -> tuple[int, int]:
+    """(first head, number of heads) of a tensor-parallel rank: NH // n each, the first NH % n
+    ranks one more."""
+    base, rem = divmod(num_heads, tp_size)
+    return tp_rank * base + min(tp_rank, rem), base + (1 if tp_rank < rem else 0)
+
+
+def param_offsets_tp(cfg: GPT2Config, tp_size: int, tp_rank: int) -> list[int]:
+    """Offsets of the 16 tensors in a tensor-parallel rank's local parameter array."""
+    offs = (C.c_size_t * 17)()
+    cc = cfg.c()
+    if lib().b200_gpt2_param_offsets_tp(C.byref(cc), tp_size, tp_rank, offs) == 0:
+        raise ValueError("model cannot be split this way")
+    return [int(o) for o in offs]
+
+
+def shard_params(cfg: GPT2Config, tp_size: int, tp_rank: int, full_params):
+    """Cuts a tensor-parallel rank's parameters out of a full host parameter array (numpy)."""
+    import numpy as np
+    local = np.empty(param_offsets_tp(cfg, tp_size, tp_rank)[16], dtype=np.float32)
+    cc = cfg.c()
+    st = lib().b200_gpt2_shard_params_host(C.byref(cc), tp_size, tp_rank, _ptr(full_params), _ptr(local))
+    if st != B200_OK:
+        raise B200Error(f"shard_params: {lib().b200_status_string(st).decode()}")
+    return local
+
+
 class GPT2:
     """gpt2_forward driver (C++ inside the library).  Allocates parameters and one reusable set
-    of activations for up to max_B x max_T tokens."""
+    of activations for up to max_B x max_T tokens.  With tp_size > 1 this is one rank of a
+    tensor-parallel group: load shard_params(...) and set an all-reduce (set_allreduce_torch)."""
 
-    def __init__(self, ctx: Context, cfg: GPT2Config, max_B: int, max_T: int):
+    def __init__(self, ctx: Context, cfg: GPT2Config, max_B: int, max_T: int, tp_size: int = 1, tp_rank: int = 0):
         self.ctx, self.cfg, self.max_B, self.max_T = ctx, cfg, max_B, max_T
+        self.tp_size, self.tp_rank = tp_size, tp_rank
         self._h = C.c_void_p()
+        self._allreduce_cb = None
         cc = cfg.c()
-        ctx.check(lib().b200_gpt2_create(C.byref(self._h), ctx._h, C.byref(cc), max_B, max_T), "gpt2_create")
+        ctx.check(lib().b200_gpt2_create_tp(C.byref(self._h), ctx._h, C.byref(cc), max_B, max_T, tp_size, tp_rank),
+                  "gpt2_create")
+
+    @property
+    def logits_width(self) -> int:
+        Vp = self.cfg.padded_vocab_size
+        return Vp // self.tp_size if (Vp % self.tp_size == 0 and (Vp // self.tp_size) % 4 == 0) else Vp
+
+    def num_local_params(self) -> int:
+        return param_offsets_tp(self.cfg, self.tp_size, self.tp_rank)[16]
+
+    def set_allreduce_torch(self, torch_stream, group=None):
+        """Uses torch.distributed (NCCL) for the one all-reduce per attention / MLP block."""
+        import torch
+        import torch.distributed as dist
+        dev = self.ctx.device
+
+        def _cb(user, buf, count, stream):
+            try:
+                t = _view_device(int(buf), (int(count),), torch.float32, dev)
+                with torch.cuda.stream(torch_stream):
+                    dist.all_reduce(t, group=group)
+                return 0
+            except Exception:  # the C side turns this into B200_ERR_CUDA
+                return 1
+
+        self._allreduce_cb = ALLREDUCE_FN(_cb)  # keep the trampoline alive
+        self.ctx.check(lib().b200_gpt2_set_allreduce(self._h, self._allreduce_cb, None), "set_allreduce")
 
     def params_ptr(self) -> int:
         return int(lib().b200_gpt2_params(self._h))
@@ -282,7 +347,7 @@ class GPT2:
     def params_tensor(self):
         """The flat fp32 parameter array as a torch view over the library's device memory."""
         import torch
-        n = self.cfg.num_params()
+        n = self.num_local_params()
         return _view_device(self.params_ptr(), (n,), torch.float32, self.ctx.device)
 
     def load_params(self, host_params):
@@ -296,7 +361,7 @@ class GPT2:
         """tokens: CUDA int32 [B,T].  Asynchronous; returns a view of the logits [B,T,Vp]."""
         import torch
         self.ctx.check(lib().b200_gpt2_forward(self._h, _ptr(tokens), B, T), "gpt2_forward")
-        return _view_device(int(lib().b200_gpt2_logits(self._h)), (B, T, self.cfg.padded_vocab_size),
+        return _view_device(int(lib().b200_gpt2_logits(self._h)), (B, T, self.logits_width),
                             torch.float32, self.ctx.device)
 
     def forward_host(self, tokens_host, B: int, T: int, logits_host=None, last_logits_host=None, argmax_host=None):

@@ -29,6 +29,16 @@ struct b200_gpt2 {
     int* tokens = nullptr;
     int* argmax = nullptr;
     int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
+    // tensor parallelism (Megatron style): this rank's share of the attention heads, of the MLP
+    // width and of the vocabulary; with tp_size == 1 these are the full dimensions
+    int tp_size = 1, tp_rank = 0;
+    int attn_c = 0;    // channels of the local heads (nh_local * 64)
+    int nh_local = 0;
+    int mlp_c = 0;     // local width of the MLP hidden layer (4C / tp_size)
+    int vp_local = 0;  // local width of the logits
+    int vp_row0 = 0;   // first row of wte used by the local lm-head
+    b200_allreduce_fn allreduce = nullptr;
+    void* allreduce_user = nullptr;
     std::map<std::pair<int, int>, cudaGraphExec_t> graphs;
     // per-operator timing (b200_gpt2_set_profile): one event pair per kernel launch
     bool profile = false;
@@ -38,6 +48,48 @@ struct b200_gpt2 {
     double prof_ms[B200_PROF_NUM] = {};
     long prof_launches[B200_PROF_NUM] = {};
 };
+
+namespace {
+
+int tp_heads(int NH, int n, int r) { return NH / n + (r < NH % n ? 1 : 0); }
+int tp_head0(int NH, int n, int r) { return r * (NH / n) + (r < NH % n ? r : NH % n); }
+
+// offsets of the 16 parameter tensors in the (rank-local) flat layout
+size_t local_param_offsets(const b200_gpt2_config* cfg, int attn_c, int mlp_c, size_t* offsets) {
+    const size_t C = cfg->channels, L = cfg->num_layers, Vp = cfg->padded_vocab_size, mT = cfg->max_seq_len;
+    const size_t A = attn_c, F = mlp_c;
+    const size_t sizes[16] = {Vp * C, mT * C, L * C, L * C, L * 3 * A * C, L * 3 * A, L * C * A, L * C,
+                              L * C, L * C, L * F * C, L * F, L * C * F, L * C, C, C};
+    size_t o = 0;
+    for (int i = 0; i < 16; ++i) { if (offsets) offsets[i] = o; o += sizes[i]; }
+    if (offsets) offsets[16] = o;
+    return o;
+}
+
+// fills the rank-local dimensions; returns false if the model cannot be split this way
+bool set_tp_dims(b200_gpt2* m, int tp_size, int tp_rank) {
+    const b200_gpt2_config& c = m->cfg;
+    if (tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size || tp_size > c.num_heads) return false;
+    if ((4 * c.channels) % tp_size || ((4 * c.channels) / tp_size) % 4) return false;
+    m->tp_size = tp_size;
+    m->tp_rank = tp_rank;
+    m->nh_local = tp_heads(c.num_heads, tp_size, tp_rank);
+    m->attn_c = m->nh_local * 64;
+    m->mlp_c = 4 * c.channels / tp_size;
+    // the lm-head is split over the vocabulary when it divides evenly (logits stay sharded),
+    // otherwise every rank computes all of it
+    if (c.padded_vocab_size % tp_size == 0 && (c.padded_vocab_size / tp_size) % 4 == 0) {
+        m->vp_local = c.padded_vocab_size / tp_size;
+        m->vp_row0 = tp_rank * m->vp_local;
+    } else {
+        m->vp_local = c.padded_vocab_size;
+        m->vp_row0 = 0;
+    }
+    m->n_params = local_param_offsets(&m->cfg, m->attn_c, m->mlp_c, m->off);
+    return true;
+}
+
+}  // namespace
 
 namespace {
 
@@ -60,11 +112,17 @@ int prof_end(b200_gpt2* m) {
     return B200_OK;
 }
 
+int tp_allreduce(b200_gpt2* m, float* buf, size_t count) {
+    if (!m->allreduce) return B200_ERR_STATE;
+    return m->allreduce(m->allreduce_user, buf, count, m->ctx->stream) == 0 ? B200_OK : B200_ERR_CUDA;
+}
+
 int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
     using namespace b200;
     b200_ctx* ctx = m->ctx;
     const b200_gpt2_config& c = m->cfg;
-    const int C = c.channels, L = c.num_layers, NH = c.num_heads, Vp = c.padded_vocab_size;
+    const int C = c.channels, L = c.num_layers, Vp = c.padded_vocab_size;
+    const int A = m->attn_c, NH = m->nh_local, F = m->mlp_c;  // rank-local widths
     const int M = B * T;
     const float* P = m->params;
     const size_t* off = m->off;
@@ -82,15 +140,15 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
     STEP(B200_PROF_ENCODER, launch_encoder(ctx, m->residual, tokens, P + off[0], P + off[1], B, T, C, Vp));
     STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], M, C, rnd));
     for (int l = 0; l < L; ++l) {
-        const float* qkvw = P + off[4] + (size_t)l * 3 * C * C;
-        const float* qkvb = P + off[5] + (size_t)l * 3 * C;
-        const float* apw = P + off[6] + (size_t)l * C * C;
+        const float* qkvw = P + off[4] + (size_t)l * 3 * A * C;
+        const float* qkvb = P + off[5] + (size_t)l * 3 * A;
+        const float* apw = P + off[6] + (size_t)l * C * A;
         const float* apb = P + off[7] + (size_t)l * C;
         const float* ln2w = P + off[8] + (size_t)l * C;
         const float* ln2b = P + off[9] + (size_t)l * C;
-        const float* fcw = P + off[10] + (size_t)l * 4 * C * C;
-        const float* fcb = P + off[11] + (size_t)l * 4 * C;
-        const float* fpw = P + off[12] + (size_t)l * C * 4 * C;
+        const float* fcw = P + off[10] + (size_t)l * F * C;
+        const float* fcb = P + off[11] + (size_t)l * F;
+        const float* fpw = P + off[12] + (size_t)l * C * F;
         const float* fpb = P + off[13] + (size_t)l * C;
         // The single-pass attention kernel multiplies q, k and v on the TF32 pipe as they are.
         // Storing them rounded-to-nearest makes them exact TF32 values, so the tensor core's
@@ -99,21 +157,24 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
         // attention needs the unrounded values.
         const bool att_x3 = (m->gemm_mode == B200_TF32X3) && m->qkv_small;
         const int qkv_flags = (!att_x3 && (m->round_operands || m->gemm_mode == B200_TF32X3)) ? GEMM_ROUND_OUT_TF32 : 0;
-        STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * C, qkv_flags, m->gemm_mode));
-        if (att_x3) STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->atty, m->qkv_small, nullptr, m->qkv, B, T, C, NH));
-        else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, C, NH, rnd));
-        STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, C, C, 0, m->gemm_mode));
+        STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * A, qkv_flags, m->gemm_mode));
+        if (att_x3) STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->atty, m->qkv_small, nullptr, m->qkv, B, T, A, NH));
+        else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, A, NH, rnd));
+        STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, A, C, 0, m->gemm_mode));
+        // tensor parallel: every rank holds a partial sum over its heads; one all-reduce per block
+        if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
         STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
                                              m->branch, ln2w, ln2b, M, C, rnd));
-        STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, 4 * C, GEMM_GELU | grnd, m->gemm_mode));
-        STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, m->branch, m->fch, fpw, fpb, nullptr, M, 4 * C, C, 0, m->gemm_mode));
+        STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, F, GEMM_GELU | grnd, m->gemm_mode));
+        STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, m->branch, m->fch, fpw, fpb, nullptr, M, F, C, 0, m->gemm_mode));
+        if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
         const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
         const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
         STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
                                              m->branch, nw, nb, M, C, rnd));
     }
-    const float* head_w = (m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0];
-    STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, Vp, 0, m->lmhead_mode));
+    const float* head_w = ((m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0]) + (size_t)m->vp_row0 * C;
+    STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, m->vp_local, 0, m->lmhead_mode));
 #undef STEP
     return B200_OK;
 }
@@ -152,7 +213,55 @@ size_t b200_gpt2_param_offsets(const b200_gpt2_config* cfg, size_t* offsets) {
     return o;
 }
 
+size_t b200_gpt2_param_offsets_tp(const b200_gpt2_config* cfg, int tp_size, int tp_rank, size_t* offsets) {
+    if (!cfg || tp_size < 1 || tp_rank < 0 || tp_rank >= tp_size || tp_size > cfg->num_heads || (4 * cfg->channels) % tp_size)
+        return 0;
+    return local_param_offsets(cfg, tp_heads(cfg->num_heads, tp_size, tp_rank) * 64, 4 * cfg->channels / tp_size, offsets);
+}
+
+int b200_gpt2_shard_params_host(const b200_gpt2_config* cfg, int tp_size, int tp_rank, const float* full, float* local) {
+    if (!cfg || !full || !local) return B200_ERR_NULL;
+    size_t fo[17], lo[17];
+    b200_gpt2_param_offsets(cfg, fo);
+    if (b200_gpt2_param_offsets_tp(cfg, tp_size, tp_rank, lo) == 0) return B200_ERR_SHAPE;
+    const size_t C = cfg->channels, L = cfg->num_layers;
+    const size_t A = (size_t)tp_heads(cfg->num_heads, tp_size, tp_rank) * 64, a0 = (size_t)tp_head0(cfg->num_heads, tp_size, tp_rank) * 64;
+    const size_t F = 4 * C / tp_size, f0 = (size_t)tp_rank * F;
+    const int same[] = {0, 1, 2, 3, 8, 9, 14, 15};  // wte, wpe and the layernorm tensors are replicated
+    for (int t : same) memcpy(local + lo[t], full + fo[t], (fo[t + 1] - fo[t]) * sizeof(float));
+    for (size_t l = 0; l < L; ++l) {
+        for (size_t part = 0; part < 3; ++part) {  // q, k, v rows of the local heads
+            memcpy(local + lo[4] + (l * 3 * A + part * A) * C, full + fo[4] + (l * 3 * C + part * C + a0) * C, A * C * sizeof(float));
+            memcpy(local + lo[5] + l * 3 * A + part * A, full + fo[5] + l * 3 * C + part * C + a0, A * sizeof(float));
+        }
+        for (size_t o = 0; o < C; ++o) {  // input columns of the two projections
+            memcpy(local + lo[6] + (l * C + o) * A, full + fo[6] + (l * C + o) * C + a0, A * sizeof(float));
+            memcpy(local + lo[12] + (l * C + o) * F, full + fo[12] + (l * C + o) * 4 * C + f0, F * sizeof(float));
+        }
+        memcpy(local + lo[10] + l * F * C, full + fo[10] + (l * 4 * C + f0) * C, F * C * sizeof(float));
+        memcpy(local + lo[11] + l * F, full + fo[11] + l * 4 * C + f0, F * sizeof(float));
+        // the projection biases are added once: by rank 0
+        for (int t : {7, 13}) {
+            if (tp_rank == 0) memcpy(local + lo[t] + l * C, full + fo[t] + l * C, C * sizeof(float));
+            else memset(local + lo[t] + l * C, 0, C * sizeof(float));
+        }
+    }
+    return B200_OK;
+}
+
 int b200_gpt2_create(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* cfg, int max_B, int max_T) {
+    return b200_gpt2_create_tp(out, ctx, cfg, max_B, max_T, 1, 0);
+}
+
+int b200_gpt2_set_allreduce(b200_gpt2* m, b200_allreduce_fn fn, void* user) {
+    if (!m) return B200_ERR_NULL;
+    m->allreduce = fn;
+    m->allreduce_user = user;
+    return B200_OK;
+}
+
+int b200_gpt2_create_tp(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* cfg, int max_B, int max_T,
+                        int tp_size, int tp_rank) {
     if (!out || !ctx || !cfg) return B200_ERR_NULL;
     *out = nullptr;
     if (cfg->channels <= 0 || cfg->num_heads <= 0 || cfg->channels % cfg->num_heads ||
@@ -163,17 +272,18 @@ int b200_gpt2_create(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* cfg
     b200_gpt2* m = new (std::nothrow) b200_gpt2();
     if (!m) return B200_ERR_CUDA;
     m->ctx = ctx; m->cfg = *cfg; m->max_B = max_B; m->max_T = max_T;
-    m->n_params = b200_gpt2_param_offsets(cfg, m->off);
-    const size_t M = (size_t)max_B * max_T, C = cfg->channels, Vp = cfg->padded_vocab_size;
+    if (!set_tp_dims(m, tp_size, tp_rank)) { delete m; return B200_ERR_SHAPE; }
+    const size_t M = (size_t)max_B * max_T, C = cfg->channels, Vp = m->vp_local;
+    const size_t A = m->attn_c, F = m->mlp_c;
     cudaError_t e = cudaSetDevice(ctx->device);
     auto alloc = [&](void** p, size_t bytes) { if (e == cudaSuccess) e = cudaMalloc(p, bytes); };
     alloc((void**)&m->params, m->n_params * 4);
     alloc((void**)&m->residual, M * C * 4);
     alloc((void**)&m->ln_out, M * C * 4);
-    alloc((void**)&m->qkv, M * 3 * C * 4);
-    alloc((void**)&m->atty, M * C * 4);
+    alloc((void**)&m->qkv, M * 3 * A * 4);
+    alloc((void**)&m->atty, M * A * 4);
     alloc((void**)&m->branch, M * C * 4);
-    alloc((void**)&m->fch, M * 4 * C * 4);
+    alloc((void**)&m->fch, M * F * 4);
     alloc((void**)&m->logits, M * Vp * 4);
     alloc((void**)&m->tokens, M * 4);
     alloc((void**)&m->argmax, M * 4);
@@ -220,7 +330,7 @@ int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int l
     }
     if (gemm_mode == B200_TF32X3 && !m->qkv_small) {
         cudaSetDevice(m->ctx->device);
-        B200_CUDA(m->ctx, cudaMalloc(&m->qkv_small, (size_t)m->max_B * m->max_T * 3 * m->cfg.channels * sizeof(float)));
+        B200_CUDA(m->ctx, cudaMalloc(&m->qkv_small, (size_t)m->max_B * m->max_T * 3 * m->attn_c * sizeof(float)));
     }
     m->round_operands = round_operands;
     m->gemm_mode = gemm_mode;
@@ -238,7 +348,8 @@ int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) {
         int st = round_weights_once(m);
         if (st != B200_OK) return st;
     }
-    if (!m->use_graph || ctx->stream == nullptr || m->profile) return enqueue_forward(m, tokens, B, T);
+    if (m->tp_size > 1 && !m->allreduce) return B200_ERR_STATE;
+    if (!m->use_graph || ctx->stream == nullptr || m->profile || m->tp_size > 1) return enqueue_forward(m, tokens, B, T);
 
     // CUDA-graph replay: the graph reads token ids from the model's own token buffer
     if (tokens != m->tokens)
@@ -277,7 +388,8 @@ int b200_gpt2_forward_host(b200_gpt2* m, const int* tokens_host, int B, int T, f
     if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
     if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
     b200_ctx* ctx = m->ctx;
-    const size_t M = (size_t)B * T, Vp = m->cfg.padded_vocab_size;
+    const size_t M = (size_t)B * T, Vp = m->vp_local;  // a tensor-parallel rank returns its slice of the vocabulary
+    if (argmax_host && m->vp_local != m->cfg.padded_vocab_size) return B200_ERR_STATE;  // needs all logits
     B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens_host, M * 4, cudaMemcpyHostToDevice, ctx->stream));
     int st = b200_gpt2_forward(m, m->tokens, B, T);
     if (st != B200_OK) return st;
@@ -398,7 +510,7 @@ extern "C" int b200_gpt2_forward_static(b200_ctx* ctx, const b200_gpt2_config* c
     view.cfg = *cfg;
     view.max_B = B;
     view.max_T = T;
-    view.n_params = b200_gpt2_param_offsets(cfg, view.off);
+    if (!set_tp_dims(&view, 1, 0)) return B200_ERR_SHAPE;
     view.params = const_cast<float*>(params);  // read only: weights are not rounded on this path
     view.round_operands = 0;                   // the arithmetic of b200_gpt2_forward with round_operands = 0
     view.residual = scratch;

@@ -196,6 +196,25 @@ float* b200_gpt2_logits(b200_gpt2* model);
  *   argmax_host      [B,T]     arg-max token over [0,V) per position (nullable) */
 int b200_gpt2_forward_host(b200_gpt2* model, const int* tokens_host, int B, int T,
                            float* logits_host, float* last_logits_host, int* argmax_host);
+/* ---- tensor parallelism (optional; Megatron style, for models like GPT-2 XL) --------------
+ * Rank r of tp_size holds the q/k/v rows and attn-proj input columns of its share of the heads
+ * (NH/tp_size each, the first NH % tp_size ranks one more), 1/tp_size of the MLP hidden width,
+ * and - when Vp divides evenly - 1/tp_size of the lm-head (logits stay sharded, [B,T,Vp/tp_size]).
+ * Layernorms, the encoder and the residual stream are replicated.  The partial [B,T,C] sums
+ * after attn-proj and after fc-proj are combined by ONE all-reduce each per block, issued
+ * through a callback so that the communication library stays the caller's choice (NCCL's
+ * ncclAllReduce, or torch.distributed): the callback must enqueue an in-place fp32 sum
+ * all-reduce of buf[0..count) over the tensor-parallel group on `stream` and return 0.
+ * Rank-local parameters use the same 16-tensor order with the local shapes;
+ * b200_gpt2_shard_params_host cuts them out of a full host parameter array. */
+typedef int (*b200_allreduce_fn)(void* user, float* buf, size_t count, void* stream);
+int b200_gpt2_create_tp(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* cfg, int max_B,
+                        int max_T, int tp_size, int tp_rank);
+int b200_gpt2_set_allreduce(b200_gpt2* model, b200_allreduce_fn fn, void* user);
+size_t b200_gpt2_param_offsets_tp(const b200_gpt2_config* cfg, int tp_size, int tp_rank, size_t* offsets);
+int b200_gpt2_shard_params_host(const b200_gpt2_config* cfg, int tp_size, int tp_rank,
+                                const float* full_params, float* local_params);
+
 /* Per-operator device timing of the forward.  While enabled, every kernel launch of
  * b200_gpt2_forward is bracketed by a CUDA event pair on the context's stream (graph replay is
  * bypassed).  b200_gpt2_read_profile synchronises the stream, adds up the elapsed milliseconds
@@ -204,7 +223,7 @@ int b200_gpt2_forward_host(b200_gpt2* model, const int* tokens_host, int B, int 
 enum {
     B200_PROF_ENCODER = 0, B200_PROF_LAYERNORM, B200_PROF_GEMM_QKV, B200_PROF_ATTENTION,
     B200_PROF_GEMM_ATTPROJ, B200_PROF_FUSED_RES_LN, B200_PROF_GEMM_FC, B200_PROF_GEMM_FCPROJ,
-    B200_PROF_GEMM_LMHEAD, B200_PROF_NUM
+    B200_PROF_GEMM_LMHEAD, B200_PROF_ALLREDUCE, B200_PROF_NUM
 };
 int b200_gpt2_set_profile(b200_gpt2* model, int enabled);
 int b200_gpt2_read_profile(b200_gpt2* model, double* ms, long* launches);
