@@ -98,9 +98,11 @@ class ClockSampler:
 
 def _random_init_(model, pkg, torch, seed: int):
     """Random-init weights of the architecture, written in place on the device: matrices
-    N(0, 0.02), layernorm weight 1 / bias 0, linear biases 0."""
+    N(0, 0.02), layernorm weight 1 / bias 0, linear biases 0.  (With tensor parallelism the
+    replicated tensors - wte, wpe, layernorms - come out identical on every rank: same seed,
+    same sizes, drawn first.)"""
     cfg = model.cfg
-    offs = pkg.param_offsets(cfg)
+    offs = pkg.param_offsets_tp(cfg, model.tp_size, model.tp_rank)
     p = model.params_tensor()
     g = torch.Generator(device="cuda")
     g.manual_seed(seed)
@@ -114,13 +116,13 @@ def _random_init_(model, pkg, torch, seed: int):
             view.zero_()
 
 
-def cpu_forward_tokens_per_s(sample_T: int, repeats: int = 1, threads: int | None = None):
-    """Times the CPU oracle's fp32 forward of GPT-2 124M on one sequence of sample_T tokens."""
+def cpu_forward_tokens_per_s(sample_T: int, repeats: int = 1, threads: int | None = None, xl: bool = False):
+    """Times the CPU oracle's fp32 forward of GPT-2 (124M, or XL) on one sequence of sample_T tokens."""
     import numpy as np
     from oracle import oracle as orc
     if threads:
         os.environ["OMP_NUM_THREADS"] = str(threads)
-    cfg = orc.GPT2_124M
+    cfg = orc.GPT2_XL if xl else orc.GPT2_124M
     offs = orc.param_offsets(cfg)
     rng = np.random.default_rng(1234)
     params = np.zeros(offs[16], dtype=np.float32)
@@ -198,18 +200,24 @@ def run_ours(args):
     torch.cuda.set_device(local_rank)
     stream = torch.cuda.Stream()
     ctx = pkg.Context(local_rank, stream)
-    cfg = pkg.GPT2_124M
+    xl = args.model == "xl"
+    cfg = pkg.GPT2_XL if xl else pkg.GPT2_124M
+    tp = bool(args.tp) and world > 1   # one tensor-parallel group over all ranks, one global batch
     B = B_PER_GPU
-    model = pkg.GPT2(ctx, cfg, B, T)
+    model = pkg.GPT2(ctx, cfg, B, T, tp_size=world if tp else 1, tp_rank=rank if tp else 0)
+    if tp:
+        model.set_allreduce_torch(stream)
     with torch.cuda.stream(stream):
         _random_init_(model, pkg, torch, seed=1234 + 0)  # same weights on every rank
         tok_dev = torch.randint(0, cfg.vocab_size, (B, T), dtype=torch.int32, device="cuda",
-                                generator=torch.Generator(device="cuda").manual_seed(4321 + rank))
+                                generator=torch.Generator(device="cuda").manual_seed(4321 + (0 if tp else rank)))
     stream.synchronize()
     tok_host = torch.empty((B, T), dtype=torch.int32).pin_memory()
     tok_host.copy_(tok_dev.cpu())
-    last_host = torch.empty((B, cfg.padded_vocab_size), dtype=torch.float32).pin_memory()
-    amax_host = torch.empty((B, T), dtype=torch.int32).pin_memory()
+    last_host = torch.empty((B, model.logits_width), dtype=torch.float32).pin_memory()
+    amax_host = None if tp else torch.empty((B, T), dtype=torch.int32).pin_memory()
+    amax_np = None if tp else amax_host.numpy()
+    replicas = 1 if tp else world   # independent batches processed per step
 
     def barrier():
         torch.cuda.synchronize()
@@ -253,28 +261,30 @@ def run_ours(args):
 
     # ------------------------------------------------ the same workload in the 3xTF32 mode
     # (split-operand GEMMs and attention: the mode that holds the 99.9 % top-1 / 1e-4 bars)
-    model.set_options(round_operands=0, gemm_mode=pkg.B200_TF32X3, lmhead_mode=pkg.B200_TF32X3)
-    for _ in range(2):
-        model.forward(tok_dev, B, T)
-    barrier()
-    ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    n_x3 = max(1, args.steps // 2)
-    ev2.record(stream)
-    for _ in range(n_x3):
-        model.forward(tok_dev, B, T)
-    ev3.record(stream)
-    barrier()
-    ctx.sync_check()
-    x3_ms = max_over_ranks(ev2.elapsed_time(ev3)) / n_x3
-    model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32)
+    x3_ms = None
+    if not xl:
+        model.set_options(round_operands=0, gemm_mode=pkg.B200_TF32X3, lmhead_mode=pkg.B200_TF32X3)
+        for _ in range(2):
+            model.forward(tok_dev, B, T)
+        barrier()
+        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        n_x3 = max(1, args.steps // 2)
+        ev2.record(stream)
+        for _ in range(n_x3):
+            model.forward(tok_dev, B, T)
+        ev3.record(stream)
+        barrier()
+        ctx.sync_check()
+        x3_ms = max_over_ranks(ev2.elapsed_time(ev3)) / n_x3
+        model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32)
 
     # ---------------------------------------------------------------- end-to-end arm
     for _ in range(2):
-        model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_host.numpy())
+        model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
     barrier()
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_host.numpy())
+        model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
 
@@ -283,14 +293,16 @@ def run_ours(args):
             dist.destroy_process_group()
         return 0
 
-    tokens_total = world * B * T * args.steps
+    tokens_total = replicas * B * T * args.steps
     value = tokens_total / (elapsed_ms * 1e-3)
     peaks = _peaks()
-    # dominant kernel: the tcgen05 TF32 GEMM (five shapes, 4L+1 launches per step)
+    # dominant kernel: the tcgen05 TF32 GEMM (five shapes, 4L+1 launches per step); rank-local widths
     M = B * T
-    Cc, L, Vp = cfg.channels, cfg.num_layers, cfg.padded_vocab_size
-    gemm_flops = {"gemm_qkv": 2.0 * M * Cc * 3 * Cc, "gemm_attproj": 2.0 * M * Cc * Cc, "gemm_fc": 2.0 * M * Cc * 4 * Cc,
-                  "gemm_fcproj": 2.0 * M * 4 * Cc * Cc, "gemm_lmhead": 2.0 * M * Cc * Vp}
+    Cc, L = cfg.channels, cfg.num_layers
+    n_tp = world if tp else 1
+    Ac, Fc, Vl = pkg.tp_heads(cfg.num_heads, n_tp, 0)[1] * 64, 4 * Cc // n_tp, model.logits_width
+    gemm_flops = {"gemm_qkv": 2.0 * M * Cc * 3 * Ac, "gemm_attproj": 2.0 * M * Ac * Cc, "gemm_fc": 2.0 * M * Cc * Fc,
+                  "gemm_fcproj": 2.0 * M * Fc * Cc, "gemm_lmhead": 2.0 * M * Cc * Vl}
     tot_flops = sum(gemm_flops[k] * prof[k][1] for k in gemm_flops)
     tot_ms = sum(prof[k][0] for k in gemm_flops)
     n_gemm = sum(prof[k][1] for k in gemm_flops)
@@ -299,7 +311,7 @@ def run_ours(args):
     per_op = {}
     hbm_bytes = {"layernorm": (2.0 * M * Cc + 2 * Cc) * 4, "fused_residual_layernorm": (4.0 * M * Cc + 2 * Cc) * 4,
                  "encoder": (2.0 * M * Cc + T * Cc) * 4 + M * 4}
-    att_flops = 4.0 * 64 * T * (T + 1) / 2 * cfg.num_heads * B
+    att_flops = 4.0 * 64 * T * (T + 1) / 2 * (Ac // 64) * B
     for name, (ms, n) in prof.items():
         if n == 0:
             continue
@@ -313,28 +325,33 @@ def run_ours(args):
             entry["gbs"] = round(hbm_bytes[name] / (avg * 1e-3) / 1e9, 1)
         per_op[name] = entry
 
-    cpu_tps, cores, _, _ = cpu_forward_tokens_per_s(1024, repeats=1)
-    d2h = B * cfg.padded_vocab_size * 4 + B * T * 4
+    cpu_T = 256 if xl else 1024
+    cpu_tps, cores, _, _ = cpu_forward_tokens_per_s(cpu_T, repeats=1, xl=xl)
+    d2h = B * model.logits_width * 4 + (0 if tp else B * T * 4)
+    workload = WORKLOAD if not xl else "GPT-2 XL 1.5B full-sequence forward, B=8 T=1024 per " + ("tensor-parallel group" if tp else "GPU") + ", fp32 storage, TF32 tensor-core GEMMs (configs[4] shapes)"
+    par = (f"tensor-parallel x{world}: heads / MLP / vocabulary split, one NCCL all-reduce per attention and MLP block" if tp
+           else f"batch-sharded x{world}, no collective")
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": world * B, "seq_len": T, "parallelism": f"batch-sharded x{world}, no collective",
-                   "l2": "no flush: each step streams 0.5 GB of weights and writes 1.65 GB of logits, far beyond the 126 MB L2",
+        "config": {"workload": workload, "global_batch": replicas * B, "seq_len": T, "parallelism": par,
+                   "l2": "no flush: each step streams the weights (0.5 GB for 124M) and writes 1.65 GB of logits, far beyond the 126 MB L2",
                    "flop_per_token": cfg.flops_per_token(T)},
         "roofline": {"bound": "tensor", "kernel": "gemm_tf32_kernel (all five GEMM shapes of the forward)",
                      "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
                      "peak_source": f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32 runs at half the bf16 rate; no TF32 peak is measured)",
                      "launches_per_step": n_gemm / args.steps, "traffic": None, "per_operator": per_op},
         "cpu_baseline": {"value": cpu_tps, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": "1 of the 8 sequences (B=1, T=1024), fp32-accumulate C/OpenMP forward, all host threads, one run"},
-        "e2e": {"value": world * B * T * args.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": B * T * 4,
+                         "sample": f"1 sequence of {cpu_T} tokens (B=1), fp32-accumulate C/OpenMP forward, all host threads, one run"},
+        "e2e": {"value": replicas * B * T * args.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": B * T * 4,
                 "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s / args.steps,
-                "result": "last-position logits [B,Vp] and per-position arg-max token ids [B,T]"},
+                "result": "last-position logits [B,Vp]" + ("" if tp else " and per-position arg-max token ids [B,T]")},
         "gpu_launches": launches,
         "clocks": clocks,
-        "tf32x3": {"value": world * B * T / (x3_ms * 1e-3), "unit": UNIT, "ms_per_step": x3_ms,
-                   "note": "same workload with gemm_mode = lmhead_mode = B200_TF32X3 (split-operand GEMMs and attention)"},
+        "tf32x3": None if x3_ms is None else {
+            "value": replicas * B * T / (x3_ms * 1e-3), "unit": UNIT, "ms_per_step": x3_ms,
+            "note": "same workload with gemm_mode = lmhead_mode = B200_TF32X3 (split-operand GEMMs and attention)"},
     }
     print(json.dumps(line), flush=True)
     model.close()
@@ -457,6 +474,10 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default="124m", choices=["124m", "xl"],
+                    help="124m = the benchmark configuration; xl = GPT-2 XL shapes, B=8 T=1024 per GPU (extra measurement)")
+    ap.add_argument("--tp", action="store_true",
+                    help="with --gpus N > 1: one tensor-parallel group over all ranks instead of batch sharding")
     ap.add_argument("--op", default=None,
                     choices=["all", "matmul", "attention", "layernorm", "fused_residual_layernorm", "rowwise"],
                     help="per-kernel sweep at 8192 rows instead of the forward benchmark")
