@@ -71,8 +71,8 @@ int b200_ctx_create(b200_ctx** out, int device, void* stream) {
     if (e != cudaSuccess) { delete ctx; return B200_ERR_CUDA; }
     if (prop.major != 10) { delete ctx; return B200_ERR_DEVICE; }
     ctx->num_sms = prop.multiProcessorCount;
-    e = cudaMalloc(&ctx->d_status, 64);
-    if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 64);
+    e = cudaMalloc(&ctx->d_status, 256);
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 256);
     if (e != cudaSuccess) { delete ctx; return B200_ERR_CUDA; }
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
@@ -83,6 +83,7 @@ int b200_ctx_create(b200_ctx** out, int device, void* stream) {
         return B200_ERR_CUDA;
     }
     ctx->encode_tiled = reinterpret_cast<b200_encode_tiled_fn>(fn);
+    if (const char* e = getenv("B200_PDL")) ctx->pdl = !(e[0] == '0');
     *out = ctx;
     return B200_OK;
 }

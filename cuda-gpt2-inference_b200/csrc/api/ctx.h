@@ -38,6 +38,7 @@ struct b200_ctx {
     cudaStream_t stream = nullptr;
     int* d_status = nullptr;  // device word: first device-side error code of any kernel
     uint64_t launches = 0;
+    bool pdl = true;  // launch with programmatic stream serialization (B200_PDL=0 turns it off)
     std::string last_error;
     b200_encode_tiled_fn encode_tiled = nullptr;
     std::unordered_map<TensorMapKey, CUtensorMap, TensorMapKeyHash> tmap_cache;

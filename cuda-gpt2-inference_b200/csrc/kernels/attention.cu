@@ -131,6 +131,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    griddep_wait();  // set-up done; from here on global memory is touched
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -353,6 +354,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_SOFTMAX);
     }
 
+    griddep_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -395,9 +397,9 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
     a.round_out = (flags & ROUND_OUT_TF32) ? 1 : 0;
     a.status = ctx->d_status;
     dim3 grid(a.num_qt, NH, B);
-    attention_kernel<<<grid, kAttThreads, AttSmem::TOTAL, ctx->stream>>>(tm, tmv, a);
+    cudaError_t le = launch_pdl(ctx, attention_kernel, grid, dim3(kAttThreads), AttSmem::TOTAL, tm, tmv, a);
     ctx->launches++;
-    B200_CUDA(ctx, cudaGetLastError());
+    B200_CUDA(ctx, le);
     return B200_OK;
 }
 

@@ -69,6 +69,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const GemmArgs args) {
     using Cfg = GemmCfg<BN, X3>;
     constexpr int STAGES = Cfg::STAGES;
+#ifdef B200_GEMM_TIMING
+    const unsigned long long dbg_t0 = globaltimer_ns();
+#endif
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;                                        // [STAGES][A_BYTES]
@@ -112,6 +115,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    griddep_wait();  // set-up done; from here on global memory is touched
+#ifdef B200_GEMM_TIMING
+    const unsigned long long dbg_t1 = globaltimer_ns();
+    unsigned long long* dbg = reinterpret_cast<unsigned long long*>(args.status + 2) + (blockIdx.x == 0 ? 0 : 8);
+    const bool dbg_on = blockIdx.x == 0 || blockIdx.x == gridDim.x - 1;
+#endif
 
     auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
         if (args.n_fastest) { n_blk = tile % args.num_n_blocks; m_blk = tile / args.num_n_blocks; }
@@ -156,6 +165,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     // in the 3xTF32 mode the split warps signal after the TMA data has landed
                     if (!mbar_wait(X3 ? &split_bar[s] : &full_bar[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
+#ifdef B200_GEMM_TIMING
+                    if (dbg_on && it == 0) dbg[2] = globaltimer_ns() - dbg_t0;
+#endif
                     const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * Cfg::A_BYTES), 16, 1024);
                     const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * Cfg::B_BYTES), 16, 1024);
 #pragma unroll
@@ -180,6 +192,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // wait (bounded) until everything issued has retired before tensor memory is freed
             umma_commit(drain_bar);
             if (!mbar_wait(drain_bar, 0, abort_flag)) ok = false;
+#ifdef B200_GEMM_TIMING
+            if (dbg_on) { dbg[0] = dbg_t1 - dbg_t0; dbg[3] = globaltimer_ns() - dbg_t0; dbg[1] = tile_iter; }
+#endif
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
         }
     } else if (warp < 6) {
@@ -199,6 +214,9 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tc_fence_before_sync();
             mbar_arrive(&tmem_empty_bar[acc]);
         }
+#ifdef B200_GEMM_TIMING
+        if (dbg_on && warp == 2 && lane == 0) dbg[4] = globaltimer_ns() - dbg_t0;
+#endif
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_EPILOGUE);
     } else if (X3) {
         // ------------------------------------------------------- split warps (3xTF32)
@@ -234,6 +252,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
     }
 
+    griddep_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -261,9 +280,9 @@ int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Gemm
     }
     const int tiles = a.num_m_blocks * a.num_n_blocks;
     const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
-    gemm_tf32_kernel<BN, X3><<<grid, Cfg::THREADS, Cfg::SMEM, ctx->stream>>>(ta, tb, a);
+    cudaError_t le = launch_pdl(ctx, gemm_tf32_kernel<BN, X3>, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM, ta, tb, a);
     ctx->launches++;
-    B200_CUDA(ctx, cudaGetLastError());
+    B200_CUDA(ctx, le);
     return B200_OK;
 }
 

@@ -94,6 +94,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     cluster_sync_all();  // the peer's barriers are initialised before anything arrives on them
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
+    griddep_wait();  // set-up done; from here on global memory is touched
 
     auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
         if (args.n_fastest) { n_blk = tile % args.num_n_blocks; m_blk = tile / args.num_n_blocks; }
@@ -210,6 +211,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_EPILOGUE);
     }
 
+    griddep_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();  // the peer is done with this CTA's shared and tensor memory
@@ -234,13 +236,15 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Gem
     cfg.blockDim = dim3(kThreads);
     cfg.dynamicSmemBytes = Cfg::SMEM;
     cfg.stream = ctx->stream;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
     attr[0].val.clusterDim.y = 1;
     attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = ctx->pdl ? 2 : 1;
     if (!resident_pairs[ctx->device & 63]) {
         B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
         cfg.gridDim = dim3(2 * num_pairs_max);

@@ -1,6 +1,7 @@
 // Internal launchers: each validates nothing (the C-ABI layer does) and enqueues kernels on
 // ctx->stream, bumping ctx->launches once per kernel launch.
 #pragma once
+#include <utility>
 #include "../api/ctx.h"
 
 namespace b200 {
@@ -33,6 +34,25 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
 // dropped low parts of qkv; two kernel launches (split + attention)
 int launch_attention_x3(b200_ctx* ctx, float* out, float* qkv_small, float* lse, const float* qkv, int B,
                         int T, int C, int NH);
+
+// Launch with programmatic stream serialization: the kernel may begin its set-up while its
+// predecessor in the stream drains.  ONLY for kernels that call griddep_wait() before their
+// first global-memory access.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(b200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = ctx->pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
 
 // fast, accurate tanh-GELU: x * sigmoid(2u), u = sqrt(2/pi) * (x + 0.044715 x^3)
 __device__ __forceinline__ float gelu_tanh(float x) {

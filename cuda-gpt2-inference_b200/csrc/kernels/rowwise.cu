@@ -32,6 +32,8 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
                       float* __restrict__ rstd, const float* inp1, const float* inp2,
                       const float* __restrict__ weight, const float* __restrict__ bias, int M, int C,
                       int flags) {
+    griddep_wait();
+    griddep_launch_dependents();
     const int lane = threadIdx.x & 31;
     const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
     if (row >= M) return;
@@ -105,10 +107,10 @@ int launch_ln_any(b200_ctx* ctx, float* out, float* res_out, float* mean, float*
                   int M, int C, int flags) {
     const int nv = (C / 4 + 31) / 32;
     const dim3 grid((M + kRowWarps - 1) / kRowWarps), block(kRowWarps * 32);
-#define B200_LN_CASE(NV)                                                                        \
-    layernorm_rows_kernel<NV, FUSED><<<grid, block, 0, ctx->stream>>>(out, res_out, mean, rstd, \
-                                                                      inp1, inp2, weight, bias, \
-                                                                      M, C, flags)
+    cudaError_t le = cudaSuccess;
+#define B200_LN_CASE(NV)                                                                                    \
+    le = launch_pdl(ctx, layernorm_rows_kernel<NV, FUSED>, grid, block, 0, out, res_out, mean, rstd, inp1, \
+                    inp2, weight, bias, M, C, flags)
     if (nv <= 2) B200_LN_CASE(2);
     else if (nv <= 4) B200_LN_CASE(4);
     else if (nv <= 6) B200_LN_CASE(6);       // C = 768
@@ -119,7 +121,7 @@ int launch_ln_any(b200_ctx* ctx, float* out, float* res_out, float* mean, float*
     else B200_LN_CASE(32);                   // C <= 4096
 #undef B200_LN_CASE
     ctx->launches++;
-    B200_CUDA(ctx, cudaGetLastError());
+    B200_CUDA(ctx, le);
     return B200_OK;
 }
 
@@ -165,6 +167,8 @@ __global__ void round_tf32_kernel(float4* data, size_t n4, float* data_s, size_t
 __global__ void encoder_kernel(float4* __restrict__ out, const int* __restrict__ tok,
                                const float4* __restrict__ wte, const float4* __restrict__ wpe,
                                int M, int T, int C4, int vocab_rows, int* status) {
+    griddep_wait();
+    griddep_launch_dependents();
     const size_t total = (size_t)M * C4;
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
@@ -268,12 +272,11 @@ int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, 
                    int B, int T, int C, int vocab_rows) {
     const size_t n4 = (size_t)B * T * (C / 4);
     const int grid = stream_grid(ctx, n4, 256, 16);
-    encoder_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<float4*>(out), tok,
-                                                  reinterpret_cast<const float4*>(wte),
-                                                  reinterpret_cast<const float4*>(wpe), B * T, T,
-                                                  C / 4, vocab_rows, ctx->d_status);
+    cudaError_t le = launch_pdl(ctx, encoder_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<float4*>(out), tok,
+                                reinterpret_cast<const float4*>(wte), reinterpret_cast<const float4*>(wpe), B * T, T,
+                                C / 4, vocab_rows, ctx->d_status);
     ctx->launches++;
-    B200_CUDA(ctx, cudaGetLastError());
+    B200_CUDA(ctx, le);
     return B200_OK;
 }
 

@@ -41,6 +41,16 @@ __device__ __forceinline__ bool elect_one() {
     return pred != 0;
 }
 
+// ------------------------------------------- programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start (and run
+// its set-up: barrier init, tensor-memory allocation, descriptor prefetch) while the kernel
+// before it in the stream is still finishing.  griddep_wait() blocks until that kernel has
+// completed and its memory is visible; nothing may read or write global memory before it.
+// griddep_launch_dependents() lets the next kernel in the stream begin its own set-up once
+// every CTA of this grid has called it (or exited).
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // ------------------------------------------------------------------ mbarrier
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
