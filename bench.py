@@ -341,7 +341,11 @@ def run_ours(args):
         "roofline": {"bound": "tensor", "kernel": "gemm_tf32_kernel (all five GEMM shapes of the forward)",
                      "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
                      "peak_source": f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32 runs at half the bf16 rate; no TF32 peak is measured)",
-                     "launches_per_step": n_gemm / args.steps, "traffic": None, "per_operator": per_op},
+                     "launches_per_step": n_gemm / args.steps,
+                     # ncu dram__bytes_read.sum + dram__bytes_write.sum, average per GEMM launch of the 124M
+                     # forward (profiles/gemm_tf32_dram_traffic_by_shape.md); not captured for other models
+                     "traffic": None if (xl or tp) else 114.2e6, "algorithmic_bytes": None if (xl or tp) else 142.9e6,
+                     "per_operator": per_op},
         "cpu_baseline": {"value": cpu_tps, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"1 sequence of {cpu_T} tokens (B=1), fp32-accumulate C/OpenMP forward, all host threads, one run"},
         "e2e": {"value": replicas * B * T * args.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": B * T * 4,

@@ -29,7 +29,7 @@ ACT_NONE, ACT_GELU = 0, 1
 EXPORTS = (
     "b200_ctx_create", "b200_ctx_destroy", "b200_ctx_set_stream", "b200_ctx_sync_check",
     "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
-    "b200_ctx_last_error",
+    "b200_ctx_last_error", "b200_ctx_wait_timeout_probe",
     "b200_matmul_forward", "b200_attention_forward", "b200_attention_forward_x3", "b200_layernorm_forward",
     "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
     "b200_encoder_forward",
@@ -70,6 +70,7 @@ def lib() -> C.CDLL:
         l.b200_ctx_destroy.argtypes = [vp]
         l.b200_ctx_set_stream.argtypes = [vp, vp]
         l.b200_ctx_sync_check.argtypes = [vp]
+        l.b200_ctx_wait_timeout_probe.argtypes = [vp, i]
         l.b200_ctx_launch_count.argtypes = [vp]
         l.b200_ctx_launch_count.restype = C.c_uint64
         l.b200_ctx_reset_launch_count.argtypes = [vp]

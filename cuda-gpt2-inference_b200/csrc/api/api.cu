@@ -116,6 +116,12 @@ int b200_ctx_sync_check(b200_ctx* ctx) {
     return B200_OK;
 }
 
+int b200_ctx_wait_timeout_probe(b200_ctx* ctx, int limit_ms) {
+    if (!ctx) return B200_ERR_NULL;
+    if (limit_ms < 1 || limit_ms > 2000) return B200_ERR_SHAPE;
+    return b200::launch_wait_timeout_probe(ctx, (unsigned long long)limit_ms * 1000000ull);
+}
+
 // debugging aid for kernel experiments: device address of the status words
 void* b200_ctx_debug_status(b200_ctx* ctx) { return ctx ? ctx->d_status : nullptr; }
 

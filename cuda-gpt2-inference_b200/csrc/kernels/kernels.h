@@ -20,6 +20,7 @@ int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, 
                    int B, int T, int C, int vocab_rows /* <=0: unchecked */);
 int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N);
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
+int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns);
 
 // epilogue flags of the GEMM
 enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2 };

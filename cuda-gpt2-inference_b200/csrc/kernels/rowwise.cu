@@ -218,6 +218,20 @@ argmax_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
     }
 }
 
+// Exercises the bounded-wait path on purpose-built inputs: one thread waits on an mbarrier that
+// nothing ever arrives on, gives up after limit_ns, and records the time-out exactly as the
+// GEMM / attention roles do.  The kernel returns normally and the context stays usable.
+__global__ void wait_timeout_probe_kernel(int* status, unsigned long long limit_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        abort_flag = 0;
+        fence_barrier_init();
+        if (!mbar_wait(&bar, 0, &abort_flag, limit_ns)) atomicCAS(status, 0, DEV_TIMEOUT_PRODUCER);
+    }
+}
+
 inline int stream_grid(const b200_ctx* ctx, size_t n4, int block, int ctas_per_sm) {
     size_t want = (n4 + block - 1) / block;
     size_t cap = (size_t)ctx->num_sms * ctas_per_sm;
@@ -277,6 +291,13 @@ int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, 
                                 C / 4, vocab_rows, ctx->d_status);
     ctx->launches++;
     B200_CUDA(ctx, le);
+    return B200_OK;
+}
+
+int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns) {
+    wait_timeout_probe_kernel<<<1, 32, 0, ctx->stream>>>(ctx->d_status, limit_ns);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;
 }
 

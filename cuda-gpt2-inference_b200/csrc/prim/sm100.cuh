@@ -102,13 +102,14 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 constexpr uint32_t kWaitSliceNs = 10000;          // one hardware-suspended poll
 
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = globaltimer_ns();
     while (true) {
         if (mbar_try_wait_hint(bar, parity, kWaitSliceNs)) return true;
         if (*abort_flag != 0) return false;
-        if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (globaltimer_ns() - t0 > limit_ns) {
             *abort_flag = 1;
             return false;
         }

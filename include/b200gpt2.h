@@ -59,6 +59,11 @@ int b200_ctx_set_stream(b200_ctx* ctx, void* stream);
 /* Synchronises the stream, then returns B200_ERR_TIMEOUT / B200_ERR_CUDA if a kernel
  * recorded a device-side wait that ran out or CUDA reports an error; clears the word. */
 int b200_ctx_sync_check(b200_ctx* ctx);
+/* Self-test of the failure path: launches one thread that waits on an mbarrier nothing arrives
+ * on and gives up after limit_ms (1..2000), exactly as the GEMM and attention roles do when a
+ * wait runs out.  The kernel returns normally; the next b200_ctx_sync_check reports
+ * B200_ERR_TIMEOUT once and the context stays usable. */
+int b200_ctx_wait_timeout_probe(b200_ctx* ctx, int limit_ms);
 /* Number of kernels this context has launched since creation (or the last reset). */
 uint64_t b200_ctx_launch_count(const b200_ctx* ctx);
 void b200_ctx_reset_launch_count(b200_ctx* ctx);

@@ -270,3 +270,22 @@ def test_attention_x3_matches_oracle(ctx, dev, orc, B, T, NH):
     assert np.abs(dev.back(lse) - wlse).max() < 2e-5
     assert np.array_equal(d_in.cpu().numpy(), qkv), "inp must not be modified"
     assert ctx.raw("attention_forward_x3", out, None, None, d_in, B, T, C, NH) == 1  # scratch is required
+
+
+def test_device_wait_that_runs_out_is_reported_and_context_survives(ctx, dev, orc, pkg):
+    """Failure detection without harming the GPU: a wait on a barrier that nothing signals gives
+    up after its limit, the kernel returns, the host reads B200_ERR_TIMEOUT once, and the same
+    context keeps working."""
+    import time
+    lib = pkg.lib()
+    t0 = time.time()
+    assert lib.b200_ctx_wait_timeout_probe(ctx._h, 100) == 0
+    assert ctx.sync_status() == 6  # B200_ERR_TIMEOUT
+    assert 0.05 < time.time() - t0 < 5.0
+    assert b"101" in lib.b200_ctx_last_error(ctx._h)
+    assert ctx.sync_status() == 0  # reported once, then clear
+    a, b = orc.fill_normal((1024,), 1), orc.fill_normal((1024,), 2)
+    out = dev.empty((1024,))
+    ctx.residual_forward(out, dev.to(a), dev.to(b), 1024)
+    assert np.array_equal(dev.back(out), a + b)
+    assert lib.b200_ctx_wait_timeout_probe(ctx._h, 0) == 2  # limit out of range
