@@ -108,7 +108,8 @@ int b200_ctx_sync_check(b200_ctx* ctx) {
     int word = 0;
     B200_CUDA(ctx, cudaMemcpy(&word, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
     if (word != 0) {
-        B200_CUDA(ctx, cudaMemset(ctx->d_status, 0, sizeof(int)));
+        // the whole area: a kernel that gave up may have left its work counters behind
+        B200_CUDA(ctx, cudaMemset(ctx->d_status, 0, 256));
         ctx->last_error = "device status word = " + std::to_string(word);
         return word == 201 ? B200_ERR_SHAPE : B200_ERR_TIMEOUT;
     }
