@@ -54,7 +54,8 @@ struct AttSmem {
     static constexpr int Q_OFF = 0;                           // 2 buffers x 2 blocks (hs 0-31, 32-63)
     static constexpr int K_OFF = Q_OFF + 4 * kBlk;            // kStages x 2 blocks
     static constexpr int V_OFF = K_OFF + 2 * kStages * kBlk;  // kStages x 2 blocks
-    static constexpr int X_OFF = V_OFF + 2 * kStages * kBlk;  // exchange buffer: 2 halves x 128 floats
+    static constexpr int OUT_OFF = V_OFF + 2 * kStages * kBlk;  // output staging: 2 blocks (hs 0-31, 32-63)
+    static constexpr int X_OFF = OUT_OFF + 2 * kBlk;            // exchange buffer: 2 halves x 128 floats
     static constexpr int BAR_OFF = X_OFF + 2 * 128 * 4;
     static constexpr int TOTAL = 1024 + BAR_OFF + 256;
 };
@@ -70,22 +71,32 @@ __device__ __forceinline__ float ex2_approx(float x) {
     return y;
 }
 
+// three-input maximum (one instruction on sm_100)
+__device__ __forceinline__ float fmax3(float a, float b, float c) {
+    float y;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
+    return y;
+}
 // barrier among the two warps that share a group of 32 query rows
 __device__ __forceinline__ void pair_bar_sync(int id) {
     asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
 }
-// the same barrier, returning whether `ok` holds in all 64 threads
-__device__ __forceinline__ bool pair_bar_all(int id, bool ok) {
+// barrier among all 256 softmax threads
+__device__ __forceinline__ void softmax_bar_sync() {
+    asm volatile("bar.sync 5, 256;" ::: "memory");
+}
+// the same barrier, returning whether `ok` holds in all 256 threads
+__device__ __forceinline__ bool softmax_bar_all(bool ok) {
     uint32_t r;
     asm volatile(
         "{\n\t"
         ".reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %2, 0;\n\t"
-        "bar.red.and.pred p, %1, 64, q;\n\t"
+        "setp.ne.u32 q, %1, 0;\n\t"
+        "bar.red.and.pred p, 5, 256, q;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(r)
-        : "r"(id), "r"((uint32_t)ok)
+        : "r"((uint32_t)ok)
         : "memory");
     return r != 0;
 }
@@ -98,6 +109,7 @@ struct AttArgs {
     int num_items;  // num_qt * NH * B
     float scale_log2;
     int round_out;  // store TF32-rounded outputs (they feed only the next GEMM)
+    int tma_out;    // T is a multiple of 128: whole tiles leave through shared memory and a TMA store
     int* status;    // [0] error word; [kWorkWord], [kWorkWord+1]: work and finished-CTA counters (zero between launches)
 };
 
@@ -112,12 +124,13 @@ __device__ __forceinline__ void decode_item(const AttArgs& a, int item, int& qt,
 
 __global__ void __launch_bounds__(kAttThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_constant__ CUtensorMap tmap_v,
-                 const AttArgs args) {
+                 const __grid_constant__ CUtensorMap tmap_out, const AttArgs args) {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* q_s = smem + AttSmem::Q_OFF;
     uint8_t* k_s = smem + AttSmem::K_OFF;
     uint8_t* v_s = smem + AttSmem::V_OFF;
+    uint8_t* out_s = smem + AttSmem::OUT_OFF;
     float* xchg = reinterpret_cast<float*>(smem + AttSmem::X_OFF);  // [2][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::BAR_OFF);
     uint64_t* item_full = bars;        // [2]  work item published
@@ -160,6 +173,7 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
         fence_barrier_init();
         tma_prefetch_desc(&tmap_qkv);
         tma_prefetch_desc(&tmap_v);
+        tma_prefetch_desc(&tmap_out);
     }
     if (warp == 1) {
         tmem_alloc(tmem_holder, kTmemCols);
@@ -301,16 +315,16 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
         const int c0 = hf * 64;                  // first key column of this thread within a block
         bool ok = true;
         uint32_t g = 0;
-        // The two warps of a pair leave together: the decision is taken once per item, on a pair
-        // barrier that also tells whether any of the 64 threads has had a wait run out.  Inside
-        // an item there is no early exit: after a failed wait the remaining waits are skipped but
-        // every pair barrier is still executed, so the partner warp can never be left alone in
-        // one (the results are discarded and the status word says why).
+        // All softmax warps leave together: the decision is taken once per item, on a barrier
+        // that also tells whether any of the 256 threads has had a wait run out.  Inside an item
+        // there is no early exit: after a failed wait the remaining waits are skipped but every
+        // barrier is still executed, so no warp can be left alone in one (the results are
+        // discarded and the status word says why).
         for (uint32_t n = 0;; ++n) {
             const int slot = n & 1;
             if (ok && !mbar_wait(&item_full[slot], (n >> 1) & 1, abort_flag)) ok = false;
-            const bool pair_ok = pair_bar_all(bar_id, ok);
-            const int item = pair_ok ? item_slot[slot] : -1;
+            const bool all_ok = softmax_bar_all(ok);
+            const int item = all_ok ? item_slot[slot] : -1;
             if (item < 0) break;
             int qt, h, b;
             decode_item(args, item, qt, h, b);
@@ -337,17 +351,26 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
             for (int j = 0; j < n_kv; ++j, ++g) {
                 const bool diag = (j == n_kv - 1);
                 // row maximum of the raw scores (the scale is positive, so it commutes with max)
-                float pm = -INFINITY;
+                // (four independent chains of three-input maxima: the loop is latency-bound)
+                float pm0 = -INFINITY, pm1 = -INFINITY, pm2 = -INFINITY, pm3 = -INFINITY;
                 if (!diag) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) pm = fmaxf(pm, fmaxf(__uint_as_float(t0[i]), __uint_as_float(t1[i])));
+                    for (int i = 0; i < 32; i += 4) {
+                        pm0 = fmax3(pm0, __uint_as_float(t0[i]), __uint_as_float(t0[i + 1]));
+                        pm1 = fmax3(pm1, __uint_as_float(t0[i + 2]), __uint_as_float(t0[i + 3]));
+                        pm2 = fmax3(pm2, __uint_as_float(t1[i]), __uint_as_float(t1[i + 1]));
+                        pm3 = fmax3(pm3, __uint_as_float(t1[i + 2]), __uint_as_float(t1[i + 3]));
+                    }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        if (c0 + i <= r) pm = fmaxf(pm, __uint_as_float(t0[i]));
-                        if (c0 + 32 + i <= r) pm = fmaxf(pm, __uint_as_float(t1[i]));
+                    for (int i = 0; i < 32; i += 4) {
+                        pm0 = fmax3(pm0, c0 + i <= r ? __uint_as_float(t0[i]) : -INFINITY, c0 + i + 1 <= r ? __uint_as_float(t0[i + 1]) : -INFINITY);
+                        pm1 = fmax3(pm1, c0 + i + 2 <= r ? __uint_as_float(t0[i + 2]) : -INFINITY, c0 + i + 3 <= r ? __uint_as_float(t0[i + 3]) : -INFINITY);
+                        pm2 = fmax3(pm2, c0 + 32 + i <= r ? __uint_as_float(t1[i]) : -INFINITY, c0 + 32 + i + 1 <= r ? __uint_as_float(t1[i + 1]) : -INFINITY);
+                        pm3 = fmax3(pm3, c0 + 32 + i + 2 <= r ? __uint_as_float(t1[i + 2]) : -INFINITY, c0 + 32 + i + 3 <= r ? __uint_as_float(t1[i + 3]) : -INFINITY);
                     }
                 }
+                float pm = fmaxf(fmaxf(pm0, pm1), fmaxf(pm2, pm3));
                 xchg[hf * 128 + r] = pm;
                 pair_bar_sync(bar_id);
                 pm = fmaxf(pm, xchg[(hf ^ 1) * 128 + r]);
@@ -359,30 +382,46 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
                 // TF32 (the low 13 bits dropped, one logic op - exactly what the tensor core would
                 // do to it as an operand) BEFORE it is summed, so numerator and denominator use the
                 // same weights and the cut only adds noise that the normalisation centres.
-                float sum = 0.f;
+                float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
                 const float neg_mx = -mx;
                 if (!diag) {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < 32; i += 2) {
                         const uint32_t u0 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(t0[i]), args.scale_log2, neg_mx))) & 0xFFFFE000u;
                         const uint32_t u1 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(t1[i]), args.scale_log2, neg_mx))) & 0xFFFFE000u;
-                        sum += __uint_as_float(u0) + __uint_as_float(u1);
+                        const uint32_t u2 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(t0[i + 1]), args.scale_log2, neg_mx))) & 0xFFFFE000u;
+                        const uint32_t u3 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(t1[i + 1]), args.scale_log2, neg_mx))) & 0xFFFFE000u;
+                        sum0 += __uint_as_float(u0);
+                        sum1 += __uint_as_float(u1);
+                        sum2 += __uint_as_float(u2);
+                        sum3 += __uint_as_float(u3);
                         t0[i] = u0;
                         t1[i] = u1;
+                        t0[i + 1] = u2;
+                        t1[i + 1] = u3;
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
+                    for (int i = 0; i < 32; i += 2) {
                         uint32_t u0 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(t0[i]), args.scale_log2, neg_mx))) & 0xFFFFE000u;
                         uint32_t u1 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(t1[i]), args.scale_log2, neg_mx))) & 0xFFFFE000u;
+                        uint32_t u2 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(t0[i + 1]), args.scale_log2, neg_mx))) & 0xFFFFE000u;
+                        uint32_t u3 = __float_as_uint(ex2_approx(fmaf(__uint_as_float(t1[i + 1]), args.scale_log2, neg_mx))) & 0xFFFFE000u;
                         if (c0 + i > r) u0 = 0u;
                         if (c0 + 32 + i > r) u1 = 0u;
-                        sum += __uint_as_float(u0) + __uint_as_float(u1);
+                        if (c0 + i + 1 > r) u2 = 0u;
+                        if (c0 + 32 + i + 1 > r) u3 = 0u;
+                        sum0 += __uint_as_float(u0);
+                        sum1 += __uint_as_float(u1);
+                        sum2 += __uint_as_float(u2);
+                        sum3 += __uint_as_float(u3);
                         t0[i] = u0;
                         t1[i] = u1;
+                        t0[i + 1] = u2;
+                        t1[i + 1] = u3;
                     }
                 }
-                l = l * alpha + sum;  // this thread's half of the row sum
+                l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));  // this thread's half of the row sum
                 // O_{j-1} has retired: its result can be read and the P columns overwritten
                 uint32_t o_prev[32];
                 if (j > 0) {
@@ -429,8 +468,30 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
             l += xchg[(hf ^ 1) * 128 + r];
             pair_bar_sync(bar_id);
             const int t_idx = q0 + r;
-            if (ok && t_idx < args.T) {
-                const float inv_l = 1.0f / l;
+            const float inv_l = 1.0f / l;
+            if (args.tma_out) {
+                // Whole tile: each thread puts its 32 columns (one 128-byte row of block hf) into
+                // the staging buffer in the 128-byte-swizzled layout, and one thread sends the two
+                // blocks off with TMA stores - full-line writes instead of 16-byte pieces of 32
+                // different rows per instruction.
+                if (threadIdx.x == 64) tma_store_wait_read();  // the previous tile has left the buffer
+                softmax_bar_sync();
+                float4* row = reinterpret_cast<float4*>(out_s + hf * kBlk + r * 128);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    float4 v = make_float4(o_acc[4 * i] * inv_l, o_acc[4 * i + 1] * inv_l,
+                                           o_acc[4 * i + 2] * inv_l, o_acc[4 * i + 3] * inv_l);
+                    if (args.round_out) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
+                    row[i ^ (r & 7)] = v;
+                }
+                fence_proxy_async_smem();
+                softmax_bar_sync();
+                if (threadIdx.x == 64 && ok) {
+                    tma_store_2d(&tmap_out, h * HS, row_base + q0, out_s);
+                    tma_store_2d(&tmap_out, h * HS + 32, row_base + q0, out_s + kBlk);
+                    tma_store_commit();
+                }
+            } else if (ok && t_idx < args.T) {
                 float* o = args.out + ((size_t)(row_base + t_idx) * args.C) + h * HS + hf * 32;
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -439,12 +500,13 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
                     if (args.round_out) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
                     *reinterpret_cast<float4*>(o + 4 * i) = v;
                 }
-                if (args.lse && hf == 0)
-                    args.lse[((size_t)b * args.NH + h) * args.T + t_idx] = m * 0.6931471805599453f + logf(l);
             }
+            if (ok && t_idx < args.T && args.lse && hf == 0)
+                args.lse[((size_t)b * args.NH + h) * args.T + t_idx] = m * 0.6931471805599453f + logf(l);
             tc_fence_before_sync();
             mbar_arrive(&item_empty[slot]);
         }
+        if (threadIdx.x == 64) tma_store_wait_all();
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_SOFTMAX);
     }
 
@@ -482,6 +544,12 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
     st = b200_get_tensor_map(ctx, &tmv, qkv, (uint64_t)B * T, (uint64_t)3 * C, (uint64_t)3 * C, BKV, 32, 1);
     if (st != B200_OK) return st;
     AttArgs a;
+    a.tma_out = (T % BQ == 0) ? 1 : 0;
+    CUtensorMap tmo = tm;  // not used unless whole tiles are stored
+    if (a.tma_out) {
+        st = b200_get_tensor_map(ctx, &tmo, out, (uint64_t)B * T, (uint64_t)C, (uint64_t)C, BQ, 32);
+        if (st != B200_OK) return st;
+    }
     a.out = out; a.lse = lse; a.B = B; a.T = T; a.C = C; a.NH = NH;
     a.num_qt = (T + BQ - 1) / BQ;
     a.num_items = a.num_qt * NH * B;
@@ -489,7 +557,7 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
     a.round_out = (flags & ROUND_OUT_TF32) ? 1 : 0;
     a.status = ctx->d_status;
     const int grid = a.num_items < ctx->num_sms ? a.num_items : ctx->num_sms;
-    cudaError_t le = launch_pdl(ctx, attention_kernel, dim3(grid), dim3(kAttThreads), AttSmem::TOTAL, tm, tmv, a);
+    cudaError_t le = launch_pdl(ctx, attention_kernel, dim3(grid), dim3(kAttThreads), AttSmem::TOTAL, tm, tmv, tmo, a);
     ctx->launches++;
     B200_CUDA(ctx, le);
     return B200_OK;
