@@ -28,6 +28,7 @@ struct b200_gpt2 {
           *branch = nullptr, *fch = nullptr, *logits = nullptr;
     int* tokens = nullptr;
     int* argmax = nullptr;
+    unsigned long long* argmax_keys = nullptr;  // per row: best (value, column) of the lm-head's fused arg-max
     int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
     // tensor parallelism (Megatron style): this rank's share of the attention heads, of the MLP
     // width and of the vocabulary; with tp_size == 1 these are the full dimensions
@@ -39,7 +40,7 @@ struct b200_gpt2 {
     int vp_row0 = 0;   // first row of wte used by the local lm-head
     b200_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
-    std::map<std::pair<int, int>, cudaGraphExec_t> graphs;
+    std::map<std::pair<std::pair<int, int>, bool>, cudaGraphExec_t> graphs;  // by (B, T, with arg-max)
     // per-operator timing (b200_gpt2_set_profile): one event pair per kernel launch
     bool profile = false;
     std::vector<cudaEvent_t> ev_pool;
@@ -117,7 +118,10 @@ int tp_allreduce(b200_gpt2* m, float* buf, size_t count) {
     return m->allreduce(m->allreduce_user, buf, count, m->ctx->stream) == 0 ? B200_OK : B200_ERR_CUDA;
 }
 
-int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
+// with_argmax: the lm-head GEMM also leaves, per position, the arg-max over the real vocabulary
+// in m->argmax (found in its epilogue while the logits are on their way out: no second pass
+// over the 1.6 GB of logits)
+int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, bool with_argmax) {
     using namespace b200;
     b200_ctx* ctx = m->ctx;
     const b200_gpt2_config& c = m->cfg;
@@ -174,7 +178,13 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T) {
                                              m->branch, nw, nb, M, C, rnd));
     }
     const float* head_w = ((m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0]) + (size_t)m->vp_row0 * C;
-    STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, m->vp_local, 0, m->lmhead_mode));
+    if (with_argmax) B200_CUDA(ctx, cudaMemsetAsync(m->argmax_keys, 0, (size_t)M * 8, ctx->stream));
+    STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, m->vp_local, 0, m->lmhead_mode,
+                                                 with_argmax ? m->argmax_keys : nullptr, c.vocab_size));
+    if (with_argmax) {
+        st = launch_argmax_decode(ctx, m->argmax, m->argmax_keys, M);
+        if (st != B200_OK) return st;
+    }
 #undef STEP
     return B200_OK;
 }
@@ -287,6 +297,7 @@ int b200_gpt2_create_tp(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* 
     alloc((void**)&m->logits, M * Vp * 4);
     alloc((void**)&m->tokens, M * 4);
     alloc((void**)&m->argmax, M * 4);
+    alloc((void**)&m->argmax_keys, M * 8);
     if (e != cudaSuccess) {
         b200_fail_cuda(ctx, e, "cudaMalloc (b200_gpt2_create)");
         b200_gpt2_destroy(m);
@@ -302,7 +313,7 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
     void* ptrs[] = {m->params, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
-                    m->fch, m->logits, m->tokens, m->argmax};
+                    m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete m;
     return B200_OK;
@@ -339,7 +350,7 @@ int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int l
     return B200_OK;
 }
 
-int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) {
+static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, bool with_argmax) {
     if (!m || !tokens) return B200_ERR_NULL;
     if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
     if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
@@ -349,22 +360,22 @@ int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) {
         if (st != B200_OK) return st;
     }
     if (m->tp_size > 1 && !m->allreduce) return B200_ERR_STATE;
-    if (!m->use_graph || ctx->stream == nullptr || m->profile || m->tp_size > 1) return enqueue_forward(m, tokens, B, T);
+    if (!m->use_graph || ctx->stream == nullptr || m->profile || m->tp_size > 1) return enqueue_forward(m, tokens, B, T, with_argmax);
 
     // CUDA-graph replay: the graph reads token ids from the model's own token buffer
     if (tokens != m->tokens)
         B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens, (size_t)B * T * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-    auto key = std::make_pair(B, T);
+    auto key = std::make_pair(std::make_pair(B, T), with_argmax);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
         // warm the tensor-map cache and function attributes outside of capture
-        int st = enqueue_forward(m, m->tokens, B, T);
+        int st = enqueue_forward(m, m->tokens, B, T, with_argmax);
         if (st != B200_OK) return st;
         B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         cudaGraph_t graph = nullptr;
         const uint64_t launches_before = ctx->launches;
         B200_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-        st = enqueue_forward(m, m->tokens, B, T);
+        st = enqueue_forward(m, m->tokens, B, T, with_argmax);
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
         ctx->launches = launches_before;
         if (st != B200_OK) { if (graph) cudaGraphDestroy(graph); return st; }
@@ -378,9 +389,11 @@ int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) {
     B200_CUDA(ctx, cudaGraphLaunch(it->second, ctx->stream));
     // kernels inside the replayed graph: encoder, first layernorm, 7 per layer (8 with the
     // 3xTF32 attention's split pass), lm-head
-    ctx->launches += 2 + (m->gemm_mode == B200_TF32X3 ? 8ull : 7ull) * m->cfg.num_layers + 1;
+    ctx->launches += 2 + (m->gemm_mode == B200_TF32X3 ? 8ull : 7ull) * m->cfg.num_layers + 1 + (with_argmax ? 1 : 0);
     return B200_OK;
 }
+
+int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) { return forward_impl(m, tokens, B, T, false); }
 
 int b200_gpt2_forward_host(b200_gpt2* m, const int* tokens_host, int B, int T, float* logits_host,
                            float* last_logits_host, int* argmax_host) {
@@ -391,13 +404,9 @@ int b200_gpt2_forward_host(b200_gpt2* m, const int* tokens_host, int B, int T, f
     const size_t M = (size_t)B * T, Vp = m->vp_local;  // a tensor-parallel rank returns its slice of the vocabulary
     if (argmax_host && m->vp_local != m->cfg.padded_vocab_size) return B200_ERR_STATE;  // needs all logits
     B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens_host, M * 4, cudaMemcpyHostToDevice, ctx->stream));
-    int st = b200_gpt2_forward(m, m->tokens, B, T);
+    int st = forward_impl(m, m->tokens, B, T, argmax_host != nullptr);
     if (st != B200_OK) return st;
-    if (argmax_host) {
-        st = b200::launch_argmax_rows(ctx, m->argmax, m->logits, (int)M, m->cfg.vocab_size, (int)Vp);
-        if (st != B200_OK) return st;
-        B200_CUDA(ctx, cudaMemcpyAsync(argmax_host, m->argmax, M * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    }
+    if (argmax_host) B200_CUDA(ctx, cudaMemcpyAsync(argmax_host, m->argmax, M * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (last_logits_host) {
         // rows (b, T-1): one strided 2-D copy
         B200_CUDA(ctx, cudaMemcpy2DAsync(last_logits_host, Vp * 4, m->logits + (size_t)(T - 1) * Vp, (size_t)T * Vp * 4,
@@ -521,5 +530,5 @@ extern "C" int b200_gpt2_forward_static(b200_ctx* ctx, const b200_gpt2_config* c
     view.fch = scratch + 7 * MC;
     view.logits = logits;
     // every region is written in full before it is read, so nothing has to be cleared between calls
-    return enqueue_forward(&view, tokens, B, T);
+    return enqueue_forward(&view, tokens, B, T, false);
 }

@@ -20,7 +20,22 @@ struct GemmArgs {
     int n_fastest;
     int flags;
     int* status;
+    // optional fused arg-max over columns [0, argmax_cols) of every output row (null: off);
+    // only for a plain epilogue (no bias, activation, residual or rounding)
+    unsigned long long* argmax_keys;
+    int argmax_cols;
 };
+
+// Arg-max keys: the value as an order-preserving 32-bit integer in the high half, the inverted
+// column in the low half, so that an unsigned 64-bit maximum picks the largest value and, among
+// equal values, the lowest column.  Keys start at zero (below every real value).
+__device__ __forceinline__ uint32_t argmax_enc(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+__device__ __forceinline__ float argmax_dec(uint32_t k) {
+    return __uint_as_float((k & 0x80000000u) ? (k ^ 0x80000000u) : ~k);
+}
 
 // One epilogue warp drains its 32 lanes x BN columns.  Thread `lane` holds row (q*32 + lane) of
 // the accumulator, 32 columns at a time.  Writing that straight to global memory would scatter
@@ -38,11 +53,41 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, uin
     const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
     const int sub_row = lane >> 3;  // 0..3: row within a group of four
     const int sub_chk = lane & 7;   // 16-byte chunk within the 128-byte row piece
+    // Fused arg-max: this thread owns one row of the tile.  It starts from the row's best key so
+    // far (other tiles of the row may have been finished by other CTAs; a stale value only costs
+    // a needless update), filters each 32-column chunk by its maximum, and looks for the column
+    // only in the rare chunk that beats the best - a handful of times per row over a whole GEMM.
+    const bool do_argmax = args.argmax_keys != nullptr;
+    const int my_row = row0 + lane;
+    unsigned long long best_key = 0ull;
+    float best_v = -INFINITY;
+    bool improved = false;
+    if (do_argmax && my_row < args.M) {
+        best_key = args.argmax_keys[my_row];
+        if (best_key != 0ull) best_v = argmax_dec((uint32_t)(best_key >> 32));
+    }
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r);
         tmem_ld_wait();
+        if (do_argmax) {
+            const int cbase = col0 + c * 32;
+            float cm = -INFINITY;  // chunk maximum (columns beyond the limit count too: only a filter)
+#pragma unroll
+            for (int i = 0; i < 32; i += 4)
+                cm = fmaxf(cm, fmaxf(fmaxf(__uint_as_float(r[i]), __uint_as_float(r[i + 1])),
+                                     fmaxf(__uint_as_float(r[i + 2]), __uint_as_float(r[i + 3]))));
+            if (cm >= best_v && cbase < args.argmax_cols) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const unsigned long long key =
+                        ((unsigned long long)argmax_enc(__uint_as_float(r[i])) << 32) | (0xFFFFFFFFu - (uint32_t)(cbase + i));
+                    if (cbase + i < args.argmax_cols && key > best_key) { best_key = key; improved = true; }
+                }
+                best_v = argmax_dec((uint32_t)(best_key >> 32));
+            }
+        }
         uint8_t* stage = stage2 + (c & 1) * 4096;
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -74,10 +119,12 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, uin
         // the buffer used two chunks ago is free again once every lane is past this point
         __syncwarp();
     }
+    if (do_argmax && improved && my_row < args.M) atomicMax(args.argmax_keys + my_row, best_key);
 }
 
 // CTA-pair GEMM (gemm_tf32_pair.cu): 256 x BN tiles computed by two CTAs sharing one UMMA.
 int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
-                          const float* bias, const float* residual, int M, int K, int N, int flags);
+                          const float* bias, const float* residual, int M, int K, int N, int flags,
+                          unsigned long long* argmax_keys, int argmax_cols);
 
 }  // namespace b200

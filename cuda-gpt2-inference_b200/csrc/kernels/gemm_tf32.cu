@@ -290,14 +290,16 @@ int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Gemm
 
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
-                     int mode) {
+                     int mode, unsigned long long* argmax_keys, int argmax_cols) {
     const bool x3 = (mode == B200_TF32X3);
+    // the fused arg-max looks at the raw accumulator: only with a plain epilogue
+    if (argmax_keys && (bias || residual || flags != 0)) { ctx->last_error = "fused arg-max needs a plain GEMM epilogue"; return B200_ERR_STATE; }
     // CTA pairs pull a third less operand traffic out of L2 per flop and win where there are many
     // tiles per SM (wide outputs: lm-head, GPT-2 XL shapes); with a few tiles per SM the
     // single-CTA kernel's finer N tiles quantise better.  B200_GEMM_PAIR=0/1 forces the choice.
     static const int pair_env = [] { const char* e = getenv("B200_GEMM_PAIR"); return e ? (e[0] == '0' ? 0 : 1) : -1; }();
     const bool use_pair = pair_env >= 0 ? pair_env == 1 : (N >= 4096 && M >= 2048);
-    if (!x3 && use_pair) return launch_gemm_tf32_pair(ctx, out, inp, weight, bias, residual, M, K, N, flags);
+    if (!x3 && use_pair) return launch_gemm_tf32_pair(ctx, out, inp, weight, bias, residual, M, K, N, flags, argmax_keys, argmax_cols);
     const int num_m = (M + BM - 1) / BM;
     // pick the N tile that minimises waves x per-tile cost on this GPU's SM count
     int best_bn = 128;
@@ -325,6 +327,8 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
     a.n_fastest = ((size_t)N * K * 4 <= (size_t)32 << 20) ? 1 : 0;
     a.flags = flags;
     a.status = ctx->d_status;
+    a.argmax_keys = argmax_keys;
+    a.argmax_cols = argmax_cols;
 
     CUtensorMap ta, tb;
     int st = b200_get_tensor_map(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);

@@ -266,7 +266,8 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Gem
 }  // namespace
 
 int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
-                          const float* bias, const float* residual, int M, int K, int N, int flags) {
+                          const float* bias, const float* residual, int M, int K, int N, int flags,
+                          unsigned long long* argmax_keys, int argmax_cols) {
     const int num_pairs_max = ctx->num_sms / 2;
     const int num_m = (M + 2 * BM - 1) / (2 * BM);
     const int num_kb = (K + BK - 1) / BK;
@@ -294,6 +295,8 @@ int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const flo
     a.n_fastest = ((size_t)N * K * 4 <= (size_t)32 << 20) ? 1 : 0;
     a.flags = flags;
     a.status = ctx->d_status;
+    a.argmax_keys = argmax_keys;
+    a.argmax_cols = argmax_cols;
 
     CUtensorMap ta, tb;
     int st = b200_get_tensor_map(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);

@@ -26,7 +26,9 @@ int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns);
 enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2 };
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
-                     int mode);
+                     int mode, unsigned long long* argmax_keys = nullptr, int argmax_cols = 0);
+// turns the keys left by a GEMM with fused arg-max into column indices (0 for an untouched key)
+int launch_argmax_decode(b200_ctx* ctx, int* out, const unsigned long long* keys, int M);
 
 int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, int B, int T, int C,
                      int NH, int flags);

@@ -301,6 +301,18 @@ int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns) {
     return B200_OK;
 }
 
+__global__ void argmax_decode_kernel(int* __restrict__ out, const unsigned long long* __restrict__ keys, int M) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < M) out[i] = keys[i] ? (int)(0xFFFFFFFFu - (uint32_t)(keys[i] & 0xFFFFFFFFull)) : 0;
+}
+
+int launch_argmax_decode(b200_ctx* ctx, int* out, const unsigned long long* keys, int M) {
+    argmax_decode_kernel<<<(M + 255) / 256, 256, 0, ctx->stream>>>(out, keys, M);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld) {
     argmax_rows_kernel<<<M, 256, 0, ctx->stream>>>(out, logits, V, ld);
     ctx->launches++;

@@ -141,6 +141,37 @@ def test_graph_replay_matches_eager(pkg, orc, ctx):
     model.close()
 
 
+@pytest.mark.parametrize("use_graph", [0, 1])
+def test_fused_argmax_matches_the_logits(pkg, orc, ctx, use_graph):
+    """The host-buffer call takes the per-position arg-max out of the lm-head GEMM's epilogue
+    instead of a second pass over the logits: it must equal the arg-max of the logits the same
+    call returns, bit for bit (ties to the lowest index, padded vocabulary columns excluded).
+    B*T = 2048 rows puts the lm-head on the CTA-pair kernel, as in the benchmark configuration;
+    the second call repeats the first (keys are reset per call; with use_graph it is a replay)."""
+    B, T = 2, 1024
+    cfg, ocfg, params, model = _make(pkg, orc, ctx, dict(num_layers=1), B, T)
+    model.set_options(use_graph=use_graph)
+    for seed in (11, 12, 11):
+        tokens = orc.fill_tokens((B, T), seed=seed, vocab=cfg.vocab_size)
+        logits = np.empty((B, T, cfg.padded_vocab_size), np.float32)
+        amax = np.empty((B, T), np.int32)
+        model.forward_host(tokens, B, T, logits_host=logits, argmax_host=amax)
+        assert np.array_equal(amax, logits[..., :cfg.vocab_size].argmax(-1))
+    # a column of the padding that would win if it were not excluded
+    params2 = params.copy()
+    off = pkg.param_offsets(cfg)
+    wte = params2[off[0]:off[0] + cfg.padded_vocab_size * cfg.channels].reshape(cfg.padded_vocab_size, cfg.channels)
+    wte[cfg.vocab_size:] = 50.0 * np.sign(wte[0])  # large positive logit wherever it correlates
+    model.load_params(params2)
+    tokens = orc.fill_tokens((B, T), seed=13, vocab=cfg.vocab_size)
+    logits = np.empty((B, T, cfg.padded_vocab_size), np.float32)
+    amax = np.empty((B, T), np.int32)
+    model.forward_host(tokens, B, T, logits_host=logits, argmax_host=amax)
+    assert (logits.argmax(-1) >= cfg.vocab_size).any(), "the padding never wins: the case tests nothing"
+    assert np.array_equal(amax, logits[..., :cfg.vocab_size].argmax(-1))
+    model.close()
+
+
 def test_xl_shapes_small_batch(pkg, orc, ctx):
     """GPT-2 XL dimensions (C=1600, 25 heads) on a 4-layer stack, B=1 T=128, against the oracle."""
     B, T = 1, 128
