@@ -42,17 +42,62 @@ def _peaks():
 
 
 class ClockSampler:
-    """nvidia-smi samples of SM clock and throttle reasons while the timed region runs."""
+    """SM clock and clock-event reasons sampled (read-only) while the timed region runs: a
+    background thread polling NVML every few milliseconds; `nvidia-smi -lms` as a fall-back when
+    the NVML bindings are missing."""
     FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
               "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown"}
 
-    def __init__(self, gpu_index: int):
-        self.gpu_index = gpu_index
+    def __init__(self, gpu_index: int, uuid: str | None = None, period_s: float = 0.004):
+        self.gpu_index, self.uuid, self.period_s = gpu_index, uuid, period_s
         self.proc = None
         self.path = None
+        self.thread = None
+        self.stop_flag = None
+        self.clocks, self.maxes, self.reasons = [], [], set()
+
+    def _nvml_loop(self, nv, handle):
+        try:
+            max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(handle, nv.NVML_CLOCK_SM))
+        except Exception:
+            max_mhz = None
+        reasons_fn = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or \
+            getattr(nv, "nvmlDeviceGetCurrentClocksThrottleReasons", None)
+        while not self.stop_flag.is_set():
+            try:
+                self.clocks.append(float(nv.nvmlDeviceGetClockInfo(handle, nv.NVML_CLOCK_SM)))
+                if max_mhz:
+                    self.maxes.append(max_mhz)
+                if reasons_fn:
+                    mask = int(reasons_fn(handle))
+                    for bit, name in self.REASON_BITS.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+            except Exception:
+                pass
+            self.stop_flag.wait(self.period_s)
 
     def start(self):
+        try:
+            import threading
+            import pynvml as nv
+            nv.nvmlInit()
+            handle = None
+            if self.uuid:
+                try:
+                    handle = nv.nvmlDeviceGetHandleByUUID(self.uuid if self.uuid.startswith("GPU-") else "GPU-" + self.uuid)
+                except Exception:
+                    handle = None
+            if handle is None:
+                handle = nv.nvmlDeviceGetHandleByIndex(self.gpu_index)
+            self.stop_flag = threading.Event()
+            self.thread = threading.Thread(target=self._nvml_loop, args=(nv, handle), daemon=True)
+            self.thread.start()
+            return
+        except Exception:
+            self.thread = None
         try:
             fd, self.path = tempfile.mkstemp(suffix=".csv")
             os.close(fd)
@@ -64,6 +109,13 @@ class ClockSampler:
 
     def stop(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.thread is not None:
+            self.stop_flag.set()
+            self.thread.join(timeout=2)
+            if self.clocks:
+                out.update(sm_mhz=statistics.median(self.clocks), sm_max_mhz=max(self.maxes) if self.maxes else None,
+                           reasons=sorted(self.reasons), samples=len(self.clocks), source="nvml")
+            return out
         if self.proc is None:
             return out
         self.proc.terminate()
@@ -92,7 +144,7 @@ class ClockSampler:
             pass
         if clocks:
             out.update(sm_mhz=statistics.median(clocks), sm_max_mhz=max(maxes), reasons=sorted(reasons),
-                       samples=len(clocks))
+                       samples=len(clocks), source="nvidia-smi")
         return out
 
 
@@ -236,7 +288,7 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):
         model.forward(tok_dev, B, T)
     ctx.sync_check()
-    sampler = ClockSampler(local_rank)
+    sampler = ClockSampler(local_rank, uuid=str(getattr(torch.cuda.get_device_properties(local_rank), "uuid", "") or "") or None)
     barrier()
     if rank == 0:
         sampler.start()

@@ -73,12 +73,14 @@ int b200_ctx_create(b200_ctx** out, int device, void* stream) {
     ctx->num_sms = prop.multiProcessorCount;
     e = cudaMalloc(&ctx->d_status, 256);
     if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 256);
-    if (e != cudaSuccess) { delete ctx; return B200_ERR_CUDA; }
+    if (e == cudaSuccess) e = cudaHostAlloc(&ctx->h_status, sizeof(int), cudaHostAllocDefault);
+    if (e != cudaSuccess) { cudaFree(ctx->d_status); delete ctx; return B200_ERR_CUDA; }
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
     if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
         cudaFree(ctx->d_status);
+        cudaFreeHost(ctx->h_status);
         delete ctx;
         return B200_ERR_CUDA;
     }
@@ -92,6 +94,7 @@ int b200_ctx_destroy(b200_ctx* ctx) {
     if (!ctx) return B200_ERR_NULL;
     cudaSetDevice(ctx->device);
     cudaFree(ctx->d_status);
+    cudaFreeHost(ctx->h_status);
     delete ctx;
     return B200_OK;
 }
@@ -104,9 +107,10 @@ int b200_ctx_set_stream(b200_ctx* ctx, void* stream) {
 
 int b200_ctx_sync_check(b200_ctx* ctx) {
     if (!ctx) return B200_ERR_NULL;
+    // the status word rides behind the queued work: one wait for both
+    B200_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
-    int word = 0;
-    B200_CUDA(ctx, cudaMemcpy(&word, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost));
+    const int word = *ctx->h_status;
     if (word != 0) {
         // the whole area: a kernel that gave up may have left its work counters behind
         B200_CUDA(ctx, cudaMemset(ctx->d_status, 0, 256));

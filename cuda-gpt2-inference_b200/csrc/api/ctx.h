@@ -37,6 +37,7 @@ struct b200_ctx {
     int num_sms = 148;
     cudaStream_t stream = nullptr;
     int* d_status = nullptr;  // device word: first device-side error code of any kernel
+    int* h_status = nullptr;  // pinned host copy of that word, filled by b200_ctx_sync_check
     uint64_t launches = 0;
     bool pdl = true;  // launch with programmatic stream serialization (B200_PDL=0 turns it off)
     std::string last_error;
