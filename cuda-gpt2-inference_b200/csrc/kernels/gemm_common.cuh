@@ -42,13 +42,16 @@ __device__ __forceinline__ float argmax_dec(uint32_t k) {
 // 16-byte pieces over 32 rows per instruction, so each chunk goes through a swizzled
 // shared-memory buffer and comes back with 8 lanes covering 128 contiguous bytes of one row;
 // bias, tanh-GELU, residual add and TF32 rounding are applied on the way out.
+// Without a residual the chunk does not come back at all: bias / GELU / rounding are applied in
+// registers, the buffer is filled in the 128-byte-swizzled layout and one lane sends it off as
+// a 32 x 32 TMA store (which also clips at the edges of the matrix).
 //   tmem_acc : tensor-memory address of the accumulator (column offset included, lane 0)
 //   row0     : global row of accumulator lane q*32
 //   col0     : global column of accumulator column 0
 //   stage2   : this warp's two 4 KB staging buffers
 template <int BN>
-__device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, uint32_t tmem_acc, int q, int lane,
-                                                       int row0, int col0, uint8_t* stage2) {
+__device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, const CUtensorMap* tmap_out, uint32_t tmem_acc,
+                                                       int q, int lane, int row0, int col0, uint8_t* stage2) {
     const bool do_gelu = (args.flags & GEMM_GELU) != 0;
     const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
     const int sub_row = lane >> 3;  // 0..3: row within a group of four
@@ -65,6 +68,11 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, uin
     if (do_argmax && my_row < args.M) {
         best_key = args.argmax_keys[my_row];
         if (best_key != 0ull) best_v = argmax_dec((uint32_t)(best_key >> 32));
+    }
+    const bool via_tma = args.residual == nullptr;
+    if (via_tma) {  // the stores of the previous tile have left the staging buffers
+        if (lane == 0) tma_store_wait_read();
+        __syncwarp();
     }
 #pragma unroll 1
     for (int c = 0; c < BN / 32; ++c) {
@@ -89,6 +97,32 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, uin
             }
         }
         uint8_t* stage = stage2 + (c & 1) * 4096;
+        if (via_tma) {
+            const int cbase = col0 + c * 32;
+            if (c >= 2) {  // the store issued two chunks ago has read this buffer
+                if (lane == 0) tma_store_wait_read_but_one();
+                __syncwarp();
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                       __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
+                if (args.bias && cbase + 4 * j < args.N) {
+                    const float4 b4 = __ldg(reinterpret_cast<const float4*>(args.bias + cbase + 4 * j));
+                    v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                }
+                if (do_gelu) { v.x = gelu_tanh(v.x); v.y = gelu_tanh(v.y); v.z = gelu_tanh(v.z); v.w = gelu_tanh(v.w); }
+                if (do_round) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
+                *reinterpret_cast<float4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) = v;
+            }
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && cbase < args.N && row0 < args.M) {
+                tma_store_2d(tmap_out, cbase, row0, stage);
+                tma_store_commit();
+            }
+            continue;
+        }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
             *reinterpret_cast<uint4*>(stage + lane * 128 + ((j ^ (lane & 7)) << 4)) =

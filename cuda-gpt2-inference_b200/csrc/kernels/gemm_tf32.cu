@@ -66,6 +66,7 @@ __device__ __forceinline__ float tf32_dropped_part(float x) {
 template <int BN, bool X3>
 __global__ void __launch_bounds__(GemmCfg<BN, X3>::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                 const __grid_constant__ CUtensorMap tmap_out,
                  const GemmArgs args) {
     using Cfg = GemmCfg<BN, X3>;
     constexpr int STAGES = Cfg::STAGES;
@@ -106,6 +107,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_out);
     }
     if (warp == 1) {
         tmem_alloc(tmem_holder, Cfg::TMEM_COLS);
@@ -209,11 +211,12 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             const uint32_t acc_ph = (tile_iter >> 1) & 1;
             if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            gemm_drain_accumulator<BN>(args, tmem_base + acc * BN, q, lane, m_blk * BM + q * 32, n_blk * BN,
+            gemm_drain_accumulator<BN>(args, &tmap_out, tmem_base + acc * BN, q, lane, m_blk * BM + q * 32, n_blk * BN,
                                        smem_epi + q * 2 * 4096);
             tc_fence_before_sync();
             mbar_arrive(&tmem_empty_bar[acc]);
         }
+        if (lane == 0) tma_store_wait_all();  // the staging buffers must outlive the stores reading them
 #ifdef B200_GEMM_TIMING
         if (dbg_on && warp == 2 && lane == 0) dbg[4] = globaltimer_ns() - dbg_t0;
 #endif
@@ -271,7 +274,7 @@ inline long tile_cost(int bn, int num_kb) {
 }
 
 template <int BN, bool X3>
-int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& a) {
+int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, GemmArgs& a) {
     using Cfg = GemmCfg<BN, X3>;
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63]) {
@@ -280,7 +283,7 @@ int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Gemm
     }
     const int tiles = a.num_m_blocks * a.num_n_blocks;
     const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
-    cudaError_t le = launch_pdl(ctx, gemm_tf32_kernel<BN, X3>, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM, ta, tb, a);
+    cudaError_t le = launch_pdl(ctx, gemm_tf32_kernel<BN, X3>, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM, ta, tb, to, a);
     ctx->launches++;
     B200_CUDA(ctx, le);
     return B200_OK;
@@ -335,13 +338,16 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
     if (st != B200_OK) return st;
     st = b200_get_tensor_map(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)best_bn, BK);
     if (st != B200_OK) return st;
-    if (x3) return launch_one<128, true>(ctx, ta, tb, a);
+    CUtensorMap to;  // the output in 32 x 32 boxes, for the epilogue's TMA stores
+    st = b200_get_tensor_map(ctx, &to, out, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 32);
+    if (st != B200_OK) return st;
+    if (x3) return launch_one<128, true>(ctx, ta, tb, to, a);
     switch (best_bn) {
-        case 256: return launch_one<256, false>(ctx, ta, tb, a);
-        case 192: return launch_one<192, false>(ctx, ta, tb, a);
-        case 128: return launch_one<128, false>(ctx, ta, tb, a);
-        case 96:  return launch_one<96, false>(ctx, ta, tb, a);
-        default:  return launch_one<64, false>(ctx, ta, tb, a);
+        case 256: return launch_one<256, false>(ctx, ta, tb, to, a);
+        case 192: return launch_one<192, false>(ctx, ta, tb, to, a);
+        case 128: return launch_one<128, false>(ctx, ta, tb, to, a);
+        case 96:  return launch_one<96, false>(ctx, ta, tb, to, a);
+        default:  return launch_one<64, false>(ctx, ta, tb, to, a);
     }
 }
 

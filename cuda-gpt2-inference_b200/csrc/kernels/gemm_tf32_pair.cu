@@ -51,6 +51,7 @@ struct PairCfg {
 template <int BN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                      const __grid_constant__ CUtensorMap tmap_out,
                       const GemmArgs args) {
     using Cfg = PairCfg<BN>;
     constexpr int STAGES = Cfg::STAGES;
@@ -84,6 +85,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         fence_barrier_init();
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_out);
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_holder, Cfg::TMEM_COLS);
@@ -201,13 +203,14 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             const uint32_t acc_ph = (tile_iter >> 1) & 1;
             if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            gemm_drain_accumulator<BN>(args, tmem_base + acc * BN, q, lane,
+            gemm_drain_accumulator<BN>(args, &tmap_out, tmem_base + acc * BN, q, lane,
                                        m_blk * 2 * BM + (int)rank * BM + q * 32, n_blk * BN,
                                        smem_epi + q * 2 * 4096);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
         }
+        if (lane == 0) tma_store_wait_all();  // the staging buffers must outlive the stores reading them
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_EPILOGUE);
     }
 
@@ -229,7 +232,8 @@ inline long pair_tile_cost(int bn, int num_kb) {
 }
 
 template <int BN>
-int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, GemmArgs& a, int num_pairs_max) {
+int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, GemmArgs& a,
+                int num_pairs_max) {
     using Cfg = PairCfg<BN>;
     static int resident_pairs[64] = {};  // CTA pairs the device can keep resident at once
     cudaLaunchConfig_t cfg = {};
@@ -258,7 +262,7 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, Gem
     const int tiles = a.num_m_blocks * a.num_n_blocks;
     const int pairs = tiles < resident_pairs[ctx->device & 63] ? tiles : resident_pairs[ctx->device & 63];
     cfg.gridDim = dim3(2 * pairs);
-    B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tf32_pair_kernel<BN>, ta, tb, a));
+    B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tf32_pair_kernel<BN>, ta, tb, to, a));
     ctx->launches++;
     return B200_OK;
 }
@@ -303,11 +307,14 @@ int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const flo
     if (st != B200_OK) return st;
     st = b200_get_tensor_map(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(best_bn / 2), BK);
     if (st != B200_OK) return st;
+    CUtensorMap to;  // the output in 32 x 32 boxes, for the epilogue's TMA stores
+    st = b200_get_tensor_map(ctx, &to, out, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 32);
+    if (st != B200_OK) return st;
     switch (best_bn) {
-        case 256: return launch_pair<256>(ctx, ta, tb, a, num_pairs_max);
-        case 192: return launch_pair<192>(ctx, ta, tb, a, num_pairs_max);
-        case 128: return launch_pair<128>(ctx, ta, tb, a, num_pairs_max);
-        default:  return launch_pair<64>(ctx, ta, tb, a, num_pairs_max);
+        case 256: return launch_pair<256>(ctx, ta, tb, to, a, num_pairs_max);
+        case 192: return launch_pair<192>(ctx, ta, tb, to, a, num_pairs_max);
+        case 128: return launch_pair<128>(ctx, ta, tb, to, a, num_pairs_max);
+        default:  return launch_pair<64>(ctx, ta, tb, to, a, num_pairs_max);
     }
 }
 
