@@ -23,6 +23,8 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "lib", "libb200gpt2.so")
 
 B200_OK = 0
+(B200_ERR_NULL, B200_ERR_SHAPE, B200_ERR_ALIGN, B200_ERR_CUDA, B200_ERR_DEVICE, B200_ERR_TIMEOUT,
+ B200_ERR_STATE, B200_ERR_LIMIT) = range(1, 9)
 B200_TF32, B200_TF32X3 = 0, 1
 ACT_NONE, ACT_GELU = 0, 1
 
@@ -41,6 +43,7 @@ EXPORTS = (
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
     "b200_gpt2_forward_static",
+    "b200_gpt2_enable_kv_cache", "b200_gpt2_prefill", "b200_gpt2_decode_step", "b200_gpt2_decode_step_host",
     "b200_gpt2_create_tp", "b200_gpt2_set_allreduce", "b200_gpt2_param_offsets_tp", "b200_gpt2_shard_params_host",
 )
 
@@ -116,6 +119,10 @@ def lib() -> C.CDLL:
         l.b200_gpt2_set_profile.argtypes = [vp, i]
         l.b200_gpt2_read_profile.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_long)]
         l.b200_gpt2_forward_static.argtypes = [vp, vp, vp, vp, i, i, vp]
+        l.b200_gpt2_enable_kv_cache.argtypes = [vp]
+        l.b200_gpt2_prefill.argtypes = [vp, vp, i, i]
+        l.b200_gpt2_decode_step.argtypes = [vp, vp, i, i]
+        l.b200_gpt2_decode_step_host.argtypes = [vp, vp, i, i, vp, vp]
         l.b200_gpt2_create_tp.argtypes = [C.POINTER(vp), vp, vp, i, i, i, i]
         l.b200_gpt2_set_allreduce.argtypes = [vp, ALLREDUCE_FN, vp]
         l.b200_gpt2_param_offsets_tp.argtypes = [vp, i, i, C.POINTER(sz)]
@@ -369,6 +376,30 @@ class GPT2:
         """Host-buffer call: H2D of tokens, forward, D2H of what is asked for; synchronous."""
         self.ctx.check(lib().b200_gpt2_forward_host(self._h, _ptr(tokens_host), B, T, _ptr(logits_host),
                                                     _ptr(last_logits_host), _ptr(argmax_host)), "gpt2_forward_host")
+
+    # ---- incremental decoding with a key/value cache
+    def enable_kv_cache(self):
+        """Allocates keys and values of every layer for max_B sequences of max_T positions."""
+        self.ctx.check(lib().b200_gpt2_enable_kv_cache(self._h), "enable_kv_cache")
+
+    def prefill(self, tokens, B: int, T: int):
+        """forward() that also stores the keys and values of positions [0,T); logits [B,T,Vp]."""
+        import torch
+        self.ctx.check(lib().b200_gpt2_prefill(self._h, _ptr(tokens), B, T), "gpt2_prefill")
+        return _view_device(int(lib().b200_gpt2_logits(self._h)), (B, T, self.cfg.padded_vocab_size),
+                            torch.float32, self.ctx.device)
+
+    def decode_step(self, tokens, B: int, pos: int):
+        """tokens: CUDA int32 [B], standing at position pos.  Asynchronous; returns a view of the
+        logits of that position, [B,Vp]."""
+        import torch
+        self.ctx.check(lib().b200_gpt2_decode_step(self._h, _ptr(tokens), B, pos), "gpt2_decode_step")
+        return _view_device(int(lib().b200_gpt2_logits(self._h)), (B, self.cfg.padded_vocab_size),
+                            torch.float32, self.ctx.device)
+
+    def decode_step_host(self, tokens_host, B: int, pos: int, logits_host=None, argmax_host=None):
+        self.ctx.check(lib().b200_gpt2_decode_step_host(self._h, _ptr(tokens_host), B, pos, _ptr(logits_host),
+                                                        _ptr(argmax_host)), "gpt2_decode_step_host")
 
     def set_profile(self, enabled: bool):
         self.ctx.check(lib().b200_gpt2_set_profile(self._h, int(enabled)), "set_profile")

@@ -23,6 +23,7 @@ SOURCES = [
     "kernels/gemm_tf32_pair.cu",
     "kernels/attention.cu",
     "kernels/attention_x3.cu",
+    "kernels/decode.cu",
     "driver/gpt2.cu",
 ]
 

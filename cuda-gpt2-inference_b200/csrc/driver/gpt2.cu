@@ -29,6 +29,8 @@ struct b200_gpt2 {
     int* tokens = nullptr;
     int* argmax = nullptr;
     unsigned long long* argmax_keys = nullptr;  // per row: best (value, column) of the lm-head's fused arg-max
+    float *kcache = nullptr, *vcache = nullptr;  // [L][max_B][max_T][C] each (b200_gpt2_enable_kv_cache)
+    bool keep_kv = false;                        // the forward being enqueued also fills the cache
     int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
     // tensor parallelism (Megatron style): this rank's share of the attention heads, of the MLP
     // width and of the vocabulary; with tp_size == 1 these are the full dimensions
@@ -162,6 +164,11 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, bool with_arg
         const bool att_x3 = (m->gemm_mode == B200_TF32X3) && m->qkv_small;
         const int qkv_flags = (!att_x3 && (m->round_operands || m->gemm_mode == B200_TF32X3)) ? GEMM_ROUND_OUT_TF32 : 0;
         STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * A, qkv_flags, m->gemm_mode));
+        if (m->keep_kv) {
+            const size_t per_layer = (size_t)m->max_B * m->max_T * C;
+            st = launch_kv_append(ctx, m->kcache + l * per_layer, m->vcache + l * per_layer, m->qkv, B, T, C, 0, m->max_T);
+            if (st != B200_OK) return st;
+        }
         if (att_x3) STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->atty, m->qkv_small, nullptr, m->qkv, B, T, A, NH));
         else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, A, NH, rnd));
         STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, A, C, 0, m->gemm_mode));
@@ -313,7 +320,7 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
     void* ptrs[] = {m->params, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
-                    m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys};
+                    m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->kcache, m->vcache};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete m;
     return B200_OK;
@@ -414,6 +421,92 @@ int b200_gpt2_forward_host(b200_gpt2* m, const int* tokens_host, int B, int T, f
     }
     if (logits_host)
         B200_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, M * Vp * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return b200_ctx_sync_check(ctx);
+}
+
+int b200_gpt2_enable_kv_cache(b200_gpt2* m) {
+    if (!m) return B200_ERR_NULL;
+    if (m->tp_size > 1) return B200_ERR_STATE;
+    if (m->kcache) return B200_OK;
+    b200_ctx* ctx = m->ctx;
+    const size_t n = (size_t)m->cfg.num_layers * m->max_B * m->max_T * m->cfg.channels;
+    B200_CUDA(ctx, cudaSetDevice(ctx->device));
+    B200_CUDA(ctx, cudaMalloc(&m->kcache, n * sizeof(float)));
+    cudaError_t e = cudaMalloc(&m->vcache, n * sizeof(float));
+    if (e != cudaSuccess) {
+        cudaFree(m->kcache);
+        m->kcache = nullptr;
+        return b200_fail_cuda(ctx, e, "cudaMalloc (kv cache)");
+    }
+    return B200_OK;
+}
+
+int b200_gpt2_prefill(b200_gpt2* m, const int* tokens, int B, int T) {
+    if (!m || !tokens) return B200_ERR_NULL;
+    if (!m->kcache) return B200_ERR_STATE;
+    if (B <= 0 || B > m->max_B || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
+    if (m->round_operands) {
+        int st = round_weights_once(m);
+        if (st != B200_OK) return st;
+    }
+    m->keep_kv = true;  // eager (the replayed graphs are those of the plain forward)
+    const int st = enqueue_forward(m, tokens, B, T, false);
+    m->keep_kv = false;
+    return st;
+}
+
+// One token per sequence at position pos: the forward's operator sequence on B rows, with the
+// attention reading keys and values of positions 0..pos out of the cache.
+int b200_gpt2_decode_step(b200_gpt2* m, const int* tokens, int B, int pos) {
+    using namespace b200;
+    if (!m || !tokens) return B200_ERR_NULL;
+    if (!m->kcache) return B200_ERR_STATE;
+    if (B <= 0 || B > 16 || B > m->max_B || pos < 0 || pos >= m->max_T) return B200_ERR_SHAPE;
+    b200_ctx* ctx = m->ctx;
+    const b200_gpt2_config& c = m->cfg;
+    const int C = c.channels, L = c.num_layers, Vp = c.padded_vocab_size, NH = c.num_heads;
+    const float* P = m->params;
+    const size_t* off = m->off;
+    const size_t per_layer = (size_t)m->max_B * m->max_T * C;
+    int st;
+#define DSTEP(call) do { st = (call); if (st != B200_OK) return st; } while (0)
+    // position pos of wpe: the encoder adds wpe[t] with t = 0 for its single column
+    DSTEP(launch_encoder(ctx, m->residual, tokens, P + off[0], P + off[1] + (size_t)pos * C, B, 1, C, Vp));
+    DSTEP(launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], B, C, 0));
+    for (int l = 0; l < L; ++l) {
+        DSTEP(launch_skinny_gemm(ctx, m->qkv, m->ln_out, P + off[4] + (size_t)l * 3 * C * C, P + off[5] + (size_t)l * 3 * C, B, C, 3 * C, 0));
+        DSTEP(launch_kv_append(ctx, m->kcache + l * per_layer, m->vcache + l * per_layer, m->qkv, B, 1, C, pos, m->max_T));
+        DSTEP(launch_decode_attention(ctx, m->atty, m->qkv, m->kcache + l * per_layer, m->vcache + l * per_layer, B, C, NH, pos, m->max_T));
+        DSTEP(launch_skinny_gemm(ctx, m->branch, m->atty, P + off[6] + (size_t)l * C * C, P + off[7] + (size_t)l * C, B, C, C, 0));
+        DSTEP(launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual, m->branch,
+                                              P + off[8] + (size_t)l * C, P + off[9] + (size_t)l * C, B, C, 0));
+        DSTEP(launch_skinny_gemm(ctx, m->fch, m->ln_out, P + off[10] + (size_t)l * 4 * C * C, P + off[11] + (size_t)l * 4 * C, B, C, 4 * C, 1));
+        DSTEP(launch_skinny_gemm(ctx, m->branch, m->fch, P + off[12] + (size_t)l * C * 4 * C, P + off[13] + (size_t)l * C, B, 4 * C, C, 0));
+        const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
+        const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
+        DSTEP(launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual, m->branch, nw, nb, B, C, 0));
+    }
+    DSTEP(launch_skinny_gemm(ctx, m->logits, m->ln_out, P + off[0], nullptr, B, C, Vp, 0));
+#undef DSTEP
+    return B200_OK;
+}
+
+int b200_gpt2_decode_step_host(b200_gpt2* m, const int* tokens_host, int B, int pos, float* logits_host,
+                               int* argmax_host) {
+    if (!m || !tokens_host) return B200_ERR_NULL;
+    if (B <= 0 || B > 16 || B > m->max_B) return B200_ERR_SHAPE;
+    b200_ctx* ctx = m->ctx;
+    const size_t Vp = m->cfg.padded_vocab_size;
+    B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens_host, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
+    int st = b200_gpt2_decode_step(m, m->tokens, B, pos);
+    if (st != B200_OK) return st;
+    if (argmax_host) {
+        st = b200::launch_argmax_rows(ctx, m->argmax, m->logits, B, m->cfg.vocab_size, (int)Vp);
+        if (st != B200_OK) return st;
+        B200_CUDA(ctx, cudaMemcpyAsync(argmax_host, m->argmax, (size_t)B * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    if (logits_host)
+        B200_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, (size_t)B * Vp * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return b200_ctx_sync_check(ctx);
 }
 

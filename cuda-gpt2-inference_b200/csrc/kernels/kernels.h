@@ -33,6 +33,17 @@ int launch_argmax_decode(b200_ctx* ctx, int* out, const unsigned long long* keys
 int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, int B, int T, int C,
                      int NH, int flags);
 
+// incremental decoding (decode.cu): B <= 16 rows, fp32 FMA, no TF32 rounding
+// out[B,N] = act(x[B,K] * W[N,K]^T + bias[N])
+int launch_skinny_gemm(b200_ctx* ctx, float* out, const float* x, const float* W, const float* bias, int B,
+                       int K, int N, int gelu);
+// k and v columns of qkv rows [B*T, 3C] -> caches [B][cache_T][C] at positions pos0 .. pos0+T-1
+int launch_kv_append(b200_ctx* ctx, float* kcache, float* vcache, const float* qkv, int B, int T, int C, int pos0,
+                     int cache_T);
+// out[B,C]: attention of the query rows qkv[B,3C] over cached positions 0 .. pos
+int launch_decode_attention(b200_ctx* ctx, float* out, const float* qkv, const float* kcache, const float* vcache,
+                            int B, int C, int NH, int pos, int cache_T);
+
 // 3xTF32 attention: qkv_small is a scratch buffer shaped like qkv ([B,T,3C]) that receives the
 // dropped low parts of qkv; two kernel launches (split + attention)
 int launch_attention_x3(b200_ctx* ctx, float* out, float* qkv_small, float* lse, const float* qkv, int B,

@@ -201,6 +201,27 @@ float* b200_gpt2_logits(b200_gpt2* model);
  *   argmax_host      [B,T]     arg-max token over [0,V) per position (nullable) */
 int b200_gpt2_forward_host(b200_gpt2* model, const int* tokens_host, int B, int T,
                            float* logits_host, float* last_logits_host, int* argmax_host);
+/* ---- incremental decoding with a key/value cache (no counterpart in the reference, which has
+ * full-sequence kernels only; the operators and their order are those of the forward above) ----
+ * b200_gpt2_enable_kv_cache allocates the cache: keys and values of every layer for max_B
+ * sequences of max_T positions, fp32, [L][max_B][max_T][C] each (2 x 302 MB for GPT-2 124M at
+ * max_B = 8, max_T = 1024).  Not available on a tensor-parallel model.
+ * b200_gpt2_prefill is b200_gpt2_forward that also stores the keys and values of positions
+ * [0,T) (T % 64 == 0 as for the forward); logits as for b200_gpt2_forward.
+ * b200_gpt2_decode_step takes one token per sequence (device int32 [B], B <= 16) standing at
+ * position pos (0 <= pos < max_T; positions [0,pos) must be in the cache, from a prefill or
+ * from earlier steps), appends its keys and values and leaves the logits of that position in
+ * the first B rows of the model's logits buffer ([B,Vp]).  A step reads every weight and the
+ * used part of the cache once, so it is bound by HBM bandwidth; it runs on the fp32 FMA pipe
+ * (no TF32 rounding anywhere).  Starting at pos = 0 with an empty cache is allowed.
+ * b200_gpt2_decode_step_host: tokens from the host, logits [B,Vp] and / or arg-max ids [B] back;
+ * synchronises.  All calls are asynchronous on the context's stream unless stated. */
+int b200_gpt2_enable_kv_cache(b200_gpt2* model);
+int b200_gpt2_prefill(b200_gpt2* model, const int* tokens, int B, int T);
+int b200_gpt2_decode_step(b200_gpt2* model, const int* tokens, int B, int pos);
+int b200_gpt2_decode_step_host(b200_gpt2* model, const int* tokens_host, int B, int pos,
+                               float* logits_host, int* argmax_host);
+
 /* ---- tensor parallelism (optional; Megatron style, for models like GPT-2 XL) --------------
  * Rank r of tp_size holds the q/k/v rows and attn-proj input columns of its share of the heads
  * (NH/tp_size each, the first NH % tp_size ranks one more), 1/tp_size of the MLP hidden width,
