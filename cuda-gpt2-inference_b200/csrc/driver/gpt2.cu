@@ -31,6 +31,9 @@ struct b200_gpt2 {
     unsigned long long* argmax_keys = nullptr;  // per row: best (value, column) of the lm-head's fused arg-max
     float *kcache = nullptr, *vcache = nullptr;  // [L][max_B][max_T][C] each (b200_gpt2_enable_kv_cache)
     bool keep_kv = false;                        // the forward being enqueued also fills the cache
+    int* pos_dev = nullptr;                      // position of the decode step being run
+    float* resid2 = nullptr;                     // second residual buffer of the decode step [16][C]
+    std::map<int, cudaGraphExec_t> decode_graphs;  // by B (the position is read from pos_dev)
     int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
     // tensor parallelism (Megatron style): this rank's share of the attention heads, of the MLP
     // width and of the vocabulary; with tp_size == 1 these are the full dimensions
@@ -318,6 +321,9 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     if (!m) return B200_ERR_NULL;
     cudaSetDevice(m->ctx->device);
     for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+    for (auto& g : m->decode_graphs) cudaGraphExecDestroy(g.second);
+    if (m->pos_dev) cudaFree(m->pos_dev);
+    if (m->resid2) cudaFree(m->resid2);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
     void* ptrs[] = {m->params, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
                     m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->kcache, m->vcache};
@@ -433,9 +439,12 @@ int b200_gpt2_enable_kv_cache(b200_gpt2* m) {
     B200_CUDA(ctx, cudaSetDevice(ctx->device));
     B200_CUDA(ctx, cudaMalloc(&m->kcache, n * sizeof(float)));
     cudaError_t e = cudaMalloc(&m->vcache, n * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&m->pos_dev, sizeof(int));
+    if (e == cudaSuccess) e = cudaMalloc(&m->resid2, (size_t)16 * m->cfg.channels * sizeof(float));
     if (e != cudaSuccess) {
         cudaFree(m->kcache);
-        m->kcache = nullptr;
+        if (m->vcache) cudaFree(m->vcache);
+        m->kcache = m->vcache = nullptr;
         return b200_fail_cuda(ctx, e, "cudaMalloc (kv cache)");
     }
     return B200_OK;
@@ -455,13 +464,10 @@ int b200_gpt2_prefill(b200_gpt2* m, const int* tokens, int B, int T) {
     return st;
 }
 
-// One token per sequence at position pos: the forward's operator sequence on B rows, with the
-// attention reading keys and values of positions 0..pos out of the cache.
-int b200_gpt2_decode_step(b200_gpt2* m, const int* tokens, int B, int pos) {
+// One token per sequence: the forward's operator sequence on B rows, with the attention reading
+// keys and values of positions 0..pos out of the cache.  The position comes from m->pos_dev.
+static int enqueue_decode(b200_gpt2* m, const int* tokens, int B) {
     using namespace b200;
-    if (!m || !tokens) return B200_ERR_NULL;
-    if (!m->kcache) return B200_ERR_STATE;
-    if (B <= 0 || B > 16 || B > m->max_B || pos < 0 || pos >= m->max_T) return B200_ERR_SHAPE;
     b200_ctx* ctx = m->ctx;
     const b200_gpt2_config& c = m->cfg;
     const int C = c.channels, L = c.num_layers, Vp = c.padded_vocab_size, NH = c.num_heads;
@@ -470,24 +476,87 @@ int b200_gpt2_decode_step(b200_gpt2* m, const int* tokens, int B, int pos) {
     const size_t per_layer = (size_t)m->max_B * m->max_T * C;
     int st;
 #define DSTEP(call) do { st = (call); if (st != B200_OK) return st; } while (0)
-    // position pos of wpe: the encoder adds wpe[t] with t = 0 for its single column
-    DSTEP(launch_encoder(ctx, m->residual, tokens, P + off[0], P + off[1] + (size_t)pos * C, B, 1, C, Vp));
-    DSTEP(launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], B, C, 0));
+    // The residual stream alternates between two buffers: every GEMM that follows a layernorm
+    // forms "residual + branch" and its layernorm itself (all of its CTAs, each for itself) and
+    // one of them stores the new residual - into the other buffer, because the old one is still
+    // being read.  C above the prologue's limit: the separate kernels, as in the full forward.
+    float* ra = m->residual;
+    float* rb = m->resid2;
+    const bool fuse_ln = C <= 1664;
+    DSTEP(launch_decode_encoder(ctx, ra, tokens, P + off[0], P + off[1], m->pos_dev, B, C, Vp));
+    const float* branch = nullptr;  // what the next layernorm adds to the residual first
     for (int l = 0; l < L; ++l) {
-        DSTEP(launch_skinny_gemm(ctx, m->qkv, m->ln_out, P + off[4] + (size_t)l * 3 * C * C, P + off[5] + (size_t)l * 3 * C, B, C, 3 * C, 0));
-        DSTEP(launch_kv_append(ctx, m->kcache + l * per_layer, m->vcache + l * per_layer, m->qkv, B, 1, C, pos, m->max_T));
-        DSTEP(launch_decode_attention(ctx, m->atty, m->qkv, m->kcache + l * per_layer, m->vcache + l * per_layer, B, C, NH, pos, m->max_T));
+        const float* qkvw = P + off[4] + (size_t)l * 3 * C * C;
+        const float* qkvb = P + off[5] + (size_t)l * 3 * C;
+        const float *ln1w = P + off[2] + (size_t)l * C, *ln1b = P + off[3] + (size_t)l * C;
+        const float *ln2w = P + off[8] + (size_t)l * C, *ln2b = P + off[9] + (size_t)l * C;
+        if (fuse_ln) {
+            DSTEP(launch_skinny_gemm(ctx, m->qkv, ra, qkvw, qkvb, B, C, 3 * C, 0, branch, ln1w, ln1b, rb));
+            std::swap(ra, rb);
+        } else {
+            if (branch) {
+                DSTEP(launch_fused_residual_layernorm(ctx, rb, m->ln_out, nullptr, nullptr, ra, branch, ln1w, ln1b, B, C, 0));
+                std::swap(ra, rb);
+            } else {
+                DSTEP(launch_layernorm(ctx, m->ln_out, nullptr, nullptr, ra, ln1w, ln1b, B, C, 0));
+            }
+            DSTEP(launch_skinny_gemm(ctx, m->qkv, m->ln_out, qkvw, qkvb, B, C, 3 * C, 0));
+        }
+        DSTEP(launch_decode_attention(ctx, m->atty, m->qkv, m->kcache + l * per_layer, m->vcache + l * per_layer, B, C, NH, m->pos_dev, m->max_T));
         DSTEP(launch_skinny_gemm(ctx, m->branch, m->atty, P + off[6] + (size_t)l * C * C, P + off[7] + (size_t)l * C, B, C, C, 0));
-        DSTEP(launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual, m->branch,
-                                              P + off[8] + (size_t)l * C, P + off[9] + (size_t)l * C, B, C, 0));
-        DSTEP(launch_skinny_gemm(ctx, m->fch, m->ln_out, P + off[10] + (size_t)l * 4 * C * C, P + off[11] + (size_t)l * 4 * C, B, C, 4 * C, 1));
+        const float* fcw = P + off[10] + (size_t)l * 4 * C * C;
+        const float* fcb = P + off[11] + (size_t)l * 4 * C;
+        if (fuse_ln) {
+            DSTEP(launch_skinny_gemm(ctx, m->fch, ra, fcw, fcb, B, C, 4 * C, 1, m->branch, ln2w, ln2b, rb));
+        } else {
+            DSTEP(launch_fused_residual_layernorm(ctx, rb, m->ln_out, nullptr, nullptr, ra, m->branch, ln2w, ln2b, B, C, 0));
+            DSTEP(launch_skinny_gemm(ctx, m->fch, m->ln_out, fcw, fcb, B, C, 4 * C, 1));
+        }
+        std::swap(ra, rb);
         DSTEP(launch_skinny_gemm(ctx, m->branch, m->fch, P + off[12] + (size_t)l * C * 4 * C, P + off[13] + (size_t)l * C, B, 4 * C, C, 0));
-        const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
-        const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
-        DSTEP(launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual, m->branch, nw, nb, B, C, 0));
+        branch = m->branch;
     }
+    // final layernorm, then the lm-head (wide: the streamed kernel, which takes plain input rows)
+    DSTEP(launch_fused_residual_layernorm(ctx, rb, m->ln_out, nullptr, nullptr, ra, branch, P + off[14], P + off[15], B, C, 0));
     DSTEP(launch_skinny_gemm(ctx, m->logits, m->ln_out, P + off[0], nullptr, B, C, Vp, 0));
 #undef DSTEP
+    return B200_OK;
+}
+
+int b200_gpt2_decode_step(b200_gpt2* m, const int* tokens, int B, int pos) {
+    if (!m || !tokens) return B200_ERR_NULL;
+    if (!m->kcache) return B200_ERR_STATE;
+    if (B <= 0 || B > 16 || B > m->max_B || pos < 0 || pos >= m->max_T) return B200_ERR_SHAPE;
+    b200_ctx* ctx = m->ctx;
+    int st = b200::launch_set_int(ctx, m->pos_dev, pos);
+    if (st != B200_OK) return st;
+    if (!m->use_graph || ctx->stream == nullptr) return enqueue_decode(m, tokens, B);
+
+    // CUDA-graph replay (one graph per B; the position is data): the graph reads the token ids
+    // from the model's own token buffer
+    if (tokens != m->tokens)
+        B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens, (size_t)B * 4, cudaMemcpyDeviceToDevice, ctx->stream));
+    auto it = m->decode_graphs.find(B);
+    if (it == m->decode_graphs.end()) {
+        st = enqueue_decode(m, m->tokens, B);  // function attributes are set outside of capture; the step is idempotent
+        if (st != B200_OK) return st;
+        B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        cudaGraph_t graph = nullptr;
+        const uint64_t launches_before = ctx->launches;
+        B200_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
+        st = enqueue_decode(m, m->tokens, B);
+        cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
+        ctx->launches = launches_before;
+        if (st != B200_OK) { if (graph) cudaGraphDestroy(graph); return st; }
+        if (e != cudaSuccess) return b200_fail_cuda(ctx, e, "cudaStreamEndCapture");
+        cudaGraphExec_t exec = nullptr;
+        e = cudaGraphInstantiate(&exec, graph, 0);
+        cudaGraphDestroy(graph);
+        if (e != cudaSuccess) return b200_fail_cuda(ctx, e, "cudaGraphInstantiate");
+        it = m->decode_graphs.emplace(B, exec).first;
+    }
+    B200_CUDA(ctx, cudaGraphLaunch(it->second, ctx->stream));
+    ctx->launches += 3 + (m->cfg.channels <= 1664 ? 5ull : 7ull) * m->cfg.num_layers;  // set_int is counted by its launcher
     return B200_OK;
 }
 

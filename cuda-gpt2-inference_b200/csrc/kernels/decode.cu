@@ -8,9 +8,12 @@
 // (exact fp32 products, no TF32 rounding) and are organised around coalesced streaming:
 //   skinny_gemm_kernel      out[b,n] = act(sum_k x[b,k] W[n,k] + bias[n]); a warp streams ROWS rows
 //                           of W, 128 floats per step, against x staged in shared memory
-//   kv_append_kernel        K and V columns of freshly computed qkv rows -> cache
-//   decode_attention_kernel one CTA per (sequence, head): half-warps walk the cached positions
-//                           with an online softmax, states are merged through shared memory
+//   kv_append_kernel        K and V columns of freshly computed qkv rows -> cache (prefill)
+//   decode_attention_kernel one CTA per (sequence, head): stores the new position's K and V,
+//                           then half-warps walk the cached positions with an online softmax
+//                           and the states are merged through shared memory
+//   decode_encoder_kernel   wte[token] + wpe[pos]
+// The position is read from device memory, so one captured CUDA graph serves every step.
 #include "kernels.h"
 #include "../prim/sm100.cuh"
 
@@ -20,59 +23,177 @@ namespace {
 
 constexpr int kSkinnyThreads = 256;
 constexpr int kSkinnyKC = 1024;  // floats of K staged per pass (x chunk: NB * 4 KB of shared memory)
+constexpr int kSkinnySteps = kSkinnyKC / 128;  // a warp covers 128 floats of a row per step
+
+// Optional prologue (ln_w != nullptr): the input rows are first formed as
+//   r = resid_in + branch (branch may be null),  x = layernorm(r) * ln_w + ln_b
+// by every CTA for itself (B rows of C = K floats: a few KB), and CTA 0 also stores r to
+// resid_out - a different buffer than resid_in, which other CTAs are still reading.  That is the
+// forward's fused residual + layernorm (two-pass variance, eps 1e-5) without a kernel of its own.
+struct SkinnyArgs {
+    float* out;
+    const float* x;         // [B,K] input rows, or resid_in when the prologue is on
+    const float* W;
+    const float* bias;
+    const float* branch;    // prologue: added to x before the layernorm (nullable)
+    const float* ln_w;      // prologue switch
+    const float* ln_b;
+    float* resid_out;       // prologue: r is stored here by CTA 0
+    int B, N, K, gelu;
+};
 
 template <int NB, int ROWS>
 __global__ void __launch_bounds__(kSkinnyThreads)
-skinny_gemm_kernel(float* __restrict__ out, const float* __restrict__ x, const float* __restrict__ W,
-                   const float* __restrict__ bias, int B, int N, int K, int gelu) {
-    extern __shared__ float4 xs4[];  // [NB][kSkinnyKC / 4]
-    griddep_wait();
-    griddep_launch_dependents();
+skinny_gemm_kernel(const SkinnyArgs a) {
+    extern __shared__ float4 xs4[];  // [NB][K / 4]: the input rows, staged once
+    const int B = a.B, N = a.N, K = a.K, K4 = a.K >> 2;
+    const float* __restrict__ W = a.W;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     constexpr int kWarps = kSkinnyThreads / 32;
     const int groups = (N + ROWS - 1) / ROWS;                  // row groups, one per warp at a time
     const int batches = (groups + kWarps - 1) / kWarps;        // a CTA takes kWarps groups at a time
+    // The kernel is a chain of memory round trips (each several hundred to two thousand cycles),
+    // so everything that does not depend on the previous kernel is requested before waiting for
+    // it: the first chunk of this warp's weight rows, the bias, the layernorm parameters.
+    float4 w[kSkinnySteps][ROWS];
+    auto request_w = [&](int n0, int kc0) {
+        const int kc = min(kSkinnyKC, K - kc0);
+#pragma unroll
+        for (int s = 0; s < kSkinnySteps; ++s) {
+            const int k4 = s * 32 + lane;  // float4 index inside the chunk
+#pragma unroll
+            for (int r = 0; r < ROWS; ++r)
+                w[s][r] = (n0 < N && k4 * 4 < kc)
+                              ? __ldg(reinterpret_cast<const float4*>(W + (size_t)min(n0 + r, N - 1) * K + kc0) + k4)
+                              : make_float4(0.f, 0.f, 0.f, 0.f);  // rows clamped: masked at the store
+        }
+    };
+    request_w((blockIdx.x * kWarps + warp) * ROWS, 0);
+    constexpr int kMaxV = 13;  // layernorm prologue: K <= 1664
+    float4* lnw4 = xs4 + NB * K4;  // layernorm weight and bias, behind the input rows
+    float4* lnb4 = lnw4 + K4;
+    if (a.ln_w) {
+        for (int c = threadIdx.x; c < K4; c += kSkinnyThreads) {
+            lnw4[c] = __ldg(reinterpret_cast<const float4*>(a.ln_w) + c);
+            lnb4[c] = __ldg(reinterpret_cast<const float4*>(a.ln_b) + c);
+        }
+    }
+    griddep_wait();
+    griddep_launch_dependents();
+    if (a.ln_w) {
+        __syncthreads();
+        // one warp per row; a lane holds float4 number lane, lane + 32, ... of the row
+        for (int b = warp; b < NB; b += kWarps) {
+            float4 v[kMaxV];
+#pragma unroll
+            for (int i = 0; i < kMaxV; ++i) {
+                const int c = lane + i * 32;
+                v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (b < B && c < K4) {
+                    v[i] = *reinterpret_cast<const float4*>(a.x + (size_t)b * K + c * 4);
+                    if (a.branch) {
+                        const float4 t = *reinterpret_cast<const float4*>(a.branch + (size_t)b * K + c * 4);
+                        v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
+                    }
+                }
+            }
+            if (blockIdx.x == 0 && b < B) {
+#pragma unroll
+                for (int i = 0; i < kMaxV; ++i) {
+                    const int c = lane + i * 32;
+                    if (c < K4) *reinterpret_cast<float4*>(a.resid_out + (size_t)b * K + c * 4) = v[i];
+                }
+            }
+            float s = 0.f;
+#pragma unroll
+            for (int i = 0; i < kMaxV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+            const float mean = s / (float)K;
+            float q = 0.f;
+#pragma unroll
+            for (int i = 0; i < kMaxV; ++i) {
+                if (lane + i * 32 < K4) {
+                    const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
+                    q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+                }
+            }
+#pragma unroll
+            for (int d = 16; d >= 1; d >>= 1) q += __shfl_xor_sync(0xffffffffu, q, d);
+            const float rstd = rsqrtf(q / (float)K + 1e-5f);
+#pragma unroll
+            for (int i = 0; i < kMaxV; ++i) {
+                const int c = lane + i * 32;
+                if (c < K4) {
+                    float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
+                    if (b < B) {
+                        const float4 lw = lnw4[c], lb = lnb4[c];
+                        y.x = (v[i].x - mean) * rstd * lw.x + lb.x;
+                        y.y = (v[i].y - mean) * rstd * lw.y + lb.y;
+                        y.z = (v[i].z - mean) * rstd * lw.z + lb.z;
+                        y.w = (v[i].w - mean) * rstd * lw.w + lb.w;
+                    }
+                    xs4[b * K4 + c] = y;
+                }
+            }
+        }
+    } else {
+        // eight independent loads per thread in flight at a time
+        const int total = NB * K4;
+        for (int i0 = threadIdx.x; i0 < total; i0 += 8 * kSkinnyThreads) {
+            float4 v[8];
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * kSkinnyThreads;
+                v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (i < B * K4) v[u] = *(reinterpret_cast<const float4*>(a.x) + i);  // rows are contiguous: [B][K]
+            }
+#pragma unroll
+            for (int u = 0; u < 8; ++u) {
+                const int i = i0 + u * kSkinnyThreads;
+                if (i < total) xs4[i] = v[u];
+            }
+        }
+    }
+    __syncthreads();
     for (int batch = blockIdx.x; batch < batches; batch += gridDim.x) {
         const int n0 = (batch * kWarps + warp) * ROWS;
+        float bias_r[ROWS];
+#pragma unroll
+        for (int r = 0; r < ROWS; ++r) bias_r[r] = (a.bias && n0 + r < N) ? __ldg(a.bias + n0 + r) : 0.f;
         float acc[ROWS][NB];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
 #pragma unroll
             for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
-        const float* wrow[ROWS];
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) wrow[r] = W + (size_t)min(n0 + r, N - 1) * K;  // clamped: masked at the store
-
         for (int kc0 = 0; kc0 < K; kc0 += kSkinnyKC) {
             const int kc = min(kSkinnyKC, K - kc0);  // multiple of 4
-            __syncthreads();                         // the previous chunk is no longer read
-            for (int i = threadIdx.x; i < NB * (kSkinnyKC / 4); i += kSkinnyThreads) {
-                const int b = i / (kSkinnyKC / 4), k4 = i % (kSkinnyKC / 4);
-                float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (b < B && k4 * 4 < kc) v = *reinterpret_cast<const float4*>(x + (size_t)b * K + kc0 + k4 * 4);
-                xs4[i] = v;
-            }
-            __syncthreads();
+            // the chunk was requested earlier (before the kernel's wait, or at the end of the
+            // previous chunk); take it over and request the next one before using it
+            float4 wc[kSkinnySteps][ROWS];
+#pragma unroll
+            for (int s = 0; s < kSkinnySteps; ++s)
+#pragma unroll
+                for (int r = 0; r < ROWS; ++r) wc[s][r] = w[s][r];
+            if (kc0 + kSkinnyKC < K) request_w(n0, kc0 + kSkinnyKC);
+            else if (batch + (int)gridDim.x < batches) request_w(((batch + gridDim.x) * kWarps + warp) * ROWS, 0);
             if (n0 < N) {
-                const int steps = (kc + 127) / 128;
-#pragma unroll 2
-                for (int s = 0; s < steps; ++s) {
-                    const int k4 = s * 32 + lane;  // float4 index inside the chunk
-                    float4 w[ROWS];
 #pragma unroll
-                    for (int r = 0; r < ROWS; ++r)
-                        w[r] = (k4 * 4 < kc) ? __ldg(reinterpret_cast<const float4*>(wrow[r] + kc0) + k4)
-                                             : make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int s = 0; s < kSkinnySteps; ++s) {
+                    const int k4 = s * 32 + lane;
+                    if (k4 * 4 < kc) {
 #pragma unroll
-                    for (int b = 0; b < NB; ++b) {
-                        const float4 xv = xs4[b * (kSkinnyKC / 4) + k4];
+                        for (int b = 0; b < NB; ++b) {
+                            const float4 xv = xs4[b * K4 + (kc0 >> 2) + k4];
 #pragma unroll
-                        for (int r = 0; r < ROWS; ++r)
-                            acc[r][b] += (w[r].x * xv.x + w[r].y * xv.y) + (w[r].z * xv.z + w[r].w * xv.w);
+                            for (int r = 0; r < ROWS; ++r)
+                                acc[r][b] += (wc[s][r].x * xv.x + wc[s][r].y * xv.y) + (wc[s][r].z * xv.z + wc[s][r].w * xv.w);
+                        }
                     }
                 }
             }
         }
+        if (n0 >= N) continue;
         // sum over the 32 lanes; afterwards every lane holds every total
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
@@ -89,11 +210,144 @@ skinny_gemm_kernel(float* __restrict__ out, const float* __restrict__ x, const f
 #pragma unroll
             for (int b = 0; b < NB; ++b) {
                 if (((r * NB + b) & 31) == lane && n0 + r < N && b < B) {
-                    float v = acc[r][b] + (bias ? __ldg(bias + n0 + r) : 0.f);
-                    if (gelu) v = gelu_tanh(v);
-                    out[(size_t)b * N + n0 + r] = v;
+                    float v = acc[r][b] + bias_r[r];
+                    if (a.gelu) v = gelu_tanh(v);
+                    a.out[(size_t)b * N + n0 + r] = v;
                 }
             }
+    }
+}
+
+// The same product with the weights streamed through shared memory by bulk copies: the kernel is
+// bound by HBM bandwidth, which wants on the order of 100 KB in flight per SM - more than
+// registers can hold.  Persistent CTAs; warp 0 is the producer: for every work item (RT
+// consecutive rows of W, all of K in chunks of KCH floats) it issues one bulk copy per row
+// segment into a ring of stages, completion on an mbarrier; eight consumer warps own RT/8 rows
+// each and multiply out of shared memory against x, which is staged once (whole, NB x K).
+constexpr int kStreamThreads = 288;  // producer warp + 8 consumer warps
+constexpr int kStreamStages = 2;
+
+struct StreamArgs {
+    float* out;
+    const float* x;
+    const float* W;
+    const float* bias;
+    int B, N, K;
+    int RT;         // rows per work item (8, 16 or 32)
+    int KCH;        // floats of K per stage (multiple of 128, or K itself when K <= KCH)
+    int num_items;  // ceil(N / RT)
+    int gelu;
+    int* status;
+};
+
+template <int NB, int RPW>  // RPW = RT / 8 rows per consumer warp
+__global__ void __launch_bounds__(kStreamThreads, 1)
+skinny_stream_kernel(const StreamArgs a) {
+    extern __shared__ uint8_t dsm_raw[];
+    uint8_t* dsm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dsm_raw) + 127) & ~uintptr_t(127));
+    const int stage_bytes = a.RT * a.KCH * 4;
+    float* xs = reinterpret_cast<float*>(dsm);                        // [NB][K]
+    uint8_t* ring = dsm + (((size_t)NB * a.K * 4 + 127) & ~(size_t)127);  // [stages][RT][KCH]
+    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)kStreamStages * stage_bytes);
+    uint64_t* full_bar = bars;                      // [stages] bulk copies landed
+    uint64_t* empty_bar = bars + kStreamStages;     // [stages] the eight consumer warps are done
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStreamStages);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStreamStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 8); }
+        *abort_flag = 0;
+        fence_barrier_init();
+    }
+    griddep_wait();
+    // x, zero-padded to NB rows
+    for (int i = threadIdx.x; i < NB * (a.K / 4); i += kStreamThreads) {
+        const int b = i / (a.K / 4), k4 = i % (a.K / 4);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (b < a.B) v = *reinterpret_cast<const float4*>(a.x + (size_t)b * a.K + k4 * 4);
+        reinterpret_cast<float4*>(xs)[i] = v;
+    }
+    __syncthreads();
+    griddep_launch_dependents();
+    const int kchunks = (a.K + a.KCH - 1) / a.KCH;
+    if (warp == 0) {
+        if (lane == 0) {
+            bool ok = true;
+            uint32_t it = 0;
+            for (int item = blockIdx.x; item < a.num_items && ok; item += gridDim.x) {
+                const int n0 = item * a.RT;
+                const int rows = min(a.RT, a.N - n0);
+                for (int c = 0; c < kchunks; ++c, ++it) {
+                    const int s = it % kStreamStages;
+                    if (!mbar_wait(&empty_bar[s], ((it / kStreamStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    const int kc0 = c * a.KCH, kc = min(a.KCH, a.K - kc0);
+                    mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(rows * kc * 4));
+                    uint8_t* dst = ring + (size_t)s * stage_bytes;
+                    if (kc == a.K) {  // whole rows: they are contiguous in memory
+                        bulk_load_1d(dst, a.W + (size_t)n0 * a.K, (uint32_t)(rows * kc * 4), &full_bar[s]);
+                    } else {
+                        for (int r = 0; r < rows; ++r)
+                            bulk_load_1d(dst + (size_t)r * a.KCH * 4, a.W + (size_t)(n0 + r) * a.K + kc0, (uint32_t)(kc * 4), &full_bar[s]);
+                    }
+                }
+            }
+            if (!ok) atomicCAS(a.status, 0, DEV_TIMEOUT_PRODUCER);
+        }
+    } else {
+        const int cw = warp - 1;  // consumer warp: rows cw*RPW .. of every item
+        bool ok = true;
+        uint32_t it = 0;
+        for (int item = blockIdx.x; item < a.num_items; item += gridDim.x) {
+            const int n0 = item * a.RT + cw * RPW;
+            float acc[RPW][NB];
+#pragma unroll
+            for (int r = 0; r < RPW; ++r)
+#pragma unroll
+                for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
+            for (int c = 0; c < kchunks; ++c, ++it) {
+                const int s = it % kStreamStages;
+                if (ok && !mbar_wait(&full_bar[s], (it / kStreamStages) & 1, abort_flag)) ok = false;
+                const int kc0 = c * a.KCH, kc = min(a.KCH, a.K - kc0);
+                // row stride inside the stage: KCH floats, or K when whole rows were copied
+                const int ld = (kc == a.K) ? a.K : a.KCH;
+                const float* wt = reinterpret_cast<const float*>(ring + (size_t)s * stage_bytes) + (size_t)(cw * RPW) * ld;
+                if (ok && n0 < a.N) {
+                    for (int k = lane * 4; k < kc; k += 128) {
+                        float4 w[RPW];
+#pragma unroll
+                        for (int r = 0; r < RPW; ++r) w[r] = *reinterpret_cast<const float4*>(wt + (size_t)r * ld + k);
+#pragma unroll
+                        for (int b = 0; b < NB; ++b) {
+                            const float4 xv = *reinterpret_cast<const float4*>(xs + (size_t)b * a.K + kc0 + k);
+#pragma unroll
+                            for (int r = 0; r < RPW; ++r)
+                                acc[r][b] += (w[r].x * xv.x + w[r].y * xv.y) + (w[r].z * xv.z + w[r].w * xv.w);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&empty_bar[s]);
+            }
+#pragma unroll
+            for (int r = 0; r < RPW; ++r)
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    float v = acc[r][b];
+#pragma unroll
+                    for (int sft = 16; sft >= 1; sft >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sft);
+                    acc[r][b] = v;
+                }
+#pragma unroll
+            for (int r = 0; r < RPW; ++r)
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    if (((r * NB + b) & 31) == lane && n0 + r < a.N && n0 + r < item * a.RT + a.RT && b < a.B && ok) {
+                        float v = acc[r][b] + (a.bias ? __ldg(a.bias + n0 + r) : 0.f);
+                        if (a.gelu) v = gelu_tanh(v);
+                        a.out[(size_t)b * a.N + n0 + r] = v;
+                    }
+                }
+        }
+        if (!ok && lane == 0) atomicCAS(a.status, 0, DEV_TIMEOUT_EPILOGUE);
     }
 }
 
@@ -117,13 +371,23 @@ constexpr int kDecAttThreads = 256;
 
 // q: row b of qkv [B, 3C] (first C columns); caches [B][cache_T][C]; positions 0..pos take part
 __global__ void __launch_bounds__(kDecAttThreads)
-decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, const float* __restrict__ kcache,
-                        const float* __restrict__ vcache, int C, int pos, int cache_T) {
+decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, float* kcache, float* vcache, int C,
+                        const int* __restrict__ pos_ptr, int cache_T) {
     __shared__ float st_m[16], st_l[16];
     __shared__ float st_o[16][64];
     griddep_wait();
     griddep_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y;
+    const int pos = *pos_ptr;
+    // this head's slice of the new position goes into the cache first (ordinary loads below: the
+    // read-only path need not see stores of the same kernel)
+    if (threadIdx.x < 32) {
+        const int which = threadIdx.x >> 4, c = (threadIdx.x & 15) * 4;
+        float* cache = which ? vcache : kcache;
+        *reinterpret_cast<float4*>(cache + ((size_t)b * cache_T + pos) * C + h * 64 + c) =
+            *reinterpret_cast<const float4*>(qkv + (size_t)b * 3 * C + (1 + which) * C + h * 64 + c);
+    }
+    __syncthreads();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int half = lane >> 4, hl = lane & 15;  // a half-warp covers the 64 floats of one cached row
     const int slot = warp * 2 + half;            // 16 half-warps walk positions slot, slot + 16, ...
@@ -136,24 +400,32 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     // every half-warp makes the same number of trips so that the shuffles stay warp-wide
     const int trips = (pos + 16) / 16;
-    for (int i = 0; i < trips; ++i) {
-        const int t = i * 16 + slot;
-        const bool live = t <= pos;
-        float4 k4 = make_float4(0.f, 0.f, 0.f, 0.f), v4 = k4;
-        if (live) {
-            k4 = __ldg(reinterpret_cast<const float4*>(kbase + (size_t)t * C));
-            v4 = __ldg(reinterpret_cast<const float4*>(vbase + (size_t)t * C));
-        }
-        float s = (q.x * k4.x + q.y * k4.y) + (q.z * k4.z + q.w * k4.w);
+    constexpr int U = 8;  // positions requested per half-warp before anything waits (bytes in flight)
+    for (int i0 = 0; i0 < trips; i0 += U) {
+        float4 k4[U], v4[U];
 #pragma unroll
-        for (int d = 8; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);  // within the half-warp
-        if (live) {
-            const float mn = fmaxf(m, s);
-            const float corr = expf(m - mn), p = expf(s - mn);  // corr = 0 on the first position
-            l = l * corr + p;
-            o.x = o.x * corr + p * v4.x; o.y = o.y * corr + p * v4.y;
-            o.z = o.z * corr + p * v4.z; o.w = o.w * corr + p * v4.w;
-            m = mn;
+        for (int u = 0; u < U; ++u) {
+            const int t = (i0 + u) * 16 + slot;
+            k4[u] = v4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (t <= pos) {
+                k4[u] = *reinterpret_cast<const float4*>(kbase + (size_t)t * C);
+                v4[u] = *reinterpret_cast<const float4*>(vbase + (size_t)t * C);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int t = (i0 + u) * 16 + slot;
+            float s = (q.x * k4[u].x + q.y * k4[u].y) + (q.z * k4[u].z + q.w * k4[u].w);
+#pragma unroll
+            for (int d = 8; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);  // within the half-warp
+            if (t <= pos) {
+                const float mn = fmaxf(m, s);
+                const float corr = expf(m - mn), p = expf(s - mn);  // corr = 0 on the first position
+                l = l * corr + p;
+                o.x = o.x * corr + p * v4[u].x; o.y = o.y * corr + p * v4[u].y;
+                o.z = o.z * corr + p * v4[u].z; o.w = o.w * corr + p * v4[u].w;
+                m = mn;
+            }
         }
     }
     if (hl == 0) { st_m[slot] = m; st_l[slot] = l; }
@@ -175,31 +447,107 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     }
 }
 
+// out[b,:] = wte[tok[b],:] + wpe[pos,:]  (one fp32 add, as the full-sequence encoder)
+__global__ void decode_encoder_kernel(float4* __restrict__ out, const int* __restrict__ tok, const float4* __restrict__ wte,
+                                      const float4* __restrict__ wpe, const int* __restrict__ pos_ptr, int B, int C4,
+                                      int vocab_rows, int* status) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int pos = *pos_ptr;
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < B * C4; i += gridDim.x * blockDim.x) {
+        const int b = i / C4, c = i % C4;
+        int id = tok[b];
+        if (id < 0 || id >= vocab_rows) {  // reported like the full-sequence encoder does
+            atomicCAS(status, 0, 201);
+            id = 0;
+        }
+        const float4 e = __ldg(wte + (size_t)id * C4 + c), p = __ldg(wpe + (size_t)pos * C4 + c);
+        out[i] = make_float4(e.x + p.x, e.y + p.y, e.z + p.z, e.w + p.w);
+    }
+}
+
+__global__ void set_int_kernel(int* dst, int value) { *dst = value; }
+
 }  // namespace
 
+int launch_set_int(b200_ctx* ctx, int* dst, int value) {
+    set_int_kernel<<<1, 1, 0, ctx->stream>>>(dst, value);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_decode_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,
+                          const int* pos_ptr, int B, int C, int vocab_rows) {
+    const int n = B * (C / 4);
+    cudaError_t le = launch_pdl(ctx, decode_encoder_kernel, dim3((n + 255) / 256), dim3(256), 0, reinterpret_cast<float4*>(out), tok,
+                                reinterpret_cast<const float4*>(wte), reinterpret_cast<const float4*>(wpe), pos_ptr, B, C / 4,
+                                vocab_rows, ctx->d_status);
+    ctx->launches++;
+    B200_CUDA(ctx, le);
+    return B200_OK;
+}
+
 int launch_skinny_gemm(b200_ctx* ctx, float* out, const float* x, const float* W, const float* bias, int B,
-                       int K, int N, int gelu) {
+                       int K, int N, int gelu, const float* branch, const float* ln_w, const float* ln_b,
+                       float* resid_out) {
     if (B < 1 || B > 16 || K % 4 || N < 1) return B200_ERR_SHAPE;
+    if (ln_w && (K > 1664 || !ln_b || !resid_out || resid_out == x)) return B200_ERR_SHAPE;
     const int nb = B <= 8 ? 8 : 16;
-    // many rows: four per warp (each x value read from shared memory serves four rows); few rows:
-    // two per warp, so that more SMs take part
-    const int rows = (N >= 64 * ctx->num_sms) ? 4 : 2;
+    const size_t x_bytes = ((size_t)nb * K * 4 + 127) & ~(size_t)127;
+    // Wide outputs (the lm-head) go through the streamed kernel; it has no layernorm prologue, so
+    // there the caller keeps the separate kernel.
+    static const bool no_stream = getenv("B200_DECODE_NO_STREAM") != nullptr;
+    if (!ln_w && N >= 64 * ctx->num_sms && x_bytes <= 98304 && !no_stream) {
+        StreamArgs a;
+        a.out = out; a.x = x; a.W = W; a.bias = bias; a.B = B; a.N = N; a.K = K; a.gelu = gelu; a.status = ctx->d_status;
+        int rt = 32;
+        const size_t budget = (size_t)222 * 1024 - x_bytes - 256;  // for the stages
+        // floats of K per stage: all of K if two stages of whole rows fit, else a multiple of 128
+        int kch = K;
+        while ((size_t)kStreamStages * rt * kch * 4 > budget) {
+            if (kch > 1024 || rt == 8) kch = ((kch / 2 + 127) / 128) * 128;
+            else rt /= 2;
+            if (kch < 128) return B200_ERR_LIMIT;
+        }
+        a.RT = rt; a.KCH = kch; a.num_items = (N + rt - 1) / rt;
+        const size_t smem = 128 + x_bytes + (size_t)kStreamStages * rt * kch * 4 + 256;
+        const int grid = a.num_items < ctx->num_sms ? a.num_items : ctx->num_sms;
+        cudaError_t le = cudaSuccess;
+#define B200_STREAM(NB, RPW)                                                                                         \
+        do {                                                                                                         \
+            static bool attr_set[64] = {};                                                                           \
+            if (!attr_set[ctx->device & 63]) {                                                                       \
+                B200_CUDA(ctx, cudaFuncSetAttribute(skinny_stream_kernel<NB, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); \
+                attr_set[ctx->device & 63] = true;                                                                   \
+            }                                                                                                        \
+            le = launch_pdl(ctx, skinny_stream_kernel<NB, RPW>, dim3(grid), dim3(kStreamThreads), smem, a);          \
+        } while (0)
+        if (nb == 8) { if (rt == 32) B200_STREAM(8, 4); else if (rt == 16) B200_STREAM(8, 2); else B200_STREAM(8, 1); }
+        else { if (rt == 32) B200_STREAM(16, 4); else if (rt == 16) B200_STREAM(16, 2); else B200_STREAM(16, 1); }
+#undef B200_STREAM
+        ctx->launches++;
+        B200_CUDA(ctx, le);
+        return B200_OK;
+    }
+    if (x_bytes > (size_t)200 * 1024) return B200_ERR_LIMIT;
+    SkinnyArgs a;
+    a.out = out; a.x = x; a.W = W; a.bias = bias; a.branch = branch; a.ln_w = ln_w; a.ln_b = ln_b; a.resid_out = resid_out;
+    a.B = B; a.N = N; a.K = K; a.gelu = gelu;
+    const int rows = 2;  // per warp
     const int groups = (N + rows - 1) / rows, batches = (groups + 7) / 8;
-    const int grid = batches < 4 * ctx->num_sms ? batches : 4 * ctx->num_sms;
-    const size_t smem = (size_t)nb * kSkinnyKC * sizeof(float);
+    const int grid = batches < 2 * ctx->num_sms ? batches : 2 * ctx->num_sms;
     cudaError_t le = cudaSuccess;
 #define B200_SKINNY(NB, ROWS)                                                                                       \
     do {                                                                                                            \
         static bool attr_set[64] = {};                                                                              \
         if (!attr_set[ctx->device & 63]) {                                                                          \
-            B200_CUDA(ctx, cudaFuncSetAttribute(skinny_gemm_kernel<NB, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+            B200_CUDA(ctx, cudaFuncSetAttribute(skinny_gemm_kernel<NB, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
             attr_set[ctx->device & 63] = true;                                                                      \
         }                                                                                                           \
-        le = launch_pdl(ctx, skinny_gemm_kernel<NB, ROWS>, dim3(grid), dim3(kSkinnyThreads), smem, out, x, W, bias, B, N, K, gelu); \
+        le = launch_pdl(ctx, skinny_gemm_kernel<NB, ROWS>, dim3(grid), dim3(kSkinnyThreads), x_bytes + (ln_w ? (size_t)2 * K * 4 : 0), a);           \
     } while (0)
-    if (nb == 8 && rows == 4) B200_SKINNY(8, 4);
-    else if (nb == 8) B200_SKINNY(8, 2);
-    else if (rows == 4) B200_SKINNY(16, 4);
+    if (nb == 8) B200_SKINNY(8, 2);
     else B200_SKINNY(16, 2);
 #undef B200_SKINNY
     ctx->launches++;
@@ -219,10 +567,10 @@ int launch_kv_append(b200_ctx* ctx, float* kcache, float* vcache, const float* q
     return B200_OK;
 }
 
-int launch_decode_attention(b200_ctx* ctx, float* out, const float* qkv, const float* kcache, const float* vcache,
-                            int B, int C, int NH, int pos, int cache_T) {
+int launch_decode_attention(b200_ctx* ctx, float* out, const float* qkv, float* kcache, float* vcache, int B, int C,
+                            int NH, const int* pos_ptr, int cache_T) {
     cudaError_t le = launch_pdl(ctx, decode_attention_kernel, dim3(NH, B), dim3(kDecAttThreads), 0, out, qkv, kcache,
-                                vcache, C, pos, cache_T);
+                                vcache, C, pos_ptr, cache_T);
     ctx->launches++;
     B200_CUDA(ctx, le);
     return B200_OK;

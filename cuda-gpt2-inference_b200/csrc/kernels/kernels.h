@@ -35,14 +35,22 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
 
 // incremental decoding (decode.cu): B <= 16 rows, fp32 FMA, no TF32 rounding
 // out[B,N] = act(x[B,K] * W[N,K]^T + bias[N])
+// with ln_w: x = layernorm(x + branch) * ln_w + ln_b first (branch nullable), and x + branch is
+// stored to resid_out (a buffer other than x)
 int launch_skinny_gemm(b200_ctx* ctx, float* out, const float* x, const float* W, const float* bias, int B,
-                       int K, int N, int gelu);
+                       int K, int N, int gelu, const float* branch = nullptr, const float* ln_w = nullptr,
+                       const float* ln_b = nullptr, float* resid_out = nullptr);
 // k and v columns of qkv rows [B*T, 3C] -> caches [B][cache_T][C] at positions pos0 .. pos0+T-1
 int launch_kv_append(b200_ctx* ctx, float* kcache, float* vcache, const float* qkv, int B, int T, int C, int pos0,
                      int cache_T);
-// out[B,C]: attention of the query rows qkv[B,3C] over cached positions 0 .. pos
-int launch_decode_attention(b200_ctx* ctx, float* out, const float* qkv, const float* kcache, const float* vcache,
-                            int B, int C, int NH, int pos, int cache_T);
+// out[B,C]: stores k and v of the rows qkv[B,3C] at position *pos_ptr, then attention of their
+// query parts over cached positions 0 .. *pos_ptr
+int launch_decode_attention(b200_ctx* ctx, float* out, const float* qkv, float* kcache, float* vcache, int B, int C,
+                            int NH, const int* pos_ptr, int cache_T);
+// out[B,C] = wte[tok[b]] + wpe[*pos_ptr]
+int launch_decode_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,
+                          const int* pos_ptr, int B, int C, int vocab_rows);
+int launch_set_int(b200_ctx* ctx, int* dst, int value);
 
 // 3xTF32 attention: qkv_small is a scratch buffer shaped like qkv ([B,T,3C]) that receives the
 // dropped low parts of qkv; two kernel launches (split + attention)

@@ -23,12 +23,15 @@ def _model(pkg, orc, ctx, kw, B, T, round_operands):
     return cfg, ocfg, params, model
 
 
-@pytest.mark.parametrize("kw,B,T", [(dict(num_layers=2), 3, 64), (dict(num_layers=2, num_heads=25, channels=1600), 2, 64),
-                                    (dict(num_layers=1), 11, 64)])
-def test_decode_from_empty_cache_matches_oracle(pkg, orc, ctx, kw, B, T):
-    """Every position decoded one token at a time (pos = 0 .. T-1): fp32-level agreement."""
+@pytest.mark.parametrize("kw,B,T,use_graph", [(dict(num_layers=2), 3, 64, 0), (dict(num_layers=2), 3, 64, 1),
+                                              (dict(num_layers=2, num_heads=25, channels=1600), 2, 64, 1),
+                                              (dict(num_layers=1), 11, 64, 0)])
+def test_decode_from_empty_cache_matches_oracle(pkg, orc, ctx, kw, B, T, use_graph):
+    """Every position decoded one token at a time (pos = 0 .. T-1): fp32-level agreement.  With
+    use_graph the steps after the first are replays of one captured graph (the position is data)."""
     import torch
     cfg, ocfg, params, model = _model(pkg, orc, ctx, kw, B, T, 0)
+    model.set_options(round_operands=0, use_graph=use_graph)
     tokens = orc.fill_tokens((B, T), seed=99, vocab=cfg.vocab_size)
     want = orc.gpt2_forward(params, ocfg, tokens, precise=True)  # [B,T,Vp]
     d_tok = torch.from_numpy(tokens).cuda()
