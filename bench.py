@@ -340,6 +340,41 @@ def run_ours(args):
     e2e_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
 
+    # ---------------------------------------------- incremental decoding (key/value cache)
+    # One new token per sequence against a cache filled by a prefill of T/2 positions; each step
+    # reads every weight and the used part of the cache once (HBM-bound).  Extra measurement on
+    # rank 0; not part of `value`.
+    decode = None
+    if rank == 0 and not tp and not xl and B <= 16:
+        try:
+            model.enable_kv_cache()
+            model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32, use_graph=1)
+            T0 = T // 2
+            model.prefill(tok_dev[:, :T0].contiguous(), B, T0)
+            col = tok_dev[:, 0].contiguous()
+            for i in range(3):
+                model.decode_step(col, B, T0)
+            ctx.sync_check()
+            n_dec = 64
+            ev4, ev5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            ev4.record(stream)
+            for i in range(n_dec):
+                model.decode_step(col, B, T0 + i)
+            ev5.record(stream)
+            ctx.sync_check()
+            dec_us = ev4.elapsed_time(ev5) * 1e3 / n_dec
+            Cc_, L_ = cfg.channels, cfg.num_layers
+            w_bytes = 4.0 * (L_ * 12 * Cc_ * Cc_ + cfg.padded_vocab_size * Cc_)
+            kv_bytes = 4.0 * L_ * B * (T0 + n_dec / 2 + 1) * 2 * Cc_
+            decode = {"value": B / (dec_us * 1e-6), "unit": "tokens/s", "us_per_step": dec_us, "batch": B,
+                      "positions": [T0, T0 + n_dec - 1],
+                      "algorithmic_bytes_per_step": w_bytes + kv_bytes,
+                      "achieved_gbs": (w_bytes + kv_bytes) / (dec_us * 1e-6) / 1e9,
+                      "frac_of_hbm_peak": (w_bytes + kv_bytes) / (dec_us * 1e-6) / 1e9 / _peaks()["hbm_gbs"],
+                      "note": "b200_gpt2_decode_step replayed as a CUDA graph; bytes = all weight matrices once + keys and values of the cached positions"}
+        except Exception as e:  # an extra measurement must not take the benchmark line down
+            decode = {"error": str(e)}
+
     if rank != 0:
         if dist is not None:
             dist.destroy_process_group()
@@ -408,6 +443,7 @@ def run_ours(args):
         "tf32x3": None if x3_ms is None else {
             "value": replicas * B * T / (x3_ms * 1e-3), "unit": UNIT, "ms_per_step": x3_ms,
             "note": "same workload with gemm_mode = lmhead_mode = B200_TF32X3 (split-operand GEMMs and attention)"},
+        "decode": decode,
     }
     print(json.dumps(line), flush=True)
     model.close()

@@ -33,6 +33,8 @@ struct b200_gpt2 {
     bool keep_kv = false;                        // the forward being enqueued also fills the cache
     int* pos_dev = nullptr;                      // position of the decode step being run
     float* resid2 = nullptr;                     // second residual buffer of the decode step [16][C]
+    float* att_partial = nullptr;                // decode attention: softmax states of the position splits
+    unsigned int* att_counters = nullptr;        // ... and their arrival counters (zero between launches)
     std::map<int, cudaGraphExec_t> decode_graphs;  // by B (the position is read from pos_dev)
     int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
     // tensor parallelism (Megatron style): this rank's share of the attention heads, of the MLP
@@ -324,6 +326,8 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     for (auto& g : m->decode_graphs) cudaGraphExecDestroy(g.second);
     if (m->pos_dev) cudaFree(m->pos_dev);
     if (m->resid2) cudaFree(m->resid2);
+    if (m->att_partial) cudaFree(m->att_partial);
+    if (m->att_counters) cudaFree(m->att_counters);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
     void* ptrs[] = {m->params, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
                     m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->kcache, m->vcache};
@@ -441,6 +445,9 @@ int b200_gpt2_enable_kv_cache(b200_gpt2* m) {
     cudaError_t e = cudaMalloc(&m->vcache, n * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&m->pos_dev, sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&m->resid2, (size_t)16 * m->cfg.channels * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&m->att_partial, (size_t)16 * m->cfg.num_heads * 4 * 66 * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&m->att_counters, (size_t)16 * m->cfg.num_heads * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(m->att_counters, 0, (size_t)16 * m->cfg.num_heads * sizeof(unsigned int));
     if (e != cudaSuccess) {
         cudaFree(m->kcache);
         if (m->vcache) cudaFree(m->vcache);
@@ -502,7 +509,7 @@ static int enqueue_decode(b200_gpt2* m, const int* tokens, int B) {
             }
             DSTEP(launch_skinny_gemm(ctx, m->qkv, m->ln_out, qkvw, qkvb, B, C, 3 * C, 0));
         }
-        DSTEP(launch_decode_attention(ctx, m->atty, m->qkv, m->kcache + l * per_layer, m->vcache + l * per_layer, B, C, NH, m->pos_dev, m->max_T));
+        DSTEP(launch_decode_attention(ctx, m->atty, m->qkv, m->kcache + l * per_layer, m->vcache + l * per_layer, B, C, NH, m->pos_dev, m->max_T, m->att_partial, m->att_counters));
         DSTEP(launch_skinny_gemm(ctx, m->branch, m->atty, P + off[6] + (size_t)l * C * C, P + off[7] + (size_t)l * C, B, C, C, 0));
         const float* fcw = P + off[10] + (size_t)l * 4 * C * C;
         const float* fcb = P + off[11] + (size_t)l * 4 * C;

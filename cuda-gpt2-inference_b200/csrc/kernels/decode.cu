@@ -368,20 +368,27 @@ __global__ void kv_append_kernel(float4* __restrict__ kcache, float4* __restrict
 }
 
 constexpr int kDecAttThreads = 256;
+constexpr int kDecAttSplits = 4;  // CTAs per (sequence, head): each walks a quarter of the positions
 
-// q: row b of qkv [B, 3C] (first C columns); caches [B][cache_T][C]; positions 0..pos take part
+// q: row b of qkv [B, 3C] (first C columns); caches [B][cache_T][C]; positions 0..pos take part.
+// grid (NH, B, kDecAttSplits).  Every CTA leaves its softmax state {m, l, o[64]} in `partial`;
+// the last one of a (sequence, head) to finish - found with a counter - merges the states in
+// split order (so the result does not depend on which CTA that was) and resets the counter.
 __global__ void __launch_bounds__(kDecAttThreads)
 decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, float* kcache, float* vcache, int C,
-                        const int* __restrict__ pos_ptr, int cache_T) {
+                        const int* __restrict__ pos_ptr, int cache_T, float* partial, unsigned int* counters) {
     __shared__ float st_m[16], st_l[16];
     __shared__ float st_o[16][64];
+    __shared__ int is_last;
     griddep_wait();
     griddep_launch_dependents();
-    const int h = blockIdx.x, b = blockIdx.y;
+    const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z;
     const int pos = *pos_ptr;
-    // this head's slice of the new position goes into the cache first (ordinary loads below: the
-    // read-only path need not see stores of the same kernel)
-    if (threadIdx.x < 32) {
+    const int per = (((pos + kDecAttSplits) / kDecAttSplits + 15) / 16) * 16;  // positions per split
+    const int t_begin = z * per, t_end = min(pos + 1, t_begin + per);
+    // this head's slice of the new position goes into the cache first, by the split that will
+    // read it (ordinary loads below: the read-only path need not see stores of the same kernel)
+    if (threadIdx.x < 32 && pos >= t_begin && pos < t_end) {
         const int which = threadIdx.x >> 4, c = (threadIdx.x & 15) * 4;
         float* cache = which ? vcache : kcache;
         *reinterpret_cast<float4*>(cache + ((size_t)b * cache_T + pos) * C + h * 64 + c) =
@@ -399,26 +406,26 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     float m = -INFINITY, l = 0.f;
     float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
     // every half-warp makes the same number of trips so that the shuffles stay warp-wide
-    const int trips = (pos + 16) / 16;
+    const int trips = (max(t_end - t_begin, 0) + 15) / 16;
     constexpr int U = 8;  // positions requested per half-warp before anything waits (bytes in flight)
     for (int i0 = 0; i0 < trips; i0 += U) {
         float4 k4[U], v4[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int t = (i0 + u) * 16 + slot;
+            const int t = t_begin + (i0 + u) * 16 + slot;
             k4[u] = v4[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (t <= pos) {
+            if (t < t_end) {
                 k4[u] = *reinterpret_cast<const float4*>(kbase + (size_t)t * C);
                 v4[u] = *reinterpret_cast<const float4*>(vbase + (size_t)t * C);
             }
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-            const int t = (i0 + u) * 16 + slot;
+            const int t = t_begin + (i0 + u) * 16 + slot;
             float s = (q.x * k4[u].x + q.y * k4[u].y) + (q.z * k4[u].z + q.w * k4[u].w);
 #pragma unroll
             for (int d = 8; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);  // within the half-warp
-            if (t <= pos) {
+            if (t < t_end) {
                 const float mn = fmaxf(m, s);
                 const float corr = expf(m - mn), p = expf(s - mn);  // corr = 0 on the first position
                 l = l * corr + p;
@@ -431,20 +438,43 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     if (hl == 0) { st_m[slot] = m; st_l[slot] = l; }
     *reinterpret_cast<float4*>(&st_o[slot][hl * 4]) = o;
     __syncthreads();
-    if (threadIdx.x < 64) {
-        const int d = threadIdx.x;
-        float mm = -INFINITY;
+    // this CTA's state: thread d < 64 owns output column d; threads 64 and 65 own l and m
+    const size_t bh = (size_t)b * gridDim.x + h;
+    float* mine = partial + (bh * kDecAttSplits + z) * 66;
+    float cm = -INFINITY;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) mm = fmaxf(mm, st_m[i]);
-        float L = 0.f, O = 0.f;
+    for (int i = 0; i < 16; ++i) cm = fmaxf(cm, st_m[i]);
+    if (threadIdx.x < 66) {
+        float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-            const float w = (st_m[i] == -INFINITY) ? 0.f : expf(st_m[i] - mm);  // a half-warp may have seen nothing
-            L += st_l[i] * w;
-            O += st_o[i][d] * w;
+            const float w = (st_m[i] == -INFINITY) ? 0.f : expf(st_m[i] - cm);  // a half-warp may have seen nothing
+            acc += (threadIdx.x < 64 ? st_o[i][threadIdx.x] : st_l[i]) * w;
         }
-        out[(size_t)b * C + h * 64 + d] = O / L;
+        mine[threadIdx.x] = (threadIdx.x == 65) ? cm : acc;
     }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = (atomicAdd(counters + bh, 1u) == kDecAttSplits - 1);
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    if (threadIdx.x < 64) {
+        const float* all = partial + bh * kDecAttSplits * 66;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int s = 0; s < kDecAttSplits; ++s) mm = fmaxf(mm, __ldcg(all + s * 66 + 65));
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int s = 0; s < kDecAttSplits; ++s) {
+            const float ms = __ldcg(all + s * 66 + 65);
+            const float w = (ms == -INFINITY) ? 0.f : expf(ms - mm);  // an empty split
+            L += __ldcg(all + s * 66 + 64) * w;
+            O += __ldcg(all + s * 66 + threadIdx.x) * w;
+        }
+        out[(size_t)b * C + h * 64 + threadIdx.x] = O / L;
+    }
+    if (threadIdx.x == 0) counters[bh] = 0u;  // for the next launch
 }
 
 // out[b,:] = wte[tok[b],:] + wpe[pos,:]  (one fp32 add, as the full-sequence encoder)
@@ -568,9 +598,9 @@ int launch_kv_append(b200_ctx* ctx, float* kcache, float* vcache, const float* q
 }
 
 int launch_decode_attention(b200_ctx* ctx, float* out, const float* qkv, float* kcache, float* vcache, int B, int C,
-                            int NH, const int* pos_ptr, int cache_T) {
-    cudaError_t le = launch_pdl(ctx, decode_attention_kernel, dim3(NH, B), dim3(kDecAttThreads), 0, out, qkv, kcache,
-                                vcache, C, pos_ptr, cache_T);
+                            int NH, const int* pos_ptr, int cache_T, float* partial, unsigned int* counters) {
+    cudaError_t le = launch_pdl(ctx, decode_attention_kernel, dim3(NH, B, kDecAttSplits), dim3(kDecAttThreads), 0, out, qkv,
+                                kcache, vcache, C, pos_ptr, cache_T, partial, counters);
     ctx->launches++;
     B200_CUDA(ctx, le);
     return B200_OK;

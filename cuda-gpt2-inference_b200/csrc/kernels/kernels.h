@@ -45,8 +45,9 @@ int launch_kv_append(b200_ctx* ctx, float* kcache, float* vcache, const float* q
                      int cache_T);
 // out[B,C]: stores k and v of the rows qkv[B,3C] at position *pos_ptr, then attention of their
 // query parts over cached positions 0 .. *pos_ptr
+// partial: scratch of B * NH * 4 * 66 floats; counters: B * NH zeroed words (left zeroed)
 int launch_decode_attention(b200_ctx* ctx, float* out, const float* qkv, float* kcache, float* vcache, int B, int C,
-                            int NH, const int* pos_ptr, int cache_T);
+                            int NH, const int* pos_ptr, int cache_T, float* partial, unsigned int* counters);
 // out[B,C] = wte[tok[b]] + wpe[*pos_ptr]
 int launch_decode_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,
                           const int* pos_ptr, int B, int C, int vocab_rows);
