@@ -523,9 +523,13 @@ static int enqueue_decode(b200_gpt2* m, const int* tokens, int B) {
         DSTEP(launch_skinny_gemm(ctx, m->branch, m->fch, P + off[12] + (size_t)l * C * 4 * C, P + off[13] + (size_t)l * C, B, 4 * C, C, 0));
         branch = m->branch;
     }
-    // final layernorm, then the lm-head (wide: the streamed kernel, which takes plain input rows)
-    DSTEP(launch_fused_residual_layernorm(ctx, rb, m->ln_out, nullptr, nullptr, ra, branch, P + off[14], P + off[15], B, C, 0));
-    DSTEP(launch_skinny_gemm(ctx, m->logits, m->ln_out, P + off[0], nullptr, B, C, Vp, 0));
+    // final layernorm and lm-head
+    if (fuse_ln) {
+        DSTEP(launch_skinny_gemm(ctx, m->logits, ra, P + off[0], nullptr, B, C, Vp, 0, branch, P + off[14], P + off[15], rb));
+    } else {
+        DSTEP(launch_fused_residual_layernorm(ctx, rb, m->ln_out, nullptr, nullptr, ra, branch, P + off[14], P + off[15], B, C, 0));
+        DSTEP(launch_skinny_gemm(ctx, m->logits, m->ln_out, P + off[0], nullptr, B, C, Vp, 0));
+    }
 #undef DSTEP
     return B200_OK;
 }
@@ -563,7 +567,7 @@ int b200_gpt2_decode_step(b200_gpt2* m, const int* tokens, int B, int pos) {
         it = m->decode_graphs.emplace(B, exec).first;
     }
     B200_CUDA(ctx, cudaGraphLaunch(it->second, ctx->stream));
-    ctx->launches += 3 + (m->cfg.channels <= 1664 ? 5ull : 7ull) * m->cfg.num_layers;  // set_int is counted by its launcher
+    ctx->launches += (m->cfg.channels <= 1664 ? 2 + 5ull * m->cfg.num_layers : 3 + 7ull * m->cfg.num_layers);  // set_int is counted by its launcher
     return B200_OK;
 }
 

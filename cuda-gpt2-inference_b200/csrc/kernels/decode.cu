@@ -8,6 +8,8 @@
 // (exact fp32 products, no TF32 rounding) and are organised around coalesced streaming:
 //   skinny_gemm_kernel      out[b,n] = act(sum_k x[b,k] W[n,k] + bias[n]); a warp streams ROWS rows
 //                           of W, 128 floats per step, against x staged in shared memory
+//                           (a variant that streamed W through a shared-memory ring with bulk
+//                           copies was measured for the lm-head and was no faster)
 //   kv_append_kernel        K and V columns of freshly computed qkv rows -> cache (prefill)
 //   decode_attention_kernel one CTA per (sequence, head): stores the new position's K and V,
 //                           then half-warps walk the cached positions with an online softmax
@@ -42,22 +44,27 @@ struct SkinnyArgs {
     int B, N, K, gelu;
 };
 
-template <int NB, int ROWS>
+// NV = float4 per lane that hold a row in the layernorm prologue (0: no prologue compiled in).
+// (Splitting K between the warps of a row group, to put narrow outputs on more SMs, was measured
+// and is slower: more batches per CTA means more weight round trips one after the other.)
+template <int NB, int ROWS, int NV>
 __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_gemm_kernel(const SkinnyArgs a) {
     extern __shared__ float4 xs4[];  // [NB][K / 4]: the input rows, staged once
     const int B = a.B, N = a.N, K = a.K, K4 = a.K >> 2;
     const float* __restrict__ W = a.W;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    constexpr int kWarps = kSkinnyThreads / 32;
+    constexpr int kWarps = kSkinnyThreads / 32, kRowWarps = kWarps;
+    const int rw = warp;
     const int groups = (N + ROWS - 1) / ROWS;                  // row groups, one per warp at a time
-    const int batches = (groups + kWarps - 1) / kWarps;        // a CTA takes kWarps groups at a time
+    const int batches = (groups + kRowWarps - 1) / kRowWarps;  // a CTA takes kRowWarps groups at a time
+    const int kbeg = 0, kend = K;
     // The kernel is a chain of memory round trips (each several hundred to two thousand cycles),
     // so everything that does not depend on the previous kernel is requested before waiting for
     // it: the first chunk of this warp's weight rows, the bias, the layernorm parameters.
     float4 w[kSkinnySteps][ROWS];
     auto request_w = [&](int n0, int kc0) {
-        const int kc = min(kSkinnyKC, K - kc0);
+        const int kc = min(kSkinnyKC, kend - kc0);
 #pragma unroll
         for (int s = 0; s < kSkinnySteps; ++s) {
             const int k4 = s * 32 + lane;  // float4 index inside the chunk
@@ -68,11 +75,10 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                               : make_float4(0.f, 0.f, 0.f, 0.f);  // rows clamped: masked at the store
         }
     };
-    request_w((blockIdx.x * kWarps + warp) * ROWS, 0);
-    constexpr int kMaxV = 13;  // layernorm prologue: K <= 1664
+    request_w((blockIdx.x * kRowWarps + rw) * ROWS, kbeg);
     float4* lnw4 = xs4 + NB * K4;  // layernorm weight and bias, behind the input rows
     float4* lnb4 = lnw4 + K4;
-    if (a.ln_w) {
+    if (NV > 0) {
         for (int c = threadIdx.x; c < K4; c += kSkinnyThreads) {
             lnw4[c] = __ldg(reinterpret_cast<const float4*>(a.ln_w) + c);
             lnb4[c] = __ldg(reinterpret_cast<const float4*>(a.ln_b) + c);
@@ -80,39 +86,40 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     }
     griddep_wait();
     griddep_launch_dependents();
-    if (a.ln_w) {
+    if (NV > 0) {
         __syncthreads();
         // one warp per row; a lane holds float4 number lane, lane + 32, ... of the row
+        constexpr int NVV = NV > 0 ? NV : 1;
         for (int b = warp; b < NB; b += kWarps) {
-            float4 v[kMaxV];
+            float4 v[NVV], t[NVV];
 #pragma unroll
-            for (int i = 0; i < kMaxV; ++i) {
+            for (int i = 0; i < NVV; ++i) {
                 const int c = lane + i * 32;
-                v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (b < B && c < K4) {
-                    v[i] = *reinterpret_cast<const float4*>(a.x + (size_t)b * K + c * 4);
-                    if (a.branch) {
-                        const float4 t = *reinterpret_cast<const float4*>(a.branch + (size_t)b * K + c * 4);
-                        v[i].x += t.x; v[i].y += t.y; v[i].z += t.z; v[i].w += t.w;
-                    }
+                v[i] = t[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (b < B && c < K4) v[i] = *reinterpret_cast<const float4*>(a.x + (size_t)b * K + c * 4);
+            }
+            if (a.branch) {
+#pragma unroll
+                for (int i = 0; i < NVV; ++i) {
+                    const int c = lane + i * 32;
+                    if (b < B && c < K4) t[i] = *reinterpret_cast<const float4*>(a.branch + (size_t)b * K + c * 4);
                 }
             }
-            if (blockIdx.x == 0 && b < B) {
 #pragma unroll
-                for (int i = 0; i < kMaxV; ++i) {
-                    const int c = lane + i * 32;
-                    if (c < K4) *reinterpret_cast<float4*>(a.resid_out + (size_t)b * K + c * 4) = v[i];
-                }
+            for (int i = 0; i < NVV; ++i) {
+                const int c = lane + i * 32;
+                v[i].x += t[i].x; v[i].y += t[i].y; v[i].z += t[i].z; v[i].w += t[i].w;
+                if (blockIdx.x == 0 && b < B && c < K4) *reinterpret_cast<float4*>(a.resid_out + (size_t)b * K + c * 4) = v[i];
             }
             float s = 0.f;
 #pragma unroll
-            for (int i = 0; i < kMaxV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+            for (int i = 0; i < NVV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
 #pragma unroll
             for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
             const float mean = s / (float)K;
             float q = 0.f;
 #pragma unroll
-            for (int i = 0; i < kMaxV; ++i) {
+            for (int i = 0; i < NVV; ++i) {
                 if (lane + i * 32 < K4) {
                     const float dx = v[i].x - mean, dy = v[i].y - mean, dz = v[i].z - mean, dw = v[i].w - mean;
                     q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
@@ -122,7 +129,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
             for (int d = 16; d >= 1; d >>= 1) q += __shfl_xor_sync(0xffffffffu, q, d);
             const float rstd = rsqrtf(q / (float)K + 1e-5f);
 #pragma unroll
-            for (int i = 0; i < kMaxV; ++i) {
+            for (int i = 0; i < NVV; ++i) {
                 const int c = lane + i * 32;
                 if (c < K4) {
                     float4 y = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -157,7 +164,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     }
     __syncthreads();
     for (int batch = blockIdx.x; batch < batches; batch += gridDim.x) {
-        const int n0 = (batch * kWarps + warp) * ROWS;
+        const int n0 = (batch * kRowWarps + rw) * ROWS;
         float bias_r[ROWS];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r) bias_r[r] = (a.bias && n0 + r < N) ? __ldg(a.bias + n0 + r) : 0.f;
@@ -166,8 +173,8 @@ skinny_gemm_kernel(const SkinnyArgs a) {
         for (int r = 0; r < ROWS; ++r)
 #pragma unroll
             for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
-        for (int kc0 = 0; kc0 < K; kc0 += kSkinnyKC) {
-            const int kc = min(kSkinnyKC, K - kc0);  // multiple of 4
+        for (int kc0 = kbeg; kc0 < kend; kc0 += kSkinnyKC) {
+            const int kc = min(kSkinnyKC, kend - kc0);  // multiple of 4
             // the chunk was requested earlier (before the kernel's wait, or at the end of the
             // previous chunk); take it over and request the next one before using it
             float4 wc[kSkinnySteps][ROWS];
@@ -175,8 +182,8 @@ skinny_gemm_kernel(const SkinnyArgs a) {
             for (int s = 0; s < kSkinnySteps; ++s)
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) wc[s][r] = w[s][r];
-            if (kc0 + kSkinnyKC < K) request_w(n0, kc0 + kSkinnyKC);
-            else if (batch + (int)gridDim.x < batches) request_w(((batch + gridDim.x) * kWarps + warp) * ROWS, 0);
+            if (kc0 + kSkinnyKC < kend) request_w(n0, kc0 + kSkinnyKC);
+            else if (batch + (int)gridDim.x < batches) request_w(((batch + gridDim.x) * kRowWarps + rw) * ROWS, kbeg);
             if (n0 < N) {
 #pragma unroll
                 for (int s = 0; s < kSkinnySteps; ++s) {
@@ -186,14 +193,19 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                         for (int b = 0; b < NB; ++b) {
                             const float4 xv = xs4[b * K4 + (kc0 >> 2) + k4];
 #pragma unroll
-                            for (int r = 0; r < ROWS; ++r)
-                                acc[r][b] += (wc[s][r].x * xv.x + wc[s][r].y * xv.y) + (wc[s][r].z * xv.z + wc[s][r].w * xv.w);
+                            for (int r = 0; r < ROWS; ++r) {
+                                float t = acc[r][b];
+                                t = fmaf(wc[s][r].x, xv.x, t);
+                                t = fmaf(wc[s][r].y, xv.y, t);
+                                t = fmaf(wc[s][r].z, xv.z, t);
+                                t = fmaf(wc[s][r].w, xv.w, t);
+                                acc[r][b] = t;
+                            }
                         }
                     }
                 }
             }
         }
-        if (n0 >= N) continue;
         // sum over the 32 lanes; afterwards every lane holds every total
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
@@ -205,149 +217,18 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                 acc[r][b] = v;
             }
         // lane i stores the totals i, i + 32, ... of the ROWS x NB block (row-major)
+        {
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r)
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                if (((r * NB + b) & 31) == lane && n0 + r < N && b < B) {
-                    float v = acc[r][b] + bias_r[r];
-                    if (a.gelu) v = gelu_tanh(v);
-                    a.out[(size_t)b * N + n0 + r] = v;
-                }
-            }
-    }
-}
-
-// The same product with the weights streamed through shared memory by bulk copies: the kernel is
-// bound by HBM bandwidth, which wants on the order of 100 KB in flight per SM - more than
-// registers can hold.  Persistent CTAs; warp 0 is the producer: for every work item (RT
-// consecutive rows of W, all of K in chunks of KCH floats) it issues one bulk copy per row
-// segment into a ring of stages, completion on an mbarrier; eight consumer warps own RT/8 rows
-// each and multiply out of shared memory against x, which is staged once (whole, NB x K).
-constexpr int kStreamThreads = 288;  // producer warp + 8 consumer warps
-constexpr int kStreamStages = 2;
-
-struct StreamArgs {
-    float* out;
-    const float* x;
-    const float* W;
-    const float* bias;
-    int B, N, K;
-    int RT;         // rows per work item (8, 16 or 32)
-    int KCH;        // floats of K per stage (multiple of 128, or K itself when K <= KCH)
-    int num_items;  // ceil(N / RT)
-    int gelu;
-    int* status;
-};
-
-template <int NB, int RPW>  // RPW = RT / 8 rows per consumer warp
-__global__ void __launch_bounds__(kStreamThreads, 1)
-skinny_stream_kernel(const StreamArgs a) {
-    extern __shared__ uint8_t dsm_raw[];
-    uint8_t* dsm = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dsm_raw) + 127) & ~uintptr_t(127));
-    const int stage_bytes = a.RT * a.KCH * 4;
-    float* xs = reinterpret_cast<float*>(dsm);                        // [NB][K]
-    uint8_t* ring = dsm + (((size_t)NB * a.K * 4 + 127) & ~(size_t)127);  // [stages][RT][KCH]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(ring + (size_t)kStreamStages * stage_bytes);
-    uint64_t* full_bar = bars;                      // [stages] bulk copies landed
-    uint64_t* empty_bar = bars + kStreamStages;     // [stages] the eight consumer warps are done
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * kStreamStages);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStreamStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 8); }
-        *abort_flag = 0;
-        fence_barrier_init();
-    }
-    griddep_wait();
-    // x, zero-padded to NB rows
-    for (int i = threadIdx.x; i < NB * (a.K / 4); i += kStreamThreads) {
-        const int b = i / (a.K / 4), k4 = i % (a.K / 4);
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (b < a.B) v = *reinterpret_cast<const float4*>(a.x + (size_t)b * a.K + k4 * 4);
-        reinterpret_cast<float4*>(xs)[i] = v;
-    }
-    __syncthreads();
-    griddep_launch_dependents();
-    const int kchunks = (a.K + a.KCH - 1) / a.KCH;
-    if (warp == 0) {
-        if (lane == 0) {
-            bool ok = true;
-            uint32_t it = 0;
-            for (int item = blockIdx.x; item < a.num_items && ok; item += gridDim.x) {
-                const int n0 = item * a.RT;
-                const int rows = min(a.RT, a.N - n0);
-                for (int c = 0; c < kchunks; ++c, ++it) {
-                    const int s = it % kStreamStages;
-                    if (!mbar_wait(&empty_bar[s], ((it / kStreamStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                    const int kc0 = c * a.KCH, kc = min(a.KCH, a.K - kc0);
-                    mbar_arrive_expect_tx(&full_bar[s], (uint32_t)(rows * kc * 4));
-                    uint8_t* dst = ring + (size_t)s * stage_bytes;
-                    if (kc == a.K) {  // whole rows: they are contiguous in memory
-                        bulk_load_1d(dst, a.W + (size_t)n0 * a.K, (uint32_t)(rows * kc * 4), &full_bar[s]);
-                    } else {
-                        for (int r = 0; r < rows; ++r)
-                            bulk_load_1d(dst + (size_t)r * a.KCH * 4, a.W + (size_t)(n0 + r) * a.K + kc0, (uint32_t)(kc * 4), &full_bar[s]);
-                    }
-                }
-            }
-            if (!ok) atomicCAS(a.status, 0, DEV_TIMEOUT_PRODUCER);
-        }
-    } else {
-        const int cw = warp - 1;  // consumer warp: rows cw*RPW .. of every item
-        bool ok = true;
-        uint32_t it = 0;
-        for (int item = blockIdx.x; item < a.num_items; item += gridDim.x) {
-            const int n0 = item * a.RT + cw * RPW;
-            float acc[RPW][NB];
-#pragma unroll
-            for (int r = 0; r < RPW; ++r)
-#pragma unroll
-                for (int b = 0; b < NB; ++b) acc[r][b] = 0.f;
-            for (int c = 0; c < kchunks; ++c, ++it) {
-                const int s = it % kStreamStages;
-                if (ok && !mbar_wait(&full_bar[s], (it / kStreamStages) & 1, abort_flag)) ok = false;
-                const int kc0 = c * a.KCH, kc = min(a.KCH, a.K - kc0);
-                // row stride inside the stage: KCH floats, or K when whole rows were copied
-                const int ld = (kc == a.K) ? a.K : a.KCH;
-                const float* wt = reinterpret_cast<const float*>(ring + (size_t)s * stage_bytes) + (size_t)(cw * RPW) * ld;
-                if (ok && n0 < a.N) {
-                    for (int k = lane * 4; k < kc; k += 128) {
-                        float4 w[RPW];
-#pragma unroll
-                        for (int r = 0; r < RPW; ++r) w[r] = *reinterpret_cast<const float4*>(wt + (size_t)r * ld + k);
-#pragma unroll
-                        for (int b = 0; b < NB; ++b) {
-                            const float4 xv = *reinterpret_cast<const float4*>(xs + (size_t)b * a.K + kc0 + k);
-#pragma unroll
-                            for (int r = 0; r < RPW; ++r)
-                                acc[r][b] += (w[r].x * xv.x + w[r].y * xv.y) + (w[r].z * xv.z + w[r].w * xv.w);
-                        }
-                    }
-                }
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&empty_bar[s]);
-            }
-#pragma unroll
-            for (int r = 0; r < RPW; ++r)
+            for (int r = 0; r < ROWS; ++r)
 #pragma unroll
                 for (int b = 0; b < NB; ++b) {
-                    float v = acc[r][b];
-#pragma unroll
-                    for (int sft = 16; sft >= 1; sft >>= 1) v += __shfl_xor_sync(0xffffffffu, v, sft);
-                    acc[r][b] = v;
-                }
-#pragma unroll
-            for (int r = 0; r < RPW; ++r)
-#pragma unroll
-                for (int b = 0; b < NB; ++b) {
-                    if (((r * NB + b) & 31) == lane && n0 + r < a.N && n0 + r < item * a.RT + a.RT && b < a.B && ok) {
-                        float v = acc[r][b] + (a.bias ? __ldg(a.bias + n0 + r) : 0.f);
+                    if (((r * NB + b) & 31) == lane && n0 + r < N && b < B) {
+                        float v = acc[r][b] + bias_r[r];
                         if (a.gelu) v = gelu_tanh(v);
-                        a.out[(size_t)b * a.N + n0 + r] = v;
+                        a.out[(size_t)b * N + n0 + r] = v;
                     }
                 }
         }
-        if (!ok && lane == 0) atomicCAS(a.status, 0, DEV_TIMEOUT_EPILOGUE);
     }
 }
 
@@ -525,60 +406,29 @@ int launch_skinny_gemm(b200_ctx* ctx, float* out, const float* x, const float* W
     if (ln_w && (K > 1664 || !ln_b || !resid_out || resid_out == x)) return B200_ERR_SHAPE;
     const int nb = B <= 8 ? 8 : 16;
     const size_t x_bytes = ((size_t)nb * K * 4 + 127) & ~(size_t)127;
-    // Wide outputs (the lm-head) go through the streamed kernel; it has no layernorm prologue, so
-    // there the caller keeps the separate kernel.
-    static const bool no_stream = getenv("B200_DECODE_NO_STREAM") != nullptr;
-    if (!ln_w && N >= 64 * ctx->num_sms && x_bytes <= 98304 && !no_stream) {
-        StreamArgs a;
-        a.out = out; a.x = x; a.W = W; a.bias = bias; a.B = B; a.N = N; a.K = K; a.gelu = gelu; a.status = ctx->d_status;
-        int rt = 32;
-        const size_t budget = (size_t)222 * 1024 - x_bytes - 256;  // for the stages
-        // floats of K per stage: all of K if two stages of whole rows fit, else a multiple of 128
-        int kch = K;
-        while ((size_t)kStreamStages * rt * kch * 4 > budget) {
-            if (kch > 1024 || rt == 8) kch = ((kch / 2 + 127) / 128) * 128;
-            else rt /= 2;
-            if (kch < 128) return B200_ERR_LIMIT;
-        }
-        a.RT = rt; a.KCH = kch; a.num_items = (N + rt - 1) / rt;
-        const size_t smem = 128 + x_bytes + (size_t)kStreamStages * rt * kch * 4 + 256;
-        const int grid = a.num_items < ctx->num_sms ? a.num_items : ctx->num_sms;
-        cudaError_t le = cudaSuccess;
-#define B200_STREAM(NB, RPW)                                                                                         \
-        do {                                                                                                         \
-            static bool attr_set[64] = {};                                                                           \
-            if (!attr_set[ctx->device & 63]) {                                                                       \
-                B200_CUDA(ctx, cudaFuncSetAttribute(skinny_stream_kernel<NB, RPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024)); \
-                attr_set[ctx->device & 63] = true;                                                                   \
-            }                                                                                                        \
-            le = launch_pdl(ctx, skinny_stream_kernel<NB, RPW>, dim3(grid), dim3(kStreamThreads), smem, a);          \
-        } while (0)
-        if (nb == 8) { if (rt == 32) B200_STREAM(8, 4); else if (rt == 16) B200_STREAM(8, 2); else B200_STREAM(8, 1); }
-        else { if (rt == 32) B200_STREAM(16, 4); else if (rt == 16) B200_STREAM(16, 2); else B200_STREAM(16, 1); }
-#undef B200_STREAM
-        ctx->launches++;
-        B200_CUDA(ctx, le);
-        return B200_OK;
-    }
     if (x_bytes > (size_t)200 * 1024) return B200_ERR_LIMIT;
     SkinnyArgs a;
     a.out = out; a.x = x; a.W = W; a.bias = bias; a.branch = branch; a.ln_w = ln_w; a.ln_b = ln_b; a.resid_out = resid_out;
     a.B = B; a.N = N; a.K = K; a.gelu = gelu;
-    const int rows = 2;  // per warp
-    const int groups = (N + rows - 1) / rows, batches = (groups + 7) / 8;
-    const int grid = batches < 2 * ctx->num_sms ? batches : 2 * ctx->num_sms;
+    constexpr int rows = 2;  // per warp
+    const int groups = (N + rows - 1) / rows;
+    const int batches = (groups + 7) / 8;
+    // one wave: a CTA stages the input rows (and normalises them) once and then loops over its batches
+    const int grid = batches < ctx->num_sms ? batches : ctx->num_sms;
+    const int nv = !ln_w ? 0 : (K <= 768 ? 6 : 13);
+    const size_t smem = x_bytes + (ln_w ? (size_t)2 * K * 4 : 0);
     cudaError_t le = cudaSuccess;
-#define B200_SKINNY(NB, ROWS)                                                                                       \
+#define B200_SKINNY(NB, NV)                                                                                     \
     do {                                                                                                            \
         static bool attr_set[64] = {};                                                                              \
         if (!attr_set[ctx->device & 63]) {                                                                          \
-            B200_CUDA(ctx, cudaFuncSetAttribute(skinny_gemm_kernel<NB, ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
+            B200_CUDA(ctx, cudaFuncSetAttribute(skinny_gemm_kernel<NB, rows, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
             attr_set[ctx->device & 63] = true;                                                                      \
         }                                                                                                           \
-        le = launch_pdl(ctx, skinny_gemm_kernel<NB, ROWS>, dim3(grid), dim3(kSkinnyThreads), x_bytes + (ln_w ? (size_t)2 * K * 4 : 0), a);           \
+        le = launch_pdl(ctx, skinny_gemm_kernel<NB, rows, NV>, dim3(grid), dim3(kSkinnyThreads), smem, a);      \
     } while (0)
-    if (nb == 8) B200_SKINNY(8, 2);
-    else B200_SKINNY(16, 2);
+    if (nb == 8) { if (nv == 0) B200_SKINNY(8, 0); else if (nv == 6) B200_SKINNY(8, 6); else B200_SKINNY(8, 13); }
+    else { if (nv == 0) B200_SKINNY(16, 0); else if (nv == 6) B200_SKINNY(16, 6); else B200_SKINNY(16, 13); }
 #undef B200_SKINNY
     ctx->launches++;
     B200_CUDA(ctx, le);
