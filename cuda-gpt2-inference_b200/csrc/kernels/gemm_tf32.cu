@@ -300,7 +300,7 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
     // CTA pairs pull a third less operand traffic out of L2 per flop and win where there are many
     // tiles per SM (wide outputs: lm-head, GPT-2 XL shapes); with a few tiles per SM the
     // single-CTA kernel's finer N tiles quantise better.  B200_GEMM_PAIR=0/1 forces the choice.
-    static const int pair_env = [] { const char* e = getenv("B200_GEMM_PAIR"); return e ? (e[0] == '0' ? 0 : 1) : -1; }();
+    static const int pair_env = [] { const char* e = getenv("B200_GEMM_PAIR"); return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1; }();
     const bool use_pair = pair_env >= 0 ? pair_env == 1 : (N >= 4096 && M >= 2048);
     if (!x3 && use_pair) return launch_gemm_tf32_pair(ctx, out, inp, weight, bias, residual, M, K, N, flags, argmax_keys, argmax_cols);
     const int num_m = (M + BM - 1) / BM;
