@@ -24,7 +24,7 @@ namespace b200 {
 namespace {
 
 constexpr int kSkinnyThreads = 256;
-constexpr int kSkinnyKC = 1024;  // floats of K staged per pass (x chunk: NB * 4 KB of shared memory)
+constexpr int kSkinnyKC = 1024;  // floats of K whose weights a warp requests at once (8 float4 per lane and row)
 constexpr int kSkinnySteps = kSkinnyKC / 128;  // a warp covers 128 floats of a row per step
 
 // Optional prologue (ln_w != nullptr): the input rows are first formed as
