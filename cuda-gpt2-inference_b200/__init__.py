@@ -43,7 +43,7 @@ EXPORTS = (
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
     "b200_gpt2_forward_static",
-    "b200_gpt2_enable_kv_cache", "b200_gpt2_prefill", "b200_gpt2_decode_step", "b200_gpt2_decode_step_host",
+    "b200_gpt2_enable_kv_cache", "b200_gpt2_prefill", "b200_gpt2_decode_step", "b200_gpt2_decode_step_host", "b200_gpt2_generate_greedy",
     "b200_gpt2_create_tp", "b200_gpt2_set_allreduce", "b200_gpt2_param_offsets_tp", "b200_gpt2_shard_params_host",
 )
 
@@ -123,6 +123,7 @@ def lib() -> C.CDLL:
         l.b200_gpt2_prefill.argtypes = [vp, vp, i, i]
         l.b200_gpt2_decode_step.argtypes = [vp, vp, i, i]
         l.b200_gpt2_decode_step_host.argtypes = [vp, vp, i, i, vp, vp]
+        l.b200_gpt2_generate_greedy.argtypes = [vp, vp, i, i, i, vp]
         l.b200_gpt2_create_tp.argtypes = [C.POINTER(vp), vp, vp, i, i, i, i]
         l.b200_gpt2_set_allreduce.argtypes = [vp, ALLREDUCE_FN, vp]
         l.b200_gpt2_param_offsets_tp.argtypes = [vp, i, i, C.POINTER(sz)]
@@ -400,6 +401,11 @@ class GPT2:
     def decode_step_host(self, tokens_host, B: int, pos: int, logits_host=None, argmax_host=None):
         self.ctx.check(lib().b200_gpt2_decode_step_host(self._h, _ptr(tokens_host), B, pos, _ptr(logits_host),
                                                         _ptr(argmax_host)), "gpt2_decode_step_host")
+
+    def generate_greedy(self, prompt_host, B: int, T0: int, n_new: int, out_host):
+        """Greedy continuation: prompt_host int32 [B,T0] -> out_host int32 [B,n_new]; synchronous."""
+        self.ctx.check(lib().b200_gpt2_generate_greedy(self._h, _ptr(prompt_host), B, T0, n_new, _ptr(out_host)),
+                       "gpt2_generate_greedy")
 
     def set_profile(self, enabled: bool):
         self.ctx.check(lib().b200_gpt2_set_profile(self._h, int(enabled)), "set_profile")

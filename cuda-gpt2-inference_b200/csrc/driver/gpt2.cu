@@ -35,6 +35,7 @@ struct b200_gpt2 {
     float* resid2 = nullptr;                     // second residual buffer of the decode step [16][C]
     float* att_partial = nullptr;                // decode attention: softmax states of the position splits
     unsigned int* att_counters = nullptr;        // ... and their arrival counters (zero between launches)
+    int* gen_tokens = nullptr;                   // greedy generation: prompt and continuation [max_B][max_T]
     std::map<int, cudaGraphExec_t> decode_graphs;  // by B (the position is read from pos_dev)
     int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
     // tensor parallelism (Megatron style): this rank's share of the attention heads, of the MLP
@@ -328,6 +329,7 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     if (m->resid2) cudaFree(m->resid2);
     if (m->att_partial) cudaFree(m->att_partial);
     if (m->att_counters) cudaFree(m->att_counters);
+    if (m->gen_tokens) cudaFree(m->gen_tokens);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
     void* ptrs[] = {m->params, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
                     m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->kcache, m->vcache};
@@ -448,6 +450,7 @@ int b200_gpt2_enable_kv_cache(b200_gpt2* m) {
     if (e == cudaSuccess) e = cudaMalloc(&m->att_partial, (size_t)16 * m->cfg.num_heads * 4 * 66 * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&m->att_counters, (size_t)16 * m->cfg.num_heads * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(m->att_counters, 0, (size_t)16 * m->cfg.num_heads * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMalloc(&m->gen_tokens, (size_t)m->max_B * m->max_T * sizeof(int));
     if (e != cudaSuccess) {
         cudaFree(m->kcache);
         if (m->vcache) cudaFree(m->vcache);
@@ -587,6 +590,49 @@ int b200_gpt2_decode_step_host(b200_gpt2* m, const int* tokens_host, int B, int 
     }
     if (logits_host)
         B200_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, (size_t)B * Vp * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    return b200_ctx_sync_check(ctx);
+}
+
+int b200_gpt2_generate_greedy(b200_gpt2* m, const int* prompt_host, int B, int T0, int n_new, int* out_host) {
+    if (!m || !prompt_host || !out_host) return B200_ERR_NULL;
+    if (!m->kcache) return B200_ERR_STATE;
+    if (B <= 0 || B > 16 || B > m->max_B || T0 < 1 || n_new < 1 || T0 + n_new > m->max_T) return B200_ERR_SHAPE;
+    b200_ctx* ctx = m->ctx;
+    const int V = m->cfg.vocab_size, Vp = m->cfg.padded_vocab_size;
+    // gen holds the prompt [B,T0] and, behind it, the continuation [B,n_new]; m->argmax doubles as
+    // the current column of token ids [B] (m->tokens belongs to the decode step's graph replay)
+    int* gen = m->gen_tokens;
+    int* rec = gen + (size_t)B * T0;
+    B200_CUDA(ctx, cudaMemcpyAsync(gen, prompt_host, (size_t)B * T0 * 4, cudaMemcpyHostToDevice, ctx->stream));
+    int st;
+    if (T0 % 64 == 0) {
+        st = b200_gpt2_prefill(m, gen, B, T0);
+        if (st != B200_OK) return st;
+        // arg-max of the last prompt position of every sequence: rows T0-1, 2*T0-1, ... of the logits
+        for (int b = 0; b < B; ++b) {
+            st = b200::launch_argmax_rows(ctx, m->argmax + b, m->logits + ((size_t)b * T0 + T0 - 1) * Vp, 1, V, Vp);
+            if (st != B200_OK) return st;
+        }
+    } else {
+        for (int t = 0; t < T0; ++t) {
+            // column t of the prompt, gathered into a contiguous [B] (the decode step reads B ids in a row)
+            B200_CUDA(ctx, cudaMemcpy2DAsync(m->argmax, 4, gen + t, (size_t)T0 * 4, 4, B, cudaMemcpyDeviceToDevice, ctx->stream));
+            st = b200_gpt2_decode_step(m, m->argmax, B, t);
+            if (st != B200_OK) return st;
+        }
+        st = b200::launch_argmax_rows(ctx, m->argmax, m->logits, B, V, Vp);
+        if (st != B200_OK) return st;
+    }
+    for (int i = 0; i < n_new; ++i) {
+        // m->argmax holds generated token i of every sequence: record it, then feed it at position T0 + i
+        B200_CUDA(ctx, cudaMemcpy2DAsync(rec + i, (size_t)n_new * 4, m->argmax, 4, 4, B, cudaMemcpyDeviceToDevice, ctx->stream));
+        if (i + 1 == n_new) break;
+        st = b200_gpt2_decode_step(m, m->argmax, B, T0 + i);
+        if (st != B200_OK) return st;
+        st = b200::launch_argmax_rows(ctx, m->argmax, m->logits, B, V, Vp);
+        if (st != B200_OK) return st;
+    }
+    B200_CUDA(ctx, cudaMemcpyAsync(out_host, rec, (size_t)B * n_new * 4, cudaMemcpyDeviceToHost, ctx->stream));
     return b200_ctx_sync_check(ctx);
 }
 

@@ -221,6 +221,13 @@ int b200_gpt2_prefill(b200_gpt2* model, const int* tokens, int B, int T);
 int b200_gpt2_decode_step(b200_gpt2* model, const int* tokens, int B, int pos);
 int b200_gpt2_decode_step_host(b200_gpt2* model, const int* tokens_host, int B, int pos,
                                float* logits_host, int* argmax_host);
+/* Greedy generation on top of the calls above.  prompt_host: int32 [B,T0] (T0 >= 1); out_host:
+ * int32 [B,n_new] receives, per sequence, the arg-max continuation of n_new tokens
+ * (T0 + n_new <= max_T).  If T0 is a multiple of 64 the prompt goes through the tensor-core
+ * prefill, otherwise it is fed token by token.  The token ids stay on the device between steps
+ * (the arg-max of a step is the input of the next); synchronises once at the end. */
+int b200_gpt2_generate_greedy(b200_gpt2* model, const int* prompt_host, int B, int T0, int n_new,
+                              int* out_host);
 
 /* ---- tensor parallelism (optional; Megatron style, for models like GPT-2 XL) --------------
  * Rank r of tp_size holds the q/k/v rows and attn-proj input columns of its share of the heads

@@ -81,3 +81,31 @@ def test_decode_preconditions(pkg, orc, ctx):
     assert lib.b200_gpt2_decode_step(model._h, tok.data_ptr(), 3, 0) == pkg.B200_ERR_SHAPE   # B beyond max_B
     assert lib.b200_gpt2_prefill(model._h, tok.data_ptr(), 2, 32) == pkg.B200_ERR_SHAPE      # T % 64
     model.close()
+
+
+@pytest.mark.parametrize("T0,use_graph", [(5, 0), (64, 1)])
+def test_generate_greedy_follows_the_oracle(pkg, orc, ctx, T0, use_graph):
+    """Greedy continuation: every generated token must be the arg-max of the oracle's logits for
+    the sequence so far.  T0 = 5 feeds the prompt token by token (fp32 path throughout); T0 = 64
+    goes through the tensor-core prefill.  A near-tie in the oracle's own logits is allowed to fall
+    either way: then the check continues with the token the engine chose."""
+    B, n_new = 3, 6
+    cfg, ocfg, params, model = _model(pkg, orc, ctx, dict(num_layers=2), B, 128, 0)
+    model.set_options(round_operands=0, use_graph=use_graph)
+    prompt = orc.fill_tokens((B, T0), seed=21, vocab=cfg.vocab_size)
+    out = np.empty((B, n_new), np.int32)
+    model.generate_greedy(np.ascontiguousarray(prompt), B, T0, n_new, out)
+    seq = prompt.copy()
+    V = cfg.vocab_size
+    for i in range(n_new):
+        T = seq.shape[1]
+        Tpad = (T + 63) // 64 * 64  # the oracle's forward is causal: padding behind the sequence changes nothing
+        padded = np.zeros((B, Tpad), np.int32)
+        padded[:, :T] = seq
+        logits = orc.gpt2_forward(params, ocfg, padded, precise=True)[:, T - 1, :V]
+        for b in range(B):
+            top2 = np.sort(logits[b])[-2:]
+            if out[b, i] != logits[b].argmax():
+                assert top2[1] - top2[0] < 2e-3 and logits[b, out[b, i]] >= top2[0] - 1e-6, (b, i)
+        seq = np.concatenate([seq, out[:, i:i + 1]], axis=1)
+    model.close()
