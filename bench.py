@@ -330,6 +330,24 @@ def run_ours(args):
         x3_ms = max_over_ranks(ev2.elapsed_time(ev3)) / n_x3
         model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32)
 
+    # ------------------------------------------------ the same workload with bf16 GEMM operands
+    # (optional reduced-precision mode; never the headline, which stays TF32)
+    bf16_ms = None
+    if not xl and not args.tp:
+        model.set_options(round_operands=1, gemm_mode=pkg.B200_BF16, lmhead_mode=pkg.B200_BF16)
+        for _ in range(3):
+            model.forward(tok_dev, B, T)
+        barrier()
+        ev4, ev5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev4.record(stream)
+        for _ in range(args.steps):
+            model.forward(tok_dev, B, T)
+        ev5.record(stream)
+        barrier()
+        ctx.sync_check()
+        bf16_ms = max_over_ranks(ev4.elapsed_time(ev5)) / args.steps
+        model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32)
+
     # ---------------------------------------------------------------- end-to-end arm
     for _ in range(2):
         model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
@@ -443,6 +461,10 @@ def run_ours(args):
         "tf32x3": None if x3_ms is None else {
             "value": replicas * B * T / (x3_ms * 1e-3), "unit": UNIT, "ms_per_step": x3_ms,
             "note": "same workload with gemm_mode = lmhead_mode = B200_TF32X3 (split-operand GEMMs and attention)"},
+        "bf16_operands": None if bf16_ms is None else {
+            "value": replicas * B * T / (bf16_ms * 1e-3), "unit": UNIT, "ms_per_step": bf16_ms,
+            "note": "same workload with gemm_mode = lmhead_mode = B200_BF16 (bf16 GEMM operands, fp32 accumulation; "
+                    "reduced precision, not comparable with the headline)"},
         "decode": decode,
     }
     print(json.dumps(line), flush=True)
@@ -479,6 +501,11 @@ def run_kernel_sweep(args):
                                        (1600, 4800, 0, False, True), (1600, 6400, 1, False, True), (6400, 1600, 0, True, True)):
             for mode in ((0, 1) if args.modes == "both" else (0,)):
                 cases.append(("matmul", dict(K=K, N=N, act=act, res=res, bias=bias, mode=mode)))
+    if args.op in ("matmul_bf16", "all"):
+        for (K, N, act, bias, out_h) in ((768, 2304, 0, True, False), (768, 768, 0, True, False), (768, 3072, 1, True, True),
+                                         (3072, 768, 0, True, False), (768, 50304, 0, False, False),
+                                         (1600, 4800, 0, True, False), (1600, 6400, 1, True, True), (6400, 1600, 0, True, False)):
+            cases.append(("matmul_bf16", dict(K=K, N=N, act=act, bias=bias, out_h=out_h)))
     if args.op in ("attention", "all"):
         cases += [("attention", dict(NH=12)), ("attention", dict(NH=25))]
     if args.op in ("layernorm", "all"):
@@ -501,6 +528,15 @@ def run_kernel_sweep(args):
             fn = lambda: ctx.matmul_forward(out, x, w, bias, Bb, Tt, K, N, act=c["act"], residual=res, mode=c["mode"])
             work, unit, peak = 2.0 * M * K * N / 1e12, "TFLOP/s", peaks["bf16_burst"] / 2
             name = f"matmul {K}->{N}" + ("+gelu" if c["act"] else "") + ("+residual" if c["res"] else "") + (" 3xTF32" if c["mode"] else "")
+        elif op == "matmul_bf16":
+            K, N = c["K"], c["N"]
+            x, w = randn(Bb, Tt, K).to(torch.bfloat16), randn(N, K, std=0.02).to(torch.bfloat16)
+            bias = randn(N, std=0.01) if c["bias"] else None
+            out = None if c["out_h"] else torch.empty(Bb, Tt, N, device="cuda")
+            outh = torch.empty(Bb, Tt, N, device="cuda", dtype=torch.bfloat16) if c["out_h"] else None
+            fn = lambda: ctx.matmul_forward_bf16(out, outh, x, w, bias, Bb, Tt, K, N, act=c["act"])
+            work, unit, peak = 2.0 * M * K * N / 1e12, "TFLOP/s", peaks["bf16_burst"]
+            name = f"matmul bf16 {K}->{N}" + ("+gelu" if c["act"] else "") + (" bf16 out" if c["out_h"] else "")
         elif op == "attention":
             NH = c["NH"]
             Cc = NH * 64
@@ -539,7 +575,7 @@ def run_kernel_sweep(args):
                 fn = lambda k=0: ctx.encoder_forward(S[k]["out"], tok, wte, wpe, Bb, Tt, Cc)
                 work = ((2.0 * M * Cc + Tt * Cc) * 4 + M * 4) / 1e9
             unit, peak, name = "GB/s", peaks["hbm_gbs"], f"{op} [8192,{Cc}]"
-        streaming = args.stream > 1 and op not in ("matmul", "attention")
+        streaming = args.stream > 1 and op not in ("matmul", "matmul_bf16", "attention")
         torch.cuda.synchronize()
         for _ in range(args.warmup):
             fn()
@@ -581,7 +617,7 @@ def main():
     ap.add_argument("--tp", action="store_true",
                     help="with --gpus N > 1: one tensor-parallel group over all ranks instead of batch sharding")
     ap.add_argument("--op", default=None,
-                    choices=["all", "matmul", "attention", "layernorm", "fused_residual_layernorm", "rowwise"],
+                    choices=["all", "matmul", "matmul_bf16", "attention", "layernorm", "fused_residual_layernorm", "rowwise"],
                     help="per-kernel sweep at 8192 rows instead of the forward benchmark")
     ap.add_argument("--case", type=int, default=None, help="with --op: run only this case of the family")
     ap.add_argument("--modes", default="tf32", choices=["tf32", "both"], help="with --op matmul: also time 3xTF32")

@@ -25,14 +25,14 @@ LIB_PATH = os.path.join(_HERE, "lib", "libb200gpt2.so")
 B200_OK = 0
 (B200_ERR_NULL, B200_ERR_SHAPE, B200_ERR_ALIGN, B200_ERR_CUDA, B200_ERR_DEVICE, B200_ERR_TIMEOUT,
  B200_ERR_STATE, B200_ERR_LIMIT) = range(1, 9)
-B200_TF32, B200_TF32X3 = 0, 1
+B200_TF32, B200_TF32X3, B200_BF16 = 0, 1, 2
 ACT_NONE, ACT_GELU = 0, 1
 
 EXPORTS = (
     "b200_ctx_create", "b200_ctx_destroy", "b200_ctx_set_stream", "b200_ctx_sync_check",
     "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
     "b200_ctx_last_error", "b200_ctx_wait_timeout_probe",
-    "b200_matmul_forward", "b200_attention_forward", "b200_attention_forward_x3", "b200_layernorm_forward",
+    "b200_matmul_forward", "b200_matmul_forward_bf16", "b200_convert_bf16", "b200_attention_forward", "b200_attention_forward_x3", "b200_layernorm_forward",
     "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
     "b200_encoder_forward",
     "matmul_forward", "matmul_forward_gelu", "attention_forward", "layernorm_forward",
@@ -83,6 +83,8 @@ def lib() -> C.CDLL:
         l.b200_ctx_last_error.argtypes = [vp]
         l.b200_ctx_last_error.restype = C.c_char_p
         l.b200_matmul_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, i]
+        l.b200_matmul_forward_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i]
+        l.b200_convert_bf16.argtypes = [vp, vp, vp, sz]
         l.b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_attention_forward_x3.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_layernorm_forward.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i]
@@ -192,6 +194,14 @@ class Context:
     def matmul_forward(self, out, inp, weight, bias, B, T, Cc, OC, act=ACT_NONE, residual=None, mode=B200_TF32):
         self.check(lib().b200_matmul_forward(self._h, _ptr(out), _ptr(inp), _ptr(weight), _ptr(bias), B, T, Cc, OC,
                                              act, _ptr(residual), mode), "matmul_forward")
+
+    def matmul_forward_bf16(self, out, out_bf16, inp, weight, bias, B, T, Cc, OC, act=ACT_NONE):
+        """inp / weight (and out_bf16, if given) hold bf16 elements; out is fp32."""
+        self.check(lib().b200_matmul_forward_bf16(self._h, _ptr(out), _ptr(out_bf16), _ptr(inp), _ptr(weight), _ptr(bias),
+                                                  B, T, Cc, OC, act), "matmul_forward_bf16")
+
+    def convert_bf16(self, out, inp, n):
+        self.check(lib().b200_convert_bf16(self._h, _ptr(out), _ptr(inp), n), "convert_bf16")
 
     def attention_forward(self, out, qkvr, att, inp, B, T, Cc, NH):
         self.check(lib().b200_attention_forward(self._h, _ptr(out), _ptr(qkvr), _ptr(att), _ptr(inp), B, T, Cc, NH),

@@ -42,6 +42,31 @@ int b200_get_tensor_map(b200_ctx* ctx, CUtensorMap* out, const float* ptr, uint6
     return B200_OK;
 }
 
+int b200_get_tensor_map_bf16(b200_ctx* ctx, CUtensorMap* out, const void* ptr, uint64_t rows,
+                             uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+    TensorMapKey key{ptr, rows, cols, ld, box_rows, box_cols, 2};  // 2: 16-bit elements
+    auto it = ctx->tmap_cache.find(key);
+    if (it != ctx->tmap_cache.end()) { *out = it->second; return B200_OK; }
+    if (!ctx->encode_tiled) return B200_ERR_STATE;
+    if (!b200_aligned16(ptr) || (ld * 2) % 16 != 0) return B200_ERR_ALIGN;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld * 2};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = ctx->encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims,
+                                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        ctx->last_error = "cuTensorMapEncodeTiled (bf16) failed with CUresult " + std::to_string((int)r);
+        return B200_ERR_CUDA;
+    }
+    if (ctx->tmap_cache.size() > 4096) ctx->tmap_cache.clear();
+    ctx->tmap_cache.emplace(key, m);
+    *out = m;
+    return B200_OK;
+}
+
 extern "C" {
 
 const char* b200_status_string(int s) {
@@ -149,6 +174,26 @@ int b200_matmul_forward(b200_ctx* ctx, float* out, const float* inp, const float
     if (mode != B200_TF32 && mode != B200_TF32X3) return B200_ERR_SHAPE;
     return b200::launch_gemm_tf32(ctx, out, inp, weight, bias, residual, B * T, C, OC,
                                   act == B200_ACT_GELU ? b200::GEMM_GELU : 0, mode);
+}
+
+int b200_matmul_forward_bf16(b200_ctx* ctx, float* out, uint16_t* out_bf16, const uint16_t* inp,
+                             const uint16_t* weight, const float* bias, int B, int T, int C, int OC, int act) {
+    if (!ctx) return B200_ERR_NULL;
+    if (out_bf16) { REQUIRE_PTR(out_bf16); } else { REQUIRE_PTR(out); }
+    REQUIRE_PTR(inp); REQUIRE_PTR(weight);
+    OPTIONAL_PTR(bias);
+    if (B <= 0 || T <= 0 || C <= 0 || OC <= 0 || C % 8 || OC % 8) return B200_ERR_SHAPE;
+    if ((long long)B * T > 0x7fffffffLL) return B200_ERR_SHAPE;
+    if (act != B200_ACT_NONE && act != B200_ACT_GELU) return B200_ERR_SHAPE;
+    return b200::launch_gemm_bf16(ctx, out, out_bf16, inp, weight, bias, B * T, C, OC,
+                                  act == B200_ACT_GELU ? b200::GEMM_GELU : 0);
+}
+
+int b200_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* inp, size_t n) {
+    if (!ctx) return B200_ERR_NULL;
+    REQUIRE_PTR(out); REQUIRE_PTR(inp);
+    if (n == 0 || n % 4) return B200_ERR_SHAPE;
+    return b200::launch_convert_bf16(ctx, out, inp, n);
 }
 
 int b200_attention_forward(b200_ctx* ctx, float* out, float* qkvr, float* att, const float* inp,

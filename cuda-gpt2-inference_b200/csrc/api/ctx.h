@@ -62,4 +62,8 @@ int b200_get_tensor_map(b200_ctx* ctx, CUtensorMap* out, const float* ptr, uint6
                         uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols,
                         int swizzle_atom32 = 0);
 
+// The same over a matrix of bf16 (16-bit) elements: 128-byte swizzle of 16-byte chunks.
+int b200_get_tensor_map_bf16(b200_ctx* ctx, CUtensorMap* out, const void* ptr, uint64_t rows,
+                             uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+
 inline bool b200_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -23,6 +23,8 @@ struct b200_gpt2 {
     float* wte_rounded = nullptr;  // TF32-rounded copy of wte for the lm-head (round_operands)
     float* qkv_small = nullptr;    // scratch of the 3xTF32 attention (allocated by set_options)
     bool weights_rounded = false;
+    uint16_t* params_h = nullptr;  // bf16 copy of the parameters (same offsets) for the B200_BF16 modes
+    bool params_h_ready = false;
     // activations, sized for max_B * max_T rows
     float *residual = nullptr, *ln_out = nullptr, *qkv = nullptr, *atty = nullptr,
           *branch = nullptr, *fch = nullptr, *logits = nullptr;
@@ -140,6 +142,15 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, bool with_arg
     const size_t* off = m->off;
     const int rnd = m->round_operands ? ROUND_OUT_TF32 : 0;
     const int grnd = m->round_operands ? GEMM_ROUND_OUT_TF32 : 0;
+    // bf16 modes: the operands of the GEMMs are bf16.  The weights come from the bf16 copy of the
+    // parameters; layernorm, attention and the GELU GEMM write their outputs as bf16 into the
+    // front half of the same activation buffers.  Everything between the GEMMs stays fp32.
+    const bool hb = m->gemm_mode == B200_BF16, hl = m->lmhead_mode == B200_BF16;
+    const uint16_t* PH = m->params_h;
+    uint16_t* ln_h = reinterpret_cast<uint16_t*>(m->ln_out);
+    uint16_t* atty_h = reinterpret_cast<uint16_t*>(m->atty);
+    uint16_t* fch_h = reinterpret_cast<uint16_t*>(m->fch);
+    const int ln_flags = hb ? OUT_BF16 : rnd;
     int st;
     const bool prof = m->profile;
 #define STEP(cat, call)                                             \
@@ -150,7 +161,7 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, bool with_arg
         if (prof) { st = prof_end(m); if (st != B200_OK) return st; } \
     } while (0)
     STEP(B200_PROF_ENCODER, launch_encoder(ctx, m->residual, tokens, P + off[0], P + off[1], B, T, C, Vp));
-    STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], M, C, rnd));
+    STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], M, C, ln_flags));
     for (int l = 0; l < L; ++l) {
         const float* qkvw = P + off[4] + (size_t)l * 3 * A * C;
         const float* qkvb = P + off[5] + (size_t)l * 3 * A;
@@ -169,30 +180,39 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, bool with_arg
         // attention needs the unrounded values.
         const bool att_x3 = (m->gemm_mode == B200_TF32X3) && m->qkv_small;
         const int qkv_flags = (!att_x3 && (m->round_operands || m->gemm_mode == B200_TF32X3)) ? GEMM_ROUND_OUT_TF32 : 0;
-        STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * A, qkv_flags, m->gemm_mode));
+        if (hb) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16(ctx, m->qkv, nullptr, ln_h, PH + (qkvw - P), qkvb, M, C, 3 * A, GEMM_ROUND_OUT_TF32));
+        else STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * A, qkv_flags, m->gemm_mode));
         if (m->keep_kv) {
             const size_t per_layer = (size_t)m->max_B * m->max_T * C;
             st = launch_kv_append(ctx, m->kcache + l * per_layer, m->vcache + l * per_layer, m->qkv, B, T, C, 0, m->max_T);
             if (st != B200_OK) return st;
         }
         if (att_x3) STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->atty, m->qkv_small, nullptr, m->qkv, B, T, A, NH));
-        else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, A, NH, rnd));
-        STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, A, C, 0, m->gemm_mode));
+        else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, A, NH, hb ? OUT_BF16 : rnd));
+        if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, m->branch, nullptr, atty_h, PH + (apw - P), apb, M, A, C, 0));
+        else STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, A, C, 0, m->gemm_mode));
         // tensor parallel: every rank holds a partial sum over its heads; one all-reduce per block
         if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
         STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
-                                             m->branch, ln2w, ln2b, M, C, rnd));
-        STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, F, GEMM_GELU | grnd, m->gemm_mode));
-        STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, m->branch, m->fch, fpw, fpb, nullptr, M, F, C, 0, m->gemm_mode));
+                                             m->branch, ln2w, ln2b, M, C, ln_flags));
+        if (hb) {
+            STEP(B200_PROF_GEMM_FC, launch_gemm_bf16(ctx, nullptr, fch_h, ln_h, PH + (fcw - P), fcb, M, C, F, GEMM_GELU));
+            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16(ctx, m->branch, nullptr, fch_h, PH + (fpw - P), fpb, M, F, C, 0));
+        } else {
+            STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, F, GEMM_GELU | grnd, m->gemm_mode));
+            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, m->branch, m->fch, fpw, fpb, nullptr, M, F, C, 0, m->gemm_mode));
+        }
         if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
         const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
         const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
         STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
-                                             m->branch, nw, nb, M, C, rnd));
+                                             m->branch, nw, nb, M, C, (l + 1 < L) ? ln_flags : (hl ? OUT_BF16 : rnd)));
     }
     const float* head_w = ((m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0]) + (size_t)m->vp_row0 * C;
     if (with_argmax) B200_CUDA(ctx, cudaMemsetAsync(m->argmax_keys, 0, (size_t)M * 8, ctx->stream));
-    STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, m->vp_local, 0, m->lmhead_mode,
+    if (hl) STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_bf16(ctx, m->logits, nullptr, ln_h, PH + off[0] + (size_t)m->vp_row0 * C, nullptr, M, C, m->vp_local, 0,
+                                                         with_argmax ? m->argmax_keys : nullptr, c.vocab_size));
+    else STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, m->vp_local, 0, m->lmhead_mode,
                                                  with_argmax ? m->argmax_keys : nullptr, c.vocab_size));
     if (with_argmax) {
         st = launch_argmax_decode(ctx, m->argmax, m->argmax_keys, M);
@@ -201,6 +221,25 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, bool with_arg
 #undef STEP
     return B200_OK;
 }
+
+// bf16 copies of the weight matrices (and of wte for the lm-head), made from the parameters as
+// they are at the first bf16 forward
+int bf16_weights_once(b200_gpt2* m) {
+    using namespace b200;
+    if (m->params_h_ready) return B200_OK;
+    b200_ctx* ctx = m->ctx;
+    if (!m->params_h) B200_CUDA(ctx, cudaMalloc(&m->params_h, m->n_params * sizeof(uint16_t)));
+    const int idx[5] = {0, 4, 6, 10, 12};  // wte, qkvw, attprojw, fcw, fcprojw
+    for (int i = 0; i < 5; ++i) {
+        int st = launch_convert_bf16(ctx, m->params_h + m->off[idx[i]], m->params + m->off[idx[i]], m->off[idx[i] + 1] - m->off[idx[i]]);
+        if (st != B200_OK) return st;
+    }
+    m->params_h_ready = true;
+    return B200_OK;
+}
+
+// what a forward needs done to the weights for the current modes
+int prepare_weights(b200_gpt2* m);
 
 int round_weights_once(b200_gpt2* m) {
     using namespace b200;
@@ -219,6 +258,17 @@ int round_weights_once(b200_gpt2* m) {
     int st = launch_round_tf32_inplace(ctx, m->wte_rounded, n_wte);
     if (st != B200_OK) return st;
     m->weights_rounded = true;
+    return B200_OK;
+}
+
+int prepare_weights(b200_gpt2* m) {
+    const bool any_bf16 = m->gemm_mode == B200_BF16 || m->lmhead_mode == B200_BF16;
+    if (any_bf16) {  // before any in-place TF32 rounding, so the copy is rounded once only
+        int st = bf16_weights_once(m);
+        if (st != B200_OK) return st;
+    }
+    const bool all_bf16 = m->gemm_mode == B200_BF16 && m->lmhead_mode == B200_BF16;
+    if (m->round_operands && !all_bf16) return round_weights_once(m);
     return B200_OK;
 }
 
@@ -331,7 +381,7 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     if (m->att_counters) cudaFree(m->att_counters);
     if (m->gen_tokens) cudaFree(m->gen_tokens);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
-    void* ptrs[] = {m->params, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
+    void* ptrs[] = {m->params, m->params_h, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
                     m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->kcache, m->vcache};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete m;
@@ -347,13 +397,15 @@ int b200_gpt2_load_params_host(b200_gpt2* m, const float* host_params, size_t co
     B200_CUDA(m->ctx, cudaMemcpyAsync(m->params, host_params, count * 4, cudaMemcpyHostToDevice, m->ctx->stream));
     B200_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
     m->weights_rounded = false;
+    m->params_h_ready = false;
     return B200_OK;
 }
 
 int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int lmhead_mode, int use_graph) {
     if (!m) return B200_ERR_NULL;
-    if ((gemm_mode != B200_TF32 && gemm_mode != B200_TF32X3) || (lmhead_mode != B200_TF32 && lmhead_mode != B200_TF32X3))
-        return B200_ERR_SHAPE;
+    if (gemm_mode < B200_TF32 || gemm_mode > B200_BF16 || lmhead_mode < B200_TF32 || lmhead_mode > B200_BF16) return B200_ERR_SHAPE;
+    // the bf16 copy of the weights follows the unsharded parameter layout
+    if ((gemm_mode == B200_BF16 || lmhead_mode == B200_BF16) && m->tp_size > 1) return B200_ERR_STATE;
     if (m->round_operands != round_operands || m->gemm_mode != gemm_mode || m->lmhead_mode != lmhead_mode) {
         for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
         m->graphs.clear();
@@ -374,8 +426,8 @@ static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, bool with
     if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
     if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
     b200_ctx* ctx = m->ctx;
-    if (m->round_operands) {
-        int st = round_weights_once(m);
+    {
+        int st = prepare_weights(m);
         if (st != B200_OK) return st;
     }
     if (m->tp_size > 1 && !m->allreduce) return B200_ERR_STATE;
@@ -464,8 +516,8 @@ int b200_gpt2_prefill(b200_gpt2* m, const int* tokens, int B, int T) {
     if (!m || !tokens) return B200_ERR_NULL;
     if (!m->kcache) return B200_ERR_STATE;
     if (B <= 0 || B > m->max_B || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
-    if (m->round_operands) {
-        int st = round_weights_once(m);
+    {
+        int st = prepare_weights(m);
         if (st != B200_OK) return st;
     }
     m->keep_kv = true;  // eager (the replayed graphs are those of the plain forward)

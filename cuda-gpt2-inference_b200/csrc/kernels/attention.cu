@@ -35,6 +35,7 @@
 // P is cut to TF32 before it is both summed and multiplied, so the denominator matches the
 // numerator.  Every wait is time-bounded (see prim/sm100.cuh).  The work counter lives in the
 // context's status area and is put back to zero by the last CTA to finish.
+#include <cuda_bf16.h>
 #include "kernels.h"
 #include "../prim/sm100.cuh"
 
@@ -110,6 +111,7 @@ struct AttArgs {
     float scale_log2;
     int round_out;  // store TF32-rounded outputs (they feed only the next GEMM)
     int tma_out;    // T is a multiple of 128: whole tiles leave through shared memory and a TMA store
+    int out_bf16;   // out addresses bf16 elements (the next GEMM runs with bf16 operands)
     int* status;    // [0] error word; [kWorkWord], [kWorkWord+1]: work and finished-CTA counters (zero between launches)
 };
 
@@ -476,6 +478,27 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
                 // different rows per instruction.
                 if (threadIdx.x == 64) tma_store_wait_read();  // the previous tile has left the buffer
                 softmax_bar_sync();
+                if (args.out_bf16) {
+                    // 64 bf16 columns are one 128-byte row: this thread's 32 columns are chunks
+                    // 4*hf .. 4*hf+3 of row r, and the tile leaves as one {128 x 64} store
+                    uint4* rowh = reinterpret_cast<uint4*>(out_s + r * 128);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        uint4 pk;
+                        __nv_bfloat162 hh;
+                        hh = __floats2bfloat162_rn(o_acc[8 * i] * inv_l, o_acc[8 * i + 1] * inv_l); pk.x = *reinterpret_cast<uint32_t*>(&hh);
+                        hh = __floats2bfloat162_rn(o_acc[8 * i + 2] * inv_l, o_acc[8 * i + 3] * inv_l); pk.y = *reinterpret_cast<uint32_t*>(&hh);
+                        hh = __floats2bfloat162_rn(o_acc[8 * i + 4] * inv_l, o_acc[8 * i + 5] * inv_l); pk.z = *reinterpret_cast<uint32_t*>(&hh);
+                        hh = __floats2bfloat162_rn(o_acc[8 * i + 6] * inv_l, o_acc[8 * i + 7] * inv_l); pk.w = *reinterpret_cast<uint32_t*>(&hh);
+                        rowh[(hf * 4 + i) ^ (r & 7)] = pk;
+                    }
+                    fence_proxy_async_smem();
+                    softmax_bar_sync();
+                    if (threadIdx.x == 64 && ok) {
+                        tma_store_2d(&tmap_out, h * HS, row_base + q0, out_s);
+                        tma_store_commit();
+                    }
+                } else {
                 float4* row = reinterpret_cast<float4*>(out_s + hf * kBlk + r * 128);
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
@@ -490,6 +513,19 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
                     tma_store_2d(&tmap_out, h * HS, row_base + q0, out_s);
                     tma_store_2d(&tmap_out, h * HS + 32, row_base + q0, out_s + kBlk);
                     tma_store_commit();
+                }
+                }
+            } else if (ok && t_idx < args.T && args.out_bf16) {
+                uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(args.out) + ((size_t)(row_base + t_idx) * args.C) + h * HS + hf * 32);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint4 pk;
+                    __nv_bfloat162 hh;
+                    hh = __floats2bfloat162_rn(o_acc[8 * i] * inv_l, o_acc[8 * i + 1] * inv_l); pk.x = *reinterpret_cast<uint32_t*>(&hh);
+                    hh = __floats2bfloat162_rn(o_acc[8 * i + 2] * inv_l, o_acc[8 * i + 3] * inv_l); pk.y = *reinterpret_cast<uint32_t*>(&hh);
+                    hh = __floats2bfloat162_rn(o_acc[8 * i + 4] * inv_l, o_acc[8 * i + 5] * inv_l); pk.z = *reinterpret_cast<uint32_t*>(&hh);
+                    hh = __floats2bfloat162_rn(o_acc[8 * i + 6] * inv_l, o_acc[8 * i + 7] * inv_l); pk.w = *reinterpret_cast<uint32_t*>(&hh);
+                    o[i] = pk;
                 }
             } else if (ok && t_idx < args.T) {
                 float* o = args.out + ((size_t)(row_base + t_idx) * args.C) + h * HS + hf * 32;
@@ -546,8 +582,10 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
     AttArgs a;
     a.tma_out = (T % BQ == 0) ? 1 : 0;
     CUtensorMap tmo = tm;  // not used unless whole tiles are stored
+    a.out_bf16 = (flags & OUT_BF16) ? 1 : 0;
     if (a.tma_out) {
-        st = b200_get_tensor_map(ctx, &tmo, out, (uint64_t)B * T, (uint64_t)C, (uint64_t)C, BQ, 32);
+        if (a.out_bf16) st = b200_get_tensor_map_bf16(ctx, &tmo, out, (uint64_t)B * T, (uint64_t)C, (uint64_t)C, BQ, 64);
+        else st = b200_get_tensor_map(ctx, &tmo, out, (uint64_t)B * T, (uint64_t)C, (uint64_t)C, BQ, 32);
         if (st != B200_OK) return st;
     }
     a.out = out; a.lse = lse; a.B = B; a.T = T; a.C = C; a.NH = NH;

@@ -1,6 +1,7 @@
 // Pieces shared by the single-CTA and the CTA-pair TF32 GEMM kernels: the argument block and
 // the epilogue that drains one 128 x BN accumulator out of tensor memory.
 #pragma once
+#include <cuda_bf16.h>
 #include "kernels.h"
 #include "../prim/sm100.cuh"
 
@@ -8,11 +9,13 @@ namespace b200 {
 
 constexpr int kGemmBM = 128;       // accumulator rows per CTA (tensor-memory lanes)
 constexpr int kGemmBK = 32;        // fp32 elements per K block = 128 bytes = one swizzle row
+constexpr int kGemmBKH = 64;       // bf16 elements per K block: the same 128 bytes
 constexpr int kGemmMaxSmem = 232448;  // 227 KB
 constexpr int kGemmEpiBytes = 4 * 2 * 4096;  // per epilogue warp two {32 rows x 128 B} buffers
 
 struct GemmArgs {
     float* out;
+    uint16_t* out_h;  // not null: the output is written as bf16 here instead (plain / bias / GELU epilogue only)
     const float* bias;
     const float* residual;
     int M, N, K;
@@ -48,10 +51,13 @@ __device__ __forceinline__ float argmax_dec(uint32_t k) {
 //   tmem_acc : tensor-memory address of the accumulator (column offset included, lane 0)
 //   row0     : global row of accumulator lane q*32
 //   col0     : global column of accumulator column 0
-//   stage2   : this warp's two 4 KB staging buffers
+//   stage2   : this warp's nbuf (1 or 2) staging buffers of 4 KB
+//   c_begin, c_end : the 32-column chunks of the accumulator this warp drains (two warps can share
+//                    a lane quarter and split the columns; with a bf16 output c_begin is even)
 template <int BN>
 __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, const CUtensorMap* tmap_out, uint32_t tmem_acc,
-                                                       int q, int lane, int row0, int col0, uint8_t* stage2) {
+                                                       int q, int lane, int row0, int col0, uint8_t* stage2,
+                                                       int c_begin = 0, int c_end = BN / 32, int nbuf = 2) {
     const bool do_gelu = (args.flags & GEMM_GELU) != 0;
     const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
     const int sub_row = lane >> 3;  // 0..3: row within a group of four
@@ -75,7 +81,8 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         __syncwarp();
     }
 #pragma unroll 1
-    for (int c = 0; c < BN / 32; ++c) {
+    for (int c = c_begin; c < c_end; ++c) {
+        const int ci = c - c_begin;
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r);
         tmem_ld_wait();
@@ -96,11 +103,54 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
                 best_v = argmax_dec((uint32_t)(best_key >> 32));
             }
         }
-        uint8_t* stage = stage2 + (c & 1) * 4096;
+        if (args.out_h) {
+            // bf16 output: 64 columns x 2 bytes fill one 128-byte row, so two 32-column chunks
+            // share a staging buffer and leave as one {32 rows x 64 columns} TMA store
+            uint8_t* sth = stage2 + ((ci >> 1) & (nbuf - 1)) * 4096;
+            const int cbase = col0 + c * 32;
+            if ((ci & 1) == 0 && (ci >> 1) >= nbuf) {  // the store that last used this buffer has read it
+                if (lane == 0) { if (nbuf == 2) tma_store_wait_read_but_one(); else tma_store_wait_read(); }
+                __syncwarp();
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * j + i]);
+                if (args.bias && cbase + 8 * j < args.N) {
+                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(args.bias + cbase + 8 * j));
+                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(args.bias + cbase + 8 * j + 4));
+                    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+                    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                }
+                if (do_gelu) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
+                }
+                uint4 pk;
+                __nv_bfloat162 h;
+                h = __floats2bfloat162_rn(v[0], v[1]); pk.x = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(v[2], v[3]); pk.y = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(v[4], v[5]); pk.z = *reinterpret_cast<uint32_t*>(&h);
+                h = __floats2bfloat162_rn(v[6], v[7]); pk.w = *reinterpret_cast<uint32_t*>(&h);
+                const int chunk = (ci & 1) * 4 + j;
+                *reinterpret_cast<uint4*>(sth + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = pk;
+            }
+            if (ci & 1) {
+                fence_proxy_async_smem();
+                __syncwarp();
+                if (lane == 0 && cbase - 32 < args.N && row0 < args.M) {
+                    tma_store_2d(tmap_out, cbase - 32, row0, sth);
+                    tma_store_commit();
+                }
+            }
+            continue;
+        }
+        uint8_t* stage = stage2 + (ci & (nbuf - 1)) * 4096;
         if (via_tma) {
             const int cbase = col0 + c * 32;
-            if (c >= 2) {  // the store issued two chunks ago has read this buffer
-                if (lane == 0) tma_store_wait_read_but_one();
+            if (ci >= nbuf) {  // the store that last used this buffer has read it
+                if (lane == 0) { if (nbuf == 2) tma_store_wait_read_but_one(); else tma_store_wait_read(); }
                 __syncwarp();
             }
 #pragma unroll
@@ -157,8 +207,9 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
 }
 
 // CTA-pair GEMM (gemm_tf32_pair.cu): 256 x BN tiles computed by two CTAs sharing one UMMA.
+// bf16 != 0: inp and weight hold bf16 elements (kind::f16); out_h as in GemmArgs.
 int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                           const float* bias, const float* residual, int M, int K, int N, int flags,
-                          unsigned long long* argmax_keys, int argmax_cols);
+                          unsigned long long* argmax_keys, int argmax_cols, int bf16 = 0, uint16_t* out_h = nullptr);
 
 }  // namespace b200

@@ -63,7 +63,7 @@ __device__ __forceinline__ float tf32_dropped_part(float x) {
     return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);
 }
 
-template <int BN, bool X3>
+template <int BN, bool X3, bool BF16>
 __global__ void __launch_bounds__(GemmCfg<BN, X3>::THREADS, 1)
 gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                  const __grid_constant__ CUtensorMap tmap_out,
@@ -93,7 +93,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int num_tiles = args.num_m_blocks * args.num_n_blocks;
-    const int num_kb = (args.K + BK - 1) / BK;
+    constexpr int BKE = BF16 ? kGemmBKH : BK;  // elements per 128-byte K block
+    const int num_kb = (args.K + BKE - 1) / BKE;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
@@ -142,8 +143,8 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
                     mbar_arrive_expect_tx(&full_bar[s], Cfg::TX_BYTES);
-                    tma_load_2d(smem_a + s * Cfg::A_BYTES, &tmap_a, kb * BK, m_blk * BM, &full_bar[s]);
-                    tma_load_2d(smem_b + s * Cfg::B_BYTES, &tmap_b, kb * BK, n_blk * BN, &full_bar[s]);
+                    tma_load_2d(smem_a + s * Cfg::A_BYTES, &tmap_a, kb * BKE, m_blk * BM, &full_bar[s]);
+                    tma_load_2d(smem_b + s * Cfg::B_BYTES, &tmap_b, kb * BKE, n_blk * BN, &full_bar[s]);
                 }
             }
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_PRODUCER);
@@ -151,7 +152,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     } else if (warp == 1) {
         // -------------------------------------------------------------- MMA issuer
         if (lane == 0) {
-            constexpr uint32_t idesc = make_idesc_tf32(BM, BN, 0);
+            constexpr uint32_t idesc = BF16 ? make_idesc_bf16(BM, BN, 0) : make_idesc_tf32(BM, BN, 0);
             uint32_t it = 0;
             bool ok = true;
             int tile_iter = 0;
@@ -174,9 +175,10 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * Cfg::B_BYTES), 16, 1024);
 #pragma unroll
                     for (int k = 0; k < BK / 8; ++k) {
-                        // advance 8 fp32 = 32 bytes along K inside the swizzled row: +2 in the
-                        // (address >> 4) field
-                        umma_tf32_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                        // advance 8 fp32 (16 bf16) = 32 bytes along K inside the swizzled row: +2 in
+                        // the (address >> 4) field
+                        if (BF16) umma_f16_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                        else umma_tf32_ss(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
                     }
                     if (X3) {
                         const uint64_t as_desc = make_smem_desc_sw128(smem_u32(smem_as + s * Cfg::A_BYTES), 16, 1024);
@@ -273,17 +275,18 @@ inline long tile_cost(int bn, int num_kb) {
     return num_kb * (tensor > feed ? tensor : feed) + 1500;
 }
 
-template <int BN, bool X3>
+template <int BN, bool X3, bool BF16>
 int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, GemmArgs& a) {
     using Cfg = GemmCfg<BN, X3>;
+    static_assert(!BF16 || (BN % 64 == 0 && !X3), "the bf16 epilogue stores 64 columns at a time");
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63]) {
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_kernel<BN, X3>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_kernel<BN, X3, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
         attr_set[ctx->device & 63] = true;
     }
     const int tiles = a.num_m_blocks * a.num_n_blocks;
     const int grid = tiles < ctx->num_sms ? tiles : ctx->num_sms;
-    cudaError_t le = launch_pdl(ctx, gemm_tf32_kernel<BN, X3>, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM, ta, tb, to, a);
+    cudaError_t le = launch_pdl(ctx, gemm_tf32_kernel<BN, X3, BF16>, dim3(grid), dim3(Cfg::THREADS), Cfg::SMEM, ta, tb, to, a);
     ctx->launches++;
     B200_CUDA(ctx, le);
     return B200_OK;
@@ -291,64 +294,109 @@ int launch_one(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, cons
 
 }  // namespace
 
-int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
-                     const float* bias, const float* residual, int M, int K, int N, int flags,
-                     int mode, unsigned long long* argmax_keys, int argmax_cols) {
+namespace {
+
+// bf16 != 0: inp / weight hold bf16 elements and out_h (if not null) receives the output as bf16.
+int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp, const void* weight,
+                    const float* bias, const float* residual, int M, int K, int N, int flags,
+                    int mode, unsigned long long* argmax_keys, int argmax_cols, bool bf16) {
     const bool x3 = (mode == B200_TF32X3);
     // the fused arg-max looks at the raw accumulator: only with a plain epilogue
-    if (argmax_keys && (bias || residual || flags != 0)) { ctx->last_error = "fused arg-max needs a plain GEMM epilogue"; return B200_ERR_STATE; }
-    // CTA pairs pull a third less operand traffic out of L2 per flop and win where there are many
-    // tiles per SM (wide outputs: lm-head, GPT-2 XL shapes); with a few tiles per SM the
-    // single-CTA kernel's finer N tiles quantise better.  B200_GEMM_PAIR=0/1 forces the choice.
-    static const int pair_env = [] { const char* e = getenv("B200_GEMM_PAIR"); return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1; }();
-    const bool use_pair = pair_env >= 0 ? pair_env == 1 : (N >= 4096 && M >= 2048);
-    if (!x3 && use_pair) return launch_gemm_tf32_pair(ctx, out, inp, weight, bias, residual, M, K, N, flags, argmax_keys, argmax_cols);
+    if (argmax_keys && (bias || residual || flags != 0 || out_h)) { ctx->last_error = "fused arg-max needs a plain GEMM epilogue"; return B200_ERR_STATE; }
+    const int bke = bf16 ? kGemmBKH : BK;
+    const int num_kb = (K + bke - 1) / bke;
     const int num_m = (M + BM - 1) / BM;
     // pick the N tile that minimises waves x per-tile cost on this GPU's SM count
     int best_bn = 128;
+    long best_cost = -1;
     if (!x3) {
         const int cands[5] = {256, 192, 128, 96, 64};
-        long best_cost = -1;
         for (int i = 0; i < 5; ++i) {
             const int bn = cands[i];
+            if (bf16 && bn % 64) continue;
             const long tiles = (long)num_m * ((N + bn - 1) / bn);
             const long waves = (tiles + ctx->num_sms - 1) / ctx->num_sms;
-            const long cost = waves * tile_cost(bn, (K + BK - 1) / BK);
+            const long cost = waves * tile_cost(bn, num_kb);
             if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
         }
         // tuning hook: B200_GEMM_BN=<64|96|128|192|256> forces the N tile
         static const int forced_bn = [] { const char* e = getenv("B200_GEMM_BN"); return e ? atoi(e) : 0; }();
-        if (forced_bn == 64 || forced_bn == 96 || forced_bn == 128 || forced_bn == 192 || forced_bn == 256) best_bn = forced_bn;
+        if ((forced_bn == 64 || forced_bn == 96 || forced_bn == 128 || forced_bn == 192 || forced_bn == 256) && !(bf16 && forced_bn % 64)) best_bn = forced_bn;
     }
+    // CTA pairs pull a third less operand traffic out of L2 per flop and win where there are many
+    // tiles per SM (wide outputs: lm-head, GPT-2 XL shapes); with a few tiles per SM the
+    // single-CTA kernel's finer N tiles quantise better.  With bf16 operands the tensor pipe
+    // needs the same bytes in half the time, so the operand feed decides nearly everywhere and
+    // pairs are used whenever there are whole pair tiles for every SM pair.
+    // B200_GEMM_PAIR=0/1 forces the choice.
+    static const int pair_env = [] { const char* e = getenv("B200_GEMM_PAIR"); return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1; }();
+    bool use_pair = N >= 4096 && M >= 2048;
+    if (bf16) use_pair = M >= 2048 && (long)((M + 255) / 256) * ((N + 255) / 256) >= ctx->num_sms / 2;
+    if (pair_env >= 0) use_pair = pair_env == 1;
+    if (!x3 && use_pair)
+        return launch_gemm_tf32_pair(ctx, out, static_cast<const float*>(inp), static_cast<const float*>(weight), bias, residual,
+                                     M, K, N, flags, argmax_keys, argmax_cols, bf16 ? 1 : 0, out_h);
     GemmArgs a;
-    a.out = out; a.bias = bias; a.residual = residual;
+    a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
     a.num_m_blocks = num_m;
     a.num_n_blocks = (N + best_bn - 1) / best_bn;
     // weight small enough to stay in L2: sweep N fastest so each inp tile is fetched once;
     // otherwise sweep M fastest so the (smaller) inp stays resident while weight streams
-    a.n_fastest = ((size_t)N * K * 4 <= (size_t)32 << 20) ? 1 : 0;
+    a.n_fastest = ((size_t)N * K * (bf16 ? 2 : 4) <= (size_t)32 << 20) ? 1 : 0;
     a.flags = flags;
     a.status = ctx->d_status;
     a.argmax_keys = argmax_keys;
     a.argmax_cols = argmax_cols;
 
-    CUtensorMap ta, tb;
-    int st = b200_get_tensor_map(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);
-    if (st != B200_OK) return st;
-    st = b200_get_tensor_map(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)best_bn, BK);
-    if (st != B200_OK) return st;
-    CUtensorMap to;  // the output in 32 x 32 boxes, for the epilogue's TMA stores
-    st = b200_get_tensor_map(ctx, &to, out, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 32);
-    if (st != B200_OK) return st;
-    if (x3) return launch_one<128, true>(ctx, ta, tb, to, a);
-    switch (best_bn) {
-        case 256: return launch_one<256, false>(ctx, ta, tb, to, a);
-        case 192: return launch_one<192, false>(ctx, ta, tb, to, a);
-        case 128: return launch_one<128, false>(ctx, ta, tb, to, a);
-        case 96:  return launch_one<96, false>(ctx, ta, tb, to, a);
-        default:  return launch_one<64, false>(ctx, ta, tb, to, a);
+    CUtensorMap ta, tb, to;
+    int st;
+    if (bf16) {
+        st = b200_get_tensor_map_bf16(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, kGemmBKH);
+        if (st != B200_OK) return st;
+        st = b200_get_tensor_map_bf16(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)best_bn, kGemmBKH);
+        if (st != B200_OK) return st;
+    } else {
+        st = b200_get_tensor_map(ctx, &ta, static_cast<const float*>(inp), (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);
+        if (st != B200_OK) return st;
+        st = b200_get_tensor_map(ctx, &tb, static_cast<const float*>(weight), (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)best_bn, BK);
+        if (st != B200_OK) return st;
     }
+    // the output in 32 x 32 boxes of fp32 (32 x 64 of bf16), for the epilogue's TMA stores
+    if (out_h) st = b200_get_tensor_map_bf16(ctx, &to, out_h, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 64);
+    else st = b200_get_tensor_map(ctx, &to, out, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 32);
+    if (st != B200_OK) return st;
+    if (bf16) {
+        switch (best_bn) {
+            case 256: return launch_one<256, false, true>(ctx, ta, tb, to, a);
+            case 192: return launch_one<192, false, true>(ctx, ta, tb, to, a);
+            case 128: return launch_one<128, false, true>(ctx, ta, tb, to, a);
+            default:  return launch_one<64, false, true>(ctx, ta, tb, to, a);
+        }
+    }
+    if (x3) return launch_one<128, true, false>(ctx, ta, tb, to, a);
+    switch (best_bn) {
+        case 256: return launch_one<256, false, false>(ctx, ta, tb, to, a);
+        case 192: return launch_one<192, false, false>(ctx, ta, tb, to, a);
+        case 128: return launch_one<128, false, false>(ctx, ta, tb, to, a);
+        case 96:  return launch_one<96, false, false>(ctx, ta, tb, to, a);
+        default:  return launch_one<64, false, false>(ctx, ta, tb, to, a);
+    }
+}
+
+}  // namespace
+
+int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
+                     const float* bias, const float* residual, int M, int K, int N, int flags,
+                     int mode, unsigned long long* argmax_keys, int argmax_cols) {
+    return launch_gemm_any(ctx, out, nullptr, inp, weight, bias, residual, M, K, N, flags, mode, argmax_keys, argmax_cols, false);
+}
+
+int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,
+                     const float* bias, int M, int K, int N, int flags,
+                     unsigned long long* argmax_keys, int argmax_cols) {
+    if (K % 8 || N % 8) { ctx->last_error = "bf16 GEMM: K and N must be multiples of 8"; return B200_ERR_SHAPE; }
+    return launch_gemm_any(ctx, out, out_h, inp, weight, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32), B200_TF32, argmax_keys, argmax_cols, true);
 }
 
 }  // namespace b200

@@ -48,7 +48,7 @@ struct PairCfg {
     static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "BN: multiple of 32, 64..256");
 };
 
-template <int BN>
+template <int BN, bool BF16>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                       const __grid_constant__ CUtensorMap tmap_out,
@@ -75,7 +75,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
     const int num_tiles = args.num_m_blocks * args.num_n_blocks;
-    const int num_kb = (args.K + BK - 1) / BK;
+    constexpr int BKE = BF16 ? kGemmBKH : BK;  // elements per 128-byte K block
+    const int num_kb = (args.K + BKE - 1) / BKE;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
@@ -123,8 +124,8 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     // without it, and the peer cannot be a whole phase ahead because its stage is
                     // only freed by the even CTA's commit.
                     if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * Cfg::STAGE_BYTES);
-                    tma_load_2d_pair(smem_a + s * Cfg::A_BYTES, &tmap_a, kb * BK, row_a, full_leader);
-                    tma_load_2d_pair(smem_b + s * Cfg::B_BYTES, &tmap_b, kb * BK, row_b, full_leader);
+                    tma_load_2d_pair(smem_a + s * Cfg::A_BYTES, &tmap_a, kb * BKE, row_a, full_leader);
+                    tma_load_2d_pair(smem_b + s * Cfg::B_BYTES, &tmap_b, kb * BKE, row_b, full_leader);
                 }
             }
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_PRODUCER);
@@ -132,7 +133,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     } else if (warp == 1) {
         // ------------------------------------------- UMMA issuer (even CTA only)
         if (rank == 0 && lane == 0) {
-            constexpr uint32_t idesc = make_idesc_tf32(2 * BM, BN, 0);
+            constexpr uint32_t idesc = BF16 ? make_idesc_bf16(2 * BM, BN, 0) : make_idesc_tf32(2 * BM, BN, 0);
             uint32_t it = 0;
             bool ok = true;
             int tile_iter = 0;
@@ -160,8 +161,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * Cfg::A_BYTES), 16, 1024);
                     const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * Cfg::B_BYTES), 16, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / 8; ++k)
-                        umma_tf32_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    for (int k = 0; k < BK / 8; ++k) {  // 32 bytes of K per instruction: 8 tf32 or 16 bf16
+                        if (BF16) umma_f16_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                        else umma_tf32_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                    }
 #ifdef B200_GEMM_TIMING
                     { long long t1 = clock64(); t_mma += t1 - t0; t0 = t1; }
 #endif
@@ -231,10 +234,11 @@ inline long pair_tile_cost(int bn, int num_kb) {
     return num_kb * (tensor > feed ? tensor : feed) + 1500;
 }
 
-template <int BN>
+template <int BN, bool BF16>
 int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, GemmArgs& a,
                 int num_pairs_max) {
     using Cfg = PairCfg<BN>;
+    static_assert(!BF16 || BN % 64 == 0, "the bf16 epilogue stores 64 columns at a time");
     static int resident_pairs[64] = {};  // CTA pairs the device can keep resident at once
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kThreads);
@@ -250,10 +254,10 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, con
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 2 : 1;
     if (!resident_pairs[ctx->device & 63]) {
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_pair_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_pair_kernel<BN, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
         cfg.gridDim = dim3(2 * num_pairs_max);
         int n = 0;
-        B200_CUDA(ctx, cudaOccupancyMaxActiveClusters(&n, gemm_tf32_pair_kernel<BN>, &cfg));
+        B200_CUDA(ctx, cudaOccupancyMaxActiveClusters(&n, gemm_tf32_pair_kernel<BN, BF16>, &cfg));
         if (n < 1) n = 1;
         resident_pairs[ctx->device & 63] = n < num_pairs_max ? n : num_pairs_max;
         if (getenv("B200_GEMM_DEBUG")) fprintf(stderr, "gemm_tf32_pair_kernel<%d>: %d resident CTA pairs (occupancy query %d), %d stages\n", BN, resident_pairs[ctx->device & 63], n, Cfg::STAGES);
@@ -262,7 +266,7 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, con
     const int tiles = a.num_m_blocks * a.num_n_blocks;
     const int pairs = tiles < resident_pairs[ctx->device & 63] ? tiles : resident_pairs[ctx->device & 63];
     cfg.gridDim = dim3(2 * pairs);
-    B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tf32_pair_kernel<BN>, ta, tb, to, a));
+    B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tf32_pair_kernel<BN, BF16>, ta, tb, to, a));
     ctx->launches++;
     return B200_OK;
 }
@@ -271,10 +275,11 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, con
 
 int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                           const float* bias, const float* residual, int M, int K, int N, int flags,
-                          unsigned long long* argmax_keys, int argmax_cols) {
+                          unsigned long long* argmax_keys, int argmax_cols, int bf16, uint16_t* out_h) {
     const int num_pairs_max = ctx->num_sms / 2;
     const int num_m = (M + 2 * BM - 1) / (2 * BM);
-    const int num_kb = (K + BK - 1) / BK;
+    const int bke = bf16 ? kGemmBKH : BK;
+    const int num_kb = (K + bke - 1) / bke;
     const int cands[4] = {256, 192, 128, 64};
     int best_bn = 256;
     long best_cost = -1;
@@ -290,31 +295,48 @@ int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const flo
     if (forced_bn == 64 || forced_bn == 128 || forced_bn == 192 || forced_bn == 256) best_bn = forced_bn;
 
     GemmArgs a;
-    a.out = out; a.bias = bias; a.residual = residual;
+    a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
     a.num_m_blocks = num_m;
     a.num_n_blocks = (N + best_bn - 1) / best_bn;
     // weight small enough to stay in L2: sweep N fastest so each inp tile is fetched once;
     // otherwise sweep M fastest so the (smaller) inp stays resident while weight streams
-    a.n_fastest = ((size_t)N * K * 4 <= (size_t)32 << 20) ? 1 : 0;
+    a.n_fastest = ((size_t)N * K * (bf16 ? 2 : 4) <= (size_t)32 << 20) ? 1 : 0;
     a.flags = flags;
     a.status = ctx->d_status;
     a.argmax_keys = argmax_keys;
     a.argmax_cols = argmax_cols;
 
-    CUtensorMap ta, tb;
-    int st = b200_get_tensor_map(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);
+    CUtensorMap ta, tb, to;
+    int st;
+    if (bf16) {
+        st = b200_get_tensor_map_bf16(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, kGemmBKH);
+        if (st != B200_OK) return st;
+        st = b200_get_tensor_map_bf16(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(best_bn / 2), kGemmBKH);
+        if (st != B200_OK) return st;
+    } else {
+        st = b200_get_tensor_map(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);
+        if (st != B200_OK) return st;
+        st = b200_get_tensor_map(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(best_bn / 2), BK);
+        if (st != B200_OK) return st;
+    }
+    // the output in 32 x 32 boxes of fp32 (32 x 64 of bf16), for the epilogue's TMA stores
+    if (out_h) st = b200_get_tensor_map_bf16(ctx, &to, out_h, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 64);
+    else st = b200_get_tensor_map(ctx, &to, out, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 32);
     if (st != B200_OK) return st;
-    st = b200_get_tensor_map(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(best_bn / 2), BK);
-    if (st != B200_OK) return st;
-    CUtensorMap to;  // the output in 32 x 32 boxes, for the epilogue's TMA stores
-    st = b200_get_tensor_map(ctx, &to, out, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 32);
-    if (st != B200_OK) return st;
+    if (bf16) {
+        switch (best_bn) {
+            case 256: return launch_pair<256, true>(ctx, ta, tb, to, a, num_pairs_max);
+            case 192: return launch_pair<192, true>(ctx, ta, tb, to, a, num_pairs_max);
+            case 128: return launch_pair<128, true>(ctx, ta, tb, to, a, num_pairs_max);
+            default:  return launch_pair<64, true>(ctx, ta, tb, to, a, num_pairs_max);
+        }
+    }
     switch (best_bn) {
-        case 256: return launch_pair<256>(ctx, ta, tb, to, a, num_pairs_max);
-        case 192: return launch_pair<192>(ctx, ta, tb, to, a, num_pairs_max);
-        case 128: return launch_pair<128>(ctx, ta, tb, to, a, num_pairs_max);
-        default:  return launch_pair<64>(ctx, ta, tb, to, a, num_pairs_max);
+        case 256: return launch_pair<256, false>(ctx, ta, tb, to, a, num_pairs_max);
+        case 192: return launch_pair<192, false>(ctx, ta, tb, to, a, num_pairs_max);
+        case 128: return launch_pair<128, false>(ctx, ta, tb, to, a, num_pairs_max);
+        default:  return launch_pair<64, false>(ctx, ta, tb, to, a, num_pairs_max);
     }
 }
 

@@ -7,7 +7,8 @@
 namespace b200 {
 
 // flags for the row-wise producers
-enum : int { ROUND_OUT_TF32 = 1 };
+// OUT_BF16: the main output pointer addresses bf16 (16-bit) elements instead of fp32
+enum : int { ROUND_OUT_TF32 = 1, OUT_BF16 = 2 };
 
 int launch_layernorm(b200_ctx* ctx, float* out, float* mean, float* rstd, const float* inp,
                      const float* weight, const float* bias, int M, int C, int flags);
@@ -19,6 +20,8 @@ int launch_gelu(b200_ctx* ctx, float* out, const float* inp, size_t N);
 int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,
                    int B, int T, int C, int vocab_rows /* <=0: unchecked */);
 int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N);
+// out[i] = bf16(in[i]), round to nearest even; N a multiple of 4
+int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N);
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
 int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns);
 
@@ -27,6 +30,12 @@ enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2 };
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      int mode, unsigned long long* argmax_keys = nullptr, int argmax_cols = 0);
+// The same product with bf16 operands (tcgen05 kind::f16, fp32 accumulation): inp [M,K] and weight
+// [N,K] hold bf16; the result goes to out (fp32) or, if out_h is not null, to out_h as bf16.
+// flags: GEMM_GELU only.  K and N multiples of 8.
+int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,
+                     const float* bias, int M, int K, int N, int flags,
+                     unsigned long long* argmax_keys = nullptr, int argmax_cols = 0);
 // turns the keys left by a GEMM with fused arg-max into column indices (0 for an untouched key)
 int launch_argmax_decode(b200_ctx* ctx, int* out, const unsigned long long* keys, int M);
 

@@ -8,6 +8,7 @@
 // mean/rstd outputs), kernels/fused_residual_layernorm/fused_residual_layernorm.cuh:28-36,59-81
 // (intent; that kernel's float4 pointer stride at :19,48-50 is not followed),
 // kernels/residual/1_residual_naive.cuh:9-12 and kernels/matmul/9_matmul_async_cg_tf32_gelu.cuh:5-11.
+#include <cuda_bf16.h>
 #include "kernels.h"
 #include "../prim/sm100.cuh"
 
@@ -84,7 +85,9 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
     const float4* w4 = reinterpret_cast<const float4*>(weight);
     const float4* b4 = reinterpret_cast<const float4*>(bias);
     float4* o = reinterpret_cast<float4*>(out + (size_t)row * C);
+    uint2* oh = reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + (size_t)row * C);  // OUT_BF16
     const bool rnd = (flags & ROUND_OUT_TF32) != 0;
+    const bool as_bf16 = (flags & OUT_BF16) != 0;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = lane + i * 32;
@@ -95,6 +98,11 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
             y.y = (v[i].y - m) * r * w.y + b.y;
             y.z = (v[i].z - m) * r * w.z + b.z;
             y.w = (v[i].w - m) * r * w.w + b.w;
+            if (as_bf16) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
+                oh[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                continue;
+            }
             if (rnd) { y.x = round_tf32(y.x); y.y = round_tf32(y.y); y.z = round_tf32(y.z); y.w = round_tf32(y.w); }
             o[c] = y;
         }
@@ -149,6 +157,15 @@ __global__ void gelu_kernel(float4* __restrict__ out, const float4* __restrict__
     }
     i = n4 * 4 + (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) out_s[i] = gelu_tanh(inp_s[i]);
+}
+
+__global__ void convert_bf16_kernel(uint2* __restrict__ out, const float4* __restrict__ in, size_t n4) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        const float4 x = in[i];
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
+        out[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+    }
 }
 
 __global__ void round_tf32_kernel(float4* data, size_t n4, float* data_s, size_t n) {
@@ -277,6 +294,16 @@ int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N) {
     const size_t n4 = N / 4;
     const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
     round_tf32_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<float4*>(data), n4, data, N);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N) {
+    if (N % 4) { ctx->last_error = "bf16 conversion: element count must be a multiple of 4"; return B200_ERR_SHAPE; }
+    const size_t n4 = N / 4;
+    const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
+    convert_bf16_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<uint2*>(out), reinterpret_cast<const float4*>(in), n4);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

@@ -43,7 +43,8 @@ enum {
 /* GEMM arithmetic modes */
 enum {
     B200_TF32 = 0,           /* one tcgen05 kind::tf32 pass (default)               */
-    B200_TF32X3 = 1          /* three-term split (big*big + small*big + big*small)  */
+    B200_TF32X3 = 1,         /* three-term split (big*big + small*big + big*small)  */
+    B200_BF16 = 2            /* bf16 operands (tcgen05 kind::f16), fp32 accumulation: model option only */
 };
 
 /* GEMM epilogue activation */
@@ -82,6 +83,16 @@ const char* b200_ctx_last_error(const b200_ctx* ctx);
 int b200_matmul_forward(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                         const float* bias, int B, int T, int C, int OC, int act,
                         const float* residual, int mode);
+
+/* The same product with bf16 operands (the reference's bf16 experiment, README.md:124-128 and
+ * kernels/matmul/5_matmul_ptx_2d.cuh, is the counterpart): inp[B,T,C] and weight[OC,C] hold bf16
+ * values (16 bits each, as uint16_t), accumulation is fp32; the result is written to out (fp32) or,
+ * when out_bf16 is not NULL, to out_bf16 as bf16 (out is then ignored and may be NULL).  bias
+ * (fp32) may be NULL.  Preconditions: C % 8 == 0, OC % 8 == 0. */
+int b200_matmul_forward_bf16(b200_ctx* ctx, float* out, uint16_t* out_bf16, const uint16_t* inp,
+                             const uint16_t* weight, const float* bias, int B, int T, int C, int OC, int act);
+/* out[i] = bf16(inp[i]), round to nearest even; n % 4 == 0. */
+int b200_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* inp, size_t n);
 
 /* Causal multi-head attention on the packed buffer inp[B,T,3C] -> out[B,T,C].
  * Replaces attention_forward_cublas (kernels/attention/1_attention_cublas.cuh:31-36),

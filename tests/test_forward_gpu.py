@@ -208,3 +208,38 @@ def test_forward_rejects_sizes_beyond_the_allocation(pkg, orc, ctx):
     with pytest.raises(pkg.B200Error):
         model.forward_host(tokens, 1, 100)  # T % 64
     model.close()
+
+
+@pytest.mark.parametrize("lmhead_bf16", [True, False])
+def test_bf16_operand_mode_stays_close_to_the_fp32_forward(pkg, orc, ctx, lmhead_bf16):
+    """The optional bf16 mode (GEMM operands rounded to bf16, fp32 accumulation, everything between
+    the GEMMs in fp32; attention stays on the TF32 path).  bf16 keeps 8 significant bits against
+    TF32's 11, so its bar is four times the TF32 one: logits within 8e-2 max-abs (measured: a
+    quarter of that) and top-1 misses only on near-ties of the oracle's own logits."""
+    import torch
+    B, T = 2, 256
+    cfg, ocfg, params, model = _make(pkg, orc, ctx, dict(), B, T)
+    model.set_options(round_operands=1, gemm_mode=pkg.B200_BF16,
+                      lmhead_mode=pkg.B200_BF16 if lmhead_bf16 else pkg.B200_TF32)
+    tokens = orc.fill_tokens((B, T), seed=4321, vocab=cfg.vocab_size)
+    want = orc.gpt2_forward(params, ocfg, tokens, precise=False)
+    d_tok = torch.from_numpy(tokens).cuda()
+    torch.cuda.synchronize()
+    logits = model.forward(d_tok, B, T)
+    ctx.sync_check()
+    assert torch.isfinite(logits).all()
+    got = logits.cpu().numpy()
+    mx, rms, agree, gaps = _compare(got.reshape(B * T, -1), want.reshape(B * T, -1), cfg.vocab_size)
+    print(f"bf16 (lm-head bf16: {lmhead_bf16}): max-abs {mx:.3e}, rms {rms:.3e}, top-1 agreement {agree:.5f}, "
+          f"largest oracle margin among the misses {gaps.max() if len(gaps) else 0:.2e}")
+    assert mx < 8e-2
+    assert rms < 6e-3
+    assert agree >= 0.95, agree
+    assert len(gaps) == 0 or gaps.max() < 2e-2, "a top-1 miss that is not a near-tie"
+    # the arg-max fused into the bf16 lm-head agrees with the logits it wrote
+    if lmhead_bf16:
+        amax = np.empty((B, T), np.int32)
+        lg = np.empty((B, T, cfg.padded_vocab_size), np.float32)
+        model.forward_host(tokens, B, T, logits_host=lg, argmax_host=amax)
+        assert np.array_equal(amax, lg[..., :cfg.vocab_size].argmax(-1))
+    model.close()

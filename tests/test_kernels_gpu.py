@@ -289,3 +289,59 @@ def test_device_wait_that_runs_out_is_reported_and_context_survives(ctx, dev, or
     ctx.residual_forward(out, dev.to(a), dev.to(b), 1024)
     assert np.array_equal(dev.back(out), a + b)
     assert lib.b200_ctx_wait_timeout_probe(ctx._h, 0) == 2  # limit out of range
+
+
+# ------------------------------------------------------------------ bf16 operand GEMM
+def _bf16_round(a):
+    """fp32 -> nearest bf16 (ties to even), returned as fp32 values and as the 16-bit patterns."""
+    u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    r = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint32)
+    return (r << 16).view(np.float32).reshape(a.shape), r.astype(np.uint16).reshape(a.shape)
+
+
+def test_convert_bf16_is_round_to_nearest_even(ctx, dev, orc):
+    import torch
+    x = orc.fill_normal((4, 1000), 301)
+    x[0, :8] = [1.00390625, 1.01171875, -1.00390625, 0.0, 3.0e38, -1e-30, 1.0, 65280.0]  # ties, large, tiny
+    out = torch.empty((4, 1000), dtype=torch.int16, device="cuda")
+    ctx.convert_bf16(out, dev.to(x), x.size)
+    ctx.sync_check()
+    _, bits = _bf16_round(x)
+    assert np.array_equal(out.cpu().numpy().view(np.uint16), bits)
+
+
+@pytest.mark.parametrize("B,T,C,OC,has_bias,act,out_h", [
+    (1, 128, 64, 64, False, 0, False),
+    (2, 192, 768, 2304, True, 0, False),     # qkv shape, ragged M
+    (4, 512, 768, 3072, True, 1, True),      # fc + GELU, bf16 out, CTA pairs
+    (1, 1000, 3072, 768, True, 0, False),    # fc-proj, M not a multiple of 128
+    (1, 320, 776, 200, True, 1, True),       # K tail (776 = 12 * 64 + 8), narrow ragged N, bf16 out
+    (2, 1024, 768, 50304, False, 0, False),  # lm-head width, CTA pairs
+])
+def test_matmul_bf16_matches_oracle_on_rounded_operands(ctx, dev, orc, B, T, C, OC, has_bias, act, out_h):
+    """bf16 x bf16 products are exact in fp32, so against the oracle fed the same bf16-rounded
+    operands only the accumulation order is left: 2e-5 of the result's magnitude.  A bf16 output
+    may differ from the rounded oracle value by one bf16 step where the fp32 value sits on a
+    rounding boundary."""
+    import torch
+    x, xb = _bf16_round(orc.fill_normal((B, T, C), 311))
+    w, wb = _bf16_round(orc.fill_normal((OC, C), 312, std=0.02))
+    bias = orc.fill_normal((OC,), 313, std=0.01) if has_bias else None
+    rows = slice(None) if B * T * OC < 40_000_000 else slice(-300, None)  # oracle on the last rows of the big case
+    want = orc.matmul_forward(x.reshape(B * T, C)[rows][None], w, bias, act=act, precise=True)[0]
+    d = "cuda"
+    d_x = torch.from_numpy(xb.view(np.int16)).to(d)
+    d_w = torch.from_numpy(wb.view(np.int16)).to(d)
+    out = None if out_h else dev.full((B, T, OC), float("nan"))
+    outh = torch.full((B, T, OC), -1, dtype=torch.int16, device=d) if out_h else None
+    ctx.matmul_forward_bf16(out, outh, d_x, d_w, None if bias is None else dev.to(bias), B, T, C, OC, act=act)
+    ctx.sync_check()
+    scale = float(np.abs(want).max())
+    if out_h:
+        got = (outh.cpu().numpy().view(np.uint16).astype(np.uint32) << 16).view(np.float32).reshape(B * T, OC)[rows]
+        assert np.isfinite(got).all()
+        assert (np.abs(got - want) <= np.abs(want) * 2.0 ** -8 + 2e-5 * scale).all()
+    else:
+        got = dev.back(out).reshape(B * T, OC)[rows]
+        assert np.isfinite(dev.back(out)).all(), "unwritten or non-finite outputs"
+        assert np.abs(got - want).max() <= 2e-5 * scale, (np.abs(got - want).max(), scale)
