@@ -443,7 +443,7 @@ def run_ours(args):
         "config": {"workload": workload, "global_batch": replicas * B, "seq_len": T, "parallelism": par,
                    "l2": "no flush: each step streams the weights (0.5 GB for 124M) and writes 1.65 GB of logits, far beyond the 126 MB L2",
                    "flop_per_token": cfg.flops_per_token(T)},
-        "roofline": {"bound": "tensor", "kernel": "gemm_tf32_kernel (all five GEMM shapes of the forward)",
+        "roofline": {"bound": "tensor", "kernel": "gemm_tf32_pair_kernel and gemm_tf32_kernel (all five GEMM shapes of the forward)",
                      "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
                      "peak_source": f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32 runs at half the bf16 rate; no TF32 peak is measured)",
                      "launches_per_step": n_gemm / args.steps,

@@ -323,14 +323,15 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
         static const int forced_bn = [] { const char* e = getenv("B200_GEMM_BN"); return e ? atoi(e) : 0; }();
         if ((forced_bn == 64 || forced_bn == 96 || forced_bn == 128 || forced_bn == 192 || forced_bn == 256) && !(bf16 && forced_bn % 64)) best_bn = forced_bn;
     }
-    // CTA pairs pull a third less operand traffic out of L2 per flop and win where there are many
-    // tiles per SM (wide outputs: lm-head, GPT-2 XL shapes); with a few tiles per SM the
-    // single-CTA kernel's finer N tiles quantise better.  With bf16 operands the tensor pipe
+    // CTA pairs pull a third less operand traffic out of L2 per flop and drain the accumulator
+    // with eight warps; measured inside the forward (124M and XL shapes, 8192 rows) they win
+    // everywhere except the square attention projection (N = K = C: few, short tiles, where the
+    // single-CTA kernel's finer N tiles quantise better).  With bf16 operands the tensor pipe
     // needs the same bytes in half the time, so the operand feed decides nearly everywhere and
     // pairs are used whenever there are whole pair tiles for every SM pair.
     // B200_GEMM_PAIR=0/1 forces the choice.
     static const int pair_env = [] { const char* e = getenv("B200_GEMM_PAIR"); return (e && (e[0] == '0' || e[0] == '1')) ? e[0] - '0' : -1; }();
-    bool use_pair = N >= 4096 && M >= 2048;
+    bool use_pair = M >= 2048 && (N >= 2048 || K >= 2048);
     if (bf16) use_pair = M >= 2048 && (long)((M + 255) / 256) * ((N + 255) / 256) >= ctx->num_sms / 2;
     if (pair_env >= 0) use_pair = pair_env == 1;
     if (!x3 && use_pair)

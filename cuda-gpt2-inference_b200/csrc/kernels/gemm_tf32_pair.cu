@@ -12,12 +12,13 @@
 // tensor-pipe cycle at BN = 256, with six stages in flight instead of four.
 // No load is broadcast across the cluster: every CTA issues its own TMA loads.
 //
-// Per CTA (6 warps): warp 0 TMA producer, warp 1 tensor-memory allocation (+ UMMA issue in the
-// even CTA), warps 2-5 epilogue.  Barriers:
+// Per CTA (10 warps): warp 0 TMA producer, warp 1 tensor-memory allocation (+ UMMA issue in the
+// even CTA), warps 2-9 epilogue (warp w reads lane quarter w % 4; warps 2-5 drain the first half
+// of the tile's columns, warps 6-9 the second, one 4 KB staging buffer each).  Barriers:
 //   full[s]        in the even CTA: its producer's one arrival announces both CTAs' TMA bytes
 //   empty[s]       in each CTA, signalled by tcgen05.commit from the even CTA (one per CTA)
 //   tmem_full[a]   in each CTA, likewise
-//   tmem_empty[a]  in the even CTA, 8 arrivals (one per epilogue warp of both CTAs)
+//   tmem_empty[a]  in the even CTA, 16 arrivals (one per epilogue warp of both CTAs)
 // Every wait is time-bounded; the two CTAs synchronise on the cluster barrier after set-up and
 // before tensor memory is freed, so neither leaves while the other can still touch its shared
 // memory.
@@ -31,7 +32,8 @@ namespace {
 
 constexpr int BM = kGemmBM;  // rows per CTA; 2*BM per pair
 constexpr int BK = kGemmBK;
-constexpr int kThreads = 192;
+constexpr int kEpiWarps = 8;  // two per tensor-memory lane quarter, each draining half of the columns
+constexpr int kThreads = 64 + 32 * kEpiWarps;
 
 template <int BN>
 struct PairCfg {
@@ -80,7 +82,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
-        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 8); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&tmem_full_bar[a], 1); mbar_init(&tmem_empty_bar[a], 2 * kEpiWarps); }
         mbar_init(drain_bar, 1);
         *abort_flag = 0;
         fence_barrier_init();
@@ -197,6 +199,12 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     } else {
         // ---------------------------------------------------------------- epilogue
         const int q = warp & 3;
+        const int ew = warp - 2;  // 0..7
+        // column split in units of one chunk (two for a bf16 output, whose stores take 64 columns)
+        const int unit = args.out_h ? 2 : 1;
+        const int n_units = BN / 32 / unit;
+        const int c_begin = (ew < 4) ? 0 : ((n_units + 1) / 2) * unit;
+        const int c_end = (ew < 4) ? ((n_units + 1) / 2) * unit : BN / 32;
         bool ok = true;
         int tile_iter = 0;
         for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tile_iter) {
@@ -208,7 +216,7 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             tc_fence_after_sync();
             gemm_drain_accumulator<BN>(args, &tmap_out, tmem_base + acc * BN, q, lane,
                                        m_blk * 2 * BM + (int)rank * BM + q * 32, n_blk * BN,
-                                       smem_epi + q * 2 * 4096);
+                                       smem_epi + ew * 4096, c_begin, c_end, 1);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
