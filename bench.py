@@ -349,7 +349,9 @@ def run_ours(args):
         model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32)
 
     # ---------------------------------------------------------------- end-to-end arm
-    for _ in range(2):
+    # (the library's own CUDA-graph replay of the forward: an option of the public call)
+    model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32, use_graph=1)
+    for _ in range(3):
         model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
     barrier()
     t0 = time.perf_counter()
@@ -449,7 +451,7 @@ def run_ours(args):
                      "launches_per_step": n_gemm / args.steps,
                      # ncu dram__bytes_read.sum + dram__bytes_write.sum, average per GEMM launch of the 124M
                      # forward (profiles/gemm_tf32_dram_traffic_by_shape.md); not captured for other models
-                     "traffic": None if (xl or tp) else 114.2e6, "algorithmic_bytes": None if (xl or tp) else 142.9e6,
+                     "traffic": None if (xl or tp) else 116.2e6, "algorithmic_bytes": None if (xl or tp) else 142.9e6,
                      "per_operator": per_op},
         "cpu_baseline": {"value": cpu_tps, "unit": UNIT, "cores": cores, "kind": "port",
                          "sample": f"1 sequence of {cpu_T} tokens (B=1), fp32-accumulate C/OpenMP forward, all host threads, one run"},

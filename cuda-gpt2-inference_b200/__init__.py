@@ -39,7 +39,7 @@ EXPORTS = (
     "fused_residual_layernorm_forward", "fused_residual_layernorm", "residual_forward",
     "gelu_forward", "encoder_forward",
     "b200_gpt2_param_offsets", "b200_gpt2_create", "b200_gpt2_destroy", "b200_gpt2_params",
-    "b200_gpt2_load_params_host", "b200_gpt2_set_options", "b200_gpt2_forward",
+    "b200_gpt2_load_params_host", "b200_gpt2_load_params_file", "b200_gpt2_set_options", "b200_gpt2_forward",
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
     "b200_gpt2_forward_static",
@@ -111,6 +111,7 @@ def lib() -> C.CDLL:
         l.b200_gpt2_params.argtypes = [vp]
         l.b200_gpt2_params.restype = vp
         l.b200_gpt2_load_params_host.argtypes = [vp, vp, sz]
+        l.b200_gpt2_load_params_file.argtypes = [vp, C.c_char_p, sz]
         l.b200_gpt2_set_options.argtypes = [vp, i, i, i, i]
         l.b200_gpt2_forward.argtypes = [vp, vp, i, i]
         l.b200_gpt2_logits.argtypes = [vp]
@@ -371,6 +372,10 @@ class GPT2:
 
     def load_params(self, host_params):
         self.ctx.check(lib().b200_gpt2_load_params_host(self._h, _ptr(host_params), host_params.size), "load_params")
+
+    def load_params_file(self, path: str, header_bytes: int = 0):
+        """Raw fp32 parameters in param_offsets order behind a header of header_bytes."""
+        self.ctx.check(lib().b200_gpt2_load_params_file(self._h, os.fsencode(path), header_bytes), "load_params_file")
 
     def set_options(self, round_operands=1, gemm_mode=B200_TF32, lmhead_mode=B200_TF32, use_graph=0):
         self.ctx.check(lib().b200_gpt2_set_options(self._h, int(round_operands), gemm_mode, lmhead_mode, int(use_graph)),

@@ -4,6 +4,7 @@
 // with every layernorm except the first fused with the residual add before it
 // (README.md:255-256).  Forward only, so one set of per-layer activations is reused by all
 // layers; parameters keep the flat fp32 layout documented in include/b200gpt2.h.
+#include <cstdio>
 #include <cstring>
 #include <map>
 #include <string>
@@ -399,6 +400,54 @@ int b200_gpt2_load_params_host(b200_gpt2* m, const float* host_params, size_t co
     m->weights_rounded = false;
     m->params_h_ready = false;
     return B200_OK;
+}
+
+int b200_gpt2_load_params_file(b200_gpt2* m, const char* path, size_t header_bytes) {
+    if (!m || !path) return B200_ERR_NULL;
+    if (m->tp_size > 1) return B200_ERR_STATE;
+    b200_ctx* ctx = m->ctx;
+    FILE* f = fopen(path, "rb");
+    if (!f) { ctx->last_error = std::string("cannot open ") + path; return B200_ERR_STATE; }
+    int st = B200_OK;
+    const unsigned long long want = (unsigned long long)header_bytes + (unsigned long long)m->n_params * 4ull;
+    if (fseek(f, 0, SEEK_END) != 0 || (unsigned long long)ftell(f) != want) {
+        ctx->last_error = std::string(path) + ": size is not header_bytes + 4 * parameter count";
+        st = B200_ERR_SHAPE;
+    } else if (fseek(f, (long)header_bytes, SEEK_SET) != 0) {
+        ctx->last_error = std::string("cannot seek in ") + path;
+        st = B200_ERR_STATE;
+    }
+    // two pinned staging buffers: the disk read of one piece overlaps the copy of the previous one
+    constexpr size_t kPiece = (size_t)32 << 20;
+    void* stage[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    cudaSetDevice(ctx->device);
+    for (int i = 0; i < 2 && st == B200_OK; ++i) {
+        cudaError_t e = cudaMallocHost(&stage[i], kPiece);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming);
+        if (e != cudaSuccess) st = b200_fail_cuda(ctx, e, "pinned staging buffers");
+    }
+    const size_t total = m->n_params * sizeof(float);
+    size_t off_bytes = 0;
+    for (int i = 0; st == B200_OK && off_bytes < total; i ^= 1) {
+        const size_t n = total - off_bytes < kPiece ? total - off_bytes : kPiece;
+        cudaError_t e = cudaEventSynchronize(done[i]);  // the copy that last used this buffer is done
+        if (e != cudaSuccess) { st = b200_fail_cuda(ctx, e, "cudaEventSynchronize"); break; }
+        if (fread(stage[i], 1, n, f) != n) { ctx->last_error = std::string("short read from ") + path; st = B200_ERR_STATE; break; }
+        e = cudaMemcpyAsync(reinterpret_cast<char*>(m->params) + off_bytes, stage[i], n, cudaMemcpyHostToDevice, ctx->stream);
+        if (e == cudaSuccess) e = cudaEventRecord(done[i], ctx->stream);
+        if (e != cudaSuccess) { st = b200_fail_cuda(ctx, e, "cudaMemcpyAsync (parameters)"); break; }
+        off_bytes += n;
+    }
+    cudaStreamSynchronize(ctx->stream);
+    for (int i = 0; i < 2; ++i) {
+        if (done[i]) cudaEventDestroy(done[i]);
+        if (stage[i]) cudaFreeHost(stage[i]);
+    }
+    fclose(f);
+    m->weights_rounded = false;
+    m->params_h_ready = false;
+    return st;
 }
 
 int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int lmhead_mode, int use_graph) {

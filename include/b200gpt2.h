@@ -190,6 +190,14 @@ int b200_gpt2_destroy(b200_gpt2* model);
 /* Device pointer of the flat parameter array (fill it in place), or copy from the host. */
 float* b200_gpt2_params(b200_gpt2* model);
 int b200_gpt2_load_params_host(b200_gpt2* model, const float* host_params, size_t count);
+/* Reads the parameters from a file: header_bytes are skipped, then the fp32 parameters follow in
+ * the order of b200_gpt2_param_offsets (wte, wpe, ln1w, ln1b, qkvw, qkvb, attprojw, attprojb, ln2w,
+ * ln2b, fcw, fcb, fcprojw, fcprojb, lnfw, lnfb), little endian, nothing after them.  Parsing a
+ * checkpoint format's header (and choosing the configuration from it) is the caller's job; the
+ * file size must be exactly header_bytes + 4 * parameter count (else B200_ERR_SHAPE; a file that
+ * cannot be opened or read is B200_ERR_STATE).  The copy goes through pinned staging buffers in
+ * 32 MB pieces.  Not for tensor-parallel models, whose parameters are stored sharded. */
+int b200_gpt2_load_params_file(b200_gpt2* model, const char* path, size_t header_bytes);
 /* Options (defaults: round_operands 1, both modes B200_TF32, use_graph 0).
  * round_operands != 0 makes every producer whose output feeds only a GEMM store
  * TF32-round-to-nearest values and, on the next forward, rounds the four linear weight

@@ -243,3 +243,29 @@ def test_bf16_operand_mode_stays_close_to_the_fp32_forward(pkg, orc, ctx, lmhead
         model.forward_host(tokens, B, T, logits_host=lg, argmax_host=amax)
         assert np.array_equal(amax, lg[..., :cfg.vocab_size].argmax(-1))
     model.close()
+
+
+def test_load_params_file_reads_raw_parameters_behind_a_header(pkg, orc, ctx, tmp_path):
+    """The raw parameter-file loader: skip the caller's header, copy the fp32 parameters in
+    param_offsets order; a file of the wrong size or a missing file is refused."""
+    kw = dict(num_layers=2)
+    cfg, ocfg, params, model = _make(pkg, orc, ctx, kw, 1, 64)
+    good = tmp_path / "params.bin"
+    with open(good, "wb") as f:
+        f.write(b"\x5a" * 1024)
+        f.write(params.tobytes())
+    fresh = pkg.GPT2(ctx, cfg, 1, 64)
+    fresh.load_params_file(str(good), 1024)
+    assert np.array_equal(fresh.params_tensor().cpu().numpy(), params)
+    tokens = orc.fill_tokens((1, 64), seed=5, vocab=cfg.vocab_size)
+    a = np.empty((1, 64, cfg.padded_vocab_size), np.float32)
+    b = np.empty_like(a)
+    model.forward_host(tokens, 1, 64, logits_host=a)
+    fresh.forward_host(tokens, 1, 64, logits_host=b)
+    assert np.array_equal(a, b)
+    with pytest.raises(pkg.B200Error):
+        fresh.load_params_file(str(good), 1020)          # size does not match
+    with pytest.raises(pkg.B200Error):
+        fresh.load_params_file(str(tmp_path / "absent.bin"), 0)
+    fresh.close()
+    model.close()
