@@ -311,6 +311,38 @@ def run_ours(args):
     model.set_profile(False)
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---------------------------------------------------------------- end-to-end arm
+    # Every step brings its tokens in from pinned host memory, runs the forward and puts the
+    # last-position logits and the arg-max ids back into pinned host memory (the library moves them
+    # with its own kernels over PCIe instead of queueing copies).  (a) the synchronous call, one step at a time;
+    # (b) the same call split into enqueue / wait with two steps in flight (each slot has its own
+    # host buffers), so the host's share of a step hides behind the GPU's - the headline `e2e`.
+    for _ in range(3):
+        model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
+    e2e_sync_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+    tok_h = [tok_host.numpy(), tok_host.clone().pin_memory().numpy()]
+    last_h = [last_host.numpy(), torch.empty_like(last_host).pin_memory().numpy()]
+    amax_h = [amax_np, None if tp else torch.empty_like(amax_host).pin_memory().numpy()]
+
+    def pipelined(n):
+        model.forward_host_enqueue(tok_h[0], B, T, 0, last_logits_host=last_h[0], argmax_host=amax_h[0])
+        for i in range(1, n):
+            model.forward_host_enqueue(tok_h[i & 1], B, T, i & 1, last_logits_host=last_h[i & 1], argmax_host=amax_h[i & 1])
+            model.forward_host_wait((i - 1) & 1)
+        model.forward_host_wait((n - 1) & 1)
+
+    pipelined(3)
+    barrier()
+    t0 = time.perf_counter()
+    pipelined(args.steps)
+    e2e_s = max_over_ranks(time.perf_counter() - t0)
+    barrier()
+
     # ------------------------------------------------ the same workload in the 3xTF32 mode
     # (split-operand GEMMs and attention: the mode that holds the 99.9 % top-1 / 1e-4 bars)
     x3_ms = None
@@ -347,18 +379,6 @@ def run_ours(args):
         ctx.sync_check()
         bf16_ms = max_over_ranks(ev4.elapsed_time(ev5)) / args.steps
         model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32)
-
-    # ---------------------------------------------------------------- end-to-end arm
-    # (the library's own CUDA-graph replay of the forward: an option of the public call)
-    model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32, use_graph=1)
-    for _ in range(3):
-        model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(args.steps):
-        model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
-    e2e_s = max_over_ranks(time.perf_counter() - t0)
-    barrier()
 
     # ---------------------------------------------- incremental decoding (key/value cache)
     # One new token per sequence against a cache filled by a prefill of T/2 positions; each step
@@ -457,7 +477,10 @@ def run_ours(args):
                          "sample": f"1 sequence of {cpu_T} tokens (B=1), fp32-accumulate C/OpenMP forward, all host threads, one run"},
         "e2e": {"value": replicas * B * T * args.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": B * T * 4,
                 "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s / args.steps,
-                "result": "last-position logits [B,Vp]" + ("" if tp else " and per-position arg-max token ids [B,T]")},
+                "result": "last-position logits [B,Vp]" + ("" if tp else " and per-position arg-max token ids [B,T]"),
+                "call": "b200_gpt2_forward_host_enqueue / _wait, two steps in flight, double-buffered pinned host buffers",
+                "synchronous_call": {"value": replicas * B * T * args.steps / e2e_sync_s, "ms_per_step": 1e3 * e2e_sync_s / args.steps,
+                                     "call": "b200_gpt2_forward_host, one step at a time"}},
         "gpu_launches": launches,
         "clocks": clocks,
         "tf32x3": None if x3_ms is None else {

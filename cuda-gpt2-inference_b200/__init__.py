@@ -40,7 +40,7 @@ EXPORTS = (
     "gelu_forward", "encoder_forward",
     "b200_gpt2_param_offsets", "b200_gpt2_create", "b200_gpt2_destroy", "b200_gpt2_params",
     "b200_gpt2_load_params_host", "b200_gpt2_load_params_file", "b200_gpt2_set_options", "b200_gpt2_forward",
-    "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_activation",
+    "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_forward_host_enqueue", "b200_gpt2_forward_host_wait", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
     "b200_gpt2_forward_static",
     "b200_gpt2_enable_kv_cache", "b200_gpt2_prefill", "b200_gpt2_decode_step", "b200_gpt2_decode_step_host", "b200_gpt2_generate_greedy",
@@ -117,6 +117,8 @@ def lib() -> C.CDLL:
         l.b200_gpt2_logits.argtypes = [vp]
         l.b200_gpt2_logits.restype = vp
         l.b200_gpt2_forward_host.argtypes = [vp, vp, i, i, vp, vp, vp]
+        l.b200_gpt2_forward_host_enqueue.argtypes = [vp, vp, i, i, vp, vp, vp, i]
+        l.b200_gpt2_forward_host_wait.argtypes = [vp, i]
         l.b200_gpt2_activation.argtypes = [vp, C.c_char_p]
         l.b200_gpt2_activation.restype = vp
         l.b200_gpt2_set_profile.argtypes = [vp, i]
@@ -392,6 +394,17 @@ class GPT2:
         """Host-buffer call: H2D of tokens, forward, D2H of what is asked for; synchronous."""
         self.ctx.check(lib().b200_gpt2_forward_host(self._h, _ptr(tokens_host), B, T, _ptr(logits_host),
                                                     _ptr(last_logits_host), _ptr(argmax_host)), "gpt2_forward_host")
+
+    def forward_host_enqueue(self, tokens_host, B: int, T: int, slot: int, logits_host=None, last_logits_host=None,
+                             argmax_host=None):
+        """forward_host without the wait: queues copy in, forward, copies back for slot 0 or 1."""
+        self.ctx.check(lib().b200_gpt2_forward_host_enqueue(self._h, _ptr(tokens_host), B, T, _ptr(logits_host),
+                                                            _ptr(last_logits_host), _ptr(argmax_host), slot),
+                       "gpt2_forward_host_enqueue")
+
+    def forward_host_wait(self, slot: int):
+        """Blocks until the results of that slot are in the host buffers."""
+        self.ctx.check(lib().b200_gpt2_forward_host_wait(self._h, slot), "gpt2_forward_host_wait")
 
     # ---- incremental decoding with a key/value cache
     def enable_kv_cache(self):

@@ -31,7 +31,8 @@ struct b200_gpt2 {
           *branch = nullptr, *fch = nullptr, *logits = nullptr;
     int* tokens = nullptr;
     int* argmax = nullptr;
-    unsigned long long* argmax_keys = nullptr;  // per row: best (value, column) of the lm-head's fused arg-max
+    unsigned long long* argmax_keys = nullptr;  // per row: best (value, column) of the lm-head's fused arg-max; zero between forwards
+    float* last_logits = nullptr;               // logits of the last position of every sequence, gathered for the host [max rows/64][Vp]
     float *kcache = nullptr, *vcache = nullptr;  // [L][max_B][max_T][C] each (b200_gpt2_enable_kv_cache)
     bool keep_kv = false;                        // the forward being enqueued also fills the cache
     int* pos_dev = nullptr;                      // position of the decode step being run
@@ -39,6 +40,12 @@ struct b200_gpt2 {
     float* att_partial = nullptr;                // decode attention: softmax states of the position splits
     unsigned int* att_counters = nullptr;        // ... and their arrival counters (zero between launches)
     int* gen_tokens = nullptr;                   // greedy generation: prompt and continuation [max_B][max_T]
+    cudaEvent_t host_done[2] = {nullptr, nullptr};  // forward_host_enqueue / _wait: results of a slot are on the host
+    int* h_slot_status = nullptr;                // pinned: the device status word as seen behind each slot's work
+    int* d_slot_status = nullptr;                // the same two words as the device addresses them
+    // Host-buffer forward without copies: device views of the caller's pinned buffers, written by
+    // the kernel behind the lm-head (null: the model's own buffers).  Set around one enqueue_forward.
+    struct HostDst { int* ids = nullptr; float* last = nullptr; int* status = nullptr; } host_dst;
     std::map<int, cudaGraphExec_t> decode_graphs;  // by B (the position is read from pos_dev)
     int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
     // tensor parallelism (Megatron style): this rank's share of the attention heads, of the MLP
@@ -51,7 +58,7 @@ struct b200_gpt2 {
     int vp_row0 = 0;   // first row of wte used by the local lm-head
     b200_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
-    std::map<std::pair<std::pair<int, int>, bool>, cudaGraphExec_t> graphs;  // by (B, T, with arg-max)
+    std::map<std::pair<std::pair<int, int>, int>, cudaGraphExec_t> graphs;  // by (B, T, results)
     // per-operator timing (b200_gpt2_set_profile): one event pair per kernel launch
     bool profile = false;
     std::vector<cudaEvent_t> ev_pool;
@@ -129,10 +136,15 @@ int tp_allreduce(b200_gpt2* m, float* buf, size_t count) {
     return m->allreduce(m->allreduce_user, buf, count, m->ctx->stream) == 0 ? B200_OK : B200_ERR_CUDA;
 }
 
-// with_argmax: the lm-head GEMM also leaves, per position, the arg-max over the real vocabulary
-// in m->argmax (found in its epilogue while the logits are on their way out: no second pass
-// over the 1.6 GB of logits)
-int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, bool with_argmax) {
+// results, what is prepared for the host behind the lm-head:
+//   RES_ARGMAX  the lm-head GEMM also leaves, per position, the arg-max over the real vocabulary
+//               in m->argmax (found in its epilogue while the logits are on their way out: no
+//               second pass over the 1.6 GB of logits)
+//   RES_LAST    the logits of the last position of every sequence, contiguous in m->last_logits
+//   RES_STATUS  the status word, written to the pinned word the host will look at
+enum : int { RES_ARGMAX = 1, RES_LAST = 2, RES_STATUS = 4 };
+int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) {
+    const bool with_argmax = (results & RES_ARGMAX) != 0;
     using namespace b200;
     b200_ctx* ctx = m->ctx;
     const b200_gpt2_config& c = m->cfg;
@@ -210,13 +222,14 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, bool with_arg
                                              m->branch, nw, nb, M, C, (l + 1 < L) ? ln_flags : (hl ? OUT_BF16 : rnd)));
     }
     const float* head_w = ((m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0]) + (size_t)m->vp_row0 * C;
-    if (with_argmax) B200_CUDA(ctx, cudaMemsetAsync(m->argmax_keys, 0, (size_t)M * 8, ctx->stream));
     if (hl) STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_bf16(ctx, m->logits, nullptr, ln_h, PH + off[0] + (size_t)m->vp_row0 * C, nullptr, M, C, m->vp_local, 0,
                                                          with_argmax ? m->argmax_keys : nullptr, c.vocab_size));
     else STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, m->vp_local, 0, m->lmhead_mode,
                                                  with_argmax ? m->argmax_keys : nullptr, c.vocab_size));
-    if (with_argmax) {
-        st = launch_argmax_decode(ctx, m->argmax, m->argmax_keys, M);
+    if (results) {
+        st = launch_host_results(ctx, m->host_dst.ids ? m->host_dst.ids : m->argmax, with_argmax ? m->argmax_keys : nullptr, M,
+                                 (results & RES_LAST) ? (m->host_dst.last ? m->host_dst.last : m->last_logits) : nullptr,
+                                 m->logits, B, T, m->vp_local, (results & RES_STATUS) ? m->host_dst.status : nullptr);
         if (st != B200_OK) return st;
     }
 #undef STEP
@@ -362,6 +375,8 @@ int b200_gpt2_create_tp(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* 
     alloc((void**)&m->tokens, M * 4);
     alloc((void**)&m->argmax, M * 4);
     alloc((void**)&m->argmax_keys, M * 8);
+    alloc((void**)&m->last_logits, (M / 64 + 1) * Vp * 4);
+    if (e == cudaSuccess) e = cudaMemset(m->argmax_keys, 0, M * 8);
     if (e != cudaSuccess) {
         b200_fail_cuda(ctx, e, "cudaMalloc (b200_gpt2_create)");
         b200_gpt2_destroy(m);
@@ -381,9 +396,11 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     if (m->att_partial) cudaFree(m->att_partial);
     if (m->att_counters) cudaFree(m->att_counters);
     if (m->gen_tokens) cudaFree(m->gen_tokens);
+    for (cudaEvent_t e : m->host_done) if (e) cudaEventDestroy(e);
+    if (m->h_slot_status) cudaFreeHost(m->h_slot_status);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
     void* ptrs[] = {m->params, m->params_h, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
-                    m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->kcache, m->vcache};
+                    m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->last_logits, m->kcache, m->vcache};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete m;
     return B200_OK;
@@ -470,7 +487,7 @@ int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int l
     return B200_OK;
 }
 
-static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, bool with_argmax) {
+static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, int results) {
     if (!m || !tokens) return B200_ERR_NULL;
     if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
     if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
@@ -480,22 +497,22 @@ static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, bool with
         if (st != B200_OK) return st;
     }
     if (m->tp_size > 1 && !m->allreduce) return B200_ERR_STATE;
-    if (!m->use_graph || ctx->stream == nullptr || m->profile || m->tp_size > 1) return enqueue_forward(m, tokens, B, T, with_argmax);
+    if (!m->use_graph || ctx->stream == nullptr || m->profile || m->tp_size > 1) return enqueue_forward(m, tokens, B, T, results);
 
     // CUDA-graph replay: the graph reads token ids from the model's own token buffer
     if (tokens != m->tokens)
         B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens, (size_t)B * T * 4, cudaMemcpyDeviceToDevice, ctx->stream));
-    auto key = std::make_pair(std::make_pair(B, T), with_argmax);
+    auto key = std::make_pair(std::make_pair(B, T), results);
     auto it = m->graphs.find(key);
     if (it == m->graphs.end()) {
         // warm the tensor-map cache and function attributes outside of capture
-        int st = enqueue_forward(m, m->tokens, B, T, with_argmax);
+        int st = enqueue_forward(m, m->tokens, B, T, results);
         if (st != B200_OK) return st;
         B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
         cudaGraph_t graph = nullptr;
         const uint64_t launches_before = ctx->launches;
         B200_CUDA(ctx, cudaStreamBeginCapture(ctx->stream, cudaStreamCaptureModeThreadLocal));
-        st = enqueue_forward(m, m->tokens, B, T, with_argmax);
+        st = enqueue_forward(m, m->tokens, B, T, results);
         cudaError_t e = cudaStreamEndCapture(ctx->stream, &graph);
         ctx->launches = launches_before;
         if (st != B200_OK) { if (graph) cudaGraphDestroy(graph); return st; }
@@ -509,32 +526,93 @@ static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, bool with
     B200_CUDA(ctx, cudaGraphLaunch(it->second, ctx->stream));
     // kernels inside the replayed graph: encoder, first layernorm, 7 per layer (8 with the
     // 3xTF32 attention's split pass), lm-head
-    ctx->launches += 2 + (m->gemm_mode == B200_TF32X3 ? 8ull : 7ull) * m->cfg.num_layers + 1 + (with_argmax ? 1 : 0);
+    ctx->launches += 2 + (m->gemm_mode == B200_TF32X3 ? 8ull : 7ull) * m->cfg.num_layers + 1 + (results ? 1 : 0);
     return B200_OK;
 }
 
-int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) { return forward_impl(m, tokens, B, T, false); }
+int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) { return forward_impl(m, tokens, B, T, 0); }
 
-int b200_gpt2_forward_host(b200_gpt2* m, const int* tokens_host, int B, int T, float* logits_host,
-                           float* last_logits_host, int* argmax_host) {
+// Device address of a pinned (page-locked, mapped) host buffer, or null for any other memory.
+static void* device_view(const void* p) {
+    if (!p) return nullptr;
+    cudaPointerAttributes a{};
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return (a.type == cudaMemoryTypeHost) ? a.devicePointer : nullptr;
+}
+
+int b200_gpt2_forward_host_enqueue(b200_gpt2* m, const int* tokens_host, int B, int T, float* logits_host,
+                                   float* last_logits_host, int* argmax_host, int slot) {
     if (!m || !tokens_host) return B200_ERR_NULL;
+    if (slot < 0 || slot > 1) return B200_ERR_SHAPE;
     if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
     if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
     b200_ctx* ctx = m->ctx;
     const size_t M = (size_t)B * T, Vp = m->vp_local;  // a tensor-parallel rank returns its slice of the vocabulary
     if (argmax_host && m->vp_local != m->cfg.padded_vocab_size) return B200_ERR_STATE;  // needs all logits
-    B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens_host, M * 4, cudaMemcpyHostToDevice, ctx->stream));
-    int st = forward_impl(m, m->tokens, B, T, argmax_host != nullptr);
-    if (st != B200_OK) return st;
-    if (argmax_host) B200_CUDA(ctx, cudaMemcpyAsync(argmax_host, m->argmax, M * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    if (last_logits_host) {
-        // rows (b, T-1): one strided 2-D copy
-        B200_CUDA(ctx, cudaMemcpy2DAsync(last_logits_host, Vp * 4, m->logits + (size_t)(T - 1) * Vp, (size_t)T * Vp * 4,
-                                         Vp * 4, B, cudaMemcpyDeviceToHost, ctx->stream));
+    if (!m->h_slot_status) {
+        B200_CUDA(ctx, cudaSetDevice(ctx->device));
+        B200_CUDA(ctx, cudaHostAlloc(&m->h_slot_status, 2 * sizeof(int), cudaHostAllocMapped | cudaHostAllocPortable));
+        m->h_slot_status[0] = m->h_slot_status[1] = 0;
+        B200_CUDA(ctx, cudaHostGetDevicePointer(&m->d_slot_status, m->h_slot_status, 0));
+        for (int i = 0; i < 2; ++i) B200_CUDA(ctx, cudaEventCreateWithFlags(&m->host_done[i], cudaEventDisableTiming));
     }
+    // Buffers in pinned host memory are read and written by kernels (one in front of the encoder
+    // fetches the token ids, the one behind the lm-head writes ids, last-position logits and the
+    // status word): no copy is queued in front of or behind the forward, each of which would
+    // cost a drained GPU and tens of microseconds.  Pageable buffers, and everything when the
+    // forward is replayed as a graph (whose kernel arguments are fixed), go through copies.
+    const bool replay = m->use_graph && ctx->stream != nullptr && !m->profile && m->tp_size == 1;
+    const int* tok_view = (replay || !b200_aligned16(tokens_host)) ? nullptr : static_cast<const int*>(device_view(tokens_host));
+    int* ids_view = replay ? nullptr : static_cast<int*>(device_view(argmax_host));
+    float* last_view = (replay || !b200_aligned16(last_logits_host)) ? nullptr : static_cast<float*>(device_view(last_logits_host));
+    int* status_view = replay ? nullptr : m->d_slot_status + slot;
+    if (tok_view) {
+        const int fs = b200::launch_fetch_ints(ctx, m->tokens, tok_view, (int)M);
+        if (fs != B200_OK) return fs;
+    } else {
+        B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens_host, M * 4, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    m->host_dst.ids = ids_view;
+    m->host_dst.last = last_view;
+    m->host_dst.status = status_view;
+    int st = forward_impl(m, m->tokens, B, T,
+                          (argmax_host ? RES_ARGMAX : 0) | (last_logits_host ? RES_LAST : 0) | (status_view ? RES_STATUS : 0));
+    m->host_dst = {};
+    if (st != B200_OK) return st;
+    if (argmax_host && !ids_view) B200_CUDA(ctx, cudaMemcpyAsync(argmax_host, m->argmax, M * 4, cudaMemcpyDeviceToHost, ctx->stream));
+    if (last_logits_host && !last_view)  // gathered behind the lm-head: one plain copy
+        B200_CUDA(ctx, cudaMemcpyAsync(last_logits_host, m->last_logits, (size_t)B * Vp * 4, cudaMemcpyDeviceToHost, ctx->stream));
     if (logits_host)
         B200_CUDA(ctx, cudaMemcpyAsync(logits_host, m->logits, M * Vp * 4, cudaMemcpyDeviceToHost, ctx->stream));
-    return b200_ctx_sync_check(ctx);
+    if (!status_view)
+        B200_CUDA(ctx, cudaMemcpyAsync(m->h_slot_status + slot, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
+    B200_CUDA(ctx, cudaEventRecord(m->host_done[slot], ctx->stream));
+    return B200_OK;
+}
+
+int b200_gpt2_forward_host_wait(b200_gpt2* m, int slot);
+
+int b200_gpt2_forward_host(b200_gpt2* m, const int* tokens_host, int B, int T, float* logits_host,
+                           float* last_logits_host, int* argmax_host) {
+    const int st = b200_gpt2_forward_host_enqueue(m, tokens_host, B, T, logits_host, last_logits_host, argmax_host, 0);
+    return st != B200_OK ? st : b200_gpt2_forward_host_wait(m, 0);
+}
+
+int b200_gpt2_forward_host_wait(b200_gpt2* m, int slot) {
+    if (!m) return B200_ERR_NULL;
+    if (slot < 0 || slot > 1) return B200_ERR_SHAPE;
+    if (!m->h_slot_status) return B200_ERR_STATE;  // nothing was enqueued
+    b200_ctx* ctx = m->ctx;
+    B200_CUDA(ctx, cudaEventSynchronize(m->host_done[slot]));
+    const int word = m->h_slot_status[slot];
+    if (word != 0) {
+        m->h_slot_status[slot] = 0;
+        // cleared behind whatever is already queued; a step enqueued meanwhile reports the word too
+        B200_CUDA(ctx, cudaMemsetAsync(ctx->d_status, 0, 256, ctx->stream));
+        ctx->last_error = "device status word = " + std::to_string(word);
+        return word == 201 ? B200_ERR_SHAPE : B200_ERR_TIMEOUT;
+    }
+    return B200_OK;
 }
 
 int b200_gpt2_enable_kv_cache(b200_gpt2* m) {

@@ -20,6 +20,8 @@ int launch_gelu(b200_ctx* ctx, float* out, const float* inp, size_t N);
 int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,
                    int B, int T, int C, int vocab_rows /* <=0: unchecked */);
 int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N);
+// dst[0..n) = src_view[0..n): src_view is the device view of a pinned host buffer (16-byte aligned)
+int launch_fetch_ints(b200_ctx* ctx, int* dst, const int* src_view, int n);
 // out[i] = bf16(in[i]), round to nearest even; N a multiple of 4
 int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N);
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
@@ -36,8 +38,12 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
 int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,
                      const float* bias, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys = nullptr, int argmax_cols = 0);
-// turns the keys left by a GEMM with fused arg-max into column indices (0 for an untouched key)
-int launch_argmax_decode(b200_ctx* ctx, int* out, const unsigned long long* keys, int M);
+// After the lm-head: turns the keys left by a GEMM with fused arg-max into column indices and
+// zeroes them (keys may be null), and gathers the last position's logits of every sequence into
+// last_dst[B,Vp] (may be null), and copies the context's status word to status_dst (may be null).
+// out, last_dst and status_dst may be device views of pinned host memory.  Vp % 4 == 0.
+int launch_host_results(b200_ctx* ctx, int* out, unsigned long long* keys, int M, float* last_dst,
+                        const float* logits, int B, int T, int Vp, int* status_dst = nullptr);
 
 int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, int B, int T, int C,
                      int NH, int flags);

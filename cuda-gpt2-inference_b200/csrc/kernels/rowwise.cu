@@ -181,24 +181,47 @@ __global__ void round_tf32_kernel(float4* data, size_t n4, float* data_s, size_t
 
 // out[bt, :] = wte[tok[bt], :] + wpe[bt % T, :]; one fp32 add per element (bit-exact).
 // An id outside [0, vocab_rows) (when checked) is recorded in *status and treated as 0.
-__global__ void encoder_kernel(float4* __restrict__ out, const int* __restrict__ tok,
-                               const float4* __restrict__ wte, const float4* __restrict__ wpe,
-                               int M, int T, int C4, int vocab_rows, int* status) {
+// One warp per row: the token id is read once per row (it may sit in pinned host memory and
+// come over PCIe) and handed to the other lanes by shuffle.
+__global__ void __launch_bounds__(kRowWarps * 32)
+encoder_kernel(float4* __restrict__ out, const int* __restrict__ tok,
+               const float4* __restrict__ wte, const float4* __restrict__ wpe,
+               int M, int T, int C4, int vocab_rows, int* status) {
     griddep_wait();
     griddep_launch_dependents();
-    const size_t total = (size_t)M * C4;
-    const size_t stride = (size_t)gridDim.x * blockDim.x;
-    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
-        const int bt = (int)(i / C4), c = (int)(i % C4);
-        int id = __ldg(tok + bt);
-        if (vocab_rows > 0 && (id < 0 || id >= vocab_rows)) {
-            if (c == 0) atomicCAS(status, 0, 201);
-            id = 0;
+    const int lane = threadIdx.x & 31;
+    const int warps = gridDim.x * kRowWarps;
+    for (int bt = blockIdx.x * kRowWarps + (threadIdx.x >> 5); bt < M; bt += warps) {
+        int id = 0;
+        if (lane == 0) {
+            id = tok[bt];
+            if (vocab_rows > 0 && (id < 0 || id >= vocab_rows)) {
+                atomicCAS(status, 0, 201);
+                id = 0;
+            }
         }
-        const float4 e = __ldg(wte + (size_t)id * C4 + c);
-        const float4 p = __ldg(wpe + (size_t)(bt % T) * C4 + c);
-        out[i] = make_float4(e.x + p.x, e.y + p.y, e.z + p.z, e.w + p.w);
+        id = __shfl_sync(0xffffffffu, id, 0);
+        const float4* e4 = wte + (size_t)id * C4;
+        const float4* p4 = wpe + (size_t)(bt % T) * C4;
+        float4* o4 = out + (size_t)bt * C4;
+        for (int c = lane; c < C4; c += 32) {
+            const float4 e = __ldg(e4 + c);
+            const float4 p = __ldg(p4 + c);
+            o4[c] = make_float4(e.x + p.x, e.y + p.y, e.z + p.z, e.w + p.w);
+        }
     }
+}
+
+// dst[i] = src[i] for n ints, src being the device view of a pinned host buffer: the token ids
+// come over PCIe in 16-byte pieces (a few hundred read requests for a whole batch; reading them
+// one id at a time from the consumer would be thousands of PCIe round trips).
+__global__ void fetch_ints_kernel(int* __restrict__ dst, const int* __restrict__ src, int n) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int n4 = n >> 2;
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n4) reinterpret_cast<int4*>(dst)[i] = reinterpret_cast<const int4*>(src)[i];
+    if (i < (n & 3)) dst[n4 * 4 + i] = src[n4 * 4 + i];
 }
 
 // arg-max over columns [0,V) of each row (ties -> lowest index); one CTA per row.
@@ -311,11 +334,19 @@ int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N)
 
 int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,
                    int B, int T, int C, int vocab_rows) {
-    const size_t n4 = (size_t)B * T * (C / 4);
-    const int grid = stream_grid(ctx, n4, 256, 16);
-    cudaError_t le = launch_pdl(ctx, encoder_kernel, dim3(grid), dim3(256), 0, reinterpret_cast<float4*>(out), tok,
+    int grid = (B * T + kRowWarps - 1) / kRowWarps;
+    if (grid > 16 * ctx->num_sms) grid = 16 * ctx->num_sms;
+    cudaError_t le = launch_pdl(ctx, encoder_kernel, dim3(grid), dim3(kRowWarps * 32), 0, reinterpret_cast<float4*>(out), tok,
                                 reinterpret_cast<const float4*>(wte), reinterpret_cast<const float4*>(wpe), B * T, T,
                                 C / 4, vocab_rows, ctx->d_status);
+    ctx->launches++;
+    B200_CUDA(ctx, le);
+    return B200_OK;
+}
+
+int launch_fetch_ints(b200_ctx* ctx, int* dst, const int* src_view, int n) {
+    const int threads = 256, grid = (n / 4 + threads) / threads;
+    cudaError_t le = launch_pdl(ctx, fetch_ints_kernel, dim3(grid), dim3(threads), 0, dst, src_view, n);
     ctx->launches++;
     B200_CUDA(ctx, le);
     return B200_OK;
@@ -328,15 +359,49 @@ int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns) {
     return B200_OK;
 }
 
-__global__ void argmax_decode_kernel(int* __restrict__ out, const unsigned long long* __restrict__ keys, int M) {
-    const int i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < M) out[i] = keys[i] ? (int)(0xFFFFFFFFu - (uint32_t)(keys[i] & 0xFFFFFFFFull)) : 0;
+// What the host-buffer forward sends back, prepared in one pass behind the lm-head:
+//  * keys != null: the arg-max keys become column indices (0 for an untouched key) and are put
+//    back to zero, which is the state the next lm-head with fused arg-max starts from;
+//  * last_dst != null: the logits of the last position of every sequence, rows (b, T-1) of
+//    logits[B*T, Vp], are gathered into the contiguous last_dst[B, Vp] (one plain copy to the
+//    host instead of a strided one);
+//  * status_dst != null: the context's status word as it stands behind all earlier kernels.
+// out, last_dst and status_dst may address pinned host memory mapped into the device's address
+// space: the results then cross PCIe from here and no copy is queued behind the forward.
+__global__ void host_results_kernel(int* __restrict__ out, unsigned long long* __restrict__ keys, int M,
+                                    float4* __restrict__ last_dst, const float4* __restrict__ logits, int B, int T,
+                                    int Vp4, int* status_dst, const int* status_src) {
+    griddep_wait();
+    if (status_dst && blockIdx.x == 0 && threadIdx.x == 0) *status_dst = *status_src;
+    const int stride = gridDim.x * blockDim.x;
+    const int t0 = blockIdx.x * blockDim.x + threadIdx.x;
+    if (keys) {
+        for (int i = t0; i < M; i += stride) {
+            const unsigned long long k = keys[i];
+            out[i] = k ? (int)(0xFFFFFFFFu - (uint32_t)(k & 0xFFFFFFFFull)) : 0;
+            keys[i] = 0ull;
+        }
+    }
+    if (last_dst) {
+        const int total = B * Vp4;
+        for (int i = t0; i < total; i += stride) {
+            const int b = i / Vp4, c = i - b * Vp4;
+            last_dst[i] = logits[((size_t)b * T + (T - 1)) * Vp4 + c];
+        }
+    }
 }
 
-int launch_argmax_decode(b200_ctx* ctx, int* out, const unsigned long long* keys, int M) {
-    argmax_decode_kernel<<<(M + 255) / 256, 256, 0, ctx->stream>>>(out, keys, M);
+int launch_host_results(b200_ctx* ctx, int* out, unsigned long long* keys, int M, float* last_dst,
+                        const float* logits, int B, int T, int Vp, int* status_dst) {
+    const int work = (keys ? M : 0) > (last_dst ? B * (Vp / 4) : 0) ? M : (last_dst ? B * (Vp / 4) : M);
+    int grid = (work + 255) / 256;
+    if (grid > 4 * ctx->num_sms) grid = 4 * ctx->num_sms;
+    if (grid < 1) grid = 1;
+    cudaError_t le = launch_pdl(ctx, host_results_kernel, dim3(grid), dim3(256), 0, out, keys, M,
+                                reinterpret_cast<float4*>(last_dst), reinterpret_cast<const float4*>(logits), B, T, Vp / 4,
+                                status_dst, static_cast<const int*>(ctx->d_status));
     ctx->launches++;
-    B200_CUDA(ctx, cudaGetLastError());
+    B200_CUDA(ctx, le);
     return B200_OK;
 }
 

@@ -220,6 +220,15 @@ float* b200_gpt2_logits(b200_gpt2* model);
  *   argmax_host      [B,T]     arg-max token over [0,V) per position (nullable) */
 int b200_gpt2_forward_host(b200_gpt2* model, const int* tokens_host, int B, int T,
                            float* logits_host, float* last_logits_host, int* argmax_host);
+/* The same call split in two, so that the host can prepare and enqueue the next batch while the
+ * GPU works on the current one (two batches in flight, slot = 0 or 1): _enqueue queues the token
+ * copy, the forward and the copies back and returns at once; _wait blocks until the results of
+ * that slot are in the caller's buffers and reports a device-side error recorded up to then.  The
+ * host buffers of a slot (pinned, for the copies to overlap) must stay untouched between the two
+ * calls.  Work is stream-ordered: the batches run one after the other on the GPU. */
+int b200_gpt2_forward_host_enqueue(b200_gpt2* model, const int* tokens_host, int B, int T,
+                                   float* logits_host, float* last_logits_host, int* argmax_host, int slot);
+int b200_gpt2_forward_host_wait(b200_gpt2* model, int slot);
 /* ---- incremental decoding with a key/value cache (no counterpart in the reference, which has
  * full-sequence kernels only; the operators and their order are those of the forward above) ----
  * b200_gpt2_enable_kv_cache allocates the cache: keys and values of every layer for max_B

@@ -269,3 +269,39 @@ def test_load_params_file_reads_raw_parameters_behind_a_header(pkg, orc, ctx, tm
         fresh.load_params_file(str(tmp_path / "absent.bin"), 0)
     fresh.close()
     model.close()
+
+
+def test_enqueue_wait_pair_matches_the_synchronous_host_call(pkg, orc, ctx):
+    """Two batches in flight through forward_host_enqueue / _wait return exactly what the
+    synchronous forward_host returns for each of them; a bad token id is reported by the wait of
+    the batch that holds it."""
+    import torch
+    B, T = 2, 128
+    cfg, ocfg, params, model = _make(pkg, orc, ctx, dict(num_layers=2), B, T)
+    V, Vp = cfg.vocab_size, cfg.padded_vocab_size
+    toks = [torch.from_numpy(orc.fill_tokens((B, T), seed=s, vocab=V)).pin_memory() for s in (11, 12, 13)]
+    want = []
+    for t in toks:
+        last, amax = np.empty((B, Vp), np.float32), np.empty((B, T), np.int32)
+        model.forward_host(t.numpy(), B, T, last_logits_host=last, argmax_host=amax)
+        want.append((last, amax))
+    bufs = [(torch.empty((B, Vp)).pin_memory(), torch.empty((B, T), dtype=torch.int32).pin_memory()) for _ in range(2)]
+    got = []
+    model.forward_host_enqueue(toks[0].numpy(), B, T, 0, last_logits_host=bufs[0][0].numpy(), argmax_host=bufs[0][1].numpy())
+    for i in (1, 2):
+        model.forward_host_enqueue(toks[i].numpy(), B, T, i & 1, last_logits_host=bufs[i & 1][0].numpy(), argmax_host=bufs[i & 1][1].numpy())
+        model.forward_host_wait((i - 1) & 1)
+        got.append((bufs[(i - 1) & 1][0].numpy().copy(), bufs[(i - 1) & 1][1].numpy().copy()))
+    model.forward_host_wait(0)
+    got.append((bufs[0][0].numpy().copy(), bufs[0][1].numpy().copy()))
+    for (wl, wa), (gl, ga) in zip(want, got):
+        assert np.array_equal(wl, gl) and np.array_equal(wa, ga)
+    bad = toks[0].clone().pin_memory()
+    bad[1, 5] = V + 1000
+    model.forward_host_enqueue(bad.numpy(), B, T, 1, last_logits_host=bufs[1][0].numpy())
+    with pytest.raises(pkg.B200Error):
+        model.forward_host_wait(1)
+    model.forward_host_enqueue(toks[0].numpy(), B, T, 0, last_logits_host=bufs[0][0].numpy())
+    model.forward_host_wait(0)  # the context is usable again
+    assert np.array_equal(bufs[0][0].numpy(), want[0][0])
+    model.close()
