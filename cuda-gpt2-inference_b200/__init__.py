@@ -43,7 +43,7 @@ EXPORTS = (
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_forward_host_enqueue", "b200_gpt2_forward_host_wait", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
     "b200_gpt2_forward_static",
-    "b200_gpt2_enable_kv_cache", "b200_gpt2_prefill", "b200_gpt2_decode_step", "b200_gpt2_decode_step_host", "b200_gpt2_generate_greedy",
+    "b200_gpt2_enable_kv_cache", "b200_gpt2_prefill", "b200_gpt2_decode_step", "b200_gpt2_decode_step_host", "b200_gpt2_generate_greedy", "b200_gpt2_generate", "b200_sample_rows",
     "b200_gpt2_create_tp", "b200_gpt2_set_allreduce", "b200_gpt2_param_offsets_tp", "b200_gpt2_shard_params_host",
 )
 
@@ -129,6 +129,8 @@ def lib() -> C.CDLL:
         l.b200_gpt2_decode_step.argtypes = [vp, vp, i, i]
         l.b200_gpt2_decode_step_host.argtypes = [vp, vp, i, i, vp, vp]
         l.b200_gpt2_generate_greedy.argtypes = [vp, vp, i, i, i, vp]
+        l.b200_gpt2_generate.argtypes = [vp, vp, i, i, i, C.c_float, C.c_uint, vp]
+        l.b200_sample_rows.argtypes = [vp, vp, vp, i, i, i, C.c_float, C.c_uint, C.c_uint]
         l.b200_gpt2_create_tp.argtypes = [C.POINTER(vp), vp, vp, i, i, i, i]
         l.b200_gpt2_set_allreduce.argtypes = [vp, ALLREDUCE_FN, vp]
         l.b200_gpt2_param_offsets_tp.argtypes = [vp, i, i, C.POINTER(sz)]
@@ -205,6 +207,10 @@ class Context:
 
     def convert_bf16(self, out, inp, n):
         self.check(lib().b200_convert_bf16(self._h, _ptr(out), _ptr(inp), n), "convert_bf16")
+
+    def sample_rows(self, out, logits, M, V, ld, temperature, seed, stream0):
+        self.check(lib().b200_sample_rows(self._h, _ptr(out), _ptr(logits), M, V, ld, float(temperature),
+                                          int(seed) & 0xFFFFFFFF, int(stream0) & 0xFFFFFFFF), "sample_rows")
 
     def attention_forward(self, out, qkvr, att, inp, B, T, Cc, NH):
         self.check(lib().b200_attention_forward(self._h, _ptr(out), _ptr(qkvr), _ptr(att), _ptr(inp), B, T, Cc, NH),
@@ -434,6 +440,11 @@ class GPT2:
         """Greedy continuation: prompt_host int32 [B,T0] -> out_host int32 [B,n_new]; synchronous."""
         self.ctx.check(lib().b200_gpt2_generate_greedy(self._h, _ptr(prompt_host), B, T0, n_new, _ptr(out_host)),
                        "gpt2_generate_greedy")
+
+    def generate(self, prompt_host, B: int, T0: int, n_new: int, out_host, temperature: float = 1.0, seed: int = 0):
+        """Sampled continuation (temperature <= 0: greedy); reproducible for a given seed."""
+        self.ctx.check(lib().b200_gpt2_generate(self._h, _ptr(prompt_host), B, T0, n_new, float(temperature),
+                                                int(seed) & 0xFFFFFFFF, _ptr(out_host)), "gpt2_generate")
 
     def set_profile(self, enabled: bool):
         self.ctx.check(lib().b200_gpt2_set_profile(self._h, int(enabled)), "set_profile")

@@ -25,6 +25,10 @@ int launch_fetch_ints(b200_ctx* ctx, int* dst, const int* src_view, int n);
 // out[i] = bf16(in[i]), round to nearest even; N a multiple of 4
 int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N);
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
+// one draw per row from softmax(logits / temperature) (Gumbel-max; temperature <= 0: arg-max);
+// row r uses the noise stream stream0 + r of the seed
+int launch_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld, float temperature,
+                       unsigned int seed, unsigned int stream0);
 int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns);
 
 // epilogue flags of the GEMM

@@ -258,6 +258,49 @@ argmax_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
     }
 }
 
+// Counter-based random bits: two rounds of a 32-bit integer mixer over (seed, stream, column).
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    return x;
+}
+__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t stream, uint32_t col) {
+    const uint32_t h = mix32(mix32(seed ^ (stream * 0x9E3779B1u)) ^ (col * 0x85EBCA77u));
+    const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0,1), 24 bits
+    return -__logf(-__logf(u));
+}
+
+// Draws one column per row from softmax(logits / temperature) over columns [0,V): the arg-max of
+// logit * inv_temp + Gumbel noise has exactly that distribution, so sampling is the greedy
+// reduction with a perturbed score.  The noise is a pure function of (seed, stream0 + row,
+// column): the same call gives the same tokens.  One CTA per row.
+__global__ void __launch_bounds__(256)
+sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, int ld, float inv_temp,
+                   uint32_t seed, uint32_t stream0) {
+    const float* row = logits + (size_t)blockIdx.x * ld;
+    const uint32_t stream = stream0 + blockIdx.x;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float sc = row[i] * inv_temp + gumbel_noise(seed, stream, (uint32_t)i);
+        if (sc > best) { best = sc; bi = i; }
+    }
+    __shared__ float sb[8];
+    __shared__ int si[8];
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, s);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, s);
+        if (ob > best || (ob == best && oi < bi)) { best = ob; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sb[threadIdx.x >> 5] = best; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sb[w] > best || (sb[w] == best && si[w] < bi)) { best = sb[w]; bi = si[w]; }
+        out[blockIdx.x] = bi;
+    }
+}
+
 // Exercises the bounded-wait path on purpose-built inputs: one thread waits on an mbarrier that
 // nothing ever arrives on, gives up after limit_ns, and records the time-out exactly as the
 // GEMM / attention roles do.  The kernel returns normally and the context stays usable.
@@ -407,6 +450,15 @@ int launch_host_results(b200_ctx* ctx, int* out, unsigned long long* keys, int M
 
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld) {
     argmax_rows_kernel<<<M, 256, 0, ctx->stream>>>(out, logits, V, ld);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld, float temperature,
+                       unsigned int seed, unsigned int stream0) {
+    if (!(temperature > 0.f)) return launch_argmax_rows(ctx, out, logits, M, V, ld);
+    sample_rows_kernel<<<M, 256, 0, ctx->stream>>>(out, logits, V, ld, 1.0f / temperature, seed, stream0);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

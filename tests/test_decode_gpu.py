@@ -109,3 +109,80 @@ def test_generate_greedy_follows_the_oracle(pkg, orc, ctx, T0, use_graph):
                 assert top2[1] - top2[0] < 2e-3 and logits[b, out[b, i]] >= top2[0] - 1e-6, (b, i)
         seq = np.concatenate([seq, out[:, i:i + 1]], axis=1)
     model.close()
+
+
+# ------------------------------------------------------------------ sampling
+def _mix32(x):
+    x = x.astype(np.uint64)
+    x ^= x >> np.uint64(16); x = (x * np.uint64(0x7feb352d)) & np.uint64(0xFFFFFFFF)
+    x ^= x >> np.uint64(15); x = (x * np.uint64(0x846ca68b)) & np.uint64(0xFFFFFFFF)
+    x ^= x >> np.uint64(16)
+    return x
+
+
+def _gumbel(seed, stream, cols):
+    """numpy restatement of the device's counter-based Gumbel noise (float64 logs)."""
+    a = _mix32(np.uint64(seed) ^ ((stream.astype(np.uint64) * np.uint64(0x9E3779B1)) & np.uint64(0xFFFFFFFF)))
+    h = _mix32(a[:, None] ^ ((cols.astype(np.uint64)[None, :] * np.uint64(0x85EBCA77)) & np.uint64(0xFFFFFFFF)))
+    u = ((h >> np.uint64(8)).astype(np.float64) + 0.5) / 16777216.0
+    return -np.log(-np.log(u))
+
+
+def test_sample_rows_draws_from_the_softmax(ctx, dev):
+    """Gumbel-max sampling: the draws equal the arg-max of logit/T + noise computed in numpy with
+    the same counter-based noise, their frequencies follow softmax(logits/T), a call is
+    reproducible, and temperature 0 is the arg-max."""
+    import torch
+    M, V, temp, seed = 20000, 8, 0.7, 1234
+    row = np.array([0.3, -1.0, 1.2, 0.0, 2.0, -0.5, 0.9, 1.5], np.float32)
+    logits = dev.to(np.tile(row, (M, 1)))
+    out = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    ctx.sample_rows(out, logits, M, V, V, temp, seed, 77)
+    ctx.sync_check()
+    got = out.cpu().numpy()
+    score = row.astype(np.float64)[None, :] / temp + _gumbel(seed, np.arange(77, 77 + M), np.arange(V))
+    assert (got == score.argmax(1)).mean() > 0.9995  # float32 logs on the device: a rare near-tie may flip
+    p = np.exp(row.astype(np.float64) / temp); p /= p.sum()
+    freq = np.bincount(got, minlength=V) / M
+    assert (np.abs(freq - p) < 5 * np.sqrt(p * (1 - p) / M)).all(), (freq, p)
+    out2 = torch.empty_like(out)
+    ctx.sample_rows(out2, logits, M, V, V, temp, seed, 77)
+    ctx.sync_check()
+    assert torch.equal(out, out2)
+    ctx.sample_rows(out2, logits, M, V, V, temp, seed + 1, 77)
+    ctx.sync_check()
+    assert not torch.equal(out, out2)
+    ctx.sample_rows(out2, logits, M, V, V, 0.0, seed, 77)
+    ctx.sync_check()
+    assert (out2.cpu().numpy() == int(row.argmax())).all()
+
+
+@pytest.mark.parametrize("T0", [5, 64])
+def test_generate_with_temperature_is_reproducible_and_follows_its_logits(pkg, orc, ctx, T0):
+    """Sampled generation: same seed, same continuation; and every drawn token is the arg-max of
+    the oracle's logits for the sequence so far, divided by the temperature, plus the noise of its
+    (position, sequence) stream - up to near-ties."""
+    B, n_new, temp, seed = 3, 5, 0.8, 99
+    cfg, ocfg, params, model = _model(pkg, orc, ctx, dict(num_layers=2), B, 128, 0)
+    model.set_options(round_operands=0)
+    prompt = np.ascontiguousarray(orc.fill_tokens((B, T0), seed=31, vocab=cfg.vocab_size))
+    out, again, greedy = (np.empty((B, n_new), np.int32) for _ in range(3))
+    model.generate(prompt, B, T0, n_new, out, temperature=temp, seed=seed)
+    model.generate(prompt, B, T0, n_new, again, temperature=temp, seed=seed)
+    model.generate(prompt, B, T0, n_new, greedy, temperature=0.0)
+    assert np.array_equal(out, again)
+    assert not np.array_equal(out, greedy)
+    V = cfg.vocab_size
+    assert out.min() >= 0 and out.max() < V
+    seq = prompt.copy()
+    for i in range(n_new):
+        T = seq.shape[1]
+        padded = np.zeros((B, (T + 63) // 64 * 64), np.int32)
+        padded[:, :T] = seq
+        logits = orc.gpt2_forward(params, ocfg, padded, precise=True)[:, T - 1, :V].astype(np.float64)
+        for b in range(B):
+            score = logits[b] / temp + _gumbel(seed, np.array([T * 16 + b]), np.arange(V))[0]
+            assert score[out[b, i]] >= score.max() - 5e-3, (b, i)
+        seq = np.concatenate([seq, out[:, i:i + 1]], axis=1)
+    model.close()
