@@ -142,7 +142,10 @@ int tp_allreduce(b200_gpt2* m, float* buf, size_t count) {
 //               second pass over the 1.6 GB of logits)
 //   RES_LAST    the logits of the last position of every sequence, contiguous in m->last_logits
 //   RES_STATUS  the status word, written to the pinned word the host will look at
-enum : int { RES_ARGMAX = 1, RES_LAST = 2, RES_STATUS = 4 };
+//   RES_NO_LOGITS  (with RES_ARGMAX) nobody reads the full logits: the lm-head writes only the
+//               32-row blocks that hold a sequence's last position - the arg-max is taken from
+//               the accumulators, so 1.6 GB of stores per step fall away
+enum : int { RES_ARGMAX = 1, RES_LAST = 2, RES_STATUS = 4, RES_NO_LOGITS = 8 };
 int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) {
     const bool with_argmax = (results & RES_ARGMAX) != 0;
     using namespace b200;
@@ -222,10 +225,11 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
                                              m->branch, nw, nb, M, C, (l + 1 < L) ? ln_flags : (hl ? OUT_BF16 : rnd)));
     }
     const float* head_w = ((m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0]) + (size_t)m->vp_row0 * C;
+    const int store_period = (with_argmax && (results & RES_NO_LOGITS)) ? T : 0;
     if (hl) STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_bf16(ctx, m->logits, nullptr, ln_h, PH + off[0] + (size_t)m->vp_row0 * C, nullptr, M, C, m->vp_local, 0,
-                                                         with_argmax ? m->argmax_keys : nullptr, c.vocab_size));
+                                                         with_argmax ? m->argmax_keys : nullptr, c.vocab_size, store_period));
     else STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, m->vp_local, 0, m->lmhead_mode,
-                                                 with_argmax ? m->argmax_keys : nullptr, c.vocab_size));
+                                                 with_argmax ? m->argmax_keys : nullptr, c.vocab_size, store_period));
     if (results) {
         st = launch_host_results(ctx, m->host_dst.ids ? m->host_dst.ids : m->argmax, with_argmax ? m->argmax_keys : nullptr, M,
                                  (results & RES_LAST) ? (m->host_dst.last ? m->host_dst.last : m->last_logits) : nullptr,
@@ -576,7 +580,8 @@ int b200_gpt2_forward_host_enqueue(b200_gpt2* m, const int* tokens_host, int B, 
     m->host_dst.last = last_view;
     m->host_dst.status = status_view;
     int st = forward_impl(m, m->tokens, B, T,
-                          (argmax_host ? RES_ARGMAX : 0) | (last_logits_host ? RES_LAST : 0) | (status_view ? RES_STATUS : 0));
+                          (argmax_host ? RES_ARGMAX : 0) | (last_logits_host ? RES_LAST : 0) | (status_view ? RES_STATUS : 0) |
+                              ((argmax_host && !logits_host) ? RES_NO_LOGITS : 0));
     m->host_dst = {};
     if (st != B200_OK) return st;
     if (argmax_host && !ids_view) B200_CUDA(ctx, cudaMemcpyAsync(argmax_host, m->argmax, M * 4, cudaMemcpyDeviceToHost, ctx->stream));

@@ -27,6 +27,9 @@ struct GemmArgs {
     // only for a plain epilogue (no bias, activation, residual or rounding)
     unsigned long long* argmax_keys;
     int argmax_cols;
+    // > 0: rows come in sequences of store_period (a multiple of 32) and only the 32-row blocks that
+    // hold a sequence's last row are written; the rest of the output is wanted as arg-max only
+    int store_period;
 };
 
 // Arg-max keys: the value as an order-preserving 32-bit integer in the high half, the inverted
@@ -76,6 +79,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         if (best_key != 0ull) best_v = argmax_dec((uint32_t)(best_key >> 32));
     }
     const bool via_tma = args.residual == nullptr;
+    const bool skip_store = args.store_period > 0 && (row0 % args.store_period) < args.store_period - 32;
     if (via_tma) {  // the stores of the previous tile have left the staging buffers
         if (lane == 0) tma_store_wait_read();
         __syncwarp();
@@ -103,6 +107,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
                 best_v = argmax_dec((uint32_t)(best_key >> 32));
             }
         }
+        if (skip_store) continue;
         if (args.out_h) {
             // bf16 output: 64 columns x 2 bytes fill one 128-byte row, so two 32-column chunks
             // share a staging buffer and leave as one {32 rows x 64 columns} TMA store
@@ -210,6 +215,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
 // bf16 != 0: inp and weight hold bf16 elements (kind::f16); out_h as in GemmArgs.
 int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                           const float* bias, const float* residual, int M, int K, int N, int flags,
-                          unsigned long long* argmax_keys, int argmax_cols, int bf16 = 0, uint16_t* out_h = nullptr);
+                          unsigned long long* argmax_keys, int argmax_cols, int bf16 = 0, uint16_t* out_h = nullptr,
+                          int store_period = 0);
 
 }  // namespace b200

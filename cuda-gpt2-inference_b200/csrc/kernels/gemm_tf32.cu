@@ -299,7 +299,8 @@ namespace {
 // bf16 != 0: inp / weight hold bf16 elements and out_h (if not null) receives the output as bf16.
 int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp, const void* weight,
                     const float* bias, const float* residual, int M, int K, int N, int flags,
-                    int mode, unsigned long long* argmax_keys, int argmax_cols, bool bf16) {
+                    int mode, unsigned long long* argmax_keys, int argmax_cols, bool bf16, int store_period) {
+    if (store_period && (store_period % 32 || residual || !argmax_keys)) { ctx->last_error = "store_period: multiple of 32, with the fused arg-max only"; return B200_ERR_STATE; }
     const bool x3 = (mode == B200_TF32X3);
     // the fused arg-max looks at the raw accumulator: only with a plain epilogue
     if (argmax_keys && (bias || residual || flags != 0 || out_h)) { ctx->last_error = "fused arg-max needs a plain GEMM epilogue"; return B200_ERR_STATE; }
@@ -336,7 +337,7 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
     if (pair_env >= 0) use_pair = pair_env == 1;
     if (!x3 && use_pair)
         return launch_gemm_tf32_pair(ctx, out, static_cast<const float*>(inp), static_cast<const float*>(weight), bias, residual,
-                                     M, K, N, flags, argmax_keys, argmax_cols, bf16 ? 1 : 0, out_h);
+                                     M, K, N, flags, argmax_keys, argmax_cols, bf16 ? 1 : 0, out_h, store_period);
     GemmArgs a;
     a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
@@ -349,6 +350,7 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
     a.status = ctx->d_status;
     a.argmax_keys = argmax_keys;
     a.argmax_cols = argmax_cols;
+    a.store_period = store_period;
 
     CUtensorMap ta, tb, to;
     int st;
@@ -389,15 +391,15 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
 
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
-                     int mode, unsigned long long* argmax_keys, int argmax_cols) {
-    return launch_gemm_any(ctx, out, nullptr, inp, weight, bias, residual, M, K, N, flags, mode, argmax_keys, argmax_cols, false);
+                     int mode, unsigned long long* argmax_keys, int argmax_cols, int store_period) {
+    return launch_gemm_any(ctx, out, nullptr, inp, weight, bias, residual, M, K, N, flags, mode, argmax_keys, argmax_cols, false, store_period);
 }
 
 int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,
                      const float* bias, int M, int K, int N, int flags,
-                     unsigned long long* argmax_keys, int argmax_cols) {
+                     unsigned long long* argmax_keys, int argmax_cols, int store_period) {
     if (K % 8 || N % 8) { ctx->last_error = "bf16 GEMM: K and N must be multiples of 8"; return B200_ERR_SHAPE; }
-    return launch_gemm_any(ctx, out, out_h, inp, weight, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32), B200_TF32, argmax_keys, argmax_cols, true);
+    return launch_gemm_any(ctx, out, out_h, inp, weight, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32), B200_TF32, argmax_keys, argmax_cols, true, store_period);
 }
 
 }  // namespace b200

@@ -283,7 +283,7 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, con
 
 int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                           const float* bias, const float* residual, int M, int K, int N, int flags,
-                          unsigned long long* argmax_keys, int argmax_cols, int bf16, uint16_t* out_h) {
+                          unsigned long long* argmax_keys, int argmax_cols, int bf16, uint16_t* out_h, int store_period) {
     const int num_pairs_max = ctx->num_sms / 2;
     const int num_m = (M + 2 * BM - 1) / (2 * BM);
     const int bke = bf16 ? kGemmBKH : BK;
@@ -314,6 +314,7 @@ int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const flo
     a.status = ctx->d_status;
     a.argmax_keys = argmax_keys;
     a.argmax_cols = argmax_cols;
+    a.store_period = store_period;
 
     CUtensorMap ta, tb, to;
     int st;

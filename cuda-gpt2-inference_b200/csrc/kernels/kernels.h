@@ -35,13 +35,15 @@ int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns);
 enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2 };
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
-                     int mode, unsigned long long* argmax_keys = nullptr, int argmax_cols = 0);
+                     int mode, unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0);
 // The same product with bf16 operands (tcgen05 kind::f16, fp32 accumulation): inp [M,K] and weight
 // [N,K] hold bf16; the result goes to out (fp32) or, if out_h is not null, to out_h as bf16.
 // flags: GEMM_GELU only.  K and N multiples of 8.
 int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,
                      const float* bias, int M, int K, int N, int flags,
-                     unsigned long long* argmax_keys = nullptr, int argmax_cols = 0);
+                     unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0);
+// (store_period > 0, with the fused arg-max: rows come in sequences of store_period and only the
+// 32-row blocks holding a sequence's last row are written to out)
 // After the lm-head: turns the keys left by a GEMM with fused arg-max into column indices and
 // zeroes them (keys may be null), and gathers the last position's logits of every sequence into
 // last_dst[B,Vp] (may be null), and copies the context's status word to status_dst (may be null).

@@ -217,7 +217,9 @@ float* b200_gpt2_logits(b200_gpt2* model);
  * and copies back what is asked for, synchronising before it returns:
  *   logits_host      [B,T,Vp]  all logits                     (nullable)
  *   last_logits_host [B,Vp]    logits of the last position    (nullable)
- *   argmax_host      [B,T]     arg-max token over [0,V) per position (nullable) */
+ *   argmax_host      [B,T]     arg-max token over [0,V) per position (nullable) 
+ * When argmax_host is given and logits_host is NULL nobody needs the full logits: the lm-head then
+ * writes only the last-position rows, and the model's device logits buffer holds nothing else. */
 int b200_gpt2_forward_host(b200_gpt2* model, const int* tokens_host, int B, int T,
                            float* logits_host, float* last_logits_host, int* argmax_host);
 /* The same call split in two, so that the host can prepare and enqueue the next batch while the

@@ -285,6 +285,12 @@ def test_enqueue_wait_pair_matches_the_synchronous_host_call(pkg, orc, ctx):
         last, amax = np.empty((B, Vp), np.float32), np.empty((B, T), np.int32)
         model.forward_host(t.numpy(), B, T, last_logits_host=last, argmax_host=amax)
         want.append((last, amax))
+    # without logits_host the lm-head skips the stores of all but the last-position rows: ids and
+    # last logits must still be those of the full logits
+    full = np.empty((B, T, Vp), np.float32)
+    model.forward_host(toks[0].numpy(), B, T, logits_host=full)
+    assert np.array_equal(want[0][0], full[:, -1, :])
+    assert np.array_equal(want[0][1], full[..., :V].argmax(-1))
     bufs = [(torch.empty((B, Vp)).pin_memory(), torch.empty((B, T), dtype=torch.int32).pin_memory()) for _ in range(2)]
     got = []
     model.forward_host_enqueue(toks[0].numpy(), B, T, 0, last_logits_host=bufs[0][0].numpy(), argmax_host=bufs[0][1].numpy())
