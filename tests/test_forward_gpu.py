@@ -271,13 +271,16 @@ def test_load_params_file_reads_raw_parameters_behind_a_header(pkg, orc, ctx, tm
     model.close()
 
 
-def test_enqueue_wait_pair_matches_the_synchronous_host_call(pkg, orc, ctx):
+@pytest.mark.parametrize("use_graph,bf16", [(0, False), (1, False), (0, True)])
+def test_enqueue_wait_pair_matches_the_synchronous_host_call(pkg, orc, ctx, use_graph, bf16):
     """Two batches in flight through forward_host_enqueue / _wait return exactly what the
     synchronous forward_host returns for each of them; a bad token id is reported by the wait of
     the batch that holds it."""
     import torch
     B, T = 2, 128
     cfg, ocfg, params, model = _make(pkg, orc, ctx, dict(num_layers=2), B, T)
+    mode = pkg.B200_BF16 if bf16 else pkg.B200_TF32
+    model.set_options(round_operands=1, gemm_mode=mode, lmhead_mode=mode, use_graph=use_graph)  # graph replay: results go through copies
     V, Vp = cfg.vocab_size, cfg.padded_vocab_size
     toks = [torch.from_numpy(orc.fill_tokens((B, T), seed=s, vocab=V)).pin_memory() for s in (11, 12, 13)]
     want = []
