@@ -57,9 +57,18 @@ __device__ __forceinline__ float argmax_dec(uint32_t k) {
 //   stage2   : this warp's nbuf (1 or 2) staging buffers of 4 KB
 //   c_begin, c_end : the 32-column chunks of the accumulator this warp drains (two warps can share
 //                    a lane quarter and split the columns; with a bf16 output c_begin is even)
+// The bias of a 32-column chunk: lane l fetches column l's (one coalesced 128-byte load per warp)
+// and the others get it by shuffle.  Fetched one chunk ahead - the first one by the caller, before
+// it waits for the accumulator - so that no chunk waits for an L2 round trip.
+__device__ __forceinline__ float gemm_bias_chunk(const GemmArgs& args, int col0, int c, int lane) {
+    const int col = col0 + c * 32 + lane;
+    return (args.bias && col < args.N) ? __ldg(args.bias + col) : 0.f;
+}
+
+//   bias_first : gemm_bias_chunk(args, col0, c_begin, lane)
 template <int BN>
 __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, const CUtensorMap* tmap_out, uint32_t tmem_acc,
-                                                       int q, int lane, int row0, int col0, uint8_t* stage2,
+                                                       int q, int lane, int row0, int col0, uint8_t* stage2, float bias_first,
                                                        int c_begin = 0, int c_end = BN / 32, int nbuf = 2) {
     const bool do_gelu = (args.flags & GEMM_GELU) != 0;
     const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
@@ -84,9 +93,12 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         if (lane == 0) tma_store_wait_read();
         __syncwarp();
     }
+    float bias_next = bias_first;
 #pragma unroll 1
     for (int c = c_begin; c < c_end; ++c) {
         const int ci = c - c_begin;
+        const float bias_cur = bias_next;
+        if (c + 1 < c_end) bias_next = gemm_bias_chunk(args, col0, c + 1, lane);
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r);
         tmem_ld_wait();
@@ -122,11 +134,9 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
                 float v[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * j + i]);
-                if (args.bias && cbase + 8 * j < args.N) {
-                    const float4 b0 = __ldg(reinterpret_cast<const float4*>(args.bias + cbase + 8 * j));
-                    const float4 b1 = __ldg(reinterpret_cast<const float4*>(args.bias + cbase + 8 * j + 4));
-                    v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
-                    v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+                if (args.bias) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] += __shfl_sync(0xffffffffu, bias_cur, 8 * j + i);
                 }
                 if (do_gelu) {
 #pragma unroll
@@ -162,9 +172,11 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
             for (int j = 0; j < 8; ++j) {
                 float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                if (args.bias && cbase + 4 * j < args.N) {
-                    const float4 b4 = __ldg(reinterpret_cast<const float4*>(args.bias + cbase + 4 * j));
-                    v.x += b4.x; v.y += b4.y; v.z += b4.z; v.w += b4.w;
+                if (args.bias) {
+                    v.x += __shfl_sync(0xffffffffu, bias_cur, 4 * j);
+                    v.y += __shfl_sync(0xffffffffu, bias_cur, 4 * j + 1);
+                    v.z += __shfl_sync(0xffffffffu, bias_cur, 4 * j + 2);
+                    v.w += __shfl_sync(0xffffffffu, bias_cur, 4 * j + 3);
                 }
                 if (do_gelu) { v.x = gelu_tanh(v.x); v.y = gelu_tanh(v.y); v.z = gelu_tanh(v.z); v.w = gelu_tanh(v.w); }
                 if (do_round) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }

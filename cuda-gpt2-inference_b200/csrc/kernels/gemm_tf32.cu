@@ -211,10 +211,11 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tile_coords(tile, m_blk, n_blk);
             const int acc = tile_iter & 1;
             const uint32_t acc_ph = (tile_iter >> 1) & 1;
+            const float bias_first = gemm_bias_chunk(args, n_blk * BN, 0, lane);  // on its way while the tile is computed
             if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
             gemm_drain_accumulator<BN>(args, &tmap_out, tmem_base + acc * BN, q, lane, m_blk * BM + q * 32, n_blk * BN,
-                                       smem_epi + q * 2 * 4096);
+                                       smem_epi + q * 2 * 4096, bias_first);
             tc_fence_before_sync();
             mbar_arrive(&tmem_empty_bar[acc]);
         }

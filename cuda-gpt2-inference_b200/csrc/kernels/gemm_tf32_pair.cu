@@ -212,11 +212,12 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             tile_coords(tile, m_blk, n_blk);
             const int acc = tile_iter & 1;
             const uint32_t acc_ph = (tile_iter >> 1) & 1;
+            const float bias_first = gemm_bias_chunk(args, n_blk * BN, c_begin, lane);  // on its way while the tile is computed
             if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
             gemm_drain_accumulator<BN>(args, &tmap_out, tmem_base + acc * BN, q, lane,
                                        m_blk * 2 * BM + (int)rank * BM + q * 32, n_blk * BN,
-                                       smem_epi + ew * 4096, c_begin, c_end, 1);
+                                       smem_epi + ew * 4096, bias_first, c_begin, c_end, 1);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
