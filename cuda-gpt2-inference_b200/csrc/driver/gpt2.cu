@@ -614,6 +614,8 @@ int b200_gpt2_forward_host_wait(b200_gpt2* m, int slot) {
         m->h_slot_status[slot] = 0;
         // cleared behind whatever is already queued; a step enqueued meanwhile reports the word too
         B200_CUDA(ctx, cudaMemsetAsync(ctx->d_status, 0, 256, ctx->stream));
+        // a forward that gave up may have left arg-max keys behind; the next one starts from zero again
+        B200_CUDA(ctx, cudaMemsetAsync(m->argmax_keys, 0, (size_t)m->max_B * m->max_T * 8, ctx->stream));
         ctx->last_error = "device status word = " + std::to_string(word);
         return word == 201 ? B200_ERR_SHAPE : B200_ERR_TIMEOUT;
     }
