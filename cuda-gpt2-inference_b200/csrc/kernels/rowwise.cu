@@ -269,19 +269,74 @@ __device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t stream, ui
     return -__logf(-__logf(u));
 }
 
+// fp32 -> uint32 with the same order (larger value, larger key)
+__device__ __forceinline__ uint32_t order_key(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// One step of a radix select over the keys of a row: histogram of `bits` key bits at `shift` among
+// the keys whose higher bits equal `prefix` (all keys if prefix_bits == 0), then the bin that
+// holds the k-th largest of them.  Returns that bin; k is reduced by the keys in higher bins.
+// 256 threads; hist has 2048 entries, part 256.
+__device__ __forceinline__ uint32_t radix_select_step(const float* __restrict__ row, int V, uint32_t prefix, int prefix_bits,
+                                                      int shift, int bits, int& k, int* hist, int* part, int* found) {
+    const int nbins = 1 << bits;
+    for (int i = threadIdx.x; i < nbins; i += blockDim.x) hist[i] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const uint32_t key = order_key(row[i]);
+        if (prefix_bits == 0 || (key >> (32 - prefix_bits)) == prefix) atomicAdd(&hist[(key >> shift) & (nbins - 1)], 1);
+    }
+    __syncthreads();
+    const int per = nbins / 256;  // bins per thread (8 or 4)
+    int sum = 0;
+    for (int j = 0; j < per; ++j) sum += hist[threadIdx.x * per + j];
+    part[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int above = 0, g = 255;
+        for (; g > 0 && above + part[g] < k; --g) above += part[g];  // group g holds the k-th largest
+        int b = g * per + per - 1;
+        for (; b > g * per && above + hist[b] < k; --b) above += hist[b];
+        found[0] = b;
+        found[1] = k - above;
+    }
+    __syncthreads();
+    k = found[1];
+    const uint32_t bin = (uint32_t)found[0];
+    __syncthreads();
+    return bin;
+}
+
 // Draws one column per row from softmax(logits / temperature) over columns [0,V): the arg-max of
 // logit * inv_temp + Gumbel noise has exactly that distribution, so sampling is the greedy
 // reduction with a perturbed score.  The noise is a pure function of (seed, stream0 + row,
-// column): the same call gives the same tokens.  One CTA per row.
+// column): the same call gives the same tokens.  0 < top_k < V restricts the draw to the top_k
+// largest logits of the row (all columns tied with the k-th one included): their threshold is
+// found first, by a three-step radix select (11 + 11 + 10 key bits).  One CTA per row.
 __global__ void __launch_bounds__(256)
 sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, int ld, float inv_temp,
-                   uint32_t seed, uint32_t stream0) {
+                   uint32_t seed, uint32_t stream0, int top_k) {
     const float* row = logits + (size_t)blockIdx.x * ld;
     const uint32_t stream = stream0 + blockIdx.x;
+    uint32_t min_key = 0u;  // columns with a smaller key are left out
+    if (top_k > 0 && top_k < V) {
+        __shared__ int hist[2048];
+        __shared__ int part[256];
+        __shared__ int found[2];
+        int k = top_k;
+        const uint32_t b0 = radix_select_step(row, V, 0u, 0, 21, 11, k, hist, part, found);
+        const uint32_t b1 = radix_select_step(row, V, b0, 11, 10, 11, k, hist, part, found);
+        const uint32_t b2 = radix_select_step(row, V, (b0 << 11) | b1, 22, 0, 10, k, hist, part, found);
+        min_key = (b0 << 21) | (b1 << 10) | b2;
+    }
     float best = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
-        const float sc = row[i] * inv_temp + gumbel_noise(seed, stream, (uint32_t)i);
+        const float x = row[i];
+        if (order_key(x) < min_key) continue;
+        const float sc = x * inv_temp + gumbel_noise(seed, stream, (uint32_t)i);
         if (sc > best) { best = sc; bi = i; }
     }
     __shared__ float sb[8];
@@ -456,9 +511,9 @@ int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int 
 }
 
 int launch_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld, float temperature,
-                       unsigned int seed, unsigned int stream0) {
+                       unsigned int seed, unsigned int stream0, int top_k) {
     if (!(temperature > 0.f)) return launch_argmax_rows(ctx, out, logits, M, V, ld);
-    sample_rows_kernel<<<M, 256, 0, ctx->stream>>>(out, logits, V, ld, 1.0f / temperature, seed, stream0);
+    sample_rows_kernel<<<M, 256, 0, ctx->stream>>>(out, logits, V, ld, 1.0f / temperature, seed, stream0, top_k);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

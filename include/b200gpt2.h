@@ -261,13 +261,14 @@ int b200_gpt2_generate_greedy(b200_gpt2* model, const int* prompt_host, int B, i
 /* The same loop drawing every new token from softmax(logits / temperature) instead of taking the
  * arg-max (temperature <= 0: greedy).  The draw is the arg-max of logit / temperature + Gumbel
  * noise, the noise being a fixed function of (seed, position, sequence, token id): the same call
- * returns the same continuation. */
+ * returns the same continuation.  top_k > 0 restricts every draw to the top_k most likely tokens
+ * (tokens tied with the k-th included); 0 draws from the whole vocabulary. */
 int b200_gpt2_generate(b200_gpt2* model, const int* prompt_host, int B, int T0, int n_new,
-                       float temperature, unsigned int seed, int* out_host);
+                       float temperature, int top_k, unsigned int seed, int* out_host);
 /* One draw per row of logits[M, ld] over columns [0,V) (device pointers; out int32 [M]), as used by
  * b200_gpt2_generate: row r takes the noise stream stream0 + r of the seed. */
 int b200_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld,
-                     float temperature, unsigned int seed, unsigned int stream0);
+                     float temperature, int top_k, unsigned int seed, unsigned int stream0);
 
 /* ---- tensor parallelism (optional; Megatron style, for models like GPT-2 XL) --------------
  * Rank r of tp_size holds the q/k/v rows and attn-proj input columns of its share of the heads

@@ -186,3 +186,54 @@ def test_generate_with_temperature_is_reproducible_and_follows_its_logits(pkg, o
             assert score[out[b, i]] >= score.max() - 5e-3, (b, i)
         seq = np.concatenate([seq, out[:, i:i + 1]], axis=1)
     model.close()
+
+
+@pytest.mark.parametrize("V,k", [(50257, 40), (50257, 1), (1000, 999), (4096, 64)])
+def test_top_k_sampling_draws_only_among_the_k_largest(ctx, dev, orc, V, k):
+    """Top-k: every draw is the arg-max of logit/T + noise over the k largest logits of its row
+    (found on the device by a radix select over order-preserving keys), for rows with distinct
+    random logits, negative ones included; and a row with ties at the threshold keeps all tied
+    columns."""
+    import torch
+    M, temp, seed = 64, 1.3, 7
+    ld = (V + 3) // 4 * 4
+    logits = np.zeros((M, ld), np.float32)
+    logits[:, :V] = orc.fill_normal((M, V), 401, std=3.0)
+    logits[:, V:] = 1e9  # padding columns must never be drawn
+    logits[0, :V] = np.round(logits[0, :V])  # many exact ties
+    out = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+    d_logits = dev.to(logits)
+    ctx.sample_rows(out, d_logits, M, V, ld, temp, seed, 5, top_k=k)
+    ctx.sync_check()
+    got = out.cpu().numpy()
+    noise = _gumbel(seed, np.arange(5, 5 + M), np.arange(V))
+    for r in range(M):
+        x = logits[r, :V].astype(np.float64)
+        kth = np.sort(x)[-k]
+        keep = x >= kth  # ties with the k-th largest stay in
+        score = np.where(keep, x / temp + noise[r], -np.inf)
+        assert keep[got[r]], (r, got[r])
+        assert score[got[r]] >= score.max() - 1e-4, (r, got[r], int(score.argmax()))
+    if k == 1:
+        assert np.array_equal(got[1:], logits[1:, :V].argmax(1))
+
+
+def test_generate_with_top_k_stays_inside_the_oracle_top_k(pkg, orc, ctx):
+    B, T0, n_new, k = 2, 7, 4, 5
+    cfg, ocfg, params, model = _model(pkg, orc, ctx, dict(num_layers=2), B, 128, 0)
+    model.set_options(round_operands=0)
+    prompt = np.ascontiguousarray(orc.fill_tokens((B, T0), seed=41, vocab=cfg.vocab_size))
+    out = np.empty((B, n_new), np.int32)
+    model.generate(prompt, B, T0, n_new, out, temperature=5.0, seed=3, top_k=k)
+    V = cfg.vocab_size
+    seq = prompt.copy()
+    for i in range(n_new):
+        T = seq.shape[1]
+        padded = np.zeros((B, 64), np.int32)
+        padded[:, :T] = seq
+        logits = orc.gpt2_forward(params, ocfg, padded, precise=True)[:, T - 1, :V]
+        for b in range(B):
+            kth = np.sort(logits[b])[-k]
+            assert logits[b, out[b, i]] >= kth - 1e-4, (b, i)  # up to the fp32 noise of the two forwards
+        seq = np.concatenate([seq, out[:, i:i + 1]], axis=1)
+    model.close()
