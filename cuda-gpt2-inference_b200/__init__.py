@@ -129,8 +129,8 @@ def lib() -> C.CDLL:
         l.b200_gpt2_decode_step.argtypes = [vp, vp, i, i]
         l.b200_gpt2_decode_step_host.argtypes = [vp, vp, i, i, vp, vp]
         l.b200_gpt2_generate_greedy.argtypes = [vp, vp, i, i, i, vp]
-        l.b200_gpt2_generate.argtypes = [vp, vp, i, i, i, C.c_float, i, C.c_uint, vp]
-        l.b200_sample_rows.argtypes = [vp, vp, vp, i, i, i, C.c_float, i, C.c_uint, C.c_uint]
+        l.b200_gpt2_generate.argtypes = [vp, vp, i, i, i, C.c_float, i, C.c_float, C.c_uint, vp]
+        l.b200_sample_rows.argtypes = [vp, vp, vp, i, i, i, C.c_float, i, C.c_float, C.c_uint, C.c_uint]
         l.b200_gpt2_create_tp.argtypes = [C.POINTER(vp), vp, vp, i, i, i, i]
         l.b200_gpt2_set_allreduce.argtypes = [vp, ALLREDUCE_FN, vp]
         l.b200_gpt2_param_offsets_tp.argtypes = [vp, i, i, C.POINTER(sz)]
@@ -208,8 +208,8 @@ class Context:
     def convert_bf16(self, out, inp, n):
         self.check(lib().b200_convert_bf16(self._h, _ptr(out), _ptr(inp), n), "convert_bf16")
 
-    def sample_rows(self, out, logits, M, V, ld, temperature, seed, stream0, top_k=0):
-        self.check(lib().b200_sample_rows(self._h, _ptr(out), _ptr(logits), M, V, ld, float(temperature), int(top_k),
+    def sample_rows(self, out, logits, M, V, ld, temperature, seed, stream0, top_k=0, top_p=0.0):
+        self.check(lib().b200_sample_rows(self._h, _ptr(out), _ptr(logits), M, V, ld, float(temperature), int(top_k), float(top_p),
                                           int(seed) & 0xFFFFFFFF, int(stream0) & 0xFFFFFFFF), "sample_rows")
 
     def attention_forward(self, out, qkvr, att, inp, B, T, Cc, NH):
@@ -442,10 +442,10 @@ class GPT2:
                        "gpt2_generate_greedy")
 
     def generate(self, prompt_host, B: int, T0: int, n_new: int, out_host, temperature: float = 1.0, seed: int = 0,
-                 top_k: int = 0):
+                 top_k: int = 0, top_p: float = 0.0):
         """Sampled continuation (temperature <= 0: greedy; top_k > 0: among the k most likely tokens);
         reproducible for a given seed."""
-        self.ctx.check(lib().b200_gpt2_generate(self._h, _ptr(prompt_host), B, T0, n_new, float(temperature), int(top_k),
+        self.ctx.check(lib().b200_gpt2_generate(self._h, _ptr(prompt_host), B, T0, n_new, float(temperature), int(top_k), float(top_p),
                                                 int(seed) & 0xFFFFFFFF, _ptr(out_host)), "gpt2_generate")
 
     def set_profile(self, enabled: bool):

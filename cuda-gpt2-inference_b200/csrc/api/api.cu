@@ -190,11 +190,11 @@ int b200_matmul_forward_bf16(b200_ctx* ctx, float* out, uint16_t* out_bf16, cons
 }
 
 int b200_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld, float temperature,
-                     int top_k, unsigned int seed, unsigned int stream0) {
+                     int top_k, float top_p, unsigned int seed, unsigned int stream0) {
     if (!ctx || !out || !logits) return B200_ERR_NULL;
     if (M <= 0 || V <= 0 || ld < V || top_k < 0) return B200_ERR_SHAPE;
     if (temperature <= 0.f && (ld % 4 || !b200_aligned16(logits))) return B200_ERR_ALIGN;  // the arg-max reads float4
-    return b200::launch_sample_rows(ctx, out, logits, M, V, ld, temperature, seed, stream0, top_k);
+    return b200::launch_sample_rows(ctx, out, logits, M, V, ld, temperature, seed, stream0, top_k, top_p);
 }
 
 int b200_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* inp, size_t n) {

@@ -780,7 +780,7 @@ int b200_gpt2_decode_step_host(b200_gpt2* m, const int* tokens_host, int B, int 
 }
 
 int b200_gpt2_generate(b200_gpt2* m, const int* prompt_host, int B, int T0, int n_new, float temperature,
-                       int top_k, unsigned int seed, int* out_host) {
+                       int top_k, float top_p, unsigned int seed, int* out_host) {
     if (!m || !prompt_host || !out_host) return B200_ERR_NULL;
     if (!m->kcache) return B200_ERR_STATE;
     if (B <= 0 || B > 16 || B > m->max_B || T0 < 1 || n_new < 1 || T0 + n_new > m->max_T || top_k < 0) return B200_ERR_SHAPE;
@@ -798,7 +798,7 @@ int b200_gpt2_generate(b200_gpt2* m, const int* prompt_host, int B, int T0, int 
         // arg-max of the last prompt position of every sequence: rows T0-1, 2*T0-1, ... of the logits
         for (int b = 0; b < B; ++b) {
             st = b200::launch_sample_rows(ctx, m->argmax + b, m->logits + ((size_t)b * T0 + T0 - 1) * Vp, 1, V, Vp,
-                                          temperature, seed, (unsigned)T0 * 16u + b, top_k);
+                                          temperature, seed, (unsigned)T0 * 16u + b, top_k, top_p);
             if (st != B200_OK) return st;
         }
     } else {
@@ -808,7 +808,7 @@ int b200_gpt2_generate(b200_gpt2* m, const int* prompt_host, int B, int T0, int 
             st = b200_gpt2_decode_step(m, m->argmax, B, t);
             if (st != B200_OK) return st;
         }
-        st = b200::launch_sample_rows(ctx, m->argmax, m->logits, B, V, Vp, temperature, seed, (unsigned)T0 * 16u, top_k);
+        st = b200::launch_sample_rows(ctx, m->argmax, m->logits, B, V, Vp, temperature, seed, (unsigned)T0 * 16u, top_k, top_p);
         if (st != B200_OK) return st;
     }
     for (int i = 0; i < n_new; ++i) {
@@ -818,7 +818,7 @@ int b200_gpt2_generate(b200_gpt2* m, const int* prompt_host, int B, int T0, int 
         st = b200_gpt2_decode_step(m, m->argmax, B, T0 + i);
         if (st != B200_OK) return st;
         // the token that will stand at position T0 + i + 1 of sequence b uses noise stream 16 * position + b
-        st = b200::launch_sample_rows(ctx, m->argmax, m->logits, B, V, Vp, temperature, seed, (unsigned)(T0 + i + 1) * 16u, top_k);
+        st = b200::launch_sample_rows(ctx, m->argmax, m->logits, B, V, Vp, temperature, seed, (unsigned)(T0 + i + 1) * 16u, top_k, top_p);
         if (st != B200_OK) return st;
     }
     B200_CUDA(ctx, cudaMemcpyAsync(out_host, rec, (size_t)B * n_new * 4, cudaMemcpyDeviceToHost, ctx->stream));
@@ -826,7 +826,7 @@ int b200_gpt2_generate(b200_gpt2* m, const int* prompt_host, int B, int T0, int 
 }
 
 int b200_gpt2_generate_greedy(b200_gpt2* m, const int* prompt_host, int B, int T0, int n_new, int* out_host) {
-    return b200_gpt2_generate(m, prompt_host, B, T0, n_new, 0.f, 0, 0u, out_host);
+    return b200_gpt2_generate(m, prompt_host, B, T0, n_new, 0.f, 0, 0.f, 0u, out_host);
 }
 
 int b200_gpt2_set_profile(b200_gpt2* m, int enabled) {

@@ -26,9 +26,10 @@ int launch_fetch_ints(b200_ctx* ctx, int* dst, const int* src_view, int n);
 int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N);
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
 // one draw per row from softmax(logits / temperature) (Gumbel-max; temperature <= 0: arg-max);
-// row r uses the noise stream stream0 + r of the seed; 0 < top_k < V: only among the top_k largest logits
+// row r uses the noise stream stream0 + r of the seed; 0 < top_k < V: only among the top_k largest logits;
+// 0 < top_p < 1: then only the most likely columns that add up to top_p of the probability
 int launch_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld, float temperature,
-                       unsigned int seed, unsigned int stream0, int top_k = 0);
+                       unsigned int seed, unsigned int stream0, int top_k = 0, float top_p = 0.f);
 int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns);
 
 // epilogue flags of the GEMM

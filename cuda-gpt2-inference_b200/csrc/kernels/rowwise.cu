@@ -309,27 +309,107 @@ __device__ __forceinline__ uint32_t radix_select_step(const float* __restrict__ 
     return bin;
 }
 
+// The same step over probability mass instead of counts, for nucleus (top-p) sampling: a key
+// weighs exp((x - m) * inv_temp); columns with a key below min_key do not take part.  Finds the
+// bin in which the mass of the larger keys reaches `target`, and reduces target by the mass of
+// the higher bins.  (Shared-memory float atomics: the sums depend on the order of arrival in
+// the last bits, which can move a column that sits exactly on the boundary in or out.)
+__device__ __forceinline__ uint32_t radix_select_mass_step(const float* __restrict__ row, int V, uint32_t min_key, uint32_t prefix,
+                                                           int prefix_bits, int shift, int bits, float& target, float m,
+                                                           float inv_temp, float* hist, float* part, int* found_i,
+                                                           float* found_f) {
+    const int nbins = 1 << bits;
+    for (int i = threadIdx.x; i < nbins; i += blockDim.x) hist[i] = 0.f;
+    __syncthreads();
+    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+        const float x = row[i];
+        const uint32_t key = order_key(x);
+        if (key < min_key) continue;
+        if (prefix_bits == 0 || (key >> (32 - prefix_bits)) == prefix)
+            atomicAdd(&hist[(key >> shift) & (nbins - 1)], __expf((x - m) * inv_temp));
+    }
+    __syncthreads();
+    const int per = nbins / 256;
+    float sum = 0.f;
+    for (int j = 0; j < per; ++j) sum += hist[threadIdx.x * per + j];
+    part[threadIdx.x] = sum;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float above = 0.f;
+        int g = 255;
+        for (; g > 0 && above + part[g] < target; --g) above += part[g];
+        int b = g * per + per - 1;
+        for (; b > g * per && above + hist[b] < target; --b) above += hist[b];
+        found_i[0] = b;
+        found_f[0] = target - above;
+    }
+    __syncthreads();
+    target = found_f[0];
+    const uint32_t bin = (uint32_t)found_i[0];
+    __syncthreads();
+    return bin;
+}
+
 // Draws one column per row from softmax(logits / temperature) over columns [0,V): the arg-max of
 // logit * inv_temp + Gumbel noise has exactly that distribution, so sampling is the greedy
 // reduction with a perturbed score.  The noise is a pure function of (seed, stream0 + row,
 // column): the same call gives the same tokens.  0 < top_k < V restricts the draw to the top_k
 // largest logits of the row (all columns tied with the k-th one included): their threshold is
-// found first, by a three-step radix select (11 + 11 + 10 key bits).  One CTA per row.
+// found first, by a three-step radix select (11 + 11 + 10 key bits).  0 < top_p < 1 then keeps,
+// of what is left, the most likely columns whose probabilities (at this temperature) add up to
+// top_p - the smallest such set, columns tied with its last member included - by the same
+// select over probability mass.  One CTA per row.
 __global__ void __launch_bounds__(256)
 sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, int ld, float inv_temp,
-                   uint32_t seed, uint32_t stream0, int top_k) {
+                   uint32_t seed, uint32_t stream0, int top_k, float top_p) {
     const float* row = logits + (size_t)blockIdx.x * ld;
     const uint32_t stream = stream0 + blockIdx.x;
     uint32_t min_key = 0u;  // columns with a smaller key are left out
+    __shared__ int hist[2048];
+    __shared__ int part[256];
+    __shared__ int found[2];
+    __shared__ float red[8];
     if (top_k > 0 && top_k < V) {
-        __shared__ int hist[2048];
-        __shared__ int part[256];
-        __shared__ int found[2];
         int k = top_k;
         const uint32_t b0 = radix_select_step(row, V, 0u, 0, 21, 11, k, hist, part, found);
         const uint32_t b1 = radix_select_step(row, V, b0, 11, 10, 11, k, hist, part, found);
         const uint32_t b2 = radix_select_step(row, V, (b0 << 11) | b1, 22, 0, 10, k, hist, part, found);
         min_key = (b0 << 21) | (b1 << 10) | b2;
+    }
+    if (top_p > 0.f && top_p < 1.f) {
+        // the row maximum and the total mass of the columns still in play
+        float m = -INFINITY;
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float x = row[i];
+            if (order_key(x) >= min_key) m = fmaxf(m, x);
+        }
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, s));
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = m;
+        __syncthreads();
+        m = red[0];
+        for (int w = 1; w < 8; ++w) m = fmaxf(m, red[w]);
+        __syncthreads();
+        float z = 0.f;
+        for (int i = threadIdx.x; i < V; i += blockDim.x) {
+            const float x = row[i];
+            if (order_key(x) >= min_key) z += __expf((x - m) * inv_temp);
+        }
+#pragma unroll
+        for (int s = 16; s >= 1; s >>= 1) z += __shfl_xor_sync(0xffffffffu, z, s);
+        if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = z;
+        __syncthreads();
+        z = 0.f;
+        for (int w = 0; w < 8; ++w) z += red[w];
+        __syncthreads();
+        float target = top_p * z;
+        float* histf = reinterpret_cast<float*>(hist);
+        float* partf = reinterpret_cast<float*>(part);
+        const uint32_t b0 = radix_select_mass_step(row, V, min_key, 0u, 0, 21, 11, target, m, inv_temp, histf, partf, found, red);
+        const uint32_t b1 = radix_select_mass_step(row, V, min_key, b0, 11, 10, 11, target, m, inv_temp, histf, partf, found, red);
+        const uint32_t b2 = radix_select_mass_step(row, V, min_key, (b0 << 11) | b1, 22, 0, 10, target, m, inv_temp, histf, partf, found, red);
+        const uint32_t key_p = (b0 << 21) | (b1 << 10) | b2;
+        if (key_p > min_key) min_key = key_p;
     }
     float best = -INFINITY;
     int bi = 0x7fffffff;
@@ -511,9 +591,9 @@ int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int 
 }
 
 int launch_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld, float temperature,
-                       unsigned int seed, unsigned int stream0, int top_k) {
+                       unsigned int seed, unsigned int stream0, int top_k, float top_p) {
     if (!(temperature > 0.f)) return launch_argmax_rows(ctx, out, logits, M, V, ld);
-    sample_rows_kernel<<<M, 256, 0, ctx->stream>>>(out, logits, V, ld, 1.0f / temperature, seed, stream0, top_k);
+    sample_rows_kernel<<<M, 256, 0, ctx->stream>>>(out, logits, V, ld, 1.0f / temperature, seed, stream0, top_k, top_p);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

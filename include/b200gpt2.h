@@ -262,13 +262,14 @@ int b200_gpt2_generate_greedy(b200_gpt2* model, const int* prompt_host, int B, i
  * arg-max (temperature <= 0: greedy).  The draw is the arg-max of logit / temperature + Gumbel
  * noise, the noise being a fixed function of (seed, position, sequence, token id): the same call
  * returns the same continuation.  top_k > 0 restricts every draw to the top_k most likely tokens
- * (tokens tied with the k-th included); 0 draws from the whole vocabulary. */
+ * (tokens tied with the k-th included); 0 < top_p < 1 then keeps the most likely of those whose
+ * probabilities add up to top_p (nucleus sampling); 0 for either switches it off. */
 int b200_gpt2_generate(b200_gpt2* model, const int* prompt_host, int B, int T0, int n_new,
-                       float temperature, int top_k, unsigned int seed, int* out_host);
+                       float temperature, int top_k, float top_p, unsigned int seed, int* out_host);
 /* One draw per row of logits[M, ld] over columns [0,V) (device pointers; out int32 [M]), as used by
  * b200_gpt2_generate: row r takes the noise stream stream0 + r of the seed. */
 int b200_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld,
-                     float temperature, int top_k, unsigned int seed, unsigned int stream0);
+                     float temperature, int top_k, float top_p, unsigned int seed, unsigned int stream0);
 
 /* ---- tensor parallelism (optional; Megatron style, for models like GPT-2 XL) --------------
  * Rank r of tp_size holds the q/k/v rows and attn-proj input columns of its share of the heads

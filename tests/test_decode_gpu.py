@@ -237,3 +237,39 @@ def test_generate_with_top_k_stays_inside_the_oracle_top_k(pkg, orc, ctx):
             assert logits[b, out[b, i]] >= kth - 1e-4, (b, i)  # up to the fp32 noise of the two forwards
         seq = np.concatenate([seq, out[:, i:i + 1]], axis=1)
     model.close()
+
+
+@pytest.mark.parametrize("V,k,p", [(50257, 0, 0.9), (50257, 50, 0.5), (2000, 0, 0.3), (4096, 0, 0.999)])
+def test_top_p_sampling_keeps_the_smallest_set_that_reaches_p(ctx, dev, orc, V, k, p):
+    """Nucleus sampling (after an optional top-k): every draw lies inside the nucleus computed by
+    numpy with a slightly larger p and is the arg-max of the perturbed score over the nucleus
+    computed with a slightly smaller p - the device sums probabilities in fp32 and in arrival
+    order, so a column exactly on the boundary may fall either way."""
+    import torch
+    M, temp, seed = 48, 0.9, 11
+    ld = (V + 3) // 4 * 4
+    logits = np.zeros((M, ld), np.float32)
+    logits[:, :V] = orc.fill_normal((M, V), 501, std=2.5)
+    out = torch.full((M,), -1, dtype=torch.int32, device="cuda")
+    ctx.sample_rows(out, dev.to(logits), M, V, ld, temp, seed, 9, top_k=k, top_p=p)
+    ctx.sync_check()
+    got = out.cpu().numpy()
+    noise = _gumbel(seed, np.arange(9, 9 + M), np.arange(V))
+
+    def nucleus(x, pp):
+        keep = np.ones(V, bool) if k == 0 else x >= np.sort(x)[-k]
+        w = np.where(keep, np.exp((x - x[keep].max()) / temp), 0.0)
+        order = np.argsort(-x, kind="stable")
+        cum = np.cumsum(w[order])
+        last = int(np.searchsorted(cum, pp * w.sum(), side="left"))  # first prefix whose mass reaches pp
+        return keep & (x >= x[order[min(last, V - 1)]])
+
+    sizes = []
+    for r in range(M):
+        x = logits[r, :V].astype(np.float64)
+        outer, inner = nucleus(x, min(p + 1e-4, 1.0)), nucleus(x, p - 1e-4)
+        sizes.append(int(inner.sum()))
+        assert outer[got[r]], (r, got[r])
+        score = np.where(inner, x / temp + noise[r], -np.inf)
+        assert x[got[r]] / temp + noise[r, got[r]] >= score.max() - 1e-4, (r, got[r])
+    assert min(sizes) >= 1 and (p > 0.99 or max(sizes) < V)
