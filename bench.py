@@ -367,7 +367,7 @@ def run_ours(args):
     # ------------------------------------------------ the same workload with bf16 GEMM operands
     # (optional reduced-precision mode; never the headline, which stays TF32)
     bf16_ms = None
-    if not xl and not args.tp:
+    if not args.tp:
         model.set_options(round_operands=1, gemm_mode=pkg.B200_BF16, lmhead_mode=pkg.B200_BF16)
         for _ in range(3):
             model.forward(tok_dev, B, T)
