@@ -69,7 +69,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
         failed |= p.returncode != 0
     if failed:
         raise RuntimeError("nvcc failed building libb200gpt2.so")
-    subprocess.check_call(["nvcc", "-shared", "--cudart", "shared", "-o", LIB_PATH, *objs])
+    subprocess.check_call(["nvcc", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "--cudart", "shared", "-o", LIB_PATH, *objs])
     return LIB_PATH
 
 
