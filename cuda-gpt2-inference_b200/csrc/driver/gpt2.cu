@@ -167,6 +167,8 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
     uint16_t* atty_h = reinterpret_cast<uint16_t*>(m->atty);
     uint16_t* fch_h = reinterpret_cast<uint16_t*>(m->fch);
     const int ln_flags = hb ? OUT_BF16 : rnd;
+    // the tensor-parallel all-reduce needs the branch as a buffer of its own
+    const int accum = (m->tp_size == 1) ? GEMM_ACCUM_OUT : 0;
     int st;
     const bool prof = m->profile;
 #define STEP(cat, call)                                             \
@@ -205,24 +207,38 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         }
         if (att_x3) STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->atty, m->qkv_small, nullptr, m->qkv, B, T, A, NH));
         else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, A, NH, hb ? OUT_BF16 : rnd));
-        if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, m->branch, nullptr, atty_h, PH + (apw - P), apb, M, A, C, 0));
-        else STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, m->branch, m->atty, apw, apb, nullptr, M, A, C, 0, m->gemm_mode));
-        // tensor parallel: every rank holds a partial sum over its heads; one all-reduce per block
-        if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
-        STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
-                                             m->branch, ln2w, ln2b, M, C, ln_flags));
+        // Without tensor parallelism the projection adds its result straight onto the residual
+        // stream (its tiles leave as TMA reductions: the same single fp32 add per element that the
+        // fused residual + layernorm kernel would do), and a plain layernorm follows: 50 MB less
+        // traffic per block than writing the branch and reading it back.
+        float* proj_out = accum ? m->residual : m->branch;
+        if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, atty_h, PH + (apw - P), apb, M, A, C, accum));
+        else STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, proj_out, m->atty, apw, apb, nullptr, M, A, C, accum, m->gemm_mode));
+        if (accum) {
+            STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, ln2w, ln2b, M, C, ln_flags));
+        } else {
+            // tensor parallel: every rank holds a partial sum over its heads; one all-reduce per block
+            if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
+            STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
+                                                 m->branch, ln2w, ln2b, M, C, ln_flags));
+        }
         if (hb) {
             STEP(B200_PROF_GEMM_FC, launch_gemm_bf16(ctx, nullptr, fch_h, ln_h, PH + (fcw - P), fcb, M, C, F, GEMM_GELU));
-            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16(ctx, m->branch, nullptr, fch_h, PH + (fpw - P), fpb, M, F, C, 0));
+            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, fch_h, PH + (fpw - P), fpb, M, F, C, accum));
         } else {
             STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, F, GEMM_GELU | grnd, m->gemm_mode));
-            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, m->branch, m->fch, fpw, fpb, nullptr, M, F, C, 0, m->gemm_mode));
+            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, proj_out, m->fch, fpw, fpb, nullptr, M, F, C, accum, m->gemm_mode));
         }
-        if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
         const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
         const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
-        STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
-                                             m->branch, nw, nb, M, C, (l + 1 < L) ? ln_flags : (hl ? OUT_BF16 : rnd)));
+        const int next_flags = (l + 1 < L) ? ln_flags : (hl ? OUT_BF16 : rnd);
+        if (accum) {
+            STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, nw, nb, M, C, next_flags));
+        } else {
+            if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
+            STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
+                                                 m->branch, nw, nb, M, C, next_flags));
+        }
     }
     const float* head_w = ((m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0]) + (size_t)m->vp_row0 * C;
     const int store_period = (with_argmax && (results & RES_NO_LOGITS)) ? T : 0;

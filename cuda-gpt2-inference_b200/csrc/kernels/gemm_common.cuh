@@ -185,7 +185,8 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0 && cbase < args.N && row0 < args.M) {
-                tma_store_2d(tmap_out, cbase, row0, stage);
+                if (args.flags & GEMM_ACCUM_OUT) tma_reduce_add_2d(tmap_out, cbase, row0, stage);
+                else tma_store_2d(tmap_out, cbase, row0, stage);
                 tma_store_commit();
             }
             continue;

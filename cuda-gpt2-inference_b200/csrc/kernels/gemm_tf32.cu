@@ -301,6 +301,7 @@ namespace {
 int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp, const void* weight,
                     const float* bias, const float* residual, int M, int K, int N, int flags,
                     int mode, unsigned long long* argmax_keys, int argmax_cols, bool bf16, int store_period) {
+    if ((flags & GEMM_ACCUM_OUT) && (residual || out_h)) { ctx->last_error = "GEMM_ACCUM_OUT: fp32 output without a residual operand"; return B200_ERR_STATE; }
     if (store_period && (store_period % 32 || residual || !argmax_keys)) { ctx->last_error = "store_period: multiple of 32, with the fused arg-max only"; return B200_ERR_STATE; }
     const bool x3 = (mode == B200_TF32X3);
     // the fused arg-max looks at the raw accumulator: only with a plain epilogue
@@ -400,7 +401,7 @@ int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t*
                      const float* bias, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys, int argmax_cols, int store_period) {
     if (K % 8 || N % 8) { ctx->last_error = "bf16 GEMM: K and N must be multiples of 8"; return B200_ERR_SHAPE; }
-    return launch_gemm_any(ctx, out, out_h, inp, weight, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32), B200_TF32, argmax_keys, argmax_cols, true, store_period);
+    return launch_gemm_any(ctx, out, out_h, inp, weight, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32 | GEMM_ACCUM_OUT), B200_TF32, argmax_keys, argmax_cols, true, store_period);
 }
 
 }  // namespace b200

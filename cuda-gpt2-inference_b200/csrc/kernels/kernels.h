@@ -33,7 +33,9 @@ int launch_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int 
 int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns);
 
 // epilogue flags of the GEMM
-enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2 };
+// GEMM_ACCUM_OUT: out += result instead of out = result (fp32 output without a residual operand: the
+// tiles leave as TMA reductions).  With out = the residual stream this is the residual add.
+enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2, GEMM_ACCUM_OUT = 4 };
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      int mode, unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0);
