@@ -25,6 +25,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# Measured DRAM traffic of the GEMM kernels of the 124M forward, launch-weighted average over the 49
+# launches of a step (ncu dram__bytes_read.sum + dram__bytes_write.sum), by arithmetic mode; the
+# capture and the per-shape figures are in the named profile.
+GEMM_DRAM_TRAFFIC = {}
+
 METRIC = "gpt2_forward_tokens_per_s"
 UNIT = "tokens/s"
 B_PER_GPU, T = 8, 1024
@@ -168,28 +173,28 @@ def _random_init_(model, pkg, torch, seed: int):
             view.zero_()
 
 
-def cpu_forward_tokens_per_s(sample_T: int, repeats: int = 1, threads: int | None = None, xl: bool = False):
-    """Times the CPU oracle's fp32 forward of GPT-2 (124M, or XL) on one sequence of sample_T tokens."""
-    import numpy as np
+def _headline_mode(pkg):
+    """The arithmetic the headline is measured in: the library's default options."""
+    return pkg.DEFAULT_MODE_NAME, dict(pkg.MODES[pkg.DEFAULT_MODE_NAME])
+
+
+def _config(world: int, tp: bool = False, xl: bool = False) -> dict:
+    """The `config` object of the JSON line; the same for this repository's arm and the reference arm."""
+    workload = WORKLOAD if not xl else ("GPT-2 XL 1.5B full-sequence forward, B=8 T=1024 per " +
+                                        ("tensor-parallel group" if tp else "GPU") + ", fp32 storage (configs[4] shapes)")
+    par = (f"tensor-parallel x{world}: heads / MLP / vocabulary split, one NCCL all-reduce per attention and MLP block" if tp
+           else f"batch-sharded x{world}, no collective")
+    return {"workload": workload, "global_batch": (1 if tp else world) * B_PER_GPU, "seq_len": T, "parallelism": par,
+            "l2": "no flush: each step streams the weights (0.5 GB for 124M) and writes 1.65 GB of logits, far beyond the 126 MB L2"}
+
+
+def _oracle_all_threads():
+    """Loads the CPU oracle and gives it every core this process may run on (torch.distributed.run
+    exports OMP_NUM_THREADS=1 to its workers)."""
     from oracle import oracle as orc
-    if threads:
-        os.environ["OMP_NUM_THREADS"] = str(threads)
-    cfg = orc.GPT2_XL if xl else orc.GPT2_124M
-    offs = orc.param_offsets(cfg)
-    rng = np.random.default_rng(1234)
-    params = np.zeros(offs[16], dtype=np.float32)
-    for i, name in enumerate(orc.PARAM_NAMES):
-        if name in ("ln1w", "ln2w", "lnfw"):
-            params[offs[i]:offs[i + 1]] = 1.0
-        elif name in ("wte", "wpe", "qkvw", "attprojw", "fcw", "fcprojw"):
-            params[offs[i]:offs[i + 1]] = rng.standard_normal(offs[i + 1] - offs[i], dtype=np.float32) * 0.02
-    tokens = orc.fill_tokens((1, sample_T), seed=4321, vocab=cfg.vocab_size)
-    times = []
-    for _ in range(repeats):
-        t0 = time.perf_counter()
-        orc.gpt2_forward(params, cfg, tokens)
-        times.append(time.perf_counter() - t0)
-    return sample_T / min(times), orc.num_threads(), params, cfg
+    orc.build()
+    cores = orc.use_all_host_threads()
+    return orc, cores
 
 
 def run_reference(args):
@@ -201,10 +206,14 @@ def run_reference(args):
     if rank != 0:
         return 0
     import numpy as np
-    from oracle import oracle as orc
-    orc.build()
+    orc, cores = _oracle_all_threads()
+    cfg = orc.GPT2_124M
+    params = orc.init_params(cfg, seed=1234)
     # calibrate on a short prefix, then size the per-step sample so the run stays bounded
-    tps_small, cores, params, cfg = cpu_forward_tokens_per_s(64)
+    tok64 = orc.fill_tokens((1, 64), seed=4321, vocab=cfg.vocab_size)
+    t0 = time.perf_counter()
+    orc.gpt2_forward(params, cfg, tok64)
+    tps_small = 64 / (time.perf_counter() - t0)
     budget_s = 150.0
     n_steps = args.steps + args.warmup
     sample_T = 1024
@@ -218,18 +227,141 @@ def run_reference(args):
         orc.gpt2_forward(params, cfg, tokens)
     dt = time.perf_counter() - t0
     value = args.steps * sample_T / dt
-    sample = f"1 sequence of {sample_T} tokens per step (of the B=8 x T=1024 workload), fp32 accumulate, OpenMP"
+    sample = (f"1 sequence of {sample_T} tokens per step (of the B=8 x T=1024 workload), fp32 accumulate, C/OpenMP, "
+              f"{cores} threads" + ("" if cores > 1 else " (ONE thread only: no more cores are available to this process)"))
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "tokens_per_step": sample_T},
+        "config": _config(args.gpus),
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
     return 0
+
+
+def _measure_matmul_peaks(torch, seconds: float = 2.0):
+    """cuBLAS through torch.matmul, 8192^3: TF32 (fp32 tensors, TF32 allowed) and bf16, each as the
+    best of 10 launches (burst) and back to back for `seconds` (sustained).  Harness only: the
+    denominators of the roofline fractions, never on the product path."""
+    out = {}
+    n = 8192
+    old = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = True
+    try:
+        for name, dt in (("tf32", torch.float32), ("bf16", torch.bfloat16)):
+            a = torch.randn(n, n, device="cuda", dtype=dt)
+            b = torch.randn(n, n, device="cuda", dtype=dt)
+            c = torch.empty(n, n, device="cuda", dtype=dt)
+            for _ in range(3):
+                torch.matmul(a, b, out=c)
+            torch.cuda.synchronize()
+            best = 1e9
+            for _ in range(10):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                torch.matmul(a, b, out=c)
+                e1.record()
+                e1.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            flop = 2.0 * n ** 3
+            out[name + "_burst_tflops"] = flop / (best * 1e-3) / 1e12
+            reps = max(10, int(seconds / (best * 1e-3)))
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(reps):
+                torch.matmul(a, b, out=c)
+            e1.record()
+            e1.synchronize()
+            out[name + "_sustained_tflops"] = flop * reps / (e0.elapsed_time(e1) * 1e-3) / 1e12
+            del a, b, c
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = old
+    out["how"] = f"torch.matmul {n}^3, best of 10 (burst) and back to back for {seconds:.0f} s (sustained), measured in this run"
+    return out
+
+
+def _time_reference_gpu_kernels(torch, np):
+    """The reference project's own CUDA kernels (built from its headers into oracle/_ref/ where a
+    checkout was present) timed on this GPU at the sweep shapes that satisfy their asserts: the
+    GPU-vs-GPU baseline per operator.  Returns None when the library is not there."""
+    import ctypes as C
+    path = os.path.join(ROOT, "oracle", "_ref", "libref_kernels.so")
+    if not os.path.exists(path):
+        return None
+    ref = C.CDLL(path)
+    p = lambda t: C.c_void_p(t.data_ptr())
+    Bb, Tt, M = 8, 1024, 8192
+    g = torch.Generator(device="cuda").manual_seed(7)
+    res = {"source": "oracle/_ref/libref_kernels.so (the reference's headers compiled for sm_100a)", "kernels": {}}
+
+    def timed(fn, reps=5):
+        for _ in range(2):
+            rc = fn()
+            if rc != 0:
+                raise RuntimeError(f"reference kernel returned {rc}")
+        ts = []
+        for _ in range(reps):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            e1.synchronize()
+            ts.append(e0.elapsed_time(e1))
+        return statistics.median(ts)
+
+    for name, K, N, gelu in (("gemm_qkv", 768, 2304, 0), ("gemm_attproj", 768, 768, 0), ("gemm_fc", 768, 3072, 1),
+                             ("gemm_fcproj", 3072, 768, 0), ("gemm_lmhead", 768, 50304, 0)):
+        x = torch.empty(M, K, device="cuda").normal_(0, 1, generator=g)
+        w = torch.empty(N, K, device="cuda").normal_(0, 0.02, generator=g)
+        b = torch.zeros(N, device="cuda")
+        o = torch.empty(M, N, device="cuda")
+        torch.cuda.synchronize()
+        ms = timed(lambda: ref.ref_matmul_forward_tf32_gelu(p(o), p(x), p(w), p(b), Bb, Tt, K, N, gelu))
+        res["kernels"][name] = {"kernel": "matmul_forward_async_cg_tf32_gelu (kernels/matmul/9_matmul_async_cg_tf32_gelu.cuh)",
+                                "ms": round(ms, 4), "tflops": round(2.0 * M * K * N / (ms * 1e-3) / 1e12, 1)}
+        del x, w, b, o
+    NH, Cc = 12, 768
+    qkv = torch.empty(Bb, Tt, 3 * Cc, device="cuda").normal_(0, 1, generator=g)
+    o = torch.empty(Bb, Tt, Cc, device="cuda")
+    torch.cuda.synchronize()
+    ms = timed(lambda: ref.ref_flash_attention_permute_forward(p(o), p(qkv), Bb, Tt, Cc, NH))
+    res["kernels"]["attention"] = {"kernel": "flash_attention_permute_forward (kernels/attention/3_flash_attention_permute.cuh)",
+                                   "ms": round(ms, 4),
+                                   "tflops_causal": round(4.0 * 64 * Tt * (Tt + 1) / 2 * NH * Bb / (ms * 1e-3) / 1e12, 1)}
+    x = torch.empty(Bb, Tt, Cc, device="cuda").normal_(0, 1, generator=g)
+    w, b = torch.ones(Cc, device="cuda"), torch.zeros(Cc, device="cuda")
+    mean, rstd = torch.empty(M, device="cuda"), torch.empty(M, device="cuda")
+    torch.cuda.synchronize()
+    ms = timed(lambda: ref.ref_layernorm_forward_block_vectorized(p(o), p(mean), p(rstd), p(x), p(w), p(b), Bb, Tt, Cc))
+    res["kernels"]["layernorm"] = {"kernel": "layernorm_forward_block_vectorized (kernels/layernorm/2_layernorm_block_vectorized.cuh)",
+                                   "ms": round(ms, 4), "gbs": round((2.0 * M * Cc + 2 * M + 2 * Cc) * 4 / (ms * 1e-3) / 1e9, 1)}
+    return res
+
+
+def _seq_hashes(torch, logits):
+    """Two 63-bit checksums per sequence over the bit patterns of logits [B,T,V] (order-dependent)."""
+    Bn = logits.shape[0]
+    bits = logits.contiguous().view(torch.int32).view(Bn, -1).to(torch.int64)
+    idx = torch.arange(bits.shape[1], device=bits.device, dtype=torch.int64) % 65521 + 1
+    return torch.stack([bits.sum(1), (bits * idx).sum(1)], dim=1)
+
+
+def _time_steps(torch, model, ctx, stream, tok, Bn, Tn, steps, warmup, barrier, max_over_ranks):
+    for _ in range(warmup):
+        model.forward(tok, Bn, Tn)
+    ctx.sync_check()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        model.forward(tok, Bn, Tn)
+    e1.record(stream)
+    barrier()
+    ctx.sync_check()
+    return max_over_ranks(e0.elapsed_time(e1)) / steps
 
 
 def run_ours(args):
@@ -256,7 +388,11 @@ def run_ours(args):
     cfg = pkg.GPT2_XL if xl else pkg.GPT2_124M
     tp = bool(args.tp) and world > 1   # one tensor-parallel group over all ranks, one global batch
     B = B_PER_GPU
+    mode_name, mode_opts = _headline_mode(pkg)
+    if tp:
+        mode_name, mode_opts = "tf32", dict(pkg.MODES["tf32"])  # the tensor-parallel driver runs the TF32 kernels
     model = pkg.GPT2(ctx, cfg, B, T, tp_size=world if tp else 1, tp_rank=rank if tp else 0)
+    model.set_options(**mode_opts)
     if tp:
         model.set_allreduce_torch(stream)
     with torch.cuda.stream(stream):
@@ -303,6 +439,10 @@ def run_ours(args):
     launches = ctx.launches
     elapsed_ms = max_over_ranks(ev0.elapsed_time(ev1))
     clocks = sampler.stop() if rank == 0 else None
+    # logits of the headline mode for the parity figures (rank 0's first sequences)
+    n_par = 0 if (tp or xl) else (8 if world == 1 else 2)
+    head_logits = model.forward(tok_dev, B, T)[:n_par].clone() if n_par else None
+    ctx.sync_check()
 
     # ---------------------------------------------------------------- end-to-end arm
     # Every step brings its tokens in from pinned host memory, runs the forward and puts the
@@ -336,6 +476,27 @@ def run_ours(args):
         model.forward_host(tok_host.numpy(), B, T, last_logits_host=last_host.numpy(), argmax_host=amax_np)
     e2e_sync_s = max_over_ranks(time.perf_counter() - t0)
     barrier()
+    # the same call returning ALL logits [B,T,Vp] to pinned host memory: the deliverable the benchmark
+    # configuration names, bound by the PCIe copy of 1.65 GB per step
+    e2e_full = None
+    if not tp and not xl:
+        try:
+            full_host = torch.empty((B, T, model.logits_width), dtype=torch.float32).pin_memory()
+            n_full = max(2, min(args.steps, 8))
+            for _ in range(2):
+                model.forward_host(tok_host.numpy(), B, T, logits_host=full_host.numpy())
+            barrier()
+            t0 = time.perf_counter()
+            for _ in range(n_full):
+                model.forward_host(tok_host.numpy(), B, T, logits_host=full_host.numpy())
+            full_s = max_over_ranks(time.perf_counter() - t0)
+            e2e_full = {"value": replicas * B * T * n_full / full_s, "unit": UNIT, "ms_per_step": 1e3 * full_s / n_full,
+                        "steps": n_full, "h2d_bytes_per_step": B * T * 4, "d2h_bytes_per_step": B * T * model.logits_width * 4,
+                        "result": "all logits [B,T,Vp] in pinned host memory", "call": "b200_gpt2_forward_host, one step at a time"}
+            del full_host
+        except Exception as e:
+            e2e_full = {"error": str(e)}
+        barrier()
 
     # the same K steps again with one CUDA-event pair around every kernel launch (on the launching
     # stream): per-operator durations for the roofline figures; not part of `value`
@@ -345,42 +506,24 @@ def run_ours(args):
     prof = model.read_profile()
     model.set_profile(False)
 
-    # ------------------------------------------------ the same workload in the 3xTF32 mode
-    # (split-operand GEMMs and attention: the mode that holds the 99.9 % top-1 / 1e-4 bars)
-    x3_ms = None
-    if not xl:
-        model.set_options(round_operands=0, gemm_mode=pkg.B200_TF32X3, lmhead_mode=pkg.B200_TF32X3)
-        for _ in range(2):
-            model.forward(tok_dev, B, T)
-        barrier()
-        ev2, ev3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        n_x3 = max(1, args.steps // 2)
-        ev2.record(stream)
-        for _ in range(n_x3):
-            model.forward(tok_dev, B, T)
-        ev3.record(stream)
-        barrier()
-        ctx.sync_check()
-        x3_ms = max_over_ranks(ev2.elapsed_time(ev3)) / n_x3
-        model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32)
-
-    # ------------------------------------------------ the same workload with bf16 GEMM operands
-    # (optional reduced-precision mode; never the headline, which stays TF32)
-    bf16_ms = None
-    if not args.tp:
-        model.set_options(round_operands=1, gemm_mode=pkg.B200_BF16, lmhead_mode=pkg.B200_BF16)
-        for _ in range(3):
-            model.forward(tok_dev, B, T)
-        barrier()
-        ev4, ev5 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        ev4.record(stream)
-        for _ in range(args.steps):
-            model.forward(tok_dev, B, T)
-        ev5.record(stream)
-        barrier()
-        ctx.sync_check()
-        bf16_ms = max_over_ranks(ev4.elapsed_time(ev5)) / args.steps
-        model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32)
+    # ------------------------------------------------ the same workload in the other arithmetic modes
+    other = {}
+    other_logits = {}
+    if not tp:
+        for name in ("tf32", "bf16x3", "bf16x3_att3", "bf16"):
+            if name == mode_name or (xl and name == "bf16x3_att3"):
+                continue
+            try:
+                model.set_options(**pkg.MODES[name])
+                n_o = max(2, args.steps // 2)
+                ms = _time_steps(torch, model, ctx, stream, tok_dev, B, T, n_o, 3, barrier, max_over_ranks)
+                other[name] = {"value": replicas * B * T / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "note": pkg.MODE_NOTES[name]}
+                if n_par:
+                    other_logits[name] = model.forward(tok_dev, B, T)[:n_par].clone()
+                    ctx.sync_check()
+            except Exception as e:
+                other[name] = {"error": str(e)}
+        model.set_options(**mode_opts)
 
     # ---------------------------------------------- incremental decoding (key/value cache)
     # One new token per sequence against a cache filled by a prefill of T/2 positions; each step
@@ -390,7 +533,7 @@ def run_ours(args):
     if rank == 0 and not tp and not xl and B <= 16:
         try:
             model.enable_kv_cache()
-            model.set_options(round_operands=1, gemm_mode=pkg.B200_TF32, lmhead_mode=pkg.B200_TF32, use_graph=1)
+            model.set_options(**dict(mode_opts, use_graph=1))
             T0 = T // 2
             model.prefill(tok_dev[:, :T0].contiguous(), B, T0)
             col = tok_dev[:, 0].contiguous()
@@ -414,10 +557,79 @@ def run_ours(args):
                       "achieved_gbs": (w_bytes + kv_bytes) / (dec_us * 1e-6) / 1e9,
                       "frac_of_hbm_peak": (w_bytes + kv_bytes) / (dec_us * 1e-6) / 1e9 / _peaks()["hbm_gbs"],
                       "note": "b200_gpt2_decode_step replayed as a CUDA graph; bytes = all weight matrices once + keys and values of the cached positions"}
+            model.set_options(**mode_opts)
         except Exception as e:  # an extra measurement must not take the benchmark line down
             decode = {"error": str(e)}
 
+    # ---------------------------------------------- parity of the timed arithmetic against the CPU oracle
+    # and the CPU baseline (rank 0): the oracle's fp32 forward on the first sequences of rank 0's batch
+    # with the model's own weights; the first one is timed.
+    parity, cpu_tps, cores, cpu_T = None, None, None, (256 if xl else 1024)
+    if rank == 0:
+        orc, cores = _oracle_all_threads()
+        ocfg = orc.GPT2Config(**cfg.__dict__)
+        host_params = model.params_tensor().cpu().numpy() if not tp else None
+        tok_np = tok_host.numpy()
+        if host_params is None:  # tensor parallel: weights are sharded on the device; time the oracle on its own weights
+            host_params = orc.init_params(ocfg, seed=1234)
+        wants = []
+        for b in range(max(1, n_par)):
+            t0 = time.perf_counter()
+            w = orc.gpt2_forward(host_params, ocfg, tok_np[b:b + 1, :cpu_T], precise=False)[0]
+            if b == 0:
+                cpu_tps = cpu_T / (time.perf_counter() - t0)
+            wants.append(w)
+        if n_par:
+            V = cfg.vocab_size
+
+            def compare(lg):
+                got = lg.cpu().numpy()
+                miss, mx, sq = 0, 0.0, 0.0
+                for b in range(n_par):
+                    err = np.abs(got[b] - wants[b])
+                    mx = max(mx, float(err.max()))
+                    sq += float((err.astype(np.float64) ** 2).mean())
+                    miss += int((got[b][:, :V].argmax(-1) != wants[b][:, :V].argmax(-1)).sum())
+                return {"top1": 1.0 - miss / (n_par * T), "top1_misses": miss, "positions": n_par * T,
+                        "max_abs": mx, "rms": (sq / n_par) ** 0.5}
+
+            parity = {"mode": mode_name, **compare(head_logits),
+                      "against": f"oracle fp32 forward (CPU) on the first {n_par} sequences of rank 0's batch, same weights",
+                      "bars": "max-abs <= 2e-2, top-1 agreement >= 0.999",
+                      "other_modes": {k: compare(v) for k, v in other_logits.items()}}
+        del host_params
+    head_logits = None
+    other_logits = None
+
+    # ---------------------------------------------- measured matmul peaks and the reference's own kernels
+    peaks_now, ref_gpu = None, None
+    if rank == 0:
+        try:
+            peaks_now = _measure_matmul_peaks(torch)
+        except Exception as e:
+            peaks_now = {"error": str(e)}
+        if world == 1 and not xl:
+            try:
+                ref_gpu = _time_reference_gpu_kernels(torch, np)
+            except Exception as e:
+                ref_gpu = {"error": str(e)}
+    barrier()
+
+    # ---------------------------------------------- GPT-2 XL (configs[4]) and the multi-GPU checks
+    extras = {}
+    if not xl and not tp and not args.no_xl:
+        model.close()
+        model = None
+        torch.cuda.empty_cache()
+        try:
+            extras = _xl_and_multi_gpu(pkg, torch, dist, ctx, stream, world, rank, barrier, max_over_ranks, mode_name)
+        except Exception as e:
+            extras = {"xl_config4": {"error": str(e)}}
+
     if rank != 0:
+        if model is not None:
+            model.close()
+        ctx.close()
         if dist is not None:
             dist.destroy_process_group()
         return 0
@@ -425,81 +637,188 @@ def run_ours(args):
     tokens_total = replicas * B * T * args.steps
     value = tokens_total / (elapsed_ms * 1e-3)
     peaks = _peaks()
-    # dominant kernel: the tcgen05 TF32 GEMM (five shapes, 4L+1 launches per step); rank-local widths
+    # dominant kernel: the tcgen05 GEMM (five shapes, 4L+1 launches per step); rank-local widths
     M = B * T
     Cc, L = cfg.channels, cfg.num_layers
     n_tp = world if tp else 1
-    Ac, Fc, Vl = pkg.tp_heads(cfg.num_heads, n_tp, 0)[1] * 64, 4 * Cc // n_tp, model.logits_width
+    Ac, Fc, Vl = pkg.tp_heads(cfg.num_heads, n_tp, 0)[1] * 64, 4 * Cc // n_tp, (cfg.padded_vocab_size // n_tp if tp else cfg.padded_vocab_size)
+    if tp and (cfg.padded_vocab_size % n_tp or (cfg.padded_vocab_size // n_tp) % 4):
+        Vl = cfg.padded_vocab_size
     gemm_flops = {"gemm_qkv": 2.0 * M * Cc * 3 * Ac, "gemm_attproj": 2.0 * M * Ac * Cc, "gemm_fc": 2.0 * M * Cc * Fc,
                   "gemm_fcproj": 2.0 * M * Fc * Cc, "gemm_lmhead": 2.0 * M * Cc * Vl}
     tot_flops = sum(gemm_flops[k] * prof[k][1] for k in gemm_flops)
     tot_ms = sum(prof[k][0] for k in gemm_flops)
     n_gemm = sum(prof[k][1] for k in gemm_flops)
-    tf32_peak = peaks["bf16_sustained"] / 2.0
     achieved = tot_flops / (tot_ms * 1e-3) / 1e12 if tot_ms > 0 else 0.0
+    # Denominator: the tensor-pipe rate this arithmetic can reach per algorithmic flop.  TF32: the
+    # cuBLAS TF32 GEMM measured in this run (burst: best launch; sustained: seconds back to back).
+    # bf16x3: three bf16 products per algorithmic product, so a third of the measured bf16 GEMM rate.
+    have_now = isinstance(peaks_now, dict) and "tf32_burst_tflops" in peaks_now
+    if mode_name.startswith("bf16x3"):
+        pk_burst = (peaks_now["bf16_burst_tflops"] if have_now else peaks["bf16_burst"]) / 3.0
+        pk_sust = (peaks_now["bf16_sustained_tflops"] if have_now else peaks["bf16_sustained"]) / 3.0
+        pk_src = ("bf16 cuBLAS GEMM " + ("measured in this run" if have_now else f"from MEASURED_PEAKS.json ({peaks['source']})") +
+                  " / 3: the kernel issues three bf16 products (hi.hi + hi.lo + lo.hi) per algorithmic product")
+    elif mode_name == "bf16":
+        pk_burst = peaks_now["bf16_burst_tflops"] if have_now else peaks["bf16_burst"]
+        pk_sust = peaks_now["bf16_sustained_tflops"] if have_now else peaks["bf16_sustained"]
+        pk_src = "bf16 cuBLAS GEMM " + ("measured in this run" if have_now else f"from MEASURED_PEAKS.json ({peaks['source']})")
+    else:
+        pk_burst = peaks_now["tf32_burst_tflops"] if have_now else peaks["bf16_burst"] / 2.0
+        pk_sust = peaks_now["tf32_sustained_tflops"] if have_now else peaks["bf16_sustained"] / 2.0
+        pk_src = ("TF32 cuBLAS GEMM measured in this run" if have_now else
+                  f"{peaks['source']} bf16 / 2 (TF32 issues at half the bf16 rate; no TF32 measurement was possible)")
     per_op = {}
     hbm_bytes = {"layernorm": (2.0 * M * Cc + 2 * Cc) * 4, "fused_residual_layernorm": (4.0 * M * Cc + 2 * Cc) * 4,
                  "encoder": (2.0 * M * Cc + T * Cc) * 4 + M * 4}
     att_flops = 4.0 * 64 * T * (T + 1) / 2 * (Ac // 64) * B
+    prof_total = sum(v[0] for v in prof.values())
     for name, (ms, n) in prof.items():
         if n == 0:
             continue
         avg = ms / n
-        entry = {"launches_per_step": n / args.steps, "avg_ms": round(avg, 5), "share": round(ms / sum(v[0] for v in prof.values()), 4)}
+        entry = {"launches_per_step": n / args.steps, "avg_ms": round(avg, 5), "share": round(ms / prof_total, 4)}
         if name in gemm_flops:
             entry["tflops"] = round(gemm_flops[name] / (avg * 1e-3) / 1e12, 1)
+            entry["frac_burst"] = round(entry["tflops"] / pk_burst, 3)
         elif name == "attention":
             entry["tflops_causal"] = round(att_flops / (avg * 1e-3) / 1e12, 1)
         elif name in hbm_bytes:
             entry["gbs"] = round(hbm_bytes[name] / (avg * 1e-3) / 1e9, 1)
+            entry["frac_hbm"] = round(entry["gbs"] / peaks["hbm_gbs"], 3)
+        if isinstance(ref_gpu, dict) and name in ref_gpu.get("kernels", {}):
+            entry["vs_reference_kernel"] = round(ref_gpu["kernels"][name]["ms"] / avg, 2)
         per_op[name] = entry
-
-    cpu_T = 256 if xl else 1024
-    cpu_tps, cores, _, _ = cpu_forward_tokens_per_s(cpu_T, repeats=1, xl=xl)
-    d2h = B * model.logits_width * 4 + (0 if tp else B * T * 4)
-    workload = WORKLOAD if not xl else "GPT-2 XL 1.5B full-sequence forward, B=8 T=1024 per " + ("tensor-parallel group" if tp else "GPU") + ", fp32 storage, TF32 tensor-core GEMMs (configs[4] shapes)"
-    par = (f"tensor-parallel x{world}: heads / MLP / vocabulary split, one NCCL all-reduce per attention and MLP block" if tp
-           else f"batch-sharded x{world}, no collective")
+    traffic = None if (xl or tp) else GEMM_DRAM_TRAFFIC.get(mode_name)
+    cfg_obj = _config(world, tp, xl)
+    cfg_obj["flop_per_token"] = cfg.flops_per_token(T)
+    cfg_obj["arithmetic"] = pkg.MODE_NOTES[mode_name]
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
         "warmup": max(args.warmup, 3), "ms_per_step": elapsed_ms / args.steps, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "tf32", "data": "synthetic",
-        "config": {"workload": workload, "global_batch": replicas * B, "seq_len": T, "parallelism": par,
-                   "l2": "no flush: each step streams the weights (0.5 GB for 124M) and writes 1.65 GB of logits, far beyond the 126 MB L2",
-                   "flop_per_token": cfg.flops_per_token(T)},
-        "roofline": {"bound": "tensor", "kernel": "gemm_tf32_pair_kernel and gemm_tf32_kernel (all five GEMM shapes of the forward)",
-                     "achieved": achieved, "peak": tf32_peak, "unit": "TFLOP/s", "frac": achieved / tf32_peak,
-                     "peak_source": f"{peaks['source']} bf16 sustained {peaks['bf16_sustained']} TFLOP/s / 2 (TF32 runs at half the bf16 rate; no TF32 peak is measured)",
+        "scaling": "weak", "vs_baseline": None, "dtype": mode_name, "data": "synthetic",
+        "config": cfg_obj,
+        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel and gemm_tf32_kernel (all five GEMM shapes of the forward)",
+                     "achieved": achieved, "peak": pk_burst, "unit": "TFLOP/s", "frac": achieved / pk_burst,
+                     "frac_burst": achieved / pk_burst, "frac_sustained": achieved / pk_sust, "peak_sustained": pk_sust,
+                     "matches_timed_region": "burst: the timed region lasts a fraction of a second (see clocks.sm_mhz)",
+                     "peak_source": pk_src, "peaks_measured_in_run": peaks_now,
                      "launches_per_step": n_gemm / args.steps,
-                     # ncu dram__bytes_read.sum + dram__bytes_write.sum, average per GEMM launch of the 124M
-                     # forward (profiles/gemm_tf32_dram_traffic_by_shape.md); not captured for other models
-                     "traffic": None if (xl or tp) else 116.2e6, "algorithmic_bytes": None if (xl or tp) else 142.9e6,
+                     "event_timing": "one event pair per launch serialises the launches: per-operator times add up to slightly more than ms_per_step",
+                     "traffic": None if traffic is None else traffic["dram_bytes_per_launch"],
+                     "algorithmic_bytes": None if traffic is None else traffic["algorithmic_bytes_per_launch"],
+                     "traffic_source": None if traffic is None else traffic["source"],
                      "per_operator": per_op},
+        "parity": parity,
         "cpu_baseline": {"value": cpu_tps, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"1 sequence of {cpu_T} tokens (B=1), fp32-accumulate C/OpenMP forward, all host threads, one run"},
+                         "sample": f"1 sequence of {cpu_T} tokens (B=1), fp32-accumulate C/OpenMP forward, {cores} host threads, one run"},
         "e2e": {"value": replicas * B * T * args.steps / e2e_s, "unit": UNIT, "h2d_bytes_per_step": B * T * 4,
-                "d2h_bytes_per_step": d2h, "ms_per_step": 1e3 * e2e_s / args.steps,
+                "d2h_bytes_per_step": B * model_logits_width(pkg, cfg, n_tp if tp else 1) * 4 + (0 if tp else B * T * 4),
+                "ms_per_step": 1e3 * e2e_s / args.steps,
                 "result": "last-position logits [B,Vp]" + ("" if tp else " and per-position arg-max token ids [B,T]"),
                 "call": "b200_gpt2_forward_host_enqueue / _wait, two steps in flight, double-buffered pinned host buffers",
                 "synchronous_call": {"value": replicas * B * T * args.steps / e2e_sync_s, "ms_per_step": 1e3 * e2e_sync_s / args.steps,
                                      "call": "b200_gpt2_forward_host, one step at a time"}},
+        "e2e_full_logits": e2e_full,
         "gpu_launches": launches,
         "clocks": clocks,
-        "tf32x3": None if x3_ms is None else {
-            "value": replicas * B * T / (x3_ms * 1e-3), "unit": UNIT, "ms_per_step": x3_ms,
-            "note": "same workload with gemm_mode = lmhead_mode = B200_TF32X3 (split-operand GEMMs and attention)"},
-        "bf16_operands": None if bf16_ms is None else {
-            "value": replicas * B * T / (bf16_ms * 1e-3), "unit": UNIT, "ms_per_step": bf16_ms,
-            "note": "same workload with gemm_mode = lmhead_mode = B200_BF16 (bf16 GEMM operands, fp32 accumulation; "
-                    "reduced precision, not comparable with the headline)"},
+        "other_modes": other,
         "decode": decode,
+        "ref_gpu_kernels": ref_gpu,
     }
+    line.update(extras)
     print(json.dumps(line), flush=True)
-    model.close()
+    if model is not None:
+        model.close()
     ctx.close()
     if dist is not None:
         dist.destroy_process_group()
     return 0
+
+
+def model_logits_width(pkg, cfg, n_tp):
+    Vp = cfg.padded_vocab_size
+    return Vp // n_tp if (Vp % n_tp == 0 and (Vp // n_tp) % 4 == 0) else Vp
+
+
+def _xl_and_multi_gpu(pkg, torch, dist, ctx, stream, world, rank, barrier, max_over_ranks, mode_name):
+    """GPT-2 XL at global batch 64 split over the ranks (strong scaling of configs[4]); with more
+    than one rank also the tensor-parallel XL forward (B=8) with its all-reduce share, and the
+    sharding checks: batch shards bitwise equal to the unsharded run, tensor-parallel logits
+    against the unsharded ones."""
+    out = {}
+    cfg = pkg.GPT2_XL
+    GB = 64
+    Bl = GB // world
+    g = torch.Generator(device="cuda").manual_seed(4321)
+    tok_all = torch.randint(0, cfg.vocab_size, (GB, T), dtype=torch.int32, device="cuda", generator=g)  # same on every rank
+    xlm = pkg.GPT2(ctx, cfg, max(Bl, 8), T)
+    xlm.set_options(**pkg.MODES[mode_name])
+    with torch.cuda.stream(stream):
+        _random_init_(xlm, pkg, torch, seed=99)
+    stream.synchronize()
+    lo = rank * Bl
+    tok_mine = tok_all[lo:lo + Bl].contiguous()
+    steps = 2 if world == 1 else 3
+    ms = _time_steps(torch, xlm, ctx, stream, tok_mine, Bl, T, steps, 1, barrier, max_over_ranks)
+    out["xl_config4"] = {"value": GB * T / (ms * 1e-3), "unit": UNIT, "ms_per_step": ms, "global_batch": GB, "batch_per_gpu": Bl,
+                         "n_gpus": world, "steps": steps, "scaling": "strong", "dtype": mode_name,
+                         "workload": "GPT-2 XL 1.5B (48 layers, 25 heads, C=1600) full-sequence forward, global batch 64 x T=1024 "
+                                     "sharded over the GPUs, no collective (configs[4])"}
+    if world == 1:
+        xlm.close()
+        return out
+
+    # ---- batch sharding is exact: sequences [0,8) computed by every rank as one batch, and each rank's
+    # own slice of them computed alone, give the same bits everywhere
+    with torch.no_grad():
+        ref8 = xlm.forward(tok_all[:8].contiguous(), 8, T)
+        ctx.sync_check()
+        h_full = _seq_hashes(torch, ref8)
+        s0, s1 = pkg.shard_batch(8, world, rank)
+        h_shard = torch.zeros((8, 2), dtype=torch.int64, device="cuda")
+        if s1 > s0:
+            part = xlm.forward(tok_all[s0:s1].contiguous(), s1 - s0, T)
+            ctx.sync_check()
+            h_shard[s0:s1] = _seq_hashes(torch, part)
+        gather_full = [torch.empty_like(h_full) for _ in range(world)]
+        dist.all_gather(gather_full, h_full)
+        dist.all_reduce(h_shard)  # every sequence is filled in by exactly one rank
+        same_full = all(torch.equal(gather_full[0], x) for x in gather_full)
+        same_shard = torch.equal(h_shard, gather_full[0])
+        out["shard_check"] = {"batch_sharded": "bitwise" if (same_full and same_shard) else "MISMATCH",
+                              "how": "GPT-2 XL, 8 sequences: per-sequence checksums of the logits' bit patterns, the full batch on "
+                                     "every rank and each rank's own shard alone, compared across the ranks"}
+
+    # ---- tensor parallel over all ranks (B = 8): weights cut out of the unsharded model's on the device
+    tpm = pkg.GPT2(ctx, cfg, 8, T, tp_size=world, tp_rank=rank)
+    tpm.set_allreduce_torch(stream)
+    with torch.cuda.stream(stream):
+        tpm.params_tensor().copy_(pkg.shard_params_torch(cfg, world, rank, xlm.params_tensor()))
+    stream.synchronize()
+    tok8 = tok_all[:8].contiguous()
+    tp_logits = tpm.forward(tok8, 8, T)
+    ctx.sync_check()
+    Vl = tpm.logits_width
+    full_slice = ref8[..., rank * Vl:(rank + 1) * Vl] if Vl != cfg.padded_vocab_size else ref8
+    diff = (tp_logits - full_slice).abs().max().reshape(1).to(torch.float64)
+    dist.all_reduce(diff, op=dist.ReduceOp.MAX)
+    out["shard_check"]["tensor_parallel_max_abs_vs_unsharded"] = float(diff.item())
+    ms_tp = _time_steps(torch, tpm, ctx, stream, tok8, 8, T, 3, 1, barrier, max_over_ranks)
+    tpm.set_profile(True)
+    for _ in range(2):
+        tpm.forward(tok8, 8, T)
+    prof = tpm.read_profile()
+    tpm.set_profile(False)
+    tot = sum(v[0] for v in prof.values())
+    out["tp_xl"] = {"value": 8 * T / (ms_tp * 1e-3), "unit": UNIT, "ms_per_step": ms_tp, "batch": 8, "tp_size": world,
+                    "allreduce_ms_per_step": prof["allreduce"][0] / 2, "allreduce_share_serialised": prof["allreduce"][0] / tot if tot else None,
+                    "allreduce_launches_per_step": prof["allreduce"][1] / 2,
+                    "note": "GPT-2 XL, one tensor-parallel group over all ranks (heads / MLP / vocabulary split), one NCCL all-reduce "
+                            "per attention and MLP block; the share is from per-launch event pairs, which serialise the streams"}
+    tpm.close()
+    xlm.close()
+    return out
 
 
 def run_kernel_sweep(args):
@@ -641,6 +960,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--model", default="124m", choices=["124m", "xl"],
                     help="124m = the benchmark configuration; xl = GPT-2 XL shapes, B=8 T=1024 per GPU (extra measurement)")
+    ap.add_argument("--no-xl", action="store_true", help="skip the GPT-2 XL / multi-GPU extras behind the main measurement")
     ap.add_argument("--tp", action="store_true",
                     help="with --gpus N > 1: one tensor-parallel group over all ranks instead of batch sharding")
     ap.add_argument("--op", default=None,

@@ -25,14 +25,15 @@ LIB_PATH = os.path.join(_HERE, "lib", "libb200gpt2.so")
 B200_OK = 0
 (B200_ERR_NULL, B200_ERR_SHAPE, B200_ERR_ALIGN, B200_ERR_CUDA, B200_ERR_DEVICE, B200_ERR_TIMEOUT,
  B200_ERR_STATE, B200_ERR_LIMIT) = range(1, 9)
-B200_TF32, B200_TF32X3, B200_BF16 = 0, 1, 2
+B200_TF32, B200_TF32X3, B200_BF16, B200_BF16X3 = 0, 1, 2, 3
 ACT_NONE, ACT_GELU = 0, 1
 
 EXPORTS = (
     "b200_ctx_create", "b200_ctx_destroy", "b200_ctx_set_stream", "b200_ctx_sync_check",
     "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
     "b200_ctx_last_error", "b200_ctx_wait_timeout_probe",
-    "b200_matmul_forward", "b200_matmul_forward_bf16", "b200_convert_bf16", "b200_attention_forward", "b200_attention_forward_x3", "b200_layernorm_forward",
+    "b200_matmul_forward", "b200_matmul_forward_bf16", "b200_convert_bf16", "b200_matmul_forward_bf16x3", "b200_split_bf16",
+    "b200_gpt2_set_attention_mode", "b200_attention_forward", "b200_attention_forward_x3", "b200_layernorm_forward",
     "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
     "b200_encoder_forward",
     "matmul_forward", "matmul_forward_gelu", "attention_forward", "layernorm_forward",
@@ -42,10 +43,28 @@ EXPORTS = (
     "b200_gpt2_load_params_host", "b200_gpt2_load_params_file", "b200_gpt2_set_options", "b200_gpt2_forward",
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_forward_host_enqueue", "b200_gpt2_forward_host_wait", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
-    "b200_gpt2_forward_static",
+    "b200_gpt2_forward_static", "b200_gpt2_static_prepare",
     "b200_gpt2_enable_kv_cache", "b200_gpt2_prefill", "b200_gpt2_decode_step", "b200_gpt2_decode_step_host", "b200_gpt2_generate_greedy", "b200_gpt2_generate", "b200_sample_rows",
     "b200_gpt2_create_tp", "b200_gpt2_set_allreduce", "b200_gpt2_param_offsets_tp", "b200_gpt2_shard_params_host",
 )
+
+# Arithmetic modes of the forward as keyword arguments of GPT2.set_options
+MODES = {
+    "tf32": dict(round_operands=1, gemm_mode=B200_TF32, lmhead_mode=B200_TF32, attention_mode=-1),
+    "bf16x3": dict(round_operands=1, gemm_mode=B200_BF16X3, lmhead_mode=B200_BF16X3, attention_mode=-1),
+    "bf16x3_att3": dict(round_operands=1, gemm_mode=B200_BF16X3, lmhead_mode=B200_BF16X3, attention_mode=B200_TF32X3),
+    "tf32x3": dict(round_operands=0, gemm_mode=B200_TF32X3, lmhead_mode=B200_TF32X3, attention_mode=-1),
+    "bf16": dict(round_operands=1, gemm_mode=B200_BF16, lmhead_mode=B200_BF16, attention_mode=-1),
+}
+MODE_NOTES = {
+    "tf32": "fp32 storage, single-pass TF32 tensor-core GEMMs (tcgen05 kind::tf32) on round-to-nearest operands, TF32 attention",
+    "bf16x3": "fp32 storage, GEMM operands split into two bf16 terms (16 significant bits), three kind::f16 products per K step, "
+              "fp32 accumulation; single-pass TF32 attention",
+    "bf16x3_att3": "bf16x3 GEMMs with split-operand (3xTF32) attention: fp32-level logits",
+    "tf32x3": "3xTF32 GEMMs and attention (three kind::tf32 products per K step)",
+    "bf16": "bf16 GEMM operands (reduced precision; not comparable with the fp32-level modes)",
+}
+DEFAULT_MODE_NAME = "bf16x3"  # what b200_gpt2_create sets (a tensor-parallel model starts in "tf32")
 
 STATIC_MAX_TOKEN_CHANNELS = 196608  # B*T*C limit of b200_gpt2_forward_static
 
@@ -85,6 +104,9 @@ def lib() -> C.CDLL:
         l.b200_matmul_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, vp, i]
         l.b200_matmul_forward_bf16.argtypes = [vp, vp, vp, vp, vp, vp, i, i, i, i, i]
         l.b200_convert_bf16.argtypes = [vp, vp, vp, sz]
+        l.b200_matmul_forward_bf16x3.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i]
+        l.b200_split_bf16.argtypes = [vp, vp, vp, vp, sz]
+        l.b200_gpt2_set_attention_mode.argtypes = [vp, i]
         l.b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_attention_forward_x3.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_layernorm_forward.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i]
@@ -124,6 +146,7 @@ def lib() -> C.CDLL:
         l.b200_gpt2_set_profile.argtypes = [vp, i]
         l.b200_gpt2_read_profile.argtypes = [vp, C.POINTER(C.c_double), C.POINTER(C.c_long)]
         l.b200_gpt2_forward_static.argtypes = [vp, vp, vp, vp, i, i, vp]
+        l.b200_gpt2_static_prepare.argtypes = [vp]
         l.b200_gpt2_enable_kv_cache.argtypes = [vp]
         l.b200_gpt2_prefill.argtypes = [vp, vp, i, i]
         l.b200_gpt2_decode_step.argtypes = [vp, vp, i, i]
@@ -207,6 +230,18 @@ class Context:
 
     def convert_bf16(self, out, inp, n):
         self.check(lib().b200_convert_bf16(self._h, _ptr(out), _ptr(inp), n), "convert_bf16")
+
+    def split_bf16(self, hi, lo, inp, n):
+        """hi = bf16(inp), lo = bf16(inp - hi)."""
+        self.check(lib().b200_split_bf16(self._h, _ptr(hi), _ptr(lo), _ptr(inp), n), "split_bf16")
+
+    def matmul_forward_bf16x3(self, out, out_split, inp_split, weight_hi, weight_lo, bias, B, T, Cc, OC, act=ACT_NONE,
+                              accumulate=False):
+        """inp_split: bf16 [2,B,T,C] (hi plane, lo plane); weight_hi / weight_lo bf16 [OC,C]; out fp32 or
+        out_split bf16 [2,B,T,OC]."""
+        self.check(lib().b200_matmul_forward_bf16x3(self._h, _ptr(out), _ptr(out_split), _ptr(inp_split), _ptr(weight_hi),
+                                                    _ptr(weight_lo), _ptr(bias), B, T, Cc, OC, act, int(accumulate)),
+                   "matmul_forward_bf16x3")
 
     def sample_rows(self, out, logits, M, V, ld, temperature, seed, stream0, top_k=0, top_p=0.0):
         self.check(lib().b200_sample_rows(self._h, _ptr(out), _ptr(logits), M, V, ld, float(temperature), int(top_k), float(top_p),
@@ -329,6 +364,34 @@ def shard_params(cfg: GPT2Config, tp_size: int, tp_rank: int, full_params):
     return local
 
 
+def shard_params_torch(cfg: GPT2Config, tp_size: int, tp_rank: int, full):
+    """The same cut as shard_params on a flat CUDA tensor of the full parameters (no host round trip)."""
+    import torch
+    fo, lo = param_offsets(cfg), param_offsets_tp(cfg, tp_size, tp_rank)
+    Cc, L = cfg.channels, cfg.num_layers
+    h0, nh = tp_heads(cfg.num_heads, tp_size, tp_rank)
+    A, a0 = nh * 64, h0 * 64
+    F = 4 * Cc // tp_size
+    f0 = tp_rank * F
+    local = torch.empty(lo[16], dtype=torch.float32, device=full.device)
+    fv = lambda i, *shape: full[fo[i]:fo[i + 1]].view(*shape)
+    lv = lambda i, *shape: local[lo[i]:lo[i + 1]].view(*shape)
+    for t in (0, 1, 2, 3, 8, 9, 14, 15):  # wte, wpe and the layernorm tensors are replicated
+        local[lo[t]:lo[t + 1]] = full[fo[t]:fo[t + 1]]
+    lv(4, L, 3, A, Cc).copy_(fv(4, L, 3, Cc, Cc)[:, :, a0:a0 + A, :])   # q, k, v rows of the local heads
+    lv(5, L, 3, A).copy_(fv(5, L, 3, Cc)[:, :, a0:a0 + A])
+    lv(6, L, Cc, A).copy_(fv(6, L, Cc, Cc)[:, :, a0:a0 + A])            # input columns of the two projections
+    lv(12, L, Cc, F).copy_(fv(12, L, Cc, 4 * Cc)[:, :, f0:f0 + F])
+    lv(10, L, F, Cc).copy_(fv(10, L, 4 * Cc, Cc)[:, f0:f0 + F, :])
+    lv(11, L, F).copy_(fv(11, L, 4 * Cc)[:, f0:f0 + F])
+    for t in (7, 13):  # the projection biases are added once: by rank 0
+        if tp_rank == 0:
+            lv(t, L, Cc).copy_(fv(t, L, Cc))
+        else:
+            lv(t, L, Cc).zero_()
+    return local
+
+
 class GPT2:
     """gpt2_forward driver (C++ inside the library).  Allocates parameters and one reusable set
     of activations for up to max_B x max_T tokens.  With tp_size > 1 this is one rank of a
@@ -385,9 +448,18 @@ class GPT2:
         """Raw fp32 parameters in param_offsets order behind a header of header_bytes."""
         self.ctx.check(lib().b200_gpt2_load_params_file(self._h, os.fsencode(path), header_bytes), "load_params_file")
 
-    def set_options(self, round_operands=1, gemm_mode=B200_TF32, lmhead_mode=B200_TF32, use_graph=0):
+    def set_options(self, round_operands=1, gemm_mode=None, lmhead_mode=None, use_graph=0, attention_mode=-1):
+        """gemm_mode / lmhead_mode default to the library's default arithmetic (DEFAULT_MODE_NAME)."""
+        d = MODES[DEFAULT_MODE_NAME if self.tp_size == 1 else "tf32"]
+        gemm_mode = d["gemm_mode"] if gemm_mode is None else gemm_mode
+        lmhead_mode = d["lmhead_mode"] if lmhead_mode is None else lmhead_mode
+        self.ctx.check(lib().b200_gpt2_set_attention_mode(self._h, int(attention_mode)), "set_attention_mode")
         self.ctx.check(lib().b200_gpt2_set_options(self._h, int(round_operands), gemm_mode, lmhead_mode, int(use_graph)),
                        "set_options")
+
+    def set_attention_mode(self, mode: int = -1):
+        """-1: follow gemm_mode; B200_TF32: single-pass kernel; B200_TF32X3: split-operand kernel."""
+        self.ctx.check(lib().b200_gpt2_set_attention_mode(self._h, int(mode)), "set_attention_mode")
 
     def forward(self, tokens, B: int, T: int):
         """tokens: CUDA int32 [B,T].  Asynchronous; returns a view of the logits [B,T,Vp]."""
@@ -469,6 +541,12 @@ class GPT2:
         if self._h:
             lib().b200_gpt2_destroy(self._h)
             self._h = C.c_void_p()
+
+
+def gpt2_static_prepare(ctx: Context) -> int:
+    """b200_gpt2_static_prepare: the one-time set-up of gpt2_forward_static on the context's device,
+    to be called while device allocation is still allowed; returns the status code."""
+    return int(lib().b200_gpt2_static_prepare(ctx._h))
 
 
 def gpt2_forward_static(ctx: Context, cfg: GPT2Config, params, tokens, B: int, T: int, logits) -> int:

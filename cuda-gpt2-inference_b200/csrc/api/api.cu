@@ -99,12 +99,16 @@ int b200_ctx_create(b200_ctx** out, int device, void* stream) {
     e = cudaMalloc(&ctx->d_status, 256);
     if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, 256);
     if (e == cudaSuccess) e = cudaHostAlloc(&ctx->h_status, sizeof(int), cudaHostAllocDefault);
-    if (e != cudaSuccess) { cudaFree(ctx->d_status); delete ctx; return B200_ERR_CUDA; }
+    ctx->split_flag_words = (size_t)1 << 18;  // 1 MB: up to 16384 K-slice tiles per launch
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->d_split_flags, ctx->split_flag_words * sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_split_flags, 0, ctx->split_flag_words * sizeof(unsigned int));
+    if (e != cudaSuccess) { cudaFree(ctx->d_status); cudaFree(ctx->d_split_flags); delete ctx; return B200_ERR_CUDA; }
     void* fn = nullptr;
     cudaDriverEntryPointQueryResult qres;
     e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &qres);
     if (e != cudaSuccess || qres != cudaDriverEntryPointSuccess || !fn) {
         cudaFree(ctx->d_status);
+        cudaFree(ctx->d_split_flags);
         cudaFreeHost(ctx->h_status);
         delete ctx;
         return B200_ERR_CUDA;
@@ -119,6 +123,7 @@ int b200_ctx_destroy(b200_ctx* ctx) {
     if (!ctx) return B200_ERR_NULL;
     cudaSetDevice(ctx->device);
     cudaFree(ctx->d_status);
+    cudaFree(ctx->d_split_flags);
     cudaFreeHost(ctx->h_status);
     delete ctx;
     return B200_OK;
@@ -137,8 +142,10 @@ int b200_ctx_sync_check(b200_ctx* ctx) {
     B200_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     const int word = *ctx->h_status;
     if (word != 0) {
-        // the whole area: a kernel that gave up may have left its work counters behind
+        // the whole area: a kernel that gave up may have left its work counters behind (and a GEMM
+        // with K slices its hand-over flags)
         B200_CUDA(ctx, cudaMemset(ctx->d_status, 0, 256));
+        B200_CUDA(ctx, cudaMemset(ctx->d_split_flags, 0, ctx->split_flag_words * sizeof(unsigned int)));
         ctx->last_error = "device status word = " + std::to_string(word);
         return word == 201 ? B200_ERR_SHAPE : B200_ERR_TIMEOUT;
     }
@@ -172,8 +179,34 @@ int b200_matmul_forward(b200_ctx* ctx, float* out, const float* inp, const float
     if ((long long)B * T > 0x7fffffffLL) return B200_ERR_SHAPE;
     if (act != B200_ACT_NONE && act != B200_ACT_GELU) return B200_ERR_SHAPE;
     if (mode != B200_TF32 && mode != B200_TF32X3) return B200_ERR_SHAPE;
-    return b200::launch_gemm_tf32(ctx, out, inp, weight, bias, residual, B * T, C, OC,
-                                  act == B200_ACT_GELU ? b200::GEMM_GELU : 0, mode);
+    int flags = act == B200_ACT_GELU ? b200::GEMM_GELU : 0;
+    if (residual == out) {  // in place: the tiles are added onto out as they retire
+        flags |= b200::GEMM_ACCUM_OUT;
+        residual = nullptr;
+    }
+    return b200::launch_gemm_tf32(ctx, out, inp, weight, bias, residual, B * T, C, OC, flags, mode);
+}
+
+int b200_matmul_forward_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_split, const uint16_t* inp_split,
+                               const uint16_t* weight_hi, const uint16_t* weight_lo, const float* bias, int B, int T,
+                               int C, int OC, int act, int accumulate) {
+    if (!ctx) return B200_ERR_NULL;
+    if (out_split) { REQUIRE_PTR(out_split); } else { REQUIRE_PTR(out); }
+    REQUIRE_PTR(inp_split); REQUIRE_PTR(weight_hi); REQUIRE_PTR(weight_lo);
+    OPTIONAL_PTR(bias);
+    if (B <= 0 || T <= 0 || C <= 0 || OC <= 0 || C % 8 || OC % 8) return B200_ERR_SHAPE;
+    if ((long long)B * T > 0x7fffffffLL) return B200_ERR_SHAPE;
+    if (act != B200_ACT_NONE && act != B200_ACT_GELU) return B200_ERR_SHAPE;
+    if (out_split && (accumulate || ((long long)B * T) % 32)) return B200_ERR_SHAPE;
+    return b200::launch_gemm_bf16x3(ctx, out, out_split, inp_split, weight_hi, weight_lo, bias, B * T, C, OC,
+                                    (act == B200_ACT_GELU ? b200::GEMM_GELU : 0) | (accumulate ? b200::GEMM_ACCUM_OUT : 0));
+}
+
+int b200_split_bf16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* inp, size_t n) {
+    if (!ctx) return B200_ERR_NULL;
+    REQUIRE_PTR(hi); REQUIRE_PTR(lo); REQUIRE_PTR(inp);
+    if (n == 0 || n % 4) return B200_ERR_SHAPE;
+    return b200::launch_convert_bf16(ctx, hi, inp, n, lo);
 }
 
 int b200_matmul_forward_bf16(b200_ctx* ctx, float* out, uint16_t* out_bf16, const uint16_t* inp,

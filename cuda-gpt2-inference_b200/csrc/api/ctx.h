@@ -38,6 +38,9 @@ struct b200_ctx {
     cudaStream_t stream = nullptr;
     int* d_status = nullptr;  // device word: first device-side error code of any kernel
     int* h_status = nullptr;  // pinned host copy of that word, filled by b200_ctx_sync_check
+    // CTA-pair GEMM with K slices: one flag word per (slice, tile, CTA, epilogue warp); all zero between launches
+    unsigned int* d_split_flags = nullptr;
+    size_t split_flag_words = 0;
     uint64_t launches = 0;
     bool pdl = true;  // launch with programmatic stream serialization (B200_PDL=0 turns it off)
     std::string last_error;
@@ -65,5 +68,18 @@ int b200_get_tensor_map(b200_ctx* ctx, CUtensorMap* out, const float* ptr, uint6
 // The same over a matrix of bf16 (16-bit) elements: 128-byte swizzle of 16-byte chunks.
 int b200_get_tensor_map_bf16(b200_ctx* ctx, CUtensorMap* out, const void* ptr, uint64_t rows,
                              uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+
+// Makes the context's device current for the lifetime of the guard (streams, events and launches
+// belong to a device) and puts the caller's device back afterwards.
+struct b200_device_guard {
+    int prev = -1;
+    bool switched = false;
+    explicit b200_device_guard(const b200_ctx* ctx) {
+        if (cudaGetDevice(&prev) == cudaSuccess && prev != ctx->device) switched = cudaSetDevice(ctx->device) == cudaSuccess;
+    }
+    ~b200_device_guard() { if (switched) cudaSetDevice(prev); }
+    b200_device_guard(const b200_device_guard&) = delete;
+    b200_device_guard& operator=(const b200_device_guard&) = delete;
+};
 
 inline bool b200_aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }

@@ -7,6 +7,7 @@
 #include <cstdio>
 #include <cstring>
 #include <map>
+#include <mutex>
 #include <string>
 #include <new>
 #include <utility>
@@ -21,11 +22,12 @@ struct b200_gpt2 {
     size_t n_params = 0;
     size_t off[17] = {};
     float* params = nullptr;
-    float* wte_rounded = nullptr;  // TF32-rounded copy of wte for the lm-head (round_operands)
+    float* params_r = nullptr;     // TF32-rounded copy of the five weight matrices (same offsets; round_operands)
     float* qkv_small = nullptr;    // scratch of the 3xTF32 attention (allocated by set_options)
     bool weights_rounded = false;
-    uint16_t* params_h = nullptr;  // bf16 copy of the parameters (same offsets) for the B200_BF16 modes
-    bool params_h_ready = false;
+    uint16_t* params_h = nullptr;  // bf16 copy of the weight matrices (same offsets) for the bf16 modes
+    uint16_t* params_l = nullptr;  // what that rounding dropped, again as bf16 (B200_BF16X3)
+    bool params_h_ready = false, params_l_ready = false;
     // activations, sized for max_B * max_T rows
     float *residual = nullptr, *ln_out = nullptr, *qkv = nullptr, *atty = nullptr,
           *branch = nullptr, *fch = nullptr, *logits = nullptr;
@@ -47,7 +49,8 @@ struct b200_gpt2 {
     // the kernel behind the lm-head (null: the model's own buffers).  Set around one enqueue_forward.
     struct HostDst { int* ids = nullptr; float* last = nullptr; int* status = nullptr; } host_dst;
     std::map<int, cudaGraphExec_t> decode_graphs;  // by B (the position is read from pos_dev)
-    int round_operands = 1, gemm_mode = B200_TF32, lmhead_mode = B200_TF32, use_graph = 0;
+    int round_operands = 1, gemm_mode = B200_BF16X3, lmhead_mode = B200_BF16X3, use_graph = 0;
+    int att_mode = -1;  // -1: split-operand attention exactly when gemm_mode is B200_TF32X3
     // tensor parallelism (Megatron style): this rank's share of the attention heads, of the MLP
     // width and of the vocabulary; with tp_size == 1 these are the full dimensions
     int tp_size = 1, tp_rank = 0;
@@ -156,17 +159,25 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
     const int M = B * T;
     const float* P = m->params;
     const size_t* off = m->off;
-    const int rnd = m->round_operands ? ROUND_OUT_TF32 : 0;
-    const int grnd = m->round_operands ? GEMM_ROUND_OUT_TF32 : 0;
-    // bf16 modes: the operands of the GEMMs are bf16.  The weights come from the bf16 copy of the
-    // parameters; layernorm, attention and the GELU GEMM write their outputs as bf16 into the
-    // front half of the same activation buffers.  Everything between the GEMMs stays fp32.
-    const bool hb = m->gemm_mode == B200_BF16, hl = m->lmhead_mode == B200_BF16;
+    // GEMM modes.  bf16 modes: the operands of the GEMMs are bf16 (B200_BF16) or pairs of bf16 planes
+    // (B200_BF16X3: value = hi + lo); the weights come from the bf16 copies of the parameters, and
+    // layernorm, attention and the GELU GEMM write their outputs in that form into the same
+    // activation buffers (two bf16 planes take exactly the room of the fp32 tensor).  Everything
+    // between the GEMMs stays fp32.
+    const bool hb = m->gemm_mode == B200_BF16, hx = m->gemm_mode == B200_BF16X3;
+    const bool hl = m->lmhead_mode == B200_BF16, hlx = m->lmhead_mode == B200_BF16X3;
+    const bool g_tf32 = !hb && !hx;
+    const int rnd = (m->round_operands && m->gemm_mode == B200_TF32) ? ROUND_OUT_TF32 : 0;
+    const int grnd = rnd ? GEMM_ROUND_OUT_TF32 : 0;
+    // single-pass TF32 GEMMs read the rounded-to-nearest copy of the weights
+    const float* W = (m->round_operands && m->params_r && m->gemm_mode == B200_TF32) ? m->params_r : P;
+    const float* W_head = (m->round_operands && m->params_r && m->lmhead_mode == B200_TF32) ? m->params_r : P;
     const uint16_t* PH = m->params_h;
+    const uint16_t* PL = m->params_l;
     uint16_t* ln_h = reinterpret_cast<uint16_t*>(m->ln_out);
     uint16_t* atty_h = reinterpret_cast<uint16_t*>(m->atty);
     uint16_t* fch_h = reinterpret_cast<uint16_t*>(m->fch);
-    const int ln_flags = hb ? OUT_BF16 : rnd;
+    const int ln_flags = hx ? OUT_BF16X2 : (hb ? OUT_BF16 : rnd);
     // the tensor-parallel all-reduce needs the branch as a buffer of its own
     const int accum = (m->tp_size == 1) ? GEMM_ACCUM_OUT : 0;
     int st;
@@ -181,39 +192,43 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
     STEP(B200_PROF_ENCODER, launch_encoder(ctx, m->residual, tokens, P + off[0], P + off[1], B, T, C, Vp));
     STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, P + off[2], P + off[3], M, C, ln_flags));
     for (int l = 0; l < L; ++l) {
-        const float* qkvw = P + off[4] + (size_t)l * 3 * A * C;
+        const size_t o_qkvw = off[4] + (size_t)l * 3 * A * C, o_apw = off[6] + (size_t)l * C * A;
+        const size_t o_fcw = off[10] + (size_t)l * F * C, o_fpw = off[12] + (size_t)l * C * F;
         const float* qkvb = P + off[5] + (size_t)l * 3 * A;
-        const float* apw = P + off[6] + (size_t)l * C * A;
         const float* apb = P + off[7] + (size_t)l * C;
         const float* ln2w = P + off[8] + (size_t)l * C;
         const float* ln2b = P + off[9] + (size_t)l * C;
-        const float* fcw = P + off[10] + (size_t)l * F * C;
         const float* fcb = P + off[11] + (size_t)l * F;
-        const float* fpw = P + off[12] + (size_t)l * C * F;
         const float* fpb = P + off[13] + (size_t)l * C;
         // The single-pass attention kernel multiplies q, k and v on the TF32 pipe as they are.
         // Storing them rounded-to-nearest makes them exact TF32 values, so the tensor core's
         // truncation no longer shrinks every product (a systematic bias); what is left is
         // unbiased rounding noise that the softmax-weighted sums average down.  The 3xTF32
         // attention needs the unrounded values.
-        const bool att_x3 = (m->gemm_mode == B200_TF32X3) && m->qkv_small;
-        const int qkv_flags = (!att_x3 && (m->round_operands || m->gemm_mode == B200_TF32X3)) ? GEMM_ROUND_OUT_TF32 : 0;
-        if (hb) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16(ctx, m->qkv, nullptr, ln_h, PH + (qkvw - P), qkvb, M, C, 3 * A, GEMM_ROUND_OUT_TF32));
-        else STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, qkvw, qkvb, nullptr, M, C, 3 * A, qkv_flags, m->gemm_mode));
+        const bool att_x3 = (g_tf32 || hx) && (m->att_mode < 0 ? m->gemm_mode == B200_TF32X3 : m->att_mode == B200_TF32X3) && m->qkv_small;
+        const int qkv_flags = (!att_x3 && (m->round_operands || m->gemm_mode != B200_TF32)) ? GEMM_ROUND_OUT_TF32 : 0;
+        if (hx) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16x3(ctx, m->qkv, nullptr, ln_h, PH + o_qkvw, PL + o_qkvw, qkvb, M, C, 3 * A, qkv_flags));
+        else if (hb) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16(ctx, m->qkv, nullptr, ln_h, PH + o_qkvw, qkvb, M, C, 3 * A, qkv_flags));
+        else STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, W + o_qkvw, qkvb, nullptr, M, C, 3 * A, qkv_flags, m->gemm_mode));
         if (m->keep_kv) {
             const size_t per_layer = (size_t)m->max_B * m->max_T * C;
             st = launch_kv_append(ctx, m->kcache + l * per_layer, m->vcache + l * per_layer, m->qkv, B, T, C, 0, m->max_T);
             if (st != B200_OK) return st;
         }
-        if (att_x3) STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->atty, m->qkv_small, nullptr, m->qkv, B, T, A, NH));
-        else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, A, NH, hb ? OUT_BF16 : rnd));
+        if (att_x3 && hx) {
+            // the split-operand attention writes fp32: through the (free) branch buffer, then split
+            STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->branch, m->qkv_small, nullptr, m->qkv, B, T, A, NH));
+            STEP(B200_PROF_ATTENTION, launch_convert_bf16(ctx, atty_h, m->branch, (size_t)M * A, atty_h + (size_t)M * A));
+        } else if (att_x3) STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->atty, m->qkv_small, nullptr, m->qkv, B, T, A, NH));
+        else STEP(B200_PROF_ATTENTION, launch_attention(ctx, m->atty, nullptr, m->qkv, B, T, A, NH, hx ? OUT_BF16X2 : (hb ? OUT_BF16 : rnd)));
         // Without tensor parallelism the projection adds its result straight onto the residual
         // stream (its tiles leave as TMA reductions: the same single fp32 add per element that the
         // fused residual + layernorm kernel would do), and a plain layernorm follows: 50 MB less
         // traffic per block than writing the branch and reading it back.
         float* proj_out = accum ? m->residual : m->branch;
-        if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, atty_h, PH + (apw - P), apb, M, A, C, accum));
-        else STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, proj_out, m->atty, apw, apb, nullptr, M, A, C, accum, m->gemm_mode));
+        if (hx) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, atty_h, PH + o_apw, PL + o_apw, apb, M, A, C, accum));
+        else if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, atty_h, PH + o_apw, apb, M, A, C, accum));
+        else STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, proj_out, m->atty, W + o_apw, apb, nullptr, M, A, C, accum, m->gemm_mode));
         if (accum) {
             STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, ln2w, ln2b, M, C, ln_flags));
         } else {
@@ -222,16 +237,20 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
             STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
                                                  m->branch, ln2w, ln2b, M, C, ln_flags));
         }
-        if (hb) {
-            STEP(B200_PROF_GEMM_FC, launch_gemm_bf16(ctx, nullptr, fch_h, ln_h, PH + (fcw - P), fcb, M, C, F, GEMM_GELU));
-            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, fch_h, PH + (fpw - P), fpb, M, F, C, accum));
+        if (hx) {
+            STEP(B200_PROF_GEMM_FC, launch_gemm_bf16x3(ctx, nullptr, fch_h, ln_h, PH + o_fcw, PL + o_fcw, fcb, M, C, F, GEMM_GELU));
+            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, fch_h, PH + o_fpw, PL + o_fpw, fpb, M, F, C, accum));
+        } else if (hb) {
+            STEP(B200_PROF_GEMM_FC, launch_gemm_bf16(ctx, nullptr, fch_h, ln_h, PH + o_fcw, fcb, M, C, F, GEMM_GELU));
+            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, fch_h, PH + o_fpw, fpb, M, F, C, accum));
         } else {
-            STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, fcw, fcb, nullptr, M, C, F, GEMM_GELU | grnd, m->gemm_mode));
-            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, proj_out, m->fch, fpw, fpb, nullptr, M, F, C, accum, m->gemm_mode));
+            STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, W + o_fcw, fcb, nullptr, M, C, F, GEMM_GELU | grnd, m->gemm_mode));
+            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, proj_out, m->fch, W + o_fpw, fpb, nullptr, M, F, C, accum, m->gemm_mode));
         }
         const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
         const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
-        const int next_flags = (l + 1 < L) ? ln_flags : (hl ? OUT_BF16 : rnd);
+        const int head_flags = hlx ? OUT_BF16X2 : (hl ? OUT_BF16 : ((m->round_operands && m->lmhead_mode == B200_TF32) ? ROUND_OUT_TF32 : 0));
+        const int next_flags = (l + 1 < L) ? ln_flags : head_flags;
         if (accum) {
             STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, nw, nb, M, C, next_flags));
         } else {
@@ -240,12 +259,15 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
                                                  m->branch, nw, nb, M, C, next_flags));
         }
     }
-    const float* head_w = ((m->round_operands && m->wte_rounded) ? m->wte_rounded : P + off[0]) + (size_t)m->vp_row0 * C;
+    const size_t o_head = off[0] + (size_t)m->vp_row0 * C;
     const int store_period = (with_argmax && (results & RES_NO_LOGITS)) ? T : 0;
-    if (hl) STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_bf16(ctx, m->logits, nullptr, ln_h, PH + off[0] + (size_t)m->vp_row0 * C, nullptr, M, C, m->vp_local, 0,
-                                                         with_argmax ? m->argmax_keys : nullptr, c.vocab_size, store_period));
-    else STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, head_w, nullptr, nullptr, M, C, m->vp_local, 0, m->lmhead_mode,
-                                                 with_argmax ? m->argmax_keys : nullptr, c.vocab_size, store_period));
+    unsigned long long* keys = with_argmax ? m->argmax_keys : nullptr;
+    if (hlx) STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_bf16x3(ctx, m->logits, nullptr, ln_h, PH + o_head, PL + o_head, nullptr, M, C, m->vp_local, 0,
+                                                          keys, c.vocab_size, store_period));
+    else if (hl) STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_bf16(ctx, m->logits, nullptr, ln_h, PH + o_head, nullptr, M, C, m->vp_local, 0,
+                                                              keys, c.vocab_size, store_period));
+    else STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, W_head + o_head, nullptr, nullptr, M, C,
+                                                      m->vp_local, 0, m->lmhead_mode, keys, c.vocab_size, store_period));
     if (results) {
         st = launch_host_results(ctx, m->host_dst.ids ? m->host_dst.ids : m->argmax, with_argmax ? m->argmax_keys : nullptr, M,
                                  (results & RES_LAST) ? (m->host_dst.last ? m->host_dst.last : m->last_logits) : nullptr,
@@ -257,52 +279,52 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
 }
 
 // bf16 copies of the weight matrices (and of wte for the lm-head), made from the parameters as
-// they are at the first bf16 forward
-int bf16_weights_once(b200_gpt2* m) {
+// they are at the first forward of a bf16 mode; with_lo: also the plane of what the rounding dropped
+int bf16_weights_once(b200_gpt2* m, bool with_lo) {
     using namespace b200;
-    if (m->params_h_ready) return B200_OK;
+    if (m->params_h_ready && (!with_lo || m->params_l_ready)) return B200_OK;
     b200_ctx* ctx = m->ctx;
     if (!m->params_h) B200_CUDA(ctx, cudaMalloc(&m->params_h, m->n_params * sizeof(uint16_t)));
+    if (with_lo && !m->params_l) B200_CUDA(ctx, cudaMalloc(&m->params_l, m->n_params * sizeof(uint16_t)));
     const int idx[5] = {0, 4, 6, 10, 12};  // wte, qkvw, attprojw, fcw, fcprojw
     for (int i = 0; i < 5; ++i) {
-        int st = launch_convert_bf16(ctx, m->params_h + m->off[idx[i]], m->params + m->off[idx[i]], m->off[idx[i] + 1] - m->off[idx[i]]);
+        int st = launch_convert_bf16(ctx, m->params_h + m->off[idx[i]], m->params + m->off[idx[i]], m->off[idx[i] + 1] - m->off[idx[i]],
+                                     with_lo ? m->params_l + m->off[idx[i]] : nullptr);
         if (st != B200_OK) return st;
     }
     m->params_h_ready = true;
+    if (with_lo) m->params_l_ready = true;
     return B200_OK;
 }
 
-// what a forward needs done to the weights for the current modes
-int prepare_weights(b200_gpt2* m);
-
+// TF32-rounded (to nearest) copy of the weight matrices for the single-pass TF32 GEMMs; the
+// parameters themselves are never modified (the encoder, the decode step and the other modes
+// read them as loaded)
 int round_weights_once(b200_gpt2* m) {
     using namespace b200;
     if (m->weights_rounded) return B200_OK;
     b200_ctx* ctx = m->ctx;
     const size_t* off = m->off;
-    const int idx[4] = {4, 6, 10, 12};  // qkvw, attprojw, fcw, fcprojw
-    for (int i = 0; i < 4; ++i) {
-        int st = launch_round_tf32_inplace(ctx, m->params + off[idx[i]], off[idx[i] + 1] - off[idx[i]]);
+    if (!m->params_r) B200_CUDA(ctx, cudaMalloc(&m->params_r, m->n_params * sizeof(float)));
+    const int idx[5] = {0, 4, 6, 10, 12};  // wte (lm-head), qkvw, attprojw, fcw, fcprojw
+    for (int i = 0; i < 5; ++i) {
+        const size_t n = off[idx[i] + 1] - off[idx[i]];
+        B200_CUDA(ctx, cudaMemcpyAsync(m->params_r + off[idx[i]], m->params + off[idx[i]], n * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
+        int st = launch_round_tf32_inplace(ctx, m->params_r + off[idx[i]], n);
         if (st != B200_OK) return st;
     }
-    // wte also feeds the encoder, which must stay bit-exact: round a copy for the lm-head
-    const size_t n_wte = off[1] - off[0];
-    if (!m->wte_rounded) B200_CUDA(ctx, cudaMalloc(&m->wte_rounded, n_wte * sizeof(float)));
-    B200_CUDA(ctx, cudaMemcpyAsync(m->wte_rounded, m->params, n_wte * sizeof(float), cudaMemcpyDeviceToDevice, ctx->stream));
-    int st = launch_round_tf32_inplace(ctx, m->wte_rounded, n_wte);
-    if (st != B200_OK) return st;
     m->weights_rounded = true;
     return B200_OK;
 }
 
+// what a forward needs done to the weights for the current modes
 int prepare_weights(b200_gpt2* m) {
-    const bool any_bf16 = m->gemm_mode == B200_BF16 || m->lmhead_mode == B200_BF16;
-    if (any_bf16) {  // before any in-place TF32 rounding, so the copy is rounded once only
-        int st = bf16_weights_once(m);
+    const bool x3 = m->gemm_mode == B200_BF16X3 || m->lmhead_mode == B200_BF16X3;
+    if (x3 || m->gemm_mode == B200_BF16 || m->lmhead_mode == B200_BF16) {
+        int st = bf16_weights_once(m, x3);
         if (st != B200_OK) return st;
     }
-    const bool all_bf16 = m->gemm_mode == B200_BF16 && m->lmhead_mode == B200_BF16;
-    if (m->round_operands && !all_bf16) return round_weights_once(m);
+    if (m->round_operands && (m->gemm_mode == B200_TF32 || m->lmhead_mode == B200_TF32)) return round_weights_once(m);
     return B200_OK;
 }
 
@@ -380,6 +402,7 @@ int b200_gpt2_create_tp(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* 
     if (!m) return B200_ERR_CUDA;
     m->ctx = ctx; m->cfg = *cfg; m->max_B = max_B; m->max_T = max_T;
     if (!set_tp_dims(m, tp_size, tp_rank)) { delete m; return B200_ERR_SHAPE; }
+    if (tp_size > 1) m->gemm_mode = m->lmhead_mode = B200_TF32;  // the bf16 modes are not wired for sharded weights
     const size_t M = (size_t)max_B * max_T, C = cfg->channels, Vp = m->vp_local;
     const size_t A = m->attn_c, F = m->mlp_c;
     cudaError_t e = cudaSetDevice(ctx->device);
@@ -419,7 +442,7 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     for (cudaEvent_t e : m->host_done) if (e) cudaEventDestroy(e);
     if (m->h_slot_status) cudaFreeHost(m->h_slot_status);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
-    void* ptrs[] = {m->params, m->params_h, m->wte_rounded, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
+    void* ptrs[] = {m->params, m->params_h, m->params_l, m->params_r, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
                     m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->last_logits, m->kcache, m->vcache};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete m;
@@ -435,7 +458,7 @@ int b200_gpt2_load_params_host(b200_gpt2* m, const float* host_params, size_t co
     B200_CUDA(m->ctx, cudaMemcpyAsync(m->params, host_params, count * 4, cudaMemcpyHostToDevice, m->ctx->stream));
     B200_CUDA(m->ctx, cudaStreamSynchronize(m->ctx->stream));
     m->weights_rounded = false;
-    m->params_h_ready = false;
+    m->params_h_ready = m->params_l_ready = false;
     return B200_OK;
 }
 
@@ -483,20 +506,20 @@ int b200_gpt2_load_params_file(b200_gpt2* m, const char* path, size_t header_byt
     }
     fclose(f);
     m->weights_rounded = false;
-    m->params_h_ready = false;
+    m->params_h_ready = m->params_l_ready = false;
     return st;
 }
 
 int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int lmhead_mode, int use_graph) {
     if (!m) return B200_ERR_NULL;
-    if (gemm_mode < B200_TF32 || gemm_mode > B200_BF16 || lmhead_mode < B200_TF32 || lmhead_mode > B200_BF16) return B200_ERR_SHAPE;
-    // the bf16 copy of the weights follows the unsharded parameter layout
-    if ((gemm_mode == B200_BF16 || lmhead_mode == B200_BF16) && m->tp_size > 1) return B200_ERR_STATE;
+    if (gemm_mode < B200_TF32 || gemm_mode > B200_BF16X3 || lmhead_mode < B200_TF32 || lmhead_mode > B200_BF16X3) return B200_ERR_SHAPE;
+    // the bf16 modes are not wired for tensor-parallel models
+    if ((gemm_mode >= B200_BF16 || lmhead_mode >= B200_BF16) && m->tp_size > 1) return B200_ERR_STATE;
     if (m->round_operands != round_operands || m->gemm_mode != gemm_mode || m->lmhead_mode != lmhead_mode) {
         for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
         m->graphs.clear();
     }
-    if (gemm_mode == B200_TF32X3 && !m->qkv_small) {
+    if ((m->att_mode < 0 ? gemm_mode == B200_TF32X3 : m->att_mode == B200_TF32X3) && !m->qkv_small) {
         cudaSetDevice(m->ctx->device);
         B200_CUDA(m->ctx, cudaMalloc(&m->qkv_small, (size_t)m->max_B * m->max_T * 3 * m->attn_c * sizeof(float)));
     }
@@ -507,11 +530,27 @@ int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int l
     return B200_OK;
 }
 
+int b200_gpt2_set_attention_mode(b200_gpt2* m, int mode) {
+    if (!m) return B200_ERR_NULL;
+    if (mode != -1 && mode != B200_TF32 && mode != B200_TF32X3) return B200_ERR_SHAPE;
+    if (mode != m->att_mode) {
+        for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
+        m->graphs.clear();
+    }
+    m->att_mode = mode;
+    if ((mode < 0 ? m->gemm_mode == B200_TF32X3 : mode == B200_TF32X3) && !m->qkv_small) {
+        cudaSetDevice(m->ctx->device);
+        B200_CUDA(m->ctx, cudaMalloc(&m->qkv_small, (size_t)m->max_B * m->max_T * 3 * m->attn_c * sizeof(float)));
+    }
+    return B200_OK;
+}
+
 static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, int results) {
     if (!m || !tokens) return B200_ERR_NULL;
     if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
     if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
     b200_ctx* ctx = m->ctx;
+    b200_device_guard on_device(ctx);
     {
         int st = prepare_weights(m);
         if (st != B200_OK) return st;
@@ -567,6 +606,7 @@ int b200_gpt2_forward_host_enqueue(b200_gpt2* m, const int* tokens_host, int B, 
     if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
     if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
     b200_ctx* ctx = m->ctx;
+    b200_device_guard on_device(ctx);
     const size_t M = (size_t)B * T, Vp = m->vp_local;  // a tensor-parallel rank returns its slice of the vocabulary
     if (argmax_host && m->vp_local != m->cfg.padded_vocab_size) return B200_ERR_STATE;  // needs all logits
     if (!m->h_slot_status) {
@@ -630,6 +670,7 @@ int b200_gpt2_forward_host_wait(b200_gpt2* m, int slot) {
         m->h_slot_status[slot] = 0;
         // cleared behind whatever is already queued; a step enqueued meanwhile reports the word too
         B200_CUDA(ctx, cudaMemsetAsync(ctx->d_status, 0, 256, ctx->stream));
+        B200_CUDA(ctx, cudaMemsetAsync(ctx->d_split_flags, 0, ctx->split_flag_words * sizeof(unsigned int), ctx->stream));
         // a forward that gave up may have left arg-max keys behind; the next one starts from zero again
         B200_CUDA(ctx, cudaMemsetAsync(m->argmax_keys, 0, (size_t)m->max_B * m->max_T * 8, ctx->stream));
         ctx->last_error = "device status word = " + std::to_string(word);
@@ -666,6 +707,7 @@ int b200_gpt2_prefill(b200_gpt2* m, const int* tokens, int B, int T) {
     if (!m || !tokens) return B200_ERR_NULL;
     if (!m->kcache) return B200_ERR_STATE;
     if (B <= 0 || B > m->max_B || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
+    b200_device_guard on_device(m->ctx);
     {
         int st = prepare_weights(m);
         if (st != B200_OK) return st;
@@ -744,6 +786,7 @@ int b200_gpt2_decode_step(b200_gpt2* m, const int* tokens, int B, int pos) {
     if (!m->kcache) return B200_ERR_STATE;
     if (B <= 0 || B > 16 || B > m->max_B || pos < 0 || pos >= m->max_T) return B200_ERR_SHAPE;
     b200_ctx* ctx = m->ctx;
+    b200_device_guard on_device(ctx);
     int st = b200::launch_set_int(ctx, m->pos_dev, pos);
     if (st != B200_OK) return st;
     if (!m->use_graph || ctx->stream == nullptr) return enqueue_decode(m, tokens, B);
@@ -781,6 +824,7 @@ int b200_gpt2_decode_step_host(b200_gpt2* m, const int* tokens_host, int B, int 
     if (!m || !tokens_host) return B200_ERR_NULL;
     if (B <= 0 || B > 16 || B > m->max_B) return B200_ERR_SHAPE;
     b200_ctx* ctx = m->ctx;
+    b200_device_guard on_device(ctx);
     const size_t Vp = m->cfg.padded_vocab_size;
     B200_CUDA(ctx, cudaMemcpyAsync(m->tokens, tokens_host, (size_t)B * 4, cudaMemcpyHostToDevice, ctx->stream));
     int st = b200_gpt2_decode_step(m, m->tokens, B, pos);
@@ -801,6 +845,7 @@ int b200_gpt2_generate(b200_gpt2* m, const int* prompt_host, int B, int T0, int 
     if (!m->kcache) return B200_ERR_STATE;
     if (B <= 0 || B > 16 || B > m->max_B || T0 < 1 || n_new < 1 || T0 + n_new > m->max_T || top_k < 0) return B200_ERR_SHAPE;
     b200_ctx* ctx = m->ctx;
+    b200_device_guard on_device(ctx);
     const int V = m->cfg.vocab_size, Vp = m->cfg.padded_vocab_size;
     // gen holds the prompt [B,T0] and, behind it, the continuation [B,n_new]; m->argmax doubles as
     // the current column of token ids [B] (m->tokens belongs to the decode step's graph replay)
@@ -902,26 +947,38 @@ static __device__ __align__(256) float g_static_scratch[kStaticScratchFloats];
 
 namespace {
 // In host code the name g_static_scratch is only a stand-in; the device address has to be asked
-// for, once per device, with that device current.
-float* static_scratch_address(b200_ctx* ctx, int* status) {
-    static float* addr[64] = {};
-    const int dev = ctx->device & 63;
-    if (!addr[dev]) {
+// for, once per device, with that device current.  Looking it up loads this file's module, and
+// the first launch of each kernel loads that kernel's code - both may allocate device memory - so
+// the set-up also loads every kernel the static forward can launch.
+std::mutex g_static_mu;
+float* g_static_addr[64] = {};
+
+int static_prepare(b200_ctx* ctx, float** scratch) {
+    if (ctx->device < 0 || ctx->device >= 64) { ctx->last_error = "b200_gpt2_forward_static: device index beyond 63"; return B200_ERR_LIMIT; }
+    std::lock_guard<std::mutex> lock(g_static_mu);
+    if (!g_static_addr[ctx->device]) {
         int cur = -1;
-        cudaError_t e = cudaGetDevice(&cur);
-        if (e == cudaSuccess && cur != ctx->device) e = cudaSetDevice(ctx->device);
+        B200_CUDA(ctx, cudaGetDevice(&cur));
+        if (cur != ctx->device) B200_CUDA(ctx, cudaSetDevice(ctx->device));
         void* p = nullptr;
-        if (e == cudaSuccess) e = cudaGetSymbolAddress(&p, g_static_scratch);
-        if (e != cudaSuccess || !p) {
-            *status = b200_fail_cuda(ctx, e, "cudaGetSymbolAddress(g_static_scratch)");
-            return nullptr;
-        }
-        addr[dev] = static_cast<float*>(p);
+        cudaError_t e = cudaGetSymbolAddress(&p, g_static_scratch);
+        int st = (e != cudaSuccess || !p) ? b200_fail_cuda(ctx, e, "cudaGetSymbolAddress(g_static_scratch)") : B200_OK;
+        if (st == B200_OK) st = b200::preload_rowwise_kernels(ctx);
+        if (st == B200_OK) st = b200::preload_gemm_kernels(ctx);
+        if (st == B200_OK) st = b200::preload_attention_kernel(ctx);
+        if (cur != ctx->device) cudaSetDevice(cur);  // leave the caller's current device as it was
+        if (st != B200_OK) return st;
+        g_static_addr[ctx->device] = static_cast<float*>(p);
     }
-    *status = B200_OK;
-    return addr[dev];
+    if (scratch) *scratch = g_static_addr[ctx->device];
+    return B200_OK;
 }
 }  // namespace
+
+extern "C" int b200_gpt2_static_prepare(b200_ctx* ctx) {
+    if (!ctx) return B200_ERR_NULL;
+    return static_prepare(ctx, nullptr);
+}
 
 extern "C" int b200_gpt2_forward_static(b200_ctx* ctx, const b200_gpt2_config* cfg, const float* params,
                                         const int* tokens, int B, int T, float* logits) {
@@ -938,9 +995,10 @@ extern "C" int b200_gpt2_forward_static(b200_ctx* ctx, const b200_gpt2_config* c
                           std::to_string(kStaticScratchRowElems) + " (B200_STATIC_MAX_TOKEN_CHANNELS); use b200_gpt2_create / b200_gpt2_forward";
         return B200_ERR_LIMIT;
     }
-    int st;
-    float* scratch = static_scratch_address(ctx, &st);
-    if (!scratch) return st;
+    float* scratch = nullptr;
+    int st = static_prepare(ctx, &scratch);  // a no-op after b200_gpt2_static_prepare or an earlier call on this device
+    if (st != B200_OK) return st;
+    b200_device_guard on_device(ctx);  // launches go to ctx->stream, which belongs to ctx->device
     // a view of the caller's parameters and logits plus the built-in scratch; nothing is owned
     b200_gpt2 view;
     view.ctx = ctx;
@@ -950,6 +1008,7 @@ extern "C" int b200_gpt2_forward_static(b200_ctx* ctx, const b200_gpt2_config* c
     if (!set_tp_dims(&view, 1, 0)) return B200_ERR_SHAPE;
     view.params = const_cast<float*>(params);  // read only: weights are not rounded on this path
     view.round_operands = 0;                   // the arithmetic of b200_gpt2_forward with round_operands = 0
+    view.gemm_mode = view.lmhead_mode = B200_TF32;  // ... and single-pass TF32 GEMMs: no copies of the weights
     view.residual = scratch;
     view.ln_out = scratch + MC;
     view.atty = scratch + 2 * MC;

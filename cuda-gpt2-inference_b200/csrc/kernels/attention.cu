@@ -111,7 +111,8 @@ struct AttArgs {
     float scale_log2;
     int round_out;  // store TF32-rounded outputs (they feed only the next GEMM)
     int tma_out;    // T is a multiple of 128: whole tiles leave through shared memory and a TMA store
-    int out_bf16;   // out addresses bf16 elements (the next GEMM runs with bf16 operands)
+    int out_bf16;   // 1: out addresses bf16 elements (the next GEMM runs with bf16 operands); 2: two bf16 planes,
+                    // bf16(o) and, B*T rows further down, bf16(o - bf16(o)) (split operands of a bf16x3 GEMM)
     int* status;    // [0] error word; [kWorkWord], [kWorkWord+1]: work and finished-CTA counters (zero between launches)
 };
 
@@ -480,22 +481,30 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
                 softmax_bar_sync();
                 if (args.out_bf16) {
                     // 64 bf16 columns are one 128-byte row: this thread's 32 columns are chunks
-                    // 4*hf .. 4*hf+3 of row r, and the tile leaves as one {128 x 64} store
+                    // 4*hf .. 4*hf+3 of row r, and the tile leaves as one {128 x 64} store (two with
+                    // split outputs: the dropped parts are staged in the second block)
                     uint4* rowh = reinterpret_cast<uint4*>(out_s + r * 128);
+                    uint4* rowl = reinterpret_cast<uint4*>(out_s + kBlk + r * 128);
+                    const bool planes = args.out_bf16 == 2;
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
-                        uint4 pk;
-                        __nv_bfloat162 hh;
-                        hh = __floats2bfloat162_rn(o_acc[8 * i] * inv_l, o_acc[8 * i + 1] * inv_l); pk.x = *reinterpret_cast<uint32_t*>(&hh);
-                        hh = __floats2bfloat162_rn(o_acc[8 * i + 2] * inv_l, o_acc[8 * i + 3] * inv_l); pk.y = *reinterpret_cast<uint32_t*>(&hh);
-                        hh = __floats2bfloat162_rn(o_acc[8 * i + 4] * inv_l, o_acc[8 * i + 5] * inv_l); pk.z = *reinterpret_cast<uint32_t*>(&hh);
-                        hh = __floats2bfloat162_rn(o_acc[8 * i + 6] * inv_l, o_acc[8 * i + 7] * inv_l); pk.w = *reinterpret_cast<uint32_t*>(&hh);
-                        rowh[(hf * 4 + i) ^ (r & 7)] = pk;
+                        uint32_t ph[4], pl[4];
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            const float a = o_acc[8 * i + 2 * k] * inv_l, b2 = o_acc[8 * i + 2 * k + 1] * inv_l;
+                            const __nv_bfloat162 hh = __floats2bfloat162_rn(a, b2);
+                            const __nv_bfloat162 ll = __floats2bfloat162_rn(a - __low2float(hh), b2 - __high2float(hh));
+                            ph[k] = *reinterpret_cast<const uint32_t*>(&hh);
+                            pl[k] = *reinterpret_cast<const uint32_t*>(&ll);
+                        }
+                        rowh[(hf * 4 + i) ^ (r & 7)] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                        if (planes) rowl[(hf * 4 + i) ^ (r & 7)] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
                     }
                     fence_proxy_async_smem();
                     softmax_bar_sync();
                     if (threadIdx.x == 64 && ok) {
                         tma_store_2d(&tmap_out, h * HS, row_base + q0, out_s);
+                        if (planes) tma_store_2d(&tmap_out, h * HS, args.B * args.T + row_base + q0, out_s + kBlk);
                         tma_store_commit();
                     }
                 } else {
@@ -516,16 +525,22 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
                 }
                 }
             } else if (ok && t_idx < args.T && args.out_bf16) {
-                uint4* o = reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(args.out) + ((size_t)(row_base + t_idx) * args.C) + h * HS + hf * 32);
+                uint16_t* oh = reinterpret_cast<uint16_t*>(args.out) + ((size_t)(row_base + t_idx) * args.C) + h * HS + hf * 32;
+                uint4* o = reinterpret_cast<uint4*>(oh);
+                uint4* o2 = reinterpret_cast<uint4*>(oh + (size_t)args.B * args.T * args.C);
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
-                    uint4 pk;
-                    __nv_bfloat162 hh;
-                    hh = __floats2bfloat162_rn(o_acc[8 * i] * inv_l, o_acc[8 * i + 1] * inv_l); pk.x = *reinterpret_cast<uint32_t*>(&hh);
-                    hh = __floats2bfloat162_rn(o_acc[8 * i + 2] * inv_l, o_acc[8 * i + 3] * inv_l); pk.y = *reinterpret_cast<uint32_t*>(&hh);
-                    hh = __floats2bfloat162_rn(o_acc[8 * i + 4] * inv_l, o_acc[8 * i + 5] * inv_l); pk.z = *reinterpret_cast<uint32_t*>(&hh);
-                    hh = __floats2bfloat162_rn(o_acc[8 * i + 6] * inv_l, o_acc[8 * i + 7] * inv_l); pk.w = *reinterpret_cast<uint32_t*>(&hh);
-                    o[i] = pk;
+                    uint32_t ph[4], pl[4];
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) {
+                        const float a = o_acc[8 * i + 2 * k] * inv_l, b2 = o_acc[8 * i + 2 * k + 1] * inv_l;
+                        const __nv_bfloat162 hh = __floats2bfloat162_rn(a, b2);
+                        const __nv_bfloat162 ll = __floats2bfloat162_rn(a - __low2float(hh), b2 - __high2float(hh));
+                        ph[k] = *reinterpret_cast<const uint32_t*>(&hh);
+                        pl[k] = *reinterpret_cast<const uint32_t*>(&ll);
+                    }
+                    o[i] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                    if (args.out_bf16 == 2) o2[i] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
                 }
             } else if (ok && t_idx < args.T) {
                 float* o = args.out + ((size_t)(row_base + t_idx) * args.C) + h * HS + hf * 32;
@@ -566,6 +581,11 @@ attention_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __grid_cons
 
 }  // namespace
 
+int preload_attention_kernel(b200_ctx* ctx) {
+    B200_CUDA(ctx, cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AttSmem::TOTAL));
+    return B200_OK;
+}
+
 int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, int B, int T, int C,
                      int NH, int flags) {
     static bool attr_set[64] = {};
@@ -582,9 +602,9 @@ int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, in
     AttArgs a;
     a.tma_out = (T % BQ == 0) ? 1 : 0;
     CUtensorMap tmo = tm;  // not used unless whole tiles are stored
-    a.out_bf16 = (flags & OUT_BF16) ? 1 : 0;
+    a.out_bf16 = (flags & OUT_BF16X2) ? 2 : ((flags & OUT_BF16) ? 1 : 0);
     if (a.tma_out) {
-        if (a.out_bf16) st = b200_get_tensor_map_bf16(ctx, &tmo, out, (uint64_t)B * T, (uint64_t)C, (uint64_t)C, BQ, 64);
+        if (a.out_bf16) st = b200_get_tensor_map_bf16(ctx, &tmo, out, (uint64_t)B * T * a.out_bf16, (uint64_t)C, (uint64_t)C, BQ, 64);
         else st = b200_get_tensor_map(ctx, &tmo, out, (uint64_t)B * T, (uint64_t)C, (uint64_t)C, BQ, 32);
         if (st != B200_OK) return st;
     }

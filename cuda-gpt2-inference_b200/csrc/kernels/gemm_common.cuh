@@ -30,6 +30,13 @@ struct GemmArgs {
     // > 0: rows come in sequences of store_period (a multiple of 32) and only the 32-row blocks that
     // hold a sequence's last row are written; the rest of the output is wanted as arg-max only
     int store_period;
+    // out_h only: it holds two bf16 planes of [M,N], the value rounded to bf16 and, M rows further
+    // down, what that rounding dropped (again as bf16): the split operands of a bf16x3 product
+    int out_planes;
+    // CTA-pair kernel: tiles of 256 rows x tile_w columns (a ragged last one narrower, in whole units
+    // of unit_cols), K cut into k_splits slices that are tiles of their own; see gemm_tf32_pair.cu
+    int tile_w, unit_cols, k_splits;
+    unsigned int* split_flags;   // per (K slice, tile, CTA, epilogue warp): set once its sums are in the output, cleared by its reader
 };
 
 // Arg-max keys: the value as an order-preserving 32-bit integer in the high half, the inverted
@@ -60,16 +67,97 @@ __device__ __forceinline__ float argmax_dec(uint32_t k) {
 // The bias of a 32-column chunk: lane l fetches column l's (one coalesced 128-byte load per warp)
 // and the others get it by shuffle.  Fetched one chunk ahead - the first one by the caller, before
 // it waits for the accumulator - so that no chunk waits for an L2 round trip.
-__device__ __forceinline__ float gemm_bias_chunk(const GemmArgs& args, int col0, int c, int lane) {
+__device__ __forceinline__ float gemm_bias_chunk(const float* bias, int N, int col0, int c, int lane) {
     const int col = col0 + c * 32 + lane;
-    return (args.bias && col < args.N) ? __ldg(args.bias + col) : 0.f;
+    return (bias && col < N) ? __ldg(bias + col) : 0.f;
 }
 
-//   bias_first : gemm_bias_chunk(args, col0, c_begin, lane)
-template <int BN>
-__device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, const CUtensorMap* tmap_out, uint32_t tmem_acc,
+// The same for a bf16 output (no arg-max, no residual): 64 columns x 2 bytes fill one 128-byte row,
+// so the accumulator is drained two 32-column chunks at a time and every such unit leaves as one
+// {32 rows x 64 columns} TMA store.  With out_planes the unit is stored twice: the values rounded to
+// bf16 into the first plane and, through the same staging buffer once that store has read it, what
+// the rounding dropped (as bf16) into the second plane M rows further down.  c_begin, c_end even.
+__device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args, const float* bias, const CUtensorMap* tmap_out, uint32_t tmem_acc,
+                                                            int q, int lane, int row0, int col0, uint8_t* stage2, float bias_first,
+                                                            int c_begin, int c_end, int nbuf) {
+    const bool do_gelu = (args.flags & GEMM_GELU) != 0;
+    const bool planes = args.out_planes != 0;
+    if (lane == 0) tma_store_wait_read();  // the stores of the previous tile have left the staging buffers
+    __syncwarp();
+    float bias0 = bias_first;
+#pragma unroll 1
+    for (int c = c_begin; c < c_end; c += 2) {
+        const int ui = (c - c_begin) >> 1;
+        const int cbase = col0 + c * 32;
+        const float bias1 = gemm_bias_chunk(bias, args.N, col0, c + 1, lane);
+        uint32_t r0[32], r1[32];
+        tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r0);
+        tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32 + 32, r1);
+        tmem_ld_wait();
+        uint8_t* sth = stage2 + (planes ? 0 : (ui & (nbuf - 1)) * 4096);
+        if (planes ? ui > 0 : ui >= nbuf) {  // the store that last used this buffer has read it
+            if (lane == 0) { if (!planes && nbuf == 2) tma_store_wait_read_but_one(); else tma_store_wait_read(); }
+            __syncwarp();
+        }
+        uint32_t lo[32];  // the dropped parts, packed two to a register (planes only)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(h ? r1[8 * j + i] : r0[8 * j + i]);
+                if (bias) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] += __shfl_sync(0xffffffffu, h ? bias1 : bias0, 8 * j + i);
+                }
+                if (do_gelu) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
+                }
+                uint32_t pk[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const __nv_bfloat162 hh = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                    pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                    if (planes) {
+                        const __nv_bfloat162 ll = __floats2bfloat162_rn(v[2 * i] - __low2float(hh), v[2 * i + 1] - __high2float(hh));
+                        lo[h * 16 + j * 4 + i] = *reinterpret_cast<const uint32_t*>(&ll);
+                    }
+                }
+                const int chunk = h * 4 + j;
+                *reinterpret_cast<uint4*>(sth + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+            }
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        const bool in_range = cbase < args.N && row0 < args.M;
+        if (lane == 0 && in_range) {
+            tma_store_2d(tmap_out, cbase, row0, sth);
+            tma_store_commit();
+        }
+        if (planes) {
+            if (lane == 0) tma_store_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int chunk = 0; chunk < 8; ++chunk)
+                *reinterpret_cast<uint4*>(sth + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
+                    make_uint4(lo[4 * chunk], lo[4 * chunk + 1], lo[4 * chunk + 2], lo[4 * chunk + 3]);
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && in_range) {
+                tma_store_2d(tmap_out, cbase, args.M + row0, sth);
+                tma_store_commit();
+            }
+        }
+        bias0 = (c + 2 < c_end) ? gemm_bias_chunk(bias, args.N, col0, c + 2, lane) : 0.f;
+    }
+}
+
+//   bias_first : gemm_bias_chunk(bias, args.N, col0, c_begin, lane)
+__device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, const float* bias, const CUtensorMap* tmap_out, uint32_t tmem_acc,
                                                        int q, int lane, int row0, int col0, uint8_t* stage2, float bias_first,
-                                                       int c_begin = 0, int c_end = BN / 32, int nbuf = 2) {
+                                                       int c_begin, int c_end, int nbuf) {
     const bool do_gelu = (args.flags & GEMM_GELU) != 0;
     const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
     const int sub_row = lane >> 3;  // 0..3: row within a group of four
@@ -93,12 +181,16 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         if (lane == 0) tma_store_wait_read();
         __syncwarp();
     }
+    if (args.out_h) {
+        gemm_drain_accumulator_bf16(args, bias, tmap_out, tmem_acc, q, lane, row0, col0, stage2, bias_first, c_begin, c_end, nbuf);
+        return;
+    }
     float bias_next = bias_first;
 #pragma unroll 1
     for (int c = c_begin; c < c_end; ++c) {
         const int ci = c - c_begin;
         const float bias_cur = bias_next;
-        if (c + 1 < c_end) bias_next = gemm_bias_chunk(args, col0, c + 1, lane);
+        if (c + 1 < c_end) bias_next = gemm_bias_chunk(bias, args.N, col0, c + 1, lane);
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r);
         tmem_ld_wait();
@@ -120,47 +212,6 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
             }
         }
         if (skip_store) continue;
-        if (args.out_h) {
-            // bf16 output: 64 columns x 2 bytes fill one 128-byte row, so two 32-column chunks
-            // share a staging buffer and leave as one {32 rows x 64 columns} TMA store
-            uint8_t* sth = stage2 + ((ci >> 1) & (nbuf - 1)) * 4096;
-            const int cbase = col0 + c * 32;
-            if ((ci & 1) == 0 && (ci >> 1) >= nbuf) {  // the store that last used this buffer has read it
-                if (lane == 0) { if (nbuf == 2) tma_store_wait_read_but_one(); else tma_store_wait_read(); }
-                __syncwarp();
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                float v[8];
-#pragma unroll
-                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[8 * j + i]);
-                if (args.bias) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] += __shfl_sync(0xffffffffu, bias_cur, 8 * j + i);
-                }
-                if (do_gelu) {
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
-                }
-                uint4 pk;
-                __nv_bfloat162 h;
-                h = __floats2bfloat162_rn(v[0], v[1]); pk.x = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(v[2], v[3]); pk.y = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(v[4], v[5]); pk.z = *reinterpret_cast<uint32_t*>(&h);
-                h = __floats2bfloat162_rn(v[6], v[7]); pk.w = *reinterpret_cast<uint32_t*>(&h);
-                const int chunk = (ci & 1) * 4 + j;
-                *reinterpret_cast<uint4*>(sth + lane * 128 + ((chunk ^ (lane & 7)) << 4)) = pk;
-            }
-            if (ci & 1) {
-                fence_proxy_async_smem();
-                __syncwarp();
-                if (lane == 0 && cbase - 32 < args.N && row0 < args.M) {
-                    tma_store_2d(tmap_out, cbase - 32, row0, sth);
-                    tma_store_commit();
-                }
-            }
-            continue;
-        }
         uint8_t* stage = stage2 + (ci & (nbuf - 1)) * 4096;
         if (via_tma) {
             const int cbase = col0 + c * 32;
@@ -172,7 +223,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
             for (int j = 0; j < 8; ++j) {
                 float4 v = make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
                                        __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3]));
-                if (args.bias) {
+                if (bias) {
                     v.x += __shfl_sync(0xffffffffu, bias_cur, 4 * j);
                     v.y += __shfl_sync(0xffffffffu, bias_cur, 4 * j + 1);
                     v.z += __shfl_sync(0xffffffffu, bias_cur, 4 * j + 2);
@@ -200,7 +251,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         const int col = col0 + c * 32 + sub_chk * 4;
         if (col < args.N) {
             float4 b4 = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (args.bias) b4 = __ldg(reinterpret_cast<const float4*>(args.bias + col));
+            if (bias) b4 = __ldg(reinterpret_cast<const float4*>(bias + col));
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int rl = i * 4 + sub_row;
@@ -224,11 +275,15 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
     if (do_argmax && improved && my_row < args.M) atomicMax(args.argmax_keys + my_row, best_key);
 }
 
-// CTA-pair GEMM (gemm_tf32_pair.cu): 256 x BN tiles computed by two CTAs sharing one UMMA.
-// bf16 != 0: inp and weight hold bf16 elements (kind::f16); out_h as in GemmArgs.
-int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
-                          const float* bias, const float* residual, int M, int K, int N, int flags,
-                          unsigned long long* argmax_keys, int argmax_cols, int bf16 = 0, uint16_t* out_h = nullptr,
-                          int store_period = 0);
+// CTA-pair GEMM (gemm_tf32_pair.cu): 256-row tiles computed by two CTAs sharing one UMMA.
+// kind: PAIR_TF32 = fp32 operands (TF32 product); PAIR_BF16 = bf16 operands; PAIR_BF16X3 = split bf16
+// operands: inp / weight address the first (hi) plane, inp_lo / weight_lo the second.  out_h as in
+// GemmArgs (out_planes: M must be a multiple of 32).
+enum : int { PAIR_TF32 = 0, PAIR_BF16 = 1, PAIR_BF16X3 = 2 };
+int preload_gemm_pair_kernels(b200_ctx* ctx);  // the PAIR_TF32 kernel: loaded now, not at its first launch
+int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp_lo, const void* weight, const void* weight_lo,
+                     const float* bias, const float* residual, int M, int K, int N, int flags,
+                     unsigned long long* argmax_keys, int argmax_cols, int kind, uint16_t* out_h = nullptr,
+                     int out_planes = 0, int store_period = 0);
 
 }  // namespace b200

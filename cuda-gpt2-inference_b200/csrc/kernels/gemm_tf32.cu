@@ -70,9 +70,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                  const GemmArgs args) {
     using Cfg = GemmCfg<BN, X3>;
     constexpr int STAGES = Cfg::STAGES;
-#ifdef B200_GEMM_TIMING
-    const unsigned long long dbg_t0 = globaltimer_ns();
-#endif
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* smem_a = smem;                                        // [STAGES][A_BYTES]
@@ -119,11 +116,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
     griddep_wait();  // set-up done; from here on global memory is touched
-#ifdef B200_GEMM_TIMING
-    const unsigned long long dbg_t1 = globaltimer_ns();
-    unsigned long long* dbg = reinterpret_cast<unsigned long long*>(args.status + 2) + (blockIdx.x == 0 ? 0 : 8);
-    const bool dbg_on = blockIdx.x == 0 || blockIdx.x == gridDim.x - 1;
-#endif
 
     auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
         if (args.n_fastest) { n_blk = tile % args.num_n_blocks; m_blk = tile / args.num_n_blocks; }
@@ -168,9 +160,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                     // in the 3xTF32 mode the split warps signal after the TMA data has landed
                     if (!mbar_wait(X3 ? &split_bar[s] : &full_bar[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-#ifdef B200_GEMM_TIMING
-                    if (dbg_on && it == 0) dbg[2] = globaltimer_ns() - dbg_t0;
-#endif
                     const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * Cfg::A_BYTES), 16, 1024);
                     const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * Cfg::B_BYTES), 16, 1024);
 #pragma unroll
@@ -196,9 +185,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             // wait (bounded) until everything issued has retired before tensor memory is freed
             umma_commit(drain_bar);
             if (!mbar_wait(drain_bar, 0, abort_flag)) ok = false;
-#ifdef B200_GEMM_TIMING
-            if (dbg_on) { dbg[0] = dbg_t1 - dbg_t0; dbg[3] = globaltimer_ns() - dbg_t0; dbg[1] = tile_iter; }
-#endif
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
         }
     } else if (warp < 6) {
@@ -211,18 +197,15 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
             tile_coords(tile, m_blk, n_blk);
             const int acc = tile_iter & 1;
             const uint32_t acc_ph = (tile_iter >> 1) & 1;
-            const float bias_first = gemm_bias_chunk(args, n_blk * BN, 0, lane);  // on its way while the tile is computed
+            const float bias_first = gemm_bias_chunk(args.bias, args.N, n_blk * BN, 0, lane);  // on its way while the tile is computed
             if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            gemm_drain_accumulator<BN>(args, &tmap_out, tmem_base + acc * BN, q, lane, m_blk * BM + q * 32, n_blk * BN,
-                                       smem_epi + q * 2 * 4096, bias_first);
+            gemm_drain_accumulator(args, args.bias, &tmap_out, tmem_base + acc * BN, q, lane, m_blk * BM + q * 32, n_blk * BN,
+                                   smem_epi + q * 2 * 4096, bias_first, 0, BN / 32, 2);
             tc_fence_before_sync();
             mbar_arrive(&tmem_empty_bar[acc]);
         }
         if (lane == 0) tma_store_wait_all();  // the staging buffers must outlive the stores reading them
-#ifdef B200_GEMM_TIMING
-        if (dbg_on && warp == 2 && lane == 0) dbg[4] = globaltimer_ns() - dbg_t0;
-#endif
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_EPILOGUE);
     } else if (X3) {
         // ------------------------------------------------------- split warps (3xTF32)
@@ -338,8 +321,8 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
     if (bf16) use_pair = M >= 2048 && (long)((M + 255) / 256) * ((N + 255) / 256) >= ctx->num_sms / 2;
     if (pair_env >= 0) use_pair = pair_env == 1;
     if (!x3 && use_pair)
-        return launch_gemm_tf32_pair(ctx, out, static_cast<const float*>(inp), static_cast<const float*>(weight), bias, residual,
-                                     M, K, N, flags, argmax_keys, argmax_cols, bf16 ? 1 : 0, out_h, store_period);
+        return launch_gemm_pair(ctx, out, inp, nullptr, weight, nullptr, bias, residual, M, K, N, flags, argmax_keys, argmax_cols,
+                                bf16 ? PAIR_BF16 : PAIR_TF32, out_h, 0, store_period);
     GemmArgs a;
     a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
@@ -353,6 +336,10 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
     a.argmax_keys = argmax_keys;
     a.argmax_cols = argmax_cols;
     a.store_period = store_period;
+    a.out_planes = 0;
+    a.tile_w = a.unit_cols = 0;
+    a.k_splits = 1;
+    a.split_flags = nullptr;
 
     CUtensorMap ta, tb, to;
     int st;
@@ -391,10 +378,42 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
 
 }  // namespace
 
+namespace {
+template <int BN>
+int preload_one(b200_ctx* ctx) {
+    B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_kernel<BN, false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<BN, false>::SMEM));
+    return B200_OK;
+}
+}  // namespace
+
+// Loads the single-pass TF32 GEMM kernels (every tile width) now rather than at their first launch.
+int preload_gemm_kernels(b200_ctx* ctx) {
+    int st = preload_one<256>(ctx);
+    if (st == B200_OK) st = preload_one<192>(ctx);
+    if (st == B200_OK) st = preload_one<128>(ctx);
+    if (st == B200_OK) st = preload_one<96>(ctx);
+    if (st == B200_OK) st = preload_one<64>(ctx);
+    if (st == B200_OK) st = preload_gemm_pair_kernels(ctx);
+    return st;
+}
+
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      int mode, unsigned long long* argmax_keys, int argmax_cols, int store_period) {
     return launch_gemm_any(ctx, out, nullptr, inp, weight, bias, residual, M, K, N, flags, mode, argmax_keys, argmax_cols, false, store_period);
+}
+
+int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const uint16_t* inp, const uint16_t* weight_hi,
+                       const uint16_t* weight_lo, const float* bias, int M, int K, int N, int flags,
+                       unsigned long long* argmax_keys, int argmax_cols, int store_period) {
+    if (K % 8 || N % 8) { ctx->last_error = "bf16x3 GEMM: K and N must be multiples of 8"; return B200_ERR_SHAPE; }
+    if (out_planes && (M % 32 || (flags & GEMM_ACCUM_OUT))) { ctx->last_error = "bf16x3 GEMM: a split output needs M % 32 == 0 and no accumulation"; return B200_ERR_SHAPE; }
+    if (store_period && (store_period % 32 || !argmax_keys)) { ctx->last_error = "store_period: multiple of 32, with the fused arg-max only"; return B200_ERR_STATE; }
+    if (argmax_keys && (bias || flags != 0 || out_planes)) { ctx->last_error = "fused arg-max needs a plain GEMM epilogue"; return B200_ERR_STATE; }
+    if (!out_planes && !out) return B200_ERR_NULL;
+    return launch_gemm_pair(ctx, out, inp, inp + (size_t)M * K, weight_hi, weight_lo, bias, nullptr, M, K, N,
+                            flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32 | GEMM_ACCUM_OUT), argmax_keys, argmax_cols, PAIR_BF16X3, out_planes,
+                            out_planes ? 1 : 0, store_period);
 }
 
 int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,

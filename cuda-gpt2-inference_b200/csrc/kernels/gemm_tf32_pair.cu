@@ -1,16 +1,42 @@
-// TF32 GEMM on CTA pairs (tcgen05 cta_group::2): the same math and epilogue as gemm_tf32.cu
+// GEMM on CTA pairs (tcgen05 cta_group::2): the same math and epilogue as gemm_tf32.cu
 // (out = act(inp . weight^T + bias) (+ residual); reference semantics
 // kernels/matmul/1_matmul_tiling.cuh:25-54, fused bias/GELU of 9_matmul_async_cg_tf32_gelu.cuh
-// :57-84,196-212), but two CTAs of a cluster compute one 256 x BN tile together.
+// :57-84,196-212), but two CTAs of a cluster compute one 256 x W tile together.
 //
-// Why: a 128 x 256 tile computed by one CTA has to pull 96 bytes of operands per tensor-pipe
+// Why pairs: a 128 x 256 tile computed by one CTA has to pull 96 bytes of operands per tensor-pipe
 // cycle out of L2, and an SM gets about 52.  In a pair, CTA r loads rows [128r,128r+128) of
-// the inp tile and only half of the weight tile (rows [BN/2*r, BN/2*r+BN/2)); one
+// the inp tile and only half of the weight tile (rows [W/2*r, W/2*r+W/2)); one
 // tcgen05.mma.cta_group::2 (M = 256) issued by the even CTA reads both halves of the weight tile
-// from the two CTAs' shared memories, and each CTA's tensor memory receives its 128 x BN part
-// of the accumulator.  Per CTA that is (128 + BN/2) x 128 bytes per K block: 64 bytes per
-// tensor-pipe cycle at BN = 256, with six stages in flight instead of four.
-// No load is broadcast across the cluster: every CTA issues its own TMA loads.
+// from the two CTAs' shared memories, and each CTA's tensor memory receives its 128 x W part
+// of the accumulator.  No load is broadcast across the cluster: every CTA issues its own TMA loads.
+//
+// Work distribution: tiles of 256 rows x W columns (W fixed per launch, chosen on the host from a
+// cost model: a multiple of 32 up to 256; the UMMA's N, the weight box and the epilogue's chunk
+// count follow it) are dealt to the resident CTA pairs round robin - columns fastest when the
+// weight matrix stays in L2, so that the pairs working side by side share an activation tile,
+// rows fastest for the lm-head, so that they share a few weight tiles while the weights stream
+// once.  (Handing every pair an equal contiguous share of finer column units was measured and
+// dropped: it removes the partly empty last wave but makes the tiles narrower, and a narrow tile
+// re-reads its 256 activation rows for fewer columns - the L2 feed, not the tensor pipe, sets the
+// pace - QKV 54 -> 86 us, fc-proj 85 -> 139 us.)
+// Split K (only for results that are ADDED onto the output, GEMM_ACCUM_OUT): with N = 768 a
+// launch has 96 or 128 tiles for 74 pairs, i.e. a second wave that is mostly empty.  K is then cut
+// into 2-4 slices that are separate tiles, each adding its partial sum onto the output with the
+// same TMA reductions; so that the sum of an element is always formed in the same order (residual
+// + slice 0 + slice 1 ...), the epilogue warp of slice s waits - bounded - for a flag that the warp
+// which owns the same rows and columns in slice s-1 sets once its reductions have completed.
+// Slice s-1 of a tile always precedes slice s in the dealing order and all pairs are resident,
+// so the wait cannot deadlock.  A flag has one writer and one reader, who puts it back to zero:
+// the words are all zero again when the kernel ends (also under graph replay).
+//
+// Arithmetic (template MODE):
+//   PAIR_TF32    fp32 operands, tcgen05.mma kind::tf32 (the tensor core reads the upper 19 bits)
+//   PAIR_BF16    bf16 operands, kind::f16
+//   PAIR_BF16X3  both operands given as two bf16 planes, x = hi + lo with hi = bf16(x) and
+//                lo = bf16(x - hi) (16 significant bits); three kind::f16 products per K step,
+//                hi.hi + hi.lo + lo.hi, accumulated in fp32: the dropped lo.lo term and the
+//                third-order parts are below 2^-16 of the product.  Same operand bytes as fp32,
+//                1.5 x the tensor time of one TF32 pass, about 30 x smaller error.
 //
 // Per CTA (10 warps): warp 0 TMA producer, warp 1 tensor-memory allocation (+ UMMA issue in the
 // even CTA), warps 2-9 epilogue (warp w reads lane quarter w % 4; warps 2-5 drain the first half
@@ -22,7 +48,6 @@
 // Every wait is time-bounded; the two CTAs synchronise on the cluster barrier after set-up and
 // before tensor memory is freed, so neither leaves while the other can still touch its shared
 // memory.
-#include <cstdio>
 #include <cstdlib>
 #include "gemm_common.cuh"
 
@@ -31,36 +56,70 @@ namespace b200 {
 namespace {
 
 constexpr int BM = kGemmBM;  // rows per CTA; 2*BM per pair
-constexpr int BK = kGemmBK;
 constexpr int kEpiWarps = 8;  // two per tensor-memory lane quarter, each draining half of the columns
 constexpr int kThreads = 64 + 32 * kEpiWarps;
+constexpr int kMaxW = 256;    // widest tile: two accumulators of 256 columns fill tensor memory
 
-template <int BN>
+template <int MODE>
 struct PairCfg {
-    static constexpr int A_BYTES = BM * BK * 4;
-    static constexpr int B_BYTES = (BN / 2) * BK * 4;  // this CTA's half of the weight tile
-    static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+    static constexpr int PARTS = (MODE == PAIR_BF16X3) ? 2 : 1;  // operand planes per matrix
+    static constexpr int A_BYTES = BM * 128;                     // one plane: 128 rows x one 128-byte K block
+    static constexpr int B_BYTES = (kMaxW / 2) * 128;            // one plane of this CTA's half of a full-width weight tile
+    static constexpr int STAGE_BYTES = PARTS * (A_BYTES + B_BYTES);
     static constexpr int BAR_BYTES = 512;
     static constexpr int STAGES_RAW = (kGemmMaxSmem - 1024 - BAR_BYTES - kGemmEpiBytes) / STAGE_BYTES;
     static constexpr int STAGES = STAGES_RAW > 8 ? 8 : STAGES_RAW;
     static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + kGemmEpiBytes + BAR_BYTES;
-    static constexpr int TMEM_COLS = (2 * BN <= 128) ? 128 : (2 * BN <= 256 ? 256 : 512);
+    static constexpr int TMEM_COLS = 512;
+    // elements of K per 128-byte block
+    static constexpr int BKE = (MODE == PAIR_TF32) ? kGemmBK : kGemmBKH;
     static_assert(SMEM > 117 * 1024, "a second resident CTA could block in tcgen05.alloc");
     static_assert(SMEM <= kGemmMaxSmem, "shared memory over the 227 KB limit");
-    static_assert(BN % 32 == 0 && BN >= 64 && BN <= 256, "BN: multiple of 32, 64..256");
+    static_assert(STAGES >= 2, "need at least a double buffer");
 };
 
-template <int BN, bool BF16>
+// The tiles of one CTA pair, in order.  Every role of both CTAs walks the same sequence.
+struct TileWalk {
+    int cur, step, total, tiles;
+    __device__ TileWalk(const GemmArgs& a, int pair, int num_pairs)
+        : cur(pair), step(num_pairs), total(a.k_splits * a.num_m_blocks * a.num_n_blocks), tiles(a.num_m_blocks * a.num_n_blocks) {}
+    // next tile: 256 rows from m_blk * 256, `width` columns from col0, K blocks [kb0, kb1) (slice ks
+    // of K); `tile` numbers the output tile (the same for all its K slices)
+    __device__ bool next(const GemmArgs& a, int num_kb, int& m_blk, int& col0, int& width, int& kb0, int& kb1, int& ks, int& tile) {
+        if (cur >= total) return false;
+        ks = cur / tiles;
+        tile = cur - ks * tiles;
+        int n_blk;
+        if (a.n_fastest) { m_blk = tile / a.num_n_blocks; n_blk = tile - m_blk * a.num_n_blocks; }
+        else { n_blk = tile / a.num_m_blocks; m_blk = tile - n_blk * a.num_m_blocks; }
+        col0 = n_blk * a.tile_w;
+        const int rest = (a.N - col0 + a.unit_cols - 1) / a.unit_cols * a.unit_cols;
+        width = rest < a.tile_w ? rest : a.tile_w;
+        kb0 = (int)((long)num_kb * ks / a.k_splits);
+        kb1 = (int)((long)num_kb * (ks + 1) / a.k_splits);
+        cur += step;
+        return true;
+    }
+};
+
+// flag word of (K slice, output tile, CTA of the pair, epilogue warp)
+__device__ __forceinline__ unsigned int* split_flag(const GemmArgs& a, int ks, int tile, int tiles, int rank, int ew) {
+    return a.split_flags + ((size_t)(ks * tiles + tile) * 2 + rank) * kEpiWarps + ew;
+}
+
+template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
-gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                      const __grid_constant__ CUtensorMap tmap_out,
-                      const GemmArgs args) {
-    using Cfg = PairCfg<BN>;
+gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_a_lo,
+                 const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_b_lo,
+                 const __grid_constant__ CUtensorMap tmap_out, const GemmArgs args) {
+    using Cfg = PairCfg<MODE>;
     constexpr int STAGES = Cfg::STAGES;
+    constexpr int PARTS = Cfg::PARTS;
+    constexpr int BKE = Cfg::BKE;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* smem_a = smem;
-    uint8_t* smem_b = smem_a + STAGES * Cfg::A_BYTES;
+    uint8_t* smem_a = smem;                                   // [STAGES][PARTS][A_BYTES]
+    uint8_t* smem_b = smem_a + STAGES * PARTS * Cfg::A_BYTES;  // [STAGES][PARTS][B_BYTES]
     uint8_t* smem_epi = smem + STAGES * Cfg::STAGE_BYTES;
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem_epi + kGemmEpiBytes);
     uint64_t* full_bar = bars;                     // [STAGES] used in the even CTA
@@ -76,8 +135,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t rank = cluster_ctarank();  // 0 = even CTA (issues the UMMAs), 1 = its peer
     const int pair = blockIdx.x >> 1;
     const int num_pairs = gridDim.x >> 1;
-    const int num_tiles = args.num_m_blocks * args.num_n_blocks;
-    constexpr int BKE = BF16 ? kGemmBKH : BK;  // elements per 128-byte K block
     const int num_kb = (args.K + BKE - 1) / BKE;
 
     if (threadIdx.x == 0) {
@@ -89,6 +146,10 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         tma_prefetch_desc(&tmap_a);
         tma_prefetch_desc(&tmap_b);
         tma_prefetch_desc(&tmap_out);
+        if (PARTS == 2) {
+            tma_prefetch_desc(&tmap_a_lo);
+            tma_prefetch_desc(&tmap_b_lo);
+        }
     }
     if (warp == 1) {
         tmem_alloc_pair(tmem_holder, Cfg::TMEM_COLS);
@@ -101,22 +162,21 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     const uint32_t tmem_base = *tmem_holder;
     griddep_wait();  // set-up done; from here on global memory is touched
 
-    auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
-        if (args.n_fastest) { n_blk = tile % args.num_n_blocks; m_blk = tile / args.num_n_blocks; }
-        else { m_blk = tile % args.num_m_blocks; n_blk = tile / args.num_m_blocks; }
-    };
-
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
         if (lane == 0) {
             uint32_t it = 0;
             bool ok = true;
-            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-                int m_blk, n_blk;
-                tile_coords(tile, m_blk, n_blk);
+            TileWalk walk(args, pair, num_pairs);
+            int m_blk, col0, width, kb0, kb1, ks, tile;
+            const int box_b = args.tile_w >> 1;  // weight rows per load: this CTA's half of a full-width tile
+            const uint32_t tx = (uint32_t)PARTS * (Cfg::A_BYTES + box_b * 128);  // per CTA; the same in both
+            while (ok && walk.next(args, num_kb, m_blk, col0, width, kb0, kb1, ks, tile)) {
+                // a ragged last tile is narrower: its halves start closer together, the box keeps its
+                // size (the rows behind the half are loaded but not multiplied)
                 const int row_a = m_blk * 2 * BM + (int)rank * BM;
-                const int row_b = n_blk * BN + (int)rank * (BN / 2);
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int row_b = col0 + (int)rank * (width >> 1);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&empty_bar[s], ph ^ 1, abort_flag)) { ok = false; break; }
@@ -125,9 +185,12 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
                     // peer's bytes may land before that arrival; the phase cannot complete
                     // without it, and the peer cannot be a whole phase ahead because its stage is
                     // only freed by the even CTA's commit.
-                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * Cfg::STAGE_BYTES);
-                    tma_load_2d_pair(smem_a + s * Cfg::A_BYTES, &tmap_a, kb * BKE, row_a, full_leader);
-                    tma_load_2d_pair(smem_b + s * Cfg::B_BYTES, &tmap_b, kb * BKE, row_b, full_leader);
+                    if (rank == 0) mbar_arrive_expect_tx(&full_bar[s], 2 * tx);
+#pragma unroll
+                    for (int p = 0; p < PARTS; ++p) {
+                        tma_load_2d_pair(smem_a + (s * PARTS + p) * Cfg::A_BYTES, p ? &tmap_a_lo : &tmap_a, kb * BKE, row_a, full_leader);
+                        tma_load_2d_pair(smem_b + (s * PARTS + p) * Cfg::B_BYTES, p ? &tmap_b_lo : &tmap_b, kb * BKE, row_b, full_leader);
+                    }
                 }
             }
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_PRODUCER);
@@ -135,48 +198,46 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     } else if (warp == 1) {
         // ------------------------------------------- UMMA issuer (even CTA only)
         if (rank == 0 && lane == 0) {
-            constexpr uint32_t idesc = BF16 ? make_idesc_bf16(2 * BM, BN, 0) : make_idesc_tf32(2 * BM, BN, 0);
             uint32_t it = 0;
             bool ok = true;
             int tile_iter = 0;
-#ifdef B200_GEMM_TIMING
-            long long t_wait = 0, t_mma = 0, t_commit = 0, t_acc = 0, t0 = clock64(), t_first = 0;
-            const long long t_begin = t0;
-#endif
-            for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tile_iter) {
+            TileWalk walk(args, pair, num_pairs);
+            int m_blk, col0, width, kb0, kb1, ks, tile;
+            while (ok && walk.next(args, num_kb, m_blk, col0, width, kb0, kb1, ks, tile)) {
                 const int acc = tile_iter & 1;
                 const uint32_t acc_ph = (tile_iter >> 1) & 1;
+                ++tile_iter;
                 if (!mbar_wait_cluster(&tmem_empty_bar[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-#ifdef B200_GEMM_TIMING
-                { long long t1 = clock64(); t_acc += t1 - t0; t0 = t1; }
-#endif
-                const uint32_t d_tmem = tmem_base + acc * BN;
-                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const uint32_t idesc = (MODE == PAIR_TF32) ? make_idesc_tf32(2 * BM, width, 0) : make_idesc_bf16(2 * BM, width, 0);
+                const uint32_t d_tmem = tmem_base + acc * kMaxW;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
                     const uint32_t ph = (it / STAGES) & 1;
                     if (!mbar_wait(&full_bar[s], ph, abort_flag)) { ok = false; break; }
                     tc_fence_after_sync();
-#ifdef B200_GEMM_TIMING
-                    { long long t1 = clock64(); t_wait += t1 - t0; t0 = t1; if (it == 0) t_first = t1 - t_begin; }
-#endif
-                    const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * Cfg::A_BYTES), 16, 1024);
-                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * Cfg::B_BYTES), 16, 1024);
+                    const uint64_t a_desc = make_smem_desc_sw128(smem_u32(smem_a + s * PARTS * Cfg::A_BYTES), 16, 1024);
+                    const uint64_t b_desc = make_smem_desc_sw128(smem_u32(smem_b + s * PARTS * Cfg::B_BYTES), 16, 1024);
+                    if (MODE == PAIR_BF16X3) {
+                        const uint64_t al_desc = make_smem_desc_sw128(smem_u32(smem_a + (s * PARTS + 1) * Cfg::A_BYTES), 16, 1024);
+                        const uint64_t bl_desc = make_smem_desc_sw128(smem_u32(smem_b + (s * PARTS + 1) * Cfg::B_BYTES), 16, 1024);
 #pragma unroll
-                    for (int k = 0; k < BK / 8; ++k) {  // 32 bytes of K per instruction: 8 tf32 or 16 bf16
-                        if (BF16) umma_f16_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
-                        else umma_tf32_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, (kb | k) != 0);
+                        for (int k = 0; k < 4; ++k) {  // 16 bf16 = 32 bytes of K per instruction
+                            umma_f16_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb0) | k) != 0);
+                            umma_f16_ss_pair(d_tmem, a_desc + 2 * k, bl_desc + 2 * k, idesc, 1);
+                            umma_f16_ss_pair(d_tmem, al_desc + 2 * k, b_desc + 2 * k, idesc, 1);
+                        }
+                    } else {
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {  // 32 bytes of K per instruction: 8 tf32 or 16 bf16
+                            if (MODE == PAIR_BF16) umma_f16_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb0) | k) != 0);
+                            else umma_tf32_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb0) | k) != 0);
+                        }
                     }
-#ifdef B200_GEMM_TIMING
-                    { long long t1 = clock64(); t_mma += t1 - t0; t0 = t1; }
-#endif
                     // free the stage in both CTAs
                     const uint32_t e = smem_u32(&empty_bar[s]);
                     umma_commit_pair(map_to_cta(e, 0));
                     umma_commit_pair(map_to_cta(e, 1));
-#ifdef B200_GEMM_TIMING
-                    { long long t1 = clock64(); t_commit += t1 - t0; t0 = t1; }
-#endif
                 }
                 if (ok) {
                     const uint32_t f = smem_u32(&tmem_full_bar[acc]);
@@ -188,13 +249,6 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
             umma_commit_pair(map_to_cta(smem_u32(drain_bar), 0));
             if (!mbar_wait(drain_bar, 0, abort_flag)) ok = false;
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
-#ifdef B200_GEMM_TIMING
-            if (blockIdx.x == 0) {
-                long long* dbg = reinterpret_cast<long long*>(args.status + 2);
-                dbg[0] = t_wait; dbg[1] = t_mma; dbg[2] = t_commit; dbg[3] = t_acc; dbg[4] = it;
-                dbg[5] = t_first; dbg[6] = clock64() - t_begin;
-            }
-#endif
         }
     } else {
         // ---------------------------------------------------------------- epilogue
@@ -202,25 +256,55 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
         const int ew = warp - 2;  // 0..7
         // column split in units of one chunk (two for a bf16 output, whose stores take 64 columns)
         const int unit = args.out_h ? 2 : 1;
-        const int n_units = BN / 32 / unit;
-        const int c_begin = (ew < 4) ? 0 : ((n_units + 1) / 2) * unit;
-        const int c_end = (ew < 4) ? ((n_units + 1) / 2) * unit : BN / 32;
         bool ok = true;
         int tile_iter = 0;
-        for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++tile_iter) {
-            int m_blk, n_blk;
-            tile_coords(tile, m_blk, n_blk);
+        TileWalk walk(args, pair, num_pairs);
+        int m_blk, col0, width, kb0, kb1, ks, tile;
+        while (ok && walk.next(args, num_kb, m_blk, col0, width, kb0, kb1, ks, tile)) {
+            const int n_units = (width >> 5) / unit;
+            const int c_mid = ((n_units + 1) / 2) * unit;
+            const int c_begin = (ew < 4) ? 0 : c_mid;
+            const int c_end = (ew < 4) ? c_mid : (width >> 5);
             const int acc = tile_iter & 1;
             const uint32_t acc_ph = (tile_iter >> 1) & 1;
-            const float bias_first = gemm_bias_chunk(args, n_blk * BN, c_begin, lane);  // on its way while the tile is computed
+            ++tile_iter;
+            const float* bias = ks == 0 ? args.bias : nullptr;  // added once, by the first K slice
+            const float bias_first = gemm_bias_chunk(bias, args.N, col0, c_begin, lane);  // on its way while the tile is computed
             if (!mbar_wait(&tmem_full_bar[acc], acc_ph, abort_flag)) { ok = false; break; }
             tc_fence_after_sync();
-            gemm_drain_accumulator<BN>(args, &tmap_out, tmem_base + acc * BN, q, lane,
-                                       m_blk * 2 * BM + (int)rank * BM + q * 32, n_blk * BN,
+            if (ks > 0) {
+                // the partial sum of the previous K slice must be in the output before this one is added
+                if (lane == 0) {
+                    const unsigned int* f = split_flag(args, ks - 1, tile, walk.tiles, (int)rank, ew);
+                    const uint64_t t0 = globaltimer_ns();
+                    unsigned int v;
+                    while (true) {
+                        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+                        if (v != 0u || *abort_flag != 0) break;
+                        if (globaltimer_ns() - t0 > kWaitLimitNs) { *abort_flag = 1; break; }
+                        __nanosleep(100);
+                    }
+                    if (v == 0u) ok = false;
+                    else *const_cast<volatile unsigned int*>(f) = 0u;  // consumed: zero again for the next launch
+                }
+                ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+                if (!ok) break;
+            }
+            if (c_begin < c_end)
+                gemm_drain_accumulator(args, bias, &tmap_out, tmem_base + acc * kMaxW, q, lane,
+                                       m_blk * 2 * BM + (int)rank * BM + q * 32, col0,
                                        smem_epi + ew * 4096, bias_first, c_begin, c_end, 1);
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+            if (lane == 0) {
+                mbar_arrive_cluster(map_to_cta(smem_u32(&tmem_empty_bar[acc]), 0));
+                if (args.k_splits > 1 && ks + 1 < args.k_splits) {
+                    // this warp's reductions have been performed: the next slice may add its own
+                    tma_store_wait_all();
+                    __threadfence();
+                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(split_flag(args, ks, tile, walk.tiles, (int)rank, ew)), "r"(1u) : "memory");
+                }
+            }
         }
         if (lane == 0) tma_store_wait_all();  // the staging buffers must outlive the stores reading them
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_EPILOGUE);
@@ -236,18 +320,9 @@ gemm_tf32_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_c
     }
 }
 
-// Estimated cycles of one 256 x BN pair tile (per CTA): per 32-deep K block the tensor pipe
-// needs 2*BN cycles and the SM pulls about 52 bytes per cycle from L2.
-inline long pair_tile_cost(int bn, int num_kb) {
-    const long tensor = 2L * bn, feed = (128L + bn / 2) * 128 / 52;
-    return num_kb * (tensor > feed ? tensor : feed) + 1500;
-}
-
-template <int BN, bool BF16>
-int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& to, GemmArgs& a,
-                int num_pairs_max) {
-    using Cfg = PairCfg<BN>;
-    static_assert(!BF16 || BN % 64 == 0, "the bf16 epilogue stores 64 columns at a time");
+template <int MODE>
+int launch_pair(b200_ctx* ctx, const CUtensorMap* maps, GemmArgs& a, int num_pairs_max) {
+    using Cfg = PairCfg<MODE>;
     static int resident_pairs[64] = {};  // CTA pairs the device can keep resident at once
     cudaLaunchConfig_t cfg = {};
     cfg.blockDim = dim3(kThreads);
@@ -263,90 +338,113 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap& ta, const CUtensorMap& tb, con
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 2 : 1;
     if (!resident_pairs[ctx->device & 63]) {
-        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_tf32_pair_kernel<BN, BF16>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
+        B200_CUDA(ctx, cudaFuncSetAttribute(gemm_pair_kernel<MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM));
         cfg.gridDim = dim3(2 * num_pairs_max);
         int n = 0;
-        B200_CUDA(ctx, cudaOccupancyMaxActiveClusters(&n, gemm_tf32_pair_kernel<BN, BF16>, &cfg));
+        B200_CUDA(ctx, cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<MODE>, &cfg));
         if (n < 1) n = 1;
         resident_pairs[ctx->device & 63] = n < num_pairs_max ? n : num_pairs_max;
-        if (getenv("B200_GEMM_DEBUG")) fprintf(stderr, "gemm_tf32_pair_kernel<%d>: %d resident CTA pairs (occupancy query %d), %d stages\n", BN, resident_pairs[ctx->device & 63], n, Cfg::STAGES);
     }
-    // persistent: never more pairs than can be resident together, or the rest would run as a tail
-    const int tiles = a.num_m_blocks * a.num_n_blocks;
-    const int pairs = tiles < resident_pairs[ctx->device & 63] ? tiles : resident_pairs[ctx->device & 63];
+    // persistent: never more pairs than can be resident together (the K slices of a tile wait for
+    // one another, and the rest would run as a tail anyway), never more than there are tiles
+    const int total = a.k_splits * a.num_m_blocks * a.num_n_blocks;
+    const int pairs = total < resident_pairs[ctx->device & 63] ? total : resident_pairs[ctx->device & 63];
     cfg.gridDim = dim3(2 * pairs);
-    B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_tf32_pair_kernel<BN, BF16>, ta, tb, to, a));
+    B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE>, maps[0], maps[1], maps[2], maps[3], maps[4], a));
     ctx->launches++;
     return B200_OK;
 }
 
 }  // namespace
 
-int launch_gemm_tf32_pair(b200_ctx* ctx, float* out, const float* inp, const float* weight,
-                          const float* bias, const float* residual, int M, int K, int N, int flags,
-                          unsigned long long* argmax_keys, int argmax_cols, int bf16, uint16_t* out_h, int store_period) {
-    const int num_pairs_max = ctx->num_sms / 2;
-    const int num_m = (M + 2 * BM - 1) / (2 * BM);
-    const int bke = bf16 ? kGemmBKH : BK;
-    const int num_kb = (K + bke - 1) / bke;
-    const int cands[4] = {256, 192, 128, 64};
-    int best_bn = 256;
-    long best_cost = -1;
-    for (int i = 0; i < 4; ++i) {
-        const int bn = cands[i];
-        const long tiles = (long)num_m * ((N + bn - 1) / bn);
-        const long waves = (tiles + num_pairs_max - 1) / num_pairs_max;
-        const long cost = waves * pair_tile_cost(bn, num_kb);
-        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_bn = bn; }
-    }
-    // tuning hook: B200_GEMM_BN=<64|128|192|256> forces the N tile
-    static const int forced_bn = [] { const char* e = getenv("B200_GEMM_BN"); return e ? atoi(e) : 0; }();
-    if (forced_bn == 64 || forced_bn == 128 || forced_bn == 192 || forced_bn == 256) best_bn = forced_bn;
+int preload_gemm_pair_kernels(b200_ctx* ctx) {
+    B200_CUDA(ctx, cudaFuncSetAttribute(gemm_pair_kernel<PAIR_TF32>, cudaFuncAttributeMaxDynamicSharedMemorySize, PairCfg<PAIR_TF32>::SMEM));
+    return B200_OK;
+}
 
+int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp_lo, const void* weight, const void* weight_lo,
+                     const float* bias, const float* residual, int M, int K, int N, int flags,
+                     unsigned long long* argmax_keys, int argmax_cols, int kind, uint16_t* out_h, int out_planes,
+                     int store_period) {
+    const int num_pairs_max = ctx->num_sms / 2;
+    const bool half = kind != PAIR_TF32;
     GemmArgs a;
     a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
-    a.num_m_blocks = num_m;
-    a.num_n_blocks = (N + best_bn - 1) / best_bn;
-    // weight small enough to stay in L2: sweep N fastest so each inp tile is fetched once;
-    // otherwise sweep M fastest so the (smaller) inp stays resident while weight streams
-    a.n_fastest = ((size_t)N * K * (bf16 ? 2 : 4) <= (size_t)32 << 20) ? 1 : 0;
+    a.num_m_blocks = (M + 2 * BM - 1) / (2 * BM);
+    // weight small enough to stay in L2: columns fastest, so the pairs working side by side share an
+    // inp tile; otherwise rows fastest, so that they share a few weight tiles while the weights stream once
+    a.n_fastest = ((size_t)N * K * 4 <= (size_t)32 << 20) ? 1 : 0;
     a.flags = flags;
     a.status = ctx->d_status;
     a.argmax_keys = argmax_keys;
     a.argmax_cols = argmax_cols;
     a.store_period = store_period;
-
-    CUtensorMap ta, tb, to;
-    int st;
-    if (bf16) {
-        st = b200_get_tensor_map_bf16(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, kGemmBKH);
-        if (st != B200_OK) return st;
-        st = b200_get_tensor_map_bf16(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(best_bn / 2), kGemmBKH);
-        if (st != B200_OK) return st;
-    } else {
-        st = b200_get_tensor_map(ctx, &ta, inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, BK);
-        if (st != B200_OK) return st;
-        st = b200_get_tensor_map(ctx, &tb, weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, (uint32_t)(best_bn / 2), BK);
-        if (st != B200_OK) return st;
-    }
-    // the output in 32 x 32 boxes of fp32 (32 x 64 of bf16), for the epilogue's TMA stores
-    if (out_h) st = b200_get_tensor_map_bf16(ctx, &to, out_h, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 64);
-    else st = b200_get_tensor_map(ctx, &to, out, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 32);
-    if (st != B200_OK) return st;
-    if (bf16) {
-        switch (best_bn) {
-            case 256: return launch_pair<256, true>(ctx, ta, tb, to, a, num_pairs_max);
-            case 192: return launch_pair<192, true>(ctx, ta, tb, to, a, num_pairs_max);
-            case 128: return launch_pair<128, true>(ctx, ta, tb, to, a, num_pairs_max);
-            default:  return launch_pair<64, true>(ctx, ta, tb, to, a, num_pairs_max);
+    a.out_planes = out_planes;
+    a.unit_cols = out_h ? 64 : 32;
+    // Tile width and K slices: fewest estimated cycles.  Per 128-byte K block a tile needs 2*W cycles
+    // of the tensor pipe per product (three products with split operands) and (128 + W/2) * 128 bytes
+    // per operand plane out of L2, of which an SM gets about 52 per cycle; plus a fixed cost per tile
+    // (pipeline fill, the part of the epilogue that is not hidden).
+    const int bke = half ? kGemmBKH : kGemmBK;
+    const int num_kb = (K + bke - 1) / bke;
+    const int parts = kind == PAIR_BF16X3 ? 2 : 1, products = kind == PAIR_BF16X3 ? 3 : 1;
+    const bool may_split = (flags & GEMM_ACCUM_OUT) && !(flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32)) && ctx->d_split_flags != nullptr;
+    int best_w = kMaxW, best_ks = 1;
+    double best_cost = -1.0;
+    for (int w = kMaxW; w >= 64; w -= 64) {
+        const long tiles = (long)a.num_m_blocks * ((N + w - 1) / w);
+        for (int ks = 1; ks <= (may_split ? 4 : 1); ++ks) {
+            if (ks > 1 && (num_kb / ks < 6 || tiles * ks * 2 * kEpiWarps > (long)ctx->split_flag_words)) break;
+            const long waves = (tiles * ks + num_pairs_max - 1) / num_pairs_max;
+            const double tensor = 2.0 * w * products, feed = parts * (128.0 + w / 2) * 128.0 / 52.0;
+            // a slice also waits for its predecessor's sums to land and for its own before it signals
+            const double cost = waves * (((num_kb + ks - 1) / ks) * (tensor > feed ? tensor : feed) + (ks > 1 ? 3500.0 : 2000.0));
+            if (best_cost < 0 || cost < best_cost * 0.999) { best_cost = cost; best_w = w; best_ks = ks; }
         }
     }
-    switch (best_bn) {
-        case 256: return launch_pair<256, false>(ctx, ta, tb, to, a, num_pairs_max);
-        case 192: return launch_pair<192, false>(ctx, ta, tb, to, a, num_pairs_max);
-        case 128: return launch_pair<128, false>(ctx, ta, tb, to, a, num_pairs_max);
-        default:  return launch_pair<64, false>(ctx, ta, tb, to, a, num_pairs_max);
+    // tuning hooks: B200_GEMM_BN = tile width (64, 128, 192, 256), B200_GEMM_KSPLIT = K slices (1-4)
+    static const int forced_w = [] { const char* e = getenv("B200_GEMM_BN"); return e ? atoi(e) : 0; }();
+    static const int forced_ks = [] { const char* e = getenv("B200_GEMM_KSPLIT"); return e ? atoi(e) : 0; }();
+    if (forced_w == 64 || forced_w == 128 || forced_w == 192 || forced_w == 256) best_w = forced_w;
+    if (forced_ks >= 1 && forced_ks <= 4 && (forced_ks == 1 || may_split)) {
+        best_ks = forced_ks;
+        const long tiles = (long)a.num_m_blocks * ((N + best_w - 1) / best_w);
+        if (num_kb < best_ks || tiles * best_ks * 2 * kEpiWarps > (long)ctx->split_flag_words) best_ks = 1;
+    }
+    a.tile_w = best_w;
+    a.num_n_blocks = (N + best_w - 1) / best_w;
+    a.k_splits = best_ks;
+    a.split_flags = ctx->d_split_flags;
+
+    CUtensorMap maps[5];  // inp, inp (lo plane), weight, weight (lo plane), out
+    int st;
+    const uint32_t box_b = (uint32_t)(best_w / 2);
+    if (half) {
+        st = b200_get_tensor_map_bf16(ctx, &maps[0], inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, bke);
+        if (st == B200_OK) st = b200_get_tensor_map_bf16(ctx, &maps[2], weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, box_b, bke);
+        if (st != B200_OK) return st;
+        if (kind == PAIR_BF16X3) {
+            st = b200_get_tensor_map_bf16(ctx, &maps[1], inp_lo, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, bke);
+            if (st == B200_OK) st = b200_get_tensor_map_bf16(ctx, &maps[3], weight_lo, (uint64_t)N, (uint64_t)K, (uint64_t)K, box_b, bke);
+            if (st != B200_OK) return st;
+        } else {
+            maps[1] = maps[0]; maps[3] = maps[2];
+        }
+    } else {
+        st = b200_get_tensor_map(ctx, &maps[0], static_cast<const float*>(inp), (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, bke);
+        if (st == B200_OK) st = b200_get_tensor_map(ctx, &maps[2], static_cast<const float*>(weight), (uint64_t)N, (uint64_t)K, (uint64_t)K, box_b, bke);
+        if (st != B200_OK) return st;
+        maps[1] = maps[0]; maps[3] = maps[2];
+    }
+    // the output in 32 x 32 boxes of fp32 (32 x 64 of bf16, both planes in one map), for the epilogue's TMA stores
+    if (out_h) st = b200_get_tensor_map_bf16(ctx, &maps[4], out_h, (uint64_t)M * (out_planes ? 2 : 1), (uint64_t)N, (uint64_t)N, 32, 64);
+    else st = b200_get_tensor_map(ctx, &maps[4], out, (uint64_t)M, (uint64_t)N, (uint64_t)N, 32, 32);
+    if (st != B200_OK) return st;
+    switch (kind) {
+        case PAIR_BF16X3: return launch_pair<PAIR_BF16X3>(ctx, maps, a, num_pairs_max);
+        case PAIR_BF16: return launch_pair<PAIR_BF16>(ctx, maps, a, num_pairs_max);
+        default: return launch_pair<PAIR_TF32>(ctx, maps, a, num_pairs_max);
     }
 }
 

@@ -8,7 +8,9 @@ namespace b200 {
 
 // flags for the row-wise producers
 // OUT_BF16: the main output pointer addresses bf16 (16-bit) elements instead of fp32
-enum : int { ROUND_OUT_TF32 = 1, OUT_BF16 = 2 };
+// OUT_BF16X2: two bf16 planes instead, hi = bf16(y) at the pointer and lo = bf16(y - hi) one whole
+// output (rows x C elements) further on
+enum : int { ROUND_OUT_TF32 = 1, OUT_BF16 = 2, OUT_BF16X2 = 4 };
 
 int launch_layernorm(b200_ctx* ctx, float* out, float* mean, float* rstd, const float* inp,
                      const float* weight, const float* bias, int M, int C, int flags);
@@ -22,8 +24,8 @@ int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, 
 int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N);
 // dst[0..n) = src_view[0..n): src_view is the device view of a pinned host buffer (16-byte aligned)
 int launch_fetch_ints(b200_ctx* ctx, int* dst, const int* src_view, int n);
-// out[i] = bf16(in[i]), round to nearest even; N a multiple of 4
-int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N);
+// out[i] = bf16(in[i]), round to nearest even; N a multiple of 4.  lo (may be null): lo[i] = bf16(in[i] - out[i])
+int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N, uint16_t* lo = nullptr);
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
 // one draw per row from softmax(logits / temperature) (Gumbel-max; temperature <= 0: arg-max);
 // row r uses the noise stream stream0 + r of the seed; 0 < top_k < V: only among the top_k largest logits;
@@ -31,6 +33,11 @@ int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int 
 int launch_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld, float temperature,
                        unsigned int seed, unsigned int stream0, int top_k = 0, float top_p = 0.f);
 int launch_wait_timeout_probe(b200_ctx* ctx, unsigned long long limit_ns);
+// Load the kernels of the single-pass TF32 forward now (CUDA loads a kernel lazily at its first use,
+// which may allocate device memory): for callers that must not allocate later.
+int preload_rowwise_kernels(b200_ctx* ctx);
+int preload_gemm_kernels(b200_ctx* ctx);
+int preload_attention_kernel(b200_ctx* ctx);
 
 // epilogue flags of the GEMM
 // GEMM_ACCUM_OUT: out += result instead of out = result (fp32 output without a residual operand: the
@@ -45,6 +52,14 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
 int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,
                      const float* bias, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0);
+// The same product from split bf16 operands (three kind::f16 products per K step, hi.hi + hi.lo +
+// lo.hi: 16 significant bits per operand).  inp holds two bf16 planes of [M,K]: hi = bf16(x) and,
+// M*K elements further on, lo = bf16(x - hi); weight_hi / weight_lo [N,K] likewise.  The result goes
+// to out (fp32; GEMM_ACCUM_OUT adds onto it) or, if out_planes is not null, there as two bf16 planes
+// of [M,N] in the same split form.  flags: GEMM_GELU, GEMM_ACCUM_OUT.  K and N multiples of 8.
+int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const uint16_t* inp, const uint16_t* weight_hi,
+                       const uint16_t* weight_lo, const float* bias, int M, int K, int N, int flags,
+                       unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0);
 // (store_period > 0, with the fused arg-max: rows come in sequences of store_period and only the
 // 32-row blocks holding a sequence's last row are written to out)
 // After the lm-head: turns the keys left by a GEMM with fused arg-max into column indices and

@@ -87,7 +87,9 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
     float4* o = reinterpret_cast<float4*>(out + (size_t)row * C);
     uint2* oh = reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + (size_t)row * C);  // OUT_BF16
     const bool rnd = (flags & ROUND_OUT_TF32) != 0;
-    const bool as_bf16 = (flags & OUT_BF16) != 0;
+    const bool as_bf16 = (flags & (OUT_BF16 | OUT_BF16X2)) != 0;
+    const bool planes = (flags & OUT_BF16X2) != 0;
+    uint2* ol = oh + (size_t)M * C4;  // OUT_BF16X2: the plane of the dropped parts
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
         const int c = lane + i * 32;
@@ -99,8 +101,13 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
             y.z = (v[i].z - m) * r * w.z + b.z;
             y.w = (v[i].w - m) * r * w.w + b.w;
             if (as_bf16) {
-                const __nv_bfloat162 lo = __floats2bfloat162_rn(y.x, y.y), hi = __floats2bfloat162_rn(y.z, y.w);
-                oh[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                const __nv_bfloat162 p0 = __floats2bfloat162_rn(y.x, y.y), p1 = __floats2bfloat162_rn(y.z, y.w);
+                oh[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1));
+                if (planes) {
+                    const __nv_bfloat162 q0 = __floats2bfloat162_rn(y.x - __low2float(p0), y.y - __high2float(p0));
+                    const __nv_bfloat162 q1 = __floats2bfloat162_rn(y.z - __low2float(p1), y.w - __high2float(p1));
+                    ol[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&q0), *reinterpret_cast<const uint32_t*>(&q1));
+                }
                 continue;
             }
             if (rnd) { y.x = round_tf32(y.x); y.y = round_tf32(y.y); y.z = round_tf32(y.z); y.w = round_tf32(y.w); }
@@ -159,12 +166,17 @@ __global__ void gelu_kernel(float4* __restrict__ out, const float4* __restrict__
     if (i < n) out_s[i] = gelu_tanh(inp_s[i]);
 }
 
-__global__ void convert_bf16_kernel(uint2* __restrict__ out, const float4* __restrict__ in, size_t n4) {
+__global__ void convert_bf16_kernel(uint2* __restrict__ out, const float4* __restrict__ in, size_t n4, uint2* __restrict__ dropped) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
         const float4 x = in[i];
-        const __nv_bfloat162 lo = __floats2bfloat162_rn(x.x, x.y), hi = __floats2bfloat162_rn(x.z, x.w);
-        out[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+        const __nv_bfloat162 p0 = __floats2bfloat162_rn(x.x, x.y), p1 = __floats2bfloat162_rn(x.z, x.w);
+        out[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1));
+        if (dropped) {  // what the rounding dropped, again as bf16 (x - bf16(x) is exact in fp32)
+            const __nv_bfloat162 q0 = __floats2bfloat162_rn(x.x - __low2float(p0), x.y - __high2float(p0));
+            const __nv_bfloat162 q1 = __floats2bfloat162_rn(x.z - __low2float(p1), x.w - __high2float(p1));
+            dropped[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&q0), *reinterpret_cast<const uint32_t*>(&q1));
+        }
     }
 }
 
@@ -491,6 +503,22 @@ int launch_gelu(b200_ctx* ctx, float* out, const float* inp, size_t N) {
     return B200_OK;
 }
 
+// Loads the code of the forward's row-wise kernels now (CUDA loads a kernel's module lazily, at its
+// first use, and that may allocate device memory).
+int preload_rowwise_kernels(b200_ctx* ctx) {
+    cudaFuncAttributes fa;
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, encoder_kernel));
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, layernorm_rows_kernel<2, false>));
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, layernorm_rows_kernel<4, false>));
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, layernorm_rows_kernel<6, false>));
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, layernorm_rows_kernel<8, false>));
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, layernorm_rows_kernel<10, false>));
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, layernorm_rows_kernel<13, false>));
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, layernorm_rows_kernel<16, false>));
+    B200_CUDA(ctx, cudaFuncGetAttributes(&fa, layernorm_rows_kernel<32, false>));
+    return B200_OK;
+}
+
 int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N) {
     const size_t n4 = N / 4;
     const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
@@ -500,11 +528,12 @@ int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N) {
     return B200_OK;
 }
 
-int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N) {
+int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N, uint16_t* lo) {
     if (N % 4) { ctx->last_error = "bf16 conversion: element count must be a multiple of 4"; return B200_ERR_SHAPE; }
     const size_t n4 = N / 4;
     const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
-    convert_bf16_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<uint2*>(out), reinterpret_cast<const float4*>(in), n4);
+    convert_bf16_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<uint2*>(out), reinterpret_cast<const float4*>(in), n4,
+                                                       reinterpret_cast<uint2*>(lo));
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

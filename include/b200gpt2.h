@@ -15,7 +15,15 @@
  *     aborts the process with a message on a precondition failure.
  *
  * Threading: a context is owned by one host thread at a time.  Nothing here synchronises
- * the stream unless stated.  All pointers must be 16-byte aligned.
+ * the stream unless stated.  All pointers must be 16-byte aligned.  The b200_gpt2_* calls make the
+ * context's device current while they run and put the caller's device back; the operator calls
+ * expect it to be current already (as the reference's do).
+ *
+ * Device-side waits: every wait inside a kernel gives up after 2 s; the kernel then returns and
+ * leaves a code in the context's status word.  b200_ctx_sync_check (or b200_gpt2_forward_host_wait)
+ * reports it as B200_ERR_TIMEOUT and clears the status area, which also holds the attention
+ * kernel's work counters and the GEMM's hand-over flags: after such an error call one of the two
+ * before the context is used again.
  */
 #ifndef B200GPT2_H
 #define B200GPT2_H
@@ -44,7 +52,10 @@ enum {
 enum {
     B200_TF32 = 0,           /* one tcgen05 kind::tf32 pass (default)               */
     B200_TF32X3 = 1,         /* three-term split (big*big + small*big + big*small)  */
-    B200_BF16 = 2            /* bf16 operands (tcgen05 kind::f16), fp32 accumulation: model option only */
+    B200_BF16 = 2,           /* bf16 operands (tcgen05 kind::f16), fp32 accumulation: model option only */
+    B200_BF16X3 = 3          /* every fp32 operand as two bf16 terms (16 significant bits), three
+                                kind::f16 products per K step, fp32 accumulation: model option and
+                                b200_matmul_forward_bf16x3 */
 };
 
 /* GEMM epilogue activation */
@@ -79,7 +90,10 @@ const char* b200_ctx_last_error(const b200_ctx* ctx);
  * matmul_forward_cublas + add_bias (2_matmul_cublas.cuh:7-61), matmul_forward_ptx_2d
  * (5_matmul_ptx_2d.cuh:165-173) and matmul_forward_async_cg_tf32_gelu
  * (9_matmul_async_cg_tf32_gelu.cuh:237-246, whose `bool is_gelu` is `act`).
- * bias and residual may be NULL.  Preconditions: C % 4 == 0, OC % 4 == 0. */
+ * bias and residual may be NULL.  residual == out (the same pointer) adds the product onto out in
+ * place: the tiles leave as element-wise fp32 reductions, one add per element, which is how the
+ * driver puts the two projections of a block onto the residual stream.
+ * Preconditions: C % 4 == 0, OC % 4 == 0. */
 int b200_matmul_forward(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                         const float* bias, int B, int T, int C, int OC, int act,
                         const float* residual, int mode);
@@ -93,6 +107,21 @@ int b200_matmul_forward_bf16(b200_ctx* ctx, float* out, uint16_t* out_bf16, cons
                              const uint16_t* weight, const float* bias, int B, int T, int C, int OC, int act);
 /* out[i] = bf16(inp[i]), round to nearest even; n % 4 == 0. */
 int b200_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* inp, size_t n);
+
+/* The same product at close to fp32 precision on the bf16 tensor path (B200_BF16X3; like the
+ * reference's bf16 experiment, README.md:124-128, but with every fp32 operand carried as TWO bf16
+ * terms): x = hi + lo, hi = bf16(x), lo = bf16(x - hi), 16 significant bits; the kernel adds
+ * hi.hi + hi.lo + lo.hi per K step in fp32.  inp_split holds the two planes of inp one after the
+ * other ([2][B,T,C] bf16, as written by b200_split_bf16 with lo = hi + B*T*C); weight_hi /
+ * weight_lo are the planes of weight[OC,C].  The result goes to out (fp32; accumulate != 0 adds
+ * it onto out, as residual == out does in b200_matmul_forward) or, when out_split is not NULL, to
+ * out_split in the same two-plane form ([2][B,T,OC]; needs B*T % 32 == 0, no accumulation) so that
+ * it can feed the next product.  bias (fp32) may be NULL.  Preconditions: C % 8 == 0, OC % 8 == 0. */
+int b200_matmul_forward_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_split, const uint16_t* inp_split,
+                               const uint16_t* weight_hi, const uint16_t* weight_lo, const float* bias, int B, int T,
+                               int C, int OC, int act, int accumulate);
+/* hi[i] = bf16(inp[i]) (round to nearest even), lo[i] = bf16(inp[i] - hi[i]); n % 4 == 0. */
+int b200_split_bf16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* inp, size_t n);
 
 /* Causal multi-head attention on the packed buffer inp[B,T,3C] -> out[B,T,C].
  * Replaces attention_forward_cublas (kernels/attention/1_attention_cublas.cuh:31-36),
@@ -198,18 +227,27 @@ int b200_gpt2_load_params_host(b200_gpt2* model, const float* host_params, size_
  * cannot be opened or read is B200_ERR_STATE).  The copy goes through pinned staging buffers in
  * 32 MB pieces.  Not for tensor-parallel models, whose parameters are stored sharded. */
 int b200_gpt2_load_params_file(b200_gpt2* model, const char* path, size_t header_bytes);
-/* Options (defaults: round_operands 1, both modes B200_TF32, use_graph 0).
- * round_operands != 0 makes every producer whose output feeds only a GEMM store
- * TF32-round-to-nearest values and, on the next forward, rounds the four linear weight
- * matrices once IN PLACE (the lm-head uses a rounded copy of wte; wte itself is untouched so
- * the encoder stays bit-exact).  The tensor core truncates raw fp32 operands, which shrinks
- * every product; rounding to nearest first removes that bias (logit error 4.6e-4 rms instead
- * of 7.9e-4 on GPT-2 124M).  gemm_mode applies to all GEMMs; lmhead_mode to the lm-head alone;
- * B200_TF32X3 ignores operand rounding; with gemm_mode == B200_TF32X3 attention also runs with
- * split operands (b200_attention_forward_x3; its scratch buffer is allocated by this call).  use_graph != 0 replays the forward from a CUDA graph after the
- * first call of a given (B,T). */
+/* Options (defaults: round_operands 1, both modes B200_BF16X3 - B200_TF32 on a tensor-parallel
+ * model -, use_graph 0).
+ * round_operands != 0 makes every producer whose output feeds only a single-pass TF32 GEMM store
+ * TF32-round-to-nearest values and makes those GEMMs read a rounded copy of the weight
+ * matrices (made on the next forward; the parameters themselves are never modified, so the
+ * encoder stays bit-exact and the decode step sees the weights as loaded).  The tensor core
+ * truncates raw fp32 operands, which shrinks every product; rounding to nearest first removes
+ * that bias (logit error 4.6e-4 rms instead of 7.9e-4 on GPT-2 124M).  gemm_mode applies to all
+ * GEMMs; lmhead_mode to the lm-head alone.  B200_TF32X3 ignores operand rounding; with gemm_mode ==
+ * B200_TF32X3 attention also runs with split operands (b200_attention_forward_x3; its scratch
+ * buffer is allocated by this call).  B200_BF16 / B200_BF16X3 keep bf16 copies of the weight
+ * matrices (made on the next forward) and have the layernorms, the attention and the GELU GEMM
+ * write their outputs as bf16 / as two bf16 planes; attention itself stays single-pass TF32 on
+ * rounded q, k, v unless b200_gpt2_set_attention_mode says otherwise.  use_graph != 0 replays the
+ * forward from a CUDA graph after the first call of a given (B,T). */
 int b200_gpt2_set_options(b200_gpt2* model, int round_operands, int gemm_mode, int lmhead_mode,
                           int use_graph);
+/* Attention arithmetic: -1 (default) follows gemm_mode as described above, B200_TF32 forces the
+ * single-pass kernel, B200_TF32X3 the split-operand one (with gemm_mode B200_TF32, B200_TF32X3 or
+ * B200_BF16X3; allocates the scratch buffer on first use). */
+int b200_gpt2_set_attention_mode(b200_gpt2* model, int mode);
 /* tokens: device int32 [B,T].  Asynchronous.  Logits: device [B,T,Vp], owned by the model. */
 int b200_gpt2_forward(b200_gpt2* model, const int* tokens, int B, int T);
 float* b200_gpt2_logits(b200_gpt2* model);
@@ -244,6 +282,7 @@ int b200_gpt2_forward_host_wait(b200_gpt2* model, int slot);
  * the first B rows of the model's logits buffer ([B,Vp]).  A step reads every weight and the
  * used part of the cache once, so it is bound by HBM bandwidth; it runs on the fp32 FMA pipe
  * (no TF32 rounding anywhere).  Starting at pos = 0 with an empty cache is allowed.
+ * The decode step always reads the parameters as loaded, whatever gemm_mode says.
  * b200_gpt2_decode_step_host: tokens from the host, logits [B,Vp] and / or arg-max ids [B] back;
  * synchronises.  All calls are asynchronous on the context's stream unless stated. */
 int b200_gpt2_enable_kv_cache(b200_gpt2* model);
@@ -320,16 +359,25 @@ void* b200_gpt2_activation(b200_gpt2* model, const char* name);
  *
  * Limit: B*T*C <= B200_STATIC_MAX_TOKEN_CHANNELS (e.g. GPT-2 124M with B=4, T=64); larger
  * problems return B200_ERR_LIMIT (text in b200_ctx_last_error) and must use b200_gpt2_create.
- * The arithmetic is that of b200_gpt2_forward with round_operands = 0 (the caller's weights are
- * never modified), bit for bit.
+ * The arithmetic is that of b200_gpt2_forward with round_operands = 0 and both modes B200_TF32
+ * (single-pass TF32 GEMMs straight from the caller's weights: the other modes need copies of
+ * the weights, i.e. allocations), bit for bit.
  *
- * The first call on a device looks up the scratch array's device address
- * (cudaGetSymbolAddress); make that first call before any stream capture begins.
+ * Set-up: b200_gpt2_static_prepare(ctx), called once per device while allocation is still allowed,
+ * looks up the scratch array's device address (cudaGetSymbolAddress) and loads the code of every
+ * kernel this forward can launch.  Both steps can make the CUDA runtime allocate device memory
+ * (it loads a kernel's module lazily, at first use), which is exactly what these callers cannot
+ * have later; after the set-up b200_gpt2_forward_static allocates nothing, implicitly or
+ * explicitly.  Without it the first b200_gpt2_forward_static on a device does the same set-up
+ * itself - make that first call (or the set-up) before any stream capture begins.  The set-up is
+ * serialised by a lock, so contexts of several host threads may race to it.
  * All calls on a device share the one scratch array: it keeps the previous call's contents
  * (nothing needs clearing - every part is rewritten before it is read), and two calls that
  * overlap on the GPU (different streams or contexts of the same device) race on it.
- * Asynchronous on the context's stream, like b200_gpt2_forward. */
+ * Asynchronous on the context's stream, like b200_gpt2_forward; the caller's current device is
+ * left as it was.  Devices 0-63. */
 #define B200_STATIC_MAX_TOKEN_CHANNELS 196608 /* 256 tokens x 768 channels */
+int b200_gpt2_static_prepare(b200_ctx* ctx);
 int b200_gpt2_forward_static(b200_ctx* ctx, const b200_gpt2_config* cfg, const float* params,
                              const int* tokens, int B, int T, float* logits);
 

@@ -81,6 +81,18 @@ ORACLE_API int oracle_num_threads(void) {
 #endif
 }
 
+/* Sets the OpenMP team size of every later call (a launcher may have exported
+ * OMP_NUM_THREADS=1 before this library was loaded); returns the size in effect. */
+ORACLE_API int oracle_set_num_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* ------------------------------------------------------------------------- */
 /* encoder_forward: out[b,t,:] = wte[tok[b,t],:] + wpe[t,:]                  */
 /* The reference has no source for it (README.md:10 names the step; 0.4 ms in */

@@ -67,6 +67,8 @@ def lib() -> C.CDLL:
         _lib.oracle_gpt2_param_offsets.restype = C.c_size_t
         _lib.oracle_gpt2_forward.restype = C.c_int
         _lib.oracle_num_threads.restype = C.c_int
+        _lib.oracle_set_num_threads.restype = C.c_int
+        _lib.oracle_set_num_threads.argtypes = [C.c_int]
     return _lib
 
 
@@ -83,6 +85,21 @@ def _f32(a) -> np.ndarray:
 
 def num_threads() -> int:
     return int(lib().oracle_num_threads())
+
+
+def set_num_threads(n: int) -> int:
+    """OpenMP team size for every later call (launchers such as torch.distributed.run export
+    OMP_NUM_THREADS=1, which would otherwise put the whole forward on one core)."""
+    return int(lib().oracle_set_num_threads(int(n)))
+
+
+def use_all_host_threads() -> int:
+    """Team size = the cores this process may run on; returns it."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    return set_num_threads(max(1, n))
 
 
 def fill_normal(shape, seed: int, stream: int = 0, mean: float = 0.0, std: float = 1.0) -> np.ndarray:

@@ -35,9 +35,9 @@ def test_gpt2_124m_b4_t64_matches_oracle(pkg, orc, ctx):
     model.forward_host(tokens, B, T, logits_host=logits, last_logits_host=last, argmax_host=amax)
     # encoder output is kept in no buffer after the forward (the residual stream is updated in
     # place), so it is checked on its own through the same entry point the driver uses
-    assert np.abs(logits - want).max() < 2e-2
+    assert np.abs(logits - want).max() < 2e-3
     agree = (logits[..., :cfg.vocab_size].argmax(-1) == want[..., :cfg.vocab_size].argmax(-1)).mean()
-    assert agree >= 0.99, agree  # 256 positions: one near-tie flip is 0.4 %; see the T=1024 test
+    assert agree >= 0.996, agree  # 256 positions: at most one near-tie flip; the 99.9 % bar is held on 8192 positions below
     assert np.array_equal(last, logits[:, -1, :])
     assert np.array_equal(amax, logits[..., :cfg.vocab_size].argmax(-1))
     model.close()
@@ -52,35 +52,42 @@ def _compare(got, want, V):
     return float(err.max()), float(np.sqrt((err ** 2).mean())), 1.0 - len(miss) / len(a_want), gaps
 
 
-@pytest.mark.parametrize("mode", ["tf32", "tf32x3"])
+@pytest.mark.parametrize("mode", ["bf16x3", "tf32", "bf16x3_att3", "tf32x3"])
 def test_gpt2_124m_full_length_sequences(pkg, orc, ctx, mode):
-    """T = 1024 as in the benchmark configuration (B=8, T=1024); the oracle is run on two of the
-    sequences, which is exact because sequences are independent.
+    """The benchmark configuration (B=8, T=1024) against the oracle on ALL eight sequences
+    (sequences are independent, so the oracle runs them one at a time).
 
     Stated tolerances: logits within 2e-2 max-abs of the fp32 forward and >= 99.9 % top-1
     agreement.  With seeded random-init weights the logits are nearly tied (the oracle's own
-    top-1/top-2 margin is below 5.4e-4 at 0.1 % and below 1.3e-3 at 1 % of the positions), so a
-    single TF32 pass, whose logit error is 4.6e-4 rms, physically cannot hold 99.9 %: it measures
-    99.4-100 % per sequence.  The single-pass mode is therefore held to the max-abs bar, to
-    >= 99 % agreement and to the property that it only ever differs from the oracle on such
-    near-ties; the 3xTF32 mode (split-operand GEMMs and attention: 1.3e-5 rms, 8e-5 max) is held to
-    the full 99.9 % bar and to 1e-4 of the largest logit."""
+    top-1/top-2 margin is below 5.4e-4 at 0.1 % and below 1.3e-3 at 1 % of the positions), so the
+    agreement is a direct reading of the logit error:
+      bf16x3       the default: GEMM operands carried as two bf16 terms (16 significant bits), TF32
+                   attention; logit error about 1.1e-4 rms (what is left comes from the attention's
+                   P.V product): holds the 99.9 % bar over the 8192 positions
+      tf32         one TF32 pass per GEMM, round-to-nearest operands: 4.6e-4 rms, which flips 0.2-0.3 %
+                   of the arg-maxes; held to max-abs, to >= 99 % and to "only near-ties are missed"
+      bf16x3_att3  the same with split-operand attention, and
+      tf32x3       3xTF32 GEMMs and attention: fp32-level logits (about 1e-5 rms), 99.9 % per
+                   sequence and 1e-4 of the largest logit."""
     import torch
+    assert pkg.DEFAULT_MODE_NAME == "bf16x3"
     B, T = 8, 1024
     cfg, ocfg, params, model = _make(pkg, orc, ctx, dict(), B, T)
-    if mode == "tf32":
-        model.set_options(round_operands=1)
-    else:
-        model.set_options(round_operands=0, gemm_mode=pkg.B200_TF32X3, lmhead_mode=pkg.B200_TF32X3)
+    if mode != pkg.DEFAULT_MODE_NAME:  # the default is what a fresh model runs
+        model.set_options(**pkg.MODES[mode])
     tokens = orc.fill_tokens((B, T), seed=4321, vocab=cfg.vocab_size)
     d_tok = torch.from_numpy(tokens).cuda()
     torch.cuda.synchronize()
     logits = model.forward(d_tok, B, T)
     ctx.sync_check()
     assert torch.isfinite(logits).all()
-    for b in (0, B - 1):
+    got_all = logits.cpu().numpy()
+    model.close()
+    misses = 0
+    for b in range(B):
         want = orc.gpt2_forward(params, ocfg, tokens[b:b + 1], precise=False)[0]
-        mx, rms, agree, gaps = _compare(logits[b].cpu().numpy(), want, cfg.vocab_size)
+        mx, rms, agree, gaps = _compare(got_all[b], want, cfg.vocab_size)
+        misses += len(gaps)
         print(f"{mode} seq {b}: max-abs {mx:.3e}, rms {rms:.3e}, top-1 agreement {agree:.5f}, "
               f"largest oracle margin among the misses {gaps.max() if len(gaps) else 0:.2e}")
         assert mx < 2e-2
@@ -88,11 +95,18 @@ def test_gpt2_124m_full_length_sequences(pkg, orc, ctx, mode):
             assert agree >= 0.99, agree
             assert rms < 7e-4
             assert len(gaps) == 0 or gaps.max() < 4e-3, "a top-1 miss that is not a near-tie"
+        elif mode == "bf16x3":
+            assert agree >= 0.997, agree
+            assert rms < 2e-4
+            assert len(gaps) == 0 or gaps.max() < 1e-3, "a top-1 miss that is not a near-tie"
         else:
             assert agree >= 0.999, agree
             assert rms < 5e-5
             assert mx < 1e-4 * np.abs(want).max()  # "within 1e-4 relative error"
-    model.close()
+    total = 1.0 - misses / (B * T)
+    print(f"{mode}: top-1 agreement over all {B * T} positions {total:.5f} ({misses} misses)")
+    if mode != "tf32":
+        assert total >= 0.999, total
 
 
 def test_batch_rows_are_independent_and_deterministic(pkg, orc, ctx):

@@ -345,3 +345,86 @@ def test_matmul_bf16_matches_oracle_on_rounded_operands(ctx, dev, orc, B, T, C, 
         got = dev.back(out).reshape(B * T, OC)[rows]
         assert np.isfinite(dev.back(out)).all(), "unwritten or non-finite outputs"
         assert np.abs(got - want).max() <= 2e-5 * scale, (np.abs(got - want).max(), scale)
+
+
+# ------------------------------------------------------------------ split bf16 (bf16x3) GEMM
+def _bits_to_f32(bits):
+    return (bits.astype(np.uint32) << 16).view(np.float32)
+
+
+def _split_bf16(a):
+    """x -> (hi, lo) bit patterns with hi = bf16(x), lo = bf16(x - hi), as the library defines them."""
+    hi_f, hi_b = _bf16_round(a)
+    _, lo_b = _bf16_round((np.ascontiguousarray(a, np.float32) - hi_f).astype(np.float32))
+    return hi_b, lo_b
+
+
+def test_split_bf16_matches_its_definition(ctx, dev, orc):
+    import torch
+    x = orc.fill_normal((3, 1000), 401)
+    x[0, :6] = [1.00390625, -1.01171875, 0.0, 3.0e38, -1e-30, 1.0]
+    hi = torch.empty((3, 1000), dtype=torch.int16, device="cuda")
+    lo = torch.empty((3, 1000), dtype=torch.int16, device="cuda")
+    ctx.split_bf16(hi, lo, dev.to(x), x.size)
+    ctx.sync_check()
+    hb, lb = _split_bf16(x)
+    assert np.array_equal(hi.cpu().numpy().view(np.uint16), hb)
+    assert np.array_equal(lo.cpu().numpy().view(np.uint16), lb)
+    # the two terms carry 16 significant bits of x
+    back = _bits_to_f32(hb) + _bits_to_f32(lb)
+    ok = np.abs(x) < 1e30
+    assert (np.abs(back - x)[ok] <= np.abs(x)[ok] * 2.0 ** -16).all()
+
+
+@pytest.mark.parametrize("B,T,C,OC,has_bias,act,mode", [
+    (1, 128, 64, 64, False, 0, "plain"),
+    (2, 192, 768, 2304, True, 0, "plain"),      # ragged M (384 rows), QKV shape
+    (4, 64, 768, 768, True, 0, "accumulate"),   # attention projection onto a residual
+    (4, 512, 768, 3072, True, 1, "split"),      # fc + GELU, split output feeding the next product
+    (1, 1024, 3072, 768, True, 0, "accumulate"),
+    (1, 320, 776, 200, True, 1, "split"),       # K tail, narrow ragged N
+    (1, 64, 1600, 4800, True, 0, "plain"),      # XL width, M < 128
+    (2, 1024, 768, 50304, False, 0, "plain"),   # lm-head width
+])
+def test_matmul_bf16x3_close_to_fp32(ctx, dev, orc, B, T, C, OC, has_bias, act, mode):
+    """Split-operand product (hi.hi + hi.lo + lo.hi on the bf16 pipe) against the fp64-accumulate
+    oracle on the unsplit fp32 operands: within 1e-4 of the result's magnitude (what is dropped is
+    below 2^-16 per operand; at large K the tensor core's own fp32 accumulation is what is left)."""
+    import torch
+    x = orc.fill_normal((B, T, C), 411)
+    w = orc.fill_normal((OC, C), 412, std=0.02)
+    bias = orc.fill_normal((OC,), 413, std=0.01) if has_bias else None
+    base = orc.fill_normal((B, T, OC), 414) if mode == "accumulate" else None
+    rows = slice(None) if B * T * OC < 40_000_000 else slice(-300, None)
+    want = orc.matmul_forward(x.reshape(B * T, C)[rows][None], w, bias, act=act, precise=True)[0]
+    d_x = torch.empty((2, B, T, C), dtype=torch.int16, device="cuda")
+    ctx.split_bf16(d_x[0], d_x[1], dev.to(x), x.size)
+    d_wh = torch.empty((OC, C), dtype=torch.int16, device="cuda")
+    d_wl = torch.empty((OC, C), dtype=torch.int16, device="cuda")
+    ctx.split_bf16(d_wh, d_wl, dev.to(w), w.size)
+    d_bias = None if bias is None else dev.to(bias)
+    scale = float(np.abs(want).max())
+    if mode == "split":
+        outs = torch.full((2, B, T, OC), -1, dtype=torch.int16, device="cuda")
+        ctx.matmul_forward_bf16x3(None, outs, d_x, d_wh, d_wl, d_bias, B, T, C, OC, act=act)
+        ctx.sync_check()
+        bits = outs.cpu().numpy().view(np.uint16)
+        got = (_bits_to_f32(bits[0]) + _bits_to_f32(bits[1])).reshape(B * T, OC)[rows]
+        assert np.isfinite(got).all()
+        # the split output itself keeps 16 bits of each value
+        assert (np.abs(got - want) <= np.abs(want) * 2.0 ** -15 + 1e-4 * scale).all()
+        # the second plane is small against the first: it only holds what the rounding dropped
+        lo_f, hi_f = _bits_to_f32(bits[1]), _bits_to_f32(bits[0])
+        assert (np.abs(lo_f) <= np.abs(hi_f) * 2.0 ** -8 + 1e-30).all()
+    else:
+        out = dev.full((B, T, OC), float("nan")) if base is None else dev.to(base)
+        ctx.matmul_forward_bf16x3(out, None, d_x, d_wh, d_wl, d_bias, B, T, C, OC, act=act, accumulate=base is not None)
+        got_all = dev.back(out)
+        assert np.isfinite(got_all).all(), "unwritten or non-finite outputs"
+        got = got_all.reshape(B * T, OC)[rows]
+        if base is not None:
+            got = got - base.reshape(B * T, OC)[rows]  # one fp32 add: exact up to its rounding
+            assert np.abs(got - want).max() <= 1e-4 * scale + 4e-7 * float(np.abs(base).max() + scale)
+        else:
+            assert np.abs(got - want).max() <= 1e-4 * scale, (np.abs(got - want).max(), scale)
+        assert _rel_rms(got, want) < (5e-5 if base is None else 2e-4)

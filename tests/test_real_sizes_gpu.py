@@ -1,0 +1,244 @@
+"""Operator-level parity at the sizes of the benchmark configurations (8192 rows; GPU).
+
+Every output buffer sits between two 4 KB sentinel bands that must come back untouched: the kernels
+write through TMA stores and reductions whose boxes are clipped by the tensor map, and nothing else
+would notice a box landing outside the tensor.  The oracle (fp64 accumulation) is run on the
+last 256 rows, which is enough to cover every column tile, both CTAs of a pair and the last row
+block; the rest is checked for finiteness.
+
+Reference semantics: kernels/matmul/9_matmul_async_cg_tf32_gelu.cuh:237-275 (GEMM + bias + GELU),
+kernels/attention/3_flash_attention_permute.cuh:346-355 (attention on the packed buffer),
+kernels/fused_residual_layernorm/fused_residual_layernorm.cuh:88-98.
+"""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+BAND = 1024  # floats: 4 KB on either side of a guarded buffer
+SENTINEL = -7.0e33
+
+
+def _guarded(torch, shape, dtype=None, fill=None):
+    """A device tensor of `shape` with sentinel bands before and after it; returns (view, check)."""
+    dtype = dtype or torch.float32
+    n = int(np.prod(shape))
+    per = 4 // torch.empty((), dtype=dtype).element_size()  # elements per 4 bytes
+    band = BAND * per
+    raw = torch.empty(n + 2 * band, dtype=dtype, device="cuda")
+    raw[:band] = SENTINEL if dtype == torch.float32 else 12345
+    raw[band + n:] = SENTINEL if dtype == torch.float32 else 12345
+    if fill is not None:
+        raw[band:band + n] = fill
+    else:
+        raw[band:band + n] = float("nan") if dtype == torch.float32 else 0
+    torch.cuda.synchronize()
+    want_lo, want_hi = raw[:band].clone(), raw[band + n:].clone()
+
+    def check():
+        assert torch.equal(raw[:band], want_lo), "a store landed in front of the output buffer"
+        assert torch.equal(raw[band + n:], want_hi), "a store landed behind the output buffer"
+
+    return raw[band:band + n].view(*shape), check
+
+
+def _rel_rms(a, b):
+    return float(np.sqrt(np.mean((a.astype(np.float64) - b) ** 2)) / (np.sqrt(np.mean(b.astype(np.float64) ** 2)) + 1e-30))
+
+
+def _round_tf32(a):
+    u = a.view(np.uint32).astype(np.uint64)
+    return ((u + 0x1000) & 0xFFFFE000).astype(np.uint32).view(np.float32)
+
+
+M_ROWS = 8192
+TAIL = 256
+
+# K, N, bias, act, accumulate
+CASES = [
+    (768, 2304, True, 0, False),    # QKV
+    (768, 768, True, 0, True),      # attention projection onto the residual stream
+    (768, 3072, True, 1, False),    # fc + GELU
+    (3072, 768, True, 0, True),     # fc projection onto the residual stream
+    (1600, 1600, True, 0, True),    # XL attention projection
+]
+
+
+@pytest.mark.parametrize("K,N,has_bias,act,accumulate", CASES)
+def test_gemm_8192_rows_against_oracle(ctx, dev, orc, K, N, has_bias, act, accumulate):
+    import torch
+    B, T = 8, 1024
+    g = torch.Generator(device="cuda").manual_seed(K * 7 + N)
+    x = torch.empty(B, T, K, device="cuda").normal_(0, 1, generator=g)
+    w = torch.empty(N, K, device="cuda").normal_(0, 0.02, generator=g)
+    bias = torch.empty(N, device="cuda").normal_(0, 0.01, generator=g) if has_bias else None
+    base = torch.empty(B, T, N, device="cuda").normal_(0, 1, generator=g) if accumulate else None
+    out, check = _guarded(torch, (B, T, N), fill=None)
+    if accumulate:
+        out.copy_(base)
+    torch.cuda.synchronize()
+    ctx.matmul_forward(out, x, w, bias, B, T, K, N, act=act, residual=out if accumulate else None)
+    ctx.sync_check()
+    check()
+    got = out.reshape(M_ROWS, N)
+    assert torch.isfinite(got).all()
+    xs = x.reshape(M_ROWS, K)[-TAIL:].cpu().numpy()
+    want = orc.matmul_forward(xs[None], w.cpu().numpy(), None if bias is None else bias.cpu().numpy(), act=act, precise=True)[0]
+    if accumulate:
+        want = want + base.reshape(M_ROWS, N)[-TAIL:].cpu().numpy()
+    gt = got[-TAIL:].cpu().numpy()
+    mag = float(np.sqrt(np.mean(want.astype(np.float64) ** 2)))
+    # the tensor core cuts the fp32 operands to TF32: about 4e-4 of the product's magnitude per element
+    assert np.abs(gt - want).max() < 8e-3 * np.sqrt(K / 768) * max(1.0, mag if not accumulate else 1.0)
+    prod = want - (base.reshape(M_ROWS, N)[-TAIL:].cpu().numpy() if accumulate else 0)
+    assert np.sqrt(np.mean((gt - want).astype(np.float64) ** 2)) < 1.5e-3 * np.sqrt(np.mean(prod.astype(np.float64) ** 2))
+    # the first row block too (the other end of the work distribution)
+    xs0 = x.reshape(M_ROWS, K)[:64].cpu().numpy()
+    want0 = orc.matmul_forward(xs0[None], w.cpu().numpy(), None if bias is None else bias.cpu().numpy(), act=act, precise=True)[0]
+    if accumulate:
+        want0 = want0 + base.reshape(M_ROWS, N)[:64].cpu().numpy()
+    assert np.abs(got[:64].cpu().numpy() - want0).max() < 8e-3 * np.sqrt(K / 768) * max(1.0, mag if not accumulate else 1.0)
+
+
+def test_accumulate_flag_is_one_add_per_element(ctx, dev, orc):
+    """out += x.w^T + bias through tile-wise reductions equals the plain product added once
+    (bitwise: the product is computed the same way, the add is a single fp32 add)."""
+    import torch
+    B, T, K, N = 8, 1024, 768, 768
+    g = torch.Generator(device="cuda").manual_seed(5)
+    x = torch.empty(B, T, K, device="cuda").normal_(0, 1, generator=g)
+    w = torch.empty(N, K, device="cuda").normal_(0, 0.02, generator=g)
+    bias = torch.empty(N, device="cuda").normal_(0, 0.01, generator=g)
+    base = torch.empty(B, T, N, device="cuda").normal_(0, 1, generator=g)
+    plain, check_p = _guarded(torch, (B, T, N))
+    acc, check_a = _guarded(torch, (B, T, N))
+    acc.copy_(base)
+    torch.cuda.synchronize()
+    ctx.matmul_forward(plain, x, w, bias, B, T, K, N)
+    ctx.matmul_forward(acc, x, w, bias, B, T, K, N, residual=acc)
+    ctx.sync_check()
+    check_p()
+    check_a()
+    assert torch.equal(acc, base + plain)
+
+
+def test_lmhead_8192_rows_with_fused_argmax(pkg, orc, ctx):
+    """768 -> 50304 at 8192 rows as the driver runs it for the host-buffer call: arg-max ids taken in
+    the epilogue, logits stored for the last position of every sequence only (store_period)."""
+    import torch
+    B, T = 8, 1024
+    cfg = pkg.GPT2Config(num_layers=1)
+    ocfg = orc.GPT2Config(num_layers=1)
+    params = orc.init_params(ocfg, seed=77)
+    model = pkg.GPT2(ctx, cfg, B, T)
+    model.load_params(params)
+    tokens = orc.fill_tokens((B, T), seed=78, vocab=cfg.vocab_size)
+    full = np.empty((B, T, cfg.padded_vocab_size), np.float32)
+    amax_full = np.empty((B, T), np.int32)
+    model.forward_host(tokens, B, T, logits_host=full, argmax_host=amax_full)
+    last = np.empty((B, cfg.padded_vocab_size), np.float32)
+    amax = np.empty((B, T), np.int32)
+    model.forward_host(tokens, B, T, last_logits_host=last, argmax_host=amax)  # logits not stored
+    V = cfg.vocab_size
+    assert np.array_equal(amax_full, full[..., :V].argmax(-1))
+    assert np.array_equal(amax, amax_full)
+    assert np.array_equal(last, full[:, -1, :])
+    want = orc.gpt2_forward(params, ocfg, tokens[-1:], precise=False)[0]
+    assert np.abs(full[-1] - want).max() < 2e-2
+    model.close()
+
+
+def test_attention_b8_nh12_t1024_against_oracle(ctx, dev, orc):
+    """The isolated attention configuration (B=8, NH=12, T=1024, N(0,1) inputs); the oracle runs on
+    two heads of two batch entries (heads are independent)."""
+    import torch
+    B, T, NH = 8, 1024, 12
+    C = NH * 64
+    g = torch.Generator(device="cuda").manual_seed(3)
+    qkv = torch.empty(B, T, 3 * C, device="cuda").normal_(0, 1, generator=g)
+    out, check = _guarded(torch, (B, T, C))
+    lse, check_l = _guarded(torch, (B, NH, T))
+    torch.cuda.synchronize()
+    ctx.attention_forward(out, None, lse, qkv, B, T, C, NH)
+    ctx.sync_check()
+    check()
+    check_l()
+    assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    for b, h in ((0, 0), (7, 11), (3, 5)):
+        sl = [slice(k * C + h * 64, k * C + (h + 1) * 64) for k in range(3)]
+        one = torch.cat([qkv[b:b + 1, :, s] for s in sl], dim=-1).cpu().numpy()
+        want, wlse = orc.attention_forward(one, 1, precise=True)
+        got = out[b, :, h * 64:(h + 1) * 64].cpu().numpy()
+        assert np.abs(got - want[0]).max() < 5e-3
+        assert np.abs(lse[b, h].cpu().numpy() - wlse[0, 0]).max() < 4e-3
+
+
+@pytest.mark.parametrize("C", [768, 1600])
+def test_fused_residual_layernorm_8192_rows(ctx, dev, orc, C):
+    import torch
+    B, T = 8, 1024
+    g = torch.Generator(device="cuda").manual_seed(C)
+    x1 = torch.empty(B, T, C, device="cuda").normal_(0, 1, generator=g)
+    x2 = torch.empty(B, T, C, device="cuda").normal_(0, 1, generator=g)
+    w = torch.empty(C, device="cuda").normal_(1, 0.1, generator=g)
+    b = torch.empty(C, device="cuda").normal_(0, 0.1, generator=g)
+    res, check_r = _guarded(torch, (B, T, C))
+    out, check_o = _guarded(torch, (B, T, C))
+    mean, check_m = _guarded(torch, (B, T))
+    rstd, check_s = _guarded(torch, (B, T))
+    torch.cuda.synchronize()
+    ctx.fused_residual_layernorm_forward(res, out, mean, rstd, x1, x2, w, b, B, T, C)
+    ctx.sync_check()
+    for c in (check_r, check_o, check_m, check_s):
+        c()
+    assert torch.equal(res, x1 + x2)
+    rows = slice(M_ROWS - TAIL, M_ROWS)
+    wres, wout, wmean, wrstd = orc.fused_residual_layernorm_forward(
+        x1.reshape(M_ROWS, C)[rows].cpu().numpy()[None], x2.reshape(M_ROWS, C)[rows].cpu().numpy()[None],
+        w.cpu().numpy(), b.cpu().numpy(), precise=True)
+    assert np.abs(out.reshape(M_ROWS, C)[rows].cpu().numpy() - wout[0]).max() < 1e-5
+    assert np.abs(mean.reshape(M_ROWS)[rows].cpu().numpy() - wmean[0]).max() < 1e-6
+    assert torch.isfinite(out).all()
+
+
+def test_layernorm_8192_rows_guarded(ctx, dev, orc):
+    import torch
+    B, T, C = 8, 1024, 768
+    g = torch.Generator(device="cuda").manual_seed(9)
+    x = torch.empty(B, T, C, device="cuda").normal_(0, 1, generator=g)
+    w = torch.empty(C, device="cuda").normal_(1, 0.1, generator=g)
+    b = torch.empty(C, device="cuda").normal_(0, 0.1, generator=g)
+    out, check = _guarded(torch, (B, T, C))
+    torch.cuda.synchronize()
+    ctx.layernorm_forward(out, None, None, x, w, b, B, T, C)
+    ctx.sync_check()
+    check()
+    want, _, _ = orc.layernorm_forward(x.reshape(M_ROWS, C)[-TAIL:].cpu().numpy()[None], w.cpu().numpy(), b.cpu().numpy(), precise=True)
+    assert np.abs(out.reshape(M_ROWS, C)[-TAIL:].cpu().numpy() - want[0]).max() < 1e-5
+    assert torch.isfinite(out).all()
+
+
+def test_xl_full_depth_sequence_t1024(pkg, orc, ctx):
+    """GPT-2 XL, all 48 layers, T = 1024, B = 2 on the GPU; the oracle runs sequence 1."""
+    import torch
+    B, T = 2, 1024
+    cfg = pkg.GPT2_XL
+    ocfg = orc.GPT2_XL
+    params = orc.init_params(ocfg, seed=1234)
+    model = pkg.GPT2(ctx, cfg, B, T)
+    model.load_params(params)
+    tokens = orc.fill_tokens((B, T), seed=4321, vocab=cfg.vocab_size)
+    d_tok = torch.from_numpy(tokens).cuda()
+    torch.cuda.synchronize()
+    logits = model.forward(d_tok, B, T)
+    ctx.sync_check()
+    assert torch.isfinite(logits).all()
+    got = logits[1].cpu().numpy()
+    model.close()
+    want = orc.gpt2_forward(params, ocfg, tokens[1:2], precise=False)[0]
+    V = cfg.vocab_size
+    err = np.abs(got - want)
+    agree = float((got[:, :V].argmax(-1) == want[:, :V].argmax(-1)).mean())
+    print(f"XL T=1024: max-abs {err.max():.3e}, rms {np.sqrt((err ** 2).mean()):.3e}, top-1 agreement {agree:.5f}")
+    assert err.max() < 2e-2
+    assert agree >= 0.99
