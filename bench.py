@@ -33,7 +33,7 @@ GEMM_DRAM_TRAFFIC = {}
 METRIC = "gpt2_forward_tokens_per_s"
 UNIT = "tokens/s"
 B_PER_GPU, T = 8, 1024
-WORKLOAD = "GPT-2 124M full-sequence forward, B=8 T=1024 per GPU, fp32 storage, TF32 tensor-core GEMMs (configs[1])"
+WORKLOAD = "GPT-2 124M full-sequence forward, B=8 T=1024 per GPU, fp32 storage, tensor-core GEMMs (configs[1]; arithmetic: see config.arithmetic)"
 
 
 def _peaks():
