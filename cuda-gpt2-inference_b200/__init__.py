@@ -40,12 +40,12 @@ EXPORTS = (
     "fused_residual_layernorm_forward", "fused_residual_layernorm", "residual_forward",
     "gelu_forward", "encoder_forward",
     "b200_gpt2_param_offsets", "b200_gpt2_create", "b200_gpt2_destroy", "b200_gpt2_params",
-    "b200_gpt2_load_params_host", "b200_gpt2_load_params_file", "b200_gpt2_set_options", "b200_gpt2_forward",
+    "b200_gpt2_load_params_host", "b200_gpt2_load_params_file", "b200_gpt2_set_options", "b200_gpt2_forward", "b200_gpt2_forward_sample",
     "b200_gpt2_logits", "b200_gpt2_forward_host", "b200_gpt2_forward_host_enqueue", "b200_gpt2_forward_host_wait", "b200_gpt2_activation",
     "b200_gpt2_set_profile", "b200_gpt2_read_profile",
     "b200_gpt2_forward_static", "b200_gpt2_static_prepare",
     "b200_gpt2_enable_kv_cache", "b200_gpt2_prefill", "b200_gpt2_decode_step", "b200_gpt2_decode_step_host", "b200_gpt2_generate_greedy", "b200_gpt2_generate", "b200_sample_rows",
-    "b200_gpt2_create_tp", "b200_gpt2_set_allreduce", "b200_gpt2_param_offsets_tp", "b200_gpt2_shard_params_host",
+    "b200_gpt2_create_tp", "b200_gpt2_set_allreduce", "b200_gpt2_set_tp_overlap", "b200_gpt2_param_offsets_tp", "b200_gpt2_shard_params_host",
 )
 
 # Arithmetic modes of the forward as keyword arguments of GPT2.set_options
@@ -136,6 +136,7 @@ def lib() -> C.CDLL:
         l.b200_gpt2_load_params_file.argtypes = [vp, C.c_char_p, sz]
         l.b200_gpt2_set_options.argtypes = [vp, i, i, i, i]
         l.b200_gpt2_forward.argtypes = [vp, vp, i, i]
+        l.b200_gpt2_forward_sample.argtypes = [vp, vp, i, i, C.c_float, C.c_uint, vp, vp, i]
         l.b200_gpt2_logits.argtypes = [vp]
         l.b200_gpt2_logits.restype = vp
         l.b200_gpt2_forward_host.argtypes = [vp, vp, i, i, vp, vp, vp]
@@ -156,6 +157,7 @@ def lib() -> C.CDLL:
         l.b200_sample_rows.argtypes = [vp, vp, vp, i, i, i, C.c_float, i, C.c_float, C.c_uint, C.c_uint]
         l.b200_gpt2_create_tp.argtypes = [C.POINTER(vp), vp, vp, i, i, i, i]
         l.b200_gpt2_set_allreduce.argtypes = [vp, ALLREDUCE_FN, vp]
+        l.b200_gpt2_set_tp_overlap.argtypes = [vp, i, i]
         l.b200_gpt2_param_offsets_tp.argtypes = [vp, i, i, C.POINTER(sz)]
         l.b200_gpt2_param_offsets_tp.restype = sz
         l.b200_gpt2_shard_params_host.argtypes = [vp, i, i, vp, vp]
@@ -414,16 +416,22 @@ class GPT2:
     def num_local_params(self) -> int:
         return param_offsets_tp(self.cfg, self.tp_size, self.tp_rank)[16]
 
-    def set_allreduce_torch(self, torch_stream, group=None):
-        """Uses torch.distributed (NCCL) for the one all-reduce per attention / MLP block."""
+    def set_allreduce_torch(self, torch_stream=None, group=None):
+        """Uses torch.distributed (NCCL) for the one all-reduce per attention / MLP block.  The
+        library names the stream every all-reduce has to be ordered on (its compute stream or its
+        communication stream); torch_stream is accepted for compatibility and ignored."""
         import torch
         import torch.distributed as dist
         dev = self.ctx.device
+        streams = {}
 
         def _cb(user, buf, count, stream):
             try:
+                key = int(stream or 0)
+                if key not in streams:
+                    streams[key] = torch.cuda.ExternalStream(key, device=dev) if key else torch.cuda.default_stream(dev)
                 t = _view_device(int(buf), (int(count),), torch.float32, dev)
-                with torch.cuda.stream(torch_stream):
+                with torch.cuda.stream(streams[key]):
                     dist.all_reduce(t, group=group)
                 return 0
             except Exception:  # the C side turns this into B200_ERR_CUDA
@@ -431,6 +439,10 @@ class GPT2:
 
         self._allreduce_cb = ALLREDUCE_FN(_cb)  # keep the trampoline alive
         self.ctx.check(lib().b200_gpt2_set_allreduce(self._h, self._allreduce_cb, None), "set_allreduce")
+
+    def set_tp_overlap(self, chunks: int = 1, reserve_sms: int = 0):
+        """Row chunks of a tensor-parallel projection and the SMs its later chunks leave to the all-reduce kernels."""
+        self.ctx.check(lib().b200_gpt2_set_tp_overlap(self._h, int(chunks), int(reserve_sms)), "set_tp_overlap")
 
     def params_ptr(self) -> int:
         return int(lib().b200_gpt2_params(self._h))
@@ -467,6 +479,13 @@ class GPT2:
         self.ctx.check(lib().b200_gpt2_forward(self._h, _ptr(tokens), B, T), "gpt2_forward")
         return _view_device(int(lib().b200_gpt2_logits(self._h)), (B, T, self.logits_width),
                             torch.float32, self.ctx.device)
+
+    def forward_sample(self, tokens, B: int, T: int, ids_out, temperature: float = 1.0, seed: int = 0, lse_out=None,
+                       store_logits: bool = False):
+        """The forward with one token per position drawn in the lm-head's epilogue (ids_out: CUDA int32
+        [B,T]) and, if lse_out (CUDA fp32 [B,T]) is given, the log-sum-exp of every row of logits."""
+        self.ctx.check(lib().b200_gpt2_forward_sample(self._h, _ptr(tokens), B, T, float(temperature), int(seed) & 0xFFFFFFFF,
+                                                      _ptr(ids_out), _ptr(lse_out), int(store_logits)), "gpt2_forward_sample")
 
     def forward_host(self, tokens_host, B: int, T: int, logits_host=None, last_logits_host=None, argmax_host=None):
         """Host-buffer call: H2D of tokens, forward, D2H of what is asked for; synchronous."""

@@ -5,6 +5,7 @@
 // (README.md:255-256).  Forward only, so one set of per-layer activations is reused by all
 // layers; parameters keep the flat fp32 layout documented in include/b200gpt2.h.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <map>
 #include <mutex>
@@ -48,6 +49,10 @@ struct b200_gpt2 {
     // Host-buffer forward without copies: device views of the caller's pinned buffers, written by
     // the kernel behind the lm-head (null: the model's own buffers).  Set around one enqueue_forward.
     struct HostDst { int* ids = nullptr; float* last = nullptr; int* status = nullptr; } host_dst;
+    // b200_gpt2_forward_sample: what the lm-head's epilogue computes besides (or instead of) the arg-max;
+    // set around one enqueue_forward
+    const b200::GemmRowStats* row_stats = nullptr;
+    float2* lse_part = nullptr;                  // log-sum-exp partials [max rows][2 * ceil(Vp / 256)]
     std::map<int, cudaGraphExec_t> decode_graphs;  // by B (the position is read from pos_dev)
     int round_operands = 1, gemm_mode = B200_BF16X3, lmhead_mode = B200_BF16X3, use_graph = 0;
     int att_mode = -1;  // -1: split-operand attention exactly when gemm_mode is B200_TF32X3
@@ -61,6 +66,16 @@ struct b200_gpt2 {
     int vp_row0 = 0;   // first row of wte used by the local lm-head
     b200_allreduce_fn allreduce = nullptr;
     void* allreduce_user = nullptr;
+    // the all-reduces of a projection run on a stream of their own, chunk by chunk under the GEMM
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t tp_ev[9] = {};  // [0..7] chunk computed, [8] all chunks reduced
+    // Row chunks of a projection (1: one GEMM, then one all-reduce on the compute stream) and the SMs
+    // the later chunks' GEMMs leave to the communication kernels running beside them.  Measured on
+    // two B200s (GPT-2 XL, 8192 rows): 40.7 ms per step unchunked, 44.0 with 2 chunks, 48.5 with 4
+    // (42.9 / 47.7 with 16 SMs set aside) - the shorter GEMMs and smaller messages cost more than
+    // the overlap hides - so chunking is off unless asked for.
+    int tp_chunks = 1;
+    int tp_reserve_sms = 0;
     std::map<std::pair<std::pair<int, int>, int>, cudaGraphExec_t> graphs;  // by (B, T, results)
     // per-operator timing (b200_gpt2_set_profile): one event pair per kernel launch
     bool profile = false;
@@ -139,6 +154,43 @@ int tp_allreduce(b200_gpt2* m, float* buf, size_t count) {
     return m->allreduce(m->allreduce_user, buf, count, m->ctx->stream) == 0 ? B200_OK : B200_ERR_CUDA;
 }
 
+// Tensor parallel: out[M,N] = inp[M,K] . w^T + bias as a partial sum, then summed over the ranks.
+// The rows are cut into chunks; each chunk's all-reduce is issued on the communication stream as
+// soon as its GEMM has been queued, so the transfer of chunk c runs under the GEMM of chunk c+1 and
+// only the last chunk's all-reduce is exposed.  The compute stream continues once every chunk is
+// reduced.  (Row chunks do not change any element's arithmetic: a GEMM row depends on its own
+// input row only.)
+int tp_projection_overlapped(b200_gpt2* m, float* out, const float* inp, const float* w, const float* bias, int M, int K, int N, int chunks) {
+    using namespace b200;
+    b200_ctx* ctx = m->ctx;
+    const int Mc = M / chunks;
+    const int all_sms = ctx->num_sms;
+    for (int c = 0; c < chunks; ++c) {
+        float* o = out + (size_t)c * Mc * N;
+        // The GEMMs are persistent, one CTA per SM: with every SM taken, the communication kernel of
+        // the previous chunk could only start as CTAs of this GEMM retire, and the GEMM's last CTAs
+        // would queue behind it.  From the second chunk on the grid leaves a few SMs free instead.
+        if (c > 0 && m->tp_reserve_sms > 0 && all_sms - m->tp_reserve_sms >= 32) ctx->num_sms = (all_sms - m->tp_reserve_sms) & ~1;
+        int st = launch_gemm_tf32(ctx, o, inp + (size_t)c * Mc * K, w, bias, nullptr, Mc, K, N, 0, m->gemm_mode);
+        ctx->num_sms = all_sms;
+        if (st != B200_OK) return st;
+        B200_CUDA(ctx, cudaEventRecord(m->tp_ev[c], ctx->stream));
+        B200_CUDA(ctx, cudaStreamWaitEvent(m->comm_stream, m->tp_ev[c], 0));
+        if (m->allreduce(m->allreduce_user, o, (size_t)Mc * N, m->comm_stream) != 0) return B200_ERR_CUDA;
+    }
+    B200_CUDA(ctx, cudaEventRecord(m->tp_ev[8], m->comm_stream));
+    B200_CUDA(ctx, cudaStreamWaitEvent(ctx->stream, m->tp_ev[8], 0));
+    return B200_OK;
+}
+
+// how many row chunks a tensor-parallel projection is cut into (1: GEMM, then one all-reduce on the compute stream)
+int tp_chunks(const b200_gpt2* m, int M, bool prof) {
+    int n = m->tp_chunks;
+    if (prof || !m->comm_stream) return 1;  // per-launch timing wants the all-reduce on the timed stream
+    while (n > 1 && (M % (n * 256) || M / n < 1024)) --n;
+    return n;
+}
+
 // results, what is prepared for the host behind the lm-head:
 //   RES_ARGMAX  the lm-head GEMM also leaves, per position, the arg-max over the real vocabulary
 //               in m->argmax (found in its epilogue while the logits are on their way out: no
@@ -182,6 +234,7 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
     const int accum = (m->tp_size == 1) ? GEMM_ACCUM_OUT : 0;
     int st;
     const bool prof = m->profile;
+    const int tpc = (m->tp_size > 1 && g_tf32 && m->gemm_mode == B200_TF32) ? tp_chunks(m, M, prof) : 1;
 #define STEP(cat, call)                                             \
     do {                                                            \
         if (prof) { st = prof_begin(m, (cat)); if (st != B200_OK) return st; } \
@@ -228,12 +281,14 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         float* proj_out = accum ? m->residual : m->branch;
         if (hx) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, atty_h, PH + o_apw, PL + o_apw, apb, M, A, C, accum));
         else if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, atty_h, PH + o_apw, apb, M, A, C, accum));
+        else if (tpc > 1) STEP(B200_PROF_GEMM_ATTPROJ, tp_projection_overlapped(m, proj_out, m->atty, W + o_apw, apb, M, A, C, tpc));
         else STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, proj_out, m->atty, W + o_apw, apb, nullptr, M, A, C, accum, m->gemm_mode));
         if (accum) {
             STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, ln2w, ln2b, M, C, ln_flags));
         } else {
             // tensor parallel: every rank holds a partial sum over its heads; one all-reduce per block
-            if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
+            // (already issued, chunk by chunk, when the projection ran overlapped)
+            if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
             STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
                                                  m->branch, ln2w, ln2b, M, C, ln_flags));
         }
@@ -245,7 +300,8 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
             STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, fch_h, PH + o_fpw, fpb, M, F, C, accum));
         } else {
             STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, W + o_fcw, fcb, nullptr, M, C, F, GEMM_GELU | grnd, m->gemm_mode));
-            STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, proj_out, m->fch, W + o_fpw, fpb, nullptr, M, F, C, accum, m->gemm_mode));
+            if (tpc > 1) STEP(B200_PROF_GEMM_FCPROJ, tp_projection_overlapped(m, proj_out, m->fch, W + o_fpw, fpb, M, F, C, tpc));
+            else STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, proj_out, m->fch, W + o_fpw, fpb, nullptr, M, F, C, accum, m->gemm_mode));
         }
         const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
         const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
@@ -254,7 +310,7 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         if (accum) {
             STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, nw, nb, M, C, next_flags));
         } else {
-            if (m->tp_size > 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
+            if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
             STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
                                                  m->branch, nw, nb, M, C, next_flags));
         }
@@ -262,12 +318,13 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
     const size_t o_head = off[0] + (size_t)m->vp_row0 * C;
     const int store_period = (with_argmax && (results & RES_NO_LOGITS)) ? T : 0;
     unsigned long long* keys = with_argmax ? m->argmax_keys : nullptr;
+    if (m->row_stats && !hlx && m->lmhead_mode != B200_TF32) { ctx->last_error = "sampling in the lm-head: lmhead_mode B200_BF16X3 or B200_TF32"; return B200_ERR_STATE; }
     if (hlx) STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_bf16x3(ctx, m->logits, nullptr, ln_h, PH + o_head, PL + o_head, nullptr, M, C, m->vp_local, 0,
-                                                          keys, c.vocab_size, store_period));
+                                                          keys, c.vocab_size, store_period, m->row_stats));
     else if (hl) STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_bf16(ctx, m->logits, nullptr, ln_h, PH + o_head, nullptr, M, C, m->vp_local, 0,
                                                               keys, c.vocab_size, store_period));
     else STEP(B200_PROF_GEMM_LMHEAD, launch_gemm_tf32(ctx, m->logits, m->ln_out, W_head + o_head, nullptr, nullptr, M, C,
-                                                      m->vp_local, 0, m->lmhead_mode, keys, c.vocab_size, store_period));
+                                                      m->vp_local, 0, m->lmhead_mode, keys, c.vocab_size, store_period, m->row_stats));
     if (results) {
         st = launch_host_results(ctx, m->host_dst.ids ? m->host_dst.ids : m->argmax, with_argmax ? m->argmax_keys : nullptr, M,
                                  (results & RES_LAST) ? (m->host_dst.last ? m->host_dst.last : m->last_logits) : nullptr,
@@ -382,6 +439,14 @@ int b200_gpt2_create(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* cfg
     return b200_gpt2_create_tp(out, ctx, cfg, max_B, max_T, 1, 0);
 }
 
+int b200_gpt2_set_tp_overlap(b200_gpt2* m, int chunks, int reserve_sms) {
+    if (!m) return B200_ERR_NULL;
+    if (chunks < 1 || chunks > 8 || reserve_sms < 0 || reserve_sms > 64) return B200_ERR_SHAPE;
+    m->tp_chunks = chunks;
+    m->tp_reserve_sms = reserve_sms;
+    return B200_OK;
+}
+
 int b200_gpt2_set_allreduce(b200_gpt2* m, b200_allreduce_fn fn, void* user) {
     if (!m) return B200_ERR_NULL;
     m->allreduce = fn;
@@ -420,6 +485,10 @@ int b200_gpt2_create_tp(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* 
     alloc((void**)&m->argmax_keys, M * 8);
     alloc((void**)&m->last_logits, (M / 64 + 1) * Vp * 4);
     if (e == cudaSuccess) e = cudaMemset(m->argmax_keys, 0, M * 8);
+    if (tp_size > 1) {
+        if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&m->comm_stream, cudaStreamNonBlocking);
+        for (int i = 0; i < 9 && e == cudaSuccess; ++i) e = cudaEventCreateWithFlags(&m->tp_ev[i], cudaEventDisableTiming);
+    }
     if (e != cudaSuccess) {
         b200_fail_cuda(ctx, e, "cudaMalloc (b200_gpt2_create)");
         b200_gpt2_destroy(m);
@@ -442,8 +511,10 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     for (cudaEvent_t e : m->host_done) if (e) cudaEventDestroy(e);
     if (m->h_slot_status) cudaFreeHost(m->h_slot_status);
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
+    for (cudaEvent_t e : m->tp_ev) if (e) cudaEventDestroy(e);
+    if (m->comm_stream) cudaStreamDestroy(m->comm_stream);
     void* ptrs[] = {m->params, m->params_h, m->params_l, m->params_r, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
-                    m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->last_logits, m->kcache, m->vcache};
+                    m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->last_logits, m->kcache, m->vcache, m->lse_part};
     for (void* p : ptrs) if (p) cudaFree(p);
     delete m;
     return B200_OK;
@@ -590,6 +661,35 @@ static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, int resul
 }
 
 int b200_gpt2_forward(b200_gpt2* m, const int* tokens, int B, int T) { return forward_impl(m, tokens, B, T, 0); }
+
+int b200_gpt2_forward_sample(b200_gpt2* m, const int* tokens, int B, int T, float temperature, unsigned int seed,
+                             int* ids_out, float* lse_out, int store_logits) {
+    if (!m || !tokens || !ids_out) return B200_ERR_NULL;
+    if (B <= 0 || T <= 0 || T % 64 || T > m->max_T) return B200_ERR_SHAPE;
+    if ((size_t)B * T > (size_t)m->max_B * m->max_T) return B200_ERR_LIMIT;
+    if (m->tp_size > 1) return B200_ERR_STATE;  // a rank sees only its slice of the vocabulary
+    b200_ctx* ctx = m->ctx;
+    b200_device_guard on_device(ctx);
+    const int slots = 2 * ((m->cfg.padded_vocab_size + 255) / 256);
+    if (lse_out && !m->lse_part)
+        B200_CUDA(ctx, cudaMalloc(&m->lse_part, (size_t)m->max_B * m->max_T * slots * sizeof(float2)));
+    int st = prepare_weights(m);
+    if (st != B200_OK) return st;
+    b200::GemmRowStats rs;
+    rs.inv_temp = temperature > 0.f ? 1.0f / temperature : 0.f;  // <= 0: greedy
+    rs.seed = seed;
+    rs.stream0 = 0u;
+    rs.lse_part = lse_out ? m->lse_part : nullptr;
+    rs.lse_slots = slots;
+    m->row_stats = &rs;
+    m->host_dst.ids = ids_out;
+    st = enqueue_forward(m, tokens, B, T, RES_ARGMAX | (store_logits ? 0 : RES_NO_LOGITS));
+    m->row_stats = nullptr;
+    m->host_dst = {};
+    if (st != B200_OK) return st;
+    if (lse_out) return b200::launch_lse_reduce(ctx, lse_out, m->lse_part, B * T, slots);
+    return B200_OK;
+}
 
 // Device address of a pinned (page-locked, mapped) host buffer, or null for any other memory.
 static void* device_view(const void* p) {

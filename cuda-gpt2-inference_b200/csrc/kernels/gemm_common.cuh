@@ -30,6 +30,12 @@ struct GemmArgs {
     // > 0: rows come in sequences of store_period (a multiple of 32) and only the 32-row blocks that
     // hold a sequence's last row are written; the rest of the output is wanted as arg-max only
     int store_period;
+    // with argmax_keys (CTA-pair kernel): sample_inv_temp > 0 turns the arg-max into a draw (see
+    // GemmRowStats); lse_part receives the log-sum-exp partials of every row
+    float sample_inv_temp;
+    unsigned int sample_seed, sample_stream0;
+    float2* lse_part;
+    int lse_slots;
     // out_h only: it holds two bf16 planes of [M,N], the value rounded to bf16 and, M rows further
     // down, what that rounding dropped (again as bf16): the split operands of a bf16x3 product
     int out_planes;
@@ -157,7 +163,7 @@ __device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args
 //   bias_first : gemm_bias_chunk(bias, args.N, col0, c_begin, lane)
 __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, const float* bias, const CUtensorMap* tmap_out, uint32_t tmem_acc,
                                                        int q, int lane, int row0, int col0, uint8_t* stage2, float bias_first,
-                                                       int c_begin, int c_end, int nbuf) {
+                                                       int c_begin, int c_end, int nbuf, int lse_slot = 0) {
     const bool do_gelu = (args.flags & GEMM_GELU) != 0;
     const bool do_round = (args.flags & GEMM_ROUND_OUT_TF32) != 0;
     const int sub_row = lane >> 3;  // 0..3: row within a group of four
@@ -175,6 +181,9 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         best_key = args.argmax_keys[my_row];
         if (best_key != 0ull) best_v = argmax_dec((uint32_t)(best_key >> 32));
     }
+    const bool do_sample = do_argmax && args.sample_inv_temp > 0.f;
+    const bool do_lse = do_argmax && args.lse_part != nullptr;
+    float lse_m = -INFINITY, lse_s = 0.f;  // running maximum and sum of exp(value - maximum) of this thread's columns
     const bool via_tma = args.residual == nullptr;
     const bool skip_store = args.store_period > 0 && (row0 % args.store_period) < args.store_period - 32;
     if (via_tma) {  // the stores of the previous tile have left the staging buffers
@@ -194,7 +203,32 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r);
         tmem_ld_wait();
-        if (do_argmax) {
+        if (do_lse) {
+            const int cbase = col0 + c * 32;
+            float cm = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < 32; ++i) cm = fmaxf(cm, cbase + i < args.argmax_cols ? __uint_as_float(r[i]) : -INFINITY);
+            if (cm > -INFINITY) {
+                const float mn = fmaxf(lse_m, cm);
+                float sum = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sum += cbase + i < args.argmax_cols ? __expf(__uint_as_float(r[i]) - mn) : 0.f;
+                lse_s = lse_s * __expf(lse_m - mn) + sum;  // exp(-inf) = 0 on the first chunk
+                lse_m = mn;
+            }
+        }
+        if (do_sample) {
+            const int cbase = col0 + c * 32;
+            if (cbase < args.argmax_cols && my_row < args.M) {
+#pragma unroll 8
+                for (int i = 0; i < 32; ++i) {
+                    const float sc = sample_score(__uint_as_float(r[i]), args.sample_inv_temp, args.sample_seed,
+                                                  args.sample_stream0 + (uint32_t)my_row, (uint32_t)(cbase + i));
+                    const unsigned long long key = ((unsigned long long)argmax_enc(sc) << 32) | (0xFFFFFFFFu - (uint32_t)(cbase + i));
+                    if (cbase + i < args.argmax_cols && key > best_key) { best_key = key; improved = true; }
+                }
+            }
+        } else if (do_argmax) {
             const int cbase = col0 + c * 32;
             float cm = -INFINITY;  // chunk maximum (columns beyond the limit count too: only a filter)
 #pragma unroll
@@ -273,6 +307,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         __syncwarp();
     }
     if (do_argmax && improved && my_row < args.M) atomicMax(args.argmax_keys + my_row, best_key);
+    if (do_lse && my_row < args.M) args.lse_part[(size_t)my_row * args.lse_slots + lse_slot] = make_float2(lse_m, lse_s);
 }
 
 // CTA-pair GEMM (gemm_tf32_pair.cu): 256-row tiles computed by two CTAs sharing one UMMA.
@@ -284,6 +319,6 @@ int preload_gemm_pair_kernels(b200_ctx* ctx);  // the PAIR_TF32 kernel: loaded n
 int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp_lo, const void* weight, const void* weight_lo,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys, int argmax_cols, int kind, uint16_t* out_h = nullptr,
-                     int out_planes = 0, int store_period = 0);
+                     int out_planes = 0, int store_period = 0, const GemmRowStats* stats = nullptr);
 
 }  // namespace b200

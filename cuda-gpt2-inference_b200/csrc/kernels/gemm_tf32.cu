@@ -283,7 +283,7 @@ namespace {
 // bf16 != 0: inp / weight hold bf16 elements and out_h (if not null) receives the output as bf16.
 int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp, const void* weight,
                     const float* bias, const float* residual, int M, int K, int N, int flags,
-                    int mode, unsigned long long* argmax_keys, int argmax_cols, bool bf16, int store_period) {
+                    int mode, unsigned long long* argmax_keys, int argmax_cols, bool bf16, int store_period, const GemmRowStats* stats) {
     if ((flags & GEMM_ACCUM_OUT) && (residual || out_h)) { ctx->last_error = "GEMM_ACCUM_OUT: fp32 output without a residual operand"; return B200_ERR_STATE; }
     if (store_period && (store_period % 32 || residual || !argmax_keys)) { ctx->last_error = "store_period: multiple of 32, with the fused arg-max only"; return B200_ERR_STATE; }
     const bool x3 = (mode == B200_TF32X3);
@@ -320,9 +320,13 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
     bool use_pair = M >= 2048 && (N >= 2048 || K >= 2048);
     if (bf16) use_pair = M >= 2048 && (long)((M + 255) / 256) * ((N + 255) / 256) >= ctx->num_sms / 2;
     if (pair_env >= 0) use_pair = pair_env == 1;
+    if (stats) {  // the sampling / log-sum-exp epilogue lives in the CTA-pair kernel
+        if (x3) { ctx->last_error = "row statistics are not available with 3xTF32 GEMMs"; return B200_ERR_STATE; }
+        use_pair = true;
+    }
     if (!x3 && use_pair)
         return launch_gemm_pair(ctx, out, inp, nullptr, weight, nullptr, bias, residual, M, K, N, flags, argmax_keys, argmax_cols,
-                                bf16 ? PAIR_BF16 : PAIR_TF32, out_h, 0, store_period);
+                                bf16 ? PAIR_BF16 : PAIR_TF32, out_h, 0, store_period, stats);
     GemmArgs a;
     a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
@@ -337,6 +341,10 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
     a.argmax_cols = argmax_cols;
     a.store_period = store_period;
     a.out_planes = 0;
+    a.sample_inv_temp = 0.f;
+    a.sample_seed = a.sample_stream0 = 0u;
+    a.lse_part = nullptr;
+    a.lse_slots = 0;
     a.tile_w = a.unit_cols = 0;
     a.k_splits = 1;
     a.split_flags = nullptr;
@@ -399,13 +407,13 @@ int preload_gemm_kernels(b200_ctx* ctx) {
 
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
-                     int mode, unsigned long long* argmax_keys, int argmax_cols, int store_period) {
-    return launch_gemm_any(ctx, out, nullptr, inp, weight, bias, residual, M, K, N, flags, mode, argmax_keys, argmax_cols, false, store_period);
+                     int mode, unsigned long long* argmax_keys, int argmax_cols, int store_period, const GemmRowStats* stats) {
+    return launch_gemm_any(ctx, out, nullptr, inp, weight, bias, residual, M, K, N, flags, mode, argmax_keys, argmax_cols, false, store_period, stats);
 }
 
 int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const uint16_t* inp, const uint16_t* weight_hi,
                        const uint16_t* weight_lo, const float* bias, int M, int K, int N, int flags,
-                       unsigned long long* argmax_keys, int argmax_cols, int store_period) {
+                       unsigned long long* argmax_keys, int argmax_cols, int store_period, const GemmRowStats* stats) {
     if (K % 8 || N % 8) { ctx->last_error = "bf16x3 GEMM: K and N must be multiples of 8"; return B200_ERR_SHAPE; }
     if (out_planes && (M % 32 || (flags & GEMM_ACCUM_OUT))) { ctx->last_error = "bf16x3 GEMM: a split output needs M % 32 == 0 and no accumulation"; return B200_ERR_SHAPE; }
     if (store_period && (store_period % 32 || !argmax_keys)) { ctx->last_error = "store_period: multiple of 32, with the fused arg-max only"; return B200_ERR_STATE; }
@@ -413,14 +421,14 @@ int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const ui
     if (!out_planes && !out) return B200_ERR_NULL;
     return launch_gemm_pair(ctx, out, inp, inp + (size_t)M * K, weight_hi, weight_lo, bias, nullptr, M, K, N,
                             flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32 | GEMM_ACCUM_OUT), argmax_keys, argmax_cols, PAIR_BF16X3, out_planes,
-                            out_planes ? 1 : 0, store_period);
+                            out_planes ? 1 : 0, store_period, stats);
 }
 
 int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,
                      const float* bias, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys, int argmax_cols, int store_period) {
     if (K % 8 || N % 8) { ctx->last_error = "bf16 GEMM: K and N must be multiples of 8"; return B200_ERR_SHAPE; }
-    return launch_gemm_any(ctx, out, out_h, inp, weight, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32 | GEMM_ACCUM_OUT), B200_TF32, argmax_keys, argmax_cols, true, store_period);
+    return launch_gemm_any(ctx, out, out_h, inp, weight, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32 | GEMM_ACCUM_OUT), B200_TF32, argmax_keys, argmax_cols, true, store_period, nullptr);
 }
 
 }  // namespace b200

@@ -290,10 +290,10 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
                 if (!ok) break;
             }
-            if (c_begin < c_end)
+            if (c_begin < c_end || args.lse_part != nullptr)  // (an empty share still owes its log-sum-exp slot)
                 gemm_drain_accumulator(args, bias, &tmap_out, tmem_base + acc * kMaxW, q, lane,
                                        m_blk * 2 * BM + (int)rank * BM + q * 32, col0,
-                                       smem_epi + ew * 4096, bias_first, c_begin, c_end, 1);
+                                       smem_epi + ew * 4096, bias_first, c_begin, c_end, 1, 2 * (col0 / kMaxW) + (ew < 4 ? 0 : 1));
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) {
@@ -348,7 +348,8 @@ int launch_pair(b200_ctx* ctx, const CUtensorMap* maps, GemmArgs& a, int num_pai
     // persistent: never more pairs than can be resident together (the K slices of a tile wait for
     // one another, and the rest would run as a tail anyway), never more than there are tiles
     const int total = a.k_splits * a.num_m_blocks * a.num_n_blocks;
-    const int pairs = total < resident_pairs[ctx->device & 63] ? total : resident_pairs[ctx->device & 63];
+    int pairs = total < resident_pairs[ctx->device & 63] ? total : resident_pairs[ctx->device & 63];
+    if (pairs > num_pairs_max) pairs = num_pairs_max;  // the caller may have set SMs aside
     cfg.gridDim = dim3(2 * pairs);
     B200_CUDA(ctx, cudaLaunchKernelEx(&cfg, gemm_pair_kernel<MODE>, maps[0], maps[1], maps[2], maps[3], maps[4], a));
     ctx->launches++;
@@ -365,7 +366,7 @@ int preload_gemm_pair_kernels(b200_ctx* ctx) {
 int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp_lo, const void* weight, const void* weight_lo,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys, int argmax_cols, int kind, uint16_t* out_h, int out_planes,
-                     int store_period) {
+                     int store_period, const GemmRowStats* stats) {
     const int num_pairs_max = ctx->num_sms / 2;
     const bool half = kind != PAIR_TF32;
     GemmArgs a;
@@ -381,6 +382,15 @@ int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp
     a.argmax_cols = argmax_cols;
     a.store_period = store_period;
     a.out_planes = out_planes;
+    a.sample_inv_temp = stats ? stats->inv_temp : 0.f;
+    a.sample_seed = stats ? stats->seed : 0u;
+    a.sample_stream0 = stats ? stats->stream0 : 0u;
+    a.lse_part = stats ? stats->lse_part : nullptr;
+    a.lse_slots = stats ? stats->lse_slots : 0;
+    if (stats && (!argmax_keys || (stats->lse_part && stats->lse_slots < 2 * ((N + kMaxW - 1) / kMaxW)))) {
+        ctx->last_error = "row statistics need the fused arg-max keys and 2 * ceil(N / 256) partial slots per row";
+        return B200_ERR_STATE;
+    }
     a.unit_cols = out_h ? 64 : 32;
     // Tile width and K slices: fewest estimated cycles.  Per 128-byte K block a tile needs 2*W cycles
     // of the tensor pipe per product (three products with split operands) and (128 + W/2) * 128 bytes
@@ -392,7 +402,7 @@ int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp
     const bool may_split = (flags & GEMM_ACCUM_OUT) && !(flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32)) && ctx->d_split_flags != nullptr;
     int best_w = kMaxW, best_ks = 1;
     double best_cost = -1.0;
-    for (int w = kMaxW; w >= 64; w -= 64) {
+    for (int w = kMaxW; w >= ((stats && stats->lse_part) ? kMaxW : 64); w -= 64) {  // the partial slots are numbered by 256-column tiles
         const long tiles = (long)a.num_m_blocks * ((N + w - 1) / w);
         for (int ks = 1; ks <= (may_split ? 4 : 1); ++ks) {
             if (ks > 1 && (num_kb / ks < 6 || tiles * ks * 2 * kEpiWarps > (long)ctx->split_flag_words)) break;
@@ -406,7 +416,7 @@ int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp
     // tuning hooks: B200_GEMM_BN = tile width (64, 128, 192, 256), B200_GEMM_KSPLIT = K slices (1-4)
     static const int forced_w = [] { const char* e = getenv("B200_GEMM_BN"); return e ? atoi(e) : 0; }();
     static const int forced_ks = [] { const char* e = getenv("B200_GEMM_KSPLIT"); return e ? atoi(e) : 0; }();
-    if (forced_w == 64 || forced_w == 128 || forced_w == 192 || forced_w == 256) best_w = forced_w;
+    if ((forced_w == 64 || forced_w == 128 || forced_w == 192 || forced_w == 256) && !(stats && stats->lse_part)) best_w = forced_w;
     if (forced_ks >= 1 && forced_ks <= 4 && (forced_ks == 1 || may_split)) {
         best_ks = forced_ks;
         const long tiles = (long)a.num_m_blocks * ((N + best_w - 1) / best_w);

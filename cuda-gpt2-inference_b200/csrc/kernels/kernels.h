@@ -43,9 +43,11 @@ int preload_attention_kernel(b200_ctx* ctx);
 // GEMM_ACCUM_OUT: out += result instead of out = result (fp32 output without a residual operand: the
 // tiles leave as TMA reductions).  With out = the residual stream this is the residual add.
 enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2, GEMM_ACCUM_OUT = 4 };
+struct GemmRowStats;
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
-                     int mode, unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0);
+                     int mode, unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0,
+                     const GemmRowStats* stats = nullptr);
 // The same product with bf16 operands (tcgen05 kind::f16, fp32 accumulation): inp [M,K] and weight
 // [N,K] hold bf16; the result goes to out (fp32) or, if out_h is not null, to out_h as bf16.
 // flags: GEMM_GELU only.  K and N multiples of 8.
@@ -59,7 +61,22 @@ int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t*
 // of [M,N] in the same split form.  flags: GEMM_GELU, GEMM_ACCUM_OUT.  K and N multiples of 8.
 int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const uint16_t* inp, const uint16_t* weight_hi,
                        const uint16_t* weight_lo, const float* bias, int M, int K, int N, int flags,
-                       unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0);
+                       unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0,
+                       const GemmRowStats* stats = nullptr);
+// Extras of the fused row reduction of a GEMM with arg-max keys (CTA-pair kernel only):
+//   inv_temp > 0: the keys hold, instead of the arg-max, the column that maximises
+//     sample_score(value, inv_temp, seed, stream0 + row, column) - a draw from softmax(row / temperature);
+//   lse_part != null: per row and per (256-column tile, half of it) the maximum m and the sum of
+//     exp(value - m) over the columns below argmax_cols, as float2 pairs [M][lse_slots]
+//     (lse_slots = 2 * ceil(N / 256)); launch_lse_reduce folds them into log-sum-exp per row.
+struct GemmRowStats {
+    float inv_temp;
+    unsigned int seed, stream0;
+    float2* lse_part;
+    int lse_slots;
+};
+// lse[r] = log sum_j exp(x[r][j]) from the partial pairs of a GEMM with GemmRowStats::lse_part
+int launch_lse_reduce(b200_ctx* ctx, float* lse, const float2* part, int M, int slots);
 // (store_period > 0, with the fused arg-max: rows come in sequences of store_period and only the
 // 32-row blocks holding a sequence's last row are written to out)
 // After the lm-head: turns the keys left by a GEMM with fused arg-max into column indices and
@@ -114,6 +131,22 @@ inline cudaError_t launch_pdl(b200_ctx* ctx, void (*kernel)(KArgs...), dim3 grid
     cfg.attrs = attr;
     cfg.numAttrs = ctx->pdl ? 1 : 0;
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
+// Counter-based random bits: two rounds of a 32-bit integer mixer over (seed, stream, column).
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    return x;
+}
+__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t stream, uint32_t col) {
+    const uint32_t h = mix32(mix32(seed ^ (stream * 0x9E3779B1u)) ^ (col * 0x85EBCA77u));
+    const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0,1), 24 bits
+    return -__logf(-__logf(u));
+}
+// The score whose arg-max over the columns is a draw from softmax(logits / temperature) (Gumbel-max);
+// one fused multiply-add, so that every kernel that draws gets the same bits for the same input.
+__device__ __forceinline__ float sample_score(float logit, float inv_temp, uint32_t seed, uint32_t stream, uint32_t col) {
+    return fmaf(logit, inv_temp, gumbel_noise(seed, stream, col));
 }
 
 // fast, accurate tanh-GELU: x * sigmoid(2u), u = sqrt(2/pi) * (x + 0.044715 x^3)

@@ -300,17 +300,6 @@ argmax_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
     }
 }
 
-// Counter-based random bits: two rounds of a 32-bit integer mixer over (seed, stream, column).
-__device__ __forceinline__ uint32_t mix32(uint32_t x) {
-    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
-    return x;
-}
-__device__ __forceinline__ float gumbel_noise(uint32_t seed, uint32_t stream, uint32_t col) {
-    const uint32_t h = mix32(mix32(seed ^ (stream * 0x9E3779B1u)) ^ (col * 0x85EBCA77u));
-    const float u = ((float)(h >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0,1), 24 bits
-    return -__logf(-__logf(u));
-}
-
 // fp32 -> uint32 with the same order (larger value, larger key)
 __device__ __forceinline__ uint32_t order_key(float f) {
     const uint32_t u = __float_as_uint(f);
@@ -458,7 +447,7 @@ sample_rows_kernel(int* __restrict__ out, const float* __restrict__ logits, int 
     for (int i = threadIdx.x; i < V; i += blockDim.x) {
         const float x = row[i];
         if (order_key(x) < min_key) continue;
-        const float sc = x * inv_temp + gumbel_noise(seed, stream, (uint32_t)i);
+        const float sc = sample_score(x, inv_temp, seed, stream, (uint32_t)i);
         if (sc > best) { best = sc; bi = i; }
     }
     __shared__ float sb[8];
@@ -637,6 +626,37 @@ int launch_host_results(b200_ctx* ctx, int* out, unsigned long long* keys, int M
     cudaError_t le = launch_pdl(ctx, host_results_kernel, dim3(grid), dim3(256), 0, out, keys, M,
                                 reinterpret_cast<float4*>(last_dst), reinterpret_cast<const float4*>(logits), B, T, Vp / 4,
                                 status_dst, static_cast<const int*>(ctx->d_status));
+    ctx->launches++;
+    B200_CUDA(ctx, le);
+    return B200_OK;
+}
+
+namespace {
+// lse[r] = m + log(sum_i s_i * exp(m_i - m)), m = max_i m_i over the row's partial pairs (m_i, s_i);
+// one warp per row
+__global__ void __launch_bounds__(256)
+lse_reduce_kernel(float* __restrict__ lse, const float2* __restrict__ part, int M, int slots) {
+    griddep_wait();
+    const int lane = threadIdx.x & 31;
+    const int row = blockIdx.x * 8 + (threadIdx.x >> 5);
+    if (row >= M) return;
+    const float2* p = part + (size_t)row * slots;
+    float m = -INFINITY;
+    for (int i = lane; i < slots; i += 32) m = fmaxf(m, p[i].x);
+#pragma unroll
+    for (int s = 16; s >= 1; s >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, s));
+    float sum = 0.f;
+    for (int i = lane; i < slots; i += 32) {
+        const float2 v = p[i];
+        if (v.y > 0.f) sum += v.y * __expf(v.x - m);
+    }
+    sum = warp_sum(sum);
+    if (lane == 0) lse[row] = m + logf(sum);
+}
+}  // namespace
+
+int launch_lse_reduce(b200_ctx* ctx, float* lse, const float2* part, int M, int slots) {
+    cudaError_t le = launch_pdl(ctx, lse_reduce_kernel, dim3((M + 7) / 8), dim3(256), 0, lse, part, M, slots);
     ctx->launches++;
     B200_CUDA(ctx, le);
     return B200_OK;

@@ -251,6 +251,23 @@ int b200_gpt2_set_attention_mode(b200_gpt2* model, int mode);
 /* tokens: device int32 [B,T].  Asynchronous.  Logits: device [B,T,Vp], owned by the model. */
 int b200_gpt2_forward(b200_gpt2* model, const int* tokens, int B, int T);
 float* b200_gpt2_logits(b200_gpt2* model);
+/* The forward with sampling (and the softmax normaliser) taken in the lm-head GEMM's epilogue, while
+ * the logits are still accumulators: nothing has to read the 1.65 GB (124M, B=8, T=1024) of logits
+ * again, and with store_logits == 0 they are not even written (only the 32-row blocks that hold
+ * a sequence's last position are; the rest of the model's logits buffer is then stale).  No
+ * counterpart in the reference, which stops at the logits.
+ *   ids_out [B,T] (device int32): per position one token drawn from softmax(logits / temperature)
+ *     over the real vocabulary [0,V) - the arg-max of logit / temperature + Gumbel noise, the
+ *     noise a fixed function of (seed, row b*T + t, token id): exactly what
+ *     b200_sample_rows(ctx, out, logits, B*T, V, Vp, temperature, 0, 0, seed, 0) draws from the
+ *     stored logits.  temperature <= 0: the arg-max.
+ *   lse_out [B,T] (device fp32, nullable): log sum_{j<V} exp(logit_j), so that
+ *     exp(logit - lse) is the softmax probability of any logit the caller still has.  The first
+ *     call with lse_out allocates the partial-sum buffer (25.8 MB for 124M at 8192 rows).
+ * Asynchronous on the context's stream; never replayed from a graph.  lmhead_mode B200_BF16X3 or
+ * B200_TF32; not on a tensor-parallel model. */
+int b200_gpt2_forward_sample(b200_gpt2* model, const int* tokens, int B, int T, float temperature,
+                             unsigned int seed, int* ids_out, float* lse_out, int store_logits);
 /* Host-buffer form: copies tokens (host, ideally pinned) to the device, runs the forward,
  * and copies back what is asked for, synchronising before it returns:
  *   logits_host      [B,T,Vp]  all logits                     (nullable)
@@ -318,13 +335,23 @@ int b200_sample_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V,
  * after attn-proj and after fc-proj are combined by ONE all-reduce each per block, issued
  * through a callback so that the communication library stays the caller's choice (NCCL's
  * ncclAllReduce, or torch.distributed): the callback must enqueue an in-place fp32 sum
- * all-reduce of buf[0..count) over the tensor-parallel group on `stream` and return 0.
+ * all-reduce of buf[0..count) over the tensor-parallel group on `stream` and return 0.  `stream` is
+ * the context's stream or, when b200_gpt2_set_tp_overlap asks for row chunks, the model's own
+ * communication stream: the all-reduce of a chunk is then issued as soon as its GEMM is queued, so
+ * that it runs under the next chunk's GEMM, and the callback is called once per chunk (same ranks,
+ * same order on every rank).
  * Rank-local parameters use the same 16-tensor order with the local shapes;
  * b200_gpt2_shard_params_host cuts them out of a full host parameter array. */
 typedef int (*b200_allreduce_fn)(void* user, float* buf, size_t count, void* stream);
 int b200_gpt2_create_tp(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* cfg, int max_B,
                         int max_T, int tp_size, int tp_rank);
 int b200_gpt2_set_allreduce(b200_gpt2* model, b200_allreduce_fn fn, void* user);
+/* How a tensor-parallel projection overlaps its all-reduce: chunks = row chunks (1-8; 1 = the
+ * whole GEMM, then one all-reduce on the compute stream), reserve_sms = SMs the GEMMs of the later
+ * chunks leave free for the communication kernels that run beside them (0-64).  Default 1, 0: on
+ * two B200s the chunked forms measured slower (GPT-2 XL, 8192 rows: 40.7 ms unchunked, 44.0 with
+ * 2 chunks, 48.5 with 4), so the overlap is an option, not the default. */
+int b200_gpt2_set_tp_overlap(b200_gpt2* model, int chunks, int reserve_sms);
 size_t b200_gpt2_param_offsets_tp(const b200_gpt2_config* cfg, int tp_size, int tp_rank, size_t* offsets);
 int b200_gpt2_shard_params_host(const b200_gpt2_config* cfg, int tp_size, int tp_rank,
                                 const float* full_params, float* local_params);

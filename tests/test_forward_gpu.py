@@ -328,3 +328,45 @@ def test_enqueue_wait_pair_matches_the_synchronous_host_call(pkg, orc, ctx, use_
     model.forward_host_wait(0)  # the context is usable again
     assert np.array_equal(bufs[0][0].numpy(), want[0][0])
     model.close()
+
+
+@pytest.mark.parametrize("mode,temperature", [("bf16x3", 0.8), ("tf32", 1.3), ("bf16x3", 0.0)])
+def test_sampling_and_lse_fused_into_the_lmhead(pkg, orc, ctx, mode, temperature):
+    """b200_gpt2_forward_sample draws every position's token and forms log-sum-exp in the lm-head
+    GEMM's epilogue.  The draw must be exactly the one b200_sample_rows makes from the stored logits of
+    the plain forward (same noise function, same logits bits), and lse must be the log-sum-exp of those
+    logits over the real vocabulary; without stored logits the results must not change."""
+    import torch
+    B, T = 2, 1024   # 2048 rows: CTA-pair kernel, as in the benchmark configuration
+    cfg, ocfg, params, model = _make(pkg, orc, ctx, dict(num_layers=1), B, T)
+    model.set_options(**pkg.MODES[mode])
+    V, Vp = cfg.vocab_size, cfg.padded_vocab_size
+    tokens = orc.fill_tokens((B, T), seed=21, vocab=V)
+    d_tok = torch.from_numpy(tokens).cuda()
+    torch.cuda.synchronize()
+    logits = model.forward(d_tok, B, T)
+    ctx.sync_check()
+    logits = logits.clone()
+    want_ids = torch.empty((B * T,), dtype=torch.int32, device="cuda")
+    ctx.sample_rows(want_ids, logits.view(B * T, Vp), B * T, V, Vp, temperature, 1234, 0)
+    ctx.sync_check()
+    want_lse = torch.logsumexp(logits.view(B * T, Vp)[:, :V].double(), dim=-1).float()
+    for store in (True, False):
+        ids = torch.full((B, T), -1, dtype=torch.int32, device="cuda")
+        lse = torch.full((B, T), float("nan"), device="cuda")
+        torch.cuda.synchronize()
+        model.forward_sample(d_tok, B, T, ids, temperature=temperature, seed=1234, lse_out=lse, store_logits=store)
+        ctx.sync_check()
+        assert torch.equal(ids.view(-1), want_ids), f"{(ids.view(-1) != want_ids).sum().item()} draws differ"
+        assert (lse.view(-1) - want_lse).abs().max().item() < 1e-4
+        if store:
+            got = model.forward(d_tok, B, T)  # same bits as before: the extra epilogue work does not touch the logits
+            ctx.sync_check()
+            assert torch.equal(got, logits)
+    if temperature > 0:
+        # the draws follow the softmax: their mean log-probability is close to its expectation (minus the entropy)
+        lp = torch.log_softmax(logits.view(B * T, Vp)[:, :V].double() / temperature, dim=-1)
+        mean_lp = lp.gather(1, want_ids.long().view(-1, 1)).mean().item()
+        ent = -(lp.exp() * lp).sum(-1).mean().item()
+        assert abs(mean_lp + ent) < 0.2, (mean_lp, ent)
+    model.close()
