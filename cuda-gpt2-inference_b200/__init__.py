@@ -33,7 +33,7 @@ EXPORTS = (
     "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
     "b200_ctx_last_error", "b200_ctx_wait_timeout_probe",
     "b200_matmul_forward", "b200_matmul_forward_bf16", "b200_convert_bf16", "b200_matmul_forward_bf16x3", "b200_split_bf16",
-    "b200_gpt2_set_attention_mode", "b200_attention_forward", "b200_attention_forward_x3", "b200_layernorm_forward",
+    "b200_gpt2_set_attention_mode", "b200_attention_forward", "b200_attention_forward_x3", "b200_attention_forward_fp16", "b200_split_fp16", "b200_layernorm_forward",
     "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
     "b200_encoder_forward",
     "matmul_forward", "matmul_forward_gelu", "attention_forward", "layernorm_forward",
@@ -52,15 +52,15 @@ EXPORTS = (
 MODES = {
     "tf32": dict(round_operands=1, gemm_mode=B200_TF32, lmhead_mode=B200_TF32, attention_mode=-1),
     "bf16x3": dict(round_operands=1, gemm_mode=B200_BF16X3, lmhead_mode=B200_BF16X3, attention_mode=-1),
-    "bf16x3_att3": dict(round_operands=1, gemm_mode=B200_BF16X3, lmhead_mode=B200_BF16X3, attention_mode=B200_TF32X3),
+    "bf16x3_att_tf32": dict(round_operands=1, gemm_mode=B200_BF16X3, lmhead_mode=B200_BF16X3, attention_mode=B200_TF32),
     "tf32x3": dict(round_operands=0, gemm_mode=B200_TF32X3, lmhead_mode=B200_TF32X3, attention_mode=-1),
     "bf16": dict(round_operands=1, gemm_mode=B200_BF16, lmhead_mode=B200_BF16, attention_mode=-1),
 }
 MODE_NOTES = {
     "tf32": "fp32 storage, single-pass TF32 tensor-core GEMMs (tcgen05 kind::tf32) on round-to-nearest operands, TF32 attention",
     "bf16x3": "fp32 storage, GEMM operands split into two bf16 terms (16 significant bits), three kind::f16 products per K step, "
-              "fp32 accumulation; single-pass TF32 attention",
-    "bf16x3_att3": "bf16x3 GEMMs with split-operand (3xTF32) attention: fp32-level logits",
+              "fp32 accumulation; attention on fp16 planes of q, k, v (q.k one product, p.v two)",
+    "bf16x3_att_tf32": "bf16x3 GEMMs with the single-pass TF32 attention kernel",
     "tf32x3": "3xTF32 GEMMs and attention (three kind::tf32 products per K step)",
     "bf16": "bf16 GEMM operands (reduced precision; not comparable with the fp32-level modes)",
 }
@@ -109,6 +109,8 @@ def lib() -> C.CDLL:
         l.b200_gpt2_set_attention_mode.argtypes = [vp, i]
         l.b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_attention_forward_x3.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
+        l.b200_attention_forward_fp16.argtypes = [vp, vp, vp, vp, i, i, i, i]
+        l.b200_split_fp16.argtypes = [vp, vp, vp, vp, sz]
         l.b200_layernorm_forward.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i]
         l.b200_fused_residual_layernorm_forward.argtypes = [vp, vp, vp, vp, vp, vp, vp, vp, vp, i, i, i]
         l.b200_residual_forward.argtypes = [vp, vp, vp, vp, sz]
@@ -257,6 +259,15 @@ class Context:
         """3xTF32 attention; qkvr ([B,T,3C] scratch) is required."""
         self.check(lib().b200_attention_forward_x3(self._h, _ptr(out), _ptr(qkvr), _ptr(att), _ptr(inp), B, T, Cc, NH),
                    "attention_forward_x3")
+
+    def attention_forward_fp16(self, out, att, inp_split, B, T, Cc, NH):
+        """fp16 attention; inp_split: fp16 [2,B,T,3C] (hi plane, lo plane)."""
+        self.check(lib().b200_attention_forward_fp16(self._h, _ptr(out), _ptr(att), _ptr(inp_split), B, T, Cc, NH),
+                   "attention_forward_fp16")
+
+    def split_fp16(self, hi, lo, inp, n):
+        """hi = fp16(inp), lo = fp16(inp - hi)."""
+        self.check(lib().b200_split_fp16(self._h, _ptr(hi), _ptr(lo), _ptr(inp), n), "split_fp16")
 
     def layernorm_forward(self, out, mean, rstd, inp, weight, bias, B, T, Cc):
         self.check(lib().b200_layernorm_forward(self._h, _ptr(out), _ptr(mean), _ptr(rstd), _ptr(inp), _ptr(weight),

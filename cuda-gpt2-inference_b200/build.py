@@ -23,6 +23,7 @@ SOURCES = [
     "kernels/gemm_tf32_pair.cu",
     "kernels/attention.cu",
     "kernels/attention_x3.cu",
+    "kernels/attention_split.cu",
     "kernels/decode.cu",
     "driver/gpt2.cu",
 ]
@@ -55,8 +56,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         obj = os.path.join(obj_dir, src.replace("/", "_") + ".o")
         objs.append(obj)
-        # B200_NVCC_EXTRA: extra nvcc flags for experiments (e.g. -DB200_GEMM_TIMING)
-        cmd = ["nvcc", *NVCC_FLAGS, *os.environ.get("B200_NVCC_EXTRA", "").split(), "-c", os.path.join(CSRC, src), "-o", obj]
+        cmd = ["nvcc", *NVCC_FLAGS, "-c", os.path.join(CSRC, src), "-o", obj]
         if verbose:
             cmd.insert(1, "-Xptxas")
             cmd.insert(2, "-v")

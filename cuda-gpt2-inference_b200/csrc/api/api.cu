@@ -254,6 +254,21 @@ int b200_attention_forward_x3(b200_ctx* ctx, float* out, float* qkvr, float* att
     return b200::launch_attention_x3(ctx, out, qkvr, att, inp, B, T, C, NH);
 }
 
+int b200_split_fp16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* inp, size_t n) {
+    if (!ctx) return B200_ERR_NULL;
+    REQUIRE_PTR(hi); REQUIRE_PTR(lo); REQUIRE_PTR(inp);
+    if (n == 0 || n % 4) return B200_ERR_SHAPE;
+    return b200::launch_split_fp16(ctx, hi, lo, inp, n);
+}
+
+int b200_attention_forward_fp16(b200_ctx* ctx, float* out, float* att, const uint16_t* inp_split,
+                                int B, int T, int C, int NH) {
+    if (!ctx) return B200_ERR_NULL;
+    REQUIRE_PTR(out); REQUIRE_PTR(inp_split); OPTIONAL_PTR(att);
+    if (B <= 0 || T <= 0 || C <= 0 || NH <= 0 || C % NH || C / NH != 64 || T % 64) return B200_ERR_SHAPE;
+    return b200::launch_attention_split(ctx, out, att, inp_split, B, T, C, NH, 0);
+}
+
 int b200_layernorm_forward(b200_ctx* ctx, float* out, float* mean, float* rstd, const float* inp,
                            const float* weight, const float* bias, int B, int T, int C) {
     if (!ctx) return B200_ERR_NULL;

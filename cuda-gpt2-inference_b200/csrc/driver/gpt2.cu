@@ -259,8 +259,13 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         // unbiased rounding noise that the softmax-weighted sums average down.  The 3xTF32
         // attention needs the unrounded values.
         const bool att_x3 = (g_tf32 || hx) && (m->att_mode < 0 ? m->gemm_mode == B200_TF32X3 : m->att_mode == B200_TF32X3) && m->qkv_small;
+        // fp16 attention: the QKV GEMM writes q, k, v as two fp16 planes into the same buffer
+        // (not while the forward also fills the fp32 key/value cache)
+        const bool att_split = hx && !m->keep_kv && (m->att_mode < 0 || m->att_mode == B200_BF16X3);
         const int qkv_flags = (!att_x3 && (m->round_operands || m->gemm_mode != B200_TF32)) ? GEMM_ROUND_OUT_TF32 : 0;
-        if (hx) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16x3(ctx, m->qkv, nullptr, ln_h, PH + o_qkvw, PL + o_qkvw, qkvb, M, C, 3 * A, qkv_flags));
+        uint16_t* qkv_h = reinterpret_cast<uint16_t*>(m->qkv);
+        if (att_split) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16x3(ctx, nullptr, qkv_h, ln_h, PH + o_qkvw, PL + o_qkvw, qkvb, M, C, 3 * A, GEMM_PLANES_FP16));
+        else if (hx) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16x3(ctx, m->qkv, nullptr, ln_h, PH + o_qkvw, PL + o_qkvw, qkvb, M, C, 3 * A, qkv_flags));
         else if (hb) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16(ctx, m->qkv, nullptr, ln_h, PH + o_qkvw, qkvb, M, C, 3 * A, qkv_flags));
         else STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, W + o_qkvw, qkvb, nullptr, M, C, 3 * A, qkv_flags, m->gemm_mode));
         if (m->keep_kv) {
@@ -268,7 +273,9 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
             st = launch_kv_append(ctx, m->kcache + l * per_layer, m->vcache + l * per_layer, m->qkv, B, T, C, 0, m->max_T);
             if (st != B200_OK) return st;
         }
-        if (att_x3 && hx) {
+        if (att_split) {
+            STEP(B200_PROF_ATTENTION, launch_attention_split(ctx, m->atty, nullptr, qkv_h, B, T, A, NH, OUT_BF16X2));
+        } else if (att_x3 && hx) {
             // the split-operand attention writes fp32: through the (free) branch buffer, then split
             STEP(B200_PROF_ATTENTION, launch_attention_x3(ctx, m->branch, m->qkv_small, nullptr, m->qkv, B, T, A, NH));
             STEP(B200_PROF_ATTENTION, launch_convert_bf16(ctx, atty_h, m->branch, (size_t)M * A, atty_h + (size_t)M * A));
@@ -603,7 +610,7 @@ int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int l
 
 int b200_gpt2_set_attention_mode(b200_gpt2* m, int mode) {
     if (!m) return B200_ERR_NULL;
-    if (mode != -1 && mode != B200_TF32 && mode != B200_TF32X3) return B200_ERR_SHAPE;
+    if (mode != -1 && mode != B200_TF32 && mode != B200_TF32X3 && mode != B200_BF16X3) return B200_ERR_SHAPE;
     if (mode != m->att_mode) {
         for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
         m->graphs.clear();

@@ -2,6 +2,7 @@
 // the epilogue that drains one 128 x BN accumulator out of tensor memory.
 #pragma once
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include "kernels.h"
 #include "../prim/sm100.cuh"
 
@@ -36,8 +37,9 @@ struct GemmArgs {
     unsigned int sample_seed, sample_stream0;
     float2* lse_part;
     int lse_slots;
-    // out_h only: it holds two bf16 planes of [M,N], the value rounded to bf16 and, M rows further
-    // down, what that rounding dropped (again as bf16): the split operands of a bf16x3 product
+    // out_h only: it holds two 16-bit planes of [M,N], the value rounded to bf16 (1) or to fp16 (2:
+    // clamped to the fp16 range first) and, M rows further down, what that rounding dropped in the
+    // same format: the split operands of a bf16x3 product / of the fp16 attention
     int out_planes;
     // CTA-pair kernel: tiles of 256 rows x tile_w columns (a ragged last one narrower, in whole units
     // of unit_cols), K cut into k_splits slices that are tiles of their own; see gemm_tf32_pair.cu
@@ -122,13 +124,24 @@ __device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args
                     for (int i = 0; i < 8; ++i) v[i] = gelu_tanh(v[i]);
                 }
                 uint32_t pk[4];
+                if (args.out_planes == 2) {
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const __nv_bfloat162 hh = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                    pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
-                    if (planes) {
-                        const __nv_bfloat162 ll = __floats2bfloat162_rn(v[2 * i] - __low2float(hh), v[2 * i + 1] - __high2float(hh));
+                    for (int i = 0; i < 4; ++i) {
+                        const float x0 = fminf(fmaxf(v[2 * i], -65504.f), 65504.f), x1 = fminf(fmaxf(v[2 * i + 1], -65504.f), 65504.f);
+                        const __half2 hh = __floats2half2_rn(x0, x1);
+                        const __half2 ll = __floats2half2_rn(x0 - __low2float(hh), x1 - __high2float(hh));
+                        pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
                         lo[h * 16 + j * 4 + i] = *reinterpret_cast<const uint32_t*>(&ll);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const __nv_bfloat162 hh = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                        pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
+                        if (planes) {
+                            const __nv_bfloat162 ll = __floats2bfloat162_rn(v[2 * i] - __low2float(hh), v[2 * i + 1] - __high2float(hh));
+                            lo[h * 16 + j * 4 + i] = *reinterpret_cast<const uint32_t*>(&ll);
+                        }
                     }
                 }
                 const int chunk = h * 4 + j;

@@ -421,7 +421,7 @@ int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const ui
     if (!out_planes && !out) return B200_ERR_NULL;
     return launch_gemm_pair(ctx, out, inp, inp + (size_t)M * K, weight_hi, weight_lo, bias, nullptr, M, K, N,
                             flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32 | GEMM_ACCUM_OUT), argmax_keys, argmax_cols, PAIR_BF16X3, out_planes,
-                            out_planes ? 1 : 0, store_period, stats);
+                            out_planes ? ((flags & GEMM_PLANES_FP16) ? 2 : 1) : 0, store_period, stats);
 }
 
 int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,

@@ -26,6 +26,8 @@ int launch_round_tf32_inplace(b200_ctx* ctx, float* data, size_t N);
 int launch_fetch_ints(b200_ctx* ctx, int* dst, const int* src_view, int n);
 // out[i] = bf16(in[i]), round to nearest even; N a multiple of 4.  lo (may be null): lo[i] = bf16(in[i] - out[i])
 int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N, uint16_t* lo = nullptr);
+// hi[i] = fp16(clamp(in[i])), lo[i] = fp16(in[i] - hi[i]); N a multiple of 4
+int launch_split_fp16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* in, size_t N);
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
 // one draw per row from softmax(logits / temperature) (Gumbel-max; temperature <= 0: arg-max);
 // row r uses the noise stream stream0 + r of the seed; 0 < top_k < V: only among the top_k largest logits;
@@ -42,7 +44,8 @@ int preload_attention_kernel(b200_ctx* ctx);
 // epilogue flags of the GEMM
 // GEMM_ACCUM_OUT: out += result instead of out = result (fp32 output without a residual operand: the
 // tiles leave as TMA reductions).  With out = the residual stream this is the residual add.
-enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2, GEMM_ACCUM_OUT = 4 };
+// GEMM_PLANES_FP16: a split output (launch_gemm_bf16x3 with out_planes) is written as two fp16 planes instead of bf16
+enum : int { GEMM_GELU = 1, GEMM_ROUND_OUT_TF32 = 2, GEMM_ACCUM_OUT = 4, GEMM_PLANES_FP16 = 8 };
 struct GemmRowStats;
 int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* weight,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
@@ -88,6 +91,12 @@ int launch_host_results(b200_ctx* ctx, int* out, unsigned long long* keys, int M
 
 int launch_attention(b200_ctx* ctx, float* out, float* lse, const float* qkv, int B, int T, int C,
                      int NH, int flags);
+
+// The same on fp16 operands (attention_split.cu): qkv_split holds the packed buffer [B*T, 3C] as two
+// fp16 planes, hi then lo (what launch_gemm_bf16x3 writes with out_planes and GEMM_PLANES_FP16);
+// kind::f16 products q_hi.k_hi and p.v_hi + p.v_lo.  flags as launch_attention.
+int launch_attention_split(b200_ctx* ctx, float* out, float* lse, const uint16_t* qkv_split, int B, int T, int C,
+                           int NH, int flags);
 
 // incremental decoding (decode.cu): B <= 16 rows, fp32 FMA, no TF32 rounding
 // out[B,N] = act(x[B,K] * W[N,K]^T + bias[N])

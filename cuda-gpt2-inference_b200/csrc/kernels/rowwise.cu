@@ -10,6 +10,7 @@
 // kernels/residual/1_residual_naive.cuh:9-12 and kernels/matmul/9_matmul_async_cg_tf32_gelu.cuh:5-11.
 #include <cstdlib>
 #include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include "kernels.h"
 #include "../prim/sm100.cuh"
 
@@ -25,13 +26,9 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
-// One warp per row at a time.  NV = float4 per lane held in registers (covers C <= 128*NV).
+// One warp per row.  NV = float4 per lane held in registers (covers C <= 128*NV).
 // FUSED: x = inp1 + inp2 is stored to res_out first (which may alias an input: every
 // element is read before it is written, by the same lane).
-// The grid is persistent (a few CTAs per SM, each warp walking rows a whole grid apart) and the
-// next row's loads are issued before the current row is reduced and stored, so that the read and
-// the write stream overlap; with one row per warp and the whole matrix resident at once, every
-// warp would first load, then all would store, and the kernel would take two memory phases.
 template <int NV, bool FUSED>
 __global__ void __launch_bounds__(kRowWarps * 32)
 layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict__ mean,
@@ -41,104 +38,83 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
     griddep_wait();
     griddep_launch_dependents();
     const int lane = threadIdx.x & 31;
-    const int stride = gridDim.x * kRowWarps;
-    int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    const int row = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
     if (row >= M) return;
     const int C4 = C >> 2;
+    const float4* x1 = reinterpret_cast<const float4*>(inp1 + (size_t)row * C);
+    const float4* x2 = FUSED ? reinterpret_cast<const float4*>(inp2 + (size_t)row * C) : nullptr;
+
+    float4 v[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        if (c < C4) {
+            v[i] = x1[c];
+            if (FUSED) {
+                const float4 b = x2[c];
+                v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
+            }
+        } else {
+            v[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
+    if (FUSED) {
+        float4* ro = reinterpret_cast<float4*>(res_out + (size_t)row * C);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane + i * 32;
+            if (c < C4) ro[c] = v[i];
+        }
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    const float m = warp_sum(s) / (float)C;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        if (c < C4) {
+            const float dx = v[i].x - m, dy = v[i].y - m, dz = v[i].z - m, dw = v[i].w - m;
+            q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+    }
+    const float r = rsqrtf(warp_sum(q) / (float)C + 1e-5f);
+    if (lane == 0) {
+        if (mean) mean[row] = m;
+        if (rstd) rstd[row] = r;
+    }
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+    const float4* b4 = reinterpret_cast<const float4*>(bias);
+    float4* o = reinterpret_cast<float4*>(out + (size_t)row * C);
+    uint2* oh = reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + (size_t)row * C);  // OUT_BF16
     const bool rnd = (flags & ROUND_OUT_TF32) != 0;
     const bool as_bf16 = (flags & (OUT_BF16 | OUT_BF16X2)) != 0;
     const bool planes = (flags & OUT_BF16X2) != 0;
-    const float4* w4 = reinterpret_cast<const float4*>(weight);
-    const float4* b4 = reinterpret_cast<const float4*>(bias);
-
-    auto load_row = [&](int r, float4 (&dst)[NV]) {
-        const float4* x1 = reinterpret_cast<const float4*>(inp1 + (size_t)r * C);
-        const float4* x2 = FUSED ? reinterpret_cast<const float4*>(inp2 + (size_t)r * C) : nullptr;
+    uint2* ol = oh + (size_t)M * C4;  // OUT_BF16X2: the plane of the dropped parts
 #pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int c = lane + i * 32;
-            if (c < C4) {
-                dst[i] = x1[c];
-                if (FUSED) {
-                    const float4 b = x2[c];
-                    dst[i].x += b.x; dst[i].y += b.y; dst[i].z += b.z; dst[i].w += b.w;
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        if (c < C4) {
+            const float4 w = __ldg(w4 + c), b = __ldg(b4 + c);
+            float4 y;
+            y.x = (v[i].x - m) * r * w.x + b.x;
+            y.y = (v[i].y - m) * r * w.y + b.y;
+            y.z = (v[i].z - m) * r * w.z + b.z;
+            y.w = (v[i].w - m) * r * w.w + b.w;
+            if (as_bf16) {
+                const __nv_bfloat162 p0 = __floats2bfloat162_rn(y.x, y.y), p1 = __floats2bfloat162_rn(y.z, y.w);
+                oh[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1));
+                if (planes) {
+                    const __nv_bfloat162 q0 = __floats2bfloat162_rn(y.x - __low2float(p0), y.y - __high2float(p0));
+                    const __nv_bfloat162 q1 = __floats2bfloat162_rn(y.z - __low2float(p1), y.w - __high2float(p1));
+                    ol[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&q0), *reinterpret_cast<const uint32_t*>(&q1));
                 }
-            } else {
-                dst[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+                continue;
             }
+            if (rnd) { y.x = round_tf32(y.x); y.y = round_tf32(y.y); y.z = round_tf32(y.z); y.w = round_tf32(y.w); }
+            o[c] = y;
         }
-    };
-
-    float4 v[NV];
-    load_row(row, v);
-    while (true) {
-        const int next = row + stride;
-        float4 nv[NV];
-        // in flight while this row is reduced (not with FUSED: res_out may alias the inputs; not for
-        // wide rows: two rows of registers would leave too few warps resident)
-        constexpr bool kPrefetch = !FUSED && NV <= 8;
-        if (kPrefetch && next < M) load_row(next, nv);
-        if (FUSED) {
-            float4* ro = reinterpret_cast<float4*>(res_out + (size_t)row * C);
-#pragma unroll
-            for (int i = 0; i < NV; ++i) {
-                const int c = lane + i * 32;
-                if (c < C4) ro[c] = v[i];
-            }
-        }
-        float s = 0.f;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
-        const float m = warp_sum(s) / (float)C;
-        float q = 0.f;
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int c = lane + i * 32;
-            if (c < C4) {
-                const float dx = v[i].x - m, dy = v[i].y - m, dz = v[i].z - m, dw = v[i].w - m;
-                q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
-            }
-        }
-        const float r = rsqrtf(warp_sum(q) / (float)C + 1e-5f);
-        if (lane == 0) {
-            if (mean) mean[row] = m;
-            if (rstd) rstd[row] = r;
-        }
-        float4* o = reinterpret_cast<float4*>(out + (size_t)row * C);
-        uint2* oh = reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + (size_t)row * C);  // bf16 outputs
-        uint2* ol = oh + (size_t)M * C4;  // OUT_BF16X2: the plane of the dropped parts
-#pragma unroll
-        for (int i = 0; i < NV; ++i) {
-            const int c = lane + i * 32;
-            if (c < C4) {
-                const float4 w = __ldg(w4 + c), b = __ldg(b4 + c);
-                float4 y;
-                y.x = (v[i].x - m) * r * w.x + b.x;
-                y.y = (v[i].y - m) * r * w.y + b.y;
-                y.z = (v[i].z - m) * r * w.z + b.z;
-                y.w = (v[i].w - m) * r * w.w + b.w;
-                if (as_bf16) {
-                    const __nv_bfloat162 p0 = __floats2bfloat162_rn(y.x, y.y), p1 = __floats2bfloat162_rn(y.z, y.w);
-                    oh[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1));
-                    if (planes) {
-                        const __nv_bfloat162 q0 = __floats2bfloat162_rn(y.x - __low2float(p0), y.y - __high2float(p0));
-                        const __nv_bfloat162 q1 = __floats2bfloat162_rn(y.z - __low2float(p1), y.w - __high2float(p1));
-                        ol[c] = make_uint2(*reinterpret_cast<const uint32_t*>(&q0), *reinterpret_cast<const uint32_t*>(&q1));
-                    }
-                    continue;
-                }
-                if (rnd) { y.x = round_tf32(y.x); y.y = round_tf32(y.y); y.z = round_tf32(y.z); y.w = round_tf32(y.w); }
-                o[c] = y;
-            }
-        }
-        if (next >= M) break;
-        if (!kPrefetch) {
-            load_row(next, v);
-        } else {
-#pragma unroll
-            for (int i = 0; i < NV; ++i) v[i] = nv[i];
-        }
-        row = next;
     }
 }
 
@@ -147,11 +123,7 @@ int launch_ln_any(b200_ctx* ctx, float* out, float* res_out, float* mean, float*
                   const float* inp1, const float* inp2, const float* weight, const float* bias,
                   int M, int C, int flags) {
     const int nv = (C / 4 + 31) / 32;
-    // persistent: a few CTAs per SM (tuning hook B200_LN_CTAS_PER_SM, default 3), never more than there are rows
-    static const int env_ctas = [] { const char* e = getenv("B200_LN_CTAS_PER_SM"); const int v = e ? atoi(e) : 0; return (v >= 1 && v <= 8) ? v : 3; }();
-    int ctas = (M + kRowWarps - 1) / kRowWarps;
-    if (!FUSED && nv <= 8 && ctas > env_ctas * ctx->num_sms) ctas = env_ctas * ctx->num_sms;  // the prefetching variants
-    const dim3 grid(ctas), block(kRowWarps * 32);
+    const dim3 grid((M + kRowWarps - 1) / kRowWarps), block(kRowWarps * 32);
     cudaError_t le = cudaSuccess;
 #define B200_LN_CASE(NV)                                                                                    \
     le = launch_pdl(ctx, layernorm_rows_kernel<NV, FUSED>, grid, block, 0, out, res_out, mean, rstd, inp1, \
@@ -207,6 +179,20 @@ __global__ void convert_bf16_kernel(uint2* __restrict__ out, const float4* __res
             const __nv_bfloat162 q1 = __floats2bfloat162_rn(x.z - __low2float(p1), x.w - __high2float(p1));
             dropped[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&q0), *reinterpret_cast<const uint32_t*>(&q1));
         }
+    }
+}
+
+__global__ void split_fp16_kernel(uint2* __restrict__ hi, uint2* __restrict__ lo, const float4* __restrict__ in, size_t n4) {
+    const size_t stride = (size_t)gridDim.x * blockDim.x;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        float4 x = in[i];
+        x.x = fminf(fmaxf(x.x, -65504.f), 65504.f); x.y = fminf(fmaxf(x.y, -65504.f), 65504.f);
+        x.z = fminf(fmaxf(x.z, -65504.f), 65504.f); x.w = fminf(fmaxf(x.w, -65504.f), 65504.f);
+        const __half2 p0 = __floats2half2_rn(x.x, x.y), p1 = __floats2half2_rn(x.z, x.w);
+        const __half2 q0 = __floats2half2_rn(x.x - __low2float(p0), x.y - __high2float(p0));
+        const __half2 q1 = __floats2half2_rn(x.z - __low2float(p1), x.w - __high2float(p1));
+        hi[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1));
+        lo[i] = make_uint2(*reinterpret_cast<const uint32_t*>(&q0), *reinterpret_cast<const uint32_t*>(&q1));
     }
 }
 
@@ -553,6 +539,16 @@ int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N,
     const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
     convert_bf16_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<uint2*>(out), reinterpret_cast<const float4*>(in), n4,
                                                        reinterpret_cast<uint2*>(lo));
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_split_fp16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* in, size_t N) {
+    if (N % 4) { ctx->last_error = "fp16 split: element count must be a multiple of 4"; return B200_ERR_SHAPE; }
+    const size_t n4 = N / 4;
+    const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
+    split_fp16_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<uint2*>(hi), reinterpret_cast<uint2*>(lo), reinterpret_cast<const float4*>(in), n4);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

@@ -140,6 +140,17 @@ int b200_attention_forward(b200_ctx* ctx, float* out, float* qkvr, float* att, c
 int b200_attention_forward_x3(b200_ctx* ctx, float* out, float* qkvr, float* att, const float* inp,
                               int B, int T, int C, int NH);
 
+/* The same operator on fp16 operands, the attention of the B200_BF16X3 mode: inp_split holds the
+ * packed buffer as two fp16 planes, [2][B,T,3C] with value = hi + lo (b200_split_fp16 of the fp32
+ * buffer; inside the driver the QKV GEMM writes it).  q.k is one kind::f16 product on the hi
+ * planes (11 significant bits, rounded to nearest), p.v the sum of two (v with both terms, p
+ * rounded to fp16 inside the kernel).  out fp32 [B,T,C]; att as above.  Values beyond the fp16
+ * range (65504) are clamped by the split. */
+int b200_attention_forward_fp16(b200_ctx* ctx, float* out, float* att, const uint16_t* inp_split,
+                                int B, int T, int C, int NH);
+/* hi[i] = fp16(inp[i]) (round to nearest even, clamped to +-65504), lo[i] = fp16(inp[i] - hi[i]); n % 4 == 0. */
+int b200_split_fp16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* inp, size_t n);
+
 /* Replaces layernorm_forward_block / _block_vectorized / _warp
  * (kernels/layernorm/1_layernorm_block.cuh:63-65, 2_...:74-76, 3_layernorm_warp.cuh:78-80).
  * mean and rstd ([B,T]) may be NULL.  Precondition: C % 4 == 0, C <= 4096. */
@@ -239,14 +250,17 @@ int b200_gpt2_load_params_file(b200_gpt2* model, const char* path, size_t header
  * B200_TF32X3 attention also runs with split operands (b200_attention_forward_x3; its scratch
  * buffer is allocated by this call).  B200_BF16 / B200_BF16X3 keep bf16 copies of the weight
  * matrices (made on the next forward) and have the layernorms, the attention and the GELU GEMM
- * write their outputs as bf16 / as two bf16 planes; attention itself stays single-pass TF32 on
- * rounded q, k, v unless b200_gpt2_set_attention_mode says otherwise.  use_graph != 0 replays the
+ * write their outputs as bf16 / as two bf16 planes; with B200_BF16 attention stays single-pass
+ * TF32 on rounded q, k, v, with B200_BF16X3 it runs on fp16 planes of q, k, v
+ * (b200_gpt2_set_attention_mode overrides).  use_graph != 0 replays the
  * forward from a CUDA graph after the first call of a given (B,T). */
 int b200_gpt2_set_options(b200_gpt2* model, int round_operands, int gemm_mode, int lmhead_mode,
                           int use_graph);
-/* Attention arithmetic: -1 (default) follows gemm_mode as described above, B200_TF32 forces the
- * single-pass kernel, B200_TF32X3 the split-operand one (with gemm_mode B200_TF32, B200_TF32X3 or
- * B200_BF16X3; allocates the scratch buffer on first use). */
+/* Attention arithmetic: -1 (default) follows gemm_mode (B200_BF16X3: fp16 attention,
+ * b200_attention_forward_fp16; B200_TF32X3: b200_attention_forward_x3; otherwise single-pass
+ * TF32), B200_TF32 forces the single-pass kernel, B200_TF32X3 the 3xTF32 one (with gemm_mode
+ * B200_TF32, B200_TF32X3 or B200_BF16X3; allocates the scratch buffer on first use), B200_BF16X3
+ * the fp16 one (gemm_mode B200_BF16X3 only). */
 int b200_gpt2_set_attention_mode(b200_gpt2* model, int mode);
 /* tokens: device int32 [B,T].  Asynchronous.  Logits: device [B,T,Vp], owned by the model. */
 int b200_gpt2_forward(b200_gpt2* model, const int* tokens, int B, int T);

@@ -428,3 +428,29 @@ def test_matmul_bf16x3_close_to_fp32(ctx, dev, orc, B, T, C, OC, has_bias, act, 
         else:
             assert np.abs(got - want).max() <= 1e-4 * scale, (np.abs(got - want).max(), scale)
         assert _rel_rms(got, want) < (5e-5 if base is None else 2e-4)
+
+
+@pytest.mark.parametrize("B,T,NH", [(1, 64, 1), (2, 128, 2), (1, 256, 12), (2, 192, 3), (1, 1024, 2), (1, 384, 25)])
+def test_attention_fp16_matches_oracle(ctx, dev, orc, B, T, NH):
+    """The attention of the default mode: q, k, v as two fp16 planes, q.k from the hi planes (11 bits,
+    rounded to nearest), p.v with both terms of v and p rounded to fp16.  On N(0,1) inputs the scores
+    reach |s| ~ 4 and carry 2^-12 relative error, i.e. the output is good to about 1e-3 absolute at
+    worst and far better on average: half the TF32 kernel's bound and a tenth of its rms."""
+    import torch
+    C = NH * 64
+    qkv = orc.fill_normal((B, T, 3 * C), 151)
+    want, wlse = orc.attention_forward(qkv, NH, precise=True)
+    planes = torch.empty((2, B, T, 3 * C), dtype=torch.int16, device="cuda")
+    ctx.split_fp16(planes[0], planes[1], dev.to(qkv), qkv.size)
+    # the split itself: hi is the nearest fp16, hi + lo carries 21 bits or more
+    hi = planes[0].cpu().numpy().view(np.float16).astype(np.float32)
+    lo = planes[1].cpu().numpy().view(np.float16).astype(np.float32)
+    assert np.array_equal(hi, qkv.astype(np.float16).astype(np.float32))
+    assert np.abs(hi + lo - qkv).max() <= 2.0 ** -20 * np.abs(qkv).max()
+    out, lse = dev.full((B, T, C), float("nan")), dev.full((B, NH, T), float("nan"))
+    ctx.attention_forward_fp16(out, lse, planes, B, T, C, NH)
+    got = dev.back(out)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() < 2.5e-3, np.abs(got - want).max()
+    assert np.sqrt(np.mean((got - want) ** 2)) < 2e-4
+    assert np.abs(dev.back(lse) - wlse).max() < 2e-3
