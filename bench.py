@@ -859,8 +859,16 @@ def run_kernel_sweep(args):
                                          (3072, 768, 0, True, False), (768, 50304, 0, False, False),
                                          (1600, 4800, 0, True, False), (1600, 6400, 1, True, True), (6400, 1600, 0, True, False)):
             cases.append(("matmul_bf16", dict(K=K, N=N, act=act, bias=bias, out_h=out_h)))
+    if args.op in ("matmul_bf16x3", "all"):
+        # K, N, act, bias, output: fp32 / split planes / accumulate onto the output
+        for (K, N, act, bias, outk) in ((768, 2304, 0, True, "split"), (768, 768, 0, True, "accumulate"), (768, 3072, 1, True, "split"),
+                                        (3072, 768, 0, True, "accumulate"), (768, 50304, 0, False, "fp32"),
+                                        (1600, 4800, 0, True, "split"), (1600, 6400, 1, True, "split"), (6400, 1600, 0, True, "accumulate")):
+            cases.append(("matmul_bf16x3", dict(K=K, N=N, act=act, bias=bias, outk=outk)))
     if args.op in ("attention", "all"):
         cases += [("attention", dict(NH=12)), ("attention", dict(NH=25))]
+    if args.op in ("attention_fp16", "all"):
+        cases += [("attention_fp16", dict(NH=12)), ("attention_fp16", dict(NH=25))]
     if args.op in ("layernorm", "all"):
         cases += [("layernorm", dict(C=768)), ("layernorm", dict(C=1600))]
     if args.op in ("fused_residual_layernorm", "all"):
@@ -890,6 +898,30 @@ def run_kernel_sweep(args):
             fn = lambda: ctx.matmul_forward_bf16(out, outh, x, w, bias, Bb, Tt, K, N, act=c["act"])
             work, unit, peak = 2.0 * M * K * N / 1e12, "TFLOP/s", peaks["bf16_burst"]
             name = f"matmul bf16 {K}->{N}" + ("+gelu" if c["act"] else "") + (" bf16 out" if c["out_h"] else "")
+        elif op == "matmul_bf16x3":
+            K, N = c["K"], c["N"]
+            xs = torch.empty(2, Bb, Tt, K, device="cuda", dtype=torch.bfloat16)
+            ctx.split_bf16(xs[0], xs[1], randn(Bb, Tt, K), M * K)
+            wh = torch.empty(N, K, device="cuda", dtype=torch.bfloat16)
+            wl = torch.empty(N, K, device="cuda", dtype=torch.bfloat16)
+            ctx.split_bf16(wh, wl, randn(N, K, std=0.02), N * K)
+            bias = randn(N, std=0.01) if c["bias"] else None
+            out = None if c["outk"] == "split" else torch.zeros(Bb, Tt, N, device="cuda")
+            outs = torch.empty(2, Bb, Tt, N, device="cuda", dtype=torch.bfloat16) if c["outk"] == "split" else None
+            fn = lambda: ctx.matmul_forward_bf16x3(out, outs, xs, wh, wl, bias, Bb, Tt, K, N, act=c["act"],
+                                                   accumulate=c["outk"] == "accumulate")
+            work, unit, peak = 2.0 * M * K * N / 1e12, "TFLOP/s", peaks["bf16_burst"] / 3
+            name = f"matmul bf16x3 {K}->{N}" + ("+gelu" if c["act"] else "") + {"split": " split out", "accumulate": " accumulate", "fp32": ""}[c["outk"]]
+        elif op == "attention_fp16":
+            NH = c["NH"]
+            Cc = NH * 64
+            planes = torch.empty(2, Bb, Tt, 3 * Cc, device="cuda", dtype=torch.float16)
+            ctx.split_fp16(planes[0], planes[1], randn(Bb, Tt, 3 * Cc), M * 3 * Cc)
+            out = torch.empty(Bb, Tt, Cc, device="cuda")
+            lse = torch.empty(Bb, NH, Tt, device="cuda")
+            fn = lambda: ctx.attention_forward_fp16(out, lse, planes, Bb, Tt, Cc, NH)
+            work, unit, peak = 4.0 * 64 * Tt * (Tt + 1) / 2 * NH * Bb / 1e12, "TFLOP/s", peaks["bf16_burst"]
+            name = f"attention fp16 B=8 T=1024 NH={NH} (causal-exact flop)"
         elif op == "attention":
             NH = c["NH"]
             Cc = NH * 64
@@ -928,7 +960,7 @@ def run_kernel_sweep(args):
                 fn = lambda k=0: ctx.encoder_forward(S[k]["out"], tok, wte, wpe, Bb, Tt, Cc)
                 work = ((2.0 * M * Cc + Tt * Cc) * 4 + M * 4) / 1e9
             unit, peak, name = "GB/s", peaks["hbm_gbs"], f"{op} [8192,{Cc}]"
-        streaming = args.stream > 1 and op not in ("matmul", "matmul_bf16", "attention")
+        streaming = args.stream > 1 and op not in ("matmul", "matmul_bf16", "matmul_bf16x3", "attention", "attention_fp16")
         torch.cuda.synchronize()
         for _ in range(args.warmup):
             fn()
@@ -971,7 +1003,8 @@ def main():
     ap.add_argument("--tp", action="store_true",
                     help="with --gpus N > 1: one tensor-parallel group over all ranks instead of batch sharding")
     ap.add_argument("--op", default=None,
-                    choices=["all", "matmul", "matmul_bf16", "attention", "layernorm", "fused_residual_layernorm", "rowwise"],
+                    choices=["all", "matmul", "matmul_bf16", "matmul_bf16x3", "attention", "attention_fp16", "layernorm",
+                             "fused_residual_layernorm", "rowwise"],
                     help="per-kernel sweep at 8192 rows instead of the forward benchmark")
     ap.add_argument("--case", type=int, default=None, help="with --op: run only this case of the family")
     ap.add_argument("--modes", default="tf32", choices=["tf32", "both"], help="with --op matmul: also time 3xTF32")
