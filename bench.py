@@ -28,7 +28,10 @@ if ROOT not in sys.path:
 # Measured DRAM traffic of the GEMM kernels of the 124M forward, launch-weighted average over the 49
 # launches of a step (ncu dram__bytes_read.sum + dram__bytes_write.sum), by arithmetic mode; the
 # capture and the per-shape figures are in the named profile.
-GEMM_DRAM_TRAFFIC = {}
+GEMM_DRAM_TRAFFIC = {
+    "bf16x3": {"dram_bytes_per_launch": 122.0e6, "algorithmic_bytes_per_launch": 155.2e6,
+               "source": "profiles/gemm_pair_bf16x3_dram_traffic_by_shape.md (lone launches per shape, launch-weighted)"},
+}
 
 METRIC = "gpt2_forward_tokens_per_s"
 UNIT = "tokens/s"
