@@ -23,6 +23,7 @@ struct GemmArgs {
     int num_m_blocks, num_n_blocks;  // tiles along M (of 128, or 256 for CTA pairs) and N
     int n_fastest;
     int flags;
+    int early_trigger;  // call griddepcontrol.launch_dependents right after this kernel's own wait instead of at its end
     int* status;
     // optional fused arg-max over columns [0, argmax_cols) of every output row (null: off);
     // only for a plain epilogue (no bias, activation, residual or rounding)

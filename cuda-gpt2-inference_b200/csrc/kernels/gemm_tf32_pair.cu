@@ -161,6 +161,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
     griddep_wait();  // set-up done; from here on global memory is touched
+    if (args.early_trigger) griddep_launch_dependents();
 
     if (warp == 0) {
         // ------------------------------------------------------------ TMA producer
@@ -310,7 +311,7 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_EPILOGUE);
     }
 
-    griddep_launch_dependents();
+    if (!args.early_trigger) griddep_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     cluster_sync_all();  // the peer is done with this CTA's shared and tensor memory
@@ -377,6 +378,7 @@ int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp
     // inp tile; otherwise rows fastest, so that they share a few weight tiles while the weights stream once
     a.n_fastest = ((size_t)N * K * 4 <= (size_t)32 << 20) ? 1 : 0;
     a.flags = flags;
+    a.early_trigger = ctx->pdl_early ? 1 : 0;
     a.status = ctx->d_status;
     a.argmax_keys = argmax_keys;
     a.argmax_cols = argmax_cols;

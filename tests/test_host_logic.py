@@ -102,3 +102,18 @@ def test_clock_sampler_without_a_gpu_returns_an_empty_record():
     s.start()
     rec = s.stop()
     assert set(("sm_mhz", "sm_max_mhz", "reasons", "samples")) <= set(rec)
+
+
+def test_shard_params_torch_equals_the_host_cut(pkg):
+    """The device-side cut of a tensor-parallel rank's parameters (used by bench.py's multi-GPU checks)
+    is the same selection as b200_gpt2_shard_params_host, for an uneven head split."""
+    import numpy as np
+    import torch
+    cfg = pkg.GPT2Config(max_seq_len=64, vocab_size=100, padded_vocab_size=128, num_layers=2, num_heads=5, channels=320)
+    n = pkg.param_offsets(cfg)[16]
+    full = np.arange(n, dtype=np.float32) * 0.001
+    for tp in (2, 4):
+        for r in range(tp):
+            want = pkg.shard_params(cfg, tp, r, full)
+            got = pkg.shard_params_torch(cfg, tp, r, torch.from_numpy(full)).numpy()
+            assert np.array_equal(got, want)
