@@ -115,7 +115,6 @@ int b200_ctx_create(b200_ctx** out, int device, void* stream) {
     }
     ctx->encode_tiled = reinterpret_cast<b200_encode_tiled_fn>(fn);
     if (const char* e = getenv("B200_PDL")) ctx->pdl = !(e[0] == '0');
-    if (const char* e = getenv("B200_PDL_EARLY")) ctx->pdl_early = (e[0] == '1');
     *out = ctx;
     return B200_OK;
 }

@@ -43,10 +43,6 @@ struct b200_ctx {
     size_t split_flag_words = 0;
     uint64_t launches = 0;
     bool pdl = true;  // launch with programmatic stream serialization (B200_PDL=0 turns it off)
-    // the tensor-core kernels let their dependents start (set up, then wait) as soon as they have passed their own
-    // wait instead of at their end: an SM that is done with this kernel begins the next one's set-up while other SMs
-    // are still on their last tile (B200_PDL_EARLY=0 turns it off)
-    bool pdl_early = false;
     std::string last_error;
     b200_encode_tiled_fn encode_tiled = nullptr;
     std::unordered_map<TensorMapKey, CUtensorMap, TensorMapKeyHash> tmap_cache;

@@ -104,7 +104,6 @@ struct AttArgs {
     int tma_out;    // T is a multiple of 128: whole tiles leave through shared memory and a TMA store
     int out_bf16;   // 1: out addresses bf16 elements (the next GEMM runs with bf16 operands); 2: two bf16 planes,
                     // bf16(o) and, B*T rows further down, bf16(o - bf16(o)) (split operands of a bf16x3 GEMM)
-    int early_trigger;  // let the next kernel start its set-up as soon as this one has passed its own wait
     int* status;    // [0] error word; [kWorkWord], [kWorkWord+1]: work and finished-CTA counters (zero between launches)
 };
 
@@ -177,7 +176,6 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __gri
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
     griddep_wait();  // set-up done; from here on global memory is touched
-    if (args.early_trigger) griddep_launch_dependents();
 
     // Every role walks the same sequence of items n = 0, 1, ... (slot n & 1) and keeps a running
     // count g of K/V blocks, from which all ring indices and barrier phases follow.
@@ -532,7 +530,7 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __gri
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_SOFTMAX);
     }
 
-    if (!args.early_trigger) griddep_launch_dependents();
+    griddep_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -579,7 +577,6 @@ int launch_attention_split(b200_ctx* ctx, float* out, float* lse, const uint16_t
     a.scale_log2 = 1.4426950408889634f / sqrtf((float)HS);
     a.round_out = (flags & ROUND_OUT_TF32) ? 1 : 0;
     a.status = ctx->d_status;
-    a.early_trigger = ctx->pdl_early ? 1 : 0;
     const int grid = a.num_items < ctx->num_sms ? a.num_items : ctx->num_sms;
     cudaError_t le = launch_pdl(ctx, attention_split_kernel, dim3(grid), dim3(kAttThreads), AttSmem::TOTAL, tm, tmo, a);
     ctx->launches++;

@@ -23,7 +23,6 @@ struct GemmArgs {
     int num_m_blocks, num_n_blocks;  // tiles along M (of 128, or 256 for CTA pairs) and N
     int n_fastest;
     int flags;
-    int early_trigger;  // call griddepcontrol.launch_dependents right after this kernel's own wait instead of at its end
     int* status;
     // optional fused arg-max over columns [0, argmax_cols) of every output row (null: off);
     // only for a plain epilogue (no bias, activation, residual or rounding)
@@ -70,7 +69,7 @@ __device__ __forceinline__ float argmax_dec(uint32_t k) {
 //   tmem_acc : tensor-memory address of the accumulator (column offset included, lane 0)
 //   row0     : global row of accumulator lane q*32
 //   col0     : global column of accumulator column 0
-//   stage2   : this warp's nbuf (1 or 2) staging buffers of 4 KB
+//   stage2   : this warp's nbuf (1, 2 or 4) staging buffers of 4 KB
 //   c_begin, c_end : the 32-column chunks of the accumulator this warp drains (two warps can share
 //                    a lane quarter and split the columns; with a bf16 output c_begin is even)
 // The bias of a 32-column chunk: lane l fetches column l's (one coalesced 128-byte load per warp)
@@ -103,8 +102,12 @@ __device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r0);
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32 + 32, r1);
         tmem_ld_wait();
-        uint8_t* sth = stage2 + (planes ? 0 : (ui & (nbuf - 1)) * 4096);
-        if (planes ? ui > 0 : ui >= nbuf) {  // the store that last used this buffer has read it
+        // buffers: without planes unit ui uses buffer ui mod nbuf; with planes its two stores use buffers
+        // 2ui and 2ui + 1 mod nbuf (one and the same buffer when there is only one)
+        const int bi = planes ? 2 * ui : ui;
+        uint8_t* sth = stage2 + (bi & (nbuf - 1)) * 4096;
+        uint8_t* stl = stage2 + ((bi + 1) & (nbuf - 1)) * 4096;
+        if (bi >= nbuf) {  // the store that last used this buffer has read it
             if (lane == 0) { if (!planes && nbuf == 2) tma_store_wait_read_but_one(); else tma_store_wait_read(); }
             __syncwarp();
         }
@@ -157,16 +160,18 @@ __device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args
             tma_store_commit();
         }
         if (planes) {
-            if (lane == 0) tma_store_wait_read();
-            __syncwarp();
+            if (bi + 1 >= nbuf) {  // with one buffer: the store just issued has to have read it
+                if (lane == 0) tma_store_wait_read();
+                __syncwarp();
+            }
 #pragma unroll
             for (int chunk = 0; chunk < 8; ++chunk)
-                *reinterpret_cast<uint4*>(sth + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
+                *reinterpret_cast<uint4*>(stl + lane * 128 + ((chunk ^ (lane & 7)) << 4)) =
                     make_uint4(lo[4 * chunk], lo[4 * chunk + 1], lo[4 * chunk + 2], lo[4 * chunk + 3]);
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0 && in_range) {
-                tma_store_2d(tmap_out, cbase, args.M + row0, sth);
+                tma_store_2d(tmap_out, cbase, args.M + row0, stl);
                 tma_store_commit();
             }
         }
@@ -264,7 +269,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         if (via_tma) {
             const int cbase = col0 + c * 32;
             if (ci >= nbuf) {  // the store that last used this buffer has read it
-                if (lane == 0) { if (nbuf == 2) tma_store_wait_read_but_one(); else tma_store_wait_read(); }
+                if (lane == 0) { if (nbuf == 4) tma_store_wait_read_but_three(); else if (nbuf == 2) tma_store_wait_read_but_one(); else tma_store_wait_read(); }
                 __syncwarp();
             }
 #pragma unroll

@@ -116,7 +116,6 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
     tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_holder;
     griddep_wait();  // set-up done; from here on global memory is touched
-    if (args.early_trigger) griddep_launch_dependents();
 
     auto tile_coords = [&](int tile, int& m_blk, int& n_blk) {
         if (args.n_fastest) { n_blk = tile % args.num_n_blocks; m_blk = tile / args.num_n_blocks; }
@@ -242,7 +241,7 @@ gemm_tf32_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
     }
 
-    if (!args.early_trigger) griddep_launch_dependents();
+    griddep_launch_dependents();
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 1) {
@@ -337,7 +336,6 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
     // otherwise sweep M fastest so the (smaller) inp stays resident while weight streams
     a.n_fastest = ((size_t)N * K * (bf16 ? 2 : 4) <= (size_t)32 << 20) ? 1 : 0;
     a.flags = flags;
-    a.early_trigger = ctx->pdl_early ? 1 : 0;
     a.status = ctx->d_status;
     a.argmax_keys = argmax_keys;
     a.argmax_cols = argmax_cols;
