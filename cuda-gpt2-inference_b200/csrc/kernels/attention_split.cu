@@ -1,28 +1,41 @@
 // Causal multi-head attention on fp16 operands (the attention of the B200_BF16X3 mode):
 //   out[b,t,h,:] = softmax_{j<=t}(q_t . k_j / sqrt(HS)) V        (HS = 64)
-// the same math, work distribution and roles as attention.cu (reference:
-// kernels/attention/3_flash_attention_permute.cuh:46-58,149-153,216-221,306,342).  Q, K and V
-// arrive the way the QKV GEMM of that mode writes them: two fp16 planes of the packed buffer
-// [B,T,3,NH,HS], value = hi + lo (22 significant bits).  The products are kind::f16 UMMAs:
+// the same math as attention.cu (reference: kernels/attention/3_flash_attention_permute.cuh:
+// 46-58,149-153,216-221,306,342).  Q, K and V arrive the way the QKV GEMM of that mode writes
+// them: two fp16 planes of the packed buffer [B,T,3,NH,HS], value = hi + lo (22 significant bits).
+// The products are kind::f16 UMMAs:
 //     S = Q K^T ~ Qhi.Khi                    O = P V ~ P.Vhi + P.Vlo
 // fp16 keeps 11 significant bits, round to nearest - what the single-pass TF32 kernel has on its
 // rounded q and k, so the scores need one product (measured on the GPT-2 forward: that part of
 // the error is 2e-5 of the 1.1e-4 rms the TF32 kernel leaves in the logits).  What dominated
-// there was P.V with V cut to 11 bits and P truncated; here V enters with both terms and P, which
-// lies in [0,1], is rounded to nearest fp16 by the softmax threads and written as packed pairs
-// into tensor memory (two keys per 32-bit column), from where the second product reads it as its
-// A operand.  Per block of 128 keys that is 4 + 16 UMMAs where the TF32 kernel issues 8 + 16 -
-// these kernels are bound by the number of UMMAs they issue, not by their arithmetic - on tiles
-// half the size (a block reads 32 + 32 KB of shared memory instead of 64 + 32).
+// there was P.V with V cut to 11 bits and P truncated; here V enters with both terms and P is
+// rounded to nearest fp16 by the softmax threads and written as packed pairs into tensor memory
+// (two keys per 32-bit column), from where the second product reads it as its A operand.
 // V is an MN-major operand; for 16-bit elements that is the ordinary 128-byte swizzle (rows of 64
 // values, 8-row atoms), so one tensor map serves every tile.
 // The two operands of a kind::f16 UMMA must have the same format: fp16 P with bf16 V is an illegal
 // instruction, which is why the QKV GEMM writes fp16 planes for this kernel.
 //
-// Persistent kernel, 11 warps: warp 0 work fetch + TMA producer (Q double buffered, K and V blocks of
-// 128 keys in separate 2-stage rings), warp 1 tensor-memory owner + S issuer, warp 10 PV issuer,
-// warps 2-9 softmax (a query row is a tensor-memory lane shared by two threads that each take 64 keys
-// and 32 output columns).  Every wait is time-bounded (prim/sm100.cuh); the work counter lives in the
+// Work distribution.  A work item is a PAIR of neighbouring query tiles (2 x 128 rows) of one
+// (batch, head); the CTA runs one pipeline per tile of the pair, and the two pipelines share
+// every K and V block that the producer loads (tile 2p needs blocks 0..2p, tile 2p+1 one more).
+// Measured on the one-tile-per-CTA version of this kernel: its time was neither the tensor pipe
+// (18 %) nor the special-function pipe (38 %) but the fact that all softmax warps are in the
+// same phase at the same time - row maximum, exponentials, tensor-memory traffic, waits -
+// so each unit idles while the others work.  Two independent tiles per CTA fall out of step by
+// themselves, and one's exponentials run under the other's waits and UMMAs.
+//
+// A query row is one thread (no exchange between threads inside the loop): 128 scores are read
+// from tensor memory into registers, reduced to the block maximum, turned into P and written
+// back as fp16 pairs.  O stays in tensor memory and accumulates over the blocks (the UMMAs add
+// to it); the reference maximum of a row is only moved - and O and the row sum rescaled - when
+// a block raises it by more than 2^8, so P never exceeds 256 (exact in fp16's range) and the
+// rescale, which needs a round trip of O through registers, is rare after the first blocks.
+//
+// Persistent kernel, 11 warps: warp 0 work fetch + TMA producer (Q pair double buffered, K and
+// V blocks of 128 keys in separate 2-stage rings), warps 1 and 2 the UMMA issuers of pipeline 0
+// and 1 (warp 1 also owns the tensor memory), warps 3-6 and 7-10 the softmax threads of
+// pipeline 0 and 1.  Every wait is time-bounded (prim/sm100.cuh); the work counter lives in the
 // context's status area and is put back to zero by the last CTA to finish.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -39,21 +52,22 @@ constexpr int BKV = 128;
 constexpr int kAttThreads = 352;
 constexpr int kBlk = 16384;  // bytes of one {64 fp16 x 128 rows} swizzled tile (one plane of Q, K or V)
 constexpr int kStages = 2;   // K/V ring
-constexpr int kSoftmaxThreads = 256;
+constexpr int kPipeThreads = 128;  // softmax threads of one pipeline (one per query row)
 
 struct AttSmem {
-    static constexpr int Q_OFF = 0;                           // 2 buffers x 2 tiles (only the first of each pair is used: hi plane)
-    static constexpr int K_OFF = Q_OFF + 4 * kBlk;            // kStages x 2 tiles (likewise)
-    static constexpr int V_OFF = K_OFF + 2 * kStages * kBlk;  // kStages x 2 tiles (hi plane, lo plane)
-    static constexpr int OUT_OFF = V_OFF + 2 * kStages * kBlk;  // output staging: 2 blocks (hs 0-31, 32-63)
-    static constexpr int X_OFF = OUT_OFF + 2 * kBlk;            // exchange buffer: 2 halves x 128 floats
-    static constexpr int BAR_OFF = X_OFF + 2 * 128 * 4;
-    static constexpr int TOTAL = 1024 + BAR_OFF + 256;
+    static constexpr int Q_OFF = 0;                              // 2 slots x 2 tiles (hi plane of each tile of the pair)
+    static constexpr int K_OFF = Q_OFF + 4 * kBlk;               // kStages x 1 tile (hi plane)
+    static constexpr int V_OFF = K_OFF + kStages * kBlk;         // kStages x 2 tiles (hi plane, lo plane)
+    static constexpr int OUT_OFF = V_OFF + 2 * kStages * kBlk;   // output staging: 2 pipelines x 2 blocks
+    static constexpr int BAR_OFF = OUT_OFF + 4 * kBlk;
+    static constexpr int TOTAL = 1024 + BAR_OFF + 512;
 };
 static_assert(AttSmem::TOTAL <= 232448 && AttSmem::TOTAL > 117 * 1024, "one CTA per SM, within 227 KB");
-constexpr int kTmemCols = 512;  // S0 [0,128)  S1 [128,256)  P [256,320) (fp16 pairs)  O0 [384,448)  O1 [448,512)
-constexpr int kPCol = 256, kOCol = 384;
+// tensor memory, per pipeline x (256 columns): S [0,128)  P [128,192) (fp16 pairs)  O [192,256)
+constexpr int kTmemCols = 512;
+constexpr int kPipeCols = 256, kPCol = 128, kOCol = 192;
 constexpr int kWorkWord = 58;  // index of the work counter in the context's 64-word status area
+constexpr float kRescaleStep = 8.0f;  // log2 of the largest P before the reference maximum moves
 
 // 2^x on the special-function unit (one instruction; 2^-inf = 0)
 __device__ __forceinline__ float ex2_approx(float x) {
@@ -68,26 +82,22 @@ __device__ __forceinline__ float fmax3(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
     return y;
 }
-// barrier among the two warps that share a group of 32 query rows
-__device__ __forceinline__ void pair_bar_sync(int id) {
-    asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+// barrier among the 128 softmax threads of one pipeline (id 1 or 2)
+__device__ __forceinline__ void pipe_bar_sync(int id) {
+    asm volatile("bar.sync %0, 128;" ::"r"(id) : "memory");
 }
-// barrier among all 256 softmax threads
-__device__ __forceinline__ void softmax_bar_sync() {
-    asm volatile("bar.sync 5, 256;" ::: "memory");
-}
-// the same barrier, returning whether `ok` holds in all 256 threads
-__device__ __forceinline__ bool softmax_bar_all(bool ok) {
+// the same barrier, returning whether `ok` holds in all 128 threads
+__device__ __forceinline__ bool pipe_bar_all(int id, bool ok) {
     uint32_t r;
     asm volatile(
         "{\n\t"
         ".reg .pred p, q;\n\t"
-        "setp.ne.u32 q, %1, 0;\n\t"
-        "bar.red.and.pred p, 5, 256, q;\n\t"
+        "setp.ne.u32 q, %2, 0;\n\t"
+        "bar.red.and.pred p, %1, 128, q;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t"
         "}\n"
         : "=r"(r)
-        : "r"((uint32_t)ok)
+        : "r"(id), "r"((uint32_t)ok)
         : "memory");
     return r != 0;
 }
@@ -97,8 +107,9 @@ struct AttArgs {
     float* lse;
     int B, T, C, NH;
     int plane_rows;  // B*T: the lo plane of the packed buffer starts this many rows below the hi plane
-    int num_qt;
-    int num_items;  // num_qt * NH * B
+    int num_qt;      // query tiles of 128 rows
+    int num_pairs;   // ceil(num_qt / 2)
+    int num_items;   // num_pairs * NH * B
     float scale_log2;
     int round_out;  // store TF32-rounded outputs (they feed only the next GEMM)
     int tma_out;    // T is a multiple of 128: whole tiles leave through shared memory and a TMA store
@@ -107,13 +118,18 @@ struct AttArgs {
     int* status;    // [0] error word; [kWorkWord], [kWorkWord+1]: work and finished-CTA counters (zero between launches)
 };
 
-// item index -> (query tile, head, batch); heavy (late) query tiles come first
-__device__ __forceinline__ void decode_item(const AttArgs& a, int item, int& qt, int& h, int& b) {
+// item index -> (tile pair, head, batch); heavy (late) pairs come first
+__device__ __forceinline__ void decode_item(const AttArgs& a, int item, int& pair, int& h, int& b) {
     const int hb = a.NH * a.B;
-    qt = a.num_qt - 1 - item / hb;
+    pair = a.num_pairs - 1 - item / hb;
     const int r = item % hb;
     h = r % a.NH;
     b = r / a.NH;
+}
+// number of key blocks pipeline x works through for a pair (0: the pair has no second tile)
+__device__ __forceinline__ int pipe_blocks(const AttArgs& a, int pair, int x) {
+    const int qt = 2 * pair + x;
+    return qt < a.num_qt ? qt + 1 : 0;
 }
 
 __global__ void __launch_bounds__(kAttThreads, 1)
@@ -123,23 +139,21 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __gri
     uint8_t* q_s = smem + AttSmem::Q_OFF;
     uint8_t* k_s = smem + AttSmem::K_OFF;
     uint8_t* v_s = smem + AttSmem::V_OFF;
-    uint8_t* out_s = smem + AttSmem::OUT_OFF;
-    float* xchg = reinterpret_cast<float*>(smem + AttSmem::X_OFF);  // [2][128]
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + AttSmem::BAR_OFF);
     uint64_t* item_full = bars;        // [2]  work item published
     uint64_t* item_empty = bars + 2;   // [2]  all consumers are done with the item slot
-    uint64_t* q_full = bars + 4;       // [2]  TMA: Q landed
-    uint64_t* q_empty = bars + 6;      // [2]  every S of the item retired
+    uint64_t* q_full = bars + 4;       // [2]  TMA: the Q tiles of the pair landed
+    uint64_t* q_empty = bars + 6;      // [2]  every S of the item retired (both pipelines)
     uint64_t* k_full = bars + 8;       // [2]  TMA: K block landed
-    uint64_t* k_empty = bars + 10;     // [2]  S of the block retired
+    uint64_t* k_empty = bars + 10;     // [2]  S of the block retired in both pipelines
     uint64_t* v_full = bars + 12;      // [2]  TMA: V block landed
-    uint64_t* v_empty = bars + 14;     // [2]  PV of the block retired
-    uint64_t* s_full = bars + 16;      // [2]  S computed
-    uint64_t* s_free = bars + 18;      // [2]  S read into registers by all softmax threads
-    uint64_t* p_full = bars + 20;      // [1]  P written by all softmax threads
-    uint64_t* o_full = bars + 21;      // [2]  O_j in tensor memory
-    uint64_t* drain_bar = bars + 23;   // [1]
-    int* item_slot = reinterpret_cast<int*>(bars + 24);              // [2]
+    uint64_t* v_empty = bars + 14;     // [2]  PV of the block retired in both pipelines
+    uint64_t* s_full = bars + 16;      // [pipeline]  S computed
+    uint64_t* s_free = bars + 18;      // [pipeline]  S read into registers by all threads of the pipeline
+    uint64_t* p_full = bars + 20;      // [pipeline]  P written (and O rescaled if needed)
+    uint64_t* o_full = bars + 22;      // [pipeline]  P V of a block retired: O updated, P free
+    uint64_t* drain_bar = bars + 24;   // [pipeline]
+    int* item_slot = reinterpret_cast<int*>(bars + 26);              // [2]
     uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(item_slot + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
 
@@ -149,19 +163,19 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __gri
     if (threadIdx.x == 0) {
         for (int s = 0; s < 2; ++s) {
             mbar_init(&item_full[s], 1);
-            mbar_init(&item_empty[s], kSoftmaxThreads + 2);  // softmax threads + the two issuers
+            mbar_init(&item_empty[s], 2 * kPipeThreads + 2);  // softmax threads + the two issuers
             mbar_init(&q_full[s], 1);
-            mbar_init(&q_empty[s], 1);
+            mbar_init(&q_empty[s], 2);
             mbar_init(&k_full[s], 1);
-            mbar_init(&k_empty[s], 1);
+            mbar_init(&k_empty[s], 2);
             mbar_init(&v_full[s], 1);
-            mbar_init(&v_empty[s], 1);
+            mbar_init(&v_empty[s], 2);
             mbar_init(&s_full[s], 1);
-            mbar_init(&s_free[s], kSoftmaxThreads);
+            mbar_init(&s_free[s], kPipeThreads);
+            mbar_init(&p_full[s], kPipeThreads);
             mbar_init(&o_full[s], 1);
+            mbar_init(&drain_bar[s], 1);
         }
-        mbar_init(p_full, kSoftmaxThreads);
-        mbar_init(drain_bar, 1);
         *abort_flag = 0;
         fence_barrier_init();
         tma_prefetch_desc(&tmap_qkv);
@@ -177,8 +191,10 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __gri
     const uint32_t tmem_base = *tmem_holder;
     griddep_wait();  // set-up done; from here on global memory is touched
 
-    // Every role walks the same sequence of items n = 0, 1, ... (slot n & 1) and keeps a running
-    // count g of K/V blocks, from which all ring indices and barrier phases follow.
+    // Every role walks the same sequence of items n = 0, 1, ... (slot n & 1).  The K/V ring is
+    // indexed by a running count of the blocks the producer loads (per item: as many as the
+    // longer pipeline needs); each pipeline keeps its own running count of the blocks it works
+    // through, from which the phases of its own barriers follow.
     if (warp == 0) {
         // ------------------------------------------- work fetch + TMA producer
         if (lane == 0) {
@@ -192,341 +208,348 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __gri
                 item_slot[slot] = item;
                 mbar_arrive(&item_full[slot]);  // release: the slot write is visible to the waiters
                 if (item < 0) break;
-                int qt, h, b;
-                decode_item(args, item, qt, h, b);
-                const int row_base = b * args.T, q0 = qt * BQ, n_kv = qt + 1;
+                int pair, h, b;
+                decode_item(args, item, pair, h, b);
+                const int n1 = pipe_blocks(args, pair, 1);
+                const int n_item = n1 > 0 ? n1 : pipe_blocks(args, pair, 0);
+                const int row_base = b * args.T, q0 = 2 * pair * BQ;
                 const int xq = h * HS, xk = args.C + h * HS, xv = 2 * args.C + h * HS;
                 if (!mbar_wait(&q_empty[slot], ((n >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                mbar_arrive_expect_tx(&q_full[slot], kBlk);
+                mbar_arrive_expect_tx(&q_full[slot], n1 > 0 ? 2 * kBlk : kBlk);
                 tma_load_2d(q_s + (2 * slot) * kBlk, &tmap_qkv, xq, row_base + q0, &q_full[slot]);
-                for (int j = 0; j < n_kv; ++j, ++g) {
-                    const int s = g % kStages;
-                    const uint32_t ph = ((g / kStages) & 1) ^ 1;
-                    const int y = row_base + j * BKV;
-                    // K is free again as soon as its S has retired, V only after its PV: separate
-                    // rings let the S issuer run two blocks ahead with two stages each
-                    if (!mbar_wait(&k_empty[s], ph, abort_flag)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&k_full[s], kBlk);
-                    tma_load_2d(k_s + (2 * s) * kBlk, &tmap_qkv, xk, y, &k_full[s]);
-                    if (!mbar_wait(&v_empty[s], ph, abort_flag)) { ok = false; break; }
-                    mbar_arrive_expect_tx(&v_full[s], 2 * kBlk);
-                    tma_load_2d(v_s + (2 * s) * kBlk, &tmap_qkv, xv, y, &v_full[s]);
-                    tma_load_2d(v_s + (2 * s + 1) * kBlk, &tmap_qkv, xv, args.plane_rows + y, &v_full[s]);
+                if (n1 > 0) tma_load_2d(q_s + (2 * slot + 1) * kBlk, &tmap_qkv, xq, row_base + q0 + BQ, &q_full[slot]);
+                // K runs one block ahead of V: K_{j+1} is wanted a whole block earlier than V_j (the
+                // scores of block j+1 are computed while the softmax threads work on block j), and
+                // its stage is free as soon as S_{j-1} has retired, V_j's only after P V of block j-2
+                for (int j = -1; j < n_item && ok; ++j) {
+                    if (j + 1 < n_item) {
+                        const uint32_t gk = g + j + 1;
+                        const int s = gk % kStages;
+                        if (!mbar_wait(&k_empty[s], ((gk / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                        mbar_arrive_expect_tx(&k_full[s], kBlk);
+                        tma_load_2d(k_s + s * kBlk, &tmap_qkv, xk, row_base + (j + 1) * BKV, &k_full[s]);
+                    }
+                    if (j >= 0) {
+                        const uint32_t gv = g + j;
+                        const int s = gv % kStages;
+                        const int y = row_base + j * BKV;
+                        if (!mbar_wait(&v_empty[s], ((gv / kStages) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                        mbar_arrive_expect_tx(&v_full[s], 2 * kBlk);
+                        tma_load_2d(v_s + (2 * s) * kBlk, &tmap_qkv, xv, y, &v_full[s]);
+                        tma_load_2d(v_s + (2 * s + 1) * kBlk, &tmap_qkv, xv, args.plane_rows + y, &v_full[s]);
+                    }
                 }
+                g += n_item;
             }
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_PRODUCER);
         }
-    } else if (warp == 1) {
-        // ------------------------------------------------------- S = Q K^T issuer
+    } else if (warp <= 2) {
+        // ------------------------------------- UMMA issuer of pipeline x: S = Q K^T and O += P V
+        // Order of issue per block j: S_{j+1} (as soon as the softmax threads have taken S_j into
+        // registers), then P_j V_j (when P_j is written) - so the next scores are ready long
+        // before the softmax threads come back for them.
+        // A barrier that counts one arrival per pipeline (q_empty, k_empty, v_empty) is only
+        // arrived on after the matching "full" barrier of the same use has been seen: that orders
+        // the arrival behind the completion of the barrier's previous phase also for a pipeline
+        // that has no use for the block (the shorter tile of the pair, or a pair without a
+        // second tile).
         if (lane == 0) {
+            const int x = warp - 1;
             constexpr uint32_t idesc_s = make_idesc_f16(BQ, BKV, 0);  // N = 128 keys
+            constexpr uint32_t idesc_o = make_idesc_f16(BQ, HS, 1);   // N = 64, V MN-major
+            const uint32_t tm = tmem_base + x * kPipeCols;
             bool ok = true;
-            uint32_t g = 0;
+            uint32_t g0 = 0;  // blocks loaded before this item (ring position)
+            uint32_t gx = 0;  // blocks of this pipeline before this item
             for (uint32_t n = 0; ok; ++n) {
                 const int slot = n & 1;
                 if (!mbar_wait(&item_full[slot], (n >> 1) & 1, abort_flag)) { ok = false; break; }
                 const int item = item_slot[slot];
                 if (item < 0) break;
-                int qt, h, b;
-                decode_item(args, item, qt, h, b);
-                const int n_kv = qt + 1;
+                int pair, h, b;
+                decode_item(args, item, pair, h, b);
+                const int n1 = pipe_blocks(args, pair, 1);
+                const int n_item = n1 > 0 ? n1 : pipe_blocks(args, pair, 0);
+                const int n_kv = pipe_blocks(args, pair, x);
                 if (!mbar_wait(&q_full[slot], (n >> 1) & 1, abort_flag)) { ok = false; break; }
-                for (int j = 0; j < n_kv; ++j, ++g) {
-                    const int s = g & 1, ks = g % kStages;
-                    if (!mbar_wait(&k_full[ks], (g / kStages) & 1, abort_flag)) { ok = false; break; }
-                    // the softmax has read the scores of two blocks ago out of these columns
-                    if (!mbar_wait(&s_free[s], ((g >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-                    tc_fence_after_sync();
-                    const uint32_t d = tmem_base + s * BKV;
+                if (n_kv == 0) mbar_arrive(&q_empty[slot]);
+                const uint32_t q_addr = smem_u32(q_s + (2 * slot + x) * kBlk);
+                // j walks the blocks of the item; S of block j and P V of block j-1 per step
+                for (int j = 0; j <= n_item && ok; ++j) {
+                    if (j < n_item) {
+                        const uint32_t g = g0 + j;
+                        const int ks = g % kStages;
+                        if (!mbar_wait(&k_full[ks], (g / kStages) & 1, abort_flag)) { ok = false; break; }
+                        if (j < n_kv) {
+                            // the softmax threads have read the previous scores out of these columns
+                            if (!mbar_wait(&s_free[x], ((gx + j) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                            tc_fence_after_sync();
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {  // 16 of the 64 head dimensions (32 bytes of the swizzled row) per instruction
-                        const uint32_t off = kk * 32;
-                        const uint64_t qh = make_smem_desc_sw128(smem_u32(q_s + 2 * slot * kBlk) + off, 16, 1024);
-                        const uint64_t kh = make_smem_desc_sw128(smem_u32(k_s + 2 * ks * kBlk) + off, 16, 1024);
-                        umma_f16_ss(d, qh, kh, idesc_s, kk != 0);
+                            for (int kk = 0; kk < 4; ++kk) {  // 16 of the 64 head dimensions (32 bytes of the swizzled row) per instruction
+                                const uint64_t qh = make_smem_desc_sw128(q_addr + kk * 32, 16, 1024);
+                                const uint64_t kh = make_smem_desc_sw128(smem_u32(k_s + ks * kBlk) + kk * 32, 16, 1024);
+                                umma_f16_ss(tm, qh, kh, idesc_s, kk != 0);
+                            }
+                            umma_commit(&s_full[x]);
+                            umma_commit(&k_empty[ks]);
+                            if (j == n_kv - 1) umma_commit(&q_empty[slot]);  // Q may be overwritten once these UMMAs have retired
+                        } else {
+                            mbar_arrive(&k_empty[ks]);
+                        }
                     }
-                    umma_commit(&s_full[s]);
-                    umma_commit(&k_empty[ks]);
+                    if (j > 0) {
+                        const int i = j - 1;
+                        const uint32_t g = g0 + i;
+                        const int vs = g % kStages;
+                        if (!mbar_wait(&v_full[vs], (g / kStages) & 1, abort_flag)) { ok = false; break; }
+                        if (i < n_kv) {
+                            if (!mbar_wait(&p_full[x], (gx + i) & 1, abort_flag)) { ok = false; break; }
+                            tc_fence_after_sync();
+#pragma unroll
+                            for (int ks = 0; ks < BKV / 16; ++ks) {
+                                // A: P in tensor memory, 16 keys = 8 columns of packed pairs per instruction
+                                const uint32_t pa = tm + kPCol + ks * 8;
+                                // B: V, MN-major: 16 keys = 16 rows of 128 bytes = two 8-row swizzle atoms 1024 bytes apart
+                                const uint64_t vh = make_smem_desc_sw128(smem_u32(v_s + 2 * vs * kBlk) + ks * 2048, 16, 1024);
+                                const uint64_t vl = make_smem_desc_sw128(smem_u32(v_s + (2 * vs + 1) * kBlk) + ks * 2048, 16, 1024);
+                                umma_f16_ts(tm + kOCol, pa, vh, idesc_o, (i | ks) != 0);  // the first block of an item starts O afresh
+                                umma_f16_ts(tm + kOCol, pa, vl, idesc_o, 1);
+                            }
+                            umma_commit(&o_full[x]);
+                            umma_commit(&v_empty[vs]);
+                        } else {
+                            mbar_arrive(&v_empty[vs]);
+                        }
+                    }
                 }
-                umma_commit(&q_empty[slot]);  // Q may be overwritten once these UMMAs have retired
+                g0 += n_item;
+                gx += n_kv;
                 mbar_arrive(&item_empty[slot]);
             }
-            if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
-        }
-    } else if (warp == 10) {
-        // --------------------------------------------------------- O = P V issuer
-        if (lane == 0) {
-            constexpr uint32_t idesc_o = make_idesc_f16(BQ, HS, 1);  // N = 64, V MN-major
-            bool ok = true;
-            uint32_t g = 0;
-            for (uint32_t n = 0; ok; ++n) {
-                const int slot = n & 1;
-                if (!mbar_wait(&item_full[slot], (n >> 1) & 1, abort_flag)) { ok = false; break; }
-                const int item = item_slot[slot];
-                if (item < 0) break;
-                int qt, h, b;
-                decode_item(args, item, qt, h, b);
-                const int n_kv = qt + 1;
-                for (int j = 0; j < n_kv; ++j, ++g) {
-                    const int s = g & 1, ks3 = g % kStages;
-                    if (!mbar_wait(&v_full[ks3], (g / kStages) & 1, abort_flag)) { ok = false; break; }
-                    if (!mbar_wait(p_full, g & 1, abort_flag)) { ok = false; break; }
-                    tc_fence_after_sync();
-                    const uint32_t d = tmem_base + kOCol + s * HS;
-#pragma unroll
-                    for (int ks = 0; ks < BKV / 16; ++ks) {
-                        // A: P_j in tensor memory, 16 keys = 8 columns of packed pairs per instruction
-                        const uint32_t pa = tmem_base + kPCol + ks * 8;
-                        // B: V, MN-major: 16 keys = 16 rows of 128 bytes = two 8-row swizzle atoms 1024 bytes apart
-                        const uint64_t vh = make_smem_desc_sw128(smem_u32(v_s + 2 * ks3 * kBlk) + ks * 2048, 16, 1024);
-                        const uint64_t vl = make_smem_desc_sw128(smem_u32(v_s + (2 * ks3 + 1) * kBlk) + ks * 2048, 16, 1024);
-                        umma_f16_ts(d, pa, vh, idesc_o, ks != 0);
-                        umma_f16_ts(d, pa, vl, idesc_o, 1);
-                    }
-                    umma_commit(&o_full[s]);
-                    umma_commit(&v_empty[ks3]);
-                }
-                mbar_arrive(&item_empty[slot]);
-            }
-            // everything issued by both issuers has retired once this commit arrives (the last PV
-            // depends on the last S through the softmax)
-            umma_commit(drain_bar);
-            if (!mbar_wait(drain_bar, 0, abort_flag)) ok = false;
+            // everything this issuer has issued has retired once this commit arrives
+            umma_commit(&drain_bar[x]);
+            if (!mbar_wait(&drain_bar[x], 0, abort_flag)) ok = false;
             if (!ok) atomicCAS(args.status, 0, DEV_TIMEOUT_MMA);
         }
     } else {
         // ----------------------------------------------------------------- softmax
+        const int x = (warp - 3) >> 2;           // pipeline = tile of the pair
         const int qd = warp & 3;                 // tensor-memory lane quarter of this warp
-        const int hf = (warp - 2) >> 2;          // which 64 keys / 32 output columns
         const int r = qd * 32 + lane;            // query row inside the tile = tensor-memory lane
-        const uint32_t lane_addr = uint32_t(qd * 32) << 16;
-        const int bar_id = 1 + qd;               // named barrier of the two warps sharing the rows
-        const uint32_t p_addr = tmem_base + lane_addr + kPCol + hf * 32;     // 64 keys = 32 columns of packed pairs
-        const int c0 = hf * 64;                  // first key column of this thread within a block
+        const uint32_t tm = tmem_base + (uint32_t(qd * 32) << 16) + x * kPipeCols;
+        const int bar_id = 1 + x;
+        const bool leader = (threadIdx.x == 96 + x * kPipeThreads);  // issues the pipeline's TMA stores
+        uint8_t* out_s = smem + AttSmem::OUT_OFF + x * 2 * kBlk;
         bool ok = true;
-        uint32_t g = 0;
-        // All softmax warps leave together: the decision is taken once per item, on a barrier
-        // that also tells whether any of the 256 threads has had a wait run out.  Inside an item
-        // there is no early exit: after a failed wait the remaining waits are skipped but every
-        // barrier is still executed, so no warp can be left alone in one (the results are
-        // discarded and the status word says why).
+        uint32_t gx = 0;  // blocks of this pipeline before this item
+        // The threads of a pipeline leave together: the decision is taken once per item, on a
+        // barrier that also tells whether any of them has had a wait run out.  Inside an item there
+        // is no early exit: after a failed wait the remaining waits are skipped but every barrier
+        // is still executed, so no warp can be left alone in one (the results are discarded and
+        // the status word says why).
         for (uint32_t n = 0;; ++n) {
             const int slot = n & 1;
             if (ok && !mbar_wait(&item_full[slot], (n >> 1) & 1, abort_flag)) ok = false;
-            const bool all_ok = softmax_bar_all(ok);
+            const bool all_ok = pipe_bar_all(bar_id, ok);
             const int item = all_ok ? item_slot[slot] : -1;
             if (item < 0) break;
-            int qt, h, b;
-            decode_item(args, item, qt, h, b);
-            const int n_kv = qt + 1, q0 = qt * BQ, row_base = b * args.T;
-            float m = -INFINITY, l = 0.f, alpha_prev = 0.f;
-            float o_acc[HS / 2];
+            int pair, h, b;
+            decode_item(args, item, pair, h, b);
+            const int n_kv = pipe_blocks(args, pair, x);
+            if (n_kv == 0) {  // the pair has no second tile
+                mbar_arrive(&item_empty[slot]);
+                continue;
+            }
+            const int q0 = (2 * pair + x) * BQ, row_base = b * args.T;
+            float m_ref = -INFINITY, l = 0.f;
+            for (int j = 0; j < n_kv; ++j) {
+                const uint32_t gi = gx + j;
+                const bool diag = (j == n_kv - 1);
+                uint32_t t[4][32];  // this row's 128 scores of the block
+                if (ok && !mbar_wait(&s_full[x], gi & 1, abort_flag)) ok = false;
+                tc_fence_after_sync();
 #pragma unroll
-            for (int i = 0; i < HS / 2; ++i) o_acc[i] = 0.f;
-
-            // Every tensor-memory read of an iteration is done before p_full is signalled, i.e.
-            // while the tensor core is not running O = P V (whose P operand also comes out of
-            // tensor memory); the arithmetic on the values runs under the UMMAs.
-            uint32_t t0[32], t1[32];  // this thread's 64 scores of the current block
-            if (ok && !mbar_wait(&s_full[g & 1], (g >> 1) & 1, abort_flag)) ok = false;
-            tc_fence_after_sync();
-            {
-                const uint32_t s_addr = tmem_base + lane_addr + (g & 1) * BKV + hf * 64;
-                tmem_ld_32x32b_x32(s_addr, t0);
-                tmem_ld_32x32b_x32(s_addr + 32, t1);
+                for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(tm + c * 32, t[c]);
                 tmem_ld_wait();
                 tc_fence_before_sync();
-                mbar_arrive(&s_free[g & 1]);
-            }
-            for (int j = 0; j < n_kv; ++j, ++g) {
-                const bool diag = (j == n_kv - 1);
+                mbar_arrive(&s_free[x]);  // the next block's scores may overwrite the columns
                 // row maximum of the raw scores (the scale is positive, so it commutes with max)
-                // (four independent chains of three-input maxima: the loop is latency-bound)
                 float pm0 = -INFINITY, pm1 = -INFINITY, pm2 = -INFINITY, pm3 = -INFINITY;
                 if (!diag) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        pm0 = fmax3(pm0, __uint_as_float(t0[i]), __uint_as_float(t0[i + 1]));
-                        pm1 = fmax3(pm1, __uint_as_float(t0[i + 2]), __uint_as_float(t0[i + 3]));
-                        pm2 = fmax3(pm2, __uint_as_float(t1[i]), __uint_as_float(t1[i + 1]));
-                        pm3 = fmax3(pm3, __uint_as_float(t1[i + 2]), __uint_as_float(t1[i + 3]));
-                    }
-                } else {
+                    for (int c = 0; c < 4; ++c) {
 #pragma unroll
-                    for (int i = 0; i < 32; i += 4) {
-                        pm0 = fmax3(pm0, c0 + i <= r ? __uint_as_float(t0[i]) : -INFINITY, c0 + i + 1 <= r ? __uint_as_float(t0[i + 1]) : -INFINITY);
-                        pm1 = fmax3(pm1, c0 + i + 2 <= r ? __uint_as_float(t0[i + 2]) : -INFINITY, c0 + i + 3 <= r ? __uint_as_float(t0[i + 3]) : -INFINITY);
-                        pm2 = fmax3(pm2, c0 + 32 + i <= r ? __uint_as_float(t1[i]) : -INFINITY, c0 + 32 + i + 1 <= r ? __uint_as_float(t1[i + 1]) : -INFINITY);
-                        pm3 = fmax3(pm3, c0 + 32 + i + 2 <= r ? __uint_as_float(t1[i + 2]) : -INFINITY, c0 + 32 + i + 3 <= r ? __uint_as_float(t1[i + 3]) : -INFINITY);
+                        for (int i = 0; i < 32; i += 8) {
+                            pm0 = fmax3(pm0, __uint_as_float(t[c][i]), __uint_as_float(t[c][i + 1]));
+                            pm1 = fmax3(pm1, __uint_as_float(t[c][i + 2]), __uint_as_float(t[c][i + 3]));
+                            pm2 = fmax3(pm2, __uint_as_float(t[c][i + 4]), __uint_as_float(t[c][i + 5]));
+                            pm3 = fmax3(pm3, __uint_as_float(t[c][i + 6]), __uint_as_float(t[c][i + 7]));
+                        }
+                    }
+                } else {  // keys behind the query do not count (key c <= row r inside the diagonal block)
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                        for (int i = 0; i < 32; i += 4) {
+                            const int k0 = c * 32 + i;
+                            pm0 = fmaxf(pm0, k0 <= r ? __uint_as_float(t[c][i]) : -INFINITY);
+                            pm1 = fmaxf(pm1, k0 + 1 <= r ? __uint_as_float(t[c][i + 1]) : -INFINITY);
+                            pm2 = fmaxf(pm2, k0 + 2 <= r ? __uint_as_float(t[c][i + 2]) : -INFINITY);
+                            pm3 = fmaxf(pm3, k0 + 3 <= r ? __uint_as_float(t[c][i + 3]) : -INFINITY);
+                        }
                     }
                 }
-                float pm = fmaxf(fmaxf(pm0, pm1), fmaxf(pm2, pm3));
-                xchg[hf * 128 + r] = pm;
-                pair_bar_sync(bar_id);
-                pm = fmaxf(pm, xchg[(hf ^ 1) * 128 + r]);
-                pair_bar_sync(bar_id);  // both have read before either writes again
-                const float mx = fmaxf(m, pm * args.scale_log2);  // log2 domain; finite (column 0 <= row)
-                const float alpha = ex2_approx(m - mx);           // 0 on the first block (m = -inf)
-                m = mx;
-                // P = exp2(s*scale - m): one FMA + one special-function op per score; neighbouring keys
-                // are packed two to a register as fp16, the A operand of O = P V.  The row sum is taken
-                // from the fp32 values.
+                // log2 domain; finite (key 0 of every block counts for every row)
+                const float cand = fmaxf(m_ref, fmaxf(fmaxf(pm0, pm1), fmaxf(pm2, pm3)) * args.scale_log2);
+                // The reference maximum moves for the whole warp at once (the tensor-memory round
+                // trip of O is a warp-wide operation), and only when some row needs it.
+                const bool moved = __any_sync(0xffffffffu, cand > m_ref + kRescaleStep);
+                float alpha = 1.f;
+                if (moved) {
+                    alpha = ex2_approx(m_ref - cand);  // 0 on the first block (m_ref = -inf)
+                    m_ref = cand;
+                }
+                // P = exp2(s*scale - m_ref): one FMA + one special-function op per score; neighbouring
+                // keys are packed two to a register as fp16, the A operand of O += P V.  The row sum is
+                // taken from the fp32 values.
                 float sum0 = 0.f, sum1 = 0.f, sum2 = 0.f, sum3 = 0.f;
-                const float neg_mx = -mx;
-                uint32_t pk[32];  // keys (c0 + 2k, c0 + 2k + 1) in register k
+                const float neg_m = -m_ref;
+                uint32_t pk[2][32];  // keys (2k, 2k+1) of the block in register k
 #pragma unroll
-                for (int k = 0; k < 16; ++k) {
-                    float a0 = ex2_approx(fmaf(__uint_as_float(t0[2 * k]), args.scale_log2, neg_mx));
-                    float a1 = ex2_approx(fmaf(__uint_as_float(t0[2 * k + 1]), args.scale_log2, neg_mx));
-                    float b0 = ex2_approx(fmaf(__uint_as_float(t1[2 * k]), args.scale_log2, neg_mx));
-                    float b1 = ex2_approx(fmaf(__uint_as_float(t1[2 * k + 1]), args.scale_log2, neg_mx));
-                    if (diag) {  // keys behind the query do not count
-                        if (c0 + 2 * k > r) a0 = 0.f;
-                        if (c0 + 2 * k + 1 > r) a1 = 0.f;
-                        if (c0 + 32 + 2 * k > r) b0 = 0.f;
-                        if (c0 + 32 + 2 * k + 1 > r) b1 = 0.f;
+                for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                    for (int k = 0; k < 16; k += 2) {
+                        float a0 = ex2_approx(fmaf(__uint_as_float(t[c][2 * k]), args.scale_log2, neg_m));
+                        float a1 = ex2_approx(fmaf(__uint_as_float(t[c][2 * k + 1]), args.scale_log2, neg_m));
+                        float b0 = ex2_approx(fmaf(__uint_as_float(t[c][2 * k + 2]), args.scale_log2, neg_m));
+                        float b1 = ex2_approx(fmaf(__uint_as_float(t[c][2 * k + 3]), args.scale_log2, neg_m));
+                        if (diag) {
+                            const int k0 = c * 32 + 2 * k;
+                            if (k0 > r) a0 = 0.f;
+                            if (k0 + 1 > r) a1 = 0.f;
+                            if (k0 + 2 > r) b0 = 0.f;
+                            if (k0 + 3 > r) b1 = 0.f;
+                        }
+                        sum0 += a0;
+                        sum1 += a1;
+                        sum2 += b0;
+                        sum3 += b1;
+                        const __half2 ah = __floats2half2_rn(a0, a1), bh = __floats2half2_rn(b0, b1);
+                        pk[c >> 1][(c & 1) * 16 + k] = *reinterpret_cast<const uint32_t*>(&ah);
+                        pk[c >> 1][(c & 1) * 16 + k + 1] = *reinterpret_cast<const uint32_t*>(&bh);
                     }
-                    sum0 += a0;
-                    sum1 += a1;
-                    sum2 += b0;
-                    sum3 += b1;
-                    const __half2 ah = __floats2half2_rn(a0, a1), bh = __floats2half2_rn(b0, b1);
-                    pk[k] = *reinterpret_cast<const uint32_t*>(&ah);
-                    pk[16 + k] = *reinterpret_cast<const uint32_t*>(&bh);
                 }
-                // O_{j-1} has retired: its result can be read and the P columns overwritten
-                uint32_t o_prev[32];
+                // P V of the previous block has retired: the P columns are free and O is complete
                 if (j > 0) {
-                    if (ok && !mbar_wait(&o_full[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag)) ok = false;
+                    if (ok && !mbar_wait(&o_full[x], (gi - 1) & 1, abort_flag)) ok = false;
                     tc_fence_after_sync();
-                    tmem_ld_32x32b_x32(tmem_base + lane_addr + kOCol + ((g - 1) & 1) * HS + hf * 32, o_prev);
+                    if (moved) {  // O *= alpha, through registers
+#pragma unroll
+                        for (int hh = 0; hh < 2; ++hh) {
+                            uint32_t o[32];
+                            tmem_ld_32x32b_x32(tm + kOCol + hh * 32, o);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                            tmem_st_32x32b_x32(tm + kOCol + hh * 32, o);
+                        }
+                    }
                 }
-                tmem_st_32x32b_x32(p_addr, pk);
-                l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));  // this thread's half of the row sum
+                tmem_st_32x32b_x32(tm + kPCol, pk[0]);
+                tmem_st_32x32b_x32(tm + kPCol + 32, pk[1]);
                 tmem_st_wait();
-                // the next block's scores, while nothing else is using tensor memory
-                if (j + 1 < n_kv) {
-                    const int sn = (g + 1) & 1;
-                    if (ok && !mbar_wait(&s_full[sn], ((g + 1) >> 1) & 1, abort_flag)) ok = false;
-                    tc_fence_after_sync();
-                    const uint32_t s_addr = tmem_base + lane_addr + sn * BKV + hf * 64;
-                    tmem_ld_32x32b_x32(s_addr, t0);
-                    tmem_ld_32x32b_x32(s_addr + 32, t1);
-                }
-                tmem_ld_wait();
                 tc_fence_before_sync();
-                if (j + 1 < n_kv) mbar_arrive(&s_free[(g + 1) & 1]);
-                mbar_arrive(p_full);
-                // under the UMMAs of O_j: fold O_{j-1} in
-                if (j > 0) {
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) o_acc[i] = o_acc[i] * alpha_prev + __uint_as_float(o_prev[i]);
-                }
-                alpha_prev = alpha;
+                mbar_arrive(&p_full[x]);
+                l = l * alpha + ((sum0 + sum1) + (sum2 + sum3));
             }
-            // the last block of the item (g has moved past it)
-            if (ok && !mbar_wait(&o_full[(g - 1) & 1], ((g - 1) >> 1) & 1, abort_flag)) ok = false;
+            gx += n_kv;
+            // the last P V of the item
+            if (ok && !mbar_wait(&o_full[x], (gx - 1) & 1, abort_flag)) ok = false;
             tc_fence_after_sync();
-            {
-                uint32_t t[32];
-                tmem_ld_32x32b_x32(tmem_base + lane_addr + kOCol + ((g - 1) & 1) * HS + hf * 32, t);
-                tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) o_acc[i] = o_acc[i] * alpha_prev + __uint_as_float(t[i]);
-            }
-            // combine the two halves of the row sum
-            xchg[hf * 128 + r] = l;
-            pair_bar_sync(bar_id);
-            l += xchg[(hf ^ 1) * 128 + r];
-            pair_bar_sync(bar_id);
             const int t_idx = q0 + r;
             const float inv_l = 1.0f / l;
+            const bool planes = args.out_bf16 == 2;
             if (args.tma_out) {
-                // Whole tile: each thread puts its 32 columns (one 128-byte row of block hf) into
-                // the staging buffer in the 128-byte-swizzled layout, and one thread sends the two
-                // blocks off with TMA stores - full-line writes instead of 16-byte pieces of 32
-                // different rows per instruction.
-                if (threadIdx.x == 64) tma_store_wait_read();  // the previous tile has left the buffer
-                softmax_bar_sync();
+                // Whole tile: each thread puts its row into the pipeline's staging buffer in the
+                // 128-byte-swizzled layout, and one thread sends the blocks off with TMA stores.
+                if (leader) tma_store_wait_read();  // the previous tile has left the buffer
+                pipe_bar_sync(bar_id);
+            }
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {  // 32 output columns at a time
+                uint32_t o[32];
+                tmem_ld_32x32b_x32(tm + kOCol + hh * 32, o);
+                tmem_ld_wait();
                 if (args.out_bf16) {
-                    // 64 bf16 columns are one 128-byte row: this thread's 32 columns are chunks
-                    // 4*hf .. 4*hf+3 of row r, and the tile leaves as one {128 x 64} store (two with
-                    // split outputs: the dropped parts are staged in the second block)
-                    uint4* rowh = reinterpret_cast<uint4*>(out_s + r * 128);
-                    uint4* rowl = reinterpret_cast<uint4*>(out_s + kBlk + r * 128);
-                    const bool planes = args.out_bf16 == 2;
+                    // 64 bf16 columns are one 128-byte row: chunks 4*hh .. 4*hh+3 of row r; with split
+                    // outputs the dropped parts go to the second block
+                    uint4 vh[4], vl[4];
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         uint32_t ph[4], pl[4];
 #pragma unroll
                         for (int k = 0; k < 4; ++k) {
-                            const float a = o_acc[8 * i + 2 * k] * inv_l, b2 = o_acc[8 * i + 2 * k + 1] * inv_l;
-                            const __nv_bfloat162 hh = __floats2bfloat162_rn(a, b2);
-                            const __nv_bfloat162 ll = __floats2bfloat162_rn(a - __low2float(hh), b2 - __high2float(hh));
-                            ph[k] = *reinterpret_cast<const uint32_t*>(&hh);
-                            pl[k] = *reinterpret_cast<const uint32_t*>(&ll);
+                            const float a = __uint_as_float(o[8 * i + 2 * k]) * inv_l, b2 = __uint_as_float(o[8 * i + 2 * k + 1]) * inv_l;
+                            const __nv_bfloat162 hv = __floats2bfloat162_rn(a, b2);
+                            const __nv_bfloat162 lv = __floats2bfloat162_rn(a - __low2float(hv), b2 - __high2float(hv));
+                            ph[k] = *reinterpret_cast<const uint32_t*>(&hv);
+                            pl[k] = *reinterpret_cast<const uint32_t*>(&lv);
                         }
-                        rowh[(hf * 4 + i) ^ (r & 7)] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                        if (planes) rowl[(hf * 4 + i) ^ (r & 7)] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
+                        vh[i] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
+                        vl[i] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
                     }
-                    fence_proxy_async_smem();
-                    softmax_bar_sync();
-                    if (threadIdx.x == 64 && ok) {
-                        tma_store_2d(&tmap_out, h * HS, row_base + q0, out_s);
-                        if (planes) tma_store_2d(&tmap_out, h * HS, args.B * args.T + row_base + q0, out_s + kBlk);
-                        tma_store_commit();
+                    if (args.tma_out) {
+                        uint4* rowh = reinterpret_cast<uint4*>(out_s + r * 128);
+                        uint4* rowl = reinterpret_cast<uint4*>(out_s + kBlk + r * 128);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            rowh[(hh * 4 + i) ^ (r & 7)] = vh[i];
+                            if (planes) rowl[(hh * 4 + i) ^ (r & 7)] = vl[i];
+                        }
+                    } else if (ok && t_idx < args.T) {
+                        uint16_t* oh = reinterpret_cast<uint16_t*>(args.out) + ((size_t)(row_base + t_idx) * args.C) + h * HS + hh * 32;
+                        uint4* o1 = reinterpret_cast<uint4*>(oh);
+                        uint4* o2 = reinterpret_cast<uint4*>(oh + (size_t)args.B * args.T * args.C);
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            o1[i] = vh[i];
+                            if (planes) o2[i] = vl[i];
+                        }
                     }
                 } else {
-                float4* row = reinterpret_cast<float4*>(out_s + hf * kBlk + r * 128);
+                    // fp32: block hh holds columns 32*hh .. +31 as 128-byte rows
+                    float4* row = reinterpret_cast<float4*>(out_s + hh * kBlk + r * 128);
+                    float* og = args.out + ((size_t)(row_base + t_idx) * args.C) + h * HS + hh * 32;
 #pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float4 v = make_float4(o_acc[4 * i] * inv_l, o_acc[4 * i + 1] * inv_l,
-                                           o_acc[4 * i + 2] * inv_l, o_acc[4 * i + 3] * inv_l);
-                    if (args.round_out) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
-                    row[i ^ (r & 7)] = v;
-                }
-                fence_proxy_async_smem();
-                softmax_bar_sync();
-                if (threadIdx.x == 64 && ok) {
-                    tma_store_2d(&tmap_out, h * HS, row_base + q0, out_s);
-                    tma_store_2d(&tmap_out, h * HS + 32, row_base + q0, out_s + kBlk);
-                    tma_store_commit();
-                }
-                }
-            } else if (ok && t_idx < args.T && args.out_bf16) {
-                uint16_t* oh = reinterpret_cast<uint16_t*>(args.out) + ((size_t)(row_base + t_idx) * args.C) + h * HS + hf * 32;
-                uint4* o = reinterpret_cast<uint4*>(oh);
-                uint4* o2 = reinterpret_cast<uint4*>(oh + (size_t)args.B * args.T * args.C);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    uint32_t ph[4], pl[4];
-#pragma unroll
-                    for (int k = 0; k < 4; ++k) {
-                        const float a = o_acc[8 * i + 2 * k] * inv_l, b2 = o_acc[8 * i + 2 * k + 1] * inv_l;
-                        const __nv_bfloat162 hh = __floats2bfloat162_rn(a, b2);
-                        const __nv_bfloat162 ll = __floats2bfloat162_rn(a - __low2float(hh), b2 - __high2float(hh));
-                        ph[k] = *reinterpret_cast<const uint32_t*>(&hh);
-                        pl[k] = *reinterpret_cast<const uint32_t*>(&ll);
+                    for (int i = 0; i < 8; ++i) {
+                        float4 v = make_float4(__uint_as_float(o[4 * i]) * inv_l, __uint_as_float(o[4 * i + 1]) * inv_l,
+                                               __uint_as_float(o[4 * i + 2]) * inv_l, __uint_as_float(o[4 * i + 3]) * inv_l);
+                        if (args.round_out) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
+                        if (args.tma_out) row[i ^ (r & 7)] = v;
+                        else if (ok && t_idx < args.T) *reinterpret_cast<float4*>(og + 4 * i) = v;
                     }
-                    o[i] = make_uint4(ph[0], ph[1], ph[2], ph[3]);
-                    if (args.out_bf16 == 2) o2[i] = make_uint4(pl[0], pl[1], pl[2], pl[3]);
-                }
-            } else if (ok && t_idx < args.T) {
-                float* o = args.out + ((size_t)(row_base + t_idx) * args.C) + h * HS + hf * 32;
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                    float4 v = make_float4(o_acc[4 * i] * inv_l, o_acc[4 * i + 1] * inv_l,
-                                           o_acc[4 * i + 2] * inv_l, o_acc[4 * i + 3] * inv_l);
-                    if (args.round_out) { v.x = round_tf32(v.x); v.y = round_tf32(v.y); v.z = round_tf32(v.z); v.w = round_tf32(v.w); }
-                    *reinterpret_cast<float4*>(o + 4 * i) = v;
                 }
             }
-            if (ok && t_idx < args.T && args.lse && hf == 0)
-                args.lse[((size_t)b * args.NH + h) * args.T + t_idx] = m * 0.6931471805599453f + logf(l);
+            if (args.tma_out) {
+                fence_proxy_async_smem();
+                pipe_bar_sync(bar_id);
+                if (leader && ok) {
+                    if (args.out_bf16) {
+                        tma_store_2d(&tmap_out, h * HS, row_base + q0, out_s);
+                        if (planes) tma_store_2d(&tmap_out, h * HS, args.B * args.T + row_base + q0, out_s + kBlk);
+                    } else {
+                        tma_store_2d(&tmap_out, h * HS, row_base + q0, out_s);
+                        tma_store_2d(&tmap_out, h * HS + 32, row_base + q0, out_s + kBlk);
+                    }
+                    tma_store_commit();
+                }
+            }
+            if (ok && t_idx < args.T && args.lse)
+                args.lse[((size_t)b * args.NH + h) * args.T + t_idx] = m_ref * 0.6931471805599453f + logf(l);
             tc_fence_before_sync();
             mbar_arrive(&item_empty[slot]);
         }
-        if (threadIdx.x == 64) tma_store_wait_all();
+        if (leader) tma_store_wait_all();
         if (!ok && lane == 0) atomicCAS(args.status, 0, DEV_TIMEOUT_SOFTMAX);
     }
 
@@ -573,7 +596,8 @@ int launch_attention_split(b200_ctx* ctx, float* out, float* lse, const uint16_t
     a.out = out; a.lse = lse; a.B = B; a.T = T; a.C = C; a.NH = NH;
     a.plane_rows = B * T;
     a.num_qt = (T + BQ - 1) / BQ;
-    a.num_items = a.num_qt * NH * B;
+    a.num_pairs = (a.num_qt + 1) / 2;
+    a.num_items = a.num_pairs * NH * B;
     a.scale_log2 = 1.4426950408889634f / sqrtf((float)HS);
     a.round_out = (flags & ROUND_OUT_TF32) ? 1 : 0;
     a.status = ctx->d_status;
