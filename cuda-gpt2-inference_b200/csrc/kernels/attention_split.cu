@@ -373,30 +373,27 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __gri
                 tmem_ld_wait();
                 tc_fence_before_sync();
                 mbar_arrive(&s_free[x]);  // the next block's scores may overwrite the columns
+                // Diagonal block: keys behind the query (key > row r) do not count.  They are set to
+                // -inf here, once, so that the maximum and the exponentials below (2^-inf = 0) need no
+                // compare-and-select per score in the other blocks.
+                if (diag) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+#pragma unroll
+                        for (int i = 0; i < 32; ++i)
+                            if (c * 32 + i > r) t[c][i] = 0xff800000u;
+                    }
+                }
                 // row maximum of the raw scores (the scale is positive, so it commutes with max)
                 float pm0 = -INFINITY, pm1 = -INFINITY, pm2 = -INFINITY, pm3 = -INFINITY;
-                if (!diag) {
 #pragma unroll
-                    for (int c = 0; c < 4; ++c) {
+                for (int c = 0; c < 4; ++c) {
 #pragma unroll
-                        for (int i = 0; i < 32; i += 8) {
-                            pm0 = fmax3(pm0, __uint_as_float(t[c][i]), __uint_as_float(t[c][i + 1]));
-                            pm1 = fmax3(pm1, __uint_as_float(t[c][i + 2]), __uint_as_float(t[c][i + 3]));
-                            pm2 = fmax3(pm2, __uint_as_float(t[c][i + 4]), __uint_as_float(t[c][i + 5]));
-                            pm3 = fmax3(pm3, __uint_as_float(t[c][i + 6]), __uint_as_float(t[c][i + 7]));
-                        }
-                    }
-                } else {  // keys behind the query do not count (key c <= row r inside the diagonal block)
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-#pragma unroll
-                        for (int i = 0; i < 32; i += 4) {
-                            const int k0 = c * 32 + i;
-                            pm0 = fmaxf(pm0, k0 <= r ? __uint_as_float(t[c][i]) : -INFINITY);
-                            pm1 = fmaxf(pm1, k0 + 1 <= r ? __uint_as_float(t[c][i + 1]) : -INFINITY);
-                            pm2 = fmaxf(pm2, k0 + 2 <= r ? __uint_as_float(t[c][i + 2]) : -INFINITY);
-                            pm3 = fmaxf(pm3, k0 + 3 <= r ? __uint_as_float(t[c][i + 3]) : -INFINITY);
-                        }
+                    for (int i = 0; i < 32; i += 8) {
+                        pm0 = fmax3(pm0, __uint_as_float(t[c][i]), __uint_as_float(t[c][i + 1]));
+                        pm1 = fmax3(pm1, __uint_as_float(t[c][i + 2]), __uint_as_float(t[c][i + 3]));
+                        pm2 = fmax3(pm2, __uint_as_float(t[c][i + 4]), __uint_as_float(t[c][i + 5]));
+                        pm3 = fmax3(pm3, __uint_as_float(t[c][i + 6]), __uint_as_float(t[c][i + 7]));
                     }
                 }
                 // log2 domain; finite (key 0 of every block counts for every row)
@@ -423,13 +420,6 @@ attention_split_kernel(const __grid_constant__ CUtensorMap tmap_qkv, const __gri
                         float a1 = ex2_approx(fmaf(__uint_as_float(t[c][2 * k + 1]), args.scale_log2, neg_m));
                         float b0 = ex2_approx(fmaf(__uint_as_float(t[c][2 * k + 2]), args.scale_log2, neg_m));
                         float b1 = ex2_approx(fmaf(__uint_as_float(t[c][2 * k + 3]), args.scale_log2, neg_m));
-                        if (diag) {
-                            const int k0 = c * 32 + 2 * k;
-                            if (k0 > r) a0 = 0.f;
-                            if (k0 + 1 > r) a1 = 0.f;
-                            if (k0 + 2 > r) b0 = 0.f;
-                            if (k0 + 3 > r) b1 = 0.f;
-                        }
                         sum0 += a0;
                         sum1 += a1;
                         sum2 += b0;
