@@ -781,18 +781,26 @@ def _xl_and_multi_gpu(pkg, torch, dist, ctx, stream, world, rank, barrier, max_o
         h_full = _seq_hashes(torch, ref8)
         s0, s1 = pkg.shard_batch(8, world, rank)
         h_shard = torch.zeros((8, 2), dtype=torch.int64, device="cuda")
+        diff = torch.zeros(1, device="cuda")
         if s1 > s0:
             part = xlm.forward(tok_all[s0:s1].contiguous(), s1 - s0, T)
             ctx.sync_check()
             h_shard[s0:s1] = _seq_hashes(torch, part)
+            diff = (part - ref8[s0:s1]).abs().max().reshape(1)
         gather_full = [torch.empty_like(h_full) for _ in range(world)]
         dist.all_gather(gather_full, h_full)
         dist.all_reduce(h_shard)  # every sequence is filled in by exactly one rank
+        dist.all_reduce(diff, op=dist.ReduceOp.MAX)
         same_full = all(torch.equal(gather_full[0], x) for x in gather_full)
         same_shard = torch.equal(h_shard, gather_full[0])
-        out["shard_check"] = {"batch_sharded": "bitwise" if (same_full and same_shard) else "MISMATCH",
+        out["shard_check"] = {"same_batch_on_every_rank": "bitwise" if same_full else "MISMATCH",
+                              "batch_sharded": "bitwise" if same_shard else "not bitwise",
+                              "batch_sharded_max_abs_vs_full_batch": float(diff.item()),
                               "how": "GPT-2 XL, 8 sequences: per-sequence checksums of the logits' bit patterns, the full batch on "
-                                     "every rank and each rank's own shard alone, compared across the ranks"}
+                                     "every rank and each rank's own shard alone, compared across the ranks.  The accumulate-GEMMs "
+                                     "choose their number of K slices from the number of rows, and the order of an fp32 sum "
+                                     "follows it: a shard whose GEMMs run with the full batch's configuration (8 / N >= 4 "
+                                     "sequences) gives the same bits, a smaller one differs by rounding (the figure above)"}
 
     # ---- tensor parallel over all ranks (B = 8): weights cut out of the unsharded model's on the device
     tpm = pkg.GPT2(ctx, cfg, 8, T, tp_size=world, tp_rank=rank)
