@@ -876,6 +876,11 @@ def run_kernel_sweep(args):
                                         (3072, 768, 0, True, "accumulate"), (768, 50304, 0, False, "fp32"),
                                         (1600, 4800, 0, True, "split"), (1600, 6400, 1, True, "split"), (6400, 1600, 0, True, "accumulate")):
             cases.append(("matmul_bf16x3", dict(K=K, N=N, act=act, bias=bias, outk=outk)))
+    if args.op in ("matmul_fp8", "all"):
+        for (K, N, act, bias, acc) in ((768, 2304, 0, True, False), (768, 768, 0, True, True), (768, 3072, 1, True, False),
+                                       (3072, 768, 0, True, True), (768, 50304, 0, False, False),
+                                       (1600, 4800, 0, True, False), (1600, 6400, 1, True, False), (6400, 1600, 0, True, True)):
+            cases.append(("matmul_fp8", dict(K=K, N=N, act=act, bias=bias, acc=acc)))
     if args.op in ("attention", "all"):
         cases += [("attention", dict(NH=12)), ("attention", dict(NH=25))]
     if args.op in ("attention_fp16", "all"):
@@ -923,6 +928,17 @@ def run_kernel_sweep(args):
                                                    accumulate=c["outk"] == "accumulate")
             work, unit, peak = 2.0 * M * K * N / 1e12, "TFLOP/s", peaks["bf16_burst"] / 3
             name = f"matmul bf16x3 {K}->{N}" + ("+gelu" if c["act"] else "") + {"split": " split out", "accumulate": " accumulate", "fp32": ""}[c["outk"]]
+        elif op == "matmul_fp8":
+            K, N = c["K"], c["N"]
+            xq = torch.empty(Bb, Tt, K, device="cuda", dtype=torch.uint8)
+            wq = torch.empty(N, K, device="cuda", dtype=torch.uint8)
+            ctx.quantize_e4m3(xq, randn(Bb, Tt, K), M * K, 1.0)
+            ctx.quantize_e4m3(wq, randn(N, K, std=0.02), N * K, 1024.0)
+            bias = randn(N, std=0.01) if c["bias"] else None
+            out = torch.zeros(Bb, Tt, N, device="cuda")
+            fn = lambda: ctx.matmul_forward_fp8(out, xq, wq, bias, Bb, Tt, K, N, act=c["act"], alpha=1.0 / 1024.0, accumulate=c["acc"])
+            work, unit, peak = 2.0 * M * K * N / 1e12, "TFLOP/s", peaks["bf16_burst"] * 2
+            name = f"matmul fp8 (e4m3) {K}->{N}" + ("+gelu" if c["act"] else "") + (" accumulate" if c["acc"] else "")
         elif op == "attention_fp16":
             NH = c["NH"]
             Cc = NH * 64
@@ -971,7 +987,7 @@ def run_kernel_sweep(args):
                 fn = lambda k=0: ctx.encoder_forward(S[k]["out"], tok, wte, wpe, Bb, Tt, Cc)
                 work = ((2.0 * M * Cc + Tt * Cc) * 4 + M * 4) / 1e9
             unit, peak, name = "GB/s", peaks["hbm_gbs"], f"{op} [8192,{Cc}]"
-        streaming = args.stream > 1 and op not in ("matmul", "matmul_bf16", "matmul_bf16x3", "attention", "attention_fp16")
+        streaming = args.stream > 1 and op not in ("matmul", "matmul_bf16", "matmul_bf16x3", "matmul_fp8", "attention", "attention_fp16")
         torch.cuda.synchronize()
         for _ in range(args.warmup):
             fn()
@@ -1014,7 +1030,7 @@ def main():
     ap.add_argument("--tp", action="store_true",
                     help="with --gpus N > 1: one tensor-parallel group over all ranks instead of batch sharding")
     ap.add_argument("--op", default=None,
-                    choices=["all", "matmul", "matmul_bf16", "matmul_bf16x3", "attention", "attention_fp16", "layernorm",
+                    choices=["all", "matmul", "matmul_bf16", "matmul_bf16x3", "matmul_fp8", "attention", "attention_fp16", "layernorm",
                              "fused_residual_layernorm", "rowwise"],
                     help="per-kernel sweep at 8192 rows instead of the forward benchmark")
     ap.add_argument("--case", type=int, default=None, help="with --op: run only this case of the family")

@@ -33,6 +33,7 @@ EXPORTS = (
     "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
     "b200_ctx_last_error", "b200_ctx_wait_timeout_probe",
     "b200_matmul_forward", "b200_matmul_forward_bf16", "b200_convert_bf16", "b200_matmul_forward_bf16x3", "b200_split_bf16",
+    "b200_matmul_forward_fp8", "b200_quantize_e4m3",
     "b200_gpt2_set_attention_mode", "b200_attention_forward", "b200_attention_forward_x3", "b200_attention_forward_fp16", "b200_split_fp16", "b200_layernorm_forward",
     "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
     "b200_encoder_forward",
@@ -106,6 +107,8 @@ def lib() -> C.CDLL:
         l.b200_convert_bf16.argtypes = [vp, vp, vp, sz]
         l.b200_matmul_forward_bf16x3.argtypes = [vp, vp, vp, vp, vp, vp, vp, i, i, i, i, i, i]
         l.b200_split_bf16.argtypes = [vp, vp, vp, vp, sz]
+        l.b200_matmul_forward_fp8.argtypes = [vp, vp, vp, vp, vp, i, i, i, i, i, C.c_float, i]
+        l.b200_quantize_e4m3.argtypes = [vp, vp, vp, sz, C.c_float]
         l.b200_gpt2_set_attention_mode.argtypes = [vp, i]
         l.b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_attention_forward_x3.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
@@ -246,6 +249,15 @@ class Context:
         self.check(lib().b200_matmul_forward_bf16x3(self._h, _ptr(out), _ptr(out_split), _ptr(inp_split), _ptr(weight_hi),
                                                     _ptr(weight_lo), _ptr(bias), B, T, Cc, OC, act, int(accumulate)),
                    "matmul_forward_bf16x3")
+
+    def quantize_e4m3(self, out, inp, n, scale=1.0):
+        """out (uint8) = e4m3(inp * scale), round to nearest even, saturating at 448."""
+        self.check(lib().b200_quantize_e4m3(self._h, _ptr(out), _ptr(inp), n, float(scale)), "quantize_e4m3")
+
+    def matmul_forward_fp8(self, out, inp_q, weight_q, bias, B, T, Cc, OC, act=ACT_NONE, alpha=1.0, accumulate=False):
+        """inp_q [B,T,C] and weight_q [OC,C] hold e4m3 bytes; out (fp32) = act(alpha * inp_q . weight_q^T + bias)."""
+        self.check(lib().b200_matmul_forward_fp8(self._h, _ptr(out), _ptr(inp_q), _ptr(weight_q), _ptr(bias), B, T, Cc, OC, act,
+                                                 float(alpha), int(accumulate)), "matmul_forward_fp8")
 
     def sample_rows(self, out, logits, M, V, ld, temperature, seed, stream0, top_k=0, top_p=0.0):
         self.check(lib().b200_sample_rows(self._h, _ptr(out), _ptr(logits), M, V, ld, float(temperature), int(top_k), float(top_p),

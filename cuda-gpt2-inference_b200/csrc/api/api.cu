@@ -67,6 +67,31 @@ int b200_get_tensor_map_bf16(b200_ctx* ctx, CUtensorMap* out, const void* ptr, u
     return B200_OK;
 }
 
+int b200_get_tensor_map_u8(b200_ctx* ctx, CUtensorMap* out, const void* ptr, uint64_t rows,
+                           uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols) {
+    TensorMapKey key{ptr, rows, cols, ld, box_rows, box_cols, 3};  // 3: 8-bit elements
+    auto it = ctx->tmap_cache.find(key);
+    if (it != ctx->tmap_cache.end()) { *out = it->second; return B200_OK; }
+    if (!ctx->encode_tiled) return B200_ERR_STATE;
+    if (!b200_aligned16(ptr) || ld % 16 != 0) return B200_ERR_ALIGN;
+    const cuuint64_t dims[2] = {cols, rows};
+    const cuuint64_t strides[1] = {ld};
+    const cuuint32_t box[2] = {box_cols, box_rows};
+    const cuuint32_t estr[2] = {1, 1};
+    CUtensorMap m;
+    CUresult r = ctx->encode_tiled(&m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(ptr), dims,
+                                   strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        ctx->last_error = "cuTensorMapEncodeTiled (8-bit) failed with CUresult " + std::to_string((int)r);
+        return B200_ERR_CUDA;
+    }
+    if (ctx->tmap_cache.size() > 4096) ctx->tmap_cache.clear();
+    ctx->tmap_cache.emplace(key, m);
+    *out = m;
+    return B200_OK;
+}
+
 extern "C" {
 
 const char* b200_status_string(int s) {
@@ -207,6 +232,26 @@ int b200_split_bf16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* inp,
     REQUIRE_PTR(hi); REQUIRE_PTR(lo); REQUIRE_PTR(inp);
     if (n == 0 || n % 4) return B200_ERR_SHAPE;
     return b200::launch_convert_bf16(ctx, hi, inp, n, lo);
+}
+
+int b200_quantize_e4m3(b200_ctx* ctx, uint8_t* out, const float* inp, size_t n, float scale) {
+    if (!ctx) return B200_ERR_NULL;
+    REQUIRE_PTR(out); REQUIRE_PTR(inp);
+    if (n == 0 || n % 4 || !(scale > 0.f)) return B200_ERR_SHAPE;
+    return b200::launch_quantize_e4m3(ctx, out, inp, n, scale);
+}
+
+int b200_matmul_forward_fp8(b200_ctx* ctx, float* out, const uint8_t* inp, const uint8_t* weight, const float* bias,
+                            int B, int T, int C, int OC, int act, float alpha, int accumulate) {
+    if (!ctx) return B200_ERR_NULL;
+    REQUIRE_PTR(out); REQUIRE_PTR(inp); REQUIRE_PTR(weight);
+    OPTIONAL_PTR(bias);
+    if (B <= 0 || T <= 0 || C <= 0 || OC <= 0 || C % 16 || OC % 8) return B200_ERR_SHAPE;
+    if ((long long)B * T > 0x7fffffffLL) return B200_ERR_SHAPE;
+    if (act != B200_ACT_NONE && act != B200_ACT_GELU) return B200_ERR_SHAPE;
+    if (accumulate && act != B200_ACT_NONE) return B200_ERR_SHAPE;
+    return b200::launch_gemm_fp8(ctx, out, inp, weight, bias, B * T, C, OC,
+                                 (act == B200_ACT_GELU ? b200::GEMM_GELU : 0) | (accumulate ? b200::GEMM_ACCUM_OUT : 0), alpha);
 }
 
 int b200_matmul_forward_bf16(b200_ctx* ctx, float* out, uint16_t* out_bf16, const uint16_t* inp,

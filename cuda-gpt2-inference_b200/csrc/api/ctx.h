@@ -69,6 +69,10 @@ int b200_get_tensor_map(b200_ctx* ctx, CUtensorMap* out, const float* ptr, uint6
 int b200_get_tensor_map_bf16(b200_ctx* ctx, CUtensorMap* out, const void* ptr, uint64_t rows,
                              uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
 
+// The same over a matrix of 8-bit elements (e4m3 operands of the fp8 GEMM).
+int b200_get_tensor_map_u8(b200_ctx* ctx, CUtensorMap* out, const void* ptr, uint64_t rows,
+                           uint64_t cols, uint64_t ld, uint32_t box_rows, uint32_t box_cols);
+
 // Makes the context's device current for the lifetime of the guard (streams, events and launches
 // belong to a device) and puts the caller's device back afterwards.
 struct b200_device_guard {

@@ -11,6 +11,7 @@ namespace b200 {
 constexpr int kGemmBM = 128;       // accumulator rows per CTA (tensor-memory lanes)
 constexpr int kGemmBK = 32;        // fp32 elements per K block = 128 bytes = one swizzle row
 constexpr int kGemmBKH = 64;       // bf16 elements per K block: the same 128 bytes
+constexpr int kGemmBKQ = 128;      // 8-bit elements per K block
 constexpr int kGemmMaxSmem = 232448;  // 227 KB
 constexpr int kGemmEpiBytes = 4 * 2 * 4096;  // per epilogue warp two {32 rows x 128 B} buffers
 
@@ -45,6 +46,7 @@ struct GemmArgs {
     // of unit_cols), K cut into k_splits slices that are tiles of their own; see gemm_tf32_pair.cu
     int tile_w, unit_cols, k_splits;
     unsigned int* split_flags;   // per (K slice, tile, CTA, epilogue warp): set once its sums are in the output, cleared by its reader
+    float alpha = 1.0f;          // the accumulator is multiplied by this before the epilogue (fp8 operands: undoes their scales)
 };
 
 // Arg-max keys: the value as an order-preserving 32-bit integer in the high half, the inverted
@@ -102,6 +104,13 @@ __device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r0);
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32 + 32, r1);
         tmem_ld_wait();
+        if (args.alpha != 1.0f) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                r0[i] = __float_as_uint(__uint_as_float(r0[i]) * args.alpha);
+                r1[i] = __float_as_uint(__uint_as_float(r1[i]) * args.alpha);
+            }
+        }
         // buffers: without planes unit ui uses buffer ui mod nbuf; with planes its two stores use buffers
         // 2ui and 2ui + 1 mod nbuf (one and the same buffer when there is only one)
         const int bi = planes ? 2 * ui : ui;
@@ -222,6 +231,10 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
         uint32_t r[32];
         tmem_ld_32x32b_x32(tmem_acc + (uint32_t(q * 32) << 16) + c * 32, r);
         tmem_ld_wait();
+        if (args.alpha != 1.0f) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * args.alpha);
+        }
         if (do_lse) {
             const int cbase = col0 + c * 32;
             float cm = -INFINITY;
@@ -333,11 +346,11 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
 // kind: PAIR_TF32 = fp32 operands (TF32 product); PAIR_BF16 = bf16 operands; PAIR_BF16X3 = split bf16
 // operands: inp / weight address the first (hi) plane, inp_lo / weight_lo the second.  out_h as in
 // GemmArgs (out_planes: M must be a multiple of 32).
-enum : int { PAIR_TF32 = 0, PAIR_BF16 = 1, PAIR_BF16X3 = 2 };
+enum : int { PAIR_TF32 = 0, PAIR_BF16 = 1, PAIR_BF16X3 = 2, PAIR_FP8 = 3 };  // PAIR_FP8: e4m3 operands (kind::f8f6f4)
 int preload_gemm_pair_kernels(b200_ctx* ctx);  // the PAIR_TF32 kernel: loaded now, not at its first launch
 int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp_lo, const void* weight, const void* weight_lo,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys, int argmax_cols, int kind, uint16_t* out_h = nullptr,
-                     int out_planes = 0, int store_period = 0, const GemmRowStats* stats = nullptr);
+                     int out_planes = 0, int store_period = 0, const GemmRowStats* stats = nullptr, float alpha = 1.0f);
 
 }  // namespace b200

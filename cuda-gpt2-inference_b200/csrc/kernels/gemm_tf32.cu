@@ -431,4 +431,12 @@ int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t*
     return launch_gemm_any(ctx, out, out_h, inp, weight, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32 | GEMM_ACCUM_OUT), B200_TF32, argmax_keys, argmax_cols, true, store_period, nullptr);
 }
 
+// e4m3 operands: always on CTA pairs (the kernel clips ragged edges itself)
+int launch_gemm_fp8(b200_ctx* ctx, float* out, const uint8_t* inp, const uint8_t* weight, const float* bias,
+                    int M, int K, int N, int flags, float alpha) {
+    if (K % 16 || N % 8) { ctx->last_error = "fp8 GEMM: K must be a multiple of 16 and N of 8"; return B200_ERR_SHAPE; }
+    return launch_gemm_pair(ctx, out, inp, nullptr, weight, nullptr, bias, nullptr, M, K, N, flags & (GEMM_GELU | GEMM_ACCUM_OUT),
+                            nullptr, 0, PAIR_FP8, nullptr, 0, 0, nullptr, alpha);
+}
+
 }  // namespace b200

@@ -32,6 +32,7 @@
 // Arithmetic (template MODE):
 //   PAIR_TF32    fp32 operands, tcgen05.mma kind::tf32 (the tensor core reads the upper 19 bits)
 //   PAIR_BF16    bf16 operands, kind::f16
+//   PAIR_FP8     e4m3 operands, kind::f8f6f4 (128 elements of K per 128-byte block, 32 per instruction)
 //   PAIR_BF16X3  both operands given as two bf16 planes, x = hi + lo with hi = bf16(x) and
 //                lo = bf16(x - hi) (16 significant bits); three kind::f16 products per K step,
 //                hi.hi + hi.lo + lo.hi, accumulated in fp32: the dropped lo.lo term and the
@@ -72,7 +73,7 @@ struct PairCfg {
     static constexpr int SMEM = 1024 + STAGES * STAGE_BYTES + kGemmEpiBytes + BAR_BYTES;
     static constexpr int TMEM_COLS = 512;
     // elements of K per 128-byte block
-    static constexpr int BKE = (MODE == PAIR_TF32) ? kGemmBK : kGemmBKH;
+    static constexpr int BKE = (MODE == PAIR_TF32) ? kGemmBK : (MODE == PAIR_FP8 ? kGemmBKQ : kGemmBKH);
     static_assert(SMEM > 117 * 1024, "a second resident CTA could block in tcgen05.alloc");
     static_assert(SMEM <= kGemmMaxSmem, "shared memory over the 227 KB limit");
     static_assert(STAGES >= 2, "need at least a double buffer");
@@ -210,7 +211,8 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                 ++tile_iter;
                 if (!mbar_wait_cluster(&tmem_empty_bar[acc], acc_ph ^ 1, abort_flag)) { ok = false; break; }
                 tc_fence_after_sync();
-                const uint32_t idesc = (MODE == PAIR_TF32) ? make_idesc_tf32(2 * BM, width, 0) : make_idesc_bf16(2 * BM, width, 0);
+                const uint32_t idesc = (MODE == PAIR_TF32) ? make_idesc_tf32(2 * BM, width, 0)
+                                     : (MODE == PAIR_FP8 ? make_idesc_e4m3(2 * BM, width, 0) : make_idesc_bf16(2 * BM, width, 0));
                 const uint32_t d_tmem = tmem_base + acc * kMaxW;
                 for (int kb = kb0; kb < kb1; ++kb, ++it) {
                     const int s = it % STAGES;
@@ -230,8 +232,9 @@ gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_consta
                         }
                     } else {
 #pragma unroll
-                        for (int k = 0; k < 4; ++k) {  // 32 bytes of K per instruction: 8 tf32 or 16 bf16
+                        for (int k = 0; k < 4; ++k) {  // 32 bytes of K per instruction: 8 tf32, 16 bf16 or 32 e4m3
                             if (MODE == PAIR_BF16) umma_f16_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb0) | k) != 0);
+                            else if (MODE == PAIR_FP8) umma_f8_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb0) | k) != 0);
                             else umma_tf32_ss_pair(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc, ((kb - kb0) | k) != 0);
                         }
                     }
@@ -374,12 +377,13 @@ int preload_gemm_pair_kernels(b200_ctx* ctx) {
 int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp_lo, const void* weight, const void* weight_lo,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys, int argmax_cols, int kind, uint16_t* out_h, int out_planes,
-                     int store_period, const GemmRowStats* stats) {
+                     int store_period, const GemmRowStats* stats, float alpha) {
     const int num_pairs_max = ctx->num_sms / 2;
-    const bool half = kind != PAIR_TF32;
+    const bool half = kind == PAIR_BF16 || kind == PAIR_BF16X3;
     GemmArgs a;
     a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
+    a.alpha = alpha;
     a.num_m_blocks = (M + 2 * BM - 1) / (2 * BM);
     // weight small enough to stay in L2: columns fastest, so the pairs working side by side share an
     // inp tile; otherwise rows fastest, so that they share a few weight tiles while the weights stream once
@@ -404,7 +408,7 @@ int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp
     // of the tensor pipe per product (three products with split operands) and (128 + W/2) * 128 bytes
     // per operand plane out of L2, of which an SM gets about 52 per cycle; plus a fixed cost per tile
     // (pipeline fill, the part of the epilogue that is not hidden).
-    const int bke = half ? kGemmBKH : kGemmBK;
+    const int bke = half ? kGemmBKH : (kind == PAIR_FP8 ? kGemmBKQ : kGemmBK);
     const int num_kb = (K + bke - 1) / bke;
     const int parts = kind == PAIR_BF16X3 ? 2 : 1, products = kind == PAIR_BF16X3 ? 3 : 1;
     const bool may_split = (flags & GEMM_ACCUM_OUT) && !(flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32)) && ctx->d_split_flags != nullptr;
@@ -449,6 +453,11 @@ int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp
         } else {
             maps[1] = maps[0]; maps[3] = maps[2];
         }
+    } else if (kind == PAIR_FP8) {
+        st = b200_get_tensor_map_u8(ctx, &maps[0], inp, (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, bke);
+        if (st == B200_OK) st = b200_get_tensor_map_u8(ctx, &maps[2], weight, (uint64_t)N, (uint64_t)K, (uint64_t)K, box_b, bke);
+        if (st != B200_OK) return st;
+        maps[1] = maps[0]; maps[3] = maps[2];
     } else {
         st = b200_get_tensor_map(ctx, &maps[0], static_cast<const float*>(inp), (uint64_t)M, (uint64_t)K, (uint64_t)K, BM, bke);
         if (st == B200_OK) st = b200_get_tensor_map(ctx, &maps[2], static_cast<const float*>(weight), (uint64_t)N, (uint64_t)K, (uint64_t)K, box_b, bke);
@@ -462,6 +471,7 @@ int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp
     switch (kind) {
         case PAIR_BF16X3: return launch_pair<PAIR_BF16X3>(ctx, maps, a, num_pairs_max);
         case PAIR_BF16: return launch_pair<PAIR_BF16>(ctx, maps, a, num_pairs_max);
+        case PAIR_FP8: return launch_pair<PAIR_FP8>(ctx, maps, a, num_pairs_max);
         default: return launch_pair<PAIR_TF32>(ctx, maps, a, num_pairs_max);
     }
 }

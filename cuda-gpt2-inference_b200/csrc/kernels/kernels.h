@@ -28,6 +28,8 @@ int launch_fetch_ints(b200_ctx* ctx, int* dst, const int* src_view, int n);
 int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N, uint16_t* lo = nullptr);
 // hi[i] = fp16(clamp(in[i])), lo[i] = fp16(in[i] - hi[i]); N a multiple of 4
 int launch_split_fp16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* in, size_t N);
+// out[i] = e4m3(in[i] * scale), round to nearest even, saturating at +-448 (N a multiple of 4)
+int launch_quantize_e4m3(b200_ctx* ctx, uint8_t* out, const float* in, size_t N, float scale);
 int launch_argmax_rows(b200_ctx* ctx, int* out, const float* logits, int M, int V, int ld);
 // one draw per row from softmax(logits / temperature) (Gumbel-max; temperature <= 0: arg-max);
 // row r uses the noise stream stream0 + r of the seed; 0 < top_k < V: only among the top_k largest logits;
@@ -62,6 +64,10 @@ int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t*
 // M*K elements further on, lo = bf16(x - hi); weight_hi / weight_lo [N,K] likewise.  The result goes
 // to out (fp32; GEMM_ACCUM_OUT adds onto it) or, if out_planes is not null, there as two bf16 planes
 // of [M,N] in the same split form.  flags: GEMM_GELU, GEMM_ACCUM_OUT.  K and N multiples of 8.
+// e4m3 operands (tcgen05 kind::f8f6f4, fp32 accumulation): out = act(alpha * inp_q . weight_q^T + bias), alpha
+// undoing the scales the operands were quantised with; flags: GEMM_GELU, GEMM_ACCUM_OUT.  K a multiple of 16.
+int launch_gemm_fp8(b200_ctx* ctx, float* out, const uint8_t* inp, const uint8_t* weight, const float* bias,
+                    int M, int K, int N, int flags, float alpha);
 int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const uint16_t* inp, const uint16_t* weight_hi,
                        const uint16_t* weight_lo, const float* bias, int M, int K, int N, int flags,
                        unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0,

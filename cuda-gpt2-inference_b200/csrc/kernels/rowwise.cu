@@ -182,6 +182,17 @@ __global__ void convert_bf16_kernel(uint2* __restrict__ out, const float4* __res
     }
 }
 
+// out[i] = e4m3(in[i] * scale): round to nearest even, saturating at the largest finite value (448)
+__global__ void quantize_e4m3_kernel(uint32_t* __restrict__ out, const float4* __restrict__ in, size_t n4, float scale) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x) {
+        const float4 v = __ldg(in + i);
+        uint16_t lo, hi;  // two e4m3 values each: the second source operand lands in the low byte
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(lo) : "f"(v.y * scale), "f"(v.x * scale));
+        asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(hi) : "f"(v.w * scale), "f"(v.z * scale));
+        out[i] = (uint32_t)lo | ((uint32_t)hi << 16);
+    }
+}
+
 __global__ void split_fp16_kernel(uint2* __restrict__ hi, uint2* __restrict__ lo, const float4* __restrict__ in, size_t n4) {
     const size_t stride = (size_t)gridDim.x * blockDim.x;
     for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
@@ -539,6 +550,16 @@ int launch_convert_bf16(b200_ctx* ctx, uint16_t* out, const float* in, size_t N,
     const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
     convert_bf16_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<uint2*>(out), reinterpret_cast<const float4*>(in), n4,
                                                        reinterpret_cast<uint2*>(lo));
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_quantize_e4m3(b200_ctx* ctx, uint8_t* out, const float* in, size_t N, float scale) {
+    if (N % 4) { ctx->last_error = "e4m3 quantisation: element count must be a multiple of 4"; return B200_ERR_SHAPE; }
+    const size_t n4 = N / 4;
+    const int grid = stream_grid(ctx, n4 > 0 ? n4 : 1, 256, 16);
+    quantize_e4m3_kernel<<<grid, 256, 0, ctx->stream>>>(reinterpret_cast<uint32_t*>(out), reinterpret_cast<const float4*>(in), n4, scale);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

@@ -123,6 +123,20 @@ int b200_matmul_forward_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_split, c
 /* hi[i] = bf16(inp[i]) (round to nearest even), lo[i] = bf16(inp[i] - hi[i]); n % 4 == 0. */
 int b200_split_bf16(b200_ctx* ctx, uint16_t* hi, uint16_t* lo, const float* inp, size_t n);
 
+/* The same product with 8-bit floating-point operands (e4m3: 4 exponent, 3 mantissa bits; tcgen05
+ * kind::f8f6f4, fp32 accumulation) - the second half of the reference's reduced-precision
+ * experiment (README.md:124-128; kernels/matmul/5_matmul_ptx_2d.cuh:165-202 is its bf16 kernel):
+ *     out = act(alpha * inp_q . weight_q^T + bias)          (accumulate != 0: out += ..., no act)
+ * inp_q[B,T,C] and weight_q[OC,C] hold e4m3 values (one byte each) as b200_quantize_e4m3 writes
+ * them, x_q = e4m3(x * scale); alpha = 1 / (scale_inp * scale_weight) undoes the two scales in the
+ * epilogue (exactly, when they are powers of two).  Products of e4m3 values are exact in fp32, so
+ * the result is the fp32-accumulated product of the quantised operands.
+ * Preconditions: C % 16 == 0, OC % 8 == 0. */
+int b200_matmul_forward_fp8(b200_ctx* ctx, float* out, const uint8_t* inp_q, const uint8_t* weight_q, const float* bias,
+                            int B, int T, int C, int OC, int act, float alpha, int accumulate);
+/* out[i] = e4m3(inp[i] * scale): round to nearest even, saturating at +-448; scale > 0, n % 4 == 0. */
+int b200_quantize_e4m3(b200_ctx* ctx, uint8_t* out, const float* inp, size_t n, float scale);
+
 /* Causal multi-head attention on the packed buffer inp[B,T,3C] -> out[B,T,C].
  * Replaces attention_forward_cublas (kernels/attention/1_attention_cublas.cuh:31-36),
  * flash_attention_forward (2_flash_attention.cuh:336-341) and

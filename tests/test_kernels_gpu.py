@@ -347,6 +347,75 @@ def test_matmul_bf16_matches_oracle_on_rounded_operands(ctx, dev, orc, B, T, C, 
         assert np.abs(got - want).max() <= 2e-5 * scale, (np.abs(got - want).max(), scale)
 
 
+# ------------------------------------------------------------------ fp8 (e4m3) operand GEMM
+def _e4m3_round(a):
+    """fp32 -> nearest e4m3 (1-4-3 bits, bias 7, no infinities; ties to even; values beyond the largest
+    finite one, 448, saturate), returned as fp32 values and as the byte patterns."""
+    a = np.ascontiguousarray(a, np.float32)
+    mag = np.abs(a).astype(np.float64)
+    e = np.floor(np.log2(np.maximum(mag, 2.0 ** -20)))
+    e = np.maximum(e, -6.0)                       # below 2^-6 the step stays 2^-9 (subnormals)
+    step = 2.0 ** (e - 3)
+    q = np.minimum(np.round(mag / step) * step, 448.0)   # np.round: half to even
+    e2 = np.floor(np.log2(np.maximum(q, 2.0 ** -20)))
+    normal = q >= 2.0 ** -6
+    expf = np.where(normal, e2 + 7, 0).astype(np.uint8)
+    mant = np.where(normal, (q / 2.0 ** np.where(normal, e2, 0) - 1.0) * 8.0, q * 2.0 ** 9).astype(np.uint8)
+    bits = (np.signbit(a).astype(np.uint8) << 7) | (expf << 3) | mant
+    return np.copysign(q, a).astype(np.float32), bits
+
+
+def test_quantize_e4m3_is_round_to_nearest_even_and_saturates(ctx, dev, orc):
+    import torch
+    x = orc.fill_normal((4, 1000), 401) * np.repeat(np.float32([1.0, 30.0, 0.01, 200.0]), 1000).reshape(4, 1000)
+    x[0, :16] = [0.0, -0.0, 448.0, 460.0, 500.0, 1e6, -1e6, 2.0 ** -9, 2.0 ** -10, 3 * 2.0 ** -10, 0.0019, 17.0, 19.0, -17.0, 1.0625, 1.1875]
+    out = torch.empty((4, 1000), dtype=torch.uint8, device="cuda")
+    ctx.quantize_e4m3(out, dev.to(x), x.size, 1.0)
+    ctx.sync_check()
+    vals, bits = _e4m3_round(x)
+    got = out.cpu().numpy()
+    assert np.array_equal(got, bits), np.flatnonzero(got.ravel() != bits.ravel())[:10]
+    # the byte patterns mean what the helper says they mean (torch's own e4m3 type as a second opinion)
+    assert np.array_equal(out.cpu().view(torch.float8_e4m3fn).to(torch.float32).numpy(), vals)
+    # a scale is applied before rounding
+    ctx.quantize_e4m3(out, dev.to(x), x.size, 64.0)
+    ctx.sync_check()
+    assert np.array_equal(out.cpu().numpy(), _e4m3_round(x * np.float32(64.0))[1])
+
+
+@pytest.mark.parametrize("B,T,C,OC,has_bias,act,accumulate", [
+    (1, 128, 64, 64, False, 0, False),
+    (2, 192, 768, 2304, True, 0, False),      # qkv shape, ragged M
+    (4, 512, 768, 3072, True, 1, False),      # fc + GELU
+    (1, 1000, 3072, 768, True, 0, False),     # fc-proj, M not a multiple of 128
+    (1, 320, 784, 200, True, 1, False),       # K tail (784 = 6 * 128 + 16), narrow ragged N
+    (8, 1024, 3072, 768, True, 0, True),      # 8192 rows added onto the output (K slices)
+])
+def test_matmul_fp8_matches_oracle_on_quantised_operands(ctx, dev, orc, B, T, C, OC, has_bias, act, accumulate):
+    """Products of e4m3 values are exact in fp32, so against the oracle fed the same quantised
+    operands (with the power-of-two scales taken out again) only the accumulation order is left:
+    2e-5 of the result's magnitude."""
+    import torch
+    sx, sw = 2.0, 1024.0
+    x, w = orc.fill_normal((B, T, C), 411), orc.fill_normal((OC, C), 412, std=0.02)
+    xv, xb = _e4m3_round(x * np.float32(sx))
+    wv, wb = _e4m3_round(w * np.float32(sw))
+    bias = orc.fill_normal((OC,), 413, std=0.01) if has_bias else None
+    rows = slice(None) if B * T * OC < 40_000_000 else slice(-300, None)
+    want = orc.matmul_forward((xv / np.float32(sx)).reshape(B * T, C)[rows][None], wv / np.float32(sw), bias, act=act, precise=True)[0]
+    res = orc.fill_normal((B, T, OC), 414) if accumulate else None
+    out = dev.to(res) if accumulate else dev.full((B, T, OC), float("nan"))
+    if accumulate:
+        want = want + res.reshape(B * T, OC)[rows]
+    ctx.matmul_forward_fp8(out, torch.from_numpy(xb).cuda(), torch.from_numpy(wb).cuda(), None if bias is None else dev.to(bias),
+                           B, T, C, OC, act=act, alpha=1.0 / (sx * sw), accumulate=accumulate)
+    ctx.sync_check()
+    got = dev.back(out).reshape(B * T, OC)[rows]
+    assert np.isfinite(dev.back(out)).all(), "unwritten or non-finite outputs"
+    scale = float(np.abs(want).max())
+    assert np.abs(got - want).max() <= 2e-5 * scale, (np.abs(got - want).max(), scale)
+
+
 # ------------------------------------------------------------------ split bf16 (bf16x3) GEMM
 def _bits_to_f32(bits):
     return (bits.astype(np.uint32) << 16).view(np.float32)
