@@ -797,7 +797,7 @@ int b200_gpt2_enable_kv_cache(b200_gpt2* m) {
     cudaError_t e = cudaMalloc(&m->vcache, n * sizeof(float));
     if (e == cudaSuccess) e = cudaMalloc(&m->pos_dev, sizeof(int));
     if (e == cudaSuccess) e = cudaMalloc(&m->resid2, (size_t)16 * m->cfg.channels * sizeof(float));
-    if (e == cudaSuccess) e = cudaMalloc(&m->att_partial, (size_t)16 * m->cfg.num_heads * 4 * 66 * sizeof(float));
+    if (e == cudaSuccess) e = cudaMalloc(&m->att_partial, (size_t)16 * m->cfg.num_heads * 8 * 66 * sizeof(float));  // up to 8 position splits
     if (e == cudaSuccess) e = cudaMalloc(&m->att_counters, (size_t)16 * m->cfg.num_heads * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMemset(m->att_counters, 0, (size_t)16 * m->cfg.num_heads * sizeof(unsigned int));
     if (e == cudaSuccess) e = cudaMalloc(&m->gen_tokens, (size_t)m->max_B * m->max_T * sizeof(int));
@@ -844,6 +844,9 @@ static int enqueue_decode(b200_gpt2* m, const int* tokens, int B) {
     float* ra = m->residual;
     float* rb = m->resid2;
     const bool fuse_ln = C <= 1664;
+    // narrow projections are computed in K slices by more CTAs; the prologue that consumes them adds the slices up
+    const int ks_att = fuse_ln ? skinny_gemm_k_splits(ctx, C, C) : 1;
+    const int ks_fc = fuse_ln ? skinny_gemm_k_splits(ctx, 4 * C, C) : 1;
     DSTEP(launch_decode_encoder(ctx, ra, tokens, P + off[0], P + off[1], m->pos_dev, B, C, Vp));
     const float* branch = nullptr;  // what the next layernorm adds to the residual first
     for (int l = 0; l < L; ++l) {
@@ -852,7 +855,7 @@ static int enqueue_decode(b200_gpt2* m, const int* tokens, int B) {
         const float *ln1w = P + off[2] + (size_t)l * C, *ln1b = P + off[3] + (size_t)l * C;
         const float *ln2w = P + off[8] + (size_t)l * C, *ln2b = P + off[9] + (size_t)l * C;
         if (fuse_ln) {
-            DSTEP(launch_skinny_gemm(ctx, m->qkv, ra, qkvw, qkvb, B, C, 3 * C, 0, branch, ln1w, ln1b, rb));
+            DSTEP(launch_skinny_gemm(ctx, m->qkv, ra, qkvw, qkvb, B, C, 3 * C, 0, branch, ln1w, ln1b, rb, 1, ks_fc));
             std::swap(ra, rb);
         } else {
             if (branch) {
@@ -864,22 +867,24 @@ static int enqueue_decode(b200_gpt2* m, const int* tokens, int B) {
             DSTEP(launch_skinny_gemm(ctx, m->qkv, m->ln_out, qkvw, qkvb, B, C, 3 * C, 0));
         }
         DSTEP(launch_decode_attention(ctx, m->atty, m->qkv, m->kcache + l * per_layer, m->vcache + l * per_layer, B, C, NH, m->pos_dev, m->max_T, m->att_partial, m->att_counters));
-        DSTEP(launch_skinny_gemm(ctx, m->branch, m->atty, P + off[6] + (size_t)l * C * C, P + off[7] + (size_t)l * C, B, C, C, 0));
+        DSTEP(launch_skinny_gemm(ctx, m->branch, m->atty, P + off[6] + (size_t)l * C * C, P + off[7] + (size_t)l * C, B, C, C, 0,
+                                 nullptr, nullptr, nullptr, nullptr, ks_att));
         const float* fcw = P + off[10] + (size_t)l * 4 * C * C;
         const float* fcb = P + off[11] + (size_t)l * 4 * C;
         if (fuse_ln) {
-            DSTEP(launch_skinny_gemm(ctx, m->fch, ra, fcw, fcb, B, C, 4 * C, 1, m->branch, ln2w, ln2b, rb));
+            DSTEP(launch_skinny_gemm(ctx, m->fch, ra, fcw, fcb, B, C, 4 * C, 1, m->branch, ln2w, ln2b, rb, 1, ks_att));
         } else {
             DSTEP(launch_fused_residual_layernorm(ctx, rb, m->ln_out, nullptr, nullptr, ra, m->branch, ln2w, ln2b, B, C, 0));
             DSTEP(launch_skinny_gemm(ctx, m->fch, m->ln_out, fcw, fcb, B, C, 4 * C, 1));
         }
         std::swap(ra, rb);
-        DSTEP(launch_skinny_gemm(ctx, m->branch, m->fch, P + off[12] + (size_t)l * C * 4 * C, P + off[13] + (size_t)l * C, B, 4 * C, C, 0));
+        DSTEP(launch_skinny_gemm(ctx, m->branch, m->fch, P + off[12] + (size_t)l * C * 4 * C, P + off[13] + (size_t)l * C, B, 4 * C, C, 0,
+                                 nullptr, nullptr, nullptr, nullptr, ks_fc));
         branch = m->branch;
     }
     // final layernorm and lm-head
     if (fuse_ln) {
-        DSTEP(launch_skinny_gemm(ctx, m->logits, ra, P + off[0], nullptr, B, C, Vp, 0, branch, P + off[14], P + off[15], rb));
+        DSTEP(launch_skinny_gemm(ctx, m->logits, ra, P + off[0], nullptr, B, C, Vp, 0, branch, P + off[14], P + off[15], rb, 1, ks_fc));
     } else {
         DSTEP(launch_fused_residual_layernorm(ctx, rb, m->ln_out, nullptr, nullptr, ra, branch, P + off[14], P + off[15], B, C, 0));
         DSTEP(launch_skinny_gemm(ctx, m->logits, m->ln_out, P + off[0], nullptr, B, C, Vp, 0));

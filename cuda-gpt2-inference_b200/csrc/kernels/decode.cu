@@ -16,6 +16,7 @@
 //                           and the states are merged through shared memory
 //   decode_encoder_kernel   wte[token] + wpe[pos]
 // The position is read from device memory, so one captured CUDA graph serves every step.
+#include <cstdlib>
 #include "kernels.h"
 #include "../prim/sm100.cuh"
 
@@ -42,6 +43,9 @@ struct SkinnyArgs {
     const float* ln_b;
     float* resid_out;       // prologue: r is stored here by CTA 0
     int B, N, K, gelu;
+    int k_splits;       // > 1: K is cut into slices computed by different CTAs; slice s writes its partial sums to out + s*B*N
+    int kslice;         // floats of K per slice (a multiple of 128; K when k_splits == 1)
+    int branch_parts;   // prologue: branch holds this many partial results [parts][B][K], summed in order
 };
 
 // NV = float4 per lane that hold a row in the layernorm prologue (0: no prologue compiled in).
@@ -58,7 +62,13 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     const int rw = warp;
     const int groups = (N + ROWS - 1) / ROWS;                  // row groups, one per warp at a time
     const int batches = (groups + kRowWarps - 1) / kRowWarps;  // a CTA takes kRowWarps groups at a time
-    const int kbeg = 0, kend = K;
+    // K slices (narrow outputs: more CTAs, each with a shorter chain of weight round trips; the
+    // consumer's prologue adds the partial results up in slice order).  The grid is a multiple of
+    // k_splits, so a CTA keeps its slice over all of its units.
+    const int ks = blockIdx.x % a.k_splits;
+    const int units = batches * a.k_splits;
+    const int kbeg = ks * a.kslice, kend = min(K, kbeg + a.kslice);
+    const int KS4 = (kend - kbeg) >> 2;  // staged floats per input row, in float4
     // The kernel is a chain of memory round trips (each several hundred to two thousand cycles),
     // so everything that does not depend on the previous kernel is requested before waiting for
     // it: the first chunk of this warp's weight rows, the bias, the layernorm parameters.
@@ -75,7 +85,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                               : make_float4(0.f, 0.f, 0.f, 0.f);  // rows clamped: masked at the store
         }
     };
-    request_w((blockIdx.x * kRowWarps + rw) * ROWS, kbeg);
+    request_w(((blockIdx.x / a.k_splits) * kRowWarps + rw) * ROWS, kbeg);
     float4* lnw4 = xs4 + NB * K4;  // layernorm weight and bias, behind the input rows
     float4* lnb4 = lnw4 + K4;
     if (NV > 0) {
@@ -103,6 +113,16 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                 for (int i = 0; i < NVV; ++i) {
                     const int c = lane + i * 32;
                     if (b < B && c < K4) t[i] = *reinterpret_cast<const float4*>(a.branch + (size_t)b * K + c * 4);
+                }
+                for (int part = 1; part < a.branch_parts; ++part) {  // the producer's K slices, in order
+#pragma unroll
+                    for (int i = 0; i < NVV; ++i) {
+                        const int c = lane + i * 32;
+                        if (b < B && c < K4) {
+                            const float4 u = *reinterpret_cast<const float4*>(a.branch + ((size_t)part * B + b) * K + c * 4);
+                            t[i].x += u.x; t[i].y += u.y; t[i].z += u.z; t[i].w += u.w;
+                        }
+                    }
                 }
             }
 #pragma unroll
@@ -146,14 +166,15 @@ skinny_gemm_kernel(const SkinnyArgs a) {
         }
     } else {
         // eight independent loads per thread in flight at a time
-        const int total = NB * K4;
+        const int total = NB * KS4;
         for (int i0 = threadIdx.x; i0 < total; i0 += 8 * kSkinnyThreads) {
             float4 v[8];
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
                 const int i = i0 + u * kSkinnyThreads;
                 v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-                if (i < B * K4) v[u] = *(reinterpret_cast<const float4*>(a.x) + i);  // rows are contiguous: [B][K]
+                const int b = i / KS4, c = i - b * KS4;  // this CTA's K slice of row b
+                if (i < B * KS4) v[u] = *reinterpret_cast<const float4*>(a.x + (size_t)b * K + kbeg + c * 4);
             }
 #pragma unroll
             for (int u = 0; u < 8; ++u) {
@@ -163,11 +184,14 @@ skinny_gemm_kernel(const SkinnyArgs a) {
         }
     }
     __syncthreads();
-    for (int batch = blockIdx.x; batch < batches; batch += gridDim.x) {
+    const int xs_stride = (NV > 0) ? K4 : KS4;  // the prologue stages whole rows
+    float* __restrict__ out = a.out + (size_t)ks * B * N;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+        const int batch = unit / a.k_splits;
         const int n0 = (batch * kRowWarps + rw) * ROWS;
         float bias_r[ROWS];
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) bias_r[r] = (a.bias && n0 + r < N) ? __ldg(a.bias + n0 + r) : 0.f;
+        for (int r = 0; r < ROWS; ++r) bias_r[r] = (a.bias && ks == 0 && n0 + r < N) ? __ldg(a.bias + n0 + r) : 0.f;
         float acc[ROWS][NB];
 #pragma unroll
         for (int r = 0; r < ROWS; ++r)
@@ -183,7 +207,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
 #pragma unroll
                 for (int r = 0; r < ROWS; ++r) wc[s][r] = w[s][r];
             if (kc0 + kSkinnyKC < kend) request_w(n0, kc0 + kSkinnyKC);
-            else if (batch + (int)gridDim.x < batches) request_w(((batch + gridDim.x) * kRowWarps + rw) * ROWS, kbeg);
+            else if (unit + (int)gridDim.x < units) request_w((((unit + gridDim.x) / a.k_splits) * kRowWarps + rw) * ROWS, kbeg);
             if (n0 < N) {
 #pragma unroll
                 for (int s = 0; s < kSkinnySteps; ++s) {
@@ -191,7 +215,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                     if (k4 * 4 < kc) {
 #pragma unroll
                         for (int b = 0; b < NB; ++b) {
-                            const float4 xv = xs4[b * K4 + (kc0 >> 2) + k4];
+                            const float4 xv = xs4[b * xs_stride + ((kc0 - kbeg) >> 2) + k4];
 #pragma unroll
                             for (int r = 0; r < ROWS; ++r) {
                                 float t = acc[r][b];
@@ -225,7 +249,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                     if (((r * NB + b) & 31) == lane && n0 + r < N && b < B) {
                         float v = acc[r][b] + bias_r[r];
                         if (a.gelu) v = gelu_tanh(v);
-                        a.out[(size_t)b * N + n0 + r] = v;
+                        out[(size_t)b * N + n0 + r] = v;
                     }
                 }
         }
@@ -249,7 +273,10 @@ __global__ void kv_append_kernel(float4* __restrict__ kcache, float4* __restrict
 }
 
 constexpr int kDecAttThreads = 256;
-constexpr int kDecAttSplits = 4;  // CTAs per (sequence, head): each walks a quarter of the positions
+#ifndef B200_DEC_SPLITS
+#define B200_DEC_SPLITS 4
+#endif
+constexpr int kDecAttSplits = B200_DEC_SPLITS;  // CTAs per (sequence, head): each walks its share of the positions (at most 8: the state buffer's size; 8 measured slower, 593 vs 560 us per step)
 
 // q: row b of qkv [B, 3C] (first C columns); caches [B][cache_T][C]; positions 0..pos take part.
 // grid (NH, B, kDecAttSplits).  Every CTA leaves its softmax state {m, l, o[64]} in `partial`;
@@ -264,6 +291,9 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     griddep_wait();
     griddep_launch_dependents();
     const int h = blockIdx.x, b = blockIdx.y, z = blockIdx.z;
+    // the query is requested together with the position (two independent round trips, not one after the other)
+    const int hl0 = threadIdx.x & 15;
+    float4 q = *reinterpret_cast<const float4*>(qkv + (size_t)b * 3 * C + h * 64 + hl0 * 4);
     const int pos = *pos_ptr;
     const int per = (((pos + kDecAttSplits) / kDecAttSplits + 15) / 16) * 16;  // positions per split
     const int t_begin = z * per, t_end = min(pos + 1, t_begin + per);
@@ -280,7 +310,6 @@ decode_attention_kernel(float* __restrict__ out, const float* __restrict__ qkv, 
     const int half = lane >> 4, hl = lane & 15;  // a half-warp covers the 64 floats of one cached row
     const int slot = warp * 2 + half;            // 16 half-warps walk positions slot, slot + 16, ...
     const float scale = 0.125f;                  // 1 / sqrt(64)
-    float4 q = *reinterpret_cast<const float4*>(qkv + (size_t)b * 3 * C + h * 64 + hl * 4);
     q.x *= scale; q.y *= scale; q.z *= scale; q.w *= scale;
     const float* kbase = kcache + (size_t)b * cache_T * C + h * 64 + hl * 4;
     const float* vbase = vcache + (size_t)b * cache_T * C + h * 64 + hl * 4;
@@ -399,22 +428,41 @@ int launch_decode_encoder(b200_ctx* ctx, float* out, const int* tok, const float
     return B200_OK;
 }
 
+// K slices of a plain product (no prologue, no activation) whose output is so narrow that its row
+// batches leave most SMs idle: as many as fit in one wave, at most 4, each at least 256 floats of K
+// in whole steps of 128.  The caller hands the same number to the consumer as branch_parts.
+int skinny_gemm_k_splits(const b200_ctx* ctx, int K, int N) {
+    // tuning hook: B200_DECODE_KSPLIT=1 switches the slices off
+    static const int forced = [] { const char* e = getenv("B200_DECODE_KSPLIT"); return e ? atoi(e) : 0; }();
+    if (forced == 1) return 1;
+    const int batches = ((N + 1) / 2 + 7) / 8;
+    int ks = ctx->num_sms / (batches > 0 ? batches : 1);
+    if (ks > 4) ks = 4;
+    while (ks > 1 && (K % (128 * ks) || K / ks < 256)) --ks;
+    return ks < 1 ? 1 : ks;
+}
+
 int launch_skinny_gemm(b200_ctx* ctx, float* out, const float* x, const float* W, const float* bias, int B,
                        int K, int N, int gelu, const float* branch, const float* ln_w, const float* ln_b,
-                       float* resid_out) {
+                       float* resid_out, int k_splits, int branch_parts) {
     if (B < 1 || B > 16 || K % 4 || N < 1) return B200_ERR_SHAPE;
     if (ln_w && (K > 1664 || !ln_b || !resid_out || resid_out == x)) return B200_ERR_SHAPE;
+    if (k_splits < 1 || branch_parts < 1) return B200_ERR_SHAPE;
+    if (k_splits > 1 && (ln_w || gelu || K % (128 * k_splits))) return B200_ERR_SHAPE;
     const int nb = B <= 8 ? 8 : 16;
-    const size_t x_bytes = ((size_t)nb * K * 4 + 127) & ~(size_t)127;
+    const int kslice = K / k_splits;
+    const size_t x_bytes = ((size_t)nb * kslice * 4 + 127) & ~(size_t)127;
     if (x_bytes > (size_t)200 * 1024) return B200_ERR_LIMIT;
     SkinnyArgs a;
     a.out = out; a.x = x; a.W = W; a.bias = bias; a.branch = branch; a.ln_w = ln_w; a.ln_b = ln_b; a.resid_out = resid_out;
     a.B = B; a.N = N; a.K = K; a.gelu = gelu;
+    a.k_splits = k_splits; a.kslice = kslice; a.branch_parts = branch_parts;
     constexpr int rows = 2;  // per warp
     const int groups = (N + rows - 1) / rows;
     const int batches = (groups + 7) / 8;
+    if (k_splits > 1 && batches * k_splits > ctx->num_sms) return B200_ERR_SHAPE;  // the slices of a unit run side by side
     // one wave: a CTA stages the input rows (and normalises them) once and then loops over its batches
-    const int grid = batches < ctx->num_sms ? batches : ctx->num_sms;
+    const int grid = batches * k_splits < ctx->num_sms ? batches * k_splits : ctx->num_sms;
     const int nv = !ln_w ? 0 : (K <= 768 ? 6 : 13);
     const size_t smem = x_bytes + (ln_w ? (size_t)2 * K * 4 : 0);
     cudaError_t le = cudaSuccess;

@@ -108,9 +108,13 @@ int launch_attention_split(b200_ctx* ctx, float* out, float* lse, const uint16_t
 // out[B,N] = act(x[B,K] * W[N,K]^T + bias[N])
 // with ln_w: x = layernorm(x + branch) * ln_w + ln_b first (branch nullable), and x + branch is
 // stored to resid_out (a buffer other than x)
+// k_splits > 1 (plain product only): K is cut into that many slices computed by different CTAs, and
+// out receives the partial results [k_splits][B][N] (the bias in slice 0) for a consumer that adds them
+// up in order - the layernorm prologue does, given branch_parts = the producer's k_splits
 int launch_skinny_gemm(b200_ctx* ctx, float* out, const float* x, const float* W, const float* bias, int B,
                        int K, int N, int gelu, const float* branch = nullptr, const float* ln_w = nullptr,
-                       const float* ln_b = nullptr, float* resid_out = nullptr);
+                       const float* ln_b = nullptr, float* resid_out = nullptr, int k_splits = 1, int branch_parts = 1);
+int skinny_gemm_k_splits(const b200_ctx* ctx, int K, int N);  // the slices worth using for a [*,K] x [N,K]^T product
 // k and v columns of qkv rows [B*T, 3C] -> caches [B][cache_T][C] at positions pos0 .. pos0+T-1
 int launch_kv_append(b200_ctx* ctx, float* kcache, float* vcache, const float* qkv, int B, int T, int C, int pos0,
                      int cache_T);
