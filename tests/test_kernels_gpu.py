@@ -499,6 +499,32 @@ def test_matmul_bf16x3_close_to_fp32(ctx, dev, orc, B, T, C, OC, has_bias, act, 
         assert _rel_rms(got, want) < (5e-5 if base is None else 2e-4)
 
 
+def test_attention_fp16_moves_its_reference_maximum(ctx, dev, orc):
+    """The kernel keeps O in tensor memory and only rescales it when a block of keys raises a row's
+    maximum by more than 2^8.  On N(0,1) inputs that happens on the first block of a tile only; here
+    the keys grow from block to block (x1, x4, x16, x64 per 128 positions, then back down), so that
+    the running maximum jumps far beyond the threshold in some blocks, by less in others and falls
+    in the rest.  q and k are given as exact fp16 values: what is compared is the softmax and P.V
+    machinery, not the 11-bit scores."""
+    import torch
+    B, T, NH = 2, 768, 2
+    C = NH * 64
+    qkv = orc.fill_normal((B, T, 3 * C), 171)
+    gain = np.float32([1, 4, 16, 64, 8, 2])[np.arange(T) // 128]
+    qkv[:, :, C:2 * C] *= gain[None, :, None]
+    qkv[:, :, :2 * C] = qkv[:, :, :2 * C].astype(np.float16).astype(np.float32)
+    want, wlse = orc.attention_forward(qkv, NH, precise=True)
+    planes = torch.empty((2, B, T, 3 * C), dtype=torch.int16, device="cuda")
+    ctx.split_fp16(planes[0], planes[1], dev.to(qkv), qkv.size)
+    out, lse = dev.full((B, T, C), float("nan")), dev.full((B, NH, T), float("nan"))
+    ctx.attention_forward_fp16(out, lse, planes, B, T, C, NH)
+    ctx.sync_check()
+    got = dev.back(out)
+    assert np.isfinite(got).all()
+    assert np.abs(got - want).max() < 2.5e-3, np.abs(got - want).max()
+    assert np.abs(dev.back(lse) - wlse).max() < 2e-3 + 1e-5 * np.abs(wlse).max()
+
+
 @pytest.mark.parametrize("B,T,NH", [(1, 64, 1), (2, 128, 2), (1, 256, 12), (2, 192, 3), (1, 1024, 2), (1, 384, 25)])
 def test_attention_fp16_matches_oracle(ctx, dev, orc, B, T, NH):
     """The attention of the default mode: q, k, v as two fp16 planes, q.k from the hi planes (11 bits,
