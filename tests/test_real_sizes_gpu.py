@@ -173,6 +173,35 @@ def test_attention_b8_nh12_t1024_against_oracle(ctx, dev, orc):
         assert np.abs(lse[b, h].cpu().numpy() - wlse[0, 0]).max() < 4e-3
 
 
+@pytest.mark.parametrize("NH", [12, 25])
+def test_attention_fp16_b8_t1024_against_oracle(ctx, dev, orc, NH):
+    """The default mode's attention at the benchmark's size (and with GPT-2 XL's 25 heads): fp16 planes
+    in, guarded fp32 output and statistics; the oracle runs on three (batch, head) pairs."""
+    import torch
+    B, T = 8, 1024
+    C = NH * 64
+    g = torch.Generator(device="cuda").manual_seed(4)
+    qkv = torch.empty(B, T, 3 * C, device="cuda").normal_(0, 1, generator=g)
+    planes = torch.empty((2, B, T, 3 * C), dtype=torch.int16, device="cuda")
+    ctx.split_fp16(planes[0], planes[1], qkv, qkv.numel())
+    out, check = _guarded(torch, (B, T, C))
+    lse, check_l = _guarded(torch, (B, NH, T))
+    torch.cuda.synchronize()
+    ctx.attention_forward_fp16(out, lse, planes, B, T, C, NH)
+    ctx.sync_check()
+    check()
+    check_l()
+    assert torch.isfinite(out).all() and torch.isfinite(lse).all()
+    for b, h in ((0, 0), (7, NH - 1), (3, 5)):
+        sl = [slice(k * C + h * 64, k * C + (h + 1) * 64) for k in range(3)]
+        one = torch.cat([qkv[b:b + 1, :, s] for s in sl], dim=-1).cpu().numpy()
+        want, wlse = orc.attention_forward(one, 1, precise=True)
+        got = out[b, :, h * 64:(h + 1) * 64].cpu().numpy()
+        assert np.abs(got - want[0]).max() < 2.5e-3
+        assert np.sqrt(np.mean((got - want[0]) ** 2)) < 2e-4
+        assert np.abs(lse[b, h].cpu().numpy() - wlse[0, 0]).max() < 2e-3
+
+
 @pytest.mark.parametrize("C", [768, 1600])
 def test_fused_residual_layernorm_8192_rows(ctx, dev, orc, C):
     import torch
