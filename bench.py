@@ -856,7 +856,9 @@ def run_kernel_sweep(args):
     g = torch.Generator(device="cuda").manual_seed(1)
 
     def randn(*shape, std=1.0):
-        return torch.empty(shape, device="cuda").normal_(0.0, std, generator=g)
+        t = torch.empty(shape, device="cuda").normal_(0.0, std, generator=g)
+        torch.cuda.synchronize()  # made on torch's stream; the library reads it on the context's
+        return t
 
     cases = []
     if args.op in ("matmul", "all"):

@@ -183,10 +183,10 @@ def test_attention_fp16_b8_t1024_against_oracle(ctx, dev, orc, NH):
     g = torch.Generator(device="cuda").manual_seed(4)
     qkv = torch.empty(B, T, 3 * C, device="cuda").normal_(0, 1, generator=g)
     planes = torch.empty((2, B, T, 3 * C), dtype=torch.int16, device="cuda")
-    ctx.split_fp16(planes[0], planes[1], qkv, qkv.numel())
     out, check = _guarded(torch, (B, T, C))
     lse, check_l = _guarded(torch, (B, NH, T))
-    torch.cuda.synchronize()
+    torch.cuda.synchronize()  # the inputs were made on torch's stream, the library runs on the context's
+    ctx.split_fp16(planes[0], planes[1], qkv, qkv.numel())
     ctx.attention_forward_fp16(out, lse, planes, B, T, C, NH)
     ctx.sync_check()
     check()
