@@ -834,6 +834,31 @@ def _xl_and_multi_gpu(pkg, torch, dist, ctx, stream, world, rank, barrier, max_o
                             "per attention and MLP block on the compute stream (row-chunked overlap on a communication stream is an "
                             "option that measured slower); the serialised figures come from a pass with one event pair per launch; "
                             "exposed = ms_per_step - (serialised - all-reduce)"}
+    if world == 2:
+        # the same model with the partial sums handed over through peer memory instead of all-reduces
+        try:
+            tpm.connect_tp_peer()
+            peer_logits = tpm.forward(tok8, 8, T)
+            ctx.sync_check()
+            same = bool(torch.equal(peer_logits, tp_logits))
+            ms_peer = _time_steps(torch, tpm, ctx, stream, tok8, 8, T, 3, 1, barrier, max_over_ranks)
+            tpm.set_profile(True)
+            for _ in range(2):
+                tpm.forward(tok8, 8, T)
+            prof = tpm.read_profile()
+            tpm.set_profile(False)
+            tot = sum(v[0] for v in prof.values())
+            ser_ms, ar_ms = tot / 2, prof["allreduce"][0] / 2
+            out["tp_xl"]["peer_handover"] = {
+                "value": 8 * T / (ms_peer * 1e-3), "unit": UNIT, "ms_per_step": ms_peer, "logits_equal_to_allreduce_run": "bitwise" if same else "MISMATCH",
+                "ms_per_step_serialised": ser_ms, "handover_ms_per_step": ar_ms,
+                "exposed_handover_ms": max(0.0, ms_peer - (ser_ms - ar_ms)),
+                "exposed_handover_share": max(0.0, ms_peer - (ser_ms - ar_ms)) / ms_peer if ms_peer else None,
+                "note": "b200_gpt2_tp_peer_*: each projection GEMM also stores its tiles into the other GPU's memory (TMA stores over "
+                        "NVLink, under the GEMM); a flag word and a bounded wait replace the all-reduce; the fused residual + layernorm "
+                        "adds the two partial sums; hand-over = the signal and wait kernels"}
+        except Exception as e:  # noqa: BLE001
+            out["tp_xl"]["peer_handover"] = {"error": str(e)}
     tpm.close()
     xlm.close()
     return out

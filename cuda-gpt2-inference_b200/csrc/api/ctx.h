@@ -40,6 +40,9 @@ struct b200_ctx {
     int* h_status = nullptr;  // pinned host copy of that word, filled by b200_ctx_sync_check
     // CTA-pair GEMM with K slices: one flag word per (slice, tile, CTA, epilogue warp); all zero between launches
     unsigned int* d_split_flags = nullptr;
+    // one-shot: device address of a CUtensorMap; the next fp32 plain-store GEMM launch on this context also stores
+    // its output tiles through it (into a peer GPU's memory) and clears the field
+    const void* next_gemm_out2 = nullptr;
     size_t split_flag_words = 0;
     uint64_t launches = 0;
     bool pdl = true;  // launch with programmatic stream serialization (B200_PDL=0 turns it off)

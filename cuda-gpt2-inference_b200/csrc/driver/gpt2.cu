@@ -76,6 +76,20 @@ struct b200_gpt2 {
     // the overlap hides - so chunking is off unless asked for.
     int tp_chunks = 1;
     int tp_reserve_sms = 0;
+    // Two-way tensor parallelism without an all-reduce (b200_gpt2_tp_peer_*): the projection GEMM
+    // stores every tile of its partial sum a second time, into the peer GPU's memory, while it
+    // computes; a word written after the GEMM tells the peer that the sum is complete, and the fused
+    // residual + layernorm adds the two partial sums itself.  Two receive buffers, used in turn:
+    // the peer's GEMM number e + 2 - the next writer of the buffer my layernorm number e reads -
+    // is behind its layernorm e + 1, which waited for my GEMM e + 1, which follows my layernorm e.
+    float* peer_in[2] = {nullptr, nullptr};   // local: receives the peer's partial sums
+    unsigned int* peer_word = nullptr;         // local: [0] the peer's epoch of completed GEMMs
+    float* peer_out[2] = {nullptr, nullptr};  // the peer's peer_in, mapped into this process
+    unsigned int* peer_word_remote = nullptr;  // the peer's peer_word, mapped
+    CUtensorMap* peer_maps = nullptr;          // device copies of the tensor maps over peer_out[0..1], per projection width
+    int peer_maps_rows = 0;
+    unsigned int peer_epoch = 0;
+    bool peer_on = false;
     std::map<std::pair<std::pair<int, int>, int>, cudaGraphExec_t> graphs;  // by (B, T, results)
     // per-operator timing (b200_gpt2_set_profile): one event pair per kernel launch
     bool profile = false;
@@ -235,6 +249,21 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
     int st;
     const bool prof = m->profile;
     const int tpc = (m->tp_size > 1 && g_tf32 && m->gemm_mode == B200_TF32) ? tp_chunks(m, M, prof) : 1;
+    // two-way tensor parallelism over peer memory instead of all-reduces (see the model's peer_* fields)
+    const bool peer = m->peer_on && m->tp_size == 2 && g_tf32 && m->gemm_mode == B200_TF32 && tpc == 1;
+    if (peer) {
+        // (a tensor-parallel forward is never replayed from a graph, so the epochs below are live values)
+        if (m->peer_maps_rows != M) {
+            CUtensorMap host_maps[2];
+            for (int i = 0; i < 2; ++i) {
+                st = b200_get_tensor_map(ctx, &host_maps[i], m->peer_out[i], (uint64_t)M, (uint64_t)C, (uint64_t)C, 32, 32);
+                if (st != B200_OK) return st;
+            }
+            B200_CUDA(ctx, cudaMemcpyAsync(m->peer_maps, host_maps, sizeof(host_maps), cudaMemcpyHostToDevice, ctx->stream));
+            m->peer_maps_rows = M;
+        }
+    }
+    unsigned int peer_e = 0;
 #define STEP(cat, call)                                             \
     do {                                                            \
         if (prof) { st = prof_begin(m, (cat)); if (st != B200_OK) return st; } \
@@ -289,15 +318,21 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         if (hx) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, atty_h, PH + o_apw, PL + o_apw, apb, M, A, C, accum));
         else if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, atty_h, PH + o_apw, apb, M, A, C, accum));
         else if (tpc > 1) STEP(B200_PROF_GEMM_ATTPROJ, tp_projection_overlapped(m, proj_out, m->atty, W + o_apw, apb, M, A, C, tpc));
-        else STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, proj_out, m->atty, W + o_apw, apb, nullptr, M, A, C, accum, m->gemm_mode));
+        else {
+            if (peer) { peer_e = ++m->peer_epoch; ctx->next_gemm_out2 = m->peer_maps + (peer_e & 1); }
+            STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, proj_out, m->atty, W + o_apw, apb, nullptr, M, A, C, accum, m->gemm_mode));
+        }
         if (accum) {
             STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, ln2w, ln2b, M, C, ln_flags));
         } else {
             // tensor parallel: every rank holds a partial sum over its heads; one all-reduce per block
             // (already issued, chunk by chunk, when the projection ran overlapped)
-            if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
+            if (peer) {
+                STEP(B200_PROF_ALLREDUCE, launch_peer_signal(ctx, m->peer_word_remote, peer_e));
+                STEP(B200_PROF_ALLREDUCE, launch_peer_wait(ctx, m->peer_word, peer_e));
+            } else if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
             STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
-                                                 m->branch, ln2w, ln2b, M, C, ln_flags));
+                                                 m->branch, ln2w, ln2b, M, C, ln_flags, peer ? m->peer_in[peer_e & 1] : nullptr));
         }
         if (hx) {
             STEP(B200_PROF_GEMM_FC, launch_gemm_bf16x3(ctx, nullptr, fch_h, ln_h, PH + o_fcw, PL + o_fcw, fcb, M, C, F, GEMM_GELU));
@@ -308,7 +343,10 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         } else {
             STEP(B200_PROF_GEMM_FC, launch_gemm_tf32(ctx, m->fch, m->ln_out, W + o_fcw, fcb, nullptr, M, C, F, GEMM_GELU | grnd, m->gemm_mode));
             if (tpc > 1) STEP(B200_PROF_GEMM_FCPROJ, tp_projection_overlapped(m, proj_out, m->fch, W + o_fpw, fpb, M, F, C, tpc));
-            else STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, proj_out, m->fch, W + o_fpw, fpb, nullptr, M, F, C, accum, m->gemm_mode));
+            else {
+                if (peer) { peer_e = ++m->peer_epoch; ctx->next_gemm_out2 = m->peer_maps + (peer_e & 1); }
+                STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, proj_out, m->fch, W + o_fpw, fpb, nullptr, M, F, C, accum, m->gemm_mode));
+            }
         }
         const float* nw = (l + 1 < L) ? P + off[2] + (size_t)(l + 1) * C : P + off[14];
         const float* nb = (l + 1 < L) ? P + off[3] + (size_t)(l + 1) * C : P + off[15];
@@ -317,9 +355,12 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         if (accum) {
             STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, nw, nb, M, C, next_flags));
         } else {
-            if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
+            if (peer) {
+                STEP(B200_PROF_ALLREDUCE, launch_peer_signal(ctx, m->peer_word_remote, peer_e));
+                STEP(B200_PROF_ALLREDUCE, launch_peer_wait(ctx, m->peer_word, peer_e));
+            } else if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
             STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
-                                                 m->branch, nw, nb, M, C, next_flags));
+                                                 m->branch, nw, nb, M, C, next_flags, peer ? m->peer_in[peer_e & 1] : nullptr));
         }
     }
     const size_t o_head = off[0] + (size_t)m->vp_row0 * C;
@@ -454,6 +495,49 @@ int b200_gpt2_set_tp_overlap(b200_gpt2* m, int chunks, int reserve_sms) {
     return B200_OK;
 }
 
+// ---- two-way tensor parallelism over peer memory -------------------------------------------------
+int b200_gpt2_tp_peer_export(b200_gpt2* m, unsigned char* handles) {
+    if (!m || !handles) return B200_ERR_NULL;
+    if (m->tp_size != 2) { m->ctx->last_error = "peer hand-over is for a tensor-parallel group of two"; return B200_ERR_STATE; }
+    b200_ctx* ctx = m->ctx;
+    b200_device_guard guard(ctx);
+    const size_t bytes = (size_t)m->max_B * m->max_T * m->cfg.channels * sizeof(float);
+    for (int i = 0; i < 2; ++i)
+        if (!m->peer_in[i]) B200_CUDA(ctx, cudaMalloc(&m->peer_in[i], bytes));
+    if (!m->peer_word) {
+        B200_CUDA(ctx, cudaMalloc(&m->peer_word, 256));
+        B200_CUDA(ctx, cudaMemset(m->peer_word, 0, 256));
+    }
+    if (!m->peer_maps) B200_CUDA(ctx, cudaMalloc(&m->peer_maps, 2 * sizeof(CUtensorMap)));
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "handle size");
+    cudaIpcMemHandle_t h;
+    B200_CUDA(ctx, cudaIpcGetMemHandle(&h, m->peer_in[0])); memcpy(handles, &h, 64);
+    B200_CUDA(ctx, cudaIpcGetMemHandle(&h, m->peer_in[1])); memcpy(handles + 64, &h, 64);
+    B200_CUDA(ctx, cudaIpcGetMemHandle(&h, m->peer_word)); memcpy(handles + 128, &h, 64);
+    return B200_OK;
+}
+
+int b200_gpt2_tp_peer_connect(b200_gpt2* m, const unsigned char* peer_handles) {
+    if (!m || !peer_handles) return B200_ERR_NULL;
+    if (m->tp_size != 2 || !m->peer_word) { m->ctx->last_error = "b200_gpt2_tp_peer_export comes first"; return B200_ERR_STATE; }
+    b200_ctx* ctx = m->ctx;
+    b200_device_guard guard(ctx);
+    cudaIpcMemHandle_t h;
+    void* q = nullptr;
+    for (int i = 0; i < 2; ++i) {
+        memcpy(&h, peer_handles + 64 * i, 64);
+        B200_CUDA(ctx, cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess));
+        m->peer_out[i] = static_cast<float*>(q);
+    }
+    memcpy(&h, peer_handles + 128, 64);
+    B200_CUDA(ctx, cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess));
+    m->peer_word_remote = static_cast<unsigned int*>(q);
+    m->peer_maps_rows = 0;
+    m->peer_epoch = 0;
+    m->peer_on = true;
+    return B200_OK;
+}
+
 int b200_gpt2_set_allreduce(b200_gpt2* m, b200_allreduce_fn fn, void* user) {
     if (!m) return B200_ERR_NULL;
     m->allreduce = fn;
@@ -520,6 +604,11 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     for (cudaEvent_t e : m->ev_pool) cudaEventDestroy(e);
     for (cudaEvent_t e : m->tp_ev) if (e) cudaEventDestroy(e);
     if (m->comm_stream) cudaStreamDestroy(m->comm_stream);
+    for (float* q : m->peer_out) if (q) cudaIpcCloseMemHandle(q);
+    if (m->peer_word_remote) cudaIpcCloseMemHandle(m->peer_word_remote);
+    for (float* q : m->peer_in) if (q) cudaFree(q);
+    if (m->peer_word) cudaFree(m->peer_word);
+    if (m->peer_maps) cudaFree(m->peer_maps);
     void* ptrs[] = {m->params, m->params_h, m->params_l, m->params_r, m->qkv_small, m->residual, m->ln_out, m->qkv, m->atty, m->branch,
                     m->fch, m->logits, m->tokens, m->argmax, m->argmax_keys, m->last_logits, m->kcache, m->vcache, m->lse_part};
     for (void* p : ptrs) if (p) cudaFree(p);

@@ -47,6 +47,9 @@ struct GemmArgs {
     int tile_w, unit_cols, k_splits;
     unsigned int* split_flags;   // per (K slice, tile, CTA, epilogue warp): set once its sums are in the output, cleared by its reader
     float alpha = 1.0f;          // the accumulator is multiplied by this before the epilogue (fp8 operands: undoes their scales)
+    // not null: a tensor map in global memory (same shape and 32 x 32 box as the output's) through which every
+    // tile of a plain-store fp32 epilogue is stored a second time - into a peer GPU's memory (tensor parallel)
+    const CUtensorMap* tmap_out2 = nullptr;
 };
 
 // Arg-max keys: the value as an order-preserving 32-bit integer in the high half, the inverted
@@ -213,6 +216,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
     const bool do_lse = do_argmax && args.lse_part != nullptr;
     float lse_m = -INFINITY, lse_s = 0.f;  // running maximum and sum of exp(value - maximum) of this thread's columns
     const bool via_tma = args.residual == nullptr;
+    if (args.tmap_out2 && lane == 0) tma_acquire_global_desc(args.tmap_out2);  // once per tile and warp: cheap next to the tile
     const bool skip_store = args.store_period > 0 && (row0 % args.store_period) < args.store_period - 32;
     if (via_tma) {  // the stores of the previous tile have left the staging buffers
         if (lane == 0) tma_store_wait_read();
@@ -304,6 +308,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
             if (lane == 0 && cbase < args.N && row0 < args.M) {
                 if (args.flags & GEMM_ACCUM_OUT) tma_reduce_add_2d(tmap_out, cbase, row0, stage);
                 else tma_store_2d(tmap_out, cbase, row0, stage);
+                if (args.tmap_out2) tma_store_2d(args.tmap_out2, cbase, row0, stage);
                 tma_store_commit();
             }
             continue;

@@ -384,6 +384,12 @@ int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp
     a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
     a.alpha = alpha;
+    a.tmap_out2 = static_cast<const CUtensorMap*>(ctx->next_gemm_out2);
+    ctx->next_gemm_out2 = nullptr;
+    if (a.tmap_out2 && (out_h || residual || (flags & GEMM_ACCUM_OUT) || store_period)) {
+        ctx->last_error = "a second output needs a plain fp32 store epilogue";
+        return B200_ERR_STATE;
+    }
     a.num_m_blocks = (M + 2 * BM - 1) / (2 * BM);
     // weight small enough to stay in L2: columns fastest, so the pairs working side by side share an
     // inp tile; otherwise rows fastest, so that they share a few weight tiles while the weights stream once

@@ -16,7 +16,10 @@ int launch_layernorm(b200_ctx* ctx, float* out, float* mean, float* rstd, const 
                      const float* weight, const float* bias, int M, int C, int flags);
 int launch_fused_residual_layernorm(b200_ctx* ctx, float* res_out, float* ln_out, float* mean,
                                     float* rstd, const float* inp1, const float* inp2,
-                                    const float* weight, const float* bias, int M, int C, int flags);
+                                    const float* weight, const float* bias, int M, int C, int flags, const float* inp3 = nullptr);  // inp3: x = inp1 + (inp2 + inp3)
+// hand-over words between two GPUs (peer-mapped memory): see rowwise.cu
+int launch_peer_signal(b200_ctx* ctx, unsigned int* peer_word, unsigned int value);
+int launch_peer_wait(b200_ctx* ctx, const unsigned int* my_word, unsigned int value);
 int launch_residual(b200_ctx* ctx, float* out, const float* a, const float* b, size_t N);
 int launch_gelu(b200_ctx* ctx, float* out, const float* inp, size_t N);
 int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,

@@ -28,13 +28,15 @@ __device__ __forceinline__ float warp_sum(float v) {
 
 // One warp per row.  NV = float4 per lane held in registers (covers C <= 128*NV).
 // FUSED: x = inp1 + inp2 is stored to res_out first (which may alias an input: every
-// element is read before it is written, by the same lane).
+// element is read before it is written, by the same lane).  With inp3: x = inp1 + (inp2 + inp3),
+// the two partial sums of a two-way tensor-parallel projection (inp2 + inp3 is what an all-reduce
+// would have left in inp2, bit for bit, on either rank).
 template <int NV, bool FUSED>
 __global__ void __launch_bounds__(kRowWarps * 32)
 layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict__ mean,
                       float* __restrict__ rstd, const float* inp1, const float* inp2,
                       const float* __restrict__ weight, const float* __restrict__ bias, int M, int C,
-                      int flags) {
+                      int flags, const float* inp3) {
     griddep_wait();
     griddep_launch_dependents();
     const int lane = threadIdx.x & 31;
@@ -43,6 +45,7 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
     const int C4 = C >> 2;
     const float4* x1 = reinterpret_cast<const float4*>(inp1 + (size_t)row * C);
     const float4* x2 = FUSED ? reinterpret_cast<const float4*>(inp2 + (size_t)row * C) : nullptr;
+    const float4* x3 = (FUSED && inp3) ? reinterpret_cast<const float4*>(inp3 + (size_t)row * C) : nullptr;
 
     float4 v[NV];
 #pragma unroll
@@ -51,7 +54,11 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
         if (c < C4) {
             v[i] = x1[c];
             if (FUSED) {
-                const float4 b = x2[c];
+                float4 b = x2[c];
+                if (x3) {
+                    const float4 b3 = x3[c];
+                    b.x += b3.x; b.y += b3.y; b.z += b3.z; b.w += b3.w;
+                }
                 v[i].x += b.x; v[i].y += b.y; v[i].z += b.z; v[i].w += b.w;
             }
         } else {
@@ -121,13 +128,13 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
 template <bool FUSED>
 int launch_ln_any(b200_ctx* ctx, float* out, float* res_out, float* mean, float* rstd,
                   const float* inp1, const float* inp2, const float* weight, const float* bias,
-                  int M, int C, int flags) {
+                  int M, int C, int flags, const float* inp3 = nullptr) {
     const int nv = (C / 4 + 31) / 32;
     const dim3 grid((M + kRowWarps - 1) / kRowWarps), block(kRowWarps * 32);
     cudaError_t le = cudaSuccess;
 #define B200_LN_CASE(NV)                                                                                    \
     le = launch_pdl(ctx, layernorm_rows_kernel<NV, FUSED>, grid, block, 0, out, res_out, mean, rstd, inp1, \
-                    inp2, weight, bias, M, C, flags)
+                    inp2, weight, bias, M, C, flags, inp3)
     if (nv <= 2) B200_LN_CASE(2);
     else if (nv <= 4) B200_LN_CASE(4);
     else if (nv <= 6) B200_LN_CASE(6);       // C = 768
@@ -494,8 +501,45 @@ int launch_layernorm(b200_ctx* ctx, float* out, float* mean, float* rstd, const 
 
 int launch_fused_residual_layernorm(b200_ctx* ctx, float* res_out, float* ln_out, float* mean,
                                     float* rstd, const float* inp1, const float* inp2,
-                                    const float* weight, const float* bias, int M, int C, int flags) {
-    return launch_ln_any<true>(ctx, ln_out, res_out, mean, rstd, inp1, inp2, weight, bias, M, C, flags);
+                                    const float* weight, const float* bias, int M, int C, int flags, const float* inp3) {
+    return launch_ln_any<true>(ctx, ln_out, res_out, mean, rstd, inp1, inp2, weight, bias, M, C, flags, inp3);
+}
+
+// ---- hand-over between two GPUs whose kernels write into each other's memory ------------------
+// signal: one release store (system scope) of `value` into a word of the peer's memory, after
+// everything queued before it on this stream - including a GEMM whose epilogue stored tiles into
+// the peer's memory - has completed.  wait: spins, for a bounded time, until this GPU's own word
+// has reached `value`.  Both are plain launches (no programmatic early start): the kernels
+// around them in the stream are ordered by them.
+__global__ void peer_signal_kernel(unsigned int* peer_word, unsigned int value) {
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(peer_word), "r"(value) : "memory");
+}
+__global__ void peer_wait_kernel(const unsigned int* my_word, unsigned int value, int* status, unsigned long long limit_ns) {
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(my_word) : "memory");
+        if ((int)(v - value) >= 0) return;  // epochs only grow (compared modulo 2^32)
+        if (globaltimer_ns() - t0 > limit_ns) {
+            atomicCAS(status, 0, DEV_TIMEOUT_PEER);
+            return;
+        }
+        __nanosleep(200);
+    }
+}
+
+int launch_peer_signal(b200_ctx* ctx, unsigned int* peer_word, unsigned int value) {
+    peer_signal_kernel<<<1, 1, 0, ctx->stream>>>(peer_word, value);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+int launch_peer_wait(b200_ctx* ctx, const unsigned int* my_word, unsigned int value) {
+    peer_wait_kernel<<<1, 1, 0, ctx->stream>>>(my_word, value, ctx->d_status, kWaitLimitNs);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
 }
 
 int launch_residual(b200_ctx* ctx, float* out, const float* a, const float* b, size_t N) {

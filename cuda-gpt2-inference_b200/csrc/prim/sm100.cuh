@@ -17,6 +17,7 @@ enum : int {
     DEV_TIMEOUT_MMA = 102,        // MMA issuer gave up waiting for operands / accumulator
     DEV_TIMEOUT_EPILOGUE = 103,   // epilogue gave up waiting for an accumulator
     DEV_TIMEOUT_SOFTMAX = 104,    // attention softmax warps gave up waiting
+    DEV_TIMEOUT_PEER = 105,       // a hand-over word from the peer GPU did not arrive in time
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -147,6 +148,11 @@ __device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.b
 __device__ __forceinline__ void tma_store_wait_read_but_one() { asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_read_but_three() { asm volatile("cp.async.bulk.wait_group.read 3;" ::: "memory"); }
 __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// A tensor map that lives in global memory (not in the kernel's parameters) may be cached by the TMA
+// unit from an earlier use of the same address: the thread that is going to use it acquires it first.
+__device__ __forceinline__ void tma_acquire_global_desc(const CUtensorMap* map) {
+    asm volatile("fence.proxy.tensormap::generic.acquire.sys [%0], 128;" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
     asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(map)) : "memory");
 }

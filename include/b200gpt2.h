@@ -380,6 +380,21 @@ int b200_gpt2_set_allreduce(b200_gpt2* model, b200_allreduce_fn fn, void* user);
  * two B200s the chunked forms measured slower (GPT-2 XL, 8192 rows: 40.7 ms unchunked, 44.0 with
  * 2 chunks, 48.5 with 4), so the overlap is an option, not the default. */
 int b200_gpt2_set_tp_overlap(b200_gpt2* model, int chunks, int reserve_sms);
+
+/* Two-way tensor parallelism without all-reduces (tp_size == 2, B200_TF32 GEMMs, the two GPUs
+ * connected by NVLink, one process each).  Each projection GEMM stores the tiles of its partial sum
+ * a second time, straight into the other GPU's memory, while it computes; a word written behind
+ * the GEMM tells the peer that the sum is complete, and the fused residual + layernorm that follows
+ * adds the two partial sums itself - the same bits an all-reduce would have produced, on both
+ * ranks.  What is left of the exchange on the critical path is a bounded wait on that word.
+ *   b200_gpt2_tp_peer_export   allocates the receive buffers and writes three CUDA IPC memory
+ *                              handles (3 x 64 bytes) for the peer process
+ *   b200_gpt2_tp_peer_connect  takes the PEER's three handles and switches the hand-over on; the
+ *                              all-reduce callback is then no longer called
+ * Both ranks must run the same sequence of forwards: every projection waits (at most 2 s, then
+ * B200_ERR_TIMEOUT at the next sync_check) for its counterpart on the peer. */
+int b200_gpt2_tp_peer_export(b200_gpt2* model, unsigned char* handles /* [192] */);
+int b200_gpt2_tp_peer_connect(b200_gpt2* model, const unsigned char* peer_handles /* [192] */);
 size_t b200_gpt2_param_offsets_tp(const b200_gpt2_config* cfg, int tp_size, int tp_rank, size_t* offsets);
 int b200_gpt2_shard_params_host(const b200_gpt2_config* cfg, int tp_size, int tp_rank,
                                 const float* full_params, float* local_params);

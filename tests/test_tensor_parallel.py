@@ -132,13 +132,27 @@ if r == 0:
     err = np.abs(got - want).max()
     assert err < 2e-2, err
     print("TP_GPU_OK", err, model.read_profile() if False else "")
+# the same forward with the partial sums handed over through peer memory instead of all-reduces:
+# local + peer is the all-reduce's sum, bit for bit, on both ranks
+nccl_logits = logits.clone()
+model.connect_tp_peer()
+for _ in range(3):
+    logits = model.forward(d_tok, 2, 128); ctx.sync_check()
+    assert torch.equal(logits, nccl_logits), float((logits - nccl_logits).abs().max())
+# another shape (the hand-over's tensor maps follow the row count)
+l2 = model.forward(d_tok[:1, :64].contiguous(), 1, 64); ctx.sync_check()
+assert torch.equal(l2[0], nccl_logits[0, :64]) or float((l2[0] - nccl_logits[0, :64]).abs().max()) < 2e-3
+dist.barrier()
+if r == 0:
+    print("TP_PEER_OK")
 dist.barrier(); dist.destroy_process_group()
 """
 
 
 @pytest.mark.gpu
 def test_tp_forward_two_gpus(tmp_path):
-    """Two CUDA ranks, one NCCL all-reduce per block (NVLS off: a plain ring is all this needs)."""
+    """Two CUDA ranks, one NCCL all-reduce per block (NVLS off: a plain ring is all this needs); then the
+    same forward with the partial sums handed over through peer memory (b200_gpt2_tp_peer_*): identical bits."""
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
@@ -150,3 +164,4 @@ def test_tp_forward_two_gpus(tmp_path):
                          capture_output=True, text=True, timeout=600, env=env, cwd=ROOT)
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_GPU_OK" in out.stdout
+    assert "TP_PEER_OK" in out.stdout
