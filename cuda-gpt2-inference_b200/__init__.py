@@ -31,7 +31,7 @@ ACT_NONE, ACT_GELU = 0, 1
 EXPORTS = (
     "b200_ctx_create", "b200_ctx_destroy", "b200_ctx_set_stream", "b200_ctx_sync_check",
     "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
-    "b200_ctx_last_error", "b200_ctx_wait_timeout_probe",
+    "b200_ctx_last_error", "b200_ctx_wait_timeout_probe", "b200_ctx_peer_wait_probe",
     "b200_matmul_forward", "b200_matmul_forward_bf16", "b200_convert_bf16", "b200_matmul_forward_bf16x3", "b200_split_bf16",
     "b200_matmul_forward_fp8", "b200_quantize_e4m3", "b200_gpt2_tp_peer_export", "b200_gpt2_tp_peer_connect",
     "b200_gpt2_set_attention_mode", "b200_attention_forward", "b200_attention_forward_x3", "b200_attention_forward_fp16", "b200_split_fp16", "b200_layernorm_forward",
@@ -94,6 +94,7 @@ def lib() -> C.CDLL:
         l.b200_ctx_set_stream.argtypes = [vp, vp]
         l.b200_ctx_sync_check.argtypes = [vp]
         l.b200_ctx_wait_timeout_probe.argtypes = [vp, i]
+        l.b200_ctx_peer_wait_probe.argtypes = [vp, i]
         l.b200_ctx_launch_count.argtypes = [vp]
         l.b200_ctx_launch_count.restype = C.c_uint64
         l.b200_ctx_reset_launch_count.argtypes = [vp]

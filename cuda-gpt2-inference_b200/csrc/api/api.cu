@@ -184,6 +184,13 @@ int b200_ctx_wait_timeout_probe(b200_ctx* ctx, int limit_ms) {
     return b200::launch_wait_timeout_probe(ctx, (unsigned long long)limit_ms * 1000000ull);
 }
 
+int b200_ctx_peer_wait_probe(b200_ctx* ctx, int limit_ms) {
+    if (!ctx) return B200_ERR_NULL;
+    if (limit_ms < 1 || limit_ms > 2000) return B200_ERR_SHAPE;
+    // word 40 of the status area is never written: the wait for it to reach 1 runs out
+    return b200::launch_peer_wait(ctx, reinterpret_cast<const unsigned int*>(ctx->d_status + 40), 1u, (unsigned long long)limit_ms * 1000000ull);
+}
+
 // debugging aid for kernel experiments: device address of the status words
 void* b200_ctx_debug_status(b200_ctx* ctx) { return ctx ? ctx->d_status : nullptr; }
 

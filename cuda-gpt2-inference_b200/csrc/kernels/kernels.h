@@ -19,7 +19,7 @@ int launch_fused_residual_layernorm(b200_ctx* ctx, float* res_out, float* ln_out
                                     const float* weight, const float* bias, int M, int C, int flags, const float* inp3 = nullptr);  // inp3: x = inp1 + (inp2 + inp3)
 // hand-over words between two GPUs (peer-mapped memory): see rowwise.cu
 int launch_peer_signal(b200_ctx* ctx, unsigned int* peer_word, unsigned int value);
-int launch_peer_wait(b200_ctx* ctx, const unsigned int* my_word, unsigned int value);
+int launch_peer_wait(b200_ctx* ctx, const unsigned int* my_word, unsigned int value, unsigned long long limit_ns = 0);  // 0: the 2 s of every device-side wait
 int launch_residual(b200_ctx* ctx, float* out, const float* a, const float* b, size_t N);
 int launch_gelu(b200_ctx* ctx, float* out, const float* inp, size_t N);
 int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,

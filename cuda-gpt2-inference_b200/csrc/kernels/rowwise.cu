@@ -535,8 +535,8 @@ int launch_peer_signal(b200_ctx* ctx, unsigned int* peer_word, unsigned int valu
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;
 }
-int launch_peer_wait(b200_ctx* ctx, const unsigned int* my_word, unsigned int value) {
-    peer_wait_kernel<<<1, 1, 0, ctx->stream>>>(my_word, value, ctx->d_status, kWaitLimitNs);
+int launch_peer_wait(b200_ctx* ctx, const unsigned int* my_word, unsigned int value, unsigned long long limit_ns) {
+    peer_wait_kernel<<<1, 1, 0, ctx->stream>>>(my_word, value, ctx->d_status, limit_ns ? limit_ns : kWaitLimitNs);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
     return B200_OK;

@@ -76,6 +76,9 @@ int b200_ctx_sync_check(b200_ctx* ctx);
  * wait runs out.  The kernel returns normally; the next b200_ctx_sync_check reports
  * B200_ERR_TIMEOUT once and the context stays usable. */
 int b200_ctx_wait_timeout_probe(b200_ctx* ctx, int limit_ms);
+/* The same for the wait on a hand-over word that another GPU writes (b200_gpt2_tp_peer_*): the kernel
+ * waits limit_ms for a word that nothing sets, gives up and reports device status 105. */
+int b200_ctx_peer_wait_probe(b200_ctx* ctx, int limit_ms);
 /* Number of kernels this context has launched since creation (or the last reset). */
 uint64_t b200_ctx_launch_count(const b200_ctx* ctx);
 void b200_ctx_reset_launch_count(b200_ctx* ctx);

@@ -289,6 +289,13 @@ def test_device_wait_that_runs_out_is_reported_and_context_survives(ctx, dev, or
     ctx.residual_forward(out, dev.to(a), dev.to(b), 1024)
     assert np.array_equal(dev.back(out), a + b)
     assert lib.b200_ctx_wait_timeout_probe(ctx._h, 0) == 2  # limit out of range
+    # the wait on a hand-over word that a peer GPU would write (tensor parallelism over peer memory)
+    t0 = time.time()
+    assert lib.b200_ctx_peer_wait_probe(ctx._h, 100) == 0
+    assert ctx.sync_status() == 6
+    assert 0.05 < time.time() - t0 < 5.0
+    assert b"105" in lib.b200_ctx_last_error(ctx._h)
+    assert ctx.sync_status() == 0
 
 
 # ------------------------------------------------------------------ bf16 operand GEMM
