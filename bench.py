@@ -830,10 +830,22 @@ def _xl_and_multi_gpu(pkg, torch, dist, ctx, stream, world, rank, barrier, max_o
                     "exposed_allreduce_ms": max(0.0, ms_tp - (ser_ms - ar_ms)),
                     "exposed_allreduce_share": max(0.0, ms_tp - (ser_ms - ar_ms)) / ms_tp if ms_tp else None,
                     "allreduce_launches_per_step": prof["allreduce"][1] / 2,
+                    "dtype": pkg.DEFAULT_MODE_NAME,
                     "note": "GPT-2 XL, one tensor-parallel group over all ranks (heads / MLP / vocabulary split), one NCCL all-reduce "
                             "per attention and MLP block on the compute stream (row-chunked overlap on a communication stream is an "
                             "option that measured slower); the serialised figures come from a pass with one event pair per launch; "
                             "exposed = ms_per_step - (serialised - all-reduce)"}
+    # single-pass TF32 arithmetic on the same sharded model (what this measurement ran in before the
+    # split-bf16 arithmetic was wired for sharded weights)
+    tpm.set_options(**pkg.MODES["tf32"])
+    for _ in range(2):
+        tpm.forward(tok8, 8, T)
+    ctx.sync_check()
+    ms_tf32 = _time_steps(torch, tpm, ctx, stream, tok8, 8, T, 3, 1, barrier, max_over_ranks)
+    out["tp_xl"]["tf32"] = {"value": 8 * T / (ms_tf32 * 1e-3), "unit": UNIT, "ms_per_step": ms_tf32}
+    tpm.set_options(**pkg.MODES[pkg.DEFAULT_MODE_NAME])
+    tpm.forward(tok8, 8, T)
+    ctx.sync_check()
     if world == 2:
         # the same model with the partial sums handed over through peer memory instead of all-reduces
         try:
@@ -849,8 +861,15 @@ def _xl_and_multi_gpu(pkg, torch, dist, ctx, stream, world, rank, barrier, max_o
             tpm.set_profile(False)
             tot = sum(v[0] for v in prof.values())
             ser_ms, ar_ms = tot / 2, prof["allreduce"][0] / 2
+            tpm.set_options(**pkg.MODES["tf32"])
+            for _ in range(2):
+                tpm.forward(tok8, 8, T)
+            ctx.sync_check()
+            ms_peer_tf32 = _time_steps(torch, tpm, ctx, stream, tok8, 8, T, 3, 1, barrier, max_over_ranks)
+            tpm.set_options(**pkg.MODES[pkg.DEFAULT_MODE_NAME])
             out["tp_xl"]["peer_handover"] = {
                 "value": 8 * T / (ms_peer * 1e-3), "unit": UNIT, "ms_per_step": ms_peer, "logits_equal_to_allreduce_run": "bitwise" if same else "MISMATCH",
+                "tf32_ms_per_step": ms_peer_tf32,
                 "ms_per_step_serialised": ser_ms, "handover_ms_per_step": ar_ms,
                 "exposed_handover_ms": max(0.0, ms_peer - (ser_ms - ar_ms)),
                 "exposed_handover_share": max(0.0, ms_peer - (ser_ms - ar_ms)) / ms_peer if ms_peer else None,

@@ -507,7 +507,7 @@ class GPT2:
 
     def set_options(self, round_operands=1, gemm_mode=None, lmhead_mode=None, use_graph=0, attention_mode=-1):
         """gemm_mode / lmhead_mode default to the library's default arithmetic (DEFAULT_MODE_NAME)."""
-        d = MODES[DEFAULT_MODE_NAME if self.tp_size == 1 else "tf32"]
+        d = MODES[DEFAULT_MODE_NAME]
         gemm_mode = d["gemm_mode"] if gemm_mode is None else gemm_mode
         lmhead_mode = d["lmhead_mode"] if lmhead_mode is None else lmhead_mode
         self.ctx.check(lib().b200_gpt2_set_attention_mode(self._h, int(attention_mode)), "set_attention_mode")

@@ -250,7 +250,7 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
     const bool prof = m->profile;
     const int tpc = (m->tp_size > 1 && g_tf32 && m->gemm_mode == B200_TF32) ? tp_chunks(m, M, prof) : 1;
     // two-way tensor parallelism over peer memory instead of all-reduces (see the model's peer_* fields)
-    const bool peer = m->peer_on && m->tp_size == 2 && g_tf32 && m->gemm_mode == B200_TF32 && tpc == 1;
+    const bool peer = m->peer_on && m->tp_size == 2 && ((g_tf32 && m->gemm_mode == B200_TF32) || hx) && tpc == 1;
     if (peer) {
         // (a tensor-parallel forward is never replayed from a graph, so the epochs below are live values)
         if (m->peer_maps_rows != M) {
@@ -315,7 +315,10 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         // fused residual + layernorm kernel would do), and a plain layernorm follows: 50 MB less
         // traffic per block than writing the branch and reading it back.
         float* proj_out = accum ? m->residual : m->branch;
-        if (hx) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, atty_h, PH + o_apw, PL + o_apw, apb, M, A, C, accum));
+        if (hx) {
+            if (peer) { peer_e = ++m->peer_epoch; ctx->next_gemm_out2 = m->peer_maps + (peer_e & 1); }
+            STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, atty_h, PH + o_apw, PL + o_apw, apb, M, A, C, accum));
+        }
         else if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, atty_h, PH + o_apw, apb, M, A, C, accum));
         else if (tpc > 1) STEP(B200_PROF_GEMM_ATTPROJ, tp_projection_overlapped(m, proj_out, m->atty, W + o_apw, apb, M, A, C, tpc));
         else {
@@ -336,6 +339,7 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         }
         if (hx) {
             STEP(B200_PROF_GEMM_FC, launch_gemm_bf16x3(ctx, nullptr, fch_h, ln_h, PH + o_fcw, PL + o_fcw, fcb, M, C, F, GEMM_GELU));
+            if (peer) { peer_e = ++m->peer_epoch; ctx->next_gemm_out2 = m->peer_maps + (peer_e & 1); }
             STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, fch_h, PH + o_fpw, PL + o_fpw, fpb, M, F, C, accum));
         } else if (hb) {
             STEP(B200_PROF_GEMM_FC, launch_gemm_bf16(ctx, nullptr, fch_h, ln_h, PH + o_fcw, fcb, M, C, F, GEMM_GELU));
@@ -558,7 +562,6 @@ int b200_gpt2_create_tp(b200_gpt2** out, b200_ctx* ctx, const b200_gpt2_config* 
     if (!m) return B200_ERR_CUDA;
     m->ctx = ctx; m->cfg = *cfg; m->max_B = max_B; m->max_T = max_T;
     if (!set_tp_dims(m, tp_size, tp_rank)) { delete m; return B200_ERR_SHAPE; }
-    if (tp_size > 1) m->gemm_mode = m->lmhead_mode = B200_TF32;  // the bf16 modes are not wired for sharded weights
     const size_t M = (size_t)max_B * max_T, C = cfg->channels, Vp = m->vp_local;
     const size_t A = m->attn_c, F = m->mlp_c;
     cudaError_t e = cudaSetDevice(ctx->device);
@@ -680,8 +683,8 @@ int b200_gpt2_load_params_file(b200_gpt2* m, const char* path, size_t header_byt
 int b200_gpt2_set_options(b200_gpt2* m, int round_operands, int gemm_mode, int lmhead_mode, int use_graph) {
     if (!m) return B200_ERR_NULL;
     if (gemm_mode < B200_TF32 || gemm_mode > B200_BF16X3 || lmhead_mode < B200_TF32 || lmhead_mode > B200_BF16X3) return B200_ERR_SHAPE;
-    // the bf16 modes are not wired for tensor-parallel models
-    if ((gemm_mode >= B200_BF16 || lmhead_mode >= B200_BF16) && m->tp_size > 1) return B200_ERR_STATE;
+    // tensor-parallel models: single-pass TF32 or the split-bf16 arithmetic (the plain bf16 mode is not wired for them)
+    if ((gemm_mode == B200_BF16 || lmhead_mode == B200_BF16) && m->tp_size > 1) return B200_ERR_STATE;
     if (m->round_operands != round_operands || m->gemm_mode != gemm_mode || m->lmhead_mode != lmhead_mode) {
         for (auto& g : m->graphs) cudaGraphExecDestroy(g.second);
         m->graphs.clear();

@@ -255,8 +255,8 @@ int b200_gpt2_load_params_host(b200_gpt2* model, const float* host_params, size_
  * cannot be opened or read is B200_ERR_STATE).  The copy goes through pinned staging buffers in
  * 32 MB pieces.  Not for tensor-parallel models, whose parameters are stored sharded. */
 int b200_gpt2_load_params_file(b200_gpt2* model, const char* path, size_t header_bytes);
-/* Options (defaults: round_operands 1, both modes B200_BF16X3 - B200_TF32 on a tensor-parallel
- * model -, use_graph 0).
+/* Options (defaults: round_operands 1, both modes B200_BF16X3, use_graph 0; a tensor-parallel model
+ * takes B200_BF16X3, B200_TF32 and B200_TF32X3, not B200_BF16).
  * round_operands != 0 makes every producer whose output feeds only a single-pass TF32 GEMM store
  * TF32-round-to-nearest values and makes those GEMMs read a rounded copy of the weight
  * matrices (made on the next forward; the parameters themselves are never modified, so the
@@ -384,7 +384,7 @@ int b200_gpt2_set_allreduce(b200_gpt2* model, b200_allreduce_fn fn, void* user);
  * 2 chunks, 48.5 with 4), so the overlap is an option, not the default. */
 int b200_gpt2_set_tp_overlap(b200_gpt2* model, int chunks, int reserve_sms);
 
-/* Two-way tensor parallelism without all-reduces (tp_size == 2, B200_TF32 GEMMs, the two GPUs
+/* Two-way tensor parallelism without all-reduces (tp_size == 2, B200_BF16X3 or B200_TF32 GEMMs, the two GPUs
  * connected by NVLink, one process each).  Each projection GEMM stores the tiles of its partial sum
  * a second time, straight into the other GPU's memory, while it computes; a word written behind
  * the GEMM tells the peer that the sum is complete, and the fused residual + layernorm that follows

@@ -145,6 +145,18 @@ assert torch.equal(l2[0], nccl_logits[0, :64]) or float((l2[0] - nccl_logits[0, 
 dist.barrier()
 if r == 0:
     print("TP_PEER_OK")
+# the default arithmetic of the unsharded model (split-bf16 GEMMs, fp16 attention) on the sharded one
+model.set_options(**pkg.MODES["bf16x3"])
+lx = model.forward(d_tok, 2, 128); ctx.sync_check()
+parts = [torch.empty_like(lx) for _ in range(n)]
+dist.all_gather(parts, lx.contiguous())
+if r == 0:
+    got = torch.cat(parts, dim=-1).cpu().numpy()
+    want = orc.gpt2_forward(full, ocfg, tokens)
+    err = np.abs(got - want).max()
+    assert err < 2e-3, err
+    assert np.sqrt(np.mean((got - want) ** 2)) < 1e-4
+    print("TP_X3_OK", err)
 dist.barrier(); dist.destroy_process_group()
 """
 
@@ -165,3 +177,4 @@ def test_tp_forward_two_gpus(tmp_path):
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_GPU_OK" in out.stdout
     assert "TP_PEER_OK" in out.stdout
+    assert "TP_X3_OK" in out.stdout
