@@ -293,7 +293,13 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         const bool att_split = hx && !m->keep_kv && (m->att_mode < 0 || m->att_mode == B200_BF16X3);
         const int qkv_flags = (!att_x3 && (m->round_operands || m->gemm_mode != B200_TF32)) ? GEMM_ROUND_OUT_TF32 : 0;
         uint16_t* qkv_h = reinterpret_cast<uint16_t*>(m->qkv);
-        if (att_split) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16x3(ctx, nullptr, qkv_h, ln_h, PH + o_qkvw, PL + o_qkvw, qkvb, M, C, 3 * A, GEMM_PLANES_FP16));
+#ifdef B200_QKV_FULL_LO
+        const int qkv_lo_col0 = 0;
+#else
+        const int qkv_lo_col0 = (2 * A) % 64 == 0 ? 2 * A : 0;  // the attention reads only v's second plane
+#endif
+        if (att_split) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16x3(ctx, nullptr, qkv_h, ln_h, PH + o_qkvw, PL + o_qkvw, qkvb, M, C, 3 * A, GEMM_PLANES_FP16,
+                                                                    nullptr, 0, 0, nullptr, qkv_lo_col0));
         else if (hx) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16x3(ctx, m->qkv, nullptr, ln_h, PH + o_qkvw, PL + o_qkvw, qkvb, M, C, 3 * A, qkv_flags));
         else if (hb) STEP(B200_PROF_GEMM_QKV, launch_gemm_bf16(ctx, m->qkv, nullptr, ln_h, PH + o_qkvw, qkvb, M, C, 3 * A, qkv_flags));
         else STEP(B200_PROF_GEMM_QKV, launch_gemm_tf32(ctx, m->qkv, m->ln_out, W + o_qkvw, qkvb, nullptr, M, C, 3 * A, qkv_flags, m->gemm_mode));

@@ -50,6 +50,9 @@ struct GemmArgs {
     // not null: a tensor map in global memory (same shape and 32 x 32 box as the output's) through which every
     // tile of a plain-store fp32 epilogue is stored a second time - into a peer GPU's memory (tensor parallel)
     const CUtensorMap* tmap_out2 = nullptr;
+    // two-plane output: the plane of the dropped parts is only written for columns >= lo_col0 (the fp16 attention
+    // reads q and k from their hi planes alone: their lo planes need neither be formed nor stored)
+    int lo_col0 = 0;
 };
 
 // Arg-max keys: the value as an order-preserving 32-bit integer in the high half, the inverted
@@ -124,6 +127,7 @@ __device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args
             __syncwarp();
         }
         uint32_t lo[32];  // the dropped parts, packed two to a register (planes only)
+        const bool want_lo = planes && cbase >= args.lo_col0;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
 #pragma unroll
@@ -145,16 +149,18 @@ __device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args
                     for (int i = 0; i < 4; ++i) {
                         const float x0 = fminf(fmaxf(v[2 * i], -65504.f), 65504.f), x1 = fminf(fmaxf(v[2 * i + 1], -65504.f), 65504.f);
                         const __half2 hh = __floats2half2_rn(x0, x1);
-                        const __half2 ll = __floats2half2_rn(x0 - __low2float(hh), x1 - __high2float(hh));
                         pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
-                        lo[h * 16 + j * 4 + i] = *reinterpret_cast<const uint32_t*>(&ll);
+                        if (want_lo) {
+                            const __half2 ll = __floats2half2_rn(x0 - __low2float(hh), x1 - __high2float(hh));
+                            lo[h * 16 + j * 4 + i] = *reinterpret_cast<const uint32_t*>(&ll);
+                        }
                     }
                 } else {
 #pragma unroll
                     for (int i = 0; i < 4; ++i) {
                         const __nv_bfloat162 hh = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
                         pk[i] = *reinterpret_cast<const uint32_t*>(&hh);
-                        if (planes) {
+                        if (want_lo) {
                             const __nv_bfloat162 ll = __floats2bfloat162_rn(v[2 * i] - __low2float(hh), v[2 * i + 1] - __high2float(hh));
                             lo[h * 16 + j * 4 + i] = *reinterpret_cast<const uint32_t*>(&ll);
                         }
@@ -171,7 +177,7 @@ __device__ __forceinline__ void gemm_drain_accumulator_bf16(const GemmArgs& args
             tma_store_2d(tmap_out, cbase, row0, sth);
             tma_store_commit();
         }
-        if (planes) {
+        if (want_lo) {
             if (bi + 1 >= nbuf) {  // with one buffer: the store just issued has to have read it
                 if (lane == 0) tma_store_wait_read();
                 __syncwarp();
@@ -356,6 +362,6 @@ int preload_gemm_pair_kernels(b200_ctx* ctx);  // the PAIR_TF32 kernel: loaded n
 int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp_lo, const void* weight, const void* weight_lo,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys, int argmax_cols, int kind, uint16_t* out_h = nullptr,
-                     int out_planes = 0, int store_period = 0, const GemmRowStats* stats = nullptr, float alpha = 1.0f);
+                     int out_planes = 0, int store_period = 0, const GemmRowStats* stats = nullptr, float alpha = 1.0f, int lo_col0 = 0);
 
 }  // namespace b200

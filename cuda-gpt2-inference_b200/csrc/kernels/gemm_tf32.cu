@@ -419,7 +419,7 @@ int launch_gemm_tf32(b200_ctx* ctx, float* out, const float* inp, const float* w
 
 int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const uint16_t* inp, const uint16_t* weight_hi,
                        const uint16_t* weight_lo, const float* bias, int M, int K, int N, int flags,
-                       unsigned long long* argmax_keys, int argmax_cols, int store_period, const GemmRowStats* stats) {
+                       unsigned long long* argmax_keys, int argmax_cols, int store_period, const GemmRowStats* stats, int lo_col0) {
     if (K % 8 || N % 8) { ctx->last_error = "bf16x3 GEMM: K and N must be multiples of 8"; return B200_ERR_SHAPE; }
     if (out_planes && (M % 32 || (flags & GEMM_ACCUM_OUT))) { ctx->last_error = "bf16x3 GEMM: a split output needs M % 32 == 0 and no accumulation"; return B200_ERR_SHAPE; }
     if (store_period && (store_period % 32 || !argmax_keys)) { ctx->last_error = "store_period: multiple of 32, with the fused arg-max only"; return B200_ERR_STATE; }
@@ -427,7 +427,7 @@ int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const ui
     if (!out_planes && !out) return B200_ERR_NULL;
     return launch_gemm_pair(ctx, out, inp, inp + (size_t)M * K, weight_hi, weight_lo, bias, nullptr, M, K, N,
                             flags & (GEMM_GELU | GEMM_ROUND_OUT_TF32 | GEMM_ACCUM_OUT), argmax_keys, argmax_cols, PAIR_BF16X3, out_planes,
-                            out_planes ? ((flags & GEMM_PLANES_FP16) ? 2 : 1) : 0, store_period, stats);
+                            out_planes ? ((flags & GEMM_PLANES_FP16) ? 2 : 1) : 0, store_period, stats, 1.0f, lo_col0);
 }
 
 int launch_gemm_bf16(b200_ctx* ctx, float* out, uint16_t* out_h, const uint16_t* inp, const uint16_t* weight,

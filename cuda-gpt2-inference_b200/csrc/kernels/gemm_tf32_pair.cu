@@ -377,13 +377,14 @@ int preload_gemm_pair_kernels(b200_ctx* ctx) {
 int launch_gemm_pair(b200_ctx* ctx, float* out, const void* inp, const void* inp_lo, const void* weight, const void* weight_lo,
                      const float* bias, const float* residual, int M, int K, int N, int flags,
                      unsigned long long* argmax_keys, int argmax_cols, int kind, uint16_t* out_h, int out_planes,
-                     int store_period, const GemmRowStats* stats, float alpha) {
+                     int store_period, const GemmRowStats* stats, float alpha, int lo_col0) {
     const int num_pairs_max = ctx->num_sms / 2;
     const bool half = kind == PAIR_BF16 || kind == PAIR_BF16X3;
     GemmArgs a;
     a.out = out; a.out_h = out_h; a.bias = bias; a.residual = residual;
     a.M = M; a.N = N; a.K = K;
     a.alpha = alpha;
+    a.lo_col0 = lo_col0;
     a.tmap_out2 = static_cast<const CUtensorMap*>(ctx->next_gemm_out2);
     ctx->next_gemm_out2 = nullptr;
     if (a.tmap_out2 && (out_h || residual || (flags & GEMM_ACCUM_OUT) || store_period)) {

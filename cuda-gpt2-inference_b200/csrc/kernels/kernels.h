@@ -74,7 +74,7 @@ int launch_gemm_fp8(b200_ctx* ctx, float* out, const uint8_t* inp, const uint8_t
 int launch_gemm_bf16x3(b200_ctx* ctx, float* out, uint16_t* out_planes, const uint16_t* inp, const uint16_t* weight_hi,
                        const uint16_t* weight_lo, const float* bias, int M, int K, int N, int flags,
                        unsigned long long* argmax_keys = nullptr, int argmax_cols = 0, int store_period = 0,
-                       const GemmRowStats* stats = nullptr);
+                       const GemmRowStats* stats = nullptr, int lo_col0 = 0);  // lo_col0: with out_planes, columns below it get no plane of dropped parts
 // Extras of the fused row reduction of a GEMM with arg-max keys (CTA-pair kernel only):
 //   inv_temp > 0: the keys hold, instead of the arg-max, the column that maximises
 //     sample_score(value, inv_temp, seed, stream0 + row, column) - a draw from softmax(row / temperature);
