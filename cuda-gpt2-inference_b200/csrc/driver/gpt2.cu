@@ -530,6 +530,7 @@ int b200_gpt2_tp_peer_export(b200_gpt2* m, unsigned char* handles) {
 int b200_gpt2_tp_peer_connect(b200_gpt2* m, const unsigned char* peer_handles) {
     if (!m || !peer_handles) return B200_ERR_NULL;
     if (m->tp_size != 2 || !m->peer_word) { m->ctx->last_error = "b200_gpt2_tp_peer_export comes first"; return B200_ERR_STATE; }
+    if (m->peer_on) { m->ctx->last_error = "the model is connected to its peer already"; return B200_ERR_STATE; }
     b200_ctx* ctx = m->ctx;
     b200_device_guard guard(ctx);
     cudaIpcMemHandle_t h;

@@ -29,7 +29,7 @@
 // from tensor memory into registers, reduced to the block maximum, turned into P and written
 // back as fp16 pairs.  O stays in tensor memory and accumulates over the blocks (the UMMAs add
 // to it); the reference maximum of a row is only moved - and O and the row sum rescaled - when
-// a block raises it by more than 2^8, so P never exceeds 256 (exact in fp16's range) and the
+// a block raises it by more than 2^8, so P never exceeds 256 (far inside fp16's range) and the
 // rescale, which needs a round trip of O through registers, is rare after the first blocks.
 //
 // Persistent kernel, 11 warps: warp 0 work fetch + TMA producer (Q pair double buffered, K and

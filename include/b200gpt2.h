@@ -395,7 +395,9 @@ int b200_gpt2_set_tp_overlap(b200_gpt2* model, int chunks, int reserve_sms);
  *   b200_gpt2_tp_peer_connect  takes the PEER's three handles and switches the hand-over on; the
  *                              all-reduce callback is then no longer called
  * Both ranks must run the same sequence of forwards: every projection waits (at most 2 s, then
- * B200_ERR_TIMEOUT at the next sync_check) for its counterpart on the peer. */
+ * B200_ERR_TIMEOUT at the next sync_check) for its counterpart on the peer.  The two ranks count their
+ * projections; after a time-out the counts may disagree, and the pair of models has to be created
+ * and connected anew.  connect is called once per model. */
 int b200_gpt2_tp_peer_export(b200_gpt2* model, unsigned char* handles /* [192] */);
 int b200_gpt2_tp_peer_connect(b200_gpt2* model, const unsigned char* peer_handles /* [192] */);
 size_t b200_gpt2_param_offsets_tp(const b200_gpt2_config* cfg, int tp_size, int tp_rank, size_t* offsets);
