@@ -25,8 +25,8 @@ namespace b200 {
 namespace {
 
 constexpr int kSkinnyThreads = 256;
-constexpr int kSkinnyKC = 1024;  // floats of K whose weights a warp requests at once (8 float4 per lane and row)
-constexpr int kSkinnySteps = kSkinnyKC / 128;  // a warp covers 128 floats of a row per step
+// STEPS (template): a warp covers 128 floats of a row per step and requests STEPS steps = STEPS * 128
+// floats of K of its ROWS rows at once (8 steps = 8 float4 per lane and row; 6 for three rows per warp)
 
 // Optional prologue (ln_w != nullptr): the input rows are first formed as
 //   r = resid_in + branch (branch may be null),  x = layernorm(r) * ln_w + ln_b
@@ -51,9 +51,10 @@ struct SkinnyArgs {
 // NV = float4 per lane that hold a row in the layernorm prologue (0: no prologue compiled in).
 // (Splitting K between the warps of a row group, to put narrow outputs on more SMs, was measured
 // and is slower: more batches per CTA means more weight round trips one after the other.)
-template <int NB, int ROWS, int NV>
+template <int NB, int ROWS, int NV, int STEPS>
 __global__ void __launch_bounds__(kSkinnyThreads)
 skinny_gemm_kernel(const SkinnyArgs a) {
+    constexpr int kSkinnySteps = STEPS, kSkinnyKC = STEPS * 128;
     extern __shared__ float4 xs4[];  // [NB][K / 4]: the input rows, staged once
     const int B = a.B, N = a.N, K = a.K, K4 = a.K >> 2;
     const float* __restrict__ W = a.W;
@@ -457,7 +458,12 @@ int launch_skinny_gemm(b200_ctx* ctx, float* out, const float* x, const float* W
     a.out = out; a.x = x; a.W = W; a.bias = bias; a.branch = branch; a.ln_w = ln_w; a.ln_b = ln_b; a.resid_out = resid_out;
     a.B = B; a.N = N; a.K = K; a.gelu = gelu;
     a.k_splits = k_splits; a.kslice = kslice; a.branch_parts = branch_parts;
-    constexpr int rows = 2;  // per warp
+    // rows per warp: two, i.e. 16 output rows per CTA and batch; three (with a shorter K chunk, for the
+    // registers) where that turns one and a bit rounds of batches into a single wave - the GELU GEMM
+    // of the 124M model: 192 batches of 16 rows on 148 SMs, 128 batches of 24
+    int rows = 2;
+    static const int rows3_off = [] { const char* e = getenv("B200_DECODE_ROWS3"); return e && e[0] == '0'; }();  // tuning hook
+    if (!rows3_off && k_splits == 1 && K <= 768 && ((N + 1) / 2 + 7) / 8 > ctx->num_sms && ((N + 2) / 3 + 7) / 8 <= ctx->num_sms) rows = 3;
     const int groups = (N + rows - 1) / rows;
     const int batches = (groups + 7) / 8;
     if (k_splits > 1 && batches * k_splits > ctx->num_sms) return B200_ERR_SHAPE;  // the slices of a unit run side by side
@@ -466,17 +472,20 @@ int launch_skinny_gemm(b200_ctx* ctx, float* out, const float* x, const float* W
     const int nv = !ln_w ? 0 : (K <= 768 ? 6 : 13);
     const size_t smem = x_bytes + (ln_w ? (size_t)2 * K * 4 : 0);
     cudaError_t le = cudaSuccess;
-#define B200_SKINNY(NB, NV)                                                                                     \
+#define B200_SKINNY(NB, ROWS_, NV, STEPS_)                                                                          \
     do {                                                                                                            \
         static bool attr_set[64] = {};                                                                              \
         if (!attr_set[ctx->device & 63]) {                                                                          \
-            B200_CUDA(ctx, cudaFuncSetAttribute(skinny_gemm_kernel<NB, rows, NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
+            B200_CUDA(ctx, cudaFuncSetAttribute(skinny_gemm_kernel<NB, ROWS_, NV, STEPS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024)); \
             attr_set[ctx->device & 63] = true;                                                                      \
         }                                                                                                           \
-        le = launch_pdl(ctx, skinny_gemm_kernel<NB, rows, NV>, dim3(grid), dim3(kSkinnyThreads), smem, a);      \
+        le = launch_pdl(ctx, skinny_gemm_kernel<NB, ROWS_, NV, STEPS_>, dim3(grid), dim3(kSkinnyThreads), smem, a); \
     } while (0)
-    if (nb == 8) { if (nv == 0) B200_SKINNY(8, 0); else if (nv == 6) B200_SKINNY(8, 6); else B200_SKINNY(8, 13); }
-    else { if (nv == 0) B200_SKINNY(16, 0); else if (nv == 6) B200_SKINNY(16, 6); else B200_SKINNY(16, 13); }
+    if (rows == 3) {
+        if (nb == 8) { if (nv == 0) B200_SKINNY(8, 3, 0, 6); else B200_SKINNY(8, 3, 6, 6); }
+        else { if (nv == 0) B200_SKINNY(16, 3, 0, 6); else B200_SKINNY(16, 3, 6, 6); }
+    } else if (nb == 8) { if (nv == 0) B200_SKINNY(8, 2, 0, 8); else if (nv == 6) B200_SKINNY(8, 2, 6, 8); else B200_SKINNY(8, 2, 13, 8); }
+    else { if (nv == 0) B200_SKINNY(16, 2, 0, 8); else if (nv == 6) B200_SKINNY(16, 2, 6, 8); else B200_SKINNY(16, 2, 13, 8); }
 #undef B200_SKINNY
     ctx->launches++;
     B200_CUDA(ctx, le);
