@@ -33,7 +33,7 @@ EXPORTS = (
     "b200_ctx_launch_count", "b200_ctx_reset_launch_count", "b200_status_string",
     "b200_ctx_last_error", "b200_ctx_wait_timeout_probe", "b200_ctx_peer_wait_probe",
     "b200_matmul_forward", "b200_matmul_forward_bf16", "b200_convert_bf16", "b200_matmul_forward_bf16x3", "b200_split_bf16",
-    "b200_matmul_forward_fp8", "b200_quantize_e4m3", "b200_gpt2_tp_peer_export", "b200_gpt2_tp_peer_connect",
+    "b200_matmul_forward_fp8", "b200_quantize_e4m3", "b200_gpt2_tp_peer_export", "b200_gpt2_tp_peer_connect", "b200_gpt2_tp_peer_enable",
     "b200_gpt2_set_attention_mode", "b200_attention_forward", "b200_attention_forward_x3", "b200_attention_forward_fp16", "b200_split_fp16", "b200_layernorm_forward",
     "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
     "b200_encoder_forward",
@@ -112,6 +112,7 @@ def lib() -> C.CDLL:
         l.b200_quantize_e4m3.argtypes = [vp, vp, vp, sz, C.c_float]
         l.b200_gpt2_tp_peer_export.argtypes = [vp, vp]
         l.b200_gpt2_tp_peer_connect.argtypes = [vp, vp]
+        l.b200_gpt2_tp_peer_enable.argtypes = [vp, i]
         l.b200_gpt2_set_attention_mode.argtypes = [vp, i]
         l.b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_attention_forward_x3.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
@@ -473,21 +474,36 @@ class GPT2:
     def connect_tp_peer(self, group=None):
         """Two-way tensor parallelism over peer memory instead of all-reduces: exchanges the CUDA IPC
         handles of the receive buffers with the other rank of the (two-rank) group through
-        torch.distributed and switches the hand-over on.  Collective: both ranks call it."""
+        torch.distributed and switches the hand-over on.  Collective: both ranks call it, and either
+        both end up connected or both raise."""
         import torch
         import torch.distributed as dist
-        mine = (C.c_ubyte * 192)()
-        self.ctx.check(lib().b200_gpt2_tp_peer_export(self._h, mine), "tp_peer_export")
-        world = dist.get_world_size(group)
-        if world != 2:
+        if dist.get_world_size(group) != 2:
             raise B200Error("connect_tp_peer needs a group of two ranks")
-        t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device=f"cuda:{self.ctx.device}")
+        dev = f"cuda:{self.ctx.device}"
+
+        def both(ok: bool) -> bool:  # the step succeeded on both ranks
+            t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+            return bool(t.item())
+
+        mine = (C.c_ubyte * 192)()
+        st = lib().b200_gpt2_tp_peer_export(self._h, mine)
+        if not both(st == 0):
+            raise B200Error(f"tp_peer_export failed on a rank (here: {st}, {lib().b200_ctx_last_error(self.ctx._h).decode()})")
+        t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device=dev)
         parts = [torch.empty_like(t) for _ in range(2)]
         dist.all_gather(parts, t, group=group)
         other = parts[1 - dist.get_rank(group)].cpu().numpy().tobytes()
         theirs = (C.c_ubyte * 192).from_buffer_copy(other)
-        self.ctx.check(lib().b200_gpt2_tp_peer_connect(self._h, theirs), "tp_peer_connect")
-        dist.barrier(group=group)  # both sides are mapped before either starts a forward
+        st = lib().b200_gpt2_tp_peer_connect(self._h, theirs)
+        if not both(st == 0):  # (also the barrier: both sides are mapped before either starts a forward)
+            if st == 0:
+                lib().b200_gpt2_tp_peer_enable(self._h, 0)
+            raise B200Error(f"tp_peer_connect failed on a rank (here: {st}, {lib().b200_ctx_last_error(self.ctx._h).decode()})")
+
+    def enable_tp_peer(self, on: bool = True):
+        self.ctx.check(lib().b200_gpt2_tp_peer_enable(self._h, int(on)), "tp_peer_enable")
 
     def params_ptr(self) -> int:
         return int(lib().b200_gpt2_params(self._h))

@@ -530,7 +530,7 @@ int b200_gpt2_tp_peer_export(b200_gpt2* m, unsigned char* handles) {
 int b200_gpt2_tp_peer_connect(b200_gpt2* m, const unsigned char* peer_handles) {
     if (!m || !peer_handles) return B200_ERR_NULL;
     if (m->tp_size != 2 || !m->peer_word) { m->ctx->last_error = "b200_gpt2_tp_peer_export comes first"; return B200_ERR_STATE; }
-    if (m->peer_on) { m->ctx->last_error = "the model is connected to its peer already"; return B200_ERR_STATE; }
+    if (m->peer_word_remote) { m->ctx->last_error = "the model is connected to its peer already"; return B200_ERR_STATE; }
     b200_ctx* ctx = m->ctx;
     b200_device_guard guard(ctx);
     cudaIpcMemHandle_t h;
@@ -546,6 +546,13 @@ int b200_gpt2_tp_peer_connect(b200_gpt2* m, const unsigned char* peer_handles) {
     m->peer_maps_rows = 0;
     m->peer_epoch = 0;
     m->peer_on = true;
+    return B200_OK;
+}
+
+int b200_gpt2_tp_peer_enable(b200_gpt2* m, int on) {
+    if (!m) return B200_ERR_NULL;
+    if (on && !m->peer_word_remote) { m->ctx->last_error = "not connected to a peer"; return B200_ERR_STATE; }
+    m->peer_on = on != 0;
     return B200_OK;
 }
 

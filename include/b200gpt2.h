@@ -400,6 +400,9 @@ int b200_gpt2_set_tp_overlap(b200_gpt2* model, int chunks, int reserve_sms);
  * and connected anew.  connect is called once per model. */
 int b200_gpt2_tp_peer_export(b200_gpt2* model, unsigned char* handles /* [192] */);
 int b200_gpt2_tp_peer_connect(b200_gpt2* model, const unsigned char* peer_handles /* [192] */);
+/* Switches the hand-over off (the all-reduce callback is used again) or back on; like every change of
+ * the exchange, on both ranks between the same two forwards. */
+int b200_gpt2_tp_peer_enable(b200_gpt2* model, int on);
 size_t b200_gpt2_param_offsets_tp(const b200_gpt2_config* cfg, int tp_size, int tp_rank, size_t* offsets);
 int b200_gpt2_shard_params_host(const b200_gpt2_config* cfg, int tp_size, int tp_rank,
                                 const float* full_params, float* local_params);

@@ -142,6 +142,13 @@ for _ in range(3):
 # another shape (the hand-over's tensor maps follow the row count)
 l2 = model.forward(d_tok[:1, :64].contiguous(), 1, 64); ctx.sync_check()
 assert torch.equal(l2[0], nccl_logits[0, :64]) or float((l2[0] - nccl_logits[0, :64]).abs().max()) < 2e-3
+# off (the all-reduce callback again) and on again: same bits every way
+model.enable_tp_peer(False)
+logits = model.forward(d_tok, 2, 128); ctx.sync_check()
+assert torch.equal(logits, nccl_logits)
+model.enable_tp_peer(True)
+logits = model.forward(d_tok, 2, 128); ctx.sync_check()
+assert torch.equal(logits, nccl_logits)
 dist.barrier()
 if r == 0:
     print("TP_PEER_OK")
