@@ -53,6 +53,10 @@ struct GemmArgs {
     // two-plane output: the plane of the dropped parts is only written for columns >= lo_col0 (the fp16 attention
     // reads q and k from their hi planes alone: their lo planes need neither be formed nor stored)
     int lo_col0 = 0;
+    // CTA-pair kernel, tail of the tile sequence: the tiles from number n_main on - what is left over after
+    // the last full round of the resident pairs - are each computed as tail_sub tiles of tile_w / tail_sub
+    // columns, so that the partly empty last round costs a fraction of a tile's time (1: off)
+    int tail_sub = 1, n_main = 0;
 };
 
 // Arg-max keys: the value as an order-preserving 32-bit integer in the high half, the inverted
