@@ -433,12 +433,13 @@ int launch_decode_encoder(b200_ctx* ctx, float* out, const int* tok, const float
 // batches leave most SMs idle: as many as fit in one wave, at most 4, each at least 256 floats of K
 // in whole steps of 128.  The caller hands the same number to the consumer as branch_parts.
 int skinny_gemm_k_splits(const b200_ctx* ctx, int K, int N) {
-    // tuning hook: B200_DECODE_KSPLIT=1 switches the slices off
+    // tuning hook: B200_DECODE_KSPLIT=1 switches the slices off, 2-4 caps their number
     static const int forced = [] { const char* e = getenv("B200_DECODE_KSPLIT"); return e ? atoi(e) : 0; }();
     if (forced == 1) return 1;
+    const int cap = (forced >= 2 && forced <= 4) ? forced : 4;
     const int batches = ((N + 1) / 2 + 7) / 8;
     int ks = ctx->num_sms / (batches > 0 ? batches : 1);
-    if (ks > 4) ks = 4;
+    if (ks > cap) ks = cap;
     while (ks > 1 && (K % (128 * ks) || K / ks < 256)) --ks;
     return ks < 1 ? 1 : ks;
 }
