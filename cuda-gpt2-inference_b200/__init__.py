@@ -34,6 +34,7 @@ EXPORTS = (
     "b200_ctx_last_error", "b200_ctx_wait_timeout_probe", "b200_ctx_peer_wait_probe",
     "b200_matmul_forward", "b200_matmul_forward_bf16", "b200_convert_bf16", "b200_matmul_forward_bf16x3", "b200_split_bf16",
     "b200_matmul_forward_fp8", "b200_quantize_e4m3", "b200_gpt2_tp_peer_export", "b200_gpt2_tp_peer_connect", "b200_gpt2_tp_peer_enable",
+    "b200_gpt2_tp_sp_export", "b200_gpt2_tp_sp_connect", "b200_gpt2_tp_sp_enable",
     "b200_gpt2_set_attention_mode", "b200_attention_forward", "b200_attention_forward_x3", "b200_attention_forward_fp16", "b200_split_fp16", "b200_layernorm_forward",
     "b200_fused_residual_layernorm_forward", "b200_residual_forward", "b200_gelu_forward",
     "b200_encoder_forward",
@@ -113,6 +114,9 @@ def lib() -> C.CDLL:
         l.b200_gpt2_tp_peer_export.argtypes = [vp, vp]
         l.b200_gpt2_tp_peer_connect.argtypes = [vp, vp]
         l.b200_gpt2_tp_peer_enable.argtypes = [vp, i]
+        l.b200_gpt2_tp_sp_export.argtypes = [vp, vp]
+        l.b200_gpt2_tp_sp_connect.argtypes = [vp, vp]
+        l.b200_gpt2_tp_sp_enable.argtypes = [vp, i]
         l.b200_gpt2_set_attention_mode.argtypes = [vp, i]
         l.b200_attention_forward.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
         l.b200_attention_forward_x3.argtypes = [vp, vp, vp, vp, vp, i, i, i, i]
@@ -501,6 +505,40 @@ class GPT2:
             if st == 0:
                 lib().b200_gpt2_tp_peer_enable(self._h, 0)
             raise B200Error(f"tp_peer_connect failed on a rank (here: {st}, {lib().b200_ctx_last_error(self.ctx._h).decode()})")
+
+    def connect_tp_sequence_parallel(self, group=None):
+        """The sequence-parallel hand-over for groups of 2 to 8 ranks (b200_gpt2_tp_sp_*): exchanges the
+        CUDA IPC handles of all ranks through torch.distributed and switches it on.  Collective; either
+        every rank ends up connected or every rank raises."""
+        import torch
+        import torch.distributed as dist
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        if world != self.tp_size:
+            raise B200Error("the group is not the model's tensor-parallel group")
+        dev = f"cuda:{self.ctx.device}"
+
+        def everyone(ok: bool) -> bool:
+            t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN, group=group)
+            return bool(t.item())
+
+        mine = (C.c_ubyte * 192)()
+        st = lib().b200_gpt2_tp_sp_export(self._h, mine)
+        if not everyone(st == 0):
+            raise B200Error(f"tp_sp_export failed on a rank (here: {st}, {lib().b200_ctx_last_error(self.ctx._h).decode()})")
+        t = torch.tensor(list(bytes(mine)), dtype=torch.uint8, device=dev)
+        parts = [torch.empty_like(t) for _ in range(world)]
+        dist.all_gather(parts, t, group=group)
+        blob = b"".join(p.cpu().numpy().tobytes() for p in parts)
+        every = (C.c_ubyte * (192 * world)).from_buffer_copy(blob)
+        st = lib().b200_gpt2_tp_sp_connect(self._h, every)
+        if not everyone(st == 0):
+            if st == 0:
+                lib().b200_gpt2_tp_sp_enable(self._h, 0)
+            raise B200Error(f"tp_sp_connect failed on a rank (here: {st}, {lib().b200_ctx_last_error(self.ctx._h).decode()})")
+
+    def enable_tp_sequence_parallel(self, on: bool = True):
+        self.ctx.check(lib().b200_gpt2_tp_sp_enable(self._h, int(on)), "tp_sp_enable")
 
     def enable_tp_peer(self, on: bool = True):
         self.ctx.check(lib().b200_gpt2_tp_peer_enable(self._h, int(on)), "tp_peer_enable")

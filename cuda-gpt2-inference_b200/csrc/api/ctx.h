@@ -43,6 +43,7 @@ struct b200_ctx {
     // one-shot: device address of a CUtensorMap; the next fp32 plain-store GEMM launch on this context also stores
     // its output tiles through it (into a peer GPU's memory) and clears the field
     const void* next_gemm_out2 = nullptr;
+    int next_gemm_out2_rows = 0;  // > 0 with it: an array of maps by owner of that many rows, and the only store (GemmArgs::out2_rows)
     size_t split_flag_words = 0;
     uint64_t launches = 0;
     bool pdl = true;  // launch with programmatic stream serialization (B200_PDL=0 turns it off)

@@ -90,6 +90,21 @@ struct b200_gpt2 {
     int peer_maps_rows = 0;
     unsigned int peer_epoch = 0;
     bool peer_on = false;
+    // Sequence-parallel hand-over for any group size (b200_gpt2_tp_sp_*): rank r owns rows [r, r+1) * M / n of
+    // the residual stream.  A projection GEMM stores every tile of its partial sum only to the owner of the
+    // tile's rows (into the slot of the source rank; TMA stores over NVLink under the GEMM), the owner's
+    // layernorm adds the n partial sums for its rows and writes the normalised rows into every rank's
+    // layernorm output, and two epoch words per peer order it all: per projection each rank sends
+    // (n-1)/n of the activation twice, like an all-reduce, the first half hidden under the GEMM.
+    bool sp_on = false;
+    float* sp_recv = nullptr;                 // local [2 (epoch parity)][max_B * max_T * C]: [source rank][own rows][C]
+    unsigned int* sp_words = nullptr;         // local: [s] projections completed by rank s, [16 + s] layernorms completed by rank s
+    float* sp_recv_peer[8] = {};              // the peers' sp_recv / layernorm output / words, mapped (own entries unused)
+    float* sp_ln_peer[8] = {};
+    unsigned int* sp_words_peer[8] = {};
+    CUtensorMap* sp_maps = nullptr;           // device [2][8]: by parity and owner, over the owner's slot for this rank
+    int sp_maps_rows = 0;
+    unsigned int sp_epoch = 0;
     std::map<std::pair<std::pair<int, int>, int>, cudaGraphExec_t> graphs;  // by (B, T, results)
     // per-operator timing (b200_gpt2_set_profile): one event pair per kernel launch
     bool profile = false;
@@ -264,6 +279,51 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         }
     }
     unsigned int peer_e = 0;
+    // the sequence-parallel hand-over (see the model's sp_* fields): rows in whole 256-row tiles per rank
+    const int spn = m->tp_size;
+    const bool sp = m->sp_on && spn > 1 && !peer && ((g_tf32 && m->gemm_mode == B200_TF32) || hx) && tpc == 1 && M % (spn * 256) == 0;
+    if (m->sp_on && spn > 1 && !sp && !m->allreduce) { ctx->last_error = "the hand-over needs B*T to be a multiple of 256 * tp_size (or an all-reduce to fall back on)"; return B200_ERR_SHAPE; }
+    const int sp_rows = sp ? M / spn : 0;
+    const size_t sp_par_stride = (size_t)m->max_B * m->max_T * C;  // floats between the two parity halves of a receive buffer
+    unsigned int* sp_sig1[8] = {};
+    unsigned int* sp_sig2[8] = {};
+    float* sp_dst[8] = {};
+    if (sp) {
+        for (int p = 0; p < spn; ++p) {
+            sp_dst[p] = p == m->tp_rank ? m->ln_out : m->sp_ln_peer[p];
+            if (p == m->tp_rank) continue;
+            sp_sig1[p] = m->sp_words_peer[p] + m->tp_rank;
+            sp_sig2[p] = m->sp_words_peer[p] + 16 + m->tp_rank;
+        }
+        if (m->sp_maps_rows != M) {
+            CUtensorMap host_maps[16];
+            for (int par = 0; par < 2; ++par)
+                for (int o = 0; o < 8; ++o) {
+                    const int oo = o < spn ? o : 0;
+                    float* base = (oo == m->tp_rank ? m->sp_recv : m->sp_recv_peer[oo]) + par * sp_par_stride + (size_t)m->tp_rank * sp_rows * C;
+                    st = b200_get_tensor_map(ctx, &host_maps[par * 8 + o], base, (uint64_t)sp_rows, (uint64_t)C, (uint64_t)C, 32, 32);
+                    if (st != B200_OK) return st;
+                }
+            B200_CUDA(ctx, cudaMemcpyAsync(m->sp_maps, host_maps, sizeof(host_maps), cudaMemcpyHostToDevice, ctx->stream));
+            m->sp_maps_rows = M;
+        }
+    }
+    unsigned int sp_e = 0;
+    // what follows a projection in this mode: tell the peers, wait for theirs, normalise the own rows into
+    // every rank's layernorm output, tell the peers, wait for theirs
+#define SP_AFTER_PROJECTION(lnw, lnb, lnflags)                                                                                          \
+    do {                                                                                                                                \
+        STEP(B200_PROF_ALLREDUCE, launch_peer_signal_many(ctx, sp_sig1, spn, sp_e));                                                    \
+        STEP(B200_PROF_ALLREDUCE, launch_peer_wait_many(ctx, m->sp_words, spn, m->tp_rank, sp_e));                                      \
+        STEP(B200_PROF_FUSED_RES_LN, launch_layernorm_sp(ctx, m->residual, m->sp_recv + (sp_e & 1) * sp_par_stride, sp_dst, spn, sp_rows, \
+                                                         m->tp_rank * sp_rows, (lnw), (lnb), M, C, (lnflags)));                         \
+        STEP(B200_PROF_ALLREDUCE, launch_peer_signal_many(ctx, sp_sig2, spn, sp_e));                                                    \
+        STEP(B200_PROF_ALLREDUCE, launch_peer_wait_many(ctx, m->sp_words + 16, spn, m->tp_rank, sp_e));                                 \
+    } while (0)
+#define SP_BEFORE_PROJECTION()                                                                                  \
+    do {                                                                                                        \
+        if (sp) { sp_e = ++m->sp_epoch; ctx->next_gemm_out2 = m->sp_maps + (sp_e & 1) * 8; ctx->next_gemm_out2_rows = sp_rows; } \
+    } while (0)
 #define STEP(cat, call)                                             \
     do {                                                            \
         if (prof) { st = prof_begin(m, (cat)); if (st != B200_OK) return st; } \
@@ -323,12 +383,14 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         float* proj_out = accum ? m->residual : m->branch;
         if (hx) {
             if (peer) { peer_e = ++m->peer_epoch; ctx->next_gemm_out2 = m->peer_maps + (peer_e & 1); }
+            SP_BEFORE_PROJECTION();
             STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, atty_h, PH + o_apw, PL + o_apw, apb, M, A, C, accum));
         }
         else if (hb) STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_bf16(ctx, proj_out, nullptr, atty_h, PH + o_apw, apb, M, A, C, accum));
         else if (tpc > 1) STEP(B200_PROF_GEMM_ATTPROJ, tp_projection_overlapped(m, proj_out, m->atty, W + o_apw, apb, M, A, C, tpc));
         else {
             if (peer) { peer_e = ++m->peer_epoch; ctx->next_gemm_out2 = m->peer_maps + (peer_e & 1); }
+            SP_BEFORE_PROJECTION();
             STEP(B200_PROF_GEMM_ATTPROJ, launch_gemm_tf32(ctx, proj_out, m->atty, W + o_apw, apb, nullptr, M, A, C, accum, m->gemm_mode));
         }
         if (accum) {
@@ -336,16 +398,21 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         } else {
             // tensor parallel: every rank holds a partial sum over its heads; one all-reduce per block
             // (already issued, chunk by chunk, when the projection ran overlapped)
-            if (peer) {
-                STEP(B200_PROF_ALLREDUCE, launch_peer_signal(ctx, m->peer_word_remote, peer_e));
-                STEP(B200_PROF_ALLREDUCE, launch_peer_wait(ctx, m->peer_word, peer_e));
-            } else if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
-            STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
-                                                 m->branch, ln2w, ln2b, M, C, ln_flags, peer ? m->peer_in[peer_e & 1] : nullptr));
+            if (sp) {
+                SP_AFTER_PROJECTION(ln2w, ln2b, ln_flags);
+            } else {
+                if (peer) {
+                    STEP(B200_PROF_ALLREDUCE, launch_peer_signal(ctx, m->peer_word_remote, peer_e));
+                    STEP(B200_PROF_ALLREDUCE, launch_peer_wait(ctx, m->peer_word, peer_e));
+                } else if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
+                STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
+                                                     m->branch, ln2w, ln2b, M, C, ln_flags, peer ? m->peer_in[peer_e & 1] : nullptr));
+            }
         }
         if (hx) {
             STEP(B200_PROF_GEMM_FC, launch_gemm_bf16x3(ctx, nullptr, fch_h, ln_h, PH + o_fcw, PL + o_fcw, fcb, M, C, F, GEMM_GELU));
             if (peer) { peer_e = ++m->peer_epoch; ctx->next_gemm_out2 = m->peer_maps + (peer_e & 1); }
+            SP_BEFORE_PROJECTION();
             STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_bf16x3(ctx, proj_out, nullptr, fch_h, PH + o_fpw, PL + o_fpw, fpb, M, F, C, accum));
         } else if (hb) {
             STEP(B200_PROF_GEMM_FC, launch_gemm_bf16(ctx, nullptr, fch_h, ln_h, PH + o_fcw, fcb, M, C, F, GEMM_GELU));
@@ -355,6 +422,7 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
             if (tpc > 1) STEP(B200_PROF_GEMM_FCPROJ, tp_projection_overlapped(m, proj_out, m->fch, W + o_fpw, fpb, M, F, C, tpc));
             else {
                 if (peer) { peer_e = ++m->peer_epoch; ctx->next_gemm_out2 = m->peer_maps + (peer_e & 1); }
+                SP_BEFORE_PROJECTION();
                 STEP(B200_PROF_GEMM_FCPROJ, launch_gemm_tf32(ctx, proj_out, m->fch, W + o_fpw, fpb, nullptr, M, F, C, accum, m->gemm_mode));
             }
         }
@@ -365,12 +433,16 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         if (accum) {
             STEP(B200_PROF_LAYERNORM, launch_layernorm(ctx, m->ln_out, nullptr, nullptr, m->residual, nw, nb, M, C, next_flags));
         } else {
-            if (peer) {
-                STEP(B200_PROF_ALLREDUCE, launch_peer_signal(ctx, m->peer_word_remote, peer_e));
-                STEP(B200_PROF_ALLREDUCE, launch_peer_wait(ctx, m->peer_word, peer_e));
-            } else if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
-            STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
-                                                 m->branch, nw, nb, M, C, next_flags, peer ? m->peer_in[peer_e & 1] : nullptr));
+            if (sp) {
+                SP_AFTER_PROJECTION(nw, nb, next_flags);
+            } else {
+                if (peer) {
+                    STEP(B200_PROF_ALLREDUCE, launch_peer_signal(ctx, m->peer_word_remote, peer_e));
+                    STEP(B200_PROF_ALLREDUCE, launch_peer_wait(ctx, m->peer_word, peer_e));
+                } else if (m->tp_size > 1 && tpc == 1) STEP(B200_PROF_ALLREDUCE, tp_allreduce(m, m->branch, (size_t)M * C));
+                STEP(B200_PROF_FUSED_RES_LN, launch_fused_residual_layernorm(ctx, m->residual, m->ln_out, nullptr, nullptr, m->residual,
+                                                     m->branch, nw, nb, M, C, next_flags, peer ? m->peer_in[peer_e & 1] : nullptr));
+            }
         }
     }
     const size_t o_head = off[0] + (size_t)m->vp_row0 * C;
@@ -390,6 +462,8 @@ int enqueue_forward(b200_gpt2* m, const int* tokens, int B, int T, int results) 
         if (st != B200_OK) return st;
     }
 #undef STEP
+#undef SP_AFTER_PROJECTION
+#undef SP_BEFORE_PROJECTION
     return B200_OK;
 }
 
@@ -556,6 +630,63 @@ int b200_gpt2_tp_peer_enable(b200_gpt2* m, int on) {
     return B200_OK;
 }
 
+// ---- sequence-parallel hand-over for a tensor-parallel group of 2..8 ranks ---------------------------
+int b200_gpt2_tp_sp_export(b200_gpt2* m, unsigned char* handles) {
+    if (!m || !handles) return B200_ERR_NULL;
+    if (m->tp_size < 2 || m->tp_size > 8) { m->ctx->last_error = "the hand-over is for tensor-parallel groups of 2 to 8"; return B200_ERR_STATE; }
+    b200_ctx* ctx = m->ctx;
+    b200_device_guard guard(ctx);
+    const size_t bytes = (size_t)2 * m->max_B * m->max_T * m->cfg.channels * sizeof(float);
+    if (!m->sp_recv) B200_CUDA(ctx, cudaMalloc(&m->sp_recv, bytes));
+    if (!m->sp_words) {
+        B200_CUDA(ctx, cudaMalloc(&m->sp_words, 256));
+        B200_CUDA(ctx, cudaMemset(m->sp_words, 0, 256));
+    }
+    if (!m->sp_maps) B200_CUDA(ctx, cudaMalloc(&m->sp_maps, 16 * sizeof(CUtensorMap)));
+    cudaIpcMemHandle_t h;
+    B200_CUDA(ctx, cudaIpcGetMemHandle(&h, m->sp_recv)); memcpy(handles, &h, 64);
+    B200_CUDA(ctx, cudaIpcGetMemHandle(&h, m->ln_out)); memcpy(handles + 64, &h, 64);
+    B200_CUDA(ctx, cudaIpcGetMemHandle(&h, m->sp_words)); memcpy(handles + 128, &h, 64);
+    return B200_OK;
+}
+
+int b200_gpt2_tp_sp_connect(b200_gpt2* m, const unsigned char* all_handles) {
+    if (!m || !all_handles) return B200_ERR_NULL;
+    if (m->tp_size < 2 || m->tp_size > 8 || !m->sp_words) { m->ctx->last_error = "b200_gpt2_tp_sp_export comes first"; return B200_ERR_STATE; }
+    for (int p = 0; p < 8; ++p)
+        if (m->sp_words_peer[p]) { m->ctx->last_error = "the model is connected to its peers already"; return B200_ERR_STATE; }
+    b200_ctx* ctx = m->ctx;
+    b200_device_guard guard(ctx);
+    for (int p = 0; p < m->tp_size; ++p) {
+        if (p == m->tp_rank) continue;
+        cudaIpcMemHandle_t h;
+        void* q = nullptr;
+        memcpy(&h, all_handles + 192 * p, 64);
+        B200_CUDA(ctx, cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess));
+        m->sp_recv_peer[p] = static_cast<float*>(q);
+        memcpy(&h, all_handles + 192 * p + 64, 64);
+        B200_CUDA(ctx, cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess));
+        m->sp_ln_peer[p] = static_cast<float*>(q);
+        memcpy(&h, all_handles + 192 * p + 128, 64);
+        B200_CUDA(ctx, cudaIpcOpenMemHandle(&q, h, cudaIpcMemLazyEnablePeerAccess));
+        m->sp_words_peer[p] = static_cast<unsigned int*>(q);
+    }
+    m->sp_maps_rows = 0;
+    m->sp_epoch = 0;
+    m->sp_on = true;
+    m->peer_on = false;
+    return B200_OK;
+}
+
+int b200_gpt2_tp_sp_enable(b200_gpt2* m, int on) {
+    if (!m) return B200_ERR_NULL;
+    bool connected = false;
+    for (int p = 0; p < 8; ++p) connected = connected || m->sp_words_peer[p] != nullptr;
+    if (on && !connected) { m->ctx->last_error = "not connected to the peers"; return B200_ERR_STATE; }
+    m->sp_on = on != 0;
+    return B200_OK;
+}
+
 int b200_gpt2_set_allreduce(b200_gpt2* m, b200_allreduce_fn fn, void* user) {
     if (!m) return B200_ERR_NULL;
     m->allreduce = fn;
@@ -622,6 +753,14 @@ int b200_gpt2_destroy(b200_gpt2* m) {
     for (cudaEvent_t e : m->tp_ev) if (e) cudaEventDestroy(e);
     if (m->comm_stream) cudaStreamDestroy(m->comm_stream);
     for (float* q : m->peer_out) if (q) cudaIpcCloseMemHandle(q);
+    for (int i = 0; i < 8; ++i) {
+        if (m->sp_recv_peer[i]) cudaIpcCloseMemHandle(m->sp_recv_peer[i]);
+        if (m->sp_ln_peer[i]) cudaIpcCloseMemHandle(m->sp_ln_peer[i]);
+        if (m->sp_words_peer[i]) cudaIpcCloseMemHandle(m->sp_words_peer[i]);
+    }
+    if (m->sp_recv) cudaFree(m->sp_recv);
+    if (m->sp_words) cudaFree(m->sp_words);
+    if (m->sp_maps) cudaFree(m->sp_maps);
     if (m->peer_word_remote) cudaIpcCloseMemHandle(m->peer_word_remote);
     for (float* q : m->peer_in) if (q) cudaFree(q);
     if (m->peer_word) cudaFree(m->peer_word);
@@ -739,7 +878,7 @@ static int forward_impl(b200_gpt2* m, const int* tokens, int B, int T, int resul
         int st = prepare_weights(m);
         if (st != B200_OK) return st;
     }
-    if (m->tp_size > 1 && !m->allreduce) return B200_ERR_STATE;
+    if (m->tp_size > 1 && !m->allreduce && !m->peer_on && !m->sp_on) return B200_ERR_STATE;  // some way to sum over the group
     if (!m->use_graph || ctx->stream == nullptr || m->profile || m->tp_size > 1) return enqueue_forward(m, tokens, B, T, results);
 
     // CUDA-graph replay: the graph reads token ids from the model's own token buffer

@@ -50,6 +50,9 @@ struct GemmArgs {
     // not null: a tensor map in global memory (same shape and 32 x 32 box as the output's) through which every
     // tile of a plain-store fp32 epilogue is stored a second time - into a peer GPU's memory (tensor parallel)
     const CUtensorMap* tmap_out2 = nullptr;
+    // > 0: tmap_out2 is an array of maps, one per owner of out2_rows consecutive output rows (each over that owner's
+    // buffer of out2_rows rows); a tile is stored ONLY through the map of the owner of its rows, not through tmap_out
+    int out2_rows = 0;
     // two-plane output: the plane of the dropped parts is only written for columns >= lo_col0 (the fp16 attention
     // reads q and k from their hi planes alone: their lo planes need neither be formed nor stored)
     int lo_col0 = 0;
@@ -226,7 +229,7 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
     const bool do_lse = do_argmax && args.lse_part != nullptr;
     float lse_m = -INFINITY, lse_s = 0.f;  // running maximum and sum of exp(value - maximum) of this thread's columns
     const bool via_tma = args.residual == nullptr;
-    if (args.tmap_out2 && lane == 0) tma_acquire_global_desc(args.tmap_out2);  // once per tile and warp: cheap next to the tile
+    if (args.tmap_out2 && lane == 0 && row0 < args.M) tma_acquire_global_desc(args.tmap_out2 + (args.out2_rows > 0 ? row0 / args.out2_rows : 0));  // once per tile and warp: cheap next to the tile
     const bool skip_store = args.store_period > 0 && (row0 % args.store_period) < args.store_period - 32;
     if (via_tma) {  // the stores of the previous tile have left the staging buffers
         if (lane == 0) tma_store_wait_read();
@@ -316,9 +319,13 @@ __device__ __forceinline__ void gemm_drain_accumulator(const GemmArgs& args, con
             fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0 && cbase < args.N && row0 < args.M) {
-                if (args.flags & GEMM_ACCUM_OUT) tma_reduce_add_2d(tmap_out, cbase, row0, stage);
-                else tma_store_2d(tmap_out, cbase, row0, stage);
-                if (args.tmap_out2) tma_store_2d(args.tmap_out2, cbase, row0, stage);
+                if (args.out2_rows > 0) {
+                    tma_store_2d(args.tmap_out2 + row0 / args.out2_rows, cbase, row0 % args.out2_rows, stage);
+                } else {
+                    if (args.flags & GEMM_ACCUM_OUT) tma_reduce_add_2d(tmap_out, cbase, row0, stage);
+                    else tma_store_2d(tmap_out, cbase, row0, stage);
+                    if (args.tmap_out2) tma_store_2d(args.tmap_out2, cbase, row0, stage);
+                }
                 tma_store_commit();
             }
             continue;

@@ -350,6 +350,8 @@ int launch_gemm_any(b200_ctx* ctx, float* out, uint16_t* out_h, const void* inp,
     a.split_flags = nullptr;
     a.tmap_out2 = static_cast<const CUtensorMap*>(ctx->next_gemm_out2);
     ctx->next_gemm_out2 = nullptr;
+    a.out2_rows = a.tmap_out2 ? ctx->next_gemm_out2_rows : 0;
+    ctx->next_gemm_out2_rows = 0;
     if (a.tmap_out2 && (out_h || residual || (flags & GEMM_ACCUM_OUT) || store_period || x3)) {
         ctx->last_error = "a second output needs a plain fp32 store epilogue";
         return B200_ERR_STATE;

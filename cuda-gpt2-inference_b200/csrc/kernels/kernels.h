@@ -20,6 +20,11 @@ int launch_fused_residual_layernorm(b200_ctx* ctx, float* res_out, float* ln_out
 // hand-over words between two GPUs (peer-mapped memory): see rowwise.cu
 int launch_peer_signal(b200_ctx* ctx, unsigned int* peer_word, unsigned int value);
 int launch_peer_wait(b200_ctx* ctx, const unsigned int* my_word, unsigned int value, unsigned long long limit_ns = 0);  // 0: the 2 s of every device-side wait
+int launch_peer_signal_many(b200_ctx* ctx, unsigned int* const* peer_words, int n, unsigned int value);  // null entries are skipped
+int launch_peer_wait_many(b200_ctx* ctx, const unsigned int* my_words, int n, int skip, unsigned int value);  // words 0..n-1 but `skip`
+// layernorm of this rank's rows over the sum of n partial sums, written to every rank's output (rowwise.cu: LnSpArgs)
+int launch_layernorm_sp(b200_ctx* ctx, float* residual, const float* parts, float* const* dst, int n, int rows, int row0,
+                        const float* weight, const float* bias, int M, int C, int flags);
 int launch_residual(b200_ctx* ctx, float* out, const float* a, const float* b, size_t N);
 int launch_gelu(b200_ctx* ctx, float* out, const float* inp, size_t N);
 int launch_encoder(b200_ctx* ctx, float* out, const int* tok, const float* wte, const float* wpe,

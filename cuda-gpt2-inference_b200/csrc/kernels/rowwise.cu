@@ -125,6 +125,104 @@ layernorm_rows_kernel(float* __restrict__ out, float* res_out, float* __restrict
     }
 }
 
+// Layernorm of a tensor-parallel rank's OWN rows (sequence-parallel hand-over, see driver/gpt2.cu):
+//   x = residual + (part[0] + part[1] + ... + part[n-1])      the n ranks' partial sums of a projection
+// for the `rows` rows from row0 on; x goes back to residual (this rank's rows only), and the
+// normalised row is written to the same place of EVERY rank's layernorm output (dst[0..n), peers'
+// memory included): as fp32 (TF32-rounded on request) or as two bf16 planes (OUT_BF16X2, the second
+// plane plane_stride elements further down).  One warp per row; NV float4 per lane.
+struct LnSpArgs {
+    float* residual;         // [M, C], local
+    const float* parts;      // [n][rows][C], local: what the ranks' GEMMs stored for these rows
+    float* dst[8];           // every rank's layernorm output buffer
+    const float* weight;
+    const float* bias;
+    int n, rows, row0, C, flags;
+    size_t plane_stride;     // elements between the two bf16 planes (M * C)
+};
+template <int NV>
+__global__ void __launch_bounds__(kRowWarps * 32)
+layernorm_sp_kernel(const LnSpArgs a) {
+    griddep_wait();
+    griddep_launch_dependents();
+    const int lane = threadIdx.x & 31;
+    const int rl = blockIdx.x * kRowWarps + (threadIdx.x >> 5);
+    if (rl >= a.rows) return;
+    const int C = a.C, C4 = C >> 2;
+    const size_t grow = (size_t)(a.row0 + rl) * C;
+    float4* res = reinterpret_cast<float4*>(a.residual + grow);
+    float4 v[NV], t[NV];
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        v[i] = t[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (c < C4) {
+            v[i] = res[c];
+            t[i] = reinterpret_cast<const float4*>(a.parts + (size_t)rl * C)[c];
+        }
+    }
+    for (int s = 1; s < a.n; ++s) {  // the partial sums in rank order: the same sum on every rank
+        const float4* ps = reinterpret_cast<const float4*>(a.parts + ((size_t)s * a.rows + rl) * C);
+#pragma unroll
+        for (int i = 0; i < NV; ++i) {
+            const int c = lane + i * 32;
+            if (c < C4) {
+                const float4 u = ps[c];
+                t[i].x += u.x; t[i].y += u.y; t[i].z += u.z; t[i].w += u.w;
+            }
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        v[i].x += t[i].x; v[i].y += t[i].y; v[i].z += t[i].z; v[i].w += t[i].w;
+        if (c < C4) res[c] = v[i];
+    }
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) s += (v[i].x + v[i].y) + (v[i].z + v[i].w);
+    const float m = warp_sum(s) / (float)C;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        if (lane + i * 32 < C4) {
+            const float dx = v[i].x - m, dy = v[i].y - m, dz = v[i].z - m, dw = v[i].w - m;
+            q += (dx * dx + dy * dy) + (dz * dz + dw * dw);
+        }
+    }
+    const float r = rsqrtf(warp_sum(q) / (float)C + 1e-5f);
+    const float4* w4 = reinterpret_cast<const float4*>(a.weight);
+    const float4* b4 = reinterpret_cast<const float4*>(a.bias);
+    const bool rnd = (a.flags & ROUND_OUT_TF32) != 0;
+    const bool planes = (a.flags & OUT_BF16X2) != 0;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+        const int c = lane + i * 32;
+        if (c >= C4) continue;
+        const float4 w = __ldg(w4 + c), b = __ldg(b4 + c);
+        float4 y;
+        y.x = (v[i].x - m) * r * w.x + b.x;
+        y.y = (v[i].y - m) * r * w.y + b.y;
+        y.z = (v[i].z - m) * r * w.z + b.z;
+        y.w = (v[i].w - m) * r * w.w + b.w;
+        if (planes) {
+            const __nv_bfloat162 p0 = __floats2bfloat162_rn(y.x, y.y), p1 = __floats2bfloat162_rn(y.z, y.w);
+            const __nv_bfloat162 q0 = __floats2bfloat162_rn(y.x - __low2float(p0), y.y - __high2float(p0));
+            const __nv_bfloat162 q1 = __floats2bfloat162_rn(y.z - __low2float(p1), y.w - __high2float(p1));
+            const uint2 hi = make_uint2(*reinterpret_cast<const uint32_t*>(&p0), *reinterpret_cast<const uint32_t*>(&p1));
+            const uint2 lo = make_uint2(*reinterpret_cast<const uint32_t*>(&q0), *reinterpret_cast<const uint32_t*>(&q1));
+            for (int d = 0; d < a.n; ++d) {
+                uint2* oh = reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(a.dst[d]) + grow);
+                oh[c] = hi;
+                (oh + a.plane_stride / 4)[c] = lo;
+            }
+        } else {
+            if (rnd) { y.x = round_tf32(y.x); y.y = round_tf32(y.y); y.z = round_tf32(y.z); y.w = round_tf32(y.w); }
+            for (int d = 0; d < a.n; ++d) reinterpret_cast<float4*>(a.dst[d] + grow)[c] = y;
+        }
+    }
+}
+
 template <bool FUSED>
 int launch_ln_any(b200_ctx* ctx, float* out, float* res_out, float* mean, float* rstd,
                   const float* inp1, const float* inp2, const float* weight, const float* bias,
@@ -539,6 +637,63 @@ int launch_peer_wait(b200_ctx* ctx, const unsigned int* my_word, unsigned int va
     peer_wait_kernel<<<1, 1, 0, ctx->stream>>>(my_word, value, ctx->d_status, limit_ns ? limit_ns : kWaitLimitNs);
     ctx->launches++;
     B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+// the same hand-over words towards / from several peers at once (thread i serves peer i)
+struct PeerWords { unsigned int* w[8]; int n; };
+__global__ void peer_signal_many_kernel(const PeerWords p, unsigned int value) {
+    if ((int)threadIdx.x >= p.n || !p.w[threadIdx.x]) return;
+    __threadfence_system();
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.w[threadIdx.x]), "r"(value) : "memory");
+}
+__global__ void peer_wait_many_kernel(const unsigned int* words, int n, int skip, unsigned int value, int* status, unsigned long long limit_ns) {
+    if ((int)threadIdx.x >= n || (int)threadIdx.x == skip) return;
+    const uint64_t t0 = globaltimer_ns();
+    while (true) {
+        unsigned int v;
+        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(words + threadIdx.x) : "memory");
+        if ((int)(v - value) >= 0) return;
+        if (globaltimer_ns() - t0 > limit_ns) {
+            atomicCAS(status, 0, DEV_TIMEOUT_PEER);
+            return;
+        }
+        __nanosleep(200);
+    }
+}
+int launch_peer_signal_many(b200_ctx* ctx, unsigned int* const* peer_words, int n, unsigned int value) {
+    PeerWords p;
+    p.n = n;
+    for (int i = 0; i < 8; ++i) p.w[i] = i < n ? peer_words[i] : nullptr;
+    peer_signal_many_kernel<<<1, 32, 0, ctx->stream>>>(p, value);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+int launch_peer_wait_many(b200_ctx* ctx, const unsigned int* my_words, int n, int skip, unsigned int value) {
+    peer_wait_many_kernel<<<1, 32, 0, ctx->stream>>>(my_words, n, skip, value, ctx->d_status, kWaitLimitNs);
+    ctx->launches++;
+    B200_CUDA(ctx, cudaGetLastError());
+    return B200_OK;
+}
+
+int launch_layernorm_sp(b200_ctx* ctx, float* residual, const float* parts, float* const* dst, int n, int rows, int row0,
+                        const float* weight, const float* bias, int M, int C, int flags) {
+    if (n < 2 || n > 8 || C % 4 || rows < 1) return B200_ERR_SHAPE;
+    LnSpArgs a;
+    a.residual = residual; a.parts = parts; a.weight = weight; a.bias = bias;
+    a.n = n; a.rows = rows; a.row0 = row0; a.C = C; a.flags = flags;
+    a.plane_stride = (size_t)M * C;
+    for (int i = 0; i < 8; ++i) a.dst[i] = i < n ? dst[i] : nullptr;
+    const int nv = (C / 4 + 31) / 32;
+    const dim3 grid((rows + kRowWarps - 1) / kRowWarps), block(kRowWarps * 32);
+    cudaError_t le = cudaSuccess;
+    if (nv <= 6) le = launch_pdl(ctx, layernorm_sp_kernel<6>, grid, block, 0, a);
+    else if (nv <= 13) le = launch_pdl(ctx, layernorm_sp_kernel<13>, grid, block, 0, a);
+    else if (nv <= 32) le = launch_pdl(ctx, layernorm_sp_kernel<32>, grid, block, 0, a);
+    else return B200_ERR_LIMIT;
+    ctx->launches++;
+    B200_CUDA(ctx, le);
     return B200_OK;
 }
 

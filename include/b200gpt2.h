@@ -403,6 +403,23 @@ int b200_gpt2_tp_peer_connect(b200_gpt2* model, const unsigned char* peer_handle
 /* Switches the hand-over off (the all-reduce callback is used again) or back on; like every change of
  * the exchange, on both ranks between the same two forwards. */
 int b200_gpt2_tp_peer_enable(b200_gpt2* model, int on);
+
+/* The same idea for a tensor-parallel group of 2 to 8 ranks (one process per GPU, all GPUs peers over
+ * NVLink): a sequence-parallel hand-over.  Rank r owns the rows [r, r+1) * B*T / tp_size of the residual
+ * stream.  A projection GEMM stores every tile of its partial sum only into the memory of the rank
+ * that owns the tile's rows; that rank's layernorm adds the tp_size partial sums for its rows (in rank
+ * order: the same sum everywhere) and writes the normalised rows into the layernorm output of every
+ * rank; epoch words order the steps (waits of at most 2 s).  Per projection a rank sends
+ * (tp_size-1)/tp_size of the activation twice - what an all-reduce moves - but the first half
+ * travels under the GEMM and no reduction kernel runs.  B*T must be a multiple of 256 * tp_size
+ * (otherwise the forward falls back on the all-reduce callback, if one is set).
+ *   b200_gpt2_tp_sp_export   writes this rank's three CUDA IPC handles (3 x 64 bytes)
+ *   b200_gpt2_tp_sp_connect  takes the handles of ALL ranks, [tp_size][192] bytes in rank order (the own
+ *                            entry is ignored), and switches the hand-over on
+ *   b200_gpt2_tp_sp_enable   off / on again, on all ranks between the same two forwards */
+int b200_gpt2_tp_sp_export(b200_gpt2* model, unsigned char* handles /* [192] */);
+int b200_gpt2_tp_sp_connect(b200_gpt2* model, const unsigned char* all_handles /* [tp_size][192] */);
+int b200_gpt2_tp_sp_enable(b200_gpt2* model, int on);
 size_t b200_gpt2_param_offsets_tp(const b200_gpt2_config* cfg, int tp_size, int tp_rank, size_t* offsets);
 int b200_gpt2_shard_params_host(const b200_gpt2_config* cfg, int tp_size, int tp_rank,
                                 const float* full_params, float* local_params);

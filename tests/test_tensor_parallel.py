@@ -116,14 +116,14 @@ n = dist.get_world_size()
 kw = dict(max_seq_len=128, vocab_size=1000, padded_vocab_size=1024, num_layers=3, num_heads=5, channels=320)
 cfg, ocfg = pkg.GPT2Config(**kw), orc.GPT2Config(**kw)
 full = orc.init_params(ocfg, 21)
-tokens = orc.fill_tokens((2, 128), 22, vocab=cfg.vocab_size)
+tokens = orc.fill_tokens((4, 128), 22, vocab=cfg.vocab_size)
 stream = torch.cuda.Stream(); ctx = pkg.Context(r, stream)
-model = pkg.GPT2(ctx, cfg, 2, 128, tp_size=n, tp_rank=r)
+model = pkg.GPT2(ctx, cfg, 4, 128, tp_size=n, tp_rank=r)
 model.load_params(pkg.shard_params(cfg, n, r, full))
 model.set_allreduce_torch(stream)
 d_tok = torch.from_numpy(tokens).cuda(); torch.cuda.synchronize()
 for _ in range(2):
-    logits = model.forward(d_tok, 2, 128); ctx.sync_check()
+    logits = model.forward(d_tok, 4, 128); ctx.sync_check()
 parts = [torch.empty_like(logits) for _ in range(n)]
 dist.all_gather(parts, logits.contiguous())
 if r == 0:
@@ -137,24 +137,36 @@ if r == 0:
 nccl_logits = logits.clone()
 model.connect_tp_peer()
 for _ in range(3):
-    logits = model.forward(d_tok, 2, 128); ctx.sync_check()
+    logits = model.forward(d_tok, 4, 128); ctx.sync_check()
     assert torch.equal(logits, nccl_logits), float((logits - nccl_logits).abs().max())
 # another shape (the hand-over's tensor maps follow the row count)
 l2 = model.forward(d_tok[:1, :64].contiguous(), 1, 64); ctx.sync_check()
 assert torch.equal(l2[0], nccl_logits[0, :64]) or float((l2[0] - nccl_logits[0, :64]).abs().max()) < 2e-3
 # off (the all-reduce callback again) and on again: same bits every way
 model.enable_tp_peer(False)
-logits = model.forward(d_tok, 2, 128); ctx.sync_check()
+logits = model.forward(d_tok, 4, 128); ctx.sync_check()
 assert torch.equal(logits, nccl_logits)
 model.enable_tp_peer(True)
-logits = model.forward(d_tok, 2, 128); ctx.sync_check()
+logits = model.forward(d_tok, 4, 128); ctx.sync_check()
 assert torch.equal(logits, nccl_logits)
+# the sequence-parallel hand-over (each rank normalises its own half of the rows): for two ranks again
+# the all-reduce's bits.  The all-reduce callback is taken away first, so a silent fall-back would fail.
+model.connect_tp_sequence_parallel()
+import ctypes
+pkg.lib().b200_gpt2_set_allreduce(model._h, pkg.ALLREDUCE_FN(), None)
+for _ in range(3):
+    logits = model.forward(d_tok, 4, 128); ctx.sync_check()
+    assert torch.equal(logits, nccl_logits), float((logits - nccl_logits).abs().max())
+model.set_allreduce_torch(stream)
+dist.barrier()
+if r == 0:
+    print("TP_SP_OK")
 dist.barrier()
 if r == 0:
     print("TP_PEER_OK")
 # the default arithmetic of the unsharded model (split-bf16 GEMMs, fp16 attention) on the sharded one
 model.set_options(**pkg.MODES["bf16x3"])
-lx = model.forward(d_tok, 2, 128); ctx.sync_check()
+lx = model.forward(d_tok, 4, 128); ctx.sync_check()
 parts = [torch.empty_like(lx) for _ in range(n)]
 dist.all_gather(parts, lx.contiguous())
 if r == 0:
@@ -184,4 +196,5 @@ def test_tp_forward_two_gpus(tmp_path):
     assert out.returncode == 0, out.stdout[-3000:] + out.stderr[-3000:]
     assert "TP_GPU_OK" in out.stdout
     assert "TP_PEER_OK" in out.stdout
+    assert "TP_SP_OK" in out.stdout
     assert "TP_X3_OK" in out.stdout
