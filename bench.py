@@ -878,6 +878,38 @@ def _xl_and_multi_gpu(pkg, torch, dist, ctx, stream, world, rank, barrier, max_o
                         "adds the two partial sums; hand-over = the signal and wait kernels"}
         except Exception as e:  # noqa: BLE001
             out["tp_xl"]["peer_handover"] = {"error": str(e)}
+    # the sequence-parallel hand-over (any group size): tiles to the owner of their rows, layernorm on the own rows
+    try:
+        tpm.set_options(**pkg.MODES[pkg.DEFAULT_MODE_NAME])
+        tpm.connect_tp_sequence_parallel()
+        sp_logits = tpm.forward(tok8, 8, T)
+        ctx.sync_check()
+        sp_diff = (sp_logits - tp_logits).abs().max().reshape(1).to(torch.float64)
+        dist.all_reduce(sp_diff, op=dist.ReduceOp.MAX)
+        ms_sp = _time_steps(torch, tpm, ctx, stream, tok8, 8, T, 3, 1, barrier, max_over_ranks)
+        tpm.set_profile(True)
+        for _ in range(2):
+            tpm.forward(tok8, 8, T)
+        prof = tpm.read_profile()
+        tpm.set_profile(False)
+        tot = sum(v[0] for v in prof.values())
+        ser_ms, ar_ms = tot / 2, prof["allreduce"][0] / 2
+        tpm.set_options(**pkg.MODES["tf32"])
+        for _ in range(2):
+            tpm.forward(tok8, 8, T)
+        ctx.sync_check()
+        ms_sp_tf32 = _time_steps(torch, tpm, ctx, stream, tok8, 8, T, 3, 1, barrier, max_over_ranks)
+        out["tp_xl"]["sequence_parallel_handover"] = {
+            "value": 8 * T / (ms_sp * 1e-3), "unit": UNIT, "ms_per_step": ms_sp, "tf32_ms_per_step": ms_sp_tf32,
+            "max_abs_vs_allreduce_run": float(sp_diff.item()),
+            "ms_per_step_serialised": ser_ms, "handover_ms_per_step": ar_ms,
+            "exposed_handover_ms": max(0.0, ms_sp - (ser_ms - ar_ms)),
+            "exposed_handover_share": max(0.0, ms_sp - (ser_ms - ar_ms)) / ms_sp if ms_sp else None,
+            "note": "b200_gpt2_tp_sp_*: every projection tile is stored only to the rank that owns its rows (TMA stores over NVLink "
+                    "under the GEMM), that rank's layernorm adds the partial sums of its rows and writes the result into every rank's "
+                    "layernorm output; hand-over = the signal and wait kernels around it"}
+    except Exception as e:  # noqa: BLE001
+        out["tp_xl"]["sequence_parallel_handover"] = {"error": str(e)}
     tpm.close()
     xlm.close()
     return out
