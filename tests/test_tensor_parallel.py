@@ -87,6 +87,46 @@ if r == 0:
     err = np.abs(got - want).max()
     assert err < 2e-5, err
     print("TP_PLAN_OK", err)
+
+# The same forward with the sequence-parallel hand-over in place of the all-reduce (the plan of
+# b200_gpt2_tp_sp_*): rank s owns the rows [s, s+1) * M / n; every rank hands the owner its partial sum
+# for the owner's rows, the owner adds the n parts in rank order to its rows of the residual stream,
+# normalises them, and every rank gathers the normalised rows of all owners.
+M = tokens.size
+rows = M // n
+def handover(x_own, partial, w, b):
+    mine = [np.ascontiguousarray(partial.reshape(M, C)[s * rows:(s + 1) * rows]) for s in range(n)]
+    got = [None] * n
+    for s in range(n):  # (gloo has no all-to-all for numpy objects: one gather per owner)
+        box = [None] * n if s == r else None
+        dist.gather_object(mine[s], box, dst=s)
+        if s == r:
+            got = box
+    total = got[0].copy()
+    for s in range(1, n):
+        total += got[s]
+    x_new, ln_own, _, _ = orc.fused_residual_layernorm_forward(x_own[None], total[None], w, b)
+    every = [None] * n
+    dist.all_gather_object(every, ln_own[0])
+    return x_new[0], np.concatenate(every, axis=0).reshape(tokens.shape + (C,))
+x = orc.encoder_forward(tokens, P(0, (cfg.padded_vocab_size, C)), P(1, (cfg.max_seq_len, C)))
+ln, _, _ = orc.layernorm_forward(x, P(2, (L, C))[0], P(3, (L, C))[0])
+x_own = x.reshape(M, C)[r * rows:(r + 1) * rows].copy()
+for l in range(L):
+    qkv = orc.matmul_forward(ln, P(4, (L, 3 * A, C))[l], P(5, (L, 3 * A))[l])
+    att, _ = orc.attention_forward(qkv, nh)
+    x_own, ln = handover(x_own, orc.matmul_forward(att, P(6, (L, C, A))[l], P(7, (L, C))[l]), P(8, (L, C))[l], P(9, (L, C))[l])
+    fch = orc.matmul_forward(ln, P(10, (L, F, C))[l], P(11, (L, F))[l], act=1)
+    nw, nb = (P(2, (L, C))[l + 1], P(3, (L, C))[l + 1]) if l + 1 < L else (P(14, (C,)), P(15, (C,)))
+    x_own, ln = handover(x_own, orc.matmul_forward(fch, P(12, (L, C, F))[l], P(13, (L, C))[l]), nw, nb)
+mine = orc.matmul_forward(ln, P(0, (cfg.padded_vocab_size, C))[r * Vl:(r + 1) * Vl], None)
+parts = [None] * n
+dist.all_gather_object(parts, mine)
+if r == 0:
+    got = np.concatenate(parts, axis=-1)
+    err = np.abs(got - want).max()
+    assert err < 2e-5, err
+    print("TP_SP_PLAN_OK", err)
 dist.barrier(); dist.destroy_process_group()
 """
 
@@ -101,6 +141,7 @@ def test_tp_plan_two_gloo_ranks(tmp_path):
                          capture_output=True, text=True, timeout=300, env=dict(os.environ, OMP_NUM_THREADS="2"), cwd=ROOT)
     assert out.returncode == 0, out.stdout + out.stderr
     assert "TP_PLAN_OK" in out.stdout
+    assert "TP_SP_PLAN_OK" in out.stdout
 
 
 _GPU_RANK = r"""
