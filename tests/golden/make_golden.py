@@ -8,6 +8,8 @@ from a checkout of GJ0407790/CUDA-GPT2-Inference:
 
 Inputs are drawn with the oracle's seeded generator (oracle_fill_normal), stored alongside the
 reference outputs, and the CPU tests (tests/test_oracle_golden.py) check the oracle against them.
+A second file beside it, reference_kernels_sizes.npz, holds the cases at the real models' widths
+(see SIZES below): outputs and seeds only.
 Only kernels that compile and are correct by reading are used (see oracle/ref_harness.cu).
 """
 import ctypes as C
@@ -85,6 +87,64 @@ def main():
     check(ref.ref_flash_attention_permute_forward(p(out), p(dev(qkv)), B, T, Cc, NH), "attention")
     fx["att_qkv"], fx["att_out"], fx["att_nh"] = qkv, out.cpu().numpy(), np.int32(NH)
 
+    np.savez_compressed(out_path, **fx)
+    print("wrote", out_path, {k: v.shape for k, v in fx.items() if k.endswith("_out")})
+    record_sizes(ref, dev, p, check, os.path.join(os.path.dirname(out_path), "reference_kernels_sizes.npz"))
+
+
+# Second fixture: the same reference kernels at the widths and depths of the real models (K = 768, 1600,
+# 3072; C = 1600; T = 1024; several heads and sequences).  Only the outputs are stored; the inputs are
+# regenerated from the seeds in `meta` (the generator is counter-based and pinned by its own test), and a
+# float64 sum of every input is stored so that a drifted generator is told apart from a drifted oracle.
+SIZES = {
+    "mm_k3072": dict(kind="mm", B=1, T=64, C=3072, OC=64, seed=2001),
+    "mmtf32_k768_gelu": dict(kind="mmtf32", B=2, T=128, C=768, OC=256, gelu=1, seed=2011),
+    "mmtf32_k3072": dict(kind="mmtf32", B=1, T=128, C=3072, OC=128, gelu=0, seed=2021),
+    "mmtf32_k1600_gelu": dict(kind="mmtf32", B=1, T=128, C=1600, OC=128, gelu=1, seed=2031),
+    "ln_block_1600": dict(kind="ln_block", B=1, T=16, C=1600, seed=2041),
+    "ln_vec_1600": dict(kind="ln_vec", B=1, T=16, C=1600, seed=2051),
+    "att_b2_t256_nh3": dict(kind="att", B=2, T=256, NH=3, seed=2061),
+    "att_t1024_nh1": dict(kind="att", B=1, T=1024, NH=1, seed=2071),
+}
+
+
+def sizes_inputs(c):
+    """The inputs of one case of SIZES, from its seed (also used by tests/test_oracle_golden.py)."""
+    k, s = c["kind"], c["seed"]
+    if k in ("mm", "mmtf32"):
+        return dict(x=orc.fill_normal((c["B"], c["T"], c["C"]), s), w=orc.fill_normal((c["OC"], c["C"]), s + 1, std=0.02),
+                    bias=orc.fill_normal((c["OC"],), s + 2, std=0.05))
+    if k in ("ln_block", "ln_vec"):
+        return dict(x=orc.fill_normal((c["B"], c["T"], c["C"]), s, mean=-0.2, std=2.0),
+                    w=orc.fill_normal((c["C"],), s + 1, mean=1.0, std=0.2), b=orc.fill_normal((c["C"],), s + 2, std=0.2))
+    return dict(qkv=orc.fill_normal((c["B"], c["T"], 3 * 64 * c["NH"]), s))
+
+
+def record_sizes(ref, dev, p, check, out_path):
+    import json
+    fx = {"meta": np.array(json.dumps(SIZES))}
+    for tag, c in SIZES.items():
+        a = sizes_inputs(c)
+        for name, v in a.items():
+            fx[f"{tag}_sum_{name}"] = np.float64(v.astype(np.float64).sum())
+        k = c["kind"]
+        if k in ("mm", "mmtf32"):
+            out = torch.empty((c["B"], c["T"], c["OC"]), device="cuda")
+            if k == "mm":
+                check(ref.ref_matmul_forward_tiling(p(out), p(dev(a["x"])), p(dev(a["w"])), p(dev(a["bias"])), c["B"], c["T"], c["C"], c["OC"]), tag)
+            else:
+                check(ref.ref_matmul_forward_tf32_gelu(p(out), p(dev(a["x"])), p(dev(a["w"])), p(dev(a["bias"])), c["B"], c["T"], c["C"], c["OC"], c["gelu"]), tag)
+        elif k in ("ln_block", "ln_vec"):
+            fn = ref.ref_layernorm_forward_block if k == "ln_block" else ref.ref_layernorm_forward_block_vectorized
+            out = torch.empty((c["B"], c["T"], c["C"]), device="cuda")
+            mean, rstd = torch.empty((c["B"], c["T"]), device="cuda"), torch.empty((c["B"], c["T"]), device="cuda")
+            check(fn(p(out), p(mean), p(rstd), p(dev(a["x"])), p(dev(a["w"])), p(dev(a["b"])), c["B"], c["T"], c["C"]), tag)
+            fx[f"{tag}_mean"], fx[f"{tag}_rstd"] = mean.cpu().numpy(), rstd.cpu().numpy()
+        else:
+            Cc = 64 * c["NH"]
+            out = torch.empty((c["B"], c["T"], Cc), device="cuda")
+            check(ref.ref_flash_attention_permute_forward(p(out), p(dev(a["qkv"])), c["B"], c["T"], Cc, c["NH"]), tag)
+        fx[f"{tag}_out"] = out.cpu().numpy()
     np.savez_compressed(out_path, **fx)
     print("wrote", out_path, {k: v.shape for k, v in fx.items() if k.endswith("_out")})
 
