@@ -463,6 +463,7 @@ def test_split_bf16_matches_its_definition(ctx, dev, orc):
     (1, 64, 1600, 4800, True, 0, "plain"),      # XL width, M < 128
     (2, 1024, 768, 50304, False, 0, "plain"),   # lm-head width
     (8, 1024, 768, 3072, True, 1, "split"),     # the forward's GELU GEMM: 384 tiles on 74 pairs, left-over tiles in quarter width
+    (5, 1000, 768, 3072, True, 0, "plain"),     # 240 tiles: quarter-width left-over tiles again, ragged last row block, fp32 stores
 ])
 def test_matmul_bf16x3_close_to_fp32(ctx, dev, orc, B, T, C, OC, has_bias, act, mode):
     """Split-operand product (hi.hi + hi.lo + lo.hi on the bf16 pipe) against the fp64-accumulate
