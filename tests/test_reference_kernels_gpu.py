@@ -21,7 +21,6 @@ Bars, with the reason for each:
 import ctypes as C
 import os
 
-import numpy as np
 import pytest
 
 pytestmark = pytest.mark.gpu
