@@ -50,10 +50,11 @@ def _randn(shape, seed, std=1.0, mean=0.0):
     return t
 
 
-@pytest.mark.parametrize("K,N,gelu", [(768, 2304, 0), (768, 768, 0), (768, 3072, 1), (3072, 768, 0)])
+@pytest.mark.parametrize("K,N,gelu", [(768, 2304, 0), (768, 768, 0), (768, 3072, 1), (3072, 768, 0),
+                                       (768, 50304, 0), (1600, 6400, 1)])  # + the lm-head width and the XL GELU GEMM
 def test_matmul_equals_reference_tf32_kernel_at_8192_rows(ctx, ref, K, N, gelu):
     """kernels/matmul/9_matmul_async_cg_tf32_gelu.cuh:237-275 against b200_matmul_forward (single TF32 pass,
-    raw operands) on the four per-layer GEMM shapes."""
+    raw operands) on the four per-layer GEMM shapes, the lm-head's and one of GPT-2 XL's."""
     import torch
     x, w, bias = _randn((B, T, K), 1), _randn((N, K), 2, std=0.02), _randn((N,), 3, std=0.05)
     want = torch.empty((B, T, N), device="cuda")
