@@ -341,6 +341,14 @@ def _time_reference_gpu_kernels(torch, np):
     ms = timed(lambda: ref.ref_layernorm_forward_block_vectorized(p(o), p(mean), p(rstd), p(x), p(w), p(b), Bb, Tt, Cc))
     res["kernels"]["layernorm"] = {"kernel": "layernorm_forward_block_vectorized (kernels/layernorm/2_layernorm_block_vectorized.cuh)",
                                    "ms": round(ms, 4), "gbs": round((2.0 * M * Cc + 2 * M + 2 * Cc) * 4 / (ms * 1e-3) / 1e9, 1)}
+    # a forward made of these kernels (the reference leaves the driver to llm.c): twelve blocks of QKV, attention,
+    # projection, two layernorms, fc and fc-proj, then the final layernorm and the lm-head; its two residual adds
+    # per block and the encoder are left out, so this is a lower bound on the chain's time
+    k = {n: v["ms"] for n, v in res["kernels"].items()}
+    chain = 12 * (k["gemm_qkv"] + k["attention"] + k["gemm_attproj"] + 2 * k["layernorm"] + k["gemm_fc"] + k["gemm_fcproj"]) \
+        + k["layernorm"] + k["gemm_lmhead"]
+    res["forward_as_a_chain_of_these_kernels"] = {"ms_per_step": round(chain, 3), "tokens_per_s": round(M / (chain * 1e-3), 1),
+                                                  "note": "sum of the kernel times above for the 124M forward at B=8, T=1024 (residual adds and encoder not counted)"}
     return res
 
 
@@ -729,6 +737,9 @@ def run_ours(args):
         "decode": decode,
         "ref_gpu_kernels": ref_gpu,
     }
+    if isinstance(ref_gpu, dict) and "forward_as_a_chain_of_these_kernels" in ref_gpu:
+        # the GPU-vs-GPU figure for the whole step: this library's device-resident value over the reference kernels' chain
+        line["vs_reference_gpu_kernels_chain"] = round(value / ref_gpu["forward_as_a_chain_of_these_kernels"]["tokens_per_s"], 2)
     line.update(extras)
     print(json.dumps(line), flush=True)
     if model is not None:
