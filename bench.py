@@ -521,8 +521,8 @@ def run_ours(args):
     other = {}
     other_logits = {}
     if not tp:
-        for name in ("tf32", "bf16x3", "bf16x3_att_tf32", "bf16"):
-            if name == mode_name or (xl and name == "bf16x3_att_tf32"):
+        for name in ("tf32", "bf16x3", "bf16x3_att_tf32", "bf16x3_lm_tf32", "bf16"):
+            if name == mode_name or (xl and name in ("bf16x3_att_tf32", "bf16x3_lm_tf32")):
                 continue
             try:
                 model.set_options(**pkg.MODES[name])

@@ -55,6 +55,7 @@ MODES = {
     "tf32": dict(round_operands=1, gemm_mode=B200_TF32, lmhead_mode=B200_TF32, attention_mode=-1),
     "bf16x3": dict(round_operands=1, gemm_mode=B200_BF16X3, lmhead_mode=B200_BF16X3, attention_mode=-1),
     "bf16x3_att_tf32": dict(round_operands=1, gemm_mode=B200_BF16X3, lmhead_mode=B200_BF16X3, attention_mode=B200_TF32),
+    "bf16x3_lm_tf32": dict(round_operands=1, gemm_mode=B200_BF16X3, lmhead_mode=B200_TF32, attention_mode=-1),
     "tf32x3": dict(round_operands=0, gemm_mode=B200_TF32X3, lmhead_mode=B200_TF32X3, attention_mode=-1),
     "bf16": dict(round_operands=1, gemm_mode=B200_BF16, lmhead_mode=B200_BF16, attention_mode=-1),
 }
@@ -63,6 +64,7 @@ MODE_NOTES = {
     "bf16x3": "fp32 storage, GEMM operands split into two bf16 terms (16 significant bits), three kind::f16 products per K step, "
               "fp32 accumulation; attention on fp16 planes of q, k, v (q.k one product, p.v two)",
     "bf16x3_att_tf32": "bf16x3 GEMMs with the single-pass TF32 attention kernel",
+    "bf16x3_lm_tf32": "bf16x3 GEMMs and fp16 attention in the blocks, the lm-head as one TF32 pass on round-to-nearest operands",
     "tf32x3": "3xTF32 GEMMs and attention (three kind::tf32 products per K step)",
     "bf16": "bf16 GEMM operands (reduced precision; not comparable with the fp32-level modes)",
 }
