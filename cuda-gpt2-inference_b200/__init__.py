@@ -68,7 +68,7 @@ MODE_NOTES = {
     "tf32x3": "3xTF32 GEMMs and attention (three kind::tf32 products per K step)",
     "bf16": "bf16 GEMM operands (reduced precision; not comparable with the fp32-level modes)",
 }
-DEFAULT_MODE_NAME = "bf16x3"  # what b200_gpt2_create sets (a tensor-parallel model starts in "tf32")
+DEFAULT_MODE_NAME = "bf16x3"  # what b200_gpt2_create and b200_gpt2_create_tp set
 
 STATIC_MAX_TOKEN_CHANNELS = 196608  # B*T*C limit of b200_gpt2_forward_static
 
