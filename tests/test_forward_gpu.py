@@ -1,6 +1,6 @@
 """End-to-end parity of the gpt2_forward driver against the CPU oracle (GPU).
 
-Tolerances are the ones stated for the default TF32 path: logits within 2e-2 max-abs of the
+Tolerances are the ones stated for the default path: logits within 2e-2 max-abs of the
 fp32 forward and at least 99.9 % top-1 token agreement; the encoder output is bit-exact.
 """
 import numpy as np
